@@ -1,0 +1,1309 @@
+// CPU oracle for the OxiONNX dense-contraction hot path.  TEST INFRASTRUCTURE ONLY:
+// see oxi_oracle.h for the contract.  Each function names the reference file (path inside
+// the oxionnx project, v0.1.7) whose arithmetic it restates.
+#include "oxi_oracle.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+#include <string>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+thread_local std::string g_err;
+int g_threads = 1;
+int g_float_accum = 0;
+
+struct Fail {
+  int code;
+};
+
+[[noreturn]] void fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  throw Fail{code};
+}
+
+int64_t numel(const oxo_tensor& t) {
+  int64_t n = 1;
+  for (int i = 0; i < t.rank; ++i) n *= t.shape[i];
+  return n;
+}
+
+struct Attrs {
+  const oxo_attr* a;
+  int n;
+  const oxo_attr* find(const char* name, int kind) const {
+    for (int i = 0; i < n; ++i)
+      if (a[i].kind == kind && std::strcmp(a[i].name, name) == 0) return &a[i];
+    return nullptr;
+  }
+  int64_t i(const char* name, int64_t d) const {
+    auto* p = find(name, OXO_ATTR_INT);
+    return p ? p->i : d;
+  }
+  float f(const char* name, float d) const {
+    auto* p = find(name, OXO_ATTR_FLOAT);
+    return p ? p->f : d;
+  }
+  std::string s(const char* name) const {
+    auto* p = find(name, OXO_ATTR_STRING);
+    return p && p->s ? std::string(p->s) : std::string();
+  }
+  std::vector<int64_t> ints(const char* name) const {
+    auto* p = find(name, OXO_ATTR_INTS);
+    return p ? std::vector<int64_t>(p->ints, p->ints + p->len) : std::vector<int64_t>();
+  }
+};
+
+struct Ctx {
+  const char* op;
+  const oxo_tensor* in;
+  int n_in;
+  Attrs attrs;
+  oxo_tensor* out;
+  int n_out;
+  // required input (OpContext::input): missing -> TensorNotFound in the reference
+  const oxo_tensor& input(int idx) const {
+    if (idx >= n_in || !in[idx].present) fail(OXO_ERR_INVALID_MODEL, "%s: missing required input %d", op, idx);
+    return in[idx];
+  }
+  const oxo_tensor* optional(int idx) const {
+    if (idx >= n_in || !in[idx].present) return nullptr;
+    return &in[idx];
+  }
+};
+
+void alloc_out(oxo_tensor& t, const std::vector<int64_t>& shape) {
+  if ((int)shape.size() > OXO_MAX_RANK) fail(OXO_ERR_UNSUPPORTED, "rank %zu exceeds oracle limit", shape.size());
+  t.rank = (int)shape.size();
+  int64_t n = 1;
+  for (int i = 0; i < t.rank; ++i) {
+    t.shape[i] = shape[i];
+    n *= shape[i];
+  }
+  t.len = n;
+  t.present = 1;
+  t.data = (float*)std::calloc((size_t)std::max<int64_t>(n, 1), sizeof(float));
+  if (!t.data) fail(OXO_ERR_INTERNAL, "out of memory");
+}
+
+std::vector<int64_t> shape_of(const oxo_tensor& t) { return std::vector<int64_t>(t.shape, t.shape + t.rank); }
+
+// ---------------------------------------------------------------------------------------
+// Rounding and requantisation: oxionnx-ops/src/registry/quant_ops/mod.rs:51-70, 79-92,
+// 153-245.
+// ---------------------------------------------------------------------------------------
+double round_ties_even_f64(double v) {
+  if (!std::isfinite(v)) return v;
+  double fl = std::floor(v);
+  double diff = v - fl;
+  // rem_euclid(2.0) != 0  <=>  floor is odd
+  double rem = std::fmod(fl, 2.0);
+  if (rem < 0) rem += 2.0;
+  bool up = diff > 0.5 || (diff == 0.5 && rem != 0.0);
+  return up ? fl + 1.0 : fl;
+}
+float round_ties_even_f32_via64(float v) { return (float)round_ties_even_f64((double)v); }
+
+// oxionnx-ops/src/indexing/quantize.rs:14-32 (rounds directly in f32)
+float round_ties_even_f32_native(float v) {
+  if (!std::isfinite(v)) return v;
+  float fl = std::floor(v);
+  float diff = v - fl;
+  if (diff > 0.5f) return fl + 1.0f;
+  if (diff < 0.5f) return fl;
+  float rem = std::fmod(fl, 2.0f);
+  if (rem < 0) rem += 2.0f;
+  return rem == 0.0f ? fl : fl + 1.0f;
+}
+
+// lane_to_i32: quant_ops/mod.rs:79-92
+int32_t lane_to_i32(float v, const char* what) {
+  if (!std::isfinite(v)) fail(OXO_ERR_INVALID_MODEL, "%s: quantized tensor contains a non-finite value (%g)", what, (double)v);
+  float r = round_ties_even_f32_via64(v);
+  if (r < (float)INT32_MIN || r > (float)INT32_MAX)
+    fail(OXO_ERR_INVALID_MODEL, "%s: quantized value %g is outside the int32 range", what, (double)v);
+  // Rust `as i32` saturates; (float)INT32_MAX == 2^31 passes the check above and saturates.
+  if (r >= 2147483648.0f) return INT32_MAX;
+  return (int32_t)r;
+}
+
+std::vector<int32_t> tensor_to_i32(const oxo_tensor& t, const char* what) {
+  std::vector<int32_t> v((size_t)t.len);
+  for (int64_t i = 0; i < t.len; ++i) v[(size_t)i] = lane_to_i32(t.data[i], what);
+  return v;
+}
+
+// scalar_f32 / scale_input: quant_ops/mod.rs:98-118
+float scale_input(const oxo_tensor& t, const char* what) {
+  if (t.len < 1) fail(OXO_ERR_INVALID_MODEL, "%s: is empty", what);
+  float v = t.data[0];
+  if (!std::isfinite(v)) fail(OXO_ERR_INVALID_MODEL, "%s: scale must be finite, got %g", what, (double)v);
+  if (v == 0.0f) fail(OXO_ERR_INVALID_MODEL, "%s: scale is zero", what);
+  return v;
+}
+
+// zero_point_lanes: quant_ops/mod.rs:121-127
+std::vector<int32_t> zero_point_lanes(const oxo_tensor* zp, const char* what) {
+  if (!zp || zp->len == 0) return {0};
+  return tensor_to_i32(*zp, what);
+}
+
+struct SatRange {
+  int64_t lo, hi;
+};
+// SatRange::infer: quant_ops/mod.rs:190-200
+SatRange sat_infer(const std::vector<int32_t>& y_zp, const std::vector<int32_t>& x_zp) {
+  const std::vector<int32_t>* lanes[2] = {&y_zp, &x_zp};
+  for (auto* l : lanes) {
+    bool gt = false, lt = false;
+    for (int32_t v : *l) {
+      gt |= v > 127;
+    }
+    if (gt) return {0, 255};
+    for (int32_t v : *l) {
+      lt |= v < 0;
+    }
+    if (lt) return {-128, 127};
+  }
+  return {-128, 255};
+}
+
+// SatRange::requantize: quant_ops/mod.rs:229-233
+float requantize(int64_t acc, float combined, int32_t zp, SatRange r) {
+  volatile double prod = (double)acc * (double)combined;  // separately rounded multiply
+  double scaled = prod + (double)zp;
+  double rounded = round_ties_even_f64(scaled);
+  // f64::clamp: NaN stays NaN
+  if (rounded < (double)r.lo) rounded = (double)r.lo;
+  if (rounded > (double)r.hi) rounded = (double)r.hi;
+  return (float)rounded;
+}
+
+// saturate_i32: quant_ops/mod.rs:243-245
+float saturate_i32(int64_t acc) {
+  int64_t c = std::min<int64_t>(std::max<int64_t>(acc, INT32_MIN), INT32_MAX);
+  return (float)c;
+}
+
+void check_len(const oxo_tensor& t, const char* op, const char* which) {
+  if (t.len != numel(t)) fail(OXO_ERR_SHAPE_MISMATCH, "%s: %s data length %lld does not match shape", op, which, (long long)t.len);
+}
+
+// ---------------------------------------------------------------------------------------
+// QuantizeLinear / DequantizeLinear: oxionnx-ops/src/indexing/quantize.rs:58-193 and
+// oxionnx-ops/src/registry/indexing_ops.rs:204-238.
+// ---------------------------------------------------------------------------------------
+int64_t normalize_axis(int64_t axis, int64_t ndim, const char* op) {
+  int64_t a = axis < 0 ? axis + ndim : axis;
+  if (a < 0 || a >= ndim) fail(OXO_ERR_INVALID_MODEL, "%s: axis %lld out of range for rank %lld", op, (long long)axis, (long long)ndim);
+  return a;
+}
+
+struct ChannelIndexer {
+  int64_t inner = 1, dim = 1, len = 1;
+  int64_t at(int64_t flat) const { return len <= 1 ? 0 : (flat / inner) % dim; }
+};
+ChannelIndexer make_indexer(const oxo_tensor& x, int64_t axis, int64_t param_len) {
+  ChannelIndexer ci;
+  ci.len = param_len;
+  if (param_len > 1) {
+    int64_t inner = 1;
+    for (int d = (int)axis + 1; d < x.rank; ++d) inner *= x.shape[d];
+    ci.inner = std::max<int64_t>(inner, 1);
+    ci.dim = std::max<int64_t>(x.shape[axis], 1);
+  }
+  return ci;
+}
+
+void op_quantize_linear(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  const oxo_tensor& scale = c.input(1);
+  const oxo_tensor* zp = c.optional(2);
+  int64_t axis = c.attrs.i("axis", 1);
+  int64_t scale_len = scale.len;
+  if (scale_len == 0) fail(OXO_ERR_INVALID_MODEL, "quantize_linear: y_scale must have at least one element");
+  if (zp && zp->len == 0) fail(OXO_ERR_INVALID_MODEL, "quantize_linear: y_zero_point must have at least one element when provided");
+  int64_t zp_len = zp ? zp->len : 0;
+  int64_t plen = std::max(scale_len, zp_len);
+  int64_t ax = plen > 1 ? normalize_axis(axis, x.rank, "quantize_linear") : 0;
+  float lo = 0.0f, hi = 255.0f;  // saturation_range: quantize.rs:58-64
+  if (zp) {
+    bool any_gt = false;
+    for (int64_t i = 0; i < zp->len; ++i) any_gt |= zp->data[i] > 127.0f;
+    if (!any_gt) {
+      lo = -128.0f;
+      hi = 127.0f;
+    }
+  }
+  ChannelIndexer si = make_indexer(x, ax, scale_len), zi = make_indexer(x, ax, zp_len);
+  // channel_index reads past the parameter vector when its length disagrees with the axis
+  // extent; the reference would panic there, the oracle reports it instead.
+  if (scale_len > 1 && scale_len < si.dim) fail(OXO_ERR_SHAPE_MISMATCH, "quantize_linear: scale length %lld < axis extent %lld", (long long)scale_len, (long long)si.dim);
+  if (zp_len > 1 && zp_len < zi.dim) fail(OXO_ERR_SHAPE_MISMATCH, "quantize_linear: zero point length %lld < axis extent %lld", (long long)zp_len, (long long)zi.dim);
+  alloc_out(c.out[0], shape_of(x));
+  float* y = c.out[0].data;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t i = 0; i < x.len; ++i) {
+    float s = scale.data[si.at(i)];
+    float z = zp ? zp->data[zi.at(i)] : 0.0f;
+    volatile float q = x.data[i] / s;
+    float v = round_ties_even_f32_native(q) + z;
+    // f32::clamp keeps NaN
+    if (v < lo) v = lo;
+    if (v > hi) v = hi;
+    y[i] = v;
+  }
+}
+
+void op_dequantize_linear(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  const oxo_tensor& scale = c.input(1);
+  const oxo_tensor* zp = c.optional(2);
+  int64_t axis = c.attrs.i("axis", 1);
+  int64_t scale_len = scale.len;
+  if (scale_len == 0) fail(OXO_ERR_INVALID_MODEL, "dequantize_linear: x_scale must have at least one element");
+  if (zp && zp->len == 0) fail(OXO_ERR_INVALID_MODEL, "dequantize_linear: x_zero_point must have at least one element when provided");
+  int64_t zp_len = zp ? zp->len : 0;
+  int64_t plen = std::max(scale_len, zp_len);
+  int64_t ax = plen > 1 ? normalize_axis(axis, x.rank, "dequantize_linear") : 0;
+  ChannelIndexer si = make_indexer(x, ax, scale_len), zi = make_indexer(x, ax, zp_len);
+  if (scale_len > 1 && scale_len < si.dim) fail(OXO_ERR_SHAPE_MISMATCH, "dequantize_linear: scale length mismatch");
+  if (zp_len > 1 && zp_len < zi.dim) fail(OXO_ERR_SHAPE_MISMATCH, "dequantize_linear: zero point length mismatch");
+  alloc_out(c.out[0], shape_of(x));
+  float* y = c.out[0].data;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t i = 0; i < x.len; ++i) {
+    float s = scale.data[si.at(i)];
+    float z = zp ? zp->data[zi.at(i)] : 0.0f;
+    volatile float d = x.data[i] - z;  // subtract, then multiply: two roundings, no FMA
+    y[i] = d * s;
+  }
+}
+
+// DynamicQuantizeLinear: oxionnx-ops/src/registry/quant_ops/dynamic_quantize.rs:51-93
+void op_dynamic_quantize_linear(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  if (x.len == 0) fail(OXO_ERR_INVALID_MODEL, "DynamicQuantizeLinear: input is empty");
+  for (int64_t i = 0; i < x.len; ++i)
+    if (!std::isfinite(x.data[i])) fail(OXO_ERR_INVALID_MODEL, "DynamicQuantizeLinear: input contains a non-finite value (%g)", (double)x.data[i]);
+  float max_x = -std::numeric_limits<float>::infinity(), min_x = std::numeric_limits<float>::infinity();
+  for (int64_t i = 0; i < x.len; ++i) {
+    max_x = std::max(max_x, x.data[i]);
+    min_x = std::min(min_x, x.data[i]);
+  }
+  max_x = std::max(max_x, 0.0f);
+  min_x = std::min(min_x, 0.0f);
+  float span = (max_x == min_x) ? 1.0f : max_x - min_x;
+  volatile float y_scale = span / 255.0f;
+  volatile float izp = 0.0f - min_x / y_scale;
+  float cl = izp;
+  if (cl < 0.0f) cl = 0.0f;
+  if (cl > 255.0f) cl = 255.0f;
+  float y_zp = round_ties_even_f32_via64(cl);
+  alloc_out(c.out[0], shape_of(x));
+  float ys = y_scale;
+  float* y = c.out[0].data;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t i = 0; i < x.len; ++i) {
+    volatile float q = x.data[i] / ys;
+    float v = round_ties_even_f32_via64(q) + y_zp;
+    if (v < 0.0f) v = 0.0f;
+    if (v > 255.0f) v = 255.0f;
+    y[i] = v;
+  }
+  if (c.n_out > 1) {
+    alloc_out(c.out[1], {});
+    c.out[1].data[0] = ys;
+  }
+  if (c.n_out > 2) {
+    alloc_out(c.out[2], {});
+    c.out[2].data[0] = y_zp;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Integer matmul family: oxionnx-ops/src/registry/quant_ops/qlinear_matmul.rs:30-254
+// ---------------------------------------------------------------------------------------
+struct MatMulShape {
+  int64_t batch, m, k, n;
+  std::vector<int64_t> out_shape;
+  bool a_broadcast, b_broadcast;
+};
+
+MatMulShape resolve_shapes(const oxo_tensor& a, const oxo_tensor& b, const char* op) {
+  if (a.rank == 0 || b.rank == 0) fail(OXO_ERR_SHAPE_MISMATCH, "%s: inputs must have rank >= 1", op);
+  bool a1 = a.rank == 1, b1 = b.rank == 1;
+  std::vector<int64_t> ad = a1 ? std::vector<int64_t>{1, a.shape[0]} : shape_of(a);
+  std::vector<int64_t> bd = b1 ? std::vector<int64_t>{b.shape[0], 1} : shape_of(b);
+  int64_t m = ad[ad.size() - 2], k = ad[ad.size() - 1], kb = bd[bd.size() - 2], n = bd[bd.size() - 1];
+  if (k != kb) fail(OXO_ERR_SHAPE_MISMATCH, "%s: inner dimensions disagree: %lld vs %lld", op, (long long)k, (long long)kb);
+  int64_t ba = 1, bb = 1;
+  for (size_t i = 0; i + 2 < ad.size(); ++i) ba *= ad[i];
+  for (size_t i = 0; i + 2 < bd.size(); ++i) bb *= bd[i];
+  int64_t batch;
+  if (ba == bb) batch = ba;
+  else if (ba == 1) batch = bb;
+  else if (bb == 1) batch = ba;
+  else fail(OXO_ERR_SHAPE_MISMATCH, "%s: batch dimensions disagree (%lld vs %lld) and neither is 1", op, (long long)ba, (long long)bb);
+  const std::vector<int64_t>& pre = ba >= bb ? ad : bd;
+  std::vector<int64_t> out(pre.begin(), pre.end() - 2);
+  if (!a1) out.push_back(m);
+  if (!b1) out.push_back(n);
+  return {batch, m, k, n, out, ba == 1 && batch != 1, bb == 1 && batch != 1};
+}
+
+inline int32_t zp_at(const std::vector<int32_t>& l, int64_t idx) {
+  if (l.size() == 1) return l[0];
+  return (size_t)idx < l.size() ? l[(size_t)idx] : 0;
+}
+
+void check_zero_point(const std::vector<int32_t>& l, int64_t expected, const char* op, const char* which) {
+  if (l.size() == 1 || (int64_t)l.size() == expected) return;
+  fail(OXO_ERR_SHAPE_MISMATCH, "%s: %s has %zu entries, expected 1 (per tensor) or %lld", op, which, l.size(), (long long)expected);
+}
+
+std::vector<int64_t> integer_matmul(const std::vector<int32_t>& a, const std::vector<int32_t>& b, const std::vector<int32_t>& a_zp,
+                                    const std::vector<int32_t>& b_zp, const MatMulShape& s) {
+  std::vector<int64_t> out((size_t)(s.batch * s.m * s.n), 0);
+  // B is re-read column-wise by the reference loop; a transposed copy changes nothing in
+  // the arithmetic and keeps the all-cores variant usable at the benchmark sizes.
+  int64_t total_rows = s.batch * s.m;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads) schedule(static)
+  for (int64_t row = 0; row < total_rows; ++row) {
+    int64_t bi = row / s.m, i = row % s.m;
+    int64_t a_base = s.a_broadcast ? 0 : bi * s.m * s.k;
+    int64_t b_base = s.b_broadcast ? 0 : bi * s.k * s.n;
+    int64_t azp = zp_at(a_zp, i);
+    std::vector<int64_t> acc((size_t)s.n, 0);
+    for (int64_t p = 0; p < s.k; ++p) {
+      int64_t av = (int64_t)a[(size_t)(a_base + i * s.k + p)] - azp;
+      const int32_t* brow = &b[(size_t)(b_base + p * s.n)];
+      if (b_zp.size() == 1) {
+        int64_t bz = b_zp[0];
+        for (int64_t j = 0; j < s.n; ++j) acc[(size_t)j] += av * ((int64_t)brow[j] - bz);
+      } else {
+        for (int64_t j = 0; j < s.n; ++j) acc[(size_t)j] += av * ((int64_t)brow[j] - (int64_t)zp_at(b_zp, j));
+      }
+    }
+    std::copy(acc.begin(), acc.end(), out.begin() + (size_t)(bi * s.m * s.n + i * s.n));
+  }
+  return out;
+}
+
+void op_matmul_integer(Ctx& c) {
+  const char* op = "MatMulInteger";
+  const oxo_tensor& a = c.input(0);
+  const oxo_tensor& b = c.input(1);
+  check_len(a, op, "A");
+  check_len(b, op, "B");
+  auto a_zp = zero_point_lanes(c.optional(2), "MatMulInteger: a_zero_point");
+  auto b_zp = zero_point_lanes(c.optional(3), "MatMulInteger: b_zero_point");
+  MatMulShape s = resolve_shapes(a, b, op);
+  check_zero_point(a_zp, s.m, op, "a_zero_point");
+  check_zero_point(b_zp, s.n, op, "b_zero_point");
+  auto ai = tensor_to_i32(a, "MatMulInteger: A");
+  auto bi = tensor_to_i32(b, "MatMulInteger: B");
+  auto acc = integer_matmul(ai, bi, a_zp, b_zp, s);
+  alloc_out(c.out[0], s.out_shape);
+  for (size_t i = 0; i < acc.size(); ++i) c.out[0].data[i] = saturate_i32(acc[i]);
+}
+
+void op_qlinear_matmul(Ctx& c) {
+  const char* op = "QLinearMatMul";
+  const oxo_tensor& a = c.input(0);
+  float a_scale = scale_input(c.input(1), "QLinearMatMul: a_scale");
+  auto a_zp = zero_point_lanes(c.optional(2), "QLinearMatMul: a_zero_point");
+  const oxo_tensor& b = c.input(3);
+  float b_scale = scale_input(c.input(4), "QLinearMatMul: b_scale");
+  auto b_zp = zero_point_lanes(c.optional(5), "QLinearMatMul: b_zero_point");
+  float y_scale = scale_input(c.input(6), "QLinearMatMul: y_scale");
+  auto y_zp_l = zero_point_lanes(c.optional(7), "QLinearMatMul: y_zero_point");
+  check_len(a, op, "a");
+  check_len(b, op, "b");
+  MatMulShape s = resolve_shapes(a, b, op);
+  check_zero_point(a_zp, s.m, op, "a_zero_point");
+  check_zero_point(b_zp, s.n, op, "b_zero_point");
+  auto ai = tensor_to_i32(a, "QLinearMatMul: a");
+  auto bi = tensor_to_i32(b, "QLinearMatMul: b");
+  auto acc = integer_matmul(ai, bi, a_zp, b_zp, s);
+  int32_t y_zp = y_zp_l.empty() ? 0 : y_zp_l[0];
+  SatRange r = sat_infer(y_zp_l, a_zp);
+  volatile float ab = a_scale * b_scale;
+  float combined = ab / y_scale;
+  alloc_out(c.out[0], s.out_shape);
+  for (size_t i = 0; i < acc.size(); ++i) c.out[0].data[i] = requantize(acc[i], combined, y_zp, r);
+}
+
+// ---------------------------------------------------------------------------------------
+// Convolution geometry: oxionnx-ops/src/conv/spatial.rs:36-50, 88-160, 204-260, 272-345,
+// 413-455.
+// ---------------------------------------------------------------------------------------
+struct ConvGeo {
+  int rank;
+  std::vector<int64_t> strides, pads, dilations, out_shape;
+  int64_t group;
+};
+
+std::vector<int64_t> read_positive_spatial(const std::vector<int64_t>& v, int rank, const char* name, const char* op) {
+  std::vector<int64_t> out((size_t)rank, 1);
+  for (int a = 0; a < rank; ++a)
+    if ((size_t)a < v.size()) {
+      if (v[(size_t)a] < 1) fail(OXO_ERR_SHAPE_MISMATCH, "%s: %s[%d] must be >= 1, got %lld", op, name, a, (long long)v[(size_t)a]);
+      out[(size_t)a] = v[(size_t)a];
+    }
+  return out;
+}
+
+std::vector<int64_t> read_pads(const std::vector<int64_t>& v, int rank, const char* op) {
+  std::vector<int64_t> out((size_t)(2 * rank), 0);
+  for (int i = 0; i < 2 * rank; ++i)
+    if ((size_t)i < v.size()) {
+      if (v[(size_t)i] < 0) fail(OXO_ERR_SHAPE_MISMATCH, "%s: pads[%d] must be >= 0, got %lld", op, i, (long long)v[(size_t)i]);
+      out[(size_t)i] = v[(size_t)i];
+    }
+  return out;
+}
+
+enum AutoPad { NOTSET, SAME_UPPER, SAME_LOWER, VALID };
+AutoPad parse_auto_pad(const std::string& raw, const char* op) {
+  if (raw.empty() || raw == "NOTSET") return NOTSET;
+  if (raw == "SAME_UPPER") return SAME_UPPER;
+  if (raw == "SAME_LOWER") return SAME_LOWER;
+  if (raw == "VALID") return VALID;
+  fail(OXO_ERR_UNSUPPORTED, "%s: unknown auto_pad value '%s' (expected NOTSET, SAME_UPPER, SAME_LOWER or VALID)", op, raw.c_str());
+}
+
+std::vector<int64_t> resolve_pads(AutoPad ap, const int64_t* in_sp, const int64_t* kernel, const std::vector<int64_t>& strides,
+                                  const std::vector<int64_t>& dil, const std::vector<int64_t>& explicit_pads, int rank) {
+  if (ap == NOTSET) return explicit_pads;
+  std::vector<int64_t> out((size_t)(2 * rank), 0);
+  if (ap == VALID) return out;
+  bool lower = ap == SAME_LOWER;
+  for (int a = 0; a < rank; ++a) {
+    int64_t stride = std::max<int64_t>(strides[(size_t)a], 1);
+    int64_t out_dim = (in_sp[a] + stride - 1) / stride;
+    int64_t eff_k = std::max<int64_t>(kernel[a] - 1, 0) * dil[(size_t)a] + 1;
+    int64_t needed = std::max<int64_t>(std::max<int64_t>(out_dim - 1, 0) * strides[(size_t)a] + eff_k - in_sp[a], 0);
+    int64_t half = needed / 2;
+    out[(size_t)a] = lower ? needed - half : half;
+    out[(size_t)(a + rank)] = lower ? half : needed - half;
+  }
+  return out;
+}
+
+int64_t pool_out_dim(const char* op, int axis, int64_t in_dim, int64_t pb, int64_t pe, int64_t kernel, int64_t dil, int64_t stride, bool ceil_mode) {
+  if (stride == 0) fail(OXO_ERR_SHAPE_MISMATCH, "%s: strides[%d] must be >= 1, got 0", op, axis);
+  if (kernel == 0 || dil == 0) fail(OXO_ERR_SHAPE_MISMATCH, "%s: invalid kernel/dilation on axis %d", op, axis);
+  int64_t eff_k = (kernel - 1) * dil + 1;
+  int64_t padded = in_dim + pb + pe;
+  if (padded < eff_k)
+    fail(OXO_ERR_SHAPE_MISMATCH, "%s: padded input extent %lld on axis %d is smaller than the dilated kernel extent %lld", op, (long long)padded, axis,
+         (long long)eff_k);
+  int64_t span = padded - eff_k;
+  int64_t out = ceil_mode ? (span + stride - 1) / stride + 1 : span / stride + 1;
+  if (ceil_mode && out > 1 && (out - 1) * stride >= in_dim + pb) out -= 1;
+  return out;
+}
+
+ConvGeo conv_geometry(const Attrs& at, const oxo_tensor& x, const oxo_tensor& w, const char* op, bool check_kernel_shape) {
+  if (x.rank < 3) fail(OXO_ERR_SHAPE_MISMATCH, "%s: input must have rank >= 3 ([N, C, d_0, ...]), got rank %d", op, x.rank);
+  int rank = x.rank - 2;
+  if (w.rank != x.rank) fail(OXO_ERR_SHAPE_MISMATCH, "%s: weight rank %d must equal input rank %d", op, w.rank, x.rank);
+  ConvGeo g;
+  g.rank = rank;
+  g.strides = read_positive_spatial(at.ints("strides"), rank, "strides", op);
+  g.dilations = read_positive_spatial(at.ints("dilations"), rank, "dilations", op);
+  g.group = at.i("group", 1);
+  if (g.group < 1) fail(OXO_ERR_SHAPE_MISMATCH, "%s: group must be >= 1, got %lld", op, (long long)g.group);
+  if (check_kernel_shape) {  // float Conv only: registry/conv_ops/conv.rs:66-77
+    auto ks = at.ints("kernel_shape");
+    if (!ks.empty()) {
+      if ((int)ks.size() < rank) fail(OXO_ERR_SHAPE_MISMATCH, "%s: kernel_shape requires %d spatial dims, got %zu", op, rank, ks.size());
+      for (int a = 0; a < rank; ++a) {
+        if (ks[(size_t)a] < 1) fail(OXO_ERR_SHAPE_MISMATCH, "%s: kernel_shape[%d] must be >= 1", op, a);
+        if (ks[(size_t)a] != w.shape[a + 2]) fail(OXO_ERR_SHAPE_MISMATCH, "%s: kernel_shape disagrees with weight spatial dims", op);
+      }
+    }
+  }
+  int64_t c_in = x.shape[1], cpg = w.shape[1];
+  if (cpg * g.group != c_in)
+    fail(OXO_ERR_SHAPE_MISMATCH, "%s: input channels %lld != weight input channels %lld * group %lld", op, (long long)c_in, (long long)cpg, (long long)g.group);
+  if (w.shape[0] % g.group != 0) fail(OXO_ERR_SHAPE_MISMATCH, "%s: output channels %lld not divisible by group %lld", op, (long long)w.shape[0], (long long)g.group);
+  auto explicit_pads = read_pads(at.ints("pads"), rank, op);
+  AutoPad ap = parse_auto_pad(at.s("auto_pad"), op);
+  g.pads = resolve_pads(ap, x.shape + 2, w.shape + 2, g.strides, g.dilations, explicit_pads, rank);
+  g.out_shape = {x.shape[0], w.shape[0]};
+  for (int a = 0; a < rank; ++a)
+    g.out_shape.push_back(pool_out_dim(op, a, x.shape[a + 2], g.pads[(size_t)a], g.pads[(size_t)(a + rank)], w.shape[a + 2], g.dilations[(size_t)a],
+                                       g.strides[(size_t)a], false));
+  return g;
+}
+
+// Visit every (output position, kernel tap) pair of a rank-generic convolution and hand
+// the caller the input spatial offset of in-bounds taps.  Mirrors the odometer loops of
+// quant_ops/conv_kernel.rs:205-249.
+struct TapTable {
+  // for each output flat index: list of (k_flat, in_off) for in-bounds taps
+  std::vector<int64_t> start;           // size out_plane+1
+  std::vector<int32_t> k_flat, in_off;  // concatenated
+};
+
+TapTable build_taps(const ConvGeo& g, const int64_t* in_sp, const int64_t* kernel) {
+  int rank = g.rank;
+  const int64_t* out_sp = g.out_shape.data() + 2;
+  int64_t out_plane = 1, k_volume = 1;
+  for (int d = 0; d < rank; ++d) {
+    out_plane *= out_sp[d];
+    k_volume *= kernel[d];
+  }
+  std::vector<int64_t> in_stride((size_t)rank, 1);
+  for (int d = rank - 2; d >= 0; --d) in_stride[(size_t)d] = in_stride[(size_t)d + 1] * in_sp[d + 1];
+  TapTable t;
+  t.start.resize((size_t)out_plane + 1);
+  std::vector<int64_t> oidx((size_t)rank, 0), kidx((size_t)rank, 0);
+  for (int64_t o = 0; o < out_plane; ++o) {
+    t.start[(size_t)o] = (int64_t)t.k_flat.size();
+    std::fill(kidx.begin(), kidx.end(), 0);
+    for (int64_t kf = 0; kf < k_volume; ++kf) {
+      int64_t off = 0;
+      bool inside = true;
+      for (int d = 0; d < rank; ++d) {
+        int64_t pos = oidx[(size_t)d] * g.strides[(size_t)d] + kidx[(size_t)d] * g.dilations[(size_t)d];
+        int64_t ip = pos - g.pads[(size_t)d];
+        if (ip < 0 || ip >= in_sp[d]) {
+          inside = false;
+          break;
+        }
+        off += ip * in_stride[(size_t)d];
+      }
+      if (inside) {
+        t.k_flat.push_back((int32_t)kf);
+        t.in_off.push_back((int32_t)off);
+      }
+      for (int d = rank - 1; d >= 0; --d) {
+        if (++kidx[(size_t)d] < kernel[d]) break;
+        kidx[(size_t)d] = 0;
+      }
+    }
+    for (int d = rank - 1; d >= 0; --d) {
+      if (++oidx[(size_t)d] < out_sp[d]) break;
+      oidx[(size_t)d] = 0;
+    }
+  }
+  t.start[(size_t)out_plane] = (int64_t)t.k_flat.size();
+  return t;
+}
+
+// integer_conv: quant_ops/conv_kernel.rs:134-254.  acc starts at the int32 bias; taps in
+// the padding are skipped.
+std::vector<int64_t> integer_conv(const oxo_tensor& x, const oxo_tensor& w, int32_t x_zp, const std::vector<int32_t>& w_zp, const oxo_tensor* bias,
+                                  const ConvGeo& g, const char* op) {
+  int64_t batch = x.shape[0], c_in = x.shape[1], c_out = w.shape[0], cpg = w.shape[1];
+  if (w_zp.size() != 1 && (int64_t)w_zp.size() != c_out)
+    fail(OXO_ERR_SHAPE_MISMATCH, "%s: w_zero_point has %zu entries, expected 1 or %lld (per output channel)", op, w_zp.size(), (long long)c_out);
+  if (x.len != numel(x)) fail(OXO_ERR_SHAPE_MISMATCH, "%s: input data length %lld does not match shape", op, (long long)x.len);
+  if (w.len != numel(w)) fail(OXO_ERR_SHAPE_MISMATCH, "%s: weight data length %lld does not match shape", op, (long long)w.len);
+  std::vector<int64_t> bias64;
+  if (bias) {
+    if (bias->len != c_out) fail(OXO_ERR_SHAPE_MISMATCH, "%s: bias has %lld entries, expected %lld", op, (long long)bias->len, (long long)c_out);
+    std::string label = std::string(op) + ": bias";
+    for (int64_t i = 0; i < c_out; ++i) bias64.push_back(lane_to_i32(bias->data[i], label.c_str()));
+  }
+  std::string li = std::string(op) + ": input", lw = std::string(op) + ": weight";
+  auto xi = tensor_to_i32(x, li.c_str());
+  auto wi = tensor_to_i32(w, lw.c_str());
+  int rank = g.rank;
+  int64_t in_plane = 1, out_plane = 1, k_volume = 1;
+  for (int d = 0; d < rank; ++d) {
+    in_plane *= x.shape[d + 2];
+    out_plane *= g.out_shape[(size_t)d + 2];
+    k_volume *= w.shape[d + 2];
+  }
+  int64_t copg = c_out / g.group;
+  TapTable taps = build_taps(g, x.shape + 2, w.shape + 2);
+  std::vector<int64_t> acc((size_t)(batch * c_out * out_plane), 0);
+  int64_t jobs = batch * c_out;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads) schedule(dynamic, 1)
+  for (int64_t job = 0; job < jobs; ++job) {
+    int64_t n = job / c_out, oc = job % c_out;
+    int64_t grp = oc / copg;
+    int64_t wz = w_zp.size() == 1 ? w_zp[0] : w_zp[(size_t)oc];
+    int64_t w_base = oc * cpg * k_volume;
+    int64_t out_base = (n * c_out + oc) * out_plane;
+    int64_t bias_term = bias64.empty() ? 0 : bias64[(size_t)oc];
+    for (int64_t o = 0; o < out_plane; ++o) {
+      int64_t sum = bias_term;
+      for (int64_t t = taps.start[(size_t)o]; t < taps.start[(size_t)o + 1]; ++t) {
+        int64_t kf = taps.k_flat[(size_t)t], off = taps.in_off[(size_t)t];
+        for (int64_t ic = 0; ic < cpg; ++ic) {
+          int64_t plane = (n * c_in + grp * cpg + ic) * in_plane;
+          int64_t xv = xi[(size_t)(plane + off)];
+          int64_t wv = wi[(size_t)(w_base + ic * k_volume + kf)];
+          sum += (xv - x_zp) * (wv - wz);
+        }
+      }
+      acc[(size_t)(out_base + o)] = sum;
+    }
+  }
+  return acc;
+}
+
+// QLinearConv: quant_ops/qlinear_conv.rs:34-103
+void op_qlinear_conv(Ctx& c) {
+  const char* op = "QLinearConv";
+  const oxo_tensor& x = c.input(0);
+  float x_scale = scale_input(c.input(1), "QLinearConv: x_scale");
+  auto x_zp_l = zero_point_lanes(c.optional(2), "QLinearConv: x_zero_point");
+  const oxo_tensor& w = c.input(3);
+  const oxo_tensor& w_scale = c.input(4);
+  auto w_zp_l = zero_point_lanes(c.optional(5), "QLinearConv: w_zero_point");
+  float y_scale = scale_input(c.input(6), "QLinearConv: y_scale");
+  auto y_zp_l = zero_point_lanes(c.optional(7), "QLinearConv: y_zero_point");
+  const oxo_tensor* bias = c.optional(8);
+  if (bias && bias->len == 0) bias = nullptr;
+  if (w_scale.len == 0) fail(OXO_ERR_INVALID_MODEL, "QLinearConv: w_scale is empty");
+  int32_t x_zp = x_zp_l.empty() ? 0 : x_zp_l[0];
+  int32_t y_zp = y_zp_l.empty() ? 0 : y_zp_l[0];
+  ConvGeo g = conv_geometry(c.attrs, x, w, op, false);
+  auto acc = integer_conv(x, w, x_zp, w_zp_l, bias, g, op);
+  int64_t c_out = w.shape[0];
+  bool per_channel = w_scale.len > 1;
+  if (per_channel && w_scale.len != c_out)
+    fail(OXO_ERR_SHAPE_MISMATCH, "QLinearConv: w_scale has %lld entries, expected 1 or %lld (per output channel)", (long long)w_scale.len, (long long)c_out);
+  for (int64_t i = 0; i < w_scale.len; ++i)
+    if (!std::isfinite(w_scale.data[i])) fail(OXO_ERR_INVALID_MODEL, "QLinearConv: w_scale[%lld] must be finite", (long long)i);
+  SatRange r = sat_infer(y_zp_l, {x_zp});
+  int64_t spatial = 1;
+  for (size_t d = 2; d < g.out_shape.size(); ++d) spatial *= g.out_shape[d];
+  alloc_out(c.out[0], g.out_shape);
+  float* y = c.out[0].data;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t flat = 0; flat < (int64_t)acc.size(); ++flat) {
+    int64_t oc = (flat / spatial) % c_out;
+    float ws = per_channel ? w_scale.data[oc] : w_scale.data[0];
+    volatile float xw = x_scale * ws;
+    float combined = xw / y_scale;
+    y[flat] = requantize(acc[(size_t)flat], combined, y_zp, r);
+  }
+}
+
+// ConvInteger: quant_ops/qlinear_conv.rs:173-203
+void op_conv_integer(Ctx& c) {
+  const char* op = "ConvInteger";
+  const oxo_tensor& x = c.input(0);
+  const oxo_tensor& w = c.input(1);
+  auto x_zp_l = zero_point_lanes(c.optional(2), "ConvInteger: x_zero_point");
+  auto w_zp_l = zero_point_lanes(c.optional(3), "ConvInteger: w_zero_point");
+  int32_t x_zp = x_zp_l.empty() ? 0 : x_zp_l[0];
+  ConvGeo g = conv_geometry(c.attrs, x, w, op, false);
+  auto acc = integer_conv(x, w, x_zp, w_zp_l, nullptr, g, op);
+  alloc_out(c.out[0], g.out_shape);
+  for (size_t i = 0; i < acc.size(); ++i) c.out[0].data[i] = saturate_i32(acc[i]);
+}
+
+// ---------------------------------------------------------------------------------------
+// Float Conv: oxionnx-ops/src/registry/conv_ops/conv.rs:40-156 (geometry + fused
+// activation) over the definition implemented by oxionnx-ops/src/conv/conv2d.rs.
+// ---------------------------------------------------------------------------------------
+void apply_fused_activation(const Attrs& at, float* data, int64_t n) {
+  std::string act = at.s("activation");
+  if (act == "relu") {
+    for (int64_t i = 0; i < n; ++i) data[i] = std::max(data[i], 0.0f);  // f32::max: NaN -> 0
+  } else if (act == "clip") {
+    float mn = at.f("activation_min", -std::numeric_limits<float>::infinity());
+    float mx = at.f("activation_max", std::numeric_limits<float>::infinity());
+    float lo = std::isnan(mn) ? -std::numeric_limits<float>::infinity() : mn;
+    float hi = std::isnan(mx) ? std::numeric_limits<float>::infinity() : mx;
+    if (lo <= hi)
+      for (int64_t i = 0; i < n; ++i) {
+        float v = data[i];
+        if (v < lo) v = lo;
+        if (v > hi) v = hi;
+        data[i] = v;
+      }
+  }
+}
+
+void op_conv(Ctx& c) {
+  const char* op = "Conv";
+  const oxo_tensor& x = c.input(0);
+  const oxo_tensor& w = c.input(1);
+  const oxo_tensor* bias = c.optional(2);
+  ConvGeo g = conv_geometry(c.attrs, x, w, op, true);
+  if (x.len != numel(x) || w.len != numel(w)) fail(OXO_ERR_SHAPE_MISMATCH, "Conv: data length does not match shape");
+  int64_t batch = x.shape[0], c_in = x.shape[1], c_out = w.shape[0], cpg = w.shape[1];
+  if (bias && bias->len != c_out) fail(OXO_ERR_SHAPE_MISMATCH, "Conv: bias has %lld entries, expected %lld", (long long)bias->len, (long long)c_out);
+  int rank = g.rank;
+  int64_t in_plane = 1, out_plane = 1, k_volume = 1;
+  for (int d = 0; d < rank; ++d) {
+    in_plane *= x.shape[d + 2];
+    out_plane *= g.out_shape[(size_t)d + 2];
+    k_volume *= w.shape[d + 2];
+  }
+  int64_t copg = c_out / g.group;
+  TapTable taps = build_taps(g, x.shape + 2, w.shape + 2);
+  alloc_out(c.out[0], g.out_shape);
+  float* y = c.out[0].data;
+  int64_t jobs = batch * c_out;
+  const int accum = g_float_accum;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads) schedule(dynamic, 1)
+  for (int64_t job = 0; job < jobs; ++job) {
+    int64_t n = job / c_out, oc = job % c_out;
+    int64_t grp = oc / copg;
+    int64_t w_base = oc * cpg * k_volume;
+    int64_t out_base = (n * c_out + oc) * out_plane;
+    float b = bias ? bias->data[oc] : 0.0f;
+    for (int64_t o = 0; o < out_plane; ++o) {
+      double sum64 = 0.0;
+      float sum32 = 0.0f;
+      for (int64_t ic = 0; ic < cpg; ++ic) {
+        int64_t plane = (n * c_in + grp * cpg + ic) * in_plane;
+        for (int64_t t = taps.start[(size_t)o]; t < taps.start[(size_t)o + 1]; ++t) {
+          float xv = x.data[plane + taps.in_off[(size_t)t]];
+          float wv = w.data[w_base + ic * k_volume + taps.k_flat[(size_t)t]];
+          if (accum == 0) sum64 += (double)xv * (double)wv;
+          else sum32 += xv * wv;
+        }
+      }
+      float r = accum == 0 ? (float)sum64 : sum32;
+      y[out_base + o] = r + b;
+    }
+  }
+  apply_fused_activation(c.attrs, y, c.out[0].len);
+}
+
+// ---------------------------------------------------------------------------------------
+// MatMul / Gemm: oxionnx-ops/src/math/matmul.rs:53-190 (alpha and beta*C applied as
+// separate passes after the raw product).
+// ---------------------------------------------------------------------------------------
+void raw_matmul(const float* a, int64_t rsa, int64_t csa, const float* b, int64_t rsb, int64_t csb, float* out, int64_t m, int64_t k, int64_t n) {
+  const int accum = g_float_accum;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      double s64 = 0.0;
+      float s32 = 0.0f;
+      for (int64_t p = 0; p < k; ++p) {
+        float av = a[i * rsa + p * csa], bv = b[p * rsb + j * csb];
+        if (accum == 0) s64 += (double)av * (double)bv;
+        else s32 += av * bv;
+      }
+      out[i * n + j] = accum == 0 ? (float)s64 : s32;
+    }
+  }
+}
+
+void op_matmul(Ctx& c) {
+  const oxo_tensor& a = c.input(0);
+  const oxo_tensor& b = c.input(1);
+  if (a.len != numel(a) || b.len != numel(b)) fail(OXO_ERR_SHAPE_MISMATCH, "MatMul: data length does not match shape");
+  MatMulShape s = resolve_shapes(a, b, "MatMul");
+  alloc_out(c.out[0], s.out_shape);
+  for (int64_t bi = 0; bi < s.batch; ++bi) {
+    const float* ap = a.data + (s.a_broadcast ? 0 : bi * s.m * s.k);
+    const float* bp = b.data + (s.b_broadcast ? 0 : bi * s.k * s.n);
+    raw_matmul(ap, s.k, 1, bp, s.n, 1, c.out[0].data + bi * s.m * s.n, s.m, s.k, s.n);
+  }
+}
+
+// unidirectional broadcast of C to [m,n] (numpy rules, right-aligned)
+float bcast2(const oxo_tensor& t, int64_t i, int64_t j, int64_t m, int64_t n) {
+  (void)m;
+  (void)n;
+  if (t.rank == 0 || t.len == 1) return t.data[0];
+  if (t.rank == 1) return t.data[t.shape[0] == 1 ? 0 : j];
+  int64_t r = t.shape[t.rank - 2], cc = t.shape[t.rank - 1];
+  return t.data[(r == 1 ? 0 : i) * cc + (cc == 1 ? 0 : j)];
+}
+
+void op_gemm(Ctx& c) {
+  const oxo_tensor& a = c.input(0);
+  const oxo_tensor& b = c.input(1);
+  const oxo_tensor* cc = c.optional(2);
+  float alpha = c.attrs.f("alpha", 1.0f), beta = c.attrs.f("beta", 1.0f);
+  bool ta = c.attrs.i("transA", 0) != 0, tb = c.attrs.i("transB", 0) != 0;
+  if (a.rank != 2 || b.rank != 2) fail(OXO_ERR_UNSUPPORTED, "Gemm: oracle covers rank-2 operands only");
+  int64_t m = ta ? a.shape[1] : a.shape[0], k = ta ? a.shape[0] : a.shape[1];
+  int64_t k2 = tb ? b.shape[1] : b.shape[0], n = tb ? b.shape[0] : b.shape[1];
+  if (k != k2) fail(OXO_ERR_SHAPE_MISMATCH, "gemm: inner dimensions mismatch %lld != %lld", (long long)k, (long long)k2);
+  alloc_out(c.out[0], {m, n});
+  float* y = c.out[0].data;
+  raw_matmul(a.data, ta ? 1 : k, ta ? m : 1, b.data, tb ? 1 : n, tb ? k : 1, y, m, k, n);
+  if (alpha != 1.0f)
+    for (int64_t i = 0; i < m * n; ++i) y[i] *= alpha;
+  if (cc) {
+    if (cc->rank > 2) fail(OXO_ERR_UNSUPPORTED, "Gemm: C rank > 2");
+    for (int64_t i = 0; i < m; ++i)
+      for (int64_t j = 0; j < n; ++j) {
+        volatile float bc = beta * bcast2(*cc, i, j, m, n);
+        y[i * n + j] += bc;
+      }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// OxiInstanceNorm: oxionnx-ops/src/registry/oxi_instance_norm.rs:58-66, 153-160
+// ---------------------------------------------------------------------------------------
+void op_oxi_instance_norm(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  float eps = c.attrs.f("epsilon", 1e-5f);
+  if (x.rank < 3) fail(OXO_ERR_SHAPE_MISMATCH, "OxiInstanceNorm: input must have rank >= 3 ([N, C, ...])");
+  if (x.len != numel(x)) fail(OXO_ERR_SHAPE_MISMATCH, "OxiInstanceNorm: element count disagrees with shape");
+  int64_t spatial = 1;
+  for (int d = 2; d < x.rank; ++d) spatial *= x.shape[d];
+  alloc_out(c.out[0], shape_of(x));
+  float* y = c.out[0].data;
+  if (spatial == 0 || x.len == 0) return;
+  int64_t planes = x.len / spatial;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t p = 0; p < planes; ++p) {
+    const float* src = x.data + p * spatial;
+    float* dst = y + p * spatial;
+    float count = (float)spatial;
+    float sum = 0.0f;
+    for (int64_t i = 0; i < spatial; ++i) sum += src[i];
+    float mean = sum / count;
+    float vs = 0.0f;
+    for (int64_t i = 0; i < spatial; ++i) {
+      volatile float d = src[i] - mean;
+      volatile float dd = d * d;
+      vs += dd;
+    }
+    float var = vs / count;
+    float inv_std = 1.0f / std::sqrt(var + eps);
+    for (int64_t i = 0; i < spatial; ++i) {
+      volatile float d = src[i] - mean;
+      dst[i] = d * inv_std;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Element-wise glue: oxionnx-ops/src/math/broadcast.rs:219-249 (numpy broadcasting),
+// oxionnx-ops/src/nn/activations.rs:5 (relu), :43 (tanh), :100 (prelu), :271 (silu).
+// ---------------------------------------------------------------------------------------
+std::vector<int64_t> broadcast_shape(const oxo_tensor& a, const oxo_tensor& b, const char* op) {
+  int r = std::max(a.rank, b.rank);
+  std::vector<int64_t> out((size_t)r);
+  for (int i = 0; i < r; ++i) {
+    int64_t da = i < r - a.rank ? 1 : a.shape[i - (r - a.rank)];
+    int64_t db = i < r - b.rank ? 1 : b.shape[i - (r - b.rank)];
+    if (da != db && da != 1 && db != 1) fail(OXO_ERR_SHAPE_MISMATCH, "%s: shapes are not broadcastable", op);
+    out[(size_t)i] = std::max(da, db);
+    if (da == 0 || db == 0) out[(size_t)i] = 0;
+  }
+  return out;
+}
+
+template <class F>
+void binary_op(Ctx& c, F f) {
+  const oxo_tensor& a = c.input(0);
+  const oxo_tensor& b = c.input(1);
+  auto os = broadcast_shape(a, b, c.op);
+  alloc_out(c.out[0], os);
+  int r = (int)os.size();
+  std::vector<int64_t> sa((size_t)r, 0), sb((size_t)r, 0);
+  int64_t st = 1;
+  for (int i = a.rank - 1; i >= 0; --i) {
+    sa[(size_t)(i + r - a.rank)] = a.shape[i] == 1 ? 0 : st;
+    st *= a.shape[i];
+  }
+  st = 1;
+  for (int i = b.rank - 1; i >= 0; --i) {
+    sb[(size_t)(i + r - b.rank)] = b.shape[i] == 1 ? 0 : st;
+    st *= b.shape[i];
+  }
+  float* y = c.out[0].data;
+  int64_t n = c.out[0].len;
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t flat = 0; flat < n; ++flat) {
+    int64_t rem = flat, ia = 0, ib = 0;
+    for (int d = r - 1; d >= 0; --d) {
+      int64_t idx = rem % os[(size_t)d];
+      rem /= os[(size_t)d];
+      ia += idx * sa[(size_t)d];
+      ib += idx * sb[(size_t)d];
+    }
+    y[flat] = f(a.data[ia], b.data[ib]);
+  }
+}
+
+template <class F>
+void unary_op(Ctx& c, F f) {
+  const oxo_tensor& x = c.input(0);
+  alloc_out(c.out[0], shape_of(x));
+  for (int64_t i = 0; i < x.len; ++i) c.out[0].data[i] = f(x.data[i]);
+}
+
+void op_prelu(Ctx& c) {
+  // slope broadcasts unidirectionally to x (per-channel [C,1,1] or scalar)
+  binary_op(c, [](float x, float s) { return x >= 0.0f ? x : x * s; });
+}
+
+// ---------------------------------------------------------------------------------------
+// Pooling: oxionnx-ops/src/conv/pooling.rs:166-260 (max_pool_into), :462-480
+// (global_avg_pool: sequential f32 sum, then divide by the count).
+// ---------------------------------------------------------------------------------------
+void op_max_pool(Ctx& c) {
+  const char* op = "MaxPool";
+  const oxo_tensor& x = c.input(0);
+  if (x.rank < 3) fail(OXO_ERR_SHAPE_MISMATCH, "MaxPool: input must have rank >= 3");
+  int rank = x.rank - 2;
+  auto ks = c.attrs.ints("kernel_shape");
+  if ((int)ks.size() < rank) fail(OXO_ERR_SHAPE_MISMATCH, "MaxPool: kernel_shape requires %d spatial dims, got %zu", rank, ks.size());
+  for (int a = 0; a < rank; ++a)
+    if (ks[(size_t)a] < 1) fail(OXO_ERR_SHAPE_MISMATCH, "MaxPool: kernel_shape[%d] must be >= 1", a);
+  ConvGeo g;
+  g.rank = rank;
+  g.strides = read_positive_spatial(c.attrs.ints("strides"), rank, "strides", op);
+  g.dilations = read_positive_spatial(c.attrs.ints("dilations"), rank, "dilations", op);
+  auto explicit_pads = read_pads(c.attrs.ints("pads"), rank, op);
+  AutoPad ap = parse_auto_pad(c.attrs.s("auto_pad"), op);
+  g.pads = resolve_pads(ap, x.shape + 2, ks.data(), g.strides, g.dilations, explicit_pads, rank);
+  bool ceil_mode = c.attrs.i("ceil_mode", 0) != 0;
+  g.out_shape = {x.shape[0], x.shape[1]};
+  for (int a = 0; a < rank; ++a)
+    g.out_shape.push_back(
+        pool_out_dim(op, a, x.shape[a + 2], g.pads[(size_t)a], g.pads[(size_t)(a + rank)], ks[(size_t)a], g.dilations[(size_t)a], g.strides[(size_t)a], ceil_mode));
+  TapTable taps = build_taps(g, x.shape + 2, ks.data());
+  int64_t in_plane = 1, out_plane = 1;
+  for (int d = 0; d < rank; ++d) {
+    in_plane *= x.shape[d + 2];
+    out_plane *= g.out_shape[(size_t)d + 2];
+  }
+  alloc_out(c.out[0], g.out_shape);
+  float* y = c.out[0].data;
+  int64_t planes = x.shape[0] * x.shape[1];
+#pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
+  for (int64_t p = 0; p < planes; ++p)
+    for (int64_t o = 0; o < out_plane; ++o) {
+      float mx = -std::numeric_limits<float>::infinity();
+      for (int64_t t = taps.start[(size_t)o]; t < taps.start[(size_t)o + 1]; ++t) {
+        float v = x.data[p * in_plane + taps.in_off[(size_t)t]];
+        if (v > mx) mx = v;
+      }
+      y[p * out_plane + o] = mx;
+    }
+}
+
+void op_global_average_pool(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  if (x.rank < 3) {
+    alloc_out(c.out[0], shape_of(x));
+    std::copy(x.data, x.data + x.len, c.out[0].data);
+    return;
+  }
+  int64_t n = x.shape[0], ch = x.shape[1], spatial = 1;
+  for (int d = 2; d < x.rank; ++d) spatial *= x.shape[d];
+  std::vector<int64_t> os = {n, ch};
+  for (int d = 2; d < x.rank; ++d) os.push_back(1);
+  alloc_out(c.out[0], os);
+  for (int64_t p = 0; p < n * ch; ++p) {
+    float sum = 0.0f;
+    for (int64_t i = 0; i < spatial; ++i) sum += x.data[p * spatial + i];
+    c.out[0].data[p] = sum / (float)spatial;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Shape glue: Flatten / Reshape (row-major reinterpretation), Concat
+// (oxionnx-ops/src/shape/sequence.rs:8), Pad constant/reflect (:356), Cast (f32 lanes are
+// already the value representation, so a cast between the lane types used here copies).
+// ---------------------------------------------------------------------------------------
+void op_flatten(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  int64_t axis = c.attrs.i("axis", 1);
+  if (axis < 0) axis += x.rank;
+  if (axis < 0 || axis > x.rank) fail(OXO_ERR_INVALID_MODEL, "Flatten: axis out of range");
+  int64_t outer = 1, inner = 1;
+  for (int d = 0; d < x.rank; ++d) (d < axis ? outer : inner) *= x.shape[d];
+  alloc_out(c.out[0], {outer, inner});
+  std::copy(x.data, x.data + x.len, c.out[0].data);
+}
+
+void op_reshape(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  const oxo_tensor& sh = c.input(1);
+  bool allowzero = c.attrs.i("allowzero", 0) != 0;
+  std::vector<int64_t> os;
+  int64_t known = 1;
+  int infer = -1;
+  for (int64_t i = 0; i < sh.len; ++i) {
+    int64_t d = (int64_t)sh.data[i];
+    if (d == -1) {
+      if (infer >= 0) fail(OXO_ERR_INVALID_MODEL, "Reshape: more than one -1");
+      infer = (int)i;
+      os.push_back(1);
+      continue;
+    }
+    if (d == 0 && !allowzero) {
+      if (i >= x.rank) fail(OXO_ERR_INVALID_MODEL, "Reshape: 0 dim out of range");
+      d = x.shape[i];
+    }
+    os.push_back(d);
+    known *= d;
+  }
+  if (infer >= 0) {
+    if (known == 0 || x.len % known != 0) fail(OXO_ERR_SHAPE_MISMATCH, "Reshape: cannot infer dimension");
+    os[(size_t)infer] = x.len / known;
+    known *= os[(size_t)infer];
+  }
+  if (known != x.len) fail(OXO_ERR_SHAPE_MISMATCH, "Reshape: element count changes");
+  alloc_out(c.out[0], os);
+  std::copy(x.data, x.data + x.len, c.out[0].data);
+}
+
+void op_concat(Ctx& c) {
+  const oxo_tensor& first = c.input(0);
+  int64_t axis = c.attrs.i("axis", 0);
+  if (axis < 0) axis += first.rank;
+  if (axis < 0 || axis >= first.rank) fail(OXO_ERR_INVALID_MODEL, "Concat: axis out of range");
+  std::vector<int64_t> os = shape_of(first);
+  os[(size_t)axis] = 0;
+  for (int i = 0; i < c.n_in; ++i) {
+    const oxo_tensor& t = c.input(i);
+    if (t.rank != first.rank) fail(OXO_ERR_SHAPE_MISMATCH, "Concat: rank mismatch");
+    for (int d = 0; d < t.rank; ++d)
+      if (d != axis && t.shape[d] != first.shape[d]) fail(OXO_ERR_SHAPE_MISMATCH, "Concat: non-axis dims disagree");
+    os[(size_t)axis] += t.shape[axis];
+  }
+  alloc_out(c.out[0], os);
+  int64_t outer = 1, inner = 1;
+  for (int d = 0; d < axis; ++d) outer *= os[(size_t)d];
+  for (int d = (int)axis + 1; d < first.rank; ++d) inner *= os[(size_t)d];
+  int64_t off = 0;
+  for (int i = 0; i < c.n_in; ++i) {
+    const oxo_tensor& t = c.in[i];
+    int64_t chunk = t.shape[axis] * inner;
+    for (int64_t o = 0; o < outer; ++o) std::copy(t.data + o * chunk, t.data + (o + 1) * chunk, c.out[0].data + o * os[(size_t)axis] * inner + off);
+    off += chunk;
+  }
+}
+
+void op_pad(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  std::vector<int64_t> pads;
+  if (const oxo_tensor* p = c.optional(1)) {
+    for (int64_t i = 0; i < p->len; ++i) pads.push_back((int64_t)p->data[i]);
+  } else {
+    pads = c.attrs.ints("pads");
+  }
+  if ((int)pads.size() != 2 * x.rank) fail(OXO_ERR_SHAPE_MISMATCH, "Pad: pads must have 2*rank entries");
+  float cval = 0.0f;
+  if (const oxo_tensor* v = c.optional(2)) {
+    if (v->len > 0) cval = v->data[0];
+  } else {
+    cval = c.attrs.f("value", 0.0f);
+  }
+  std::string mode = c.attrs.s("mode");
+  if (mode.empty()) mode = "constant";
+  if (mode != "constant" && mode != "reflect" && mode != "edge") fail(OXO_ERR_UNSUPPORTED, "Pad: unsupported mode '%s'", mode.c_str());
+  std::vector<int64_t> os = shape_of(x);
+  for (int d = 0; d < x.rank; ++d) {
+    if (pads[(size_t)d] < 0 || pads[(size_t)(d + x.rank)] < 0) fail(OXO_ERR_UNSUPPORTED, "Pad: negative pads not covered by the oracle");
+    os[(size_t)d] += pads[(size_t)d] + pads[(size_t)(d + x.rank)];
+    if (mode == "reflect" && (pads[(size_t)d] >= x.shape[d] || pads[(size_t)(d + x.rank)] >= x.shape[d]) && x.shape[d] > 0 &&
+        (pads[(size_t)d] > 0 || pads[(size_t)(d + x.rank)] > 0))
+      fail(OXO_ERR_INVALID_MODEL, "Pad: reflect pad must be smaller than the axis extent");
+  }
+  alloc_out(c.out[0], os);
+  std::vector<int64_t> xs((size_t)x.rank, 1);
+  for (int d = x.rank - 2; d >= 0; --d) xs[(size_t)d] = xs[(size_t)d + 1] * x.shape[d + 1];
+  for (int64_t flat = 0; flat < c.out[0].len; ++flat) {
+    int64_t rem = flat, src = 0;
+    bool outside = false;
+    for (int d = x.rank - 1; d >= 0; --d) {
+      int64_t idx = rem % os[(size_t)d] - pads[(size_t)d];
+      rem /= os[(size_t)d];
+      int64_t ext = x.shape[d];
+      if (idx < 0 || idx >= ext) {
+        if (mode == "constant") outside = true;
+        else if (mode == "edge") idx = idx < 0 ? 0 : ext - 1;
+        else idx = idx < 0 ? -idx : 2 * (ext - 1) - idx;
+      }
+      if (!outside) src += idx * xs[(size_t)d];
+    }
+    c.out[0].data[flat] = outside ? cval : x.data[src];
+  }
+}
+
+void op_identity(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  alloc_out(c.out[0], shape_of(x));
+  std::copy(x.data, x.data + x.len, c.out[0].data);
+}
+
+// Resize, nearest and linear, for the 4-D NCHW upsampling the face-swap decoder uses:
+// oxionnx-ops/src/resize.rs (coordinate transforms half_pixel / pytorch_half_pixel /
+// asymmetric / align_corners; nearest_mode round_prefer_floor / floor / ceil /
+// round_prefer_ceil).  Only scale factors on the two spatial axes are covered.
+float resize_src_coord(const std::string& mode, int64_t o, float scale, int64_t in_size, int64_t out_size) {
+  if (mode == "asymmetric") return (float)o / scale;
+  if (mode == "align_corners") return out_size <= 1 ? 0.0f : (float)o * (float)(in_size - 1) / (float)(out_size - 1);
+  if (mode == "pytorch_half_pixel") return out_size > 1 ? ((float)o + 0.5f) / scale - 0.5f : 0.0f;
+  return ((float)o + 0.5f) / scale - 0.5f;  // half_pixel
+}
+
+void op_resize(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  if (x.rank != 4) fail(OXO_ERR_UNSUPPORTED, "Resize: oracle covers NCHW rank-4 input only");
+  const oxo_tensor* scales = c.optional(2);
+  const oxo_tensor* sizes = c.optional(3);
+  std::string mode = c.attrs.s("mode");
+  if (mode.empty()) mode = "nearest";
+  std::string coord = c.attrs.s("coordinate_transformation_mode");
+  if (coord.empty()) coord = "half_pixel";
+  std::string nearest = c.attrs.s("nearest_mode");
+  if (nearest.empty()) nearest = "round_prefer_floor";
+  if (c.attrs.i("antialias", 0) != 0) fail(OXO_ERR_UNSUPPORTED, "Resize: antialias not covered by the oracle");
+  if (coord != "half_pixel" && coord != "pytorch_half_pixel" && coord != "asymmetric" && coord != "align_corners")
+    fail(OXO_ERR_UNSUPPORTED, "Resize: coordinate mode '%s' not covered by the oracle", coord.c_str());
+  std::vector<int64_t> os = shape_of(x);
+  float sc[4] = {1, 1, 1, 1};
+  if (scales && scales->len == 4) {
+    for (int d = 0; d < 4; ++d) {
+      sc[d] = scales->data[d];
+      os[(size_t)d] = (int64_t)std::floor((float)x.shape[d] * sc[d]);
+    }
+  } else if (sizes && sizes->len == 4) {
+    for (int d = 0; d < 4; ++d) {
+      os[(size_t)d] = (int64_t)sizes->data[d];
+      sc[d] = (float)os[(size_t)d] / (float)x.shape[d];
+    }
+  } else {
+    fail(OXO_ERR_INVALID_MODEL, "Resize: needs scales or sizes with 4 entries");
+  }
+  if (os[0] != x.shape[0] || os[1] != x.shape[1]) fail(OXO_ERR_UNSUPPORTED, "Resize: only spatial axes may change in the oracle");
+  alloc_out(c.out[0], os);
+  int64_t H = x.shape[2], W = x.shape[3], OH = os[2], OW = os[3];
+  bool lin = mode == "linear" || mode == "bilinear";
+  if (!lin && mode != "nearest") fail(OXO_ERR_UNSUPPORTED, "Resize: mode '%s' not covered by the oracle", mode.c_str());
+  auto nearest_idx = [&](float s, int64_t in_size) {
+    float r;
+    if (nearest == "floor") r = std::floor(s);
+    else if (nearest == "ceil") r = std::ceil(s);
+    else if (nearest == "round_prefer_ceil") r = std::floor(s + 0.5f);
+    else r = std::ceil(s - 0.5f);  // round_prefer_floor
+    int64_t i = (int64_t)r;
+    return std::min<int64_t>(std::max<int64_t>(i, 0), in_size - 1);
+  };
+  for (int64_t p = 0; p < x.shape[0] * x.shape[1]; ++p) {
+    const float* src = x.data + p * H * W;
+    float* dst = c.out[0].data + p * OH * OW;
+    for (int64_t oy = 0; oy < OH; ++oy) {
+      float sy = resize_src_coord(coord, oy, sc[2], H, OH);
+      for (int64_t ox = 0; ox < OW; ++ox) {
+        float sx = resize_src_coord(coord, ox, sc[3], W, OW);
+        if (!lin) {
+          dst[oy * OW + ox] = src[nearest_idx(sy, H) * W + nearest_idx(sx, W)];
+        } else {
+          float cy = std::min(std::max(sy, 0.0f), (float)(H - 1)), cx = std::min(std::max(sx, 0.0f), (float)(W - 1));
+          int64_t y0 = (int64_t)std::floor(cy), x0 = (int64_t)std::floor(cx);
+          int64_t y1 = std::min(y0 + 1, H - 1), x1 = std::min(x0 + 1, W - 1);
+          float fy = cy - (float)y0, fx = cx - (float)x0;
+          float top = src[y0 * W + x0] * (1.0f - fx) + src[y0 * W + x1] * fx;
+          float bot = src[y1 * W + x0] * (1.0f - fx) + src[y1 * W + x1] * fx;
+          dst[oy * OW + ox] = top * (1.0f - fy) + bot * fy;
+        }
+      }
+    }
+  }
+}
+
+struct OpEntry {
+  const char* name;
+  void (*fn)(Ctx&);
+  int min_out;
+};
+
+const OpEntry kOps[] = {
+    {"QuantizeLinear", op_quantize_linear, 1},
+    {"DequantizeLinear", op_dequantize_linear, 1},
+    {"DynamicQuantizeLinear", op_dynamic_quantize_linear, 1},
+    {"MatMulInteger", op_matmul_integer, 1},
+    {"QLinearMatMul", op_qlinear_matmul, 1},
+    {"QLinearConv", op_qlinear_conv, 1},
+    {"ConvInteger", op_conv_integer, 1},
+    {"Conv", op_conv, 1},
+    {"MatMul", op_matmul, 1},
+    {"Gemm", op_gemm, 1},
+    {"OxiInstanceNorm", op_oxi_instance_norm, 1},
+    {"Add", [](Ctx& c) { binary_op(c, [](float a, float b) { return a + b; }); }, 1},
+    {"Sub", [](Ctx& c) { binary_op(c, [](float a, float b) { return a - b; }); }, 1},
+    {"Mul", [](Ctx& c) { binary_op(c, [](float a, float b) { return a * b; }); }, 1},
+    {"Div", [](Ctx& c) { binary_op(c, [](float a, float b) { return a / b; }); }, 1},
+    {"Relu", [](Ctx& c) { unary_op(c, [](float v) { return std::max(v, 0.0f); }); }, 1},
+    {"Tanh", [](Ctx& c) { unary_op(c, [](float v) { return std::tanh(v); }); }, 1},
+    {"Sigmoid", [](Ctx& c) { unary_op(c, [](float v) { return 1.0f / (1.0f + std::exp(-v)); }); }, 1},
+    {"Silu", [](Ctx& c) { unary_op(c, [](float v) { return v / (1.0f + std::exp(-v)); }); }, 1},
+    {"PRelu", op_prelu, 1},
+    {"MaxPool", op_max_pool, 1},
+    {"GlobalAveragePool", op_global_average_pool, 1},
+    {"Flatten", op_flatten, 1},
+    {"Reshape", op_reshape, 1},
+    {"Concat", op_concat, 1},
+    {"Pad", op_pad, 1},
+    {"Resize", op_resize, 1},
+    {"Cast", op_identity, 1},
+    {"Identity", op_identity, 1},
+};
+
+}  // namespace
+
+extern "C" {
+
+int oxo_run_node(const char* op_type, const oxo_tensor* inputs, int32_t n_inputs, const oxo_attr* attrs, int32_t n_attrs, oxo_tensor* outputs,
+                 int32_t n_outputs) {
+  for (int i = 0; i < n_outputs; ++i) std::memset(&outputs[i], 0, sizeof(oxo_tensor));
+  try {
+    for (const OpEntry& e : kOps) {
+      if (std::strcmp(e.name, op_type) == 0) {
+        if (n_outputs < e.min_out) fail(OXO_ERR_INTERNAL, "%s: expected at least %d output slot(s)", op_type, e.min_out);
+        Ctx c{op_type, inputs, n_inputs, Attrs{attrs, n_attrs}, outputs, n_outputs};
+        e.fn(c);
+        return OXO_OK;
+      }
+    }
+    fail(OXO_ERR_UNSUPPORTED, "operator '%s' is not covered by the oracle", op_type);
+  } catch (const Fail& f) {
+    for (int i = 0; i < n_outputs; ++i) oxo_free_tensor(&outputs[i]);
+    return f.code;
+  } catch (const std::exception& e) {
+    g_err = e.what();
+    for (int i = 0; i < n_outputs; ++i) oxo_free_tensor(&outputs[i]);
+    return OXO_ERR_INTERNAL;
+  }
+}
+
+void oxo_free_tensor(oxo_tensor* t) {
+  if (t && t->data) {
+    std::free(t->data);
+    t->data = nullptr;
+  }
+}
+
+const char* oxo_last_error(void) { return g_err.c_str(); }
+void oxo_set_threads(int32_t threads) { g_threads = threads < 1 ? 1 : threads; }
+int32_t oxo_get_threads(void) { return g_threads; }
+void oxo_set_float_accum(int32_t mode) { g_float_accum = mode ? 1 : 0; }
+double oxo_round_ties_even_f64(double v) { return round_ties_even_f64(v); }
+float oxo_round_ties_even_f32(float v) { return round_ties_even_f32_native(v); }
+float oxo_requantize(int64_t acc, float combined, int32_t zero_point, int64_t lo, int64_t hi) {
+  return requantize(acc, combined, zero_point, SatRange{lo, hi});
+}
+
+}  // extern "C"
