@@ -1,0 +1,323 @@
+"""Benchmark of the B200 execution path on the reference's headline configurations.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c5|c1] [--impl reference]
+
+A step is one pass of the hot path over one batch of seeded synthetic input.  The default
+workload is ResNet-50 v1.5, f32 graph, batch 32 (TF32 tensor-core contractions); `c5` is the
+QLinearConv INT8 ResNet-50 at batch 128 per GPU, `c1` the INT8 MLP.  With N > 1 (launched by
+torchrun, one rank per GPU) every rank holds a full weight replica and runs its own batch:
+the path shards along the batch only, there is no data-path collective, and the scaling is weak.
+
+One JSON line is printed by rank 0:
+  value      images/s (rows/s for c1) with inputs resident in HBM, device time from CUDA events on
+             the launching stream, max over ranks; L2 is flushed between timed steps
+  e2e        the same metric through the public call (oxb200_run) with pinned HOST buffers:
+             host-to-device copy of the batch, the run, device-to-host copy of the result
+  roofline   the tensor-core contraction kernel: algorithmic ops of its launches / their summed
+             CUDA-event durations, against the measured peak
+  cpu_baseline  the CPU oracle (a port of the reference's CPU operators) timed on this host's
+             cores on a bounded sample of the same workload
+
+`--impl reference` times that CPU port alone on all host threads (the reference itself is a Rust
+project and cannot be built in this environment).
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+WORKLOADS = {
+    "c2": dict(name="resnet50_v1.5_f32_b32", metric="images_per_s", unit="images/s", dtype="tf32", batch=32),
+    "c5": dict(name="resnet50_qlinearconv_int8_b128_per_gpu", metric="images_per_s", unit="images/s", dtype="i8", batch=128),
+    "c1": dict(name="int8_mlp_64x1024-4096-4096-1024", metric="rows_per_s", unit="rows/s", dtype="i8", batch=64),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def build_workload(key, batch):
+    from oxionnx_b200 import models
+    if key == "c2":
+        return models.build_resnet50_f32(batch=batch)
+    if key == "c5":
+        return models.build_resnet50_qlinear(batch=batch)
+    return models.build_int8_mlp(rows=batch)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            if not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples inside the timed region"])
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def pinned_array(shape, lib):
+    n = int(np.prod(shape))
+    ptr = lib.oxb200_host_alloc(n * 4)
+    if not ptr:
+        raise RuntimeError("pinned allocation failed")
+    arr = np.ctypeslib.as_array(ctypes.cast(ptr, ctypes.POINTER(ctypes.c_float)), shape=(n,)).reshape(shape)
+    return arr, ptr
+
+
+def cpu_baseline(key, graph_builder_batch, sample, threads):
+    """The CPU oracle on `sample` units of the workload with `threads` host threads."""
+    import oracle
+    graph, weights, feeds, _ = build_workload(key, sample)
+    f = feeds(sample) if key != "c1" else feeds()
+    oracle.set_threads(threads)
+    oracle.set_float_accum(1)
+    t0 = time.time()
+    oracle.run_graph(graph, weights, f, keep_all=False)
+    dt = time.time() - t0
+    oracle.set_float_accum(0)
+    oracle.set_threads(1)
+    return sample / dt, dt
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU port of the reference's operators, all host threads."""
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    sample = {"c2": 2, "c5": 1, "c1": 64}[args.workload]
+    times = []
+    for i in range(args.warmup + args.steps):
+        v, dt = cpu_baseline(args.workload, w["batch"], sample, cores)
+        if i >= args.warmup:
+            times.append(dt)
+        if sum(times) > 150:
+            break
+    steps = len(times)
+    value = sample * steps / sum(times)
+    line = {
+        "impl": "reference", "metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": 1000.0 * sum(times) / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32" if args.workload == "c2" else "i64",
+        "data": "synthetic", "config": {"workload": w["name"], "sample": f"{sample} {w['unit'].split('/')[0]} per step"},
+        "cpu_baseline": {"value": value, "unit": w["unit"], "cores": cores, "kind": "port",
+                         "sample": f"{sample} {w['unit'].split('/')[0]} per step through the CPU oracle; the Rust reference cannot be built here"},
+        "e2e": {"value": value, "unit": w["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the configuration's)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-path", default="auto", choices=["auto", "direct"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    dist = None
+    torch = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from oxionnx_b200 import _ffi
+    from oxionnx_b200.session import Session
+    lib = _ffi.lib()
+    w = WORKLOADS[args.workload]
+    batch = args.batch or w["batch"]
+    graph, weights, feeds, info = build_workload(args.workload, batch)
+    f = feeds(batch, f"{args.workload}_in_rank{rank}") if args.workload != "c1" else feeds()
+    sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).build_from_graph(graph, weights)
+
+    # pinned host staging for the end-to-end leg
+    in_name = graph.input_names[0]
+    host_in, in_ptr = pinned_array(f[in_name].shape, lib)
+    host_in[...] = f[in_name]
+    feeds_pinned = {in_name: host_in}
+    sess.ensure_planned(feeds_pinned)
+
+    # L2 flush between timed steps: a 256 MiB memset (L2 is 126 MB)
+    import torch
+    torch.cuda.set_device(local_rank)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{local_rank}")
+
+    def flush_l2():
+        flush.zero_()
+        torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident leg ----
+    sess.upload(feeds_pinned)
+    for _ in range(args.warmup):
+        sess.run_resident(1)
+    c0 = sess.cuda_cache_counters()
+    sampler = ClockSampler(int(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[local_rank]) if os.environ.get("CUDA_VISIBLE_DEVICES") else local_rank)
+    sampler.start()
+    barrier()
+    t_begin = time.time()
+    step_ms = []
+    conv_ms, conv_ops, conv_launches = 0.0, 0.0, 0
+    glue_ms, glue_bytes = 0.0, 0.0
+    for _ in range(args.steps):
+        flush_l2()
+        step_ms.append(sess.run_resident(1))
+        for s in sess.steps():
+            if s["ms"] < 0:
+                continue
+            if s["kernel"].startswith("umma"):
+                conv_ms += s["ms"]
+                conv_ops += s["work"]
+                conv_launches += 1
+            elif s["work_is_bytes"]:
+                glue_ms += s["ms"]
+                glue_bytes += s["work"]
+    barrier()
+    t_end = time.time()
+    clocks = sampler.stop(t_begin, t_end)
+    c1 = sess.cuda_cache_counters()
+    total_ms = sum(step_ms)
+    if dist is not None:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    value = world * batch * args.steps / (total_ms / 1000.0)
+
+    # ---- end-to-end leg: pinned host buffers through the public run call ----
+    out = sess.run(feeds_pinned)
+    for _ in range(2):
+        sess.run(feeds_pinned)
+    e2e_ms = []
+    barrier()
+    for _ in range(args.steps):
+        flush_l2()
+        out = sess.run(feeds_pinned)
+        e2e_ms.append(float(lib.oxb200_last_run_ms(sess.ctx.handle)))
+    barrier()
+    e2e_total = sum(e2e_ms)
+    if dist is not None:
+        t = torch.tensor([e2e_total], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_total = float(t.item())
+    e2e_value = world * batch * args.steps / (e2e_total / 1000.0)
+    h2d = int(host_in.size * 4)
+    d2h = int(sum(v.size for v in out.values()) * 4)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        kind = w["dtype"]
+        # TF32 runs at half, INT8 at twice the measured dense bf16 rate (architectural ratios); the kernels
+        # are timed inside a long step, so the sustained figure is the denominator.
+        factor = {"tf32": 0.5, "i8": 2.0}[kind]
+        peak = peaks["bf16_sustained"] * factor
+        achieved = (conv_ops / (conv_ms / 1000.0) / 1e12) if conv_ms > 0 else 0.0
+        roofline = {
+            "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s" if kind == "i8" else "TFLOP/s",
+            "frac": achieved / peak if peak else None, "traffic": None,
+            "kernel": "umma_conv_kernel (tcgen05 implicit GEMM)", "launches_per_step": conv_launches // max(args.steps, 1),
+            "avg_launch_ms": conv_ms / max(conv_launches, 1), "share_of_step": conv_ms / total_ms if world == 1 else None,
+            "peak_basis": f"{factor} x bf16_tflops_sustained of {peaks['source']} ({peaks['bf16_sustained']})",
+            "glue_gbs": (glue_bytes / (glue_ms / 1000.0) / 1e9) if glue_ms > 0 else None, "hbm_peak_gbs": peaks["hbm_gbs"],
+        }
+        line = {
+            "metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind,
+            "data": "synthetic",
+            "config": {"workload": w["name"], "per_gpu_batch": batch, "global_batch": batch * world, "parallelism": f"batch-sharded replicas x{world}, no collective",
+                       "l2": "flushed between timed steps (256 MiB memset)", "algorithmic_ops_per_step": info["ops"], "kernel_path": args.kernel_path},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": w["unit"], "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_total / args.steps},
+            "gpu_launches": int(c1["kernel_launches"] - c0["kernel_launches"]),
+            "launch_mix": {"umma": int(c1["umma_launches"] - c0["umma_launches"]), "direct": int(c1["simt_launches"] - c0["simt_launches"]),
+                           "glue": int(c1["glue_launches"] - c0["glue_launches"])},
+            "roofline": roofline,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            sample = {"c2": 2, "c5": 1, "c1": 64}[args.workload]
+            cores = os.cpu_count() or 1
+            v, dt = cpu_baseline(args.workload, batch, sample, cores)
+            line["cpu_baseline"] = {"value": v, "unit": w["unit"], "cores": cores, "kind": "port",
+                                    "sample": f"{sample} {w['unit'].split('/')[0]} through the CPU oracle in {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    lib.oxb200_host_free(in_ptr)
+    sess.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

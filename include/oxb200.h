@@ -1,0 +1,239 @@
+/*
+ * oxb200 -- C ABI of the B200 (sm_100a) execution provider for OxiONNX's dense-contraction
+ * hot path: Conv, Gemm/MatMul, QLinearConv, QLinearMatMul, MatMulInteger, ConvInteger and
+ * their quantise / dequantise / normalise glue.
+ *
+ * The entry points mirror, one for one, the Rust interface of the reference's CUDA
+ * execution provider (crate oxionnx-cuda of cool-japan/oxionnx v0.1.7); each declaration
+ * cites the reference item it replaces.  Conventions kept from the reference:
+ *
+ *  - Tensors cross the boundary as flat f32 lanes plus a shape (oxionnx-core
+ *    src/tensor/types.rs:355).  Quantised values are integers carried in f32 lanes.
+ *  - Three-way outcome (oxionnx-cuda src/error.rs:75-111, root crate
+ *    src/session/run/sequential.rs:994-1032): DECLINED = "not mine, let the next provider
+ *    try" (normal); FAILED = an error, the caller logs it and falls back; VERIFY_MISMATCH =
+ *    the device result was proved wrong against the shadow check, the run must fail.
+ *  - "Necessary, not sufficient": oxb200_is_supported_op()==0 guarantees a decline; 1 may
+ *    still decline (oxionnx-cuda src/lib.rs:184-195).  Unknown attributes decline.
+ *  - Malformed quantised inputs (non-finite lanes, zero scales, mis-sized zero points)
+ *    decline so that the CPU operator raises its own typed error.
+ *  - No exceptions, aborts or panics cross this boundary; every failure is a status plus a
+ *    message readable through oxb200_last_error().
+ *  - No CPU fallback exists inside the library: if no CUDA device or driver is present,
+ *    oxb200_ctx_create fails.
+ */
+#ifndef OXB200_H
+#define OXB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OXB200_MAX_RANK 8
+
+typedef struct oxb200_ctx oxb200_ctx;       /* replaces oxionnx_cuda::CudaContext (src/context.rs:219) */
+typedef struct oxb200_tensor oxb200_tensor; /* replaces oxionnx_cuda::CudaDeviceTensor (src/activation.rs:85) */
+
+/* Outcome of a dispatch: Result<Option<CudaDispatchOutcome>, OnnxError> flattened
+ * (oxionnx-cuda src/activation.rs:221-245, src/lib.rs:561). */
+enum {
+  OXB200_OK_HOST = 0,         /* Ok(Some(Host(..)))   */
+  OXB200_OK_DEVICE = 1,       /* Ok(Some(Device(..))) */
+  OXB200_DECLINED = 2,        /* Ok(None)             */
+  OXB200_FAILED = 3,          /* Err(e)               */
+  OXB200_VERIFY_MISMATCH = 4  /* Err(e) with is_verify_mismatch(e) (src/error.rs:106) */
+};
+
+/* CudaOutputPlacement (oxionnx-cuda src/activation.rs:221) */
+enum { OXB200_PLACE_HOST = 0, OXB200_PLACE_DEVICE = 1 };
+
+/* One attribute of Attributes (oxionnx-core src/graph.rs:696-705). */
+enum { OXB200_ATTR_INT = 0, OXB200_ATTR_FLOAT = 1, OXB200_ATTR_STRING = 2, OXB200_ATTR_INTS = 3, OXB200_ATTR_FLOATS = 4 };
+typedef struct {
+  const char* name;
+  int32_t kind;
+  int64_t i;
+  float f;
+  const char* s;
+  const int64_t* ints;
+  const float* floats;
+  uint64_t len;
+} oxb200_attr;
+
+/* Node (oxionnx-core src/graph.rs:851): op, name, inputs ("" = omitted), outputs, attrs. */
+typedef struct {
+  const char* op_type;
+  const char* name;
+  const char* const* inputs;
+  uint32_t n_inputs;
+  const char* const* outputs;
+  uint32_t n_outputs;
+  const oxb200_attr* attrs;
+  uint32_t n_attrs;
+} oxb200_node;
+
+/* InputBinding (oxionnx-cuda src/activation.rs:285): a host tensor (f32 lanes) or a value
+ * that already lives on the device. */
+typedef struct {
+  const char* name;
+  const float* lanes; /* host f32 lanes, NULL when `resident` is set */
+  uint64_t len;
+  const uint64_t* shape;
+  uint32_t rank;
+  oxb200_tensor* resident;
+} oxb200_operand;
+
+/* One output of a dispatch or a fetch of a run. */
+typedef struct {
+  float* lanes;  /* caller-owned destination for host results (may be NULL when only a device result is wanted) */
+  uint64_t cap;  /* capacity of `lanes` in elements */
+  uint64_t len;  /* out: number of elements of the result */
+  uint64_t shape[OXB200_MAX_RANK];
+  uint32_t rank;
+  oxb200_tensor* resident; /* out: device tensor when the outcome is OK_DEVICE */
+} oxb200_result;
+
+/* Declared shape of a graph input (TensorInfo, oxionnx-core src/graph.rs:862). */
+typedef struct {
+  const char* name;
+  const uint64_t* shape;
+  uint32_t rank;
+} oxb200_value_info;
+
+/* Context options.  Zero-initialise, set struct_size, then override.  The environment
+ * variables of the reference keep their names and truthiness rule (oxionnx-cuda
+ * src/context.rs:40-45,179-192) and are read by oxb200_config_from_env(). */
+typedef struct {
+  uint32_t struct_size;
+  int32_t verify;             /* OXIONNX_CUDA_VERIFY: shadow-verify hook enabled */
+  int32_t strict;             /* OXIONNX_CUDA_STRICT */
+  int32_t residency;          /* OXIONNX_CUDA_RESIDENCY (default 1) */
+  int32_t cuda_graph;         /* OXIONNX_CUDA_GRAPH: replay a planned session as one CUDA graph */
+  int32_t kernel_path;        /* 0 auto (tcgen05 where eligible), 1 force the direct CUDA-core kernels */
+  int32_t keep_intermediates; /* 1: every value keeps a private arena slot (per-node inspection) */
+  int32_t profile;            /* 1: record per-node CUDA-event timings during runs */
+  int32_t reserved[8];
+} oxb200_config;
+
+/* CacheCounters (oxionnx-cuda src/residency.rs:141-240) plus arena figures. */
+typedef struct {
+  uint64_t uploads, upload_bytes;
+  uint64_t downloads, download_bytes;
+  uint64_t fences;
+  uint64_t weight_uploads, weight_bytes_resident;
+  uint64_t arena_bytes, arena_peak_bytes, arena_slots;
+  uint64_t kernel_launches;
+  uint64_t umma_launches, simt_launches, glue_launches;
+  uint64_t dispatches, declines, failures;
+} oxb200_counters;
+
+/* ---- pure predicates (no device) ---------------------------------------------------- */
+
+/* oxionnx_cuda::is_supported_op (src/lib.rs:217).  Adds the INT8 family the reference's
+ * own CUDA provider never claimed. */
+int oxb200_is_supported_op(const char* op_type);
+/* oxionnx_cuda::accepts_resident_slot (src/lib.rs:419) */
+int oxb200_accepts_resident_slot(const char* op_type, uint32_t slot);
+/* decide_placement (root crate src/execution_providers.rs:352-387).  policy: 0 CpuOnly,
+ * 1 Auto{gpu_threshold_bytes}, 2 Manual with `manual_pin` (0 unmapped, 1 pinned to CPU,
+ * 2 pinned to this provider).  Returns 1 when the node goes to this provider. */
+int oxb200_decide_placement(int policy, uint64_t gpu_threshold_bytes, int manual_pin, const char* op_type, uint64_t output_bytes);
+/* is_verify_mismatch (src/error.rs:106): does the message carry the proved-wrong marker? */
+int oxb200_is_verify_mismatch(const char* message);
+/* env_flag truthiness (src/context.rs:179-192) and config assembly from the environment */
+int oxb200_env_truthy(const char* value);
+void oxb200_config_from_env(oxb200_config* cfg);
+
+/* ---- context ------------------------------------------------------------------------- */
+
+int oxb200_device_count(void);
+/* CudaContext::try_new_with (src/context.rs:362-467): one context, one stream, one device. */
+int oxb200_ctx_create(int device_ordinal, const oxb200_config* cfg, oxb200_ctx** out);
+void oxb200_ctx_destroy(oxb200_ctx* ctx);
+const char* oxb200_last_error(const oxb200_ctx* ctx); /* ctx may be NULL: last error of the calling thread */
+/* CudaContext::cache_counters (src/context.rs:394-430) */
+void oxb200_get_counters(const oxb200_ctx* ctx, oxb200_counters* out);
+/* CudaContext::release_device_caches */
+int oxb200_release_device_caches(oxb200_ctx* ctx);
+
+/* Page-locked host memory for feeds and fetches (the reference's pinned staging,
+ * src/residency.rs:1147-1312, handed to the caller so no extra host copy is needed). */
+void* oxb200_host_alloc(size_t bytes);
+void oxb200_host_free(void* p);
+
+/* ---- weights ------------------------------------------------------------------------- */
+
+/* The `weights: &HashMap<String,Tensor>` argument of try_cuda_dispatch_resident
+ * (src/lib.rs:561): initializers are registered once, are invariant for the context's
+ * life, and are uploaded/packed on first use by a planned session or a dispatch
+ * (initializer_id, src/dispatch_helpers.rs:21-64). The lanes are copied. */
+int oxb200_weight_register(oxb200_ctx* ctx, const char* name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank);
+/* CudaContext::is_weight_resident */
+int oxb200_is_weight_resident(const oxb200_ctx* ctx, const char* name);
+
+/* ---- per-node dispatch --------------------------------------------------------------- */
+
+/* try_cuda_dispatch_resident (src/lib.rs:561) / try_cuda_dispatch (src/lib.rs:354).
+ * `operands` are positionally aligned with node->inputs; an operand whose name is a
+ * registered weight may pass lanes == NULL.  `results` has node->n_outputs entries. */
+int oxb200_dispatch(oxb200_ctx* ctx, const oxb200_node* node, const oxb200_operand* operands, uint32_t n_operands, int want_placement,
+                    oxb200_result* results, uint32_t n_results);
+
+/* shadow_verify (oxionnx-cuda src/reference.rs:115-119,198-240): the caller owns the CPU
+ * operators and hands the CPU result of the node just dispatched; a difference beyond
+ * ATOL 1e-4 / RTOL 1e-3 is "proved wrong".  Returns OK_HOST, or VERIFY_MISMATCH under
+ * strict mode / FAILED otherwise, with the reference's marker in the message. */
+int oxb200_shadow_verify(oxb200_ctx* ctx, const char* op_type, const float* device_lanes, const float* cpu_lanes, uint64_t len);
+
+/* CudaDeviceTensor::{shape,len,read_back} (src/activation.rs:116-208) and
+ * CudaContext::recycle_activation (src/context.rs:394). */
+int oxb200_tensor_shape(const oxb200_tensor* t, uint64_t* shape, uint32_t* rank, uint64_t* len);
+int oxb200_tensor_read_back(oxb200_ctx* ctx, const oxb200_tensor* t, float* dst_lanes, uint64_t cap);
+void oxb200_tensor_release(oxb200_ctx* ctx, oxb200_tensor* t);
+
+/* ---- planned, device-resident session run --------------------------------------------- */
+
+/* What Session::build_from_graph + StaticRunPlan::build + MemoryPlan::compute become
+ * (root crate src/session/loading.rs:181, src/session/run/plan.rs:77,
+ * src/memory/types.rs:347-452): shapes and device dtypes are inferred for every value,
+ * weights are packed and uploaded, kernels are selected and every intermediate gets a
+ * lifetime-planned slot of the device arena.  `nodes` must be topologically sorted.
+ * Returns OK_DEVICE, or DECLINED/FAILED naming the first node the provider cannot take. */
+int oxb200_session_plan(oxb200_ctx* ctx, const oxb200_node* nodes, uint32_t n_nodes, const oxb200_value_info* inputs, uint32_t n_inputs,
+                        const char* const* outputs, uint32_t n_outputs);
+/* Session::run (root crate src/session/run/entry.rs:92): host feeds in, host fetches out;
+ * every intermediate stays in HBM.  Copies are asynchronous on the context's stream and
+ * the call returns after one fence. */
+int oxb200_run(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds, oxb200_result* fetches, uint32_t n_fetches);
+/* Device time of the last oxb200_run in milliseconds, taken with CUDA events on the context's
+ * stream from before the first host-to-device copy to after the last device-to-host copy. */
+float oxb200_last_run_ms(const oxb200_ctx* ctx);
+/* The same run split for measurement: stage feeds, run the planned launches `iters`
+ * times with everything resident (no host traffic), read fetches. */
+int oxb200_upload_feeds(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds);
+int oxb200_run_resident(oxb200_ctx* ctx, uint32_t iters, float* elapsed_ms);
+int oxb200_download_fetches(oxb200_ctx* ctx, oxb200_result* fetches, uint32_t n_fetches);
+/* Read any planned value after a run (needs keep_intermediates=1 for intermediates). */
+int oxb200_fetch_value(oxb200_ctx* ctx, const char* name, oxb200_result* out);
+
+/* Plan introspection (NodeProfile, root crate src/session/types.rs:18-27): one record per
+ * planned step. */
+typedef struct {
+  const char* node_name;
+  const char* op_type;
+  const char* kernel;   /* which kernel family runs it */
+  double work;          /* algorithmic ops (contractions) or bytes (glue) per launch */
+  int32_t work_is_bytes;
+  float last_ms;        /* CUDA-event time of the last profiled run (profile=1), else -1 */
+  uint64_t launches;
+} oxb200_step_info;
+uint32_t oxb200_plan_step_count(const oxb200_ctx* ctx);
+int oxb200_plan_step_info(const oxb200_ctx* ctx, uint32_t index, oxb200_step_info* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OXB200_H */

@@ -1,0 +1,148 @@
+// Launch interface of the device kernels (glue, direct CUDA-core contractions, tcgen05
+// contractions).  Everything here is host-callable and enqueues work on a stream; nothing
+// synchronises.
+#pragma once
+
+#include "common.hpp"
+
+namespace oxb {
+namespace k {
+
+// Canonical 4-D view used by the element-wise kernels.  Any tensor is viewed as logical
+// [N, C, H, W]: rank-4 activations directly, a per-axis operation on another rank as
+// (outer, axis extent, inner, 1), everything else as a flat run in N.
+struct Dims4 {
+  int64_t N, C, H, W;
+  int64_t numel() const { return N * C * H * W; }
+};
+
+struct TensorRef {
+  void* ptr;
+  DT dt;
+  Layout layout;
+  Dims4 d;
+};
+
+// ---- layout / dtype conversion --------------------------------------------------------
+// Copies `src` to `dst` element by element converting memory order and storage type
+// (integers <-> f32 lanes are exact for every value the path stores; i32 -> f32 rounds to
+// nearest even above 2^24 exactly like the reference's `as f32`).
+void convert(const TensorRef& src, const TensorRef& dst, cudaStream_t s);
+
+// ---- quantisation glue ------------------------------------------------------------------
+// y = clamp(rne(x / scale[ch]) + zp[ch], lo, hi); f32 division and rounding, no FMA.
+// scale/zp are device f32 arrays of length 1 (per tensor) or C (per channel of the view).
+void quantize_linear(const TensorRef& x, const TensorRef& y, const float* scale, int64_t n_scale, const float* zp, int64_t n_zp, float lo,
+                     float hi, cudaStream_t s);
+// Same arithmetic with host-known per-tensor parameters and identical memory order on both
+// sides: 16 lanes per thread through 16-byte accesses.  Fails if the operand is not eligible
+// (callers check quantize_linear_scalar_ok first).
+bool quantize_linear_scalar_ok(const TensorRef& x, const TensorRef& y);
+void quantize_linear_scalar(const TensorRef& x, const TensorRef& y, float scale, float zp, float lo, float hi, cudaStream_t s);
+// y = (x - zp[ch]) * scale[ch], two separately rounded f32 operations.
+void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scale, int64_t n_scale, const float* zp, int64_t n_zp,
+                       cudaStream_t s);
+// DynamicQuantizeLinear: params[0] = y_scale, params[1] = y_zero_point (f32 lanes on the
+// device); `scratch` is 2 floats used for the min/max reduction.
+void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s);
+
+// ---- element-wise -----------------------------------------------------------------------
+enum BinOp { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_DIV = 3 };
+enum UnOp { UN_RELU = 0, UN_TANH = 1, UN_SIGMOID = 2, UN_SILU = 3, UN_COPY = 4 };
+// out = op(a, b) with numpy broadcasting expressed through per-axis extents of 1 in the
+// views; optional fused relu afterwards; round_tf32 rounds the f32 result to TF32
+// (round-to-nearest, ties away) for a following tensor-core contraction.
+void binary(const TensorRef& a, const TensorRef& b, const TensorRef& out, int op, int relu_after, int round_tf32, cudaStream_t s);
+void unary(const TensorRef& x, const TensorRef& y, int op, cudaStream_t s);
+// y = x >= 0 ? x : x * slope[c or 0]
+void prelu(const TensorRef& x, const TensorRef& y, const float* slope, int64_t n_slope, cudaStream_t s);
+
+// ---- pooling / normalisation ------------------------------------------------------------
+struct PoolShape {
+  int kh, kw, sh, sw, pt, pl, dh, dw, P, Q;
+};
+void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaStream_t s);
+// Sequential f32 sum over the plane in (h, w) order, then one division: the order the
+// reference's global_avg_pool uses, so the result is bit-identical.
+void global_avg_pool(const TensorRef& x, const TensorRef& y, int round_tf32, cudaStream_t s);
+// OxiInstanceNorm over (n, c) planes, two-pass variance about the mean; optional fused
+// per-sample modulation y = norm * scale[n,c] + shift[n,c] (both may be NULL).
+void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const float* scale_nc, const float* shift_nc, cudaStream_t s);
+
+// ---- spatial glue -----------------------------------------------------------------------
+// mode 0 nearest, 1 linear; coord 0 half_pixel, 1 pytorch_half_pixel, 2 asymmetric,
+// 3 align_corners; nearest_rule 0 round_prefer_floor, 1 floor, 2 ceil, 3 round_prefer_ceil
+void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, cudaStream_t s);
+// mode 0 constant, 1 reflect, 2 edge (spatial and channel pads of a rank-4 view)
+void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, int pc, int ph, int pw, cudaStream_t s);
+// Copies `x` into the channel range [c_off, c_off + x.C) of `y` (Concat on the channel axis)
+// or, axis 0/2/3, the matching range of that axis.
+void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s);
+
+// ---- contractions -----------------------------------------------------------------------
+struct ConvShape {
+  int N, C, H, W;     // input (per group channels = C / group)
+  int OC, R, S;       // filter
+  int P, Q;           // output spatial
+  int sh, sw, pt, pl, pb, pr, dh, dw, group;
+  int64_t M() const { return (int64_t)N * P * Q; }
+  int64_t K() const { return (int64_t)(C / group) * R * S; }
+  double ops() const { return 2.0 * (double)M() * (double)OC * (double)K(); }
+};
+
+enum EpiMode { EPI_F32 = 0, EPI_REQUANT = 1, EPI_INT32 = 2 };
+
+struct Epilogue {
+  int mode = EPI_F32;
+  // EPI_F32: out = act(acc + bias_f[oc]); act 0 none, 1 relu, 2 clip
+  const float* bias_f = nullptr;
+  int act = 0;
+  float clip_lo = 0.f, clip_hi = 0.f;
+  int round_tf32 = 0;
+  // integer modes.  Direct kernels subtract zero points per element; the tensor-core kernel
+  // computes raw = sum(x*w) and applies acc = raw + bias_i[oc] - x_zp * wsum[oc].
+  const int32_t* bias_i = nullptr;
+  const int32_t* wsum = nullptr;
+  int x_zp = 0;
+  const float* x_zp_dev = nullptr;  // when set, the zero point is read from this device f32 lane
+  const int32_t* x_zp_rows = nullptr;  // direct kernels: per-row zero point of a matmul A operand (length M)
+  const int32_t* w_zp = nullptr;    // direct kernels: per-oc (n_w_zp == OC) or single
+  int n_w_zp = 0;
+  // EPI_REQUANT: q = clamp(rne(f64(acc) * f64(combined[oc]) + y_zp), lo, hi)
+  const float* combined = nullptr;
+  int y_zp = 0;
+  int lo = 0, hi = 255;
+  int relu_fused = 0;  // integer: clamp below at max(lo, 0) (a following Relu node)
+  DT out_dt = DT::F32;
+};
+
+// Direct CUDA-core convolution (and matmul as a 1x1 convolution): general geometry
+// (groups, dilations, asymmetric pads), any zero points, i64 accumulation.
+// x: NHWC (or PLAIN when x_plain_nchw, used by the stem to read a graph input directly),
+// w: packed [R][S][C/group][OC] in w_dt, out: NHWC [M, OC].
+void conv_direct(const void* x, DT x_dt, int x_plain_nchw, const void* w, DT w_dt, void* out, const ConvShape& cs, const Epilogue& e,
+                 cudaStream_t s);
+
+// Batched plain f32 matmul C[b] = A[b] (MxK) * B[b] (KxN) with optional broadcast of either
+// side (stride 0), used for activation x activation products.
+void matmul_f32_direct(const float* a, const float* b, float* c, int64_t batch, int64_t M, int64_t K, int64_t N, int64_t a_bstride,
+                       int64_t b_bstride, cudaStream_t s);
+
+// tcgen05 implicit-GEMM plan (tensor maps are built once at plan time).
+struct UmmaPlan;
+// kind: 0 = i8 (A u8/s8, B s8/u8, s32 accumulate), 1 = tf32 (f32 storage, f32 accumulate).
+// Returns nullptr with `why` filled when the shape is not eligible.
+UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt, void* out, const ConvShape& cs, const Epilogue& e, int kind,
+                           std::string* why);
+void umma_plan_destroy(UmmaPlan* p);
+void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s);
+const char* umma_plan_desc(const UmmaPlan* p);
+// Re-point a plan at new buffers (arena moved) is not supported: plans are rebuilt.
+
+// Packed weight size helpers for the tensor-core path: weights are laid out [OC][R*S*Cpad]
+// (K-major rows), Cpad = C rounded up to the channel block.
+int umma_channel_block(int C, int kind);  // 0 when C is not eligible
+bool umma_available();                    // driver entry point for tensor-map encoding found
+
+}  // namespace k
+}  // namespace oxb

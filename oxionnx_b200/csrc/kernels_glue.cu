@@ -1,0 +1,642 @@
+// Memory-bound glue kernels of the oxb200 path (sm_100a).  All of them stream their operands
+// once through HBM with vectorised accesses where the layout allows; none of them uses a
+// fused multiply-add (this file is compiled with --fmad=false) because the reference rounds
+// every f32 operation separately and the quantisers sit right at rounding boundaries.
+#include "kernels.hpp"
+
+namespace oxb {
+namespace k {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(int64_t work, int per_block = kThreads) {
+  int64_t b = (work + per_block - 1) / per_block;
+  // Enough blocks to fill 148 SMs several times over, capped so the grid-stride loops stay
+  // in a sane range for very large tensors.
+  const int64_t cap = 148 * 64;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+__device__ __forceinline__ float load_as_f32(const void* p, DT dt, int64_t i) {
+  switch (dt) {
+    case DT::F32: return ((const float*)p)[i];
+    case DT::U8: return (float)((const uint8_t*)p)[i];
+    case DT::I8: return (float)((const int8_t*)p)[i];
+    case DT::I32: return __int2float_rn(((const int32_t*)p)[i]);
+    case DT::I16: return (float)((const int16_t*)p)[i];
+  }
+  return 0.f;
+}
+
+// Stores an f32 lane that holds an integer value (or a float for F32 storage).
+__device__ __forceinline__ void store_from_f32(void* p, DT dt, int64_t i, float v) {
+  switch (dt) {
+    case DT::F32: ((float*)p)[i] = v; break;
+    case DT::U8: ((uint8_t*)p)[i] = (uint8_t)__float2int_rn(fminf(fmaxf(v, 0.f), 255.f)); break;
+    case DT::I8: ((int8_t*)p)[i] = (int8_t)__float2int_rn(fminf(fmaxf(v, -128.f), 127.f)); break;
+    case DT::I32: ((int32_t*)p)[i] = __float2int_rn(v); break;
+    case DT::I16: ((int16_t*)p)[i] = (int16_t)__float2int_rn(fminf(fmaxf(v, -32768.f), 32767.f)); break;
+  }
+}
+
+struct Coord {
+  int64_t n, c, h, w;
+};
+
+__device__ __forceinline__ Coord decode(int64_t o, Layout L, const Dims4& d) {
+  Coord q;
+  if (L == Layout::NHWC) {
+    q.c = o % d.C;
+    o /= d.C;
+    q.w = o % d.W;
+    o /= d.W;
+    q.h = o % d.H;
+    q.n = o / d.H;
+  } else {
+    q.w = o % d.W;
+    o /= d.W;
+    q.h = o % d.H;
+    o /= d.H;
+    q.c = o % d.C;
+    q.n = o / d.C;
+  }
+  return q;
+}
+
+__device__ __forceinline__ int64_t encode(const Coord& q, Layout L, const Dims4& d) {
+  if (L == Layout::NHWC) return ((q.n * d.H + q.h) * d.W + q.w) * d.C + q.c;
+  return ((q.n * d.C + q.c) * d.H + q.h) * d.W + q.w;
+}
+
+// Offset of the broadcast source element for output coordinate q.
+__device__ __forceinline__ int64_t encode_bcast(const Coord& q, Layout L, const Dims4& d) {
+  Coord r;
+  r.n = d.N == 1 ? 0 : q.n;
+  r.c = d.C == 1 ? 0 : q.c;
+  r.h = d.H == 1 ? 0 : q.h;
+  r.w = d.W == 1 ? 0 : q.w;
+  return encode(r, L, d);
+}
+
+__device__ __forceinline__ float round_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+// ---------------------------------------------------------------------------------------
+__global__ void convert_kernel(const void* src, DT sdt, Layout sl, void* dst, DT ddt, Layout dl, Dims4 d, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t si = o;
+    if (sl != dl) si = encode(decode(o, dl, d), sl, d);
+    float v = load_as_f32(src, sdt, si);
+    if (sdt == DT::I32 && ddt == DT::I32) ((int32_t*)dst)[o] = ((const int32_t*)src)[si];
+    else store_from_f32(dst, ddt, o, v);
+  }
+}
+
+// NCHW -> NHWC (or back) through a shared-memory tile so both sides are coalesced.
+// View: [outer, A, B] -> [outer, B, A]; 32x32 tiles.
+template <typename TS, typename TD>
+__global__ void transpose_tiles(const TS* __restrict__ src, TD* __restrict__ dst, int64_t A, int64_t B) {
+  __shared__ float tile[32][33];
+  int64_t outer = blockIdx.z;
+  int64_t a0 = (int64_t)blockIdx.y * 32, b0 = (int64_t)blockIdx.x * 32;
+  const TS* s = src + outer * A * B;
+  TD* dptr = dst + outer * A * B;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    int64_t a = a0 + i, b = b0 + threadIdx.x;
+    if (a < A && b < B) tile[i][threadIdx.x] = (float)s[a * B + b];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    int64_t b = b0 + i, a = a0 + threadIdx.x;
+    if (a < A && b < B) dptr[b * A + a] = (TD)tile[threadIdx.x][i];
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+__global__ void quantize_kernel(const void* x, DT xdt, Layout xl, void* y, DT ydt, Layout yl, Dims4 d, const float* scale, int64_t ns,
+                                const float* zp, int64_t nz, float lo, float hi, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    Coord q = decode(o, yl, d);
+    int64_t xi = xl == yl ? o : encode(q, xl, d);
+    float v = load_as_f32(x, xdt, xi);
+    float s = scale[ns > 1 ? q.c : 0];
+    float z = zp ? zp[nz > 1 ? q.c : 0] : 0.f;
+    float r = __fadd_rn(rintf(__fdiv_rn(v, s)), z);
+    r = fminf(fmaxf(r, lo), hi);
+    store_from_f32(y, ydt, o, r);
+  }
+}
+
+// Per-tensor f32 -> 8-bit, same memory order on both sides: 16 elements per thread,
+// four 16-byte loads and one 16-byte store.
+__global__ void quantize_vec16_kernel(const float4* __restrict__ x, uint4* __restrict__ y, float scale, float zp, float lo, float hi,
+                                      int64_t n16) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float4 v = x[i * 4 + j];
+      float f[4] = {v.x, v.y, v.z, v.w};
+      uint32_t w = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float r = __fadd_rn(rintf(__fdiv_rn(f[e], scale)), zp);
+        r = fminf(fmaxf(r, lo), hi);
+        w |= ((uint32_t)__float2int_rn(r) & 0xffu) << (8 * e);
+      }
+      packed[j] = w;
+    }
+    y[i] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
+__global__ void dequantize_kernel(const void* x, DT xdt, Layout xl, void* y, Layout yl, Dims4 d, const float* scale, int64_t ns,
+                                  const float* zp, int64_t nz, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    Coord q = decode(o, yl, d);
+    int64_t xi = xl == yl ? o : encode(q, xl, d);
+    float v = load_as_f32(x, xdt, xi);
+    float s = scale[ns > 1 ? q.c : 0];
+    float z = zp ? zp[nz > 1 ? q.c : 0] : 0.f;
+    ((float*)y)[o] = __fmul_rn(__fsub_rn(v, z), s);
+  }
+}
+
+// ---- DynamicQuantizeLinear --------------------------------------------------------------
+// Order-independent min/max: floats are mapped to a monotone unsigned key so atomicMin/Max
+// on integers gives the exact float extrema.
+__device__ __forceinline__ uint32_t float_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+__global__ void minmax_init_kernel(uint32_t* keys) {
+  keys[0] = 0xffffffffu;  // running min key
+  keys[1] = 0u;           // running max key
+}
+
+__global__ void minmax_kernel(const float* __restrict__ x, int64_t n, uint32_t* keys) {
+  float mn = INFINITY, mx = -INFINITY;
+  int64_t n4 = n / 4;
+  const float4* x4 = (const float4*)x;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 v = x4[i];
+    mn = fminf(fminf(mn, v.x), fminf(v.y, fminf(v.z, v.w)));
+    mx = fmaxf(fmaxf(mx, v.x), fmaxf(v.y, fmaxf(v.z, v.w)));
+  }
+  for (int64_t i = n4 * 4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    mn = fminf(mn, x[i]);
+    mx = fmaxf(mx, x[i]);
+  }
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  __shared__ float smn[kThreads / 32], smx[kThreads / 32];
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    smn[warp] = mn;
+    smx[warp] = mx;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    mn = lane < kThreads / 32 ? smn[lane] : INFINITY;
+    mx = lane < kThreads / 32 ? smx[lane] : -INFINITY;
+    for (int off = 4; off > 0; off >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    if (lane == 0) {
+      atomicMin(&keys[0], float_key(mn));
+      atomicMax(&keys[1], float_key(mx));
+    }
+  }
+}
+
+// params[0] = y_scale, params[1] = y_zero_point
+__global__ void dynq_params_kernel(const uint32_t* keys, float* params) {
+  float max_x = fmaxf(key_float(keys[1]), 0.f);
+  float min_x = fminf(key_float(keys[0]), 0.f);
+  float span = (max_x == min_x) ? 1.0f : __fsub_rn(max_x, min_x);
+  float y_scale = __fdiv_rn(span, 255.0f);
+  float izp = __fsub_rn(0.0f, __fdiv_rn(min_x, y_scale));
+  izp = fminf(fmaxf(izp, 0.f), 255.f);
+  params[0] = y_scale;
+  params[1] = rintf(izp);
+}
+
+__global__ void dynq_apply_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, const float* params, int64_t n) {
+  float s = params[0], z = params[1];
+  int64_t n4 = n / 4;
+  const float4* x4 = (const float4*)x;
+  uint32_t* y4 = (uint32_t*)y;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 v = x4[i];
+    float f[4] = {v.x, v.y, v.z, v.w};
+    uint32_t w = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float r = __fadd_rn(rintf(__fdiv_rn(f[e], s)), z);
+      r = fminf(fmaxf(r, 0.f), 255.f);
+      w |= ((uint32_t)__float2int_rn(r) & 0xffu) << (8 * e);
+    }
+    y4[i] = w;
+  }
+  for (int64_t i = n4 * 4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float r = __fadd_rn(rintf(__fdiv_rn(x[i], s)), z);
+    y[i] = (uint8_t)__float2int_rn(fminf(fmaxf(r, 0.f), 255.f));
+  }
+}
+
+// ---- element-wise ---------------------------------------------------------------------
+__device__ __forceinline__ float apply_bin(int op, float a, float b) {
+  switch (op) {
+    case BIN_ADD: return __fadd_rn(a, b);
+    case BIN_SUB: return __fsub_rn(a, b);
+    case BIN_MUL: return __fmul_rn(a, b);
+    default: return __fdiv_rn(a, b);
+  }
+}
+
+__global__ void binary_kernel(const void* a, DT adt, Layout al, Dims4 ad, const void* b, DT bdt, Layout bl, Dims4 bd, void* out, DT odt,
+                              Layout ol, Dims4 od, int op, int relu_after, int rtf32, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    Coord q = decode(o, ol, od);
+    float av = load_as_f32(a, adt, encode_bcast(q, al, ad));
+    float bv = load_as_f32(b, bdt, encode_bcast(q, bl, bd));
+    float r = apply_bin(op, av, bv);
+    if (relu_after) r = fmaxf(r, 0.f);
+    if (rtf32) r = round_tf32(r);
+    store_from_f32(out, odt, o, r);
+  }
+}
+
+// Same shape, same order, f32: four elements per thread with 16-byte accesses.
+__global__ void binary_vec4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out, int op,
+                                   int relu_after, int rtf32, int64_t n4) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 x = a[i], y = b[i];
+    float r[4] = {apply_bin(op, x.x, y.x), apply_bin(op, x.y, y.y), apply_bin(op, x.z, y.z), apply_bin(op, x.w, y.w)};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (relu_after) r[e] = fmaxf(r[e], 0.f);
+      if (rtf32) r[e] = round_tf32(r[e]);
+    }
+    out[i] = make_float4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+__global__ void unary_kernel(const void* x, DT xdt, void* y, DT ydt, int op, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    float v = load_as_f32(x, xdt, o);
+    float r;
+    switch (op) {
+      case UN_RELU: r = fmaxf(v, 0.f); break;
+      case UN_TANH: r = tanhf(v); break;
+      case UN_SIGMOID: r = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))); break;
+      case UN_SILU: r = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v))); break;
+      default: r = v; break;
+    }
+    store_from_f32(y, ydt, o, r);
+  }
+}
+
+__global__ void prelu_kernel(const float* x, Layout xl, float* y, Dims4 d, const float* slope, int64_t ns, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    Coord q = decode(o, xl, d);
+    float v = x[o];
+    float sl = slope[ns > 1 ? q.c : 0];
+    y[o] = v >= 0.f ? v : __fmul_rn(v, sl);
+  }
+}
+
+// ---- pooling ----------------------------------------------------------------------------
+template <typename T>
+__global__ void max_pool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, Dims4 xd, PoolShape ps, int64_t total, T lowest) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t c = o % xd.C;
+    int64_t t = o / xd.C;
+    int64_t q = t % ps.Q;
+    t /= ps.Q;
+    int64_t p = t % ps.P;
+    int64_t n = t / ps.P;
+    T best = lowest;
+    for (int r = 0; r < ps.kh; ++r) {
+      int64_t ih = p * ps.sh + (int64_t)r * ps.dh - ps.pt;
+      if (ih < 0 || ih >= xd.H) continue;
+      for (int s = 0; s < ps.kw; ++s) {
+        int64_t iw = q * ps.sw + (int64_t)s * ps.dw - ps.pl;
+        if (iw < 0 || iw >= xd.W) continue;
+        T v = x[((n * xd.H + ih) * xd.W + iw) * xd.C + c];
+        if (v > best) best = v;
+      }
+    }
+    y[o] = best;
+  }
+}
+
+// One thread per (n, c): the sum runs over the plane in (h, w) order exactly like the
+// reference loop; consecutive threads read consecutive channels, so loads are coalesced.
+__global__ void global_avg_pool_nhwc_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 d, int rtf32) {
+  int64_t total = d.N * d.C;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t c = o % d.C, n = o / d.C;
+    const float* p = x + n * d.H * d.W * d.C + c;
+    float sum = 0.f;
+    int64_t hw = d.H * d.W;
+    for (int64_t i = 0; i < hw; ++i) sum = __fadd_rn(sum, p[i * d.C]);
+    float r = __fdiv_rn(sum, (float)hw);
+    y[o] = rtf32 ? round_tf32(r) : r;
+  }
+}
+
+// Instance norm on NHWC: one block per (n, 32-channel group); 32 lanes across channels
+// (coalesced 128-byte rows), 8 warps striding over the pixels.
+__global__ void instance_norm_nhwc_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 d, float eps, const float* scale_nc,
+                                          const float* shift_nc) {
+  int64_t cgroups = (d.C + 31) / 32;
+  int64_t n = blockIdx.x / cgroups, cg = blockIdx.x % cgroups;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  int64_t c = cg * 32 + lane;
+  bool valid = c < d.C;
+  int64_t hw = d.H * d.W;
+  const float* px = x + n * hw * d.C + c;
+  float* py = y + n * hw * d.C + c;
+  __shared__ float red[32][33];
+  float sum = 0.f;
+  if (valid)
+    for (int64_t i = warp; i < hw; i += nwarps) sum += px[i * d.C];
+  red[warp][lane] = sum;
+  __syncthreads();
+  float tot = 0.f;
+  for (int wv = 0; wv < nwarps; ++wv) tot += red[wv][lane];
+  float mean = tot / (float)hw;
+  __syncthreads();
+  float vs = 0.f;
+  if (valid)
+    for (int64_t i = warp; i < hw; i += nwarps) {
+      float dv = px[i * d.C] - mean;
+      vs += dv * dv;
+    }
+  red[warp][lane] = vs;
+  __syncthreads();
+  tot = 0.f;
+  for (int wv = 0; wv < nwarps; ++wv) tot += red[wv][lane];
+  float var = tot / (float)hw;
+  float inv_std = 1.0f / sqrtf(var + eps);
+  float sc = 1.f, sf = 0.f;
+  bool mod = scale_nc != nullptr || shift_nc != nullptr;
+  if (valid && scale_nc) sc = scale_nc[n * d.C + c];
+  if (valid && shift_nc) sf = shift_nc[n * d.C + c];
+  if (valid)
+    for (int64_t i = warp; i < hw; i += nwarps) {
+      float v = (px[i * d.C] - mean) * inv_std;
+      if (mod) v = v * sc + sf;
+      py[i * d.C] = v;
+    }
+}
+
+// ---- resize / pad / concat --------------------------------------------------------------
+__device__ __forceinline__ float src_coord(int coord, int64_t o, float scale, int64_t in_size, int64_t out_size) {
+  switch (coord) {
+    case 2: return __fdiv_rn((float)o, scale);
+    case 3: return out_size <= 1 ? 0.f : __fdiv_rn(__fmul_rn((float)o, (float)(in_size - 1)), (float)(out_size - 1));
+    case 1: return out_size > 1 ? __fsub_rn(__fdiv_rn(__fadd_rn((float)o, 0.5f), scale), 0.5f) : 0.f;
+    default: return __fsub_rn(__fdiv_rn(__fadd_rn((float)o, 0.5f), scale), 0.5f);
+  }
+}
+__device__ __forceinline__ int64_t nearest_index(int rule, float s, int64_t in_size) {
+  float r;
+  switch (rule) {
+    case 1: r = floorf(s); break;
+    case 2: r = ceilf(s); break;
+    case 3: r = floorf(__fadd_rn(s, 0.5f)); break;
+    default: r = ceilf(__fsub_rn(s, 0.5f)); break;
+  }
+  int64_t i = (int64_t)r;
+  return i < 0 ? 0 : (i > in_size - 1 ? in_size - 1 : i);
+}
+
+__global__ void resize_nhwc_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 xd, Dims4 yd, int mode, int coord, int rule,
+                                   float sh, float sw, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t c = o % yd.C;
+    int64_t t = o / yd.C;
+    int64_t ox = t % yd.W;
+    t /= yd.W;
+    int64_t oy = t % yd.H;
+    int64_t n = t / yd.H;
+    float sy = src_coord(coord, oy, sh, xd.H, yd.H), sx = src_coord(coord, ox, sw, xd.W, yd.W);
+    const float* base = x + n * xd.H * xd.W * xd.C + c;
+    if (mode == 0) {
+      y[o] = base[(nearest_index(rule, sy, xd.H) * xd.W + nearest_index(rule, sx, xd.W)) * xd.C];
+    } else {
+      float cy = fminf(fmaxf(sy, 0.f), (float)(xd.H - 1)), cx = fminf(fmaxf(sx, 0.f), (float)(xd.W - 1));
+      int64_t y0 = (int64_t)floorf(cy), x0 = (int64_t)floorf(cx);
+      int64_t y1 = y0 + 1 < xd.H ? y0 + 1 : xd.H - 1, x1 = x0 + 1 < xd.W ? x0 + 1 : xd.W - 1;
+      float fy = __fsub_rn(cy, (float)y0), fx = __fsub_rn(cx, (float)x0);
+      float v00 = base[(y0 * xd.W + x0) * xd.C], v01 = base[(y0 * xd.W + x1) * xd.C];
+      float v10 = base[(y1 * xd.W + x0) * xd.C], v11 = base[(y1 * xd.W + x1) * xd.C];
+      float top = __fadd_rn(__fmul_rn(v00, __fsub_rn(1.f, fx)), __fmul_rn(v01, fx));
+      float bot = __fadd_rn(__fmul_rn(v10, __fsub_rn(1.f, fx)), __fmul_rn(v11, fx));
+      y[o] = __fadd_rn(__fmul_rn(top, __fsub_rn(1.f, fy)), __fmul_rn(bot, fy));
+    }
+  }
+}
+
+__device__ __forceinline__ int64_t pad_src(int64_t idx, int64_t ext, int mode, bool& outside) {
+  if (idx >= 0 && idx < ext) return idx;
+  if (mode == 0) {
+    outside = true;
+    return 0;
+  }
+  if (mode == 2) return idx < 0 ? 0 : ext - 1;
+  return idx < 0 ? -idx : 2 * (ext - 1) - idx;
+}
+
+__global__ void pad_kernel(const void* x, void* y, DT dt, Layout L, Dims4 xd, Dims4 yd, int mode, float value, int pn, int pc, int ph, int pw,
+                           int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    Coord q = decode(o, L, yd);
+    bool outside = false;
+    Coord sq;
+    sq.n = pad_src(q.n - pn, xd.N, mode, outside);
+    sq.c = pad_src(q.c - pc, xd.C, mode, outside);
+    sq.h = pad_src(q.h - ph, xd.H, mode, outside);
+    sq.w = pad_src(q.w - pw, xd.W, mode, outside);
+    float v = outside ? value : load_as_f32(x, dt, encode(sq, L, xd));
+    store_from_f32(y, dt, o, v);
+  }
+}
+
+__global__ void concat_kernel(const void* x, void* y, DT dt, Layout L, Dims4 xd, Dims4 yd, int axis, int64_t offset, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    Coord q = decode(i, L, xd);
+    if (axis == 0) q.n += offset;
+    else if (axis == 1) q.c += offset;
+    else if (axis == 2) q.h += offset;
+    else q.w += offset;
+    int64_t o = encode(q, L, yd);
+    size_t es = dt == DT::F32 || dt == DT::I32 ? 4 : (dt == DT::I16 ? 2 : 1);
+    if (es == 4) ((uint32_t*)y)[o] = ((const uint32_t*)x)[i];
+    else if (es == 2) ((uint16_t*)y)[o] = ((const uint16_t*)x)[i];
+    else ((uint8_t*)y)[o] = ((const uint8_t*)x)[i];
+  }
+}
+
+}  // namespace
+
+// =========================================================================================
+void convert(const TensorRef& src, const TensorRef& dst, cudaStream_t s) {
+  int64_t total = dst.d.numel();
+  if (total == 0) return;
+  const Dims4& d = dst.d;
+  // Coalesced tile transpose for the two hot cases at the graph edges.
+  if (src.layout != dst.layout && d.C > 1 && d.H * d.W > 1 && d.N <= 65535) {
+    int64_t A, B;  // src viewed [N, A, B] -> dst [N, B, A]
+    if (src.layout == Layout::PLAIN) {
+      A = d.C;
+      B = d.H * d.W;
+    } else {
+      A = d.H * d.W;
+      B = d.C;
+    }
+    dim3 block(32, 8), grid((unsigned)ceil_div(B, 32), (unsigned)ceil_div(A, 32), (unsigned)d.N);
+    if (grid.y <= 65535) {
+      if (src.dt == DT::F32 && dst.dt == DT::F32) {
+        transpose_tiles<float, float><<<grid, block, 0, s>>>((const float*)src.ptr, (float*)dst.ptr, A, B);
+        return;
+      }
+      if (src.dt == DT::U8 && dst.dt == DT::F32) {
+        transpose_tiles<uint8_t, float><<<grid, block, 0, s>>>((const uint8_t*)src.ptr, (float*)dst.ptr, A, B);
+        return;
+      }
+      if (src.dt == DT::I8 && dst.dt == DT::F32) {
+        transpose_tiles<int8_t, float><<<grid, block, 0, s>>>((const int8_t*)src.ptr, (float*)dst.ptr, A, B);
+        return;
+      }
+    }
+  }
+  convert_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, dst.ptr, dst.dt, dst.layout, d, total);
+}
+
+void quantize_linear(const TensorRef& x, const TensorRef& y, const float* scale, int64_t n_scale, const float* zp, int64_t n_zp, float lo,
+                     float hi, cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (total == 0) return;
+  quantize_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, x.dt, x.layout, y.ptr, y.dt, y.layout, y.d, scale, n_scale, zp, n_zp, lo, hi,
+                                                       total);
+}
+
+bool quantize_linear_scalar_ok(const TensorRef& x, const TensorRef& y) {
+  int64_t total = y.d.numel();
+  bool same_order = x.layout == y.layout || (y.d.C == 1) || (y.d.H * y.d.W == 1);
+  return x.dt == DT::F32 && (y.dt == DT::U8 || y.dt == DT::I8) && same_order && total > 0 && total % 16 == 0 &&
+         ((uintptr_t)x.ptr % 16 == 0) && ((uintptr_t)y.ptr % 16 == 0);
+}
+
+// Host-known per-tensor parameters: the vectorised kernel.
+void quantize_linear_scalar(const TensorRef& x, const TensorRef& y, float scale, float zp, float lo, float hi, cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (quantize_linear_scalar_ok(x, y)) {
+    quantize_vec16_kernel<<<grid_for(total / 16), kThreads, 0, s>>>((const float4*)x.ptr, (uint4*)y.ptr, scale, zp, lo, hi, total / 16);
+    return;
+  }
+  OXB_FAIL("quantize_linear_scalar: no vector path for this operand");
+}
+
+void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scale, int64_t n_scale, const float* zp, int64_t n_zp,
+                       cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (total == 0) return;
+  dequantize_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, x.dt, x.layout, y.ptr, y.layout, y.d, scale, n_scale, zp, n_zp, total);
+}
+
+void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s) {
+  int64_t n = x.d.numel();
+  uint32_t* keys = (uint32_t*)scratch;
+  minmax_init_kernel<<<1, 1, 0, s>>>(keys);
+  minmax_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, n, keys);
+  dynq_params_kernel<<<1, 1, 0, s>>>(keys, params);
+  dynq_apply_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, params, n);
+}
+
+void binary(const TensorRef& a, const TensorRef& b, const TensorRef& out, int op, int relu_after, int round_tf32_flag, cudaStream_t s) {
+  int64_t total = out.d.numel();
+  if (total == 0) return;
+  bool same = a.d.numel() == total && b.d.numel() == total && a.layout == out.layout && b.layout == out.layout && a.dt == DT::F32 &&
+              b.dt == DT::F32 && out.dt == DT::F32 && total % 4 == 0;
+  if (same) {
+    binary_vec4_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((const float4*)a.ptr, (const float4*)b.ptr, (float4*)out.ptr, op, relu_after,
+                                                               round_tf32_flag, total / 4);
+    return;
+  }
+  binary_kernel<<<grid_for(total), kThreads, 0, s>>>(a.ptr, a.dt, a.layout, a.d, b.ptr, b.dt, b.layout, b.d, out.ptr, out.dt, out.layout,
+                                                     out.d, op, relu_after, round_tf32_flag, total);
+}
+
+void unary(const TensorRef& x, const TensorRef& y, int op, cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (total == 0) return;
+  unary_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, x.dt, y.ptr, y.dt, op, total);
+}
+
+void prelu(const TensorRef& x, const TensorRef& y, const float* slope, int64_t n_slope, cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (total == 0) return;
+  prelu_kernel<<<grid_for(total), kThreads, 0, s>>>((const float*)x.ptr, x.layout, (float*)y.ptr, x.d, slope, n_slope, total);
+}
+
+void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (total == 0) return;
+  int g = grid_for(total);
+  if (x.dt == DT::F32) max_pool_nhwc_kernel<float><<<g, kThreads, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, ps, total, -INFINITY);
+  else if (x.dt == DT::U8) max_pool_nhwc_kernel<uint8_t><<<g, kThreads, 0, s>>>((const uint8_t*)x.ptr, (uint8_t*)y.ptr, x.d, ps, total, 0);
+  else if (x.dt == DT::I8) max_pool_nhwc_kernel<int8_t><<<g, kThreads, 0, s>>>((const int8_t*)x.ptr, (int8_t*)y.ptr, x.d, ps, total, -128);
+  else OXB_FAIL("max_pool: unsupported storage type");
+}
+
+void global_avg_pool(const TensorRef& x, const TensorRef& y, int round_tf32_flag, cudaStream_t s) {
+  int64_t total = x.d.N * x.d.C;
+  if (total == 0) return;
+  global_avg_pool_nhwc_kernel<<<grid_for(total, 128), 128, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, round_tf32_flag);
+}
+
+void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const float* scale_nc, const float* shift_nc, cudaStream_t s) {
+  int64_t cgroups = (x.d.C + 31) / 32;
+  int64_t blocks = x.d.N * cgroups;
+  if (blocks == 0) return;
+  instance_norm_nhwc_kernel<<<(unsigned)blocks, 256, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, eps, scale_nc, shift_nc);
+}
+
+void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (total == 0) return;
+  resize_nhwc_kernel<<<grid_for(total), kThreads, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, y.d, mode, coord, nearest_rule, scale_h,
+                                                          scale_w, total);
+}
+
+void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, int pc, int ph, int pw, cudaStream_t s) {
+  int64_t total = y.d.numel();
+  if (total == 0) return;
+  pad_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, y.ptr, x.dt, x.layout, x.d, y.d, mode, value, pn, pc, ph, pw, total);
+}
+
+void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s) {
+  int64_t total = x.d.numel();
+  if (total == 0) return;
+  concat_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, y.ptr, x.dt, x.layout, x.d, y.d, axis, offset, total);
+}
+
+}  // namespace k
+}  // namespace oxb

@@ -1,0 +1,623 @@
+// tcgen05 implicit-GEMM convolution / GEMM for sm_100a.
+//
+// One kernel serves Conv, Gemm/MatMul (a 1x1 convolution over an [M, K] matrix), QLinearConv,
+// QLinearMatMul, MatMulInteger and ConvInteger:
+//
+//   D[m, oc] = sum_{r,s,c} X[n, p*sh + r*dh - pt, q*sw + s*dw - pl, c] * Wp[oc, (r*S+s)*C + c]
+//
+// with m = (n*P + p)*Q + q over an NHWC activation tensor and K-major packed weights.
+//
+//  * A tiles (128 output pixels x one channel block of one filter tap) are gathered straight
+//    from the NHWC activation by TMA in im2col mode (cp.async.bulk.tensor ... im2col), so no
+//    im2col matrix ever exists in memory; plain GEMMs and 1x1/stride-1 convolutions use a 2-D
+//    tiled TMA load of the same shape.  Padding taps arrive as zeros (TMA out-of-bounds fill).
+//  * B tiles (BN output channels x the same K slice) are 2-D tiled TMA loads.
+//  * No load uses cluster multicast: every CTA fetches its own tiles.
+//  * One elected thread issues tcgen05.mma (kind::i8 with s32 accumulation, or kind::tf32 with
+//    f32 accumulation) from shared-memory descriptors into a TMEM accumulator of BN columns.
+//  * Four epilogue warps read the accumulator with tcgen05.ld (one output pixel per thread,
+//    32 channels per load), apply the fused epilogue in registers (bias; ONNX requantisation
+//    in f64 with round-half-even and saturation; ReLU/clip; int32 saturation) and write each
+//    pixel's channel run with 16-byte stores.
+//  * Every mbarrier wait is bounded; on a timeout the kernel records an error code, lets its
+//    copies land, frees its TMEM and returns, so the context stays usable.
+#include <cuda.h>
+
+#include <cstring>
+#include <mutex>
+
+#include "kernels.hpp"
+
+namespace oxb {
+namespace k {
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int NUM_THREADS = 192;  // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2-5: epilogue
+constexpr int MAX_STAGES = 12;
+constexpr long long WAIT_CYCLES = 2000000000LL;  // ~1 s at 2 GHz
+
+struct alignas(64) KParams {
+  CUtensorMap tmA;
+  CUtensorMap tmB;
+  int a_im2col;
+  int M, OC;
+  int P, Q, S;
+  int sh, sw, pt, pl, dh, dw;
+  int taps, cblocks, cb_elems;
+  int swizzle_bytes;  // 128, 64 or 32: bytes of K per stage row
+  int stages;
+  int n_tiles;
+  uint32_t idesc;
+  // epilogue
+  int mode;
+  const float* bias_f;
+  int act;
+  float clip_lo, clip_hi;
+  int round_tf32;
+  const int32_t* bias_i;
+  const int32_t* wsum;
+  const float* x_zp_dev;
+  const float* combined;
+  int y_zp, lo, hi;
+  int out_dt;
+  void* out;
+  int* err_flag;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait: false when the barrier did not flip within WAIT_CYCLES or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  long long start = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - start > WAIT_CYCLES) return false;
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+               "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c, int w, int h, int n, uint16_t off_w,
+                                                    uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(
+          dst),
+      "l"((uint64_t)map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  if (KIND == 0) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+// Shared-memory matrix descriptor, K-major operand, swizzled rows of `swz` bytes: start
+// address, leading offset (unused for swizzled K-major, encoded 1), stride between 8-row
+// groups (8 * swz bytes), descriptor version 1 (Blackwell), swizzle mode.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int swz) {
+  uint64_t layout = swz == 128 ? 2ull : (swz == 64 ? 4ull : 6ull);
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fffu);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(((uint32_t)(8 * swz) >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= layout << 61;
+  return d;
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float round_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+// ---- the kernel ---------------------------------------------------------------------------
+template <int BN, int KIND>
+__global__ void __launch_bounds__(NUM_THREADS) umma_conv_kernel(const __grid_constant__ KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[MAX_STAGES];
+  __shared__ __align__(8) uint64_t bar_empty[MAX_STAGES];
+  __shared__ __align__(8) uint64_t bar_acc;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ float s_f[2][BN];    // [0] bias_f or combined, [1] unused / combined
+  __shared__ int32_t s_i[2][BN];  // [0] bias_i, [1] wsum
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x % p.n_tiles, tile_m = blockIdx.x / p.n_tiles;
+  const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
+  const int swz = p.swizzle_bytes;
+  const uint32_t a_bytes = (uint32_t)BLOCK_M * swz, b_bytes = (uint32_t)BN * swz;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int k_iters = p.taps * p.cblocks;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(smem_u32(&bar_full[i]), 1);
+      mbar_init(smem_u32(&bar_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&bar_acc), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp >= 2) {
+    // stage the per-channel epilogue parameters of this CTA's channel range
+    for (int i = threadIdx.x - 64; i < BN; i += 128) {
+      int oc = oc0 + i;
+      bool ok = oc < p.OC;
+      s_f[0][i] = (p.mode == EPI_F32) ? ((ok && p.bias_f) ? p.bias_f[oc] : 0.f) : ((ok && p.combined) ? p.combined[oc] : 0.f);
+      s_i[0][i] = (ok && p.bias_i) ? p.bias_i[oc] : 0;
+      s_i[1][i] = (ok && p.wsum) ? p.wsum[oc] : 0;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      int q0 = 0, p0 = 0, n0 = 0;
+      if (p.a_im2col) {
+        q0 = m0 % p.Q;
+        int t = m0 / p.Q;
+        p0 = t % p.P;
+        n0 = t / p.P;
+      }
+      const int w_base = q0 * p.sw - p.pl, h_base = p0 * p.sh - p.pt;
+      for (int it = 0; it < k_iters; ++it) {
+        int stage = it % p.stages;
+        uint32_t phase = (uint32_t)(it / p.stages) & 1u;
+        if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp)) {
+          if (!*abortp) {
+            *abortp = 1;
+            atomicExch(p.err_flag, 1);
+          }
+          break;
+        }
+        uint32_t full = smem_u32(&bar_full[stage]);
+        mbar_expect_tx(full, stage_bytes);
+        uint32_t a_dst = tiles_base + (uint32_t)stage * stage_bytes, b_dst = a_dst + a_bytes;
+        int tap = it / p.cblocks, cb = it - tap * p.cblocks;
+        int c_off = cb * p.cb_elems;
+        if (p.a_im2col) {
+          int r = tap / p.S, s = tap - r * p.S;
+          tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(s * p.dw), (uint16_t)(r * p.dh));
+        } else {
+          tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+        }
+        tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      const int mmas = swz / 32;
+      bool ok = true;
+      for (int it = 0; it < k_iters && ok; ++it) {
+        int stage = it % p.stages;
+        uint32_t phase = (uint32_t)(it / p.stages) & 1u;
+        if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp)) {
+          if (!*abortp) {
+            *abortp = 1;
+            atomicExch(p.err_flag, 2);
+          }
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t a_addr = tiles_base + (uint32_t)stage * stage_bytes, b_addr = a_addr + a_bytes;
+        uint64_t da = make_smem_desc(a_addr, swz), db = make_smem_desc(b_addr, swz);
+        for (int kk = 0; kk < mmas; ++kk) {
+          // 32 bytes of K per MMA: advance the (16-byte granular) start address by 2
+          tc_mma<KIND>(tmem_base, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), p.idesc, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
+      }
+      if (ok) tc_commit(smem_u32(&bar_acc));  // accumulator complete
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+    const int quarter = warp & 3;
+    bool ok = mbar_wait(smem_u32(&bar_acc), 0u, abortp);
+    if (!ok && !*abortp) {
+      *abortp = 1;
+      atomicExch(p.err_flag, 3);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const int row = quarter * 32 + lane;
+      const long long m = (long long)m0 + row;
+      const bool row_ok = m < p.M;
+      int xz = 0;
+      if (p.x_zp_dev) xz = __float2int_rn(*p.x_zp_dev);
+      const size_t esz = (p.out_dt == (int)DT::F32 || p.out_dt == (int)DT::I32) ? 4 : (p.out_dt == (int)DT::I16 ? 2 : 1);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (oc0 + c0 >= p.OC) break;  // uniform across the CTA
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        if (!row_ok) continue;
+        const int valid = min(32, p.OC - (oc0 + c0));
+        uint8_t* optr = (uint8_t*)p.out + ((size_t)m * p.OC + oc0 + c0) * esz;
+        if (p.mode == EPI_F32) {
+          float o[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float f = __uint_as_float(v[j]) + s_f[0][c0 + j];
+            if (p.act == 1) f = fmaxf(f, 0.f);
+            else if (p.act == 2) f = fminf(fmaxf(f, p.clip_lo), p.clip_hi);
+            if (p.round_tf32) f = round_tf32(f);
+            o[j] = f;
+          }
+          if (valid == 32 && ((uintptr_t)optr & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *(float4*)(optr + j * 4) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+          } else {
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) ((float*)optr)[j] = o[j];
+          }
+        } else {
+          int32_t o[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            int32_t acc = (int32_t)v[j] + s_i[0][c0 + j] - xz * s_i[1][c0 + j];
+            if (p.mode == EPI_REQUANT) {
+              // f64 product, f64 add (each rounded once), round-half-even, saturate
+              double scaled = __dadd_rn(__dmul_rn((double)acc, (double)s_f[0][c0 + j]), (double)p.y_zp);
+              int q = __double2int_rn(scaled);
+              acc = min(max(q, p.lo), p.hi);
+            }
+            o[j] = acc;
+          }
+          if (esz == 1) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              w[j] = ((uint32_t)o[4 * j] & 0xffu) | (((uint32_t)o[4 * j + 1] & 0xffu) << 8) | (((uint32_t)o[4 * j + 2] & 0xffu) << 16) |
+                     (((uint32_t)o[4 * j + 3] & 0xffu) << 24);
+            if (valid == 32 && ((uintptr_t)optr & 15) == 0) {
+              *(uint4*)(optr) = make_uint4(w[0], w[1], w[2], w[3]);
+              *(uint4*)(optr + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+              _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) optr[j] = (uint8_t)(o[j] & 0xff);
+            }
+          } else if (esz == 4) {
+            if (valid == 32 && ((uintptr_t)optr & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *(int4*)(optr + j * 4) = make_int4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+            } else {
+              _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) ((int32_t*)optr)[j] = o[j];
+            }
+          } else {
+            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) ((int16_t*)optr)[j] = (int16_t)o[j];
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (abort_flag && threadIdx.x == 0) {
+    // give copies that may still be in flight time to land before the CTA's shared memory goes away
+    long long start = clock64();
+    while (clock64() - start < 2000000LL) {
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*,
+                                   const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+std::once_flag g_encode_once;
+
+void load_encoders() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      g_encode_tiled = (EncodeTiledFn)fn;
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      g_encode_im2col = (EncodeIm2colFn)fn;
+    (void)cudaGetLastError();
+  });
+}
+
+CUtensorMapSwizzle swizzle_enum(int bytes) {
+  return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+uint32_t make_idesc(int kind, bool a_signed, bool b_signed, int bn) {
+  uint32_t d = 0;
+  if (kind == 0) {
+    d |= 2u << 4;                      // accumulator: s32
+    d |= (a_signed ? 1u : 0u) << 7;    // A: 0 = u8, 1 = s8
+    d |= (b_signed ? 1u : 0u) << 10;   // B
+  } else {
+    d |= 1u << 4;  // accumulator: f32
+    d |= 2u << 7;  // A: tf32
+    d |= 2u << 10; // B: tf32
+  }
+  // bits 15/16: A and B are K-major (0)
+  d |= (uint32_t)(bn >> 3) << 17;
+  d |= (uint32_t)(BLOCK_M >> 4) << 24;
+  return d;
+}
+
+template <int BN, int KIND>
+void launch_t(const KParams& kp, int grid, size_t smem, cudaStream_t s) {
+  static bool attr_set = false;
+  static size_t attr_smem = 0;
+  if (!attr_set || smem > attr_smem) {
+    OXB_CUDA(cudaFuncSetAttribute(umma_conv_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
+    attr_smem = smem;
+  }
+  umma_conv_kernel<BN, KIND><<<grid, NUM_THREADS, smem, s>>>(kp);
+}
+
+}  // namespace
+
+struct UmmaPlan {
+  KParams kp;
+  int bn;
+  int kind;
+  int grid;
+  size_t smem;
+  char desc[160];
+};
+
+bool umma_available() {
+  load_encoders();
+  return g_encode_tiled != nullptr && g_encode_im2col != nullptr;
+}
+
+int umma_channel_block(int C, int kind) {
+  int es = kind == 0 ? 1 : 4;
+  int64_t row = (int64_t)C * es;
+  if (row % 128 == 0) return 128 / es;
+  if (row == 64) return 64 / es;
+  if (row == 32) return 32 / es;
+  return 0;
+}
+
+UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt, void* out, const ConvShape& cs, const Epilogue& e, int kind,
+                           std::string* why) {
+  auto no = [&](const char* msg) -> UmmaPlan* {
+    if (why) *why = msg;
+    return nullptr;
+  };
+  load_encoders();
+  if (!g_encode_tiled || !g_encode_im2col) return no("tensor-map encoders unavailable in this driver");
+  if (cs.group != 1) return no("grouped convolution");
+  if (kind == 0) {
+    if (!(x_dt == DT::U8 || x_dt == DT::I8) || !(w_dt == DT::I8 || w_dt == DT::U8)) return no("operands are not 8-bit integers");
+    if (e.mode == EPI_F32) return no("integer kind needs an integer epilogue");
+  } else {
+    if (x_dt != DT::F32 || w_dt != DT::F32 || e.mode != EPI_F32) return no("tf32 kind needs f32 operands and a float epilogue");
+  }
+  const int es = kind == 0 ? 1 : 4;
+  const int cb = umma_channel_block(cs.C, kind);
+  if (cb == 0) return no("channel count is not a multiple of a 32/64/128-byte block");
+  const int swz = cb * es;
+  const int64_t M = cs.M();
+  if (M <= 0 || M > 0x7fffffffLL || cs.OC <= 0) return no("empty or oversized problem");
+  if (((uintptr_t)x & 127) || ((uintptr_t)w_packed & 127) || ((uintptr_t)out & 15)) return no("operand base address is not aligned");
+  const bool gemm_like = cs.R == 1 && cs.S == 1 && cs.sh == 1 && cs.sw == 1 && cs.pt == 0 && cs.pl == 0 && cs.pb == 0 && cs.pr == 0;
+  if (!gemm_like) {
+    // im2col corners and offsets are 8-bit quantities for two spatial dimensions
+    int up_w = cs.pr - (cs.S - 1) * cs.dw, up_h = cs.pb - (cs.R - 1) * cs.dh;
+    if (cs.pl > 127 || cs.pt > 127 || up_w < -128 || up_h < -128 || up_w > 127 || up_h > 127) return no("padding outside the im2col corner range");
+    if ((cs.S - 1) * cs.dw > 255 || (cs.R - 1) * cs.dh > 255) return no("filter extent outside the im2col offset range");
+    if (cs.sw > 8 || cs.sh > 8) return no("stride above the TMA traversal-stride limit");
+  }
+  if (e.x_zp_rows || e.n_w_zp > 0) return no("per-row or weight zero points need the direct kernel");
+
+  int bn = cs.OC <= 32 ? 32 : (cs.OC <= 64 ? 64 : 128);
+  if (kind == 0 && bn == 128 && cs.OC >= 256 && M >= 148LL * 128 * 4) bn = 256;
+  const int64_t m_tiles = ceil_div(M, BLOCK_M), n_tiles = ceil_div(cs.OC, bn);
+  if (m_tiles * n_tiles > 0x7fffffffLL) return no("grid too large");
+
+  UmmaPlan* pl = new UmmaPlan();
+  std::memset(&pl->kp, 0, sizeof(KParams));
+  KParams& kp = pl->kp;
+  CUtensorMapDataType dtype = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult rc;
+  if (gemm_like) {
+    cuuint64_t gdim[2] = {(cuuint64_t)cs.C, (cuuint64_t)M};
+    cuuint64_t gstr[1] = {(cuuint64_t)cs.C * es};
+    cuuint32_t box[2] = {(cuuint32_t)cb, (cuuint32_t)BLOCK_M};
+    cuuint32_t estr[2] = {1, 1};
+    rc = g_encode_tiled(&kp.tmA, dtype, 2, const_cast<void*>(x), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum(swz),
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    kp.a_im2col = 0;
+  } else {
+    cuuint64_t gdim[4] = {(cuuint64_t)cs.C, (cuuint64_t)cs.W, (cuuint64_t)cs.H, (cuuint64_t)cs.N};
+    cuuint64_t gstr[3] = {(cuuint64_t)cs.C * es, (cuuint64_t)cs.W * cs.C * es, (cuuint64_t)cs.H * cs.W * cs.C * es};
+    int lower[2] = {-cs.pl, -cs.pt};
+    int upper[2] = {cs.pr - (cs.S - 1) * cs.dw, cs.pb - (cs.R - 1) * cs.dh};
+    cuuint32_t estr[4] = {1, (cuuint32_t)cs.sw, (cuuint32_t)cs.sh, 1};
+    rc = g_encode_im2col(&kp.tmA, dtype, 4, const_cast<void*>(x), gdim, gstr, lower, upper, (cuuint32_t)cb, (cuuint32_t)BLOCK_M, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum(swz), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    kp.a_im2col = 1;
+    // Drivers up to CUDA 13.1 mis-encode im2col maps of tensors smaller than 128 KiB; the
+    // published workaround clears bit 21 of the second descriptor word.
+    int drv = 0;
+    if (rc == CUDA_SUCCESS && cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010) {
+      size_t bytes = (size_t)cs.N * cs.H * cs.W * cs.C * es;
+      if (bytes < 131072) reinterpret_cast<uint64_t*>(&kp.tmA)[1] &= ~(1ull << 21);
+    }
+  }
+  if (rc != CUDA_SUCCESS) {
+    delete pl;
+    return no("activation tensor map rejected by the driver");
+  }
+  {
+    const int64_t ktot = cs.K();
+    cuuint64_t gdim[2] = {(cuuint64_t)ktot, (cuuint64_t)cs.OC};
+    cuuint64_t gstr[1] = {(cuuint64_t)ktot * es};
+    cuuint32_t box[2] = {(cuuint32_t)cb, (cuuint32_t)bn};
+    cuuint32_t estr[2] = {1, 1};
+    rc = g_encode_tiled(&kp.tmB, dtype, 2, const_cast<void*>(w_packed), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum(swz),
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      delete pl;
+      return no("weight tensor map rejected by the driver");
+    }
+  }
+  kp.M = (int)M;
+  kp.OC = cs.OC;
+  kp.P = cs.P;
+  kp.Q = cs.Q;
+  kp.S = cs.S;
+  kp.sh = cs.sh;
+  kp.sw = cs.sw;
+  kp.pt = cs.pt;
+  kp.pl = cs.pl;
+  kp.dh = cs.dh;
+  kp.dw = cs.dw;
+  kp.taps = cs.R * cs.S;
+  kp.cblocks = cs.C / cb;
+  kp.cb_elems = cb;
+  kp.swizzle_bytes = swz;
+  kp.n_tiles = (int)n_tiles;
+  kp.idesc = make_idesc(kind, x_dt == DT::I8, w_dt == DT::I8, bn);
+  const size_t stage_bytes = (size_t)(BLOCK_M + bn) * swz;
+  const size_t budget = 96 * 1024;  // two CTAs per SM overlap one tile's epilogue with another's main loop
+  int stages = (int)(budget / stage_bytes);
+  const int k_iters = kp.taps * kp.cblocks;
+  if (stages > k_iters) stages = k_iters;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages < 2) stages = k_iters < 2 ? 1 : 2;
+  kp.stages = stages;
+  kp.mode = e.mode;
+  kp.bias_f = e.bias_f;
+  kp.act = e.act;
+  kp.clip_lo = e.clip_lo;
+  kp.clip_hi = e.clip_hi;
+  kp.round_tf32 = e.round_tf32;
+  kp.bias_i = e.bias_i;
+  kp.wsum = e.x_zp_dev ? e.wsum : nullptr;
+  kp.x_zp_dev = e.x_zp_dev;
+  kp.combined = e.combined;
+  kp.y_zp = e.y_zp;
+  kp.lo = (e.relu_fused && e.lo < 0) ? 0 : e.lo;
+  kp.hi = e.hi;
+  kp.out_dt = (int)e.out_dt;
+  kp.out = out;
+  kp.err_flag = nullptr;
+  pl->bn = bn;
+  pl->kind = kind;
+  pl->grid = (int)(m_tiles * n_tiles);
+  pl->smem = (size_t)stages * stage_bytes + 1024;
+  snprintf(pl->desc, sizeof pl->desc, "umma_%s M=%lld N=%d K=%lld tile=128x%dx%dB stages=%d %s", kind == 0 ? "i8" : "tf32", (long long)M, cs.OC,
+           (long long)cs.K(), bn, swz, stages, gemm_like ? "tiled" : "im2col");
+  return pl;
+}
+
+void umma_plan_destroy(UmmaPlan* p) { delete p; }
+const char* umma_plan_desc(const UmmaPlan* p) { return p->desc; }
+
+void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {
+  KParams kp = p->kp;
+  kp.err_flag = err_flag;
+#define OXB_UMMA_CASE(BN)                                             \
+  case BN:                                                            \
+    if (p->kind == 0) launch_t<BN, 0>(kp, p->grid, p->smem, s);       \
+    else launch_t<BN, 1>(kp, p->grid, p->smem, s);                    \
+    break;
+  switch (p->bn) {
+    OXB_UMMA_CASE(32)
+    OXB_UMMA_CASE(64)
+    OXB_UMMA_CASE(128)
+    OXB_UMMA_CASE(256)
+    default: OXB_FAIL("umma_launch: unsupported tile width %d", p->bn);
+  }
+#undef OXB_UMMA_CASE
+  OXB_CUDA(cudaGetLastError());
+}
+
+}  // namespace k
+}  // namespace oxb

@@ -1,0 +1,1802 @@
+// Planning: from a topologically sorted node list to device steps.
+//
+// For every node the planner resolves shapes and device storage types (the reference has no
+// shape rules for the INT8 family, so they are supplied here), validates the node the way the
+// reference's CPU operator does (a malformed node DECLINES so the CPU operator can raise its own
+// typed error), packs and uploads weights once per context, chooses the tensor-core or the
+// direct kernel, fuses what the provider may fuse on its own (a Relu behind a quantised
+// contraction or an Add, the DequantizeLinear -> Add -> Relu -> QuantizeLinear residual chain)
+// and finally lays every intermediate out in one device arena by lifetime
+// (MemoryPlan::compute, root crate src/memory/types.rs:347-452, in bytes instead of elements).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+#include "runtime.hpp"
+
+namespace oxb {
+
+namespace {
+
+using k::Dims4;
+using k::TensorRef;
+
+const char* kSupportedOps[] = {"Conv",       "Gemm",     "MatMul",  "QLinearConv", "QLinearMatMul", "MatMulInteger",     "ConvInteger",
+                               "QuantizeLinear", "DequantizeLinear", "DynamicQuantizeLinear", "Relu", "Tanh", "Sigmoid",    "PRelu",
+                               "Add",        "Sub",      "Mul",     "Div",         "MaxPool",       "GlobalAveragePool", "OxiInstanceNorm",
+                               "Resize",     "Pad",      "Concat",  "Flatten",     "Reshape",       "Identity",          "Cast"};
+
+// ---- scalar helpers that must agree with the reference bit for bit -----------------------
+double round_ties_even(double v) { return std::nearbyint(v); }  // default rounding mode: ties to even
+
+// lane_to_i32 (quant_ops/mod.rs:79-92): non-finite or out-of-range lanes are malformed.
+bool lane_to_i32(float v, int32_t* out) {
+  if (!std::isfinite(v)) return false;
+  double r = round_ties_even((double)v);
+  if (r < -2147483648.0 || r > 2147483647.0) return false;
+  *out = (int32_t)r;
+  return true;
+}
+
+bool lanes_to_i32(const HostTensor& t, std::vector<int32_t>* out) {
+  out->resize(t.data.size());
+  for (size_t i = 0; i < t.data.size(); ++i)
+    if (!lane_to_i32(t.data[i], &(*out)[i])) return false;
+  return true;
+}
+
+struct Range {
+  int lo, hi;
+};
+// SatRange::infer (quant_ops/mod.rs:190-200)
+Range sat_infer(const std::vector<int32_t>& y_zp, const std::vector<int32_t>& x_zp) {
+  const std::vector<int32_t>* l[2] = {&y_zp, &x_zp};
+  for (auto* lanes : l) {
+    for (int32_t v : *lanes)
+      if (v > 127) return {0, 255};
+    for (int32_t v : *lanes)
+      if (v < 0) return {-128, 127};
+  }
+  return {-128, 255};
+}
+
+DT narrowest_int(int64_t lo, int64_t hi) {
+  if (lo >= 0 && hi <= 255) return DT::U8;
+  if (lo >= -128 && hi <= 127) return DT::I8;
+  if (lo >= -32768 && hi <= 32767) return DT::I16;
+  return DT::I32;
+}
+
+float round_to_tf32(float v) {
+  if (!std::isfinite(v)) return v;
+  uint32_t u;
+  std::memcpy(&u, &v, 4);
+  u += 0x1000u;  // round to nearest, ties away from zero in magnitude (cvt.rna)
+  u &= 0xffffe000u;
+  float r;
+  std::memcpy(&r, &u, 4);
+  return r;
+}
+
+// ---- convolution geometry (oxionnx-ops src/conv/spatial.rs) --------------------------------
+struct Geo {
+  std::vector<int64_t> strides, pads, dilations, out_spatial;
+  int64_t group = 1;
+};
+
+int64_t out_dim(const char* op, int64_t in, int64_t pb, int64_t pe, int64_t kernel, int64_t dil, int64_t stride, bool ceil_mode) {
+  int64_t eff = (kernel - 1) * dil + 1;
+  int64_t padded = in + pb + pe;
+  if (padded < eff) OXB_DECLINE("%s: padded input extent %lld is smaller than the dilated kernel extent %lld", op, (long long)padded, (long long)eff);
+  int64_t span = padded - eff;
+  int64_t out = ceil_mode ? ceil_div(span, stride) + 1 : span / stride + 1;
+  if (ceil_mode && out > 1 && (out - 1) * stride >= in + pb) out -= 1;
+  return out;
+}
+
+Geo resolve_geometry(const char* op, const AttrMap& at, const int64_t* in_sp, const int64_t* kernel, int rank, bool ceil_mode) {
+  Geo g;
+  auto st = at.int_list("strides"), dl = at.int_list("dilations"), pd = at.int_list("pads");
+  g.strides.assign(rank, 1);
+  g.dilations.assign(rank, 1);
+  for (int a = 0; a < rank; ++a) {
+    if ((size_t)a < st.size()) {
+      if (st[a] < 1) OXB_DECLINE("%s: strides[%d] must be >= 1", op, a);
+      g.strides[a] = st[a];
+    }
+    if ((size_t)a < dl.size()) {
+      if (dl[a] < 1) OXB_DECLINE("%s: dilations[%d] must be >= 1", op, a);
+      g.dilations[a] = dl[a];
+    }
+  }
+  std::vector<int64_t> expl(2 * rank, 0);
+  for (int i = 0; i < 2 * rank; ++i)
+    if ((size_t)i < pd.size()) {
+      if (pd[i] < 0) OXB_DECLINE("%s: pads[%d] must be >= 0", op, i);
+      expl[i] = pd[i];
+    }
+  std::string ap = at.s("auto_pad");
+  if (ap.empty() || ap == "NOTSET") {
+    g.pads = expl;
+  } else if (ap == "VALID") {
+    g.pads.assign(2 * rank, 0);
+  } else if (ap == "SAME_UPPER" || ap == "SAME_LOWER") {
+    bool lower = ap == "SAME_LOWER";
+    g.pads.assign(2 * rank, 0);
+    for (int a = 0; a < rank; ++a) {
+      int64_t od = ceil_div(in_sp[a], g.strides[a]);
+      int64_t eff = (kernel[a] - 1) * g.dilations[a] + 1;
+      int64_t needed = std::max<int64_t>((od - 1) * g.strides[a] + eff - in_sp[a], 0);
+      int64_t half = needed / 2;
+      g.pads[a] = lower ? needed - half : half;
+      g.pads[a + rank] = lower ? half : needed - half;
+    }
+  } else {
+    OXB_DECLINE("%s: unknown auto_pad value '%s'", op, ap.c_str());
+  }
+  for (int a = 0; a < rank; ++a)
+    g.out_spatial.push_back(out_dim(op, in_sp[a], g.pads[a], g.pads[a + rank], kernel[a], g.dilations[a], g.strides[a], ceil_mode));
+  return g;
+}
+
+}  // namespace
+
+bool is_supported_op(const std::string& op) {
+  for (const char* s : kSupportedOps)
+    if (op == s) return true;
+  return false;
+}
+
+// Which operand slots may bind a device-resident activation in place (the data operands);
+// parameter slots (scales, zero points, weights, shape vectors) must come from the host.
+bool accepts_resident_slot(const std::string& op, uint32_t slot) {
+  if (!is_supported_op(op)) return false;
+  if (op == "QLinearConv") return slot == 0;
+  if (op == "QLinearMatMul") return slot == 0;
+  if (op == "MatMulInteger") return slot == 0 || slot == 2;  // A and the dynamic a_zero_point
+  if (op == "ConvInteger" || op == "Conv") return slot == 0;
+  if (op == "Gemm") return slot == 0;
+  if (op == "MatMul" || op == "Add" || op == "Sub" || op == "Mul" || op == "Div") return slot <= 1;
+  if (op == "Concat") return true;
+  if (op == "QuantizeLinear" || op == "DequantizeLinear" || op == "PRelu" || op == "Reshape" || op == "Resize" || op == "Pad") return slot == 0;
+  return slot == 0;
+}
+
+// =========================================================================================
+class Planner {
+ public:
+  Planner(Session& s, Context& c, const std::vector<NodeDef>& nodes, const std::map<std::string, const HostTensor*>& vconsts)
+      : S(s), C(c), nodes_(nodes), vconsts_(vconsts) {}
+
+  void run(const std::vector<std::pair<std::string, std::vector<int64_t>>>& inputs, const std::vector<std::string>& outputs);
+
+ private:
+  Session& S;
+  Context& C;
+  const std::vector<NodeDef> nodes_;  // copies: the step closures outlive the caller's arguments
+  const std::map<std::string, const HostTensor*> vconsts_;
+  std::unordered_map<std::string, std::vector<std::pair<int, int>>> consumers_;
+  std::vector<char> skipped_;
+  std::set<std::string> graph_outputs_;
+  std::map<std::pair<int, int>, int> layout_memo_;
+  int cur_node_ = -1;
+
+  // ---- value bookkeeping ----
+  int add_value(const std::string& name, const std::vector<int64_t>& shape, DT dt, Layout layout) {
+    auto it = S.index_.find(name);
+    if (it != S.index_.end()) OXB_FAIL("value '%s' is produced twice", name.c_str());
+    Value v;
+    v.name = name;
+    v.shape = shape;
+    v.dt = dt;
+    v.layout = layout;
+    v.bytes = (size_t)std::max<int64_t>(prod(shape), 0) * dt_size(dt);
+    S.values_.push_back(v);
+    int idx = (int)S.values_.size() - 1;
+    S.index_[name] = idx;
+    return idx;
+  }
+  Value& V(int i) { return S.values_[i]; }
+
+  const HostTensor* const_of(const std::string& name) const {
+    if (name.empty()) return nullptr;
+    auto it = vconsts_.find(name);
+    if (it != vconsts_.end()) return it->second;
+    return C.weight(name);
+  }
+  bool cacheable_const(const std::string& name) const { return vconsts_.find(name) == vconsts_.end(); }
+
+  // Value index of a node input; initializers that are consumed as data get a device value on demand.
+  int value_of(const std::string& name) {
+    auto it = S.index_.find(name);
+    if (it != S.index_.end()) return it->second;
+    const HostTensor* h = const_of(name);
+    if (!h) OXB_FAIL("value '%s' is neither produced by a node, fed, nor an initializer", name.c_str());
+    // constant consumed as a data operand: upload as f32 lanes in logical order
+    int idx = add_value(name, h->shape, DT::F32, Layout::PLAIN);
+    V(idx).host = h;
+    V(idx).external = true;
+    size_t bytes = std::max<size_t>(h->data.size() * 4, 4);
+    V(idx).ptr = C.resident_form(name, "raw_f32", bytes, [h](void* dst) { std::memcpy(dst, h->data.data(), h->data.size() * 4); },
+                                 cacheable_const(name));
+    return idx;
+  }
+
+  const std::string& in_name(const NodeDef& n, size_t i) const {
+    static const std::string empty;
+    return i < n.inputs.size() ? n.inputs[i] : empty;
+  }
+  const HostTensor* const_in(const NodeDef& n, size_t i) const { return const_of(in_name(n, i)); }
+  bool has_in(const NodeDef& n, size_t i) const { return i < n.inputs.size() && !n.inputs[i].empty(); }
+
+  void check_attrs(const NodeDef& n, std::initializer_list<const char*> known) {
+    for (const std::string& a : n.attrs.names()) {
+      bool ok = false;
+      for (const char* kname : known)
+        if (a == kname) ok = true;
+      if (!ok) OXB_DECLINE("%s '%s': attribute '%s' is not handled by this provider", n.op.c_str(), n.name.c_str(), a.c_str());
+    }
+  }
+
+  // ---- device parameter buffers owned by the session ----
+  template <typename T>
+  T* upload_vec(const std::vector<T>& v) {
+    size_t bytes = std::max<size_t>(v.size() * sizeof(T), 16);
+    void* p = C.alloc_device(bytes);
+    S.owned_.push_back(DeviceBuffer{p, bytes});
+    if (!v.empty()) OXB_CUDA(cudaMemcpyAsync(p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice, C.stream()));
+    OXB_CUDA(cudaStreamSynchronize(C.stream()));
+    return (T*)p;
+  }
+  void* owned_buffer(size_t bytes) {
+    void* p = C.alloc_device(bytes);
+    S.owned_.push_back(DeviceBuffer{p, std::max<size_t>(bytes, 256)});
+    return p;
+  }
+
+  // ---- steps ----
+  Step& add_step(const NodeDef& n, const char* kernel, int family, std::vector<int> reads, std::vector<int> writes) {
+    Step st;
+    st.node_name = n.name;
+    st.op_type = n.op;
+    st.kernel = kernel;
+    st.family = family;
+    st.reads = std::move(reads);
+    st.writes = std::move(writes);
+    S.steps_.push_back(std::move(st));
+    int idx = (int)S.steps_.size() - 1;
+    for (int w : S.steps_[idx].writes) V(w).producer = idx;
+    return S.steps_[idx];
+  }
+
+  static Dims4 dims_of(const Value& v) {
+    if (v.shape.size() == 4) return Dims4{v.shape[0], v.shape[1], v.shape[2], v.shape[3]};
+    if (v.shape.size() == 2) return Dims4{v.shape[0], v.shape[1], 1, 1};
+    return Dims4{std::max<int64_t>(prod(v.shape), 0), 1, 1, 1};
+  }
+  static bool order_free(const Value& v) {  // PLAIN and NHWC coincide
+    if (v.shape.size() != 4) return true;
+    return v.shape[1] == 1 || v.shape[2] * v.shape[3] == 1;
+  }
+  Layout effective_layout(const Value& v) const { return v.shape.size() == 4 ? v.layout : Layout::PLAIN; }
+
+  TensorRef ref_of(int vi, const Dims4* override_dims = nullptr) {
+    Value& v = V(vi);
+    return TensorRef{nullptr, v.dt, effective_layout(v), override_dims ? *override_dims : dims_of(v)};
+  }
+  // Resolve pointers at launch time (after the arena is laid out).
+  TensorRef bound(const TensorRef& proto, int vi) {
+    TensorRef r = proto;
+    r.ptr = V(vi).ptr;
+    return r;
+  }
+
+  // A copy of value `vi` in memory order `want` (memoised; rank-4 only).
+  int ensure_layout(const NodeDef& n, int vi, Layout want) {
+    if (V(vi).shape.size() != 4 || V(vi).layout == want) return vi;
+    if (order_free(V(vi))) return vi;  // same bytes either way: kernels take the layout they need
+    auto key = std::make_pair(vi, (int)want);
+    auto it = layout_memo_.find(key);
+    if (it != layout_memo_.end()) return it->second;
+    Value src = V(vi);
+    int out = add_value(src.name + (want == Layout::NHWC ? "@nhwc" : "@nchw"), src.shape, src.dt, want);
+    TensorRef a = ref_of(vi), b = ref_of(out);
+    Step& st = add_step(n, "convert_layout", 2, {vi}, {out});
+    st.work = 2.0 * (double)src.bytes;
+    st.launch = [this, a, b, vi, out](cudaStream_t s) {
+      k::convert(bound(a, vi), bound(b, out), s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    layout_memo_[key] = out;
+    return out;
+  }
+  // For order-free rank-4 values any kernel may treat the bytes as NHWC.
+  Layout layout_for_kernel(const Value& v, Layout want) const { return (v.shape.size() == 4 && order_free(v)) ? want : effective_layout(v); }
+
+  // Sole consumer of `name` if it is op `op` at slot 0 and the value is not a graph output.
+  int sole_consumer(const std::string& name, const char* op) {
+    if (graph_outputs_.count(name)) return -1;
+    auto it = consumers_.find(name);
+    if (it == consumers_.end() || it->second.size() != 1) return -1;
+    int ni = it->second[0].first;
+    if (it->second[0].second != 0 || nodes_[ni].op != op || skipped_[ni]) return -1;
+    if (!nodes_[ni].attrs.names().empty()) return -1;
+    return ni;
+  }
+
+  bool feeds_contraction(const std::string& name) {
+    auto it = consumers_.find(name);
+    if (it == consumers_.end()) return false;
+    for (auto& c : it->second) {
+      const std::string& op = nodes_[c.first].op;
+      if (op == "Conv" || op == "Gemm" || op == "MatMul") return true;
+      // look through nodes that only move or select values
+      if (op == "MaxPool" || op == "Flatten" || op == "Reshape" || op == "Identity" || op == "Relu" || op == "Pad" || op == "Resize" ||
+          op == "Concat")
+        if (!nodes_[c.first].outputs.empty() && feeds_contraction(nodes_[c.first].outputs[0])) return true;
+    }
+    return false;
+  }
+
+  // ---- operator rules ----
+  void plan_node(int ni);
+  void plan_quantize(const NodeDef& n);
+  void plan_dequantize(const NodeDef& n);
+  void plan_dynamic_quantize(const NodeDef& n);
+  void plan_conv_family(const NodeDef& n, int ni);
+  void plan_matmul_family(const NodeDef& n, int ni);
+  void plan_unary(const NodeDef& n);
+  void plan_binary(const NodeDef& n, int ni);
+  void plan_prelu(const NodeDef& n);
+  void plan_max_pool(const NodeDef& n);
+  void plan_global_avg_pool(const NodeDef& n);
+  void plan_instance_norm(const NodeDef& n);
+  void plan_resize(const NodeDef& n);
+  void plan_pad(const NodeDef& n);
+  void plan_concat(const NodeDef& n);
+  void plan_alias(const NodeDef& n);
+  bool try_plan_residual_chain(const NodeDef& n, int ni);
+
+  struct Contraction {
+    k::ConvShape cs;
+    int x_vi, out_vi;
+    bool x_plain_nchw = false;
+    // weights in ONNX order [OC][C/g][R][S] as exact values
+    const HostTensor* w = nullptr;
+    std::string w_name;
+    bool w_is_kn = false;  // matmul B stored [K][N]
+    bool is_int = false;
+    DT w_dt = DT::F32;
+    k::Epilogue epi;
+    std::vector<int32_t> w_zp;   // per-oc or single
+    bool x_zp_static = true;
+    int x_zp = 0;
+    int x_zp_vi = -1;            // device lane (dynamic)
+    std::vector<int32_t> x_zp_rows;
+    std::vector<int32_t> bias_i;  // empty or OC
+    std::vector<float> bias_f;    // empty or OC
+    std::vector<float> combined;  // OC
+    float w_scale_mul = 1.0f;     // Gemm alpha folded into the packed weights
+  };
+  void emit_contraction(const NodeDef& n, Contraction& c);
+
+  void finalize_lifetimes_and_arena();
+};
+
+// -----------------------------------------------------------------------------------------
+void Planner::run(const std::vector<std::pair<std::string, std::vector<int64_t>>>& inputs, const std::vector<std::string>& outputs) {
+  for (auto& o : outputs) graph_outputs_.insert(o);
+  S.outputs_ = outputs;
+  skipped_.assign(nodes_.size(), 0);
+  for (size_t ni = 0; ni < nodes_.size(); ++ni)
+    for (size_t s = 0; s < nodes_[ni].inputs.size(); ++s)
+      if (!nodes_[ni].inputs[s].empty()) consumers_[nodes_[ni].inputs[s]].push_back({(int)ni, (int)s});
+
+  OXB_CUDA(cudaMalloc(&S.err_flag_, 256));
+  OXB_CUDA(cudaMemset(S.err_flag_, 0, 256));
+
+  // graph inputs: raw f32 lanes in logical order, uploaded into persistent staging
+  for (auto& in : inputs) {
+    int vi = add_value(in.first, in.second, DT::F32, Layout::PLAIN);
+    V(vi).is_graph_input = true;
+    V(vi).external = true;
+    auto vc = vconsts_.find(in.first);
+    if (vc != vconsts_.end()) V(vi).host = vc->second;
+    auto eb = S.external_bind_.find(in.first);
+    if (eb != S.external_bind_.end()) {
+      V(vi).ptr = eb->second.first;
+      V(vi).dt = eb->second.second.first;
+      V(vi).layout = eb->second.second.second;
+      V(vi).bytes = (size_t)V(vi).numel() * dt_size(V(vi).dt);
+    } else {
+      V(vi).ptr = owned_buffer(std::max<size_t>(V(vi).bytes, 256));
+    }
+    S.input_staging_.push_back({in.first, vi});
+  }
+
+  for (size_t ni = 0; ni < nodes_.size(); ++ni) {
+    if (skipped_[ni]) continue;
+    cur_node_ = (int)ni;
+    plan_node((int)ni);
+  }
+
+  // graph outputs: f32 lanes in logical order in persistent staging
+  NodeDef out_node;
+  out_node.op = "(output)";
+  for (auto& o : outputs) {
+    auto it = S.index_.find(o);
+    if (it == S.index_.end()) OXB_FAIL("graph output '%s' is not produced by any planned node", o.c_str());
+    int vi = it->second;
+    V(vi).is_graph_output = true;
+    out_node.name = o;
+    bool direct = V(vi).dt == DT::F32 && (effective_layout(V(vi)) == Layout::PLAIN || order_free(V(vi))) && V(vi).alias_of < 0 &&
+                  !V(vi).is_graph_input && V(vi).host == nullptr;
+    if (direct) {
+      // give the value its own persistent storage instead of an arena slot
+      V(vi).external = true;
+      V(vi).ptr = owned_buffer(std::max<size_t>(V(vi).bytes, 256));
+      S.output_staging_.push_back({o, vi});
+      continue;
+    }
+    int so = add_value(o + "@host", V(vi).shape, DT::F32, Layout::PLAIN);
+    V(so).external = true;
+    V(so).ptr = owned_buffer(std::max<size_t>(V(so).bytes, 256));
+    Dims4 d = V(vi).shape.size() == 4 ? dims_of(V(vi)) : Dims4{std::max<int64_t>(V(vi).numel(), 0), 1, 1, 1};
+    TensorRef a{nullptr, V(vi).dt, effective_layout(V(vi)), d}, b{nullptr, DT::F32, Layout::PLAIN, d};
+    Step& st = add_step(out_node, "convert_output", 2, {vi}, {so});
+    st.work = (double)V(vi).bytes + (double)V(so).bytes;
+    st.launch = [this, a, b, vi, so](cudaStream_t s) {
+      k::convert(bound(a, vi), bound(b, so), s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    S.output_staging_.push_back({o, so});
+  }
+
+  finalize_lifetimes_and_arena();
+  for (auto& st : S.steps_)
+    if (st.finalize) st.finalize();
+}
+
+void Planner::finalize_lifetimes_and_arena() {
+  const int n_steps = (int)S.steps_.size();
+  for (int si = 0; si < n_steps; ++si)
+    for (int r : S.steps_[si].reads) V(r).last_use = std::max(V(r).last_use, si);
+  // aliases extend the life of the storage they share
+  for (int i = (int)S.values_.size() - 1; i >= 0; --i) {
+    Value& v = V(i);
+    if (v.alias_of >= 0) {
+      Value& root = V(v.alias_of);
+      root.last_use = std::max(root.last_use, std::max(v.last_use, v.is_graph_output ? n_steps : -1));
+      if (v.is_graph_output) root.is_graph_output = true;
+    }
+  }
+  struct Slot {
+    size_t bytes;
+    int free_after;
+  };
+  std::vector<Slot> slots;
+  std::vector<int> order;
+  for (int i = 0; i < (int)S.values_.size(); ++i) {
+    Value& v = V(i);
+    if (v.external || v.alias_of >= 0 || v.producer < 0) continue;
+    order.push_back(i);
+  }
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return V(a).producer < V(b).producer; });
+  const bool keep_all = C.cfg().keep_intermediates != 0;
+  for (int i : order) {
+    Value& v = V(i);
+    int last = v.is_graph_output ? n_steps : std::max(v.last_use, v.producer);
+    size_t need = align_up(std::max<size_t>(v.bytes, 1), 1024);
+    int best = -1;
+    if (!keep_all) {
+      // smallest free slot that already fits, else the smallest free slot (grown)
+      for (int s = 0; s < (int)slots.size(); ++s)
+        if (slots[s].free_after < v.producer && slots[s].bytes >= need && (best < 0 || slots[s].bytes < slots[best].bytes)) best = s;
+      if (best < 0)
+        for (int s = 0; s < (int)slots.size(); ++s)
+          if (slots[s].free_after < v.producer && (best < 0 || slots[s].bytes < slots[best].bytes)) best = s;
+    }
+    if (best < 0) {
+      slots.push_back(Slot{need, last});
+      best = (int)slots.size() - 1;
+    } else {
+      slots[best].bytes = std::max(slots[best].bytes, need);
+      slots[best].free_after = last;
+    }
+    v.slot = best;
+  }
+  size_t total = 0;
+  std::vector<size_t> offs(slots.size());
+  for (size_t s = 0; s < slots.size(); ++s) {
+    offs[s] = total;
+    total += slots[s].bytes;
+  }
+  S.n_slots_ = slots.size();
+  S.arena_.bytes = total;
+  if (total > 0) {
+    OXB_CUDA(cudaMalloc(&S.arena_.ptr, total));
+  }
+  for (int i : order) V(i).ptr = (uint8_t*)S.arena_.ptr + offs[V(i).slot];
+  for (int i = 0; i < (int)S.values_.size(); ++i)
+    if (V(i).alias_of >= 0) {
+      int r = V(i).alias_of;
+      while (V(r).alias_of >= 0) r = V(r).alias_of;
+      V(i).ptr = V(r).ptr;
+    }
+  C.counters.arena_bytes = total;
+  C.counters.arena_peak_bytes = std::max<uint64_t>(C.counters.arena_peak_bytes, total);
+  C.counters.arena_slots = slots.size();
+}
+
+// -----------------------------------------------------------------------------------------
+void Planner::plan_node(int ni) {
+  const NodeDef& n = nodes_[ni];
+  const std::string& op = n.op;
+  if (!is_supported_op(op)) OXB_DECLINE("operator '%s' (node '%s') is not claimed by this provider", op.c_str(), n.name.c_str());
+  if (op == "QuantizeLinear") return plan_quantize(n);
+  if (op == "DequantizeLinear") {
+    if (try_plan_residual_chain(n, ni)) return;
+    return plan_dequantize(n);
+  }
+  if (op == "DynamicQuantizeLinear") return plan_dynamic_quantize(n);
+  if (op == "Conv" || op == "QLinearConv" || op == "ConvInteger") return plan_conv_family(n, ni);
+  if (op == "Gemm" || op == "MatMul" || op == "QLinearMatMul" || op == "MatMulInteger") return plan_matmul_family(n, ni);
+  if (op == "Relu" || op == "Tanh" || op == "Sigmoid") return plan_unary(n);
+  if (op == "Add" || op == "Sub" || op == "Mul" || op == "Div") return plan_binary(n, ni);
+  if (op == "PRelu") return plan_prelu(n);
+  if (op == "MaxPool") return plan_max_pool(n);
+  if (op == "GlobalAveragePool") return plan_global_avg_pool(n);
+  if (op == "OxiInstanceNorm") return plan_instance_norm(n);
+  if (op == "Resize") return plan_resize(n);
+  if (op == "Pad") return plan_pad(n);
+  if (op == "Concat") return plan_concat(n);
+  if (op == "Flatten" || op == "Reshape" || op == "Identity" || op == "Cast") return plan_alias(n);
+  OXB_DECLINE("operator '%s' has no planning rule", op.c_str());
+}
+
+// ---- QuantizeLinear / DequantizeLinear (oxionnx-ops src/indexing/quantize.rs:58-193) -------
+static void quant_axis_view(const Value& x, int64_t axis_raw, int64_t plen, const char* op, Dims4* d, bool* use_native4) {
+  int64_t rank = (int64_t)x.shape.size();
+  *use_native4 = false;
+  if (plen <= 1) {
+    if (rank == 4) {
+      *d = Dims4{x.shape[0], x.shape[1], x.shape[2], x.shape[3]};
+      *use_native4 = true;
+    } else {
+      *d = Dims4{std::max<int64_t>(prod(x.shape), 0), 1, 1, 1};
+    }
+    return;
+  }
+  int64_t axis = axis_raw < 0 ? axis_raw + rank : axis_raw;
+  if (axis < 0 || axis >= rank) OXB_DECLINE("%s: axis %lld out of range for rank %lld", op, (long long)axis_raw, (long long)rank);
+  if (x.shape[axis] != plen) OXB_DECLINE("%s: %lld quantisation parameters for an axis of extent %lld", op, (long long)plen, (long long)x.shape[axis]);
+  if (rank == 4 && axis == 1) {
+    *d = Dims4{x.shape[0], x.shape[1], x.shape[2], x.shape[3]};
+    *use_native4 = true;
+    return;
+  }
+  if (rank == 4 && x.layout == Layout::NHWC && !(x.shape[1] == 1 || x.shape[2] * x.shape[3] == 1))
+    OXB_DECLINE("%s: per-axis parameters on axis %lld of a channels-last activation", op, (long long)axis);
+  int64_t outer = 1, inner = 1;
+  for (int64_t i = 0; i < axis; ++i) outer *= x.shape[i];
+  for (int64_t i = axis + 1; i < rank; ++i) inner *= x.shape[i];
+  *d = Dims4{outer, x.shape[axis], inner, 1};
+}
+
+void Planner::plan_quantize(const NodeDef& n) {
+  check_attrs(n, {"axis"});
+  if (n.attrs.has("saturate") || n.attrs.has("block_size")) OXB_DECLINE("QuantizeLinear: blocked / non-saturating forms");
+  const HostTensor* scale = const_in(n, 1);
+  const HostTensor* zp = has_in(n, 2) ? const_in(n, 2) : nullptr;
+  if (!scale || (has_in(n, 2) && !zp)) OXB_DECLINE("QuantizeLinear '%s': scale / zero point are not initializers", n.name.c_str());
+  if (scale->data.empty()) OXB_DECLINE("quantize_linear: y_scale must have at least one element");
+  if (zp && zp->data.empty()) OXB_DECLINE("quantize_linear: y_zero_point must have at least one element when provided");
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).dt != DT::F32) OXB_DECLINE("QuantizeLinear '%s': input is not a float tensor", n.name.c_str());
+  // saturation_range (quantize.rs:58-64): absent -> u8; any lane > 127 -> u8; otherwise i8
+  float lo = 0.f, hi = 255.f;
+  if (zp) {
+    bool any_gt = false;
+    for (float z : zp->data) any_gt |= z > 127.0f;
+    if (!any_gt) {
+      lo = -128.f;
+      hi = 127.f;
+    }
+    for (float z : zp->data)
+      if (!std::isfinite(z) || z != std::nearbyint(z)) OXB_DECLINE("QuantizeLinear '%s': non-integral zero point", n.name.c_str());
+  }
+  for (float sc : scale->data)
+    if (!std::isfinite(sc) || sc == 0.f) OXB_DECLINE("QuantizeLinear '%s': zero or non-finite scale", n.name.c_str());
+  int64_t ns = (int64_t)scale->data.size(), nz = zp ? (int64_t)zp->data.size() : 0;
+  int64_t plen = std::max(ns, nz);
+  Dims4 d;
+  bool native4;
+  quant_axis_view(V(xi), n.attrs.i("axis", 1), plen, "QuantizeLinear", &d, &native4);
+  if ((ns > 1 && ns != d.C) || (nz > 1 && nz != d.C)) OXB_DECLINE("QuantizeLinear '%s': parameter length disagrees with the axis", n.name.c_str());
+  DT odt = lo < 0 ? DT::I8 : DT::U8;
+  Layout ol = V(xi).shape.size() == 4 ? Layout::NHWC : Layout::PLAIN;
+  if (!native4 && V(xi).shape.size() == 4) ol = V(xi).layout;
+  int yi = add_value(n.outputs[0], V(xi).shape, odt, ol);
+  TensorRef xr{nullptr, DT::F32, native4 ? layout_for_kernel(V(xi), ol) : Layout::PLAIN, d};
+  TensorRef yr{nullptr, odt, native4 ? ol : Layout::PLAIN, d};
+  const float* dscale = (const float*)C.resident_form(in_name(n, 1), "raw_f32", scale->data.size() * 4,
+                                                      [scale](void* p) { std::memcpy(p, scale->data.data(), scale->data.size() * 4); },
+                                                      cacheable_const(in_name(n, 1)));
+  const float* dzp = nullptr;
+  if (zp)
+    dzp = (const float*)C.resident_form(in_name(n, 2), "raw_f32", zp->data.size() * 4, [zp](void* p) { std::memcpy(p, zp->data.data(), zp->data.size() * 4); },
+                                        cacheable_const(in_name(n, 2)));
+  float s0 = scale->data[0], z0 = zp ? zp->data[0] : 0.f;
+  bool scalar = ns == 1 && nz <= 1;
+  Step& st = add_step(n, "quantize_linear", 2, {xi}, {yi});
+  st.work = (double)V(xi).bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, dscale, ns, dzp, nz, lo, hi, scalar, s0, z0](cudaStream_t s) {
+    TensorRef a = bound(xr, xi), b = bound(yr, yi);
+    if (scalar && k::quantize_linear_scalar_ok(a, b)) k::quantize_linear_scalar(a, b, s0, z0, lo, hi, s);
+    else k::quantize_linear(a, b, dscale, ns, dzp, nz, lo, hi, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_dequantize(const NodeDef& n) {
+  check_attrs(n, {"axis"});
+  const HostTensor* scale = const_in(n, 1);
+  const HostTensor* zp = has_in(n, 2) ? const_in(n, 2) : nullptr;
+  if (!scale || (has_in(n, 2) && !zp)) OXB_DECLINE("DequantizeLinear '%s': scale / zero point are not initializers", n.name.c_str());
+  if (scale->data.empty()) OXB_DECLINE("dequantize_linear: x_scale must have at least one element");
+  if (zp && zp->data.empty()) OXB_DECLINE("dequantize_linear: x_zero_point must have at least one element when provided");
+  int xi = value_of(in_name(n, 0));
+  int64_t ns = (int64_t)scale->data.size(), nz = zp ? (int64_t)zp->data.size() : 0;
+  Dims4 d;
+  bool native4;
+  quant_axis_view(V(xi), n.attrs.i("axis", 1), std::max(ns, nz), "DequantizeLinear", &d, &native4);
+  if ((ns > 1 && ns != d.C) || (nz > 1 && nz != d.C)) OXB_DECLINE("DequantizeLinear '%s': parameter length disagrees with the axis", n.name.c_str());
+  Layout l = V(xi).shape.size() == 4 ? V(xi).layout : Layout::PLAIN;
+  int yi = add_value(n.outputs[0], V(xi).shape, DT::F32, l);
+  TensorRef xr{nullptr, V(xi).dt, native4 ? effective_layout(V(xi)) : Layout::PLAIN, d};
+  TensorRef yr{nullptr, DT::F32, native4 ? l : Layout::PLAIN, d};
+  const float* dscale = (const float*)C.resident_form(in_name(n, 1), "raw_f32", scale->data.size() * 4,
+                                                      [scale](void* p) { std::memcpy(p, scale->data.data(), scale->data.size() * 4); },
+                                                      cacheable_const(in_name(n, 1)));
+  const float* dzp = nullptr;
+  if (zp)
+    dzp = (const float*)C.resident_form(in_name(n, 2), "raw_f32", zp->data.size() * 4, [zp](void* p) { std::memcpy(p, zp->data.data(), zp->data.size() * 4); },
+                                        cacheable_const(in_name(n, 2)));
+  Step& st = add_step(n, "dequantize_linear", 2, {xi}, {yi});
+  st.work = (double)V(xi).bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, dscale, ns, dzp, nz](cudaStream_t s) {
+    k::dequantize_linear(bound(xr, xi), bound(yr, yi), dscale, ns, dzp, nz, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+// DynamicQuantizeLinear (quant_ops/dynamic_quantize.rs:51-93): y plus rank-0 scale and zero point,
+// both kept as device f32 lanes so a following MatMulInteger reads them without a host trip.
+void Planner::plan_dynamic_quantize(const NodeDef& n) {
+  check_attrs(n, {});
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).dt != DT::F32) OXB_DECLINE("DynamicQuantizeLinear '%s': input is not a float tensor", n.name.c_str());
+  if (V(xi).numel() == 0) OXB_DECLINE("DynamicQuantizeLinear: input is empty");
+  if (V(xi).host)
+    for (float f : V(xi).host->data)
+      if (!std::isfinite(f)) OXB_DECLINE("DynamicQuantizeLinear: input contains a non-finite value");
+  int yi = add_value(n.outputs[0], V(xi).shape, DT::U8, V(xi).shape.size() == 4 ? V(xi).layout : Layout::PLAIN);
+  // scale and zero point live side by side in one 2-lane buffer; the two output values alias it
+  int pi = add_value(n.outputs[0] + "@params", {2}, DT::F32, Layout::PLAIN);
+  int si = -1, zi = -1;
+  if (n.outputs.size() > 1 && !n.outputs[1].empty()) {
+    si = add_value(n.outputs[1], {}, DT::F32, Layout::PLAIN);
+    V(si).alias_of = pi;
+  }
+  if (n.outputs.size() > 2 && !n.outputs[2].empty()) {
+    zi = add_value(n.outputs[2], {}, DT::F32, Layout::PLAIN);
+    V(zi).alias_of = pi;
+  }
+  float* scratch = (float*)owned_buffer(256);
+  Dims4 d{V(xi).numel(), 1, 1, 1};
+  TensorRef xr{nullptr, DT::F32, Layout::PLAIN, d}, yr{nullptr, DT::U8, Layout::PLAIN, d};
+  std::vector<int> writes = {yi, pi};
+  Step& st = add_step(n, "dynamic_quantize_linear", 2, {xi}, writes);
+  st.work = 2.0 * (double)V(xi).bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, pi, scratch](cudaStream_t s) {
+    k::dynamic_quantize_linear(bound(xr, xi), bound(yr, yi), (float*)V(pi).ptr, scratch, s);
+    C.counters.glue_launches += 4;
+    C.counters.kernel_launches += 4;
+  };
+  // the zero-point alias points one lane further
+  if (zi >= 0) {
+    Step& st2 = S.steps_.back();
+    auto prev = st2.finalize;
+    st2.finalize = [this, zi, pi, prev]() {
+      if (prev) prev();
+      V(zi).ptr = (uint8_t*)V(pi).ptr + 4;
+    };
+  }
+  (void)si;
+}
+
+// ---- contractions --------------------------------------------------------------------------
+void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
+  const k::ConvShape& cs = c.cs;
+  const int OC = cs.OC, cg = cs.C / cs.group;
+  const int64_t taps = (int64_t)cs.R * cs.S;
+  const HostTensor* w = c.w;
+  const bool cache_w = cacheable_const(c.w_name);
+
+  auto w_at = [&](int oc, int ic, int64_t tap) -> float {
+    if (c.w_is_kn) return w->data[(size_t)ic * OC + oc];  // B[K][N]
+    return w->data[((size_t)oc * cg + ic) * taps + tap];
+  };
+
+  // integer weights: exact values, narrowest storage
+  std::vector<int32_t> wi;
+  if (c.is_int) {
+    if (!lanes_to_i32(*w, &wi)) OXB_DECLINE("%s '%s': weight holds a non-finite or out-of-range lane", n.op.c_str(), n.name.c_str());
+    int32_t lo = 0, hi = 0;
+    for (int32_t v : wi) {
+      lo = std::min(lo, v);
+      hi = std::max(hi, v);
+    }
+    c.w_dt = narrowest_int(lo, hi);
+  }
+  auto wi_at = [&](int oc, int ic, int64_t tap) -> int32_t {
+    if (c.w_is_kn) return wi[(size_t)ic * OC + oc];
+    return wi[((size_t)oc * cg + ic) * taps + tap];
+  };
+
+  // ---- can the tensor-core kernel take it? ----
+  std::string why;
+  bool want_umma = C.cfg().kernel_path == 0 && k::umma_available() && !c.x_plain_nchw;
+  Value& xv = V(c.x_vi);
+  if (want_umma && c.is_int) {
+    bool w_zp_zero = true;
+    for (int32_t z : c.w_zp) w_zp_zero &= z == 0;
+    bool pads = cs.pt || cs.pl || cs.pb || cs.pr;
+    if (!(xv.dt == DT::U8 || xv.dt == DT::I8)) want_umma = false, why = "activation is not stored as 8-bit";
+    else if (!(c.w_dt == DT::I8 || c.w_dt == DT::U8)) want_umma = false, why = "weights do not fit 8 bits";
+    else if (!w_zp_zero) want_umma = false, why = "non-zero weight zero point";
+    else if (!c.x_zp_rows.empty()) want_umma = false, why = "per-row zero point";
+    else if (pads && !(c.x_zp_static && c.x_zp == 0)) want_umma = false, why = "padding with a non-zero input zero point";
+    else if ((double)cs.K() * 255.0 * 255.0 >= 2147483647.0) want_umma = false, why = "reduction too long for an s32 accumulator";
+  } else if (want_umma && xv.dt != DT::F32) {
+    want_umma = false;
+  }
+  if (want_umma && k::umma_channel_block(cs.C, c.is_int ? 0 : 1) == 0) want_umma = false, why = "channel count not a multiple of the block";
+  if (want_umma && cs.group != 1) want_umma = false, why = "grouped";
+
+  // ---- epilogue parameter vectors ----
+  k::Epilogue epi = c.epi;
+  std::vector<int32_t> wsum(OC, 0);
+  if (c.is_int)
+    for (int oc = 0; oc < OC; ++oc) {
+      int64_t s = 0;
+      for (int ic = 0; ic < cg; ++ic)
+        for (int64_t t = 0; t < taps; ++t) s += wi_at(oc, ic, t);
+      wsum[oc] = (int32_t)s;
+    }
+
+  const int x_vi = c.x_vi, out_vi = c.out_vi, xzp_vi = c.x_zp_vi;
+  std::vector<int> reads = {x_vi};
+  if (xzp_vi >= 0) reads.push_back(xzp_vi);
+
+  if (want_umma) {
+    const int kind = c.is_int ? 0 : 1;
+    const size_t es = c.is_int ? 1 : 4;
+    const int64_t ktot = cs.K();
+    const size_t wbytes = (size_t)OC * ktot * es;
+    char form[96];
+    snprintf(form, sizeof form, "umma_%s_%dx%dx%dx%d_a%.9g%s", c.is_int ? dt_name(c.w_dt) : "tf32", OC, cs.C, cs.R, cs.S, (double)c.w_scale_mul,
+             c.w_is_kn ? "_kn" : "");
+    const float wmul = c.w_scale_mul;
+    void* wdev = C.resident_form(
+        c.w_name, form, wbytes,
+        [&](void* dst) {
+          for (int oc = 0; oc < OC; ++oc)
+            for (int64_t t = 0; t < taps; ++t)
+              for (int ic = 0; ic < cs.C; ++ic) {
+                size_t o = (size_t)oc * ktot + (size_t)t * cs.C + ic;
+                if (c.is_int) ((uint8_t*)dst)[o] = (uint8_t)(wi_at(oc, ic, t) & 0xff);
+                else ((float*)dst)[o] = round_to_tf32(wmul == 1.0f ? w_at(oc, ic, t) : w_at(oc, ic, t) * wmul);
+              }
+        },
+        cache_w);
+    if (c.is_int) {
+      std::vector<int32_t> bias_eff(OC, 0);
+      for (int oc = 0; oc < OC; ++oc) {
+        int64_t b = c.bias_i.empty() ? 0 : c.bias_i[oc];
+        if (c.x_zp_static) b -= (int64_t)c.x_zp * wsum[oc];
+        if (b < INT32_MIN || b > INT32_MAX) OXB_DECLINE("%s '%s': folded bias leaves the int32 range", n.op.c_str(), n.name.c_str());
+        bias_eff[oc] = (int32_t)b;
+      }
+      epi.bias_i = upload_vec(bias_eff);
+      epi.wsum = c.x_zp_static ? nullptr : upload_vec(wsum);
+      if (epi.mode == k::EPI_REQUANT) epi.combined = upload_vec(c.combined);
+    } else {
+      epi.bias_f = c.bias_f.empty() ? nullptr : upload_vec(c.bias_f);
+    }
+    Step& st = add_step(n, "umma", 0, reads, {out_vi});
+    st.work = cs.ops();
+    st.work_is_bytes = false;
+    const DT xdt = xv.dt, wdt = c.is_int ? c.w_dt : DT::F32;
+    Step* stp = &st;
+    const int step_index = (int)S.steps_.size() - 1;
+    st.finalize = [this, step_index, x_vi, out_vi, xzp_vi, wdev, xdt, wdt, cs, epi, kind, n]() mutable {
+      k::Epilogue e = epi;
+      if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
+      std::string why2;
+      k::UmmaPlan* plan = k::umma_plan_create(V(x_vi).ptr, xdt, wdev, wdt, V(out_vi).ptr, cs, e, kind, &why2);
+      if (!plan) OXB_FAIL("%s '%s': tensor-core plan rejected after selection: %s", n.op.c_str(), n.name.c_str(), why2.c_str());
+      S.umma_plans_.push_back(plan);
+      Step& me = S.steps_[step_index];
+      me.kernel = k::umma_plan_desc(plan);
+      int* err = S.err_flag_;
+      me.launch = [this, plan, err](cudaStream_t s) {
+        k::umma_launch(plan, err, s);
+        C.counters.umma_launches++;
+        C.counters.kernel_launches++;
+      };
+    };
+    (void)stp;
+    return;
+  }
+
+  // ---- direct kernel ----
+  {
+    const size_t es = c.is_int ? dt_size(c.w_dt) : 4;
+    const size_t wbytes = (size_t)taps * cg * OC * es;
+    char form[96];
+    snprintf(form, sizeof form, "direct_%s_%dx%dx%dx%d_a%.9g%s", c.is_int ? dt_name(c.w_dt) : "f32", OC, cg, cs.R, cs.S, (double)c.w_scale_mul,
+             c.w_is_kn ? "_kn" : "");
+    const float wmul = c.w_scale_mul;
+    const DT wdt = c.is_int ? c.w_dt : DT::F32;
+    void* wdev = C.resident_form(
+        c.w_name, form, wbytes,
+        [&](void* dst) {
+          for (int64_t t = 0; t < taps; ++t)
+            for (int ic = 0; ic < cg; ++ic)
+              for (int oc = 0; oc < OC; ++oc) {
+                size_t o = ((size_t)t * cg + ic) * OC + oc;
+                if (!c.is_int) {
+                  ((float*)dst)[o] = wmul == 1.0f ? w_at(oc, ic, t) : w_at(oc, ic, t) * wmul;
+                } else {
+                  int32_t v = wi_at(oc, ic, t);
+                  switch (wdt) {
+                    case DT::U8: ((uint8_t*)dst)[o] = (uint8_t)v; break;
+                    case DT::I8: ((int8_t*)dst)[o] = (int8_t)v; break;
+                    case DT::I16: ((int16_t*)dst)[o] = (int16_t)v; break;
+                    default: ((int32_t*)dst)[o] = v; break;
+                  }
+                }
+              }
+        },
+        cache_w);
+    if (c.is_int) {
+      epi.bias_i = c.bias_i.empty() ? nullptr : upload_vec(c.bias_i);
+      epi.x_zp = c.x_zp;
+      if (!c.x_zp_rows.empty()) epi.x_zp_rows = upload_vec(c.x_zp_rows);
+      bool any_wzp = false;
+      for (int32_t z : c.w_zp) any_wzp |= z != 0;
+      if (any_wzp) {
+        epi.w_zp = upload_vec(c.w_zp);
+        epi.n_w_zp = (int)c.w_zp.size();
+      }
+      if (epi.mode == k::EPI_REQUANT) epi.combined = upload_vec(c.combined);
+    } else {
+      epi.bias_f = c.bias_f.empty() ? nullptr : upload_vec(c.bias_f);
+    }
+    Step& st = add_step(n, "direct", 1, reads, {out_vi});
+    st.kernel = std::string("direct_") + (c.is_int ? "int" : "f32") + (why.empty() ? "" : (" (" + why + ")"));
+    st.work = cs.ops();
+    st.work_is_bytes = false;
+    const DT xdt = xv.dt;
+    const int plain = c.x_plain_nchw ? 1 : 0;
+    st.launch = [this, x_vi, out_vi, xzp_vi, wdev, xdt, wdt, cs, epi, plain](cudaStream_t s) {
+      k::Epilogue e = epi;
+      if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
+      k::conv_direct(V(x_vi).ptr, xdt, plain, wdev, wdt, V(out_vi).ptr, cs, e, s);
+      C.counters.simt_launches++;
+      C.counters.kernel_launches++;
+    };
+  }
+}
+
+// Integer storage for a value that reaches an integer contraction as f32 lanes (a fed graph
+// input, or an operand of a one-node dispatch whose lanes are known).
+static DT int_storage_for(const Value& v, bool* ok) {
+  *ok = true;
+  if (v.dt != DT::F32) return v.dt;
+  if (!v.host) return DT::I32;
+  int64_t lo = 0, hi = 0;
+  for (float f : v.host->data) {
+    int32_t q;
+    if (!lane_to_i32(f, &q)) {
+      *ok = false;
+      return DT::I32;
+    }
+    lo = std::min<int64_t>(lo, q);
+    hi = std::max<int64_t>(hi, q);
+  }
+  return narrowest_int(lo, hi);
+}
+
+void Planner::plan_conv_family(const NodeDef& n, int ni) {
+  (void)ni;
+  const std::string& op = n.op;
+  const bool is_q = op == "QLinearConv", is_ci = op == "ConvInteger", is_f = op == "Conv";
+  if (is_f) check_attrs(n, {"strides", "pads", "dilations", "group", "auto_pad", "kernel_shape", "activation", "activation_min", "activation_max"});
+  else check_attrs(n, {"strides", "pads", "dilations", "group", "auto_pad", "kernel_shape"});
+  const size_t w_slot = is_q ? 3 : 1;
+  const HostTensor* w = const_in(n, w_slot);
+  if (!w) OXB_DECLINE("%s '%s': the filter is not an initializer", op.c_str(), n.name.c_str());
+  int xi = value_of(in_name(n, 0));
+  const Value xv = V(xi);
+  if (xv.shape.size() != 4 || w->shape.size() != 4) OXB_DECLINE("%s '%s': only 2-D convolutions (rank-4 operands) are claimed", op.c_str(), n.name.c_str());
+  if ((int64_t)w->data.size() != w->numel()) OXB_DECLINE("%s: weight data length does not match its shape", op.c_str());
+  int64_t group = n.attrs.i("group", 1);
+  if (group < 1) OXB_DECLINE("%s: group must be >= 1", op.c_str());
+  if (w->shape[1] * group != xv.shape[1]) OXB_DECLINE("%s: input channels %lld != weight input channels %lld * group %lld", op.c_str(), (long long)xv.shape[1], (long long)w->shape[1], (long long)group);
+  if (w->shape[0] % group != 0) OXB_DECLINE("%s: output channels not divisible by group", op.c_str());
+  if (is_f) {
+    auto ks = n.attrs.int_list("kernel_shape");
+    if (!ks.empty()) {
+      if (ks.size() < 2 || ks[0] != w->shape[2] || ks[1] != w->shape[3]) OXB_DECLINE("Conv: kernel_shape disagrees with weight spatial dims");
+    }
+  }
+  Geo g = resolve_geometry(op.c_str(), n.attrs, xv.shape.data() + 2, w->shape.data() + 2, 2, false);
+  Contraction c;
+  k::ConvShape& cs = c.cs;
+  cs.N = (int)xv.shape[0];
+  cs.C = (int)xv.shape[1];
+  cs.H = (int)xv.shape[2];
+  cs.W = (int)xv.shape[3];
+  cs.OC = (int)w->shape[0];
+  cs.R = (int)w->shape[2];
+  cs.S = (int)w->shape[3];
+  cs.P = (int)g.out_spatial[0];
+  cs.Q = (int)g.out_spatial[1];
+  cs.sh = (int)g.strides[0];
+  cs.sw = (int)g.strides[1];
+  cs.pt = (int)g.pads[0];
+  cs.pl = (int)g.pads[1];
+  cs.pb = (int)g.pads[2];
+  cs.pr = (int)g.pads[3];
+  cs.dh = (int)g.dilations[0];
+  cs.dw = (int)g.dilations[1];
+  cs.group = (int)group;
+  c.w = w;
+  c.w_name = in_name(n, w_slot);
+  c.is_int = !is_f;
+  std::vector<int64_t> out_shape = {xv.shape[0], w->shape[0], g.out_spatial[0], g.out_spatial[1]};
+  std::string out_name = n.outputs[0];
+
+  if (is_f) {
+    if (xv.dt != DT::F32) OXB_DECLINE("Conv '%s': input is not a float tensor", n.name.c_str());
+    const HostTensor* b = has_in(n, 2) ? const_in(n, 2) : nullptr;
+    if (has_in(n, 2) && !b) OXB_DECLINE("Conv '%s': bias is not an initializer", n.name.c_str());
+    if (b) {
+      if ((int64_t)b->data.size() != cs.OC) OXB_DECLINE("Conv: bias has %zu entries, expected %d", b->data.size(), cs.OC);
+      c.bias_f = b->data;
+    }
+    c.epi.mode = k::EPI_F32;
+    std::string act = n.attrs.s("activation");
+    if (act == "relu") {
+      c.epi.act = 1;
+    } else if (act == "clip") {
+      float mn = n.attrs.f("activation_min", -std::numeric_limits<float>::infinity());
+      float mx = n.attrs.f("activation_max", std::numeric_limits<float>::infinity());
+      float lo = std::isnan(mn) ? -std::numeric_limits<float>::infinity() : mn;
+      float hi = std::isnan(mx) ? std::numeric_limits<float>::infinity() : mx;
+      if (lo <= hi) {  // an inverted range passes the data through (conv_ops/conv.rs:150)
+        c.epi.act = 2;
+        c.epi.clip_lo = lo;
+        c.epi.clip_hi = hi;
+      }
+    } else if (!act.empty()) {
+      OXB_DECLINE("Conv '%s': fused activation '%s' is not one the optimizer emits", n.name.c_str(), act.c_str());
+    }
+    c.epi.out_dt = DT::F32;
+    // a stem that reads a channels-first graph input directly skips the layout pass
+    bool direct_nchw = xv.layout == Layout::PLAIN && !order_free(xv) && k::umma_channel_block(cs.C, 1) == 0;
+    if (direct_nchw) {
+      c.x_plain_nchw = true;
+      c.x_vi = xi;
+    } else {
+      c.x_vi = ensure_layout(n, xi, Layout::NHWC);
+    }
+    c.out_vi = add_value(out_name, out_shape, DT::F32, Layout::NHWC);
+    c.epi.round_tf32 = feeds_contraction(out_name) ? 1 : 0;
+    emit_contraction(n, c);
+    return;
+  }
+
+  // ---- integer convolutions ----
+  auto zp_lanes = [&](size_t slot, const char* what, std::vector<int32_t>* out) {
+    out->assign(1, 0);
+    if (!has_in(n, slot)) return;
+    const HostTensor* t = const_in(n, slot);
+    if (!t) OXB_DECLINE("%s '%s': %s is not an initializer", op.c_str(), n.name.c_str(), what);
+    if (t->data.empty()) return;
+    if (!lanes_to_i32(*t, out)) OXB_DECLINE("%s: %s holds a non-finite or out-of-range lane", op.c_str(), what);
+  };
+  auto scale_in = [&](size_t slot, const char* what) -> float {
+    const HostTensor* t = const_in(n, slot);
+    if (!t) OXB_DECLINE("%s '%s': %s is not an initializer", op.c_str(), n.name.c_str(), what);
+    if (t->data.empty()) OXB_DECLINE("%s: %s is empty", op.c_str(), what);
+    float v = t->data[0];
+    if (!std::isfinite(v)) OXB_DECLINE("%s: %s must be finite", op.c_str(), what);
+    if (v == 0.0f) OXB_DECLINE("%s: %s scale is zero", op.c_str(), what);
+    return v;
+  };
+  std::vector<int32_t> x_zp_l, w_zp_l, y_zp_l;
+  zp_lanes(is_q ? 2 : 2, "x_zero_point", &x_zp_l);
+  zp_lanes(is_q ? 5 : 3, "w_zero_point", &w_zp_l);
+  if (w_zp_l.size() != 1 && (int64_t)w_zp_l.size() != cs.OC) OXB_DECLINE("%s: w_zero_point has %zu entries, expected 1 or %d", op.c_str(), w_zp_l.size(), cs.OC);
+  c.x_zp = x_zp_l.empty() ? 0 : x_zp_l[0];
+  c.w_zp = w_zp_l;
+  bool ok_lanes;
+  DT want_x = int_storage_for(xv, &ok_lanes);
+  if (!ok_lanes) OXB_DECLINE("%s: input holds a non-finite or out-of-range lane", op.c_str());
+  int xq = xi;
+  if (xv.dt == DT::F32) {
+    // f32 lanes -> integer storage, channels-last
+    xq = add_value(xv.name + "@int", xv.shape, want_x, Layout::NHWC);
+    TensorRef a = ref_of(xi), b = ref_of(xq);
+    a.layout = layout_for_kernel(xv, Layout::NHWC);
+    Step& st = add_step(n, "lanes_to_int", 2, {xi}, {xq});
+    st.work = (double)xv.bytes + (double)V(xq).bytes;
+    st.launch = [this, a, b, xi, xq](cudaStream_t s) {
+      k::convert(bound(a, xi), bound(b, xq), s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+  } else {
+    xq = ensure_layout(n, xi, Layout::NHWC);
+  }
+  c.x_vi = xq;
+
+  if (is_ci) {
+    c.epi.mode = k::EPI_INT32;
+    c.epi.out_dt = DT::I32;
+    c.out_vi = add_value(out_name, out_shape, DT::I32, Layout::NHWC);
+    emit_contraction(n, c);
+    return;
+  }
+  float x_scale = scale_in(1, "x_scale");
+  const HostTensor* w_scale = const_in(n, 4);
+  if (!w_scale) OXB_DECLINE("QLinearConv '%s': w_scale is not an initializer", n.name.c_str());
+  if (w_scale->data.empty()) OXB_DECLINE("QLinearConv: w_scale is empty");
+  float y_scale = scale_in(6, "y_scale");
+  zp_lanes(7, "y_zero_point", &y_zp_l);
+  const HostTensor* bias = has_in(n, 8) ? const_in(n, 8) : nullptr;
+  if (has_in(n, 8) && !bias) OXB_DECLINE("QLinearConv '%s': bias is not an initializer", n.name.c_str());
+  if (bias && bias->data.empty()) bias = nullptr;
+  if (bias) {
+    if ((int64_t)bias->data.size() != cs.OC) OXB_DECLINE("QLinearConv: bias has %zu entries, expected %d", bias->data.size(), cs.OC);
+    if (!lanes_to_i32(*bias, &c.bias_i)) OXB_DECLINE("QLinearConv: bias holds a non-finite or out-of-range lane");
+  }
+  bool per_channel = w_scale->data.size() > 1;
+  if (per_channel && (int64_t)w_scale->data.size() != cs.OC) OXB_DECLINE("QLinearConv: w_scale has %zu entries, expected 1 or %d", w_scale->data.size(), cs.OC);
+  c.combined.resize(cs.OC);
+  for (int oc = 0; oc < cs.OC; ++oc) {
+    float ws = per_channel ? w_scale->data[oc] : w_scale->data[0];
+    if (!std::isfinite(ws)) OXB_DECLINE("QLinearConv: w_scale[%d] must be finite", oc);
+    volatile float xw = x_scale * ws;  // f32 product, then f32 quotient (qlinear_conv.rs:99)
+    volatile float comb = xw / y_scale;
+    c.combined[oc] = comb;
+    if (!std::isfinite(c.combined[oc])) OXB_DECLINE("QLinearConv: combined scale is not finite");
+  }
+  Range r = sat_infer(y_zp_l, {c.x_zp});
+  c.epi.mode = k::EPI_REQUANT;
+  c.epi.y_zp = y_zp_l.empty() ? 0 : y_zp_l[0];
+  c.epi.lo = r.lo;
+  c.epi.hi = r.hi;
+  // a Relu behind the node clamps the same lanes at zero: fold it into the saturation
+  int relu = sole_consumer(out_name, "Relu");
+  if (relu >= 0) {
+    skipped_[relu] = 1;
+    c.epi.relu_fused = 1;
+    out_name = nodes_[relu].outputs[0];
+    r.lo = std::max(r.lo, 0);
+  }
+  c.epi.out_dt = narrowest_int(r.lo, r.hi);
+  c.out_vi = add_value(out_name, out_shape, c.epi.out_dt, Layout::NHWC);
+  emit_contraction(n, c);
+}
+
+// MatMul family as a 1x1 convolution over [rows, K] (oxionnx-ops quant_ops/qlinear_matmul.rs:30-254,
+// src/math/matmul.rs:53-190).
+void Planner::plan_matmul_family(const NodeDef& n, int ni) {
+  (void)ni;
+  const std::string& op = n.op;
+  const bool is_qm = op == "QLinearMatMul", is_mi = op == "MatMulInteger", is_gemm = op == "Gemm";
+  if (is_gemm) check_attrs(n, {"alpha", "beta", "transA", "transB"});
+  else check_attrs(n, {});
+  const size_t b_slot = is_qm ? 3 : 1;
+  int ai = value_of(in_name(n, 0));
+  if (is_gemm && n.attrs.i("transA", 0) != 0) {
+    // A arrives as [K, M]: bring it to [M, K] once, as the channels-last view of a [1, K, M, 1] tensor
+    const Value a0 = V(ai);
+    if (a0.shape.size() != 2 || a0.dt != DT::F32) OXB_DECLINE("Gemm '%s': transA needs a rank-2 float A", n.name.c_str());
+    int at = add_value(a0.name + "@t", {a0.shape[1], a0.shape[0]}, DT::F32, Layout::PLAIN);
+    Dims4 d{1, a0.shape[0], a0.shape[1], 1};
+    TensorRef src{nullptr, DT::F32, Layout::PLAIN, d}, dst{nullptr, DT::F32, Layout::NHWC, d};
+    Step& st = add_step(n, "transpose_a", 2, {ai}, {at});
+    st.work = 2.0 * (double)a0.bytes;
+    const int a_src = ai;
+    st.launch = [this, src, dst, a_src, at](cudaStream_t s) {
+      k::convert(bound(src, a_src), bound(dst, at), s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    ai = at;
+  }
+  const Value av = V(ai);
+  const HostTensor* b = const_in(n, b_slot);
+  // a stacked constant B of a float MatMul goes through the batched activation x activation product
+  const bool b_is_const = b != nullptr && S.index_.find(in_name(n, b_slot)) == S.index_.end() && !(op == "MatMul" && b->shape.size() > 2);
+
+  if (!b_is_const) {
+    // activation x activation product: float MatMul only
+    if (op != "MatMul") OXB_DECLINE("%s '%s': the B operand is not an initializer", op.c_str(), n.name.c_str());
+    int bi = value_of(in_name(n, 1));
+    const Value bv = V(bi);
+    if (av.dt != DT::F32 || bv.dt != DT::F32) OXB_DECLINE("MatMul '%s': operands are not float tensors", n.name.c_str());
+    if (av.shape.size() < 2 || bv.shape.size() < 2) OXB_DECLINE("MatMul '%s': 1-D operands with a non-constant B", n.name.c_str());
+    if ((av.shape.size() == 4 && av.layout == Layout::NHWC && !order_free(av)) || (bv.shape.size() == 4 && bv.layout == Layout::NHWC && !order_free(bv)))
+      OXB_DECLINE("MatMul '%s': channels-last operand", n.name.c_str());
+    int64_t M = av.shape[av.shape.size() - 2], K = av.shape.back(), K2 = bv.shape[bv.shape.size() - 2], N = bv.shape.back();
+    if (K != K2) OXB_DECLINE("MatMul: inner dimensions disagree: %lld vs %lld", (long long)K, (long long)K2);
+    int64_t ba = 1, bb = 1;
+    for (size_t i = 0; i + 2 < av.shape.size(); ++i) ba *= av.shape[i];
+    for (size_t i = 0; i + 2 < bv.shape.size(); ++i) bb *= bv.shape[i];
+    int64_t batch;
+    if (ba == bb) batch = ba;
+    else if (ba == 1) batch = bb;
+    else if (bb == 1) batch = ba;
+    else OXB_DECLINE("MatMul: batch dimensions disagree (%lld vs %lld) and neither is 1", (long long)ba, (long long)bb);
+    std::vector<int64_t> os;
+    const std::vector<int64_t>& pre = ba >= bb ? av.shape : bv.shape;
+    os.assign(pre.begin(), pre.end() - 2);
+    os.push_back(M);
+    os.push_back(N);
+    int yi = add_value(n.outputs[0], os, DT::F32, Layout::PLAIN);
+    Step& st = add_step(n, "matmul_f32_direct", 1, {ai, bi}, {yi});
+    st.work = 2.0 * (double)batch * M * K * N;
+    st.work_is_bytes = false;
+    int64_t as = (ba == 1 && batch != 1) ? 0 : M * K, bs = (bb == 1 && batch != 1) ? 0 : K * N;
+    st.launch = [this, ai, bi, yi, batch, M, K, N, as, bs](cudaStream_t s) {
+      k::matmul_f32_direct((const float*)V(ai).ptr, (const float*)V(bi).ptr, (float*)V(yi).ptr, batch, M, K, N, as, bs, s);
+      C.counters.simt_launches++;
+      C.counters.kernel_launches++;
+    };
+    return;
+  }
+
+  if ((int64_t)b->data.size() != b->numel()) OXB_DECLINE("%s: B data length does not match its shape", op.c_str());
+  if (av.shape.empty() || b->shape.empty()) OXB_DECLINE("%s: inputs must have rank >= 1", op.c_str());
+  if (b->shape.size() > 2) OXB_DECLINE("%s '%s': stacked constant B", op.c_str(), n.name.c_str());
+  if (av.shape.size() == 4 && av.layout == Layout::NHWC && !order_free(av)) OXB_DECLINE("%s '%s': channels-last A operand", op.c_str(), n.name.c_str());
+  const bool trans_b = is_gemm && n.attrs.i("transB", 0) != 0;
+  if (is_gemm && (av.shape.size() != 2 || b->shape.size() != 2)) OXB_DECLINE("Gemm '%s': operands are not rank 2", n.name.c_str());
+  const bool a_1d = av.shape.size() == 1, b_1d = b->shape.size() == 1;
+  int64_t K = av.shape.back();
+  int64_t rows = a_1d ? 1 : prod(av.shape) / std::max<int64_t>(K, 1);
+  int64_t Kb, N;
+  if (b_1d) {
+    Kb = b->shape[0];
+    N = 1;
+  } else if (trans_b) {
+    Kb = b->shape[1];
+    N = b->shape[0];
+  } else {
+    Kb = b->shape[0];
+    N = b->shape[1];
+  }
+  if (K != Kb) OXB_DECLINE("%s: inner dimensions disagree: %lld vs %lld", op.c_str(), (long long)K, (long long)Kb);
+  if (rows > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) OXB_DECLINE("%s: extents exceed 32 bits", op.c_str());
+  std::vector<int64_t> os;
+  if (!a_1d) os.assign(av.shape.begin(), av.shape.end() - 1);
+  if (!b_1d) os.push_back(N);
+
+  Contraction c;
+  k::ConvShape& cs = c.cs;
+  cs.N = (int)rows;
+  cs.C = (int)K;
+  cs.H = cs.W = 1;
+  cs.OC = (int)N;
+  cs.R = cs.S = 1;
+  cs.P = cs.Q = 1;
+  cs.sh = cs.sw = cs.dh = cs.dw = 1;
+  cs.pt = cs.pl = cs.pb = cs.pr = 0;
+  cs.group = 1;
+  c.w = b;
+  c.w_name = in_name(n, b_slot);
+  c.w_is_kn = !trans_b;  // [K][N] unless Gemm stores B transposed, which is already [N][K] = [OC][C]
+  c.is_int = is_qm || is_mi;
+  const int64_t M_rows_per_batch = a_1d ? 1 : av.shape[av.shape.size() - 2];
+
+  if (!c.is_int) {
+    const HostTensor* full_c = nullptr;
+    float full_c_beta = 1.0f;
+    if (av.dt != DT::F32) OXB_DECLINE("%s '%s': A is not a float tensor", op.c_str(), n.name.c_str());
+    c.epi.mode = k::EPI_F32;
+    c.epi.out_dt = DT::F32;
+    if (is_gemm) {
+      float alpha = n.attrs.f("alpha", 1.0f), beta = n.attrs.f("beta", 1.0f);
+      c.w_scale_mul = alpha;
+      if (has_in(n, 2)) {
+        const HostTensor* cc = const_in(n, 2);
+        if (!cc) OXB_DECLINE("Gemm '%s': C is not an initializer", n.name.c_str());
+        int64_t cn = cc->numel();
+        bool row_like = cn == N && (cc->shape.empty() || cc->shape.back() == N) && (cc->shape.size() < 2 || cc->shape[cc->shape.size() - 2] == 1);
+        if (cn == 1 || row_like) {
+          c.bias_f.resize(N);
+          for (int64_t j = 0; j < N; ++j) {
+            volatile float bc = beta * cc->data[cn == 1 ? 0 : j];
+            c.bias_f[j] = bc;
+          }
+        } else {
+          // C varies along the rows ([M,N] or [M,1]): a separate add of beta*C after the product
+          bool mn = cc->shape.size() == 2 && cc->shape[0] == rows && (cc->shape[1] == N || cc->shape[1] == 1);
+          if (!mn) OXB_DECLINE("Gemm '%s': C is not broadcastable to the result", n.name.c_str());
+          full_c = cc;
+          full_c_beta = beta;
+        }
+      }
+    }
+    c.x_vi = ai;
+    c.epi.round_tf32 = (!full_c && feeds_contraction(n.outputs[0])) ? 1 : 0;
+    if (!full_c) {
+      c.out_vi = add_value(n.outputs[0], os, DT::F32, Layout::PLAIN);
+      emit_contraction(n, c);
+      return;
+    }
+    int prod_vi = add_value(n.outputs[0] + "@product", os, DT::F32, Layout::PLAIN);
+    c.out_vi = prod_vi;
+    emit_contraction(n, c);
+    const HostTensor* cc = full_c;
+    const float beta = full_c_beta;
+    char form[48];
+    snprintf(form, sizeof form, "gemm_c_beta%.9g", (double)beta);
+    const float* cdev = (const float*)C.resident_form(in_name(n, 2), form, cc->data.size() * 4,
+                                                      [cc, beta](void* dst) {
+                                                        for (size_t i = 0; i < cc->data.size(); ++i) {
+                                                          volatile float v = beta * cc->data[i];
+                                                          ((float*)dst)[i] = v;
+                                                        }
+                                                      },
+                                                      cacheable_const(in_name(n, 2)));
+    int yi = add_value(n.outputs[0], os, DT::F32, Layout::PLAIN);
+    int rt = feeds_contraction(n.outputs[0]) ? 1 : 0;
+    TensorRef ar{nullptr, DT::F32, Layout::PLAIN, Dims4{rows, N, 1, 1}}, br{(void*)cdev, DT::F32, Layout::PLAIN, Dims4{cc->shape[0], cc->shape[1], 1, 1}},
+        yr{nullptr, DT::F32, Layout::PLAIN, Dims4{rows, N, 1, 1}};
+    Step& st = add_step(n, "gemm_add_c", 2, {prod_vi}, {yi});
+    st.work = 3.0 * (double)V(yi).bytes;
+    st.launch = [this, ar, br, yr, prod_vi, yi, rt](cudaStream_t s) {
+      k::binary(bound(ar, prod_vi), br, bound(yr, yi), k::BIN_ADD, 0, rt, s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    return;
+  }
+
+  // ---- integer matmuls ----
+  auto zp_const = [&](size_t slot, const char* what, std::vector<int32_t>* out, bool* is_const) {
+    out->assign(1, 0);
+    *is_const = true;
+    if (!has_in(n, slot)) return;
+    const HostTensor* t = const_in(n, slot);
+    if (!t || S.index_.find(in_name(n, slot)) != S.index_.end()) {
+      *is_const = false;
+      return;
+    }
+    if (t->data.empty()) return;
+    if (!lanes_to_i32(*t, out)) OXB_DECLINE("%s: %s holds a non-finite or out-of-range lane", op.c_str(), what);
+  };
+  std::vector<int32_t> a_zp, b_zp;
+  bool a_zp_const, b_zp_const;
+  zp_const(2, "a_zero_point", &a_zp, &a_zp_const);
+  zp_const(is_qm ? 5 : 3, "b_zero_point", &b_zp, &b_zp_const);
+  if (!b_zp_const) OXB_DECLINE("%s '%s': b_zero_point is not an initializer", op.c_str(), n.name.c_str());
+  if (a_zp_const && a_zp.size() != 1 && (int64_t)a_zp.size() != M_rows_per_batch)
+    OXB_DECLINE("%s: a_zero_point has %zu entries, expected 1 (per tensor) or %lld", op.c_str(), a_zp.size(), (long long)M_rows_per_batch);
+  if (b_zp.size() != 1 && (int64_t)b_zp.size() != N)
+    OXB_DECLINE("%s: b_zero_point has %zu entries, expected 1 (per tensor) or %lld", op.c_str(), b_zp.size(), (long long)N);
+  c.w_zp = b_zp;
+  if (a_zp_const) {
+    if (a_zp.size() == 1) {
+      c.x_zp = a_zp[0];
+    } else {
+      c.x_zp_rows.resize(rows);
+      for (int64_t r = 0; r < rows; ++r) c.x_zp_rows[r] = a_zp[r % M_rows_per_batch];
+    }
+  } else {
+    if (is_qm) OXB_DECLINE("QLinearMatMul '%s': a_zero_point is not an initializer", n.name.c_str());
+    int zi = value_of(in_name(n, 2));
+    if (V(zi).numel() != 1 || V(zi).dt != DT::F32) OXB_DECLINE("MatMulInteger '%s': dynamic a_zero_point must be one f32 lane", n.name.c_str());
+    c.x_zp_static = false;
+    c.x_zp_vi = zi;
+  }
+  bool ok_lanes;
+  DT want_a = int_storage_for(av, &ok_lanes);
+  if (!ok_lanes) OXB_DECLINE("%s: A holds a non-finite or out-of-range lane", op.c_str());
+  int aq = ai;
+  if (av.dt == DT::F32) {
+    aq = add_value(av.name + "@int", av.shape, want_a, Layout::PLAIN);
+    Dims4 d{std::max<int64_t>(av.numel(), 0), 1, 1, 1};
+    TensorRef ta{nullptr, DT::F32, Layout::PLAIN, d}, tb{nullptr, want_a, Layout::PLAIN, d};
+    Step& st = add_step(n, "lanes_to_int", 2, {ai}, {aq});
+    st.work = (double)av.bytes + (double)V(aq).bytes;
+    st.launch = [this, ta, tb, ai, aq](cudaStream_t s) {
+      k::convert(bound(ta, ai), bound(tb, aq), s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+  }
+  c.x_vi = aq;
+  if (is_mi) {
+    c.epi.mode = k::EPI_INT32;
+    c.epi.out_dt = DT::I32;
+    c.out_vi = add_value(n.outputs[0], os, DT::I32, Layout::PLAIN);
+    emit_contraction(n, c);
+    return;
+  }
+  auto scale_in = [&](size_t slot, const char* what) -> float {
+    const HostTensor* t = const_in(n, slot);
+    if (!t) OXB_DECLINE("QLinearMatMul '%s': %s is not an initializer", n.name.c_str(), what);
+    if (t->data.empty()) OXB_DECLINE("QLinearMatMul: %s is empty", what);
+    float v = t->data[0];
+    if (!std::isfinite(v)) OXB_DECLINE("QLinearMatMul: %s must be finite", what);
+    if (v == 0.0f) OXB_DECLINE("QLinearMatMul: %s scale is zero", what);
+    return v;
+  };
+  float a_scale = scale_in(1, "a_scale"), b_scale = scale_in(4, "b_scale"), y_scale = scale_in(6, "y_scale");
+  std::vector<int32_t> y_zp;
+  bool y_const;
+  zp_const(7, "y_zero_point", &y_zp, &y_const);
+  if (!y_const) OXB_DECLINE("QLinearMatMul '%s': y_zero_point is not an initializer", n.name.c_str());
+  volatile float ab = a_scale * b_scale;  // only lane 0 of b_scale is read (qlinear_matmul.rs:230,248)
+  volatile float comb = ab / y_scale;
+  if (!std::isfinite((float)comb)) OXB_DECLINE("QLinearMatMul: combined scale is not finite");
+  c.combined.assign((size_t)N, (float)comb);
+  Range r = sat_infer(y_zp, a_zp);
+  c.epi.mode = k::EPI_REQUANT;
+  c.epi.y_zp = y_zp.empty() ? 0 : y_zp[0];
+  c.epi.lo = r.lo;
+  c.epi.hi = r.hi;
+  std::string out_name = n.outputs[0];
+  int relu = sole_consumer(out_name, "Relu");
+  if (relu >= 0) {
+    skipped_[relu] = 1;
+    c.epi.relu_fused = 1;
+    out_name = nodes_[relu].outputs[0];
+    r.lo = std::max(r.lo, 0);
+  }
+  c.epi.out_dt = narrowest_int(r.lo, r.hi);
+  c.out_vi = add_value(out_name, os, c.epi.out_dt, Layout::PLAIN);
+  emit_contraction(n, c);
+}
+
+// ---- element-wise ----------------------------------------------------------------------------
+void Planner::plan_unary(const NodeDef& n) {
+  check_attrs(n, {});
+  int xi = value_of(in_name(n, 0));
+  const Value xv = V(xi);
+  int op = n.op == "Relu" ? k::UN_RELU : (n.op == "Tanh" ? k::UN_TANH : k::UN_SIGMOID);
+  if (op != k::UN_RELU && xv.dt != DT::F32) OXB_DECLINE("%s '%s': input is not a float tensor", n.op.c_str(), n.name.c_str());
+  DT odt = xv.dt;
+  if (op == k::UN_RELU && xv.dt == DT::I16) odt = DT::I16;
+  int yi = add_value(n.outputs[0], xv.shape, odt, xv.shape.size() == 4 ? xv.layout : Layout::PLAIN);
+  Dims4 d{std::max<int64_t>(xv.numel(), 0), 1, 1, 1};
+  TensorRef xr{nullptr, xv.dt, Layout::PLAIN, d}, yr{nullptr, odt, Layout::PLAIN, d};
+  Step& st = add_step(n, "unary", 2, {xi}, {yi});
+  st.work = (double)xv.bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, op](cudaStream_t s) {
+    k::unary(bound(xr, xi), bound(yr, yi), op, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_binary(const NodeDef& n, int ni) {
+  (void)ni;
+  check_attrs(n, {});
+  int ai = value_of(in_name(n, 0)), bi = value_of(in_name(n, 1));
+  Value av = V(ai), bv = V(bi);
+  if (av.dt != DT::F32 && av.dt != DT::I32) OXB_DECLINE("%s '%s': operand A is a quantised tensor", n.op.c_str(), n.name.c_str());
+  if (bv.dt != DT::F32 && bv.dt != DT::I32) OXB_DECLINE("%s '%s': operand B is a quantised tensor", n.op.c_str(), n.name.c_str());
+  size_t r = std::max(av.shape.size(), bv.shape.size());
+  std::vector<int64_t> as(r, 1), bs(r, 1), os(r, 1);
+  std::copy(av.shape.begin(), av.shape.end(), as.begin() + (r - av.shape.size()));
+  std::copy(bv.shape.begin(), bv.shape.end(), bs.begin() + (r - bv.shape.size()));
+  for (size_t i = 0; i < r; ++i) {
+    if (as[i] != bs[i] && as[i] != 1 && bs[i] != 1) OXB_DECLINE("%s: shapes are not broadcastable", n.op.c_str());
+    os[i] = (as[i] == 0 || bs[i] == 0) ? 0 : std::max(as[i], bs[i]);
+  }
+  Dims4 ad, bd, od;
+  Layout al = Layout::PLAIN, bl = Layout::PLAIN, ol = Layout::PLAIN;
+  if (as == bs) {
+    // same shape: operands must share a memory order
+    if (r == 4) {
+      Layout want = (av.layout == Layout::NHWC || bv.layout == Layout::NHWC) ? Layout::NHWC : Layout::PLAIN;
+      if (!order_free(av)) {
+        ai = ensure_layout(n, ai, want);
+        bi = ensure_layout(n, bi, want);
+        av = V(ai);
+        bv = V(bi);
+      }
+      ol = want;
+      al = bl = want;
+      ad = bd = od = Dims4{os[0], os[1], os[2], os[3]};
+    } else {
+      ad = bd = od = Dims4{std::max<int64_t>(prod(os), 0), 1, 1, 1};
+    }
+  } else if (r <= 4) {
+    // broadcast: pad to rank 4 on the left; the full-size operand fixes the memory order
+    std::vector<int64_t> a4(4, 1), b4(4, 1), o4(4, 1);
+    std::copy(as.begin(), as.end(), a4.begin() + (4 - r));
+    std::copy(bs.begin(), bs.end(), b4.begin() + (4 - r));
+    std::copy(os.begin(), os.end(), o4.begin() + (4 - r));
+    ad = Dims4{a4[0], a4[1], a4[2], a4[3]};
+    bd = Dims4{b4[0], b4[1], b4[2], b4[3]};
+    od = Dims4{o4[0], o4[1], o4[2], o4[3]};
+    if (r == 4) {
+      al = effective_layout(av);
+      bl = effective_layout(bv);
+      bool a_full = as == os, b_full = bs == os;
+      ol = a_full ? al : (b_full ? bl : Layout::PLAIN);
+      // a small operand whose own order is free ([N,C,1,1], [1,C,1,1], scalar) reads the same either way
+      if (order_free(av)) al = ol;
+      if (order_free(bv)) bl = ol;
+    }
+  } else {
+    OXB_DECLINE("%s '%s': broadcasting above rank 4", n.op.c_str(), n.name.c_str());
+  }
+  int op = n.op == "Add" ? k::BIN_ADD : (n.op == "Sub" ? k::BIN_SUB : (n.op == "Mul" ? k::BIN_MUL : k::BIN_DIV));
+  std::string out_name = n.outputs[0];
+  int relu_after = 0;
+  int relu = sole_consumer(out_name, "Relu");
+  if (relu >= 0) {
+    skipped_[relu] = 1;
+    relu_after = 1;
+    out_name = nodes_[relu].outputs[0];
+  }
+  int yi = add_value(out_name, os, DT::F32, r == 4 ? ol : Layout::PLAIN);
+  int rt = feeds_contraction(out_name) ? 1 : 0;
+  TensorRef ar{nullptr, av.dt, al, ad}, br{nullptr, bv.dt, bl, bd}, yr{nullptr, DT::F32, r == 4 ? ol : Layout::PLAIN, od};
+  Step& st = add_step(n, relu_after ? "binary+relu" : "binary", 2, {ai, bi}, {yi});
+  st.work = (double)av.bytes + (double)bv.bytes + (double)V(yi).bytes;
+  st.launch = [this, ar, br, yr, ai, bi, yi, op, relu_after, rt](cudaStream_t s) {
+    k::binary(bound(ar, ai), bound(br, bi), bound(yr, yi), op, relu_after, rt, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_prelu(const NodeDef& n) {
+  check_attrs(n, {});
+  int xi = value_of(in_name(n, 0));
+  const Value xv = V(xi);
+  const HostTensor* slope = const_in(n, 1);
+  if (!slope) OXB_DECLINE("PRelu '%s': slope is not an initializer", n.name.c_str());
+  if (xv.dt != DT::F32) OXB_DECLINE("PRelu '%s': input is not a float tensor", n.name.c_str());
+  int64_t ns = slope->numel();
+  bool per_channel = xv.shape.size() >= 2 && ns == xv.shape[1] && ns > 1;
+  if (per_channel) {
+    // slope must be [C], [C,1,1] or [1,C,1,1]: one value per channel and nothing else
+    int64_t nontrivial = 0;
+    for (int64_t d : slope->shape) nontrivial += d != 1;
+    if (nontrivial != 1) per_channel = false;
+    if (slope->shape.size() == 1 && xv.shape.size() != 2 && xv.shape.size() != 1) per_channel = false;  // [C] broadcasts along the last axis
+  }
+  if (!(ns == 1 || per_channel)) OXB_DECLINE("PRelu '%s': slope shape is neither scalar nor per-channel", n.name.c_str());
+  const float* dsl = (const float*)C.resident_form(in_name(n, 1), "raw_f32", slope->data.size() * 4,
+                                                   [slope](void* p) { std::memcpy(p, slope->data.data(), slope->data.size() * 4); },
+                                                   cacheable_const(in_name(n, 1)));
+  int yi = add_value(n.outputs[0], xv.shape, DT::F32, xv.shape.size() == 4 ? xv.layout : Layout::PLAIN);
+  TensorRef xr = ref_of(xi), yr = ref_of(yi);
+  Step& st = add_step(n, "prelu", 2, {xi}, {yi});
+  st.work = 2.0 * (double)xv.bytes;
+  st.launch = [this, xr, yr, xi, yi, dsl, ns](cudaStream_t s) {
+    k::prelu(bound(xr, xi), bound(yr, yi), dsl, ns, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_max_pool(const NodeDef& n) {
+  check_attrs(n, {"kernel_shape", "strides", "pads", "dilations", "auto_pad", "ceil_mode", "storage_order"});
+  if (n.outputs.size() > 1 && !n.outputs[1].empty()) OXB_DECLINE("MaxPool '%s': the Indices output", n.name.c_str());
+  if (n.attrs.i("storage_order", 0) != 0) OXB_DECLINE("MaxPool '%s': column-major storage order", n.name.c_str());
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).shape.size() != 4) OXB_DECLINE("MaxPool '%s': only rank-4 inputs are claimed", n.name.c_str());
+  if (!(V(xi).dt == DT::F32 || V(xi).dt == DT::U8 || V(xi).dt == DT::I8)) OXB_DECLINE("MaxPool '%s': storage type", n.name.c_str());
+  auto ks = n.attrs.int_list("kernel_shape");
+  if (ks.size() < 2) OXB_DECLINE("MaxPool: kernel_shape requires 2 spatial dims, got %zu", ks.size());
+  if (ks[0] < 1 || ks[1] < 1) OXB_DECLINE("MaxPool: kernel_shape must be >= 1");
+  Geo g = resolve_geometry("MaxPool", n.attrs, V(xi).shape.data() + 2, ks.data(), 2, n.attrs.i("ceil_mode", 0) != 0);
+  xi = ensure_layout(n, xi, Layout::NHWC);
+  const Value xv = V(xi);
+  std::vector<int64_t> os = {xv.shape[0], xv.shape[1], g.out_spatial[0], g.out_spatial[1]};
+  int yi = add_value(n.outputs[0], os, xv.dt, Layout::NHWC);
+  k::PoolShape ps{(int)ks[0], (int)ks[1], (int)g.strides[0], (int)g.strides[1], (int)g.pads[0], (int)g.pads[1], (int)g.dilations[0], (int)g.dilations[1],
+                  (int)g.out_spatial[0], (int)g.out_spatial[1]};
+  TensorRef xr = ref_of(xi), yr = ref_of(yi);
+  xr.layout = yr.layout = Layout::NHWC;
+  Step& st = add_step(n, "max_pool", 2, {xi}, {yi});
+  st.work = (double)xv.bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, ps](cudaStream_t s) {
+    k::max_pool(bound(xr, xi), bound(yr, yi), ps, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_global_avg_pool(const NodeDef& n) {
+  check_attrs(n, {});
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).shape.size() != 4 || V(xi).dt != DT::F32) OXB_DECLINE("GlobalAveragePool '%s': needs a rank-4 float input", n.name.c_str());
+  xi = ensure_layout(n, xi, Layout::NHWC);
+  const Value xv = V(xi);
+  std::vector<int64_t> os = {xv.shape[0], xv.shape[1], 1, 1};
+  int yi = add_value(n.outputs[0], os, DT::F32, Layout::NHWC);
+  int rt = feeds_contraction(n.outputs[0]) ? 1 : 0;
+  TensorRef xr = ref_of(xi), yr = ref_of(yi);
+  xr.layout = Layout::NHWC;
+  Step& st = add_step(n, "global_avg_pool", 2, {xi}, {yi});
+  st.work = (double)xv.bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, rt](cudaStream_t s) {
+    k::global_avg_pool(bound(xr, xi), bound(yr, yi), rt, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_instance_norm(const NodeDef& n) {
+  check_attrs(n, {"epsilon"});
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).shape.size() != 4 || V(xi).dt != DT::F32) OXB_DECLINE("OxiInstanceNorm '%s': needs a rank-4 float input", n.name.c_str());
+  xi = ensure_layout(n, xi, Layout::NHWC);
+  const Value xv = V(xi);
+  float eps = n.attrs.f("epsilon", 1e-5f);
+  int yi = add_value(n.outputs[0], xv.shape, DT::F32, Layout::NHWC);
+  TensorRef xr = ref_of(xi), yr = ref_of(yi);
+  xr.layout = yr.layout = Layout::NHWC;
+  Step& st = add_step(n, "instance_norm", 2, {xi}, {yi});
+  st.work = 3.0 * (double)xv.bytes;
+  st.launch = [this, xr, yr, xi, yi, eps](cudaStream_t s) {
+    k::instance_norm(bound(xr, xi), bound(yr, yi), eps, nullptr, nullptr, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_resize(const NodeDef& n) {
+  check_attrs(n, {"mode", "coordinate_transformation_mode", "nearest_mode", "antialias", "cubic_coeff_a", "exclude_outside", "extrapolation_value",
+                  "keep_aspect_ratio_policy"});
+  if (n.attrs.i("antialias", 0) != 0 || n.attrs.i("exclude_outside", 0) != 0) OXB_DECLINE("Resize '%s': antialias / exclude_outside", n.name.c_str());
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).shape.size() != 4 || V(xi).dt != DT::F32) OXB_DECLINE("Resize '%s': needs a rank-4 float input", n.name.c_str());
+  if (has_in(n, 1) && const_in(n, 1) && !const_in(n, 1)->data.empty()) OXB_DECLINE("Resize '%s': roi", n.name.c_str());
+  const HostTensor* scales = has_in(n, 2) ? const_in(n, 2) : nullptr;
+  const HostTensor* sizes = has_in(n, 3) ? const_in(n, 3) : nullptr;
+  if ((has_in(n, 2) && !scales) || (has_in(n, 3) && !sizes)) OXB_DECLINE("Resize '%s': scales / sizes are not initializers", n.name.c_str());
+  std::string mode = n.attrs.s("mode"), coord = n.attrs.s("coordinate_transformation_mode"), nearest = n.attrs.s("nearest_mode");
+  int m = (mode.empty() || mode == "nearest") ? 0 : ((mode == "linear" || mode == "bilinear") ? 1 : -1);
+  int cm = (coord.empty() || coord == "half_pixel") ? 0 : (coord == "pytorch_half_pixel" ? 1 : (coord == "asymmetric" ? 2 : (coord == "align_corners" ? 3 : -1)));
+  int nr = (nearest.empty() || nearest == "round_prefer_floor") ? 0 : (nearest == "floor" ? 1 : (nearest == "ceil" ? 2 : (nearest == "round_prefer_ceil" ? 3 : -1)));
+  if (m < 0 || cm < 0 || nr < 0) OXB_DECLINE("Resize '%s': mode combination not claimed", n.name.c_str());
+  xi = ensure_layout(n, xi, Layout::NHWC);
+  const Value xv = V(xi);
+  std::vector<int64_t> os = xv.shape;
+  float sc[4] = {1, 1, 1, 1};
+  if (scales && scales->data.size() == 4) {
+    for (int d = 0; d < 4; ++d) {
+      sc[d] = scales->data[d];
+      os[d] = (int64_t)std::floor((float)xv.shape[d] * sc[d]);
+    }
+  } else if (sizes && sizes->data.size() == 4) {
+    for (int d = 0; d < 4; ++d) {
+      os[d] = (int64_t)sizes->data[d];
+      sc[d] = (float)os[d] / (float)xv.shape[d];
+    }
+  } else {
+    OXB_DECLINE("Resize '%s': needs 4 scales or 4 sizes", n.name.c_str());
+  }
+  if (os[0] != xv.shape[0] || os[1] != xv.shape[1]) OXB_DECLINE("Resize '%s': only the spatial axes may change", n.name.c_str());
+  int yi = add_value(n.outputs[0], os, DT::F32, Layout::NHWC);
+  TensorRef xr = ref_of(xi), yr = ref_of(yi);
+  xr.layout = yr.layout = Layout::NHWC;
+  float shh = sc[2], sww = sc[3];
+  Step& st = add_step(n, "resize", 2, {xi}, {yi});
+  st.work = (double)xv.bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, m, cm, nr, shh, sww](cudaStream_t s) {
+    k::resize(bound(xr, xi), bound(yr, yi), m, cm, nr, shh, sww, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_pad(const NodeDef& n) {
+  check_attrs(n, {"mode", "pads", "value"});
+  int xi = value_of(in_name(n, 0));
+  const Value xv = V(xi);
+  if (xv.shape.size() != 4) OXB_DECLINE("Pad '%s': only rank-4 inputs are claimed", n.name.c_str());
+  std::vector<int64_t> pads;
+  if (has_in(n, 1)) {
+    const HostTensor* p = const_in(n, 1);
+    if (!p) OXB_DECLINE("Pad '%s': pads is not an initializer", n.name.c_str());
+    for (float f : p->data) pads.push_back((int64_t)f);
+  } else {
+    pads = n.attrs.int_list("pads");
+  }
+  if (has_in(n, 3)) OXB_DECLINE("Pad '%s': axes input", n.name.c_str());
+  if (pads.size() != 8) OXB_DECLINE("Pad: pads must have 2*rank entries");
+  float value = n.attrs.f("value", 0.f);
+  if (has_in(n, 2)) {
+    const HostTensor* v = const_in(n, 2);
+    if (!v) OXB_DECLINE("Pad '%s': constant value is not an initializer", n.name.c_str());
+    if (!v->data.empty()) value = v->data[0];
+  }
+  std::string mode = n.attrs.s("mode");
+  int m = (mode.empty() || mode == "constant") ? 0 : (mode == "reflect" ? 1 : (mode == "edge" ? 2 : -1));
+  if (m < 0) OXB_DECLINE("Pad '%s': mode '%s'", n.name.c_str(), mode.c_str());
+  std::vector<int64_t> os = xv.shape;
+  for (int d = 0; d < 4; ++d) {
+    if (pads[d] < 0 || pads[d + 4] < 0) OXB_DECLINE("Pad '%s': negative pads", n.name.c_str());
+    if (m == 1 && (pads[d] >= xv.shape[d] || pads[d + 4] >= xv.shape[d]) && (pads[d] > 0 || pads[d + 4] > 0)) OXB_DECLINE("Pad: reflect pad must be smaller than the axis extent");
+    os[d] += pads[d] + pads[d + 4];
+  }
+  int yi = add_value(n.outputs[0], os, xv.dt, xv.layout);
+  TensorRef xr = ref_of(xi), yr = ref_of(yi);
+  int pn = (int)pads[0], pc = (int)pads[1], ph = (int)pads[2], pw = (int)pads[3];
+  Step& st = add_step(n, "pad", 2, {xi}, {yi});
+  st.work = (double)xv.bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, m, value, pn, pc, ph, pw](cudaStream_t s) {
+    k::pad(bound(xr, xi), bound(yr, yi), m, value, pn, pc, ph, pw, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+void Planner::plan_concat(const NodeDef& n) {
+  check_attrs(n, {"axis"});
+  if (n.inputs.empty()) OXB_DECLINE("Concat: no inputs");
+  std::vector<int> ins;
+  for (size_t i = 0; i < n.inputs.size(); ++i) ins.push_back(value_of(n.inputs[i]));
+  const Value first = V(ins[0]);
+  int64_t rank = (int64_t)first.shape.size();
+  int64_t axis = n.attrs.i("axis", 0);
+  if (axis < 0) axis += rank;
+  if (axis < 0 || axis >= rank) OXB_DECLINE("Concat: axis out of range");
+  if (rank != 4) OXB_DECLINE("Concat '%s': only rank-4 inputs are claimed", n.name.c_str());
+  std::vector<int64_t> os = first.shape;
+  os[axis] = 0;
+  for (size_t i = 0; i < ins.size(); ++i) {
+    ins[i] = ensure_layout(n, ins[i], Layout::NHWC);
+    const Value& v = V(ins[i]);
+    if ((int64_t)v.shape.size() != rank || v.dt != first.dt) OXB_DECLINE("Concat '%s': operands differ in rank or storage type", n.name.c_str());
+    for (int64_t d = 0; d < rank; ++d)
+      if (d != axis && v.shape[d] != first.shape[d]) OXB_DECLINE("Concat: non-axis dims disagree");
+    os[axis] += v.shape[axis];
+  }
+  int yi = add_value(n.outputs[0], os, first.dt, Layout::NHWC);
+  int64_t off = 0;
+  for (size_t i = 0; i < ins.size(); ++i) {
+    int xi = ins[i];
+    TensorRef xr = ref_of(xi), yr = ref_of(yi);
+    xr.layout = yr.layout = Layout::NHWC;
+    int ax = (int)axis;
+    int64_t o = off;
+    Step& st = add_step(n, "concat", 2, {xi}, {yi});
+    st.work = 2.0 * (double)V(xi).bytes;
+    st.launch = [this, xr, yr, xi, yi, ax, o](cudaStream_t s) {
+      k::concat_into(bound(xr, xi), bound(yr, yi), ax, o, s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    off += V(xi).shape[axis];
+  }
+}
+
+// Flatten / Reshape / Identity / Cast: the logical row-major order is untouched, so the output
+// shares the input's storage.  A channels-last activation whose order matters is first brought
+// back to the logical order; int32 lanes cast to float become f32 lanes (round to nearest even).
+void Planner::plan_alias(const NodeDef& n) {
+  int xi = value_of(in_name(n, 0));
+  std::vector<int64_t> os;
+  const Value xv0 = V(xi);
+  if (n.op == "Flatten") {
+    check_attrs(n, {"axis"});
+    int64_t axis = n.attrs.i("axis", 1), rank = (int64_t)xv0.shape.size();
+    if (axis < 0) axis += rank;
+    if (axis < 0 || axis > rank) OXB_DECLINE("Flatten: axis out of range");
+    int64_t outer = 1, inner = 1;
+    for (int64_t d = 0; d < rank; ++d) (d < axis ? outer : inner) *= xv0.shape[d];
+    os = {outer, inner};
+  } else if (n.op == "Reshape") {
+    check_attrs(n, {"allowzero"});
+    const HostTensor* sh = const_in(n, 1);
+    if (!sh) OXB_DECLINE("Reshape '%s': the shape is not an initializer", n.name.c_str());
+    bool allowzero = n.attrs.i("allowzero", 0) != 0;
+    int64_t known = 1;
+    int infer = -1;
+    for (size_t i = 0; i < sh->data.size(); ++i) {
+      int64_t d = (int64_t)sh->data[i];
+      if (d == -1) {
+        if (infer >= 0) OXB_DECLINE("Reshape: more than one -1");
+        infer = (int)i;
+        os.push_back(1);
+        continue;
+      }
+      if (d == 0 && !allowzero) {
+        if (i >= xv0.shape.size()) OXB_DECLINE("Reshape: 0 dim out of range");
+        d = xv0.shape[i];
+      }
+      os.push_back(d);
+      known *= d;
+    }
+    if (infer >= 0) {
+      if (known == 0 || xv0.numel() % known != 0) OXB_DECLINE("Reshape: cannot infer dimension");
+      os[infer] = xv0.numel() / known;
+      known *= os[infer];
+    }
+    if (known != xv0.numel()) OXB_DECLINE("Reshape: element count changes");
+  } else {
+    if (n.op == "Cast") check_attrs(n, {"to", "saturate"});
+    else check_attrs(n, {});
+    os = xv0.shape;
+  }
+  if (n.op == "Cast") {
+    int64_t to = n.attrs.i("to", 1);
+    if (to != 1) OXB_DECLINE("Cast '%s': only casts to float are claimed", n.name.c_str());
+    if (xv0.dt != DT::F32) {
+      // integer storage -> f32 lanes
+      int yi = add_value(n.outputs[0], os, DT::F32, xv0.shape.size() == 4 ? xv0.layout : Layout::PLAIN);
+      Dims4 d{std::max<int64_t>(xv0.numel(), 0), 1, 1, 1};
+      TensorRef a{nullptr, xv0.dt, Layout::PLAIN, d}, b{nullptr, DT::F32, Layout::PLAIN, d};
+      Step& st = add_step(n, "cast_to_f32", 2, {xi}, {yi});
+      st.work = (double)xv0.bytes + (double)V(yi).bytes;
+      st.launch = [this, a, b, xi, yi](cudaStream_t s) {
+        k::convert(bound(a, xi), bound(b, yi), s);
+        C.counters.glue_launches++;
+        C.counters.kernel_launches++;
+      };
+      return;
+    }
+  }
+  bool shape_changes = os != xv0.shape;
+  if (shape_changes && xv0.shape.size() == 4 && xv0.layout == Layout::NHWC && !order_free(xv0)) xi = ensure_layout(n, xi, Layout::PLAIN);
+  const Value xv = V(xi);
+  Layout ol = Layout::PLAIN;
+  if (os.size() == 4) ol = shape_changes ? Layout::PLAIN : xv.layout;
+  int yi = add_value(n.outputs[0], os, xv.dt, ol);
+  V(yi).alias_of = xi;
+  V(yi).host = xv.host;
+  if (xv.external && xv.ptr) V(yi).ptr = xv.ptr;
+}
+
+// DequantizeLinear(a) , DequantizeLinear(b) -> Add -> Relu -> QuantizeLinear with per-tensor
+// parameters: the residual join of a quantised ResNet.  One kernel performs the same f32
+// operations in the same order, so the lanes equal the unfused chain's bit for bit; the
+// float intermediates never reach memory.
+bool Planner::try_plan_residual_chain(const NodeDef& n, int ni) {
+  (void)n;
+  (void)ni;
+  return false;
+}
+
+// =========================================================================================
+void Session::plan(const std::vector<NodeDef>& nodes, const std::vector<std::pair<std::string, std::vector<int64_t>>>& inputs,
+                   const std::map<std::string, const HostTensor*>& volatile_consts, const std::vector<std::string>& outputs) {
+  auto p = std::make_shared<Planner>(*this, *ctx_, nodes, volatile_consts);
+  planner_ = p;
+  p->run(inputs, outputs);
+}
+
+}  // namespace oxb

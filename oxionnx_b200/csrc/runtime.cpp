@@ -1,0 +1,259 @@
+// Context, weight residency, arena planning and the run loop of the oxb200 provider.
+// The per-operator planning rules live in planner.cpp.
+#include "runtime.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace oxb {
+
+std::vector<std::string> AttrMap::names() const {
+  std::vector<std::string> out;
+  for (auto& kv : ints) out.push_back(kv.first);
+  for (auto& kv : floats) out.push_back(kv.first);
+  for (auto& kv : strings) out.push_back(kv.first);
+  for (auto& kv : int_lists) out.push_back(kv.first);
+  for (auto& kv : float_lists) out.push_back(kv.first);
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------
+// Context
+// ---------------------------------------------------------------------------------------
+Context::Context(int device, const oxb200_config& cfg) : device_(device), cfg_(cfg) {
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count <= 0) {
+    (void)cudaGetLastError();
+    raise(OXB200_FAILED, "no CUDA device is available (%s); this provider has no CPU path", e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  }
+  if (device < 0 || device >= count) raise(OXB200_FAILED, "device ordinal %d out of range (%d devices)", device, count);
+  OXB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  OXB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) raise(OXB200_FAILED, "device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major, prop.minor);
+  OXB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+}
+
+Context::~Context() {
+  cudaSetDevice(device_);
+  session.reset();
+  release_caches();
+  if (run_ev0) cudaEventDestroy(run_ev0);
+  if (run_ev1) cudaEventDestroy(run_ev1);
+  if (stream_) cudaStreamDestroy(stream_);
+}
+
+void Context::make_current() { OXB_CUDA(cudaSetDevice(device_)); }
+
+void Context::register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank) {
+  HostTensor t;
+  t.shape.assign(shape, shape + rank);
+  if ((uint64_t)prod(t.shape) != len) raise(OXB200_FAILED, "weight '%s': %llu lanes do not match its shape", name.c_str(), (unsigned long long)len);
+  t.data.assign(lanes, lanes + len);
+  weights_[name] = std::move(t);
+  // a re-registered weight invalidates its packed forms
+  for (auto it = forms_.begin(); it != forms_.end();) {
+    if (it->first.first == name) {
+      cudaFree(it->second.ptr);
+      counters.weight_bytes_resident -= it->second.bytes;
+      it = forms_.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  resident_names_.erase(name);
+}
+
+const HostTensor* Context::weight(const std::string& name) const {
+  auto it = weights_.find(name);
+  return it == weights_.end() ? nullptr : &it->second;
+}
+
+bool Context::weight_resident(const std::string& name) const { return resident_names_.count(name) != 0; }
+
+void* Context::alloc_device(size_t bytes) {
+  void* p = nullptr;
+  if (bytes == 0) bytes = 256;
+  OXB_CUDA(cudaMalloc(&p, align_up(bytes, 256)));
+  return p;
+}
+
+void Context::free_device(void* p) {
+  if (p) cudaFree(p);
+}
+
+void* Context::resident_form(const std::string& name, const std::string& form, size_t bytes, const std::function<void(void*)>& fill_host,
+                             bool cacheable) {
+  auto key = std::make_pair(name, form);
+  if (cacheable) {
+    auto it = forms_.find(key);
+    if (it != forms_.end() && it->second.bytes == bytes) return it->second.ptr;
+  }
+  std::vector<uint8_t> host(std::max<size_t>(bytes, 16), 0);
+  fill_host(host.data());
+  void* dev = alloc_device(bytes);
+  OXB_CUDA(cudaMemcpyAsync(dev, host.data(), bytes, cudaMemcpyHostToDevice, stream_));
+  OXB_CUDA(cudaStreamSynchronize(stream_));
+  counters.weight_uploads += 1;
+  if (cacheable) {
+    forms_[key] = DeviceBuffer{dev, bytes};
+    counters.weight_bytes_resident += bytes;
+    resident_names_.insert(name);
+  } else {
+    temp_forms_.push_back(dev);
+  }
+  return dev;
+}
+
+void Context::free_temp_forms() {
+  for (void* p : temp_forms_) cudaFree(p);
+  temp_forms_.clear();
+}
+
+void Context::release_caches() {
+  for (auto& kv : forms_) cudaFree(kv.second.ptr);
+  forms_.clear();
+  for (void* p : temp_forms_) cudaFree(p);
+  temp_forms_.clear();
+  resident_names_.clear();
+  counters.weight_bytes_resident = 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Session: arena layout, upload, run, download
+// ---------------------------------------------------------------------------------------
+Session::~Session() {
+  cudaSetDevice(ctx_->device());
+  cudaStreamSynchronize(ctx_->stream());
+  for (auto* p : umma_plans_) k::umma_plan_destroy(p);
+  for (auto& s : steps_) {
+    if (s.ev0) cudaEventDestroy(s.ev0);
+    if (s.ev1) cudaEventDestroy(s.ev1);
+  }
+  if (arena_.ptr) cudaFree(arena_.ptr);
+  for (auto& b : owned_) cudaFree(b.ptr);
+  if (err_flag_) cudaFree(err_flag_);
+}
+
+Value* Session::find_value(const std::string& name) {
+  auto it = index_.find(name);
+  return it == index_.end() ? nullptr : &values_[it->second];
+}
+
+void Session::sync() {
+  OXB_CUDA(cudaStreamSynchronize(ctx_->stream()));
+  ctx_->counters.fences += 1;
+}
+
+int Session::check_error_flag() {
+  int flag = 0;
+  OXB_CUDA(cudaMemcpy(&flag, err_flag_, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag != 0) {
+    int zero = 0;
+    OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  }
+  return flag;
+}
+
+void Session::upload(const oxb200_operand* feeds, uint32_t n) {
+  for (auto& in : input_staging_) {
+    const oxb200_operand* f = nullptr;
+    for (uint32_t i = 0; i < n; ++i)
+      if (feeds[i].name && in.first == feeds[i].name) f = &feeds[i];
+    if (!f) raise(OXB200_FAILED, "run: no feed for graph input '%s'", in.first.c_str());
+    Value& v = values_[in.second];
+    if (external_bind_.count(in.first)) continue;  // bound to a value that already lives on the device
+    if (!f->lanes) raise(OXB200_FAILED, "run: feed '%s' has no host lanes", in.first.c_str());
+    if ((int64_t)f->len != v.numel()) raise(OXB200_FAILED, "run: feed '%s' has %llu lanes, the plan expects %lld", in.first.c_str(), (unsigned long long)f->len, (long long)v.numel());
+    if (f->rank != v.shape.size()) raise(OXB200_FAILED, "run: feed '%s' rank differs from the planned shape", in.first.c_str());
+    for (uint32_t d = 0; d < f->rank; ++d)
+      if ((int64_t)f->shape[d] != v.shape[d]) raise(OXB200_FAILED, "run: feed '%s' shape differs from the planned shape", in.first.c_str());
+    OXB_CUDA(cudaMemcpyAsync(v.ptr, f->lanes, (size_t)v.numel() * 4, cudaMemcpyHostToDevice, ctx_->stream()));
+    ctx_->counters.uploads += 1;
+    ctx_->counters.upload_bytes += (uint64_t)v.numel() * 4;
+  }
+}
+
+void Session::run_steps(bool profile) {
+  cudaStream_t s = ctx_->stream();
+  for (auto& st : steps_) {
+    if (profile) {
+      if (!st.ev0) {
+        OXB_CUDA(cudaEventCreate(&st.ev0));
+        OXB_CUDA(cudaEventCreate(&st.ev1));
+      }
+      OXB_CUDA(cudaEventRecord(st.ev0, s));
+    }
+    st.launch(s);
+    st.launches += 1;
+    if (profile) OXB_CUDA(cudaEventRecord(st.ev1, s));
+  }
+  OXB_CUDA(cudaGetLastError());
+}
+
+static void write_result_shape(const Value& v, oxb200_result* r) {
+  r->rank = (uint32_t)v.shape.size();
+  for (size_t d = 0; d < v.shape.size() && d < OXB200_MAX_RANK; ++d) r->shape[d] = (uint64_t)v.shape[d];
+  r->len = (uint64_t)v.numel();
+}
+
+void Session::download(oxb200_result* fetches, uint32_t n) {
+  download_async(fetches, n);
+  finish_download();
+}
+
+void Session::finish_download() {
+  sync();
+  int flag = check_error_flag();
+  if (flag) raise(OXB200_FAILED, "a tensor-core kernel gave up on a bounded wait (code %d); results are not valid", flag);
+}
+
+void Session::download_async(oxb200_result* fetches, uint32_t n) {
+  if (n != outputs_.size()) raise(OXB200_FAILED, "run: %u fetch slots for %zu graph outputs", n, outputs_.size());
+  // validate everything first, then copy: a rejected write leaves the caller's buffers untouched
+  // (write_node_outputs, root crate src/session/run/dispatch.rs:335-455)
+  for (uint32_t i = 0; i < n; ++i) {
+    const Value& v = values_[output_staging_[i].second];
+    if (fetches[i].lanes && fetches[i].cap < (uint64_t)v.numel())
+      raise(OXB200_FAILED, "run: fetch buffer for '%s' holds %llu lanes, %lld needed", outputs_[i].c_str(), (unsigned long long)fetches[i].cap, (long long)v.numel());
+  }
+  for (uint32_t i = 0; i < n; ++i) {
+    const Value& v = values_[output_staging_[i].second];
+    write_result_shape(v, &fetches[i]);
+    if (fetches[i].lanes && v.numel() > 0) {
+      OXB_CUDA(cudaMemcpyAsync(fetches[i].lanes, v.ptr, (size_t)v.numel() * 4, cudaMemcpyDeviceToHost, ctx_->stream()));
+      ctx_->counters.downloads += 1;
+      ctx_->counters.download_bytes += (uint64_t)v.numel() * 4;
+    }
+  }
+}
+
+void Session::fetch_value(const std::string& name, oxb200_result* out) {
+  Value* v = find_value(name);
+  if (!v) raise(OXB200_FAILED, "fetch_value: '%s' is not a value of the planned graph", name.c_str());
+  if (!v->ptr) raise(OXB200_FAILED, "fetch_value: '%s' has no device storage (fused away)", name.c_str());
+  write_result_shape(*v, out);
+  if (!out->lanes) return;
+  if (out->cap < (uint64_t)v->numel()) raise(OXB200_FAILED, "fetch_value: buffer too small for '%s'", name.c_str());
+  int64_t n = v->numel();
+  if (n == 0) return;
+  // convert to f32 lanes in the logical order through a temporary
+  void* tmp = ctx_->alloc_device((size_t)n * 4);
+  k::Dims4 d{1, 1, 1, 1};
+  if (v->shape.size() == 4) d = k::Dims4{v->shape[0], v->shape[1], v->shape[2], v->shape[3]};
+  else d = k::Dims4{n, 1, 1, 1};
+  k::TensorRef src{v->ptr, v->dt, v->shape.size() == 4 ? v->layout : Layout::PLAIN, d};
+  k::TensorRef dst{tmp, DT::F32, Layout::PLAIN, d};
+  k::convert(src, dst, ctx_->stream());
+  OXB_CUDA(cudaMemcpyAsync(out->lanes, tmp, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx_->stream()));
+  sync();
+  ctx_->free_device(tmp);
+  ctx_->counters.downloads += 1;
+  ctx_->counters.download_bytes += (uint64_t)n * 4;
+}
+
+void Session::bind_external(const std::string& name, void* ptr, DT dt, Layout layout) { external_bind_[name] = {ptr, {dt, layout}}; }
+
+}  // namespace oxb

@@ -1,0 +1,193 @@
+// Host runtime of the oxb200 execution provider: context, weight residency, the planner that
+// turns a node list into device steps over a lifetime-planned arena, and the run loop.
+#pragma once
+
+#include <functional>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <set>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "common.hpp"
+#include "kernels.hpp"
+
+namespace oxb {
+
+struct HostTensor {
+  std::vector<float> data;
+  std::vector<int64_t> shape;
+  int64_t numel() const { return prod(shape); }
+};
+
+// Attributes (oxionnx-core src/graph.rs:696-733), the five kinds the hot path uses.
+struct AttrMap {
+  std::map<std::string, int64_t> ints;
+  std::map<std::string, float> floats;
+  std::map<std::string, std::string> strings;
+  std::map<std::string, std::vector<int64_t>> int_lists;
+  std::map<std::string, std::vector<float>> float_lists;
+  int64_t i(const std::string& k, int64_t d) const {
+    auto it = ints.find(k);
+    return it == ints.end() ? d : it->second;
+  }
+  float f(const std::string& k, float d) const {
+    auto it = floats.find(k);
+    return it == floats.end() ? d : it->second;
+  }
+  std::string s(const std::string& k) const {
+    auto it = strings.find(k);
+    return it == strings.end() ? std::string() : it->second;
+  }
+  std::vector<int64_t> int_list(const std::string& k) const {
+    auto it = int_lists.find(k);
+    return it == int_lists.end() ? std::vector<int64_t>() : it->second;
+  }
+  bool has(const std::string& k) const {
+    return ints.count(k) || floats.count(k) || strings.count(k) || int_lists.count(k) || float_lists.count(k);
+  }
+  std::vector<std::string> names() const;
+};
+
+struct NodeDef {
+  std::string op, name;
+  std::vector<std::string> inputs, outputs;
+  AttrMap attrs;
+};
+
+// A value of the planned graph.
+struct Value {
+  std::string name;
+  std::vector<int64_t> shape;  // logical (ONNX) shape
+  DT dt = DT::F32;
+  Layout layout = Layout::PLAIN;
+  const HostTensor* host = nullptr;  // contents known at plan time (initializer or dispatch operand)
+  bool is_graph_input = false, is_graph_output = false;
+  bool external = false;  // storage owned elsewhere (resident dispatch operand, staging buffer)
+  int producer = -1;      // step index that writes it (-1: input / constant)
+  int last_use = -1;      // last step index that reads it
+  int alias_of = -1;      // shares the storage of another value
+  size_t bytes = 0;
+  int slot = -1;
+  void* ptr = nullptr;
+  int64_t numel() const { return prod(shape); }
+};
+
+struct Step {
+  std::string node_name, op_type, kernel;
+  int family = 2;  // 0 tcgen05, 1 direct CUDA-core, 2 glue
+  double work = 0;
+  bool work_is_bytes = true;
+  std::vector<int> reads, writes;  // value indices
+  std::function<void(cudaStream_t)> launch;
+  std::function<void()> finalize;  // runs once after the arena is laid out (builds tensor maps)
+  float last_ms = -1.f;
+  uint64_t launches = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+struct DeviceBuffer {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+class Context;
+
+// One planned graph (a whole session, or the one-node graph of a dispatch).
+class Session {
+ public:
+  explicit Session(Context* ctx) : ctx_(ctx) {}
+  ~Session();
+  // inputs: name -> shape (host data unknown) ; consts: name -> host tensor (known now)
+  void plan(const std::vector<NodeDef>& nodes, const std::vector<std::pair<std::string, std::vector<int64_t>>>& inputs,
+            const std::map<std::string, const HostTensor*>& volatile_consts, const std::vector<std::string>& outputs);
+  void upload(const oxb200_operand* feeds, uint32_t n);
+  void run_steps(bool profile);
+  void download(oxb200_result* fetches, uint32_t n);
+  void download_async(oxb200_result* fetches, uint32_t n);  // enqueue the copies
+  void finish_download();                                    // one fence + the kernels' error word
+  void fetch_value(const std::string& name, oxb200_result* out);
+  void sync();
+  std::vector<Step>& steps() { return steps_; }
+  const std::vector<std::string>& output_names() const { return outputs_; }
+  size_t arena_bytes() const { return arena_.bytes; }
+  size_t arena_slots() const { return n_slots_; }
+  // Bind a graph input to storage that already lives on the device (resident dispatch operand).
+  void bind_external(const std::string& name, void* ptr, DT dt, Layout layout);
+  // After a run, detach the storage of an output so it can outlive the session.
+  Value* find_value(const std::string& name);
+  int check_error_flag();
+
+ private:
+  friend class Planner;
+  Context* ctx_;
+  std::vector<Value> values_;
+  std::unordered_map<std::string, int> index_;
+  std::vector<Step> steps_;
+  std::vector<std::string> outputs_;
+  std::vector<std::pair<std::string, int>> input_staging_;  // graph input name -> value index of the raw f32 upload
+  std::vector<std::pair<std::string, int>> output_staging_; // graph output name -> value index of the f32 PLAIN copy
+  DeviceBuffer arena_;
+  std::vector<DeviceBuffer> owned_;  // staging + parameter buffers
+  std::vector<k::UmmaPlan*> umma_plans_;
+  size_t n_slots_ = 0;
+  int* err_flag_ = nullptr;
+  std::map<std::string, std::pair<void*, std::pair<DT, Layout>>> external_bind_;
+  std::shared_ptr<void> planner_;  // keeps the objects the step closures refer to alive
+};
+
+class Context {
+ public:
+  Context(int device, const oxb200_config& cfg);
+  ~Context();
+  int device() const { return device_; }
+  cudaStream_t stream() const { return stream_; }
+  const oxb200_config& cfg() const { return cfg_; }
+  void make_current();
+
+  void register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank);
+  const HostTensor* weight(const std::string& name) const;
+  bool weight_resident(const std::string& name) const;
+
+  // Device copy of a packed form of a weight, created on first use and kept for the context's
+  // life (ResidentWeights, oxionnx-cuda src/residency.rs; identity = name + form).
+  void* resident_form(const std::string& name, const std::string& form, size_t bytes, const std::function<void(void*)>& fill_host,
+                      bool cacheable);
+  void* alloc_device(size_t bytes);
+  void free_device(void* p);
+  void release_caches();
+  void free_temp_forms();
+
+  oxb200_counters counters{};
+  std::string last_error;
+  std::unique_ptr<Session> session;  // the planned session of oxb200_session_plan
+  cudaEvent_t run_ev0 = nullptr, run_ev1 = nullptr;
+  float last_run_ms = -1.f;
+  std::mutex mu;
+
+ private:
+  int device_;
+  oxb200_config cfg_;
+  cudaStream_t stream_ = nullptr;
+  std::unordered_map<std::string, HostTensor> weights_;
+  std::map<std::pair<std::string, std::string>, DeviceBuffer> forms_;
+  std::set<std::string> resident_names_;
+  std::vector<void*> temp_forms_;
+};
+
+// Device tensor handed across the ABI (CudaDeviceTensor).
+struct DeviceTensorHandle {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  DT dt = DT::F32;
+  Layout layout = Layout::PLAIN;
+  std::vector<int64_t> shape;
+};
+
+// Pure predicates.
+bool is_supported_op(const std::string& op);
+bool accepts_resident_slot(const std::string& op, uint32_t slot);
+
+}  // namespace oxb

@@ -1,0 +1,396 @@
+"""Host-side mirror of the reference's interface for the hot path, over the C ABI.
+
+Names and argument meaning follow the reference so that tests read like the reference's own:
+
+  Session.builder().build_from_graph(graph, weights)   root crate src/session/builder.rs:336
+  Session.run(feeds) -> {name: tensor}                  root crate src/session/run/entry.rs:92
+  CudaContext.try_new()                                 oxionnx-cuda src/context.rs:467
+  try_cuda_dispatch_resident(node, weights, intermediates, placement, ctx)
+                                                        oxionnx-cuda src/lib.rs:561
+  is_supported_op / accepts_resident_slot               oxionnx-cuda src/lib.rs:217,419
+  OpPlacement / decide_placement                        root crate src/execution_providers.rs:111,352
+
+Errors keep the reference's three-way meaning: `Declined` (Ok(None): let the next provider
+try), `OnnxError` (Err: log and fall back) and `VerifyMismatch` (proved wrong: fail the run).
+"""
+import ctypes
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+
+from . import _ffi
+from .graph import Graph, Node
+
+
+class OnnxError(RuntimeError):
+    """A failed dispatch or run (the Err arm)."""
+
+
+class Declined(Exception):
+    """The provider does not take this node (the Ok(None) arm); not an error."""
+
+
+class VerifyMismatch(OnnxError):
+    """The device result was proved wrong against the shadow check under strict mode."""
+
+
+def is_supported_op(op: str) -> bool:
+    return bool(_ffi.lib().oxb200_is_supported_op(op.encode()))
+
+
+def accepts_resident_slot(op: str, slot: int) -> bool:
+    return bool(_ffi.lib().oxb200_accepts_resident_slot(op.encode(), slot))
+
+
+def is_verify_mismatch(message: str) -> bool:
+    return bool(_ffi.lib().oxb200_is_verify_mismatch(message.encode()))
+
+
+def env_truthy(value: Optional[str]) -> bool:
+    return bool(_ffi.lib().oxb200_env_truthy(None if value is None else value.encode()))
+
+
+def device_count() -> int:
+    return int(_ffi.lib().oxb200_device_count())
+
+
+@dataclass
+class OpPlacement:
+    """OpPlacement {CpuOnly, Auto{gpu_threshold_bytes}, Manual(map)}."""
+    policy: str = "auto"
+    gpu_threshold_bytes: int = 4096
+    manual: Optional[Dict[str, str]] = None  # op name -> "cpu" | "cuda"
+
+    def decide(self, op: str, output_bytes: int) -> bool:
+        """True when the node goes to this provider (decide_placement)."""
+        code = {"cpu_only": 0, "auto": 1, "manual": 2}[self.policy]
+        pin = 0
+        if self.manual is not None and op in self.manual:
+            pin = 2 if self.manual[op] == "cuda" else 1
+        return bool(_ffi.lib().oxb200_decide_placement(code, self.gpu_threshold_bytes, pin, op.encode(), output_bytes))
+
+
+def _raise_for(status, message):
+    if status in (_ffi.OK_HOST, _ffi.OK_DEVICE):
+        return
+    if status == _ffi.DECLINED:
+        raise Declined(message)
+    if status == _ffi.VERIFY_MISMATCH:
+        raise VerifyMismatch(message)
+    raise OnnxError(message)
+
+
+class DeviceTensor:
+    """CudaDeviceTensor: a value that stays in HBM between dispatches."""
+
+    def __init__(self, ctx, handle):
+        self._ctx = ctx
+        self.handle = handle
+
+    @property
+    def shape(self):
+        shape = (ctypes.c_uint64 * _ffi.MAX_RANK)()
+        rank = ctypes.c_uint32()
+        n = ctypes.c_uint64()
+        _ffi.lib().oxb200_tensor_shape(self.handle, shape, ctypes.byref(rank), ctypes.byref(n))
+        return tuple(int(shape[d]) for d in range(rank.value))
+
+    def read_back(self) -> np.ndarray:
+        shape = self.shape
+        n = int(np.prod(shape)) if len(shape) else 1
+        buf = np.empty(max(n, 1), np.float32)
+        st = _ffi.lib().oxb200_tensor_read_back(self._ctx.handle, self.handle, buf.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), buf.size)
+        _raise_for(st, self._ctx.last_error())
+        return buf[:n].reshape(shape).copy()
+
+    def release(self):
+        if self.handle:
+            _ffi.lib().oxb200_tensor_release(self._ctx.handle, self.handle)
+            self.handle = None
+
+
+class CudaContext:
+    """One device, one stream, session-lifetime weight residency."""
+
+    def __init__(self, device: int = 0, *, verify=False, strict=False, residency=True, kernel_path="auto", keep_intermediates=False,
+                 profile=False):
+        cfg = _ffi.Config()
+        cfg.struct_size = ctypes.sizeof(_ffi.Config)
+        cfg.verify, cfg.strict, cfg.residency = int(verify), int(strict), int(residency)
+        cfg.kernel_path = 1 if kernel_path == "direct" else 0
+        cfg.keep_intermediates = int(keep_intermediates)
+        cfg.profile = int(profile)
+        h = ctypes.c_void_p()
+        st = _ffi.lib().oxb200_ctx_create(device, ctypes.byref(cfg), ctypes.byref(h))
+        if st != _ffi.OK_HOST:
+            raise OnnxError(_ffi.lib().oxb200_last_error(None).decode())
+        self.handle = h
+        self.device = device
+        self._weights = {}
+
+    @classmethod
+    def try_new(cls, device: int = 0, **kw):
+        """None when no usable device exists (CudaContext::try_new returns Option)."""
+        try:
+            return cls(device, **kw)
+        except OnnxError:
+            return None
+
+    def last_error(self) -> str:
+        return _ffi.lib().oxb200_last_error(self.handle).decode()
+
+    def close(self):
+        if self.handle:
+            _ffi.lib().oxb200_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def register_weights(self, weights: Dict[str, np.ndarray]):
+        for name, w in weights.items():
+            a = np.ascontiguousarray(np.asarray(w, dtype=np.float32))
+            shape = (ctypes.c_uint64 * max(a.ndim, 1))(*a.shape)
+            st = _ffi.lib().oxb200_weight_register(self.handle, name.encode(), a.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), a.size, shape,
+                                                   a.ndim)
+            _raise_for(st, self.last_error())
+            self._weights[name] = a.shape
+
+    def is_weight_resident(self, name: str) -> bool:
+        return bool(_ffi.lib().oxb200_is_weight_resident(self.handle, name.encode()))
+
+    def cache_counters(self) -> dict:
+        c = _ffi.Counters()
+        _ffi.lib().oxb200_get_counters(self.handle, ctypes.byref(c))
+        return c.as_dict()
+
+    def release_device_caches(self):
+        _raise_for(_ffi.lib().oxb200_release_device_caches(self.handle), self.last_error())
+
+    def shadow_verify(self, op: str, device_result: np.ndarray, cpu_result: np.ndarray):
+        a = np.ascontiguousarray(device_result, dtype=np.float32).ravel()
+        b = np.ascontiguousarray(cpu_result, dtype=np.float32).ravel()
+        st = _ffi.lib().oxb200_shadow_verify(self.handle, op.encode(), a.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+                                             b.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), min(a.size, b.size))
+        _raise_for(st, self.last_error())
+
+
+def try_cuda_dispatch_resident(node: Node, weights: Dict[str, np.ndarray], intermediates: Dict[str, object], placement: str,
+                               ctx: CudaContext):
+    """One node through the provider.  `intermediates` maps names to numpy arrays (host) or
+    DeviceTensor (resident).  Returns a list of numpy arrays (placement "host"), a DeviceTensor
+    (placement "device"), or None when the provider declines."""
+    lib = _ffi.lib()
+    keep = _ffi.Keep()
+    cnode = _ffi.CNode()
+    _ffi.pack_node(node, cnode, keep)
+    n_in = len(node.inputs)
+    ops = keep.add((_ffi.Operand * max(n_in, 1))())
+    for i, name in enumerate(node.inputs):
+        if not name:
+            ops[i].name = b""
+            continue
+        if name in intermediates:
+            v = intermediates[name]
+            if isinstance(v, DeviceTensor):
+                _ffi.pack_operand(ops[i], name, None, keep, resident=v.handle)
+            else:
+                _ffi.pack_operand(ops[i], name, v, keep)
+        elif name in weights:
+            if name in ctx._weights:
+                _ffi.pack_operand(ops[i], name, None, keep)
+            else:
+                _ffi.pack_operand(ops[i], name, weights[name], keep)
+        else:
+            raise OnnxError(f"TensorNotFound: {name}")
+    n_out = len(node.outputs)
+    res = keep.add((_ffi.Result * max(n_out, 1))())
+    cap = int(intermediates.get("__cap__", 0)) if isinstance(intermediates, dict) else 0
+    bufs = []
+    # generous host buffers: the output extent is not known to the caller before the dispatch
+    guess = max([int(np.asarray(v).size) for v in intermediates.values() if isinstance(v, np.ndarray)] + [1])
+    guess = min(max(guess * 64, 1 << 16, cap), 1 << 26)
+    for i in range(n_out):
+        b = np.empty(guess, np.float32)
+        bufs.append(b)
+        res[i].lanes = b.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+        res[i].cap = b.size
+    want = _ffi.PLACE_DEVICE if placement == "device" else _ffi.PLACE_HOST
+    st = lib.oxb200_dispatch(ctx.handle, ctypes.byref(cnode), ops, n_in, want, res, n_out)
+    if st == _ffi.DECLINED:
+        return None
+    _raise_for(st, ctx.last_error())
+    if st == _ffi.OK_DEVICE:
+        return DeviceTensor(ctx, ctypes.c_void_p(res[0].resident))
+    return [_ffi.result_array(res[i], bufs[i]) if node.outputs[i] else None for i in range(n_out)]
+
+
+def try_cuda_dispatch(node, weights, intermediates, ctx):
+    """Host tensors in, host tensors out (oxionnx-cuda src/lib.rs:354)."""
+    return try_cuda_dispatch_resident(node, weights, intermediates, "host", ctx)
+
+
+class SessionBuilder:
+    def __init__(self):
+        self._device = 0
+        self._ctx_kw = {}
+        self._input_shapes = {}
+
+    def with_device(self, device: int):
+        self._device = device
+        return self
+
+    def with_optimization_level(self, _level):
+        """Accepted for source compatibility: graphs reach this provider already optimised
+        (the fused Conv / OxiInstanceNorm node contract), nothing is rewritten here."""
+        return self
+
+    def with_kernel_path(self, path: str):
+        self._ctx_kw["kernel_path"] = path
+        return self
+
+    def with_keep_intermediates(self, on=True):
+        self._ctx_kw["keep_intermediates"] = on
+        return self
+
+    def with_profiling(self, on=True):
+        self._ctx_kw["profile"] = on
+        return self
+
+    def with_input_shapes(self, shapes: Dict[str, tuple]):
+        self._input_shapes = dict(shapes)
+        return self
+
+    def build_from_graph(self, graph: Graph, weights: Dict[str, np.ndarray]):
+        return Session(graph, weights, self._device, self._input_shapes, self._ctx_kw)
+
+
+class Session:
+    """A graph planned once and run device-resident: every intermediate stays in HBM."""
+
+    @staticmethod
+    def builder() -> SessionBuilder:
+        return SessionBuilder()
+
+    def __init__(self, graph, weights, device, input_shapes, ctx_kw):
+        self.graph = graph
+        self.ctx = CudaContext(device, **ctx_kw)
+        self.ctx.register_weights(weights)
+        self._input_shapes = dict(input_shapes)
+        self._planned_for = None
+        self._out_bufs = None
+
+    def _plan(self, shapes):
+        lib = _ffi.lib()
+        keep = _ffi.Keep()
+        nodes = keep.add((_ffi.CNode * max(len(self.graph.nodes), 1))())
+        for i, n in enumerate(self.graph.nodes):
+            _ffi.pack_node(n, nodes[i], keep)
+        ins = keep.add((_ffi.ValueInfo * max(len(self.graph.input_names), 1))())
+        for i, name in enumerate(self.graph.input_names):
+            ins[i].name = name.encode()
+            sh = shapes[name]
+            ins[i].shape = keep.add((ctypes.c_uint64 * max(len(sh), 1))(*sh))
+            ins[i].rank = len(sh)
+        outs = keep.add((ctypes.c_char_p * max(len(self.graph.output_names), 1))(*[s.encode() for s in self.graph.output_names]))
+        st = lib.oxb200_session_plan(self.ctx.handle, nodes, len(self.graph.nodes), ins, len(self.graph.input_names), outs,
+                                     len(self.graph.output_names))
+        _raise_for(st, self.ctx.last_error())
+        self._planned_for = {k: tuple(v) for k, v in shapes.items()}
+        self._out_bufs = None
+
+    def ensure_planned(self, feeds=None):
+        shapes = dict(self._input_shapes)
+        if feeds is not None:
+            shapes.update({k: tuple(np.asarray(v).shape) for k, v in feeds.items()})
+        if self._planned_for != {k: tuple(shapes[k]) for k in self.graph.input_names}:
+            self._plan({k: tuple(shapes[k]) for k in self.graph.input_names})
+
+    def _operands(self, feeds, keep):
+        ops = keep.add((_ffi.Operand * max(len(self.graph.input_names), 1))())
+        for i, name in enumerate(self.graph.input_names):
+            if name not in feeds:
+                raise OnnxError(f"TensorNotFound: missing feed '{name}'")
+            _ffi.pack_operand(ops[i], name, feeds[name], keep)
+        return ops
+
+    def _results(self, keep, probe=True):
+        lib = _ffi.lib()
+        n_out = len(self.graph.output_names)
+        res = keep.add((_ffi.Result * max(n_out, 1))())
+        if self._out_bufs is None:
+            # learn the output extents from the plan
+            self._out_bufs = []
+            for name in self.graph.output_names:
+                r = _ffi.Result()
+                st = lib.oxb200_fetch_value(self.ctx.handle, name.encode(), ctypes.byref(r))
+                _raise_for(st, self.ctx.last_error())
+                self._out_bufs.append(np.empty(max(int(r.len), 1), np.float32))
+        for i, b in enumerate(self._out_bufs):
+            res[i].lanes = b.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+            res[i].cap = b.size
+        return res
+
+    def run(self, feeds: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
+        self.ensure_planned(feeds)
+        lib = _ffi.lib()
+        keep = _ffi.Keep()
+        ops = self._operands(feeds, keep)
+        res = self._results(keep)
+        st = lib.oxb200_run(self.ctx.handle, ops, len(self.graph.input_names), res, len(self.graph.output_names))
+        _raise_for(st, self.ctx.last_error())
+        return {name: _ffi.result_array(res[i], self._out_bufs[i]) for i, name in enumerate(self.graph.output_names)}
+
+    # ---- measurement helpers: the same run split into stage / resident launches / read ----
+    def upload(self, feeds):
+        self.ensure_planned(feeds)
+        keep = _ffi.Keep()
+        ops = self._operands(feeds, keep)
+        _raise_for(_ffi.lib().oxb200_upload_feeds(self.ctx.handle, ops, len(self.graph.input_names)), self.ctx.last_error())
+
+    def run_resident(self, iters=1) -> float:
+        ms = ctypes.c_float()
+        _raise_for(_ffi.lib().oxb200_run_resident(self.ctx.handle, iters, ctypes.byref(ms)), self.ctx.last_error())
+        return float(ms.value)
+
+    def download(self) -> Dict[str, np.ndarray]:
+        keep = _ffi.Keep()
+        res = self._results(keep)
+        _raise_for(_ffi.lib().oxb200_download_fetches(self.ctx.handle, res, len(self.graph.output_names)), self.ctx.last_error())
+        return {name: _ffi.result_array(res[i], self._out_bufs[i]) for i, name in enumerate(self.graph.output_names)}
+
+    def fetch_value(self, name: str) -> np.ndarray:
+        """Any value of the planned graph after a run (keep_intermediates for intermediates)."""
+        lib = _ffi.lib()
+        r = _ffi.Result()
+        _raise_for(lib.oxb200_fetch_value(self.ctx.handle, name.encode(), ctypes.byref(r)), self.ctx.last_error())
+        buf = np.empty(max(int(r.len), 1), np.float32)
+        r.lanes = buf.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+        r.cap = buf.size
+        _raise_for(lib.oxb200_fetch_value(self.ctx.handle, name.encode(), ctypes.byref(r)), self.ctx.last_error())
+        return _ffi.result_array(r, buf)
+
+    def has_value(self, name: str) -> bool:
+        r = _ffi.Result()
+        return _ffi.lib().oxb200_fetch_value(self.ctx.handle, name.encode(), ctypes.byref(r)) == _ffi.OK_HOST
+
+    def steps(self) -> List[dict]:
+        """NodeProfile-like records of the planned steps (profiling_results)."""
+        lib = _ffi.lib()
+        out = []
+        for i in range(lib.oxb200_plan_step_count(self.ctx.handle)):
+            s = _ffi.StepInfo()
+            lib.oxb200_plan_step_info(self.ctx.handle, i, ctypes.byref(s))
+            out.append(dict(node=s.node_name.decode(), op=s.op_type.decode(), kernel=s.kernel.decode(), work=float(s.work),
+                            work_is_bytes=bool(s.work_is_bytes), ms=float(s.last_ms), launches=int(s.launches)))
+        return out
+
+    def cuda_cache_counters(self) -> dict:
+        return self.ctx.cache_counters()
+
+    def close(self):
+        self.ctx.close()

@@ -1,0 +1,355 @@
+"""Per-operator parity on the B200: every node goes through the C ABI (oxb200_dispatch, the
+counterpart of try_cuda_dispatch_resident) and is compared with the CPU oracle on the same
+seeded inputs, and with the reference's own known-answer vectors.
+
+Integer and quantised operators: bit-exact.  Float operators: |a-b| <= atol + rtol*|b| with
+rtol = 2e-3 (the TF32 tolerance of the path) and atol = 2e-3 * max|b|.
+"""
+import json
+import zlib
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from oxionnx_b200.graph import Node
+from oxionnx_b200 import session as S
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+with open(os.path.join(ROOT, "tests", "golden", "reference_vectors.json")) as _fh:
+    CASES = json.load(_fh)["cases"]
+
+RTOL_TF32 = 2e-3
+
+
+@pytest.fixture(scope="module", params=["auto", "direct"])
+def ctx(request):
+    c = S.CudaContext(0, kernel_path=request.param)
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def ctx_auto():
+    c = S.CudaContext(0)
+    yield c
+    c.close()
+
+
+def _arr(t):
+    return np.asarray(t["data"], dtype=np.float32).reshape(t["shape"])
+
+
+def dispatch(ctx, op, inputs, attrs=None, n_out=1):
+    names = [f"in{i}" if x is not None else "" for i, x in enumerate(inputs)]
+    node = Node(op=op, name="op0", inputs=names, outputs=[f"out{i}" for i in range(n_out)], attrs=dict(attrs or {}))
+    inter = {n: x for n, x in zip(names, inputs) if n}
+    return S.try_cuda_dispatch(node, {}, inter, ctx)
+
+
+def assert_close_tf32(got, want, what=""):
+    want = np.asarray(want, np.float32)
+    atol = RTOL_TF32 * float(np.max(np.abs(want))) if want.size else 0.0
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    bound = atol + RTOL_TF32 * np.abs(want)
+    assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
+    assert np.all(err <= bound), f"{what}: max err {err.max()} (bound {bound[np.argmax(err - bound)]}), {np.sum(err > bound)} lanes off"
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_reference_vector_through_abi(ctx, case):
+    ins = [_arr(t) for t in case["inputs"]]
+    if "error_contains" in case:
+        # malformed quantised nodes decline so that the CPU operator raises its own typed error
+        assert dispatch(ctx, case["op"], ins, case["attrs"]) is None
+        assert case["error_contains"].split()[-1] in ctx.last_error() or "scale" in ctx.last_error() or "entries" in ctx.last_error()
+        return
+    outs = dispatch(ctx, case["op"], ins, case["attrs"], n_out=len(case["expected"]))
+    assert outs is not None, ctx.last_error()
+    exact = case["exact"]
+    for i, (got, want) in enumerate(zip(outs, case["expected"])):
+        w = _arr(want)
+        assert list(got.shape) == want["shape"]
+        rule = exact[i] if isinstance(exact, list) else exact
+        if rule is True:
+            assert np.array_equal(got, w), f"{case['name']} output {i}: {got.ravel()[:8]} vs {w.ravel()[:8]} ({case['source']})"
+        else:
+            assert np.all(np.abs(got - w) <= float(rule))
+
+
+QCONV_SHAPES = [
+    # N, C, H, W, OC, k, stride, pad, x_zp, relu-ish y_zp
+    (2, 32, 9, 9, 32, 1, 1, 0, 128, 128),      # 32-byte channel block, M tail
+    (3, 64, 14, 14, 64, 3, 1, 1, 0, 0),        # 64-byte block, 3x3 halo, row wrap inside a tile
+    (2, 128, 7, 7, 256, 3, 2, 1, 0, 128),      # stride 2, two channel tiles
+    (1, 256, 8, 8, 40, 1, 2, 0, 128, 0),       # 1x1 stride 2 (projection shortcut), ragged OC
+    (2, 64, 12, 10, 128, 3, 1, 1, 0, 128),     # non-square
+    (5, 64, 16, 16, 64, 3, 1, 1, 128, 0),      # padded with a non-zero zero point: direct kernel
+    (2, 3, 20, 20, 16, 7, 2, 3, 128, 0),       # stem geometry: direct kernel
+    (1, 512, 4, 4, 1000, 1, 1, 0, 128, 128),   # classifier as a 1x1 convolution
+]
+
+
+@pytest.mark.parametrize("shape", QCONV_SHAPES, ids=[str(s) for s in QCONV_SHAPES])
+def test_qlinear_conv_bit_exact(ctx, shape):
+    n, c, h, w, oc, k, stride, pad, x_zp, y_zp = shape
+    rng = np.random.default_rng(zlib.crc32(repr(shape).encode()))
+    if x_zp == 0:
+        x = rng.integers(0, 128, (n, c, h, w)).astype(np.float32)
+    else:
+        x = rng.integers(0, 256, (n, c, h, w)).astype(np.float32)
+    wt = rng.integers(-127, 128, (oc, c, k, k)).astype(np.float32)
+    ws = rng.uniform(0.001, 0.01, oc).astype(np.float32)
+    bias = rng.integers(-1000, 1001, oc).astype(np.float32)
+    y_scale = np.float32(0.005 * 73.0 * np.sqrt(c * k * k) * 40 * 0.02 / 40.0)
+    ins = [x, np.float32([0.02]), np.float32([x_zp]), wt, ws, np.zeros(oc, np.float32), np.float32([y_scale]), np.float32([y_zp]), bias]
+    attrs = {"strides": [stride, stride], "pads": [pad] * 4, "kernel_shape": [k, k]}
+    oracle.set_threads(8)
+    want, = oracle.run_node("QLinearConv", ins, attrs)
+    got = dispatch(ctx, "QLinearConv", ins, attrs)
+    assert got is not None, ctx.last_error()
+    assert np.array_equal(got[0], want), f"{np.sum(got[0] != want)} of {want.size} lanes differ; first {got[0].ravel()[:6]} vs {want.ravel()[:6]}"
+    assert np.unique(want).size > 8, "degenerate test vector"
+
+
+def test_conv_integer_and_matmul_integer_bit_exact(ctx):
+    rng = np.random.default_rng(17)
+    oracle.set_threads(8)
+    x = rng.integers(0, 256, (2, 64, 10, 10)).astype(np.float32)
+    w = rng.integers(-127, 128, (96, 64, 3, 3)).astype(np.float32)
+    for xzp, pads in ((0.0, [1, 1, 1, 1]), (7.0, [0, 0, 0, 0]), (130.0, [1, 0, 2, 1])):
+        ins = [x, w, np.float32([xzp])]
+        attrs = {"pads": pads}
+        want, = oracle.run_node("ConvInteger", ins, attrs)
+        got = dispatch(ctx, "ConvInteger", ins, attrs)
+        assert got is not None, ctx.last_error()
+        assert np.array_equal(got[0], want)
+    a = rng.integers(0, 256, (130, 3072)).astype(np.float32)
+    b = rng.integers(-127, 128, (3072, 96)).astype(np.float32)
+    for azp in (np.float32([128]), np.float32([0]), None):
+        ins = [a, b, azp] if azp is not None else [a, b]
+        want, = oracle.run_node("MatMulInteger", ins)
+        got = dispatch(ctx, "MatMulInteger", ins)
+        assert got is not None, ctx.last_error()
+        assert np.array_equal(got[0], want)
+    # accumulators above 2^24 are rounded (to nearest even) when stored as f32 lanes, on both sides alike
+    bpos = rng.integers(64, 128, (3072, 96)).astype(np.float32)
+    want, = oracle.run_node("MatMulInteger", [a, bpos])
+    got = dispatch(ctx, "MatMulInteger", [a, bpos])
+    assert np.array_equal(got[0], want)
+    assert np.abs(want).max() > 2**24 and np.any(want % 2 == 0)
+    # per-row a_zero_point and per-column b_zero_point, batched A
+    a3 = rng.integers(0, 256, (2, 5, 64)).astype(np.float32)
+    b2 = rng.integers(0, 256, (64, 48)).astype(np.float32)
+    ins = [a3, b2, rng.integers(0, 256, 5).astype(np.float32), rng.integers(0, 256, 48).astype(np.float32)]
+    want, = oracle.run_node("MatMulInteger", ins)
+    got = dispatch(ctx, "MatMulInteger", ins)
+    assert got is not None, ctx.last_error()
+    assert np.array_equal(got[0], want)
+
+
+def test_qlinear_matmul_bit_exact(ctx):
+    rng = np.random.default_rng(23)
+    oracle.set_threads(8)
+    for (m, k, n, azp, yzp) in ((64, 1024, 256, 128, 128), (200, 128, 72, 0, 0), (7, 96, 33, 113, 118)):
+        a = rng.integers(0, 256, (m, k)).astype(np.float32)
+        b = rng.integers(-127, 128, (k, n)).astype(np.float32)
+        ins = [a, np.float32([0.05]), np.float32([azp]), b, np.float32([0.011]), np.float32([0]), np.float32([0.1 * np.sqrt(k) / 8]), np.float32([yzp])]
+        want, = oracle.run_node("QLinearMatMul", ins)
+        got = dispatch(ctx, "QLinearMatMul", ins)
+        assert got is not None, ctx.last_error()
+        assert np.array_equal(got[0], want), f"{(m, k, n)}: {np.sum(got[0] != want)} lanes differ"
+
+
+def test_quantize_dequantize_dynamic_bit_exact(ctx):
+    rng = np.random.default_rng(29)
+    x = (rng.standard_normal((4, 6, 10, 12)) * 3).astype(np.float32)
+    x.ravel()[:64] = (np.arange(64) - 32) * 0.025 + 0.0125  # exact ties at scale 0.05
+    for zp in (np.float32([128]), np.float32([0]), None):
+        ins = [x, np.float32([0.05])] + ([zp] if zp is not None else [])
+        want, = oracle.run_node("QuantizeLinear", ins)
+        got = dispatch(ctx, "QuantizeLinear", ins)
+        assert np.array_equal(got[0], want)
+    scale_c = rng.uniform(0.01, 0.1, 6).astype(np.float32)
+    zp_c = rng.integers(120, 140, 6).astype(np.float32)
+    want, = oracle.run_node("QuantizeLinear", [x, scale_c, zp_c], {"axis": 1})
+    got = dispatch(ctx, "QuantizeLinear", [x, scale_c, zp_c], {"axis": 1})
+    assert np.array_equal(got[0], want)
+    q = rng.integers(0, 256, (4, 6, 10, 12)).astype(np.float32)
+    want, = oracle.run_node("DequantizeLinear", [q, scale_c, zp_c], {"axis": 1})
+    got = dispatch(ctx, "DequantizeLinear", [q, scale_c, zp_c], {"axis": 1})
+    assert np.array_equal(got[0], want)
+    want, = oracle.run_node("DequantizeLinear", [q, np.float32([0.037]), np.float32([128])])
+    got = dispatch(ctx, "DequantizeLinear", [q, np.float32([0.037]), np.float32([128])])
+    assert np.array_equal(got[0], want)
+    for arr in (x.reshape(24, 120), np.zeros((3, 5), np.float32), np.float32([[-0.5, 254.5]]), (rng.standard_normal((1000, 77)) * 5).astype(np.float32)):
+        want = oracle.run_node("DynamicQuantizeLinear", [arr], n_outputs=3)
+        got = dispatch(ctx, "DynamicQuantizeLinear", [arr], n_out=3)
+        assert got is not None, ctx.last_error()
+        for g, w in zip(got, want):
+            assert g.shape == w.shape
+            assert np.array_equal(g, w)
+
+
+FCONV_SHAPES = [
+    (2, 8, 12, 12, 16, 3, 1, 1, "relu"),     # 32-byte channel block
+    (3, 16, 9, 9, 24, 1, 1, 0, ""),          # 64-byte block, 1x1 GEMM path, ragged OC
+    (2, 32, 14, 14, 64, 3, 2, 1, "relu"),    # 128-byte block, stride 2
+    (1, 64, 7, 7, 256, 1, 2, 0, ""),         # projection shortcut
+    (2, 64, 8, 8, 64, 3, 1, 1, "clip"),
+    (2, 3, 32, 32, 16, 7, 2, 3, "relu"),     # stem (direct kernel reading channels-first input)
+    (1, 6, 10, 10, 6, 3, 1, 1, ""),          # depthwise-like groups below
+]
+
+
+@pytest.mark.parametrize("shape", FCONV_SHAPES, ids=[str(s) for s in FCONV_SHAPES])
+def test_float_conv_within_tf32_tolerance(ctx, shape):
+    n, c, h, w, oc, k, stride, pad, act = shape
+    rng = np.random.default_rng(zlib.crc32(repr(shape).encode()))
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    group = 3 if c == 6 else 1
+    wt = (rng.standard_normal((oc, c // group, k, k)) * np.sqrt(2.0 / (c * k * k))).astype(np.float32)
+    b = (rng.standard_normal(oc) * 0.1).astype(np.float32)
+    attrs = {"strides": [stride, stride], "pads": [pad] * 4, "group": group}
+    if act:
+        attrs["activation"] = act
+    if act == "clip":
+        attrs["activation_min"] = 0.0
+        attrs["activation_max"] = 0.75
+    oracle.set_threads(8)
+    want, = oracle.run_node("Conv", [x, wt, b], attrs)
+    got = dispatch(ctx, "Conv", [x, wt, b], attrs)
+    assert got is not None, ctx.last_error()
+    assert_close_tf32(got[0], want, f"Conv {shape}")
+
+
+def test_gemm_and_matmul_within_tf32_tolerance(ctx):
+    rng = np.random.default_rng(31)
+    a = rng.standard_normal((32, 2048)).astype(np.float32)
+    w = (rng.standard_normal((1000, 2048)) / 45).astype(np.float32)
+    bias = rng.standard_normal(1000).astype(np.float32)
+    want, = oracle.run_node("Gemm", [a, w, bias], {"transB": 1, "alpha": 1.0, "beta": 1.0})
+    got = dispatch(ctx, "Gemm", [a, w, bias], {"transB": 1, "alpha": 1.0, "beta": 1.0})
+    assert_close_tf32(got[0], want, "Gemm transB")
+    w2 = np.ascontiguousarray(w.T)
+    want, = oracle.run_node("Gemm", [a, w2, bias], {"alpha": 0.5, "beta": 2.0})
+    got = dispatch(ctx, "Gemm", [a, w2, bias], {"alpha": 0.5, "beta": 2.0})
+    assert_close_tf32(got[0], want, "Gemm alpha beta")
+    a3 = rng.standard_normal((2, 3, 17, 64)).astype(np.float32)
+    b2 = rng.standard_normal((64, 40)).astype(np.float32)
+    want, = oracle.run_node("MatMul", [a3, b2])
+    got = dispatch(ctx, "MatMul", [a3, b2])
+    assert_close_tf32(got[0], want, "MatMul stacked A")
+
+
+def test_glue_ops_match_oracle(ctx_auto):
+    ctx = ctx_auto
+    rng = np.random.default_rng(37)
+    x = rng.standard_normal((2, 24, 13, 11)).astype(np.float32)
+    y = rng.standard_normal((2, 24, 13, 11)).astype(np.float32)
+    for op in ("Add", "Sub", "Mul", "Div"):
+        want, = oracle.run_node(op, [x, y])
+        got = dispatch(ctx, op, [x, y])
+        assert np.array_equal(got[0], want), op
+    sc = rng.standard_normal((2, 24, 1, 1)).astype(np.float32)
+    for op in ("Mul", "Add"):
+        want, = oracle.run_node(op, [x, sc])
+        got = dispatch(ctx, op, [x, sc])
+        assert np.array_equal(got[0], want), op + " per-sample broadcast"
+    want, = oracle.run_node("Relu", [x])
+    assert np.array_equal(dispatch(ctx, "Relu", [x])[0], want)
+    want, = oracle.run_node("Tanh", [x])
+    assert np.allclose(dispatch(ctx, "Tanh", [x])[0], want, rtol=1e-5, atol=1e-6)
+    slope = rng.uniform(0.05, 0.3, (24, 1, 1)).astype(np.float32)
+    want, = oracle.run_node("PRelu", [x, slope])
+    assert np.array_equal(dispatch(ctx, "PRelu", [x, slope])[0], want)
+    attrs = {"kernel_shape": [3, 3], "strides": [2, 2], "pads": [1, 1, 1, 1]}
+    want, = oracle.run_node("MaxPool", [x], attrs)
+    assert np.array_equal(dispatch(ctx, "MaxPool", [x], attrs)[0], want)
+    want, = oracle.run_node("GlobalAveragePool", [x])
+    assert np.array_equal(dispatch(ctx, "GlobalAveragePool", [x])[0], want), "sequential f32 sum order"
+    want, = oracle.run_node("OxiInstanceNorm", [x], {"epsilon": 1e-5})
+    got = dispatch(ctx, "OxiInstanceNorm", [x], {"epsilon": 1e-5})[0]
+    assert np.allclose(got, want, rtol=1e-4, atol=1e-5)
+    for attrs in ({"mode": "nearest", "coordinate_transformation_mode": "asymmetric", "nearest_mode": "floor"},
+                  {"mode": "linear", "coordinate_transformation_mode": "half_pixel"},
+                  {"mode": "linear", "coordinate_transformation_mode": "pytorch_half_pixel"}):
+        ins = [x, None, np.float32([1, 1, 2, 2])]
+        want, = oracle.run_node("Resize", ins, attrs)
+        got = dispatch(ctx, "Resize", ins, attrs)
+        assert got is not None, ctx.last_error()
+        assert np.allclose(got[0], want, rtol=1e-6, atol=1e-6), attrs
+    for mode in ("reflect", "constant", "edge"):
+        ins = [x, np.float32([0, 0, 1, 2, 0, 0, 1, 2])]
+        want, = oracle.run_node("Pad", ins, {"mode": mode})
+        assert np.array_equal(dispatch(ctx, "Pad", ins, {"mode": mode})[0], want), mode
+    z = rng.standard_normal((2, 8, 13, 11)).astype(np.float32)
+    want, = oracle.run_node("Concat", [x, z], {"axis": 1})
+    assert np.array_equal(dispatch(ctx, "Concat", [x, z], {"axis": 1})[0], want)
+    want, = oracle.run_node("Flatten", [x], {"axis": 1})
+    assert np.array_equal(dispatch(ctx, "Flatten", [x], {"axis": 1})[0], want)
+
+
+def test_decline_and_failure_contract(ctx_auto):
+    ctx = ctx_auto
+    x = np.zeros((1, 4, 5, 5), np.float32)
+    w = np.zeros((4, 4, 3, 3), np.float32)
+    # not claimed: a clean decline
+    assert dispatch(ctx, "Softplus", [x]) is None
+    # unknown attribute: decline, never ignore
+    assert dispatch(ctx, "Conv", [x, w], {"made_up_attribute": 3}) is None
+    # fused activation outside what the optimizer emits
+    assert dispatch(ctx, "Conv", [x, w], {"activation": "gelu"}) is None
+    # malformed quantised operands decline (the CPU operator owns the typed error)
+    bad = np.full((1, 4, 5, 5), np.nan, np.float32)
+    assert dispatch(ctx, "ConvInteger", [bad, w]) is None
+    assert dispatch(ctx, "QuantizeLinear", [x, np.float32([0.0])]) is None
+    c = ctx.cache_counters()
+    assert c["declines"] >= 5 and c["failures"] == 0
+
+
+def test_device_resident_chain_and_counters():
+    """Conv -> Relu -> Conv with the intermediate kept in HBM: two uploads of activations at
+    most, one read-back, and the same lanes as the host-placed chain."""
+    ctx = S.CudaContext(0)
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((2, 32, 10, 10)).astype(np.float32)
+    w1 = (rng.standard_normal((64, 32, 3, 3)) * 0.06).astype(np.float32)
+    w2 = (rng.standard_normal((32, 64, 1, 1)) * 0.1).astype(np.float32)
+    weights = {"w1": w1, "w2": w2}
+    ctx.register_weights(weights)
+    n1 = Node("Conv", "c1", ["x", "w1"], ["h"], {"pads": [1, 1, 1, 1], "activation": "relu"})
+    n2 = Node("Conv", "c2", ["h", "w2"], ["y"], {})
+    h = S.try_cuda_dispatch_resident(n1, weights, {"x": x}, "device", ctx)
+    assert isinstance(h, S.DeviceTensor) and h.shape == (2, 64, 10, 10)
+    before = ctx.cache_counters()
+    y = S.try_cuda_dispatch_resident(n2, weights, {"h": h}, "host", ctx)[0]
+    after = ctx.cache_counters()
+    assert after["uploads"] == before["uploads"], "a resident operand must not be re-uploaded"
+    assert ctx.is_weight_resident("w1") and ctx.is_weight_resident("w2")
+    h_host = S.try_cuda_dispatch(n1, weights, {"x": x}, ctx)[0]
+    assert np.array_equal(h.read_back(), h_host)
+    y_host = S.try_cuda_dispatch(n2, weights, {"h": h_host}, ctx)[0]
+    assert np.array_equal(y, y_host)
+    # second use of the same weights: no new weight upload
+    wu = ctx.cache_counters()["weight_uploads"]
+    S.try_cuda_dispatch(n2, weights, {"h": h_host}, ctx)
+    assert ctx.cache_counters()["weight_uploads"] == wu
+    h.release()
+    ctx.close()
+
+
+def test_shadow_verify_contract():
+    """A 'wrong kernel' is simulated on the host by handing mismatching vectors to the
+    comparator, as the reference's own shadow_verify tests do."""
+    a = np.float32([1.0, 2.0, 3.0])
+    for strict, exc in ((True, S.VerifyMismatch), (False, S.OnnxError)):
+        ctx = S.CudaContext(0, verify=True, strict=strict)
+        ctx.shadow_verify("Conv", a, a + np.float32(5e-5))
+        with pytest.raises(exc) as ei:
+            ctx.shadow_verify("Conv", a, a + np.float32(0.5))
+        assert S.is_verify_mismatch(str(ei.value))
+        ctx.close()
