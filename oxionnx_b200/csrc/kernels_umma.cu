@@ -23,6 +23,8 @@
 //    copies land, frees its TMEM and returns, so the context stays usable.
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -41,6 +43,9 @@ constexpr long long WAIT_CYCLES = 2000000000LL;  // ~1 s at 2 GHz
 struct alignas(64) KParams {
   CUtensorMap tmA;
   CUtensorMap tmB;
+  CUtensorMap tmO;
+  int out_tma, out_row_bytes;
+  int dbg;  // timing experiments only: 1 skip the epilogue work, 2 TMEM reads only, 3 reads + math, 0 normal
   int a_im2col;
   int M, OC;
   int P, Q, S;
@@ -48,7 +53,7 @@ struct alignas(64) KParams {
   int taps, cblocks, cb_elems;
   int swizzle_bytes;  // 128, 64 or 32: bytes of K per stage row
   int stages;
-  int n_tiles;
+  int n_tiles, m_tiles;
   uint32_t idesc;
   // epilogue
   int mode;
@@ -170,26 +175,153 @@ __device__ __forceinline__ float round_tf32(float v) {
 }
 
 // ---- the kernel ---------------------------------------------------------------------------
+// Persistent: one CTA per SM walks the tile list (channel tile fastest, so CTAs that share an
+// activation tile run together and meet in L2).  The shared-memory ring and the two TMEM
+// accumulators are both pipelined across tiles: while the epilogue warps drain accumulator b,
+// the MMA issuer fills accumulator b^1 and the producer is already loading further ahead.
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ONNX requantisation of one accumulator, bit-identical to the reference's
+//   clamp(round_half_even(f64(acc) * f64(combined) + f64(zero_point)), lo, hi).
+// The FP64 pipe of this part is far too narrow for an epilogue, so the value is first formed
+// in f32: a = (float)acc, r = fma(a, c, zp) with |r - exact| <= (|acc*c| + |r|) * 2^-24.  For
+// |r| <= 1024 that is below 2^-12, so whenever r is further than 2^-10 from every half-integer
+// the f32 and the f64 values round to the same integer; for |r| > 1024 both saturate on the
+// same side.  Only the few lanes that land within 2^-10 of a tie take the exact f64 path.
+__device__ __forceinline__ int requant_exact(int32_t acc, float c, float zpf, int zp, int lo, int hi) {
+  const float r = fmaf(__int2float_rn(acc), c, zpf);
+  const float q = rintf(r);
+  const bool near_tie = fabsf(r - q) > 0.4990234375f && fabsf(r) <= 1024.0f;
+  int out;
+  if (!near_tie) {
+    out = __float2int_rn(r);
+  } else {
+    const double scaled = __dadd_rn(__dmul_rn((double)acc, (double)c), (double)zp);
+    out = __double2int_rn(scaled);
+  }
+  return min(max(out, lo), hi);
+}
+
+// Fused epilogue of one 32-channel run of one output pixel: bias / zero-point correction,
+// requantisation or activation, packed into 32-bit words (8 for 8-bit outputs, 16 for 16-bit,
+// 32 for 32-bit).
+__device__ __forceinline__ void epilogue_math(const KParams& p, const uint32_t (&v)[32], const float* sf, const int32_t* sb, const int32_t* sw, int xz,
+                                              int c0, size_t esz, uint32_t (&w)[32]) {
+  if (p.mode == EPI_F32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float f = __uint_as_float(v[j]) + sf[c0 + j];
+      if (p.act == 1) f = fmaxf(f, 0.f);
+      else if (p.act == 2) f = fminf(fmaxf(f, p.clip_lo), p.clip_hi);
+      if (p.round_tf32) f = round_tf32(f);
+      w[j] = __float_as_uint(f);
+    }
+    return;
+  }
+  int32_t o[32];
+  const float zpf = (float)p.y_zp;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    int32_t acc = (int32_t)v[j] + sb[c0 + j] - xz * sw[c0 + j];
+    if (p.mode == EPI_REQUANT) acc = requant_exact(acc, sf[c0 + j], zpf, p.y_zp, p.lo, p.hi);
+    o[j] = acc;
+  }
+  if (esz == 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j] = ((uint32_t)o[4 * j] & 0xffu) | (((uint32_t)o[4 * j + 1] & 0xffu) << 8) | (((uint32_t)o[4 * j + 2] & 0xffu) << 16) |
+             (((uint32_t)o[4 * j + 3] & 0xffu) << 24);
+  } else if (esz == 2) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = ((uint32_t)o[2 * j] & 0xffffu) | (((uint32_t)o[2 * j + 1] & 0xffffu) << 16);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = (uint32_t)o[j];
+  }
+}
+
+// Direct store of a packed 32-channel run (ragged channel counts, unaligned rows).
+__device__ __forceinline__ void store_direct(const uint32_t (&w)[32], uint8_t* optr, size_t esz, int valid) {
+  const int bytes = 32 * (int)esz;
+  if (valid == 32 && ((uintptr_t)optr & 15) == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j * 16 < bytes) *(uint4*)(optr + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    return;
+  }
+  if (esz == 4) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) ((uint32_t*)optr)[j] = w[j];
+  } else if (esz == 2) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) ((uint16_t*)optr)[j] = (uint16_t)(w[j >> 1] >> (16 * (j & 1)));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) optr[j] = (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
+  }
+}
+
+// Staged store: the run goes into this warp's shared-memory staging rows in the swizzled order a
+// TMA store with the matching swizzle mode expects (16-byte chunk index XOR row-derived bits), so
+// that the tile leaves the SM as full-line writes instead of 32 scattered 16-byte pieces.
+__device__ __forceinline__ void store_staged(const uint32_t (&w)[32], uint32_t stage_addr, int row, int pitch, int byte_off, int bytes) {
+  const uint32_t xor_bits = ((uint32_t)(row * pitch) >> 7) & (uint32_t)(pitch / 16 - 1);
+  const uint32_t row_addr = stage_addr + (uint32_t)(row * pitch);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (j * 16 < bytes) {
+      const uint32_t chunk = ((uint32_t)(byte_off >> 4) + (uint32_t)j) ^ xor_bits;
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + chunk * 16u), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]),
+                   "r"(w[4 * j + 3])
+                   : "memory");
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+
 template <int BN, int KIND>
-__global__ void __launch_bounds__(NUM_THREADS) umma_conv_kernel(const __grid_constant__ KParams p) {
+__global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[MAX_STAGES];
   __shared__ __align__(8) uint64_t bar_empty[MAX_STAGES];
-  __shared__ __align__(8) uint64_t bar_acc;
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float s_f[2][BN];    // [0] bias_f or combined, [1] unused / combined
-  __shared__ int32_t s_i[2][BN];  // [0] bias_i, [1] wsum
+  // per epilogue warp: [0] bias_f or combined (f32), [1] bias_i, [2] wsum
+  __shared__ uint32_t s_par[4][3][BN];
+  // per epilogue warp: two staging buffers of 32 rows x up to 128 bytes for the TMA stores
+  __shared__ __align__(1024) uint8_t s_stage[4][2][32 * 128];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x % p.n_tiles, tile_m = blockIdx.x / p.n_tiles;
-  const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
   const int swz = p.swizzle_bytes;
   const uint32_t a_bytes = (uint32_t)BLOCK_M * swz, b_bytes = (uint32_t)BN * swz;
   const uint32_t stage_bytes = a_bytes + b_bytes;
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int k_iters = p.taps * p.cblocks;
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -197,23 +329,16 @@ __global__ void __launch_bounds__(NUM_THREADS) umma_conv_kernel(const __grid_con
       mbar_init(smem_u32(&bar_full[i]), 1);
       mbar_init(smem_u32(&bar_empty[i]), 1);
     }
-    mbar_init(smem_u32(&bar_acc), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bar_acc_full[i]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[i]), 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  if (warp >= 2) {
-    // stage the per-channel epilogue parameters of this CTA's channel range
-    for (int i = threadIdx.x - 64; i < BN; i += 128) {
-      int oc = oc0 + i;
-      bool ok = oc < p.OC;
-      s_f[0][i] = (p.mode == EPI_F32) ? ((ok && p.bias_f) ? p.bias_f[oc] : 0.f) : ((ok && p.combined) ? p.combined[oc] : 0.f);
-      s_i[0][i] = (ok && p.bias_i) ? p.bias_i[oc] : 0;
-      s_i[1][i] = (ok && p.wsum) ? p.wsum[oc] : 0;
-    }
   }
   tc_fence_before();
   __syncthreads();
@@ -224,144 +349,199 @@ __global__ void __launch_bounds__(NUM_THREADS) umma_conv_kernel(const __grid_con
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer ----------------
-      int q0 = 0, p0 = 0, n0 = 0;
-      if (p.a_im2col) {
-        q0 = m0 % p.Q;
-        int t = m0 / p.Q;
-        p0 = t % p.P;
-        n0 = t / p.P;
-      }
-      const int w_base = q0 * p.sw - p.pl, h_base = p0 * p.sh - p.pt;
-      for (int it = 0; it < k_iters; ++it) {
-        int stage = it % p.stages;
-        uint32_t phase = (uint32_t)(it / p.stages) & 1u;
-        if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp)) {
-          if (!*abortp) {
-            *abortp = 1;
-            atomicExch(p.err_flag, 1);
-          }
-          break;
-        }
-        uint32_t full = smem_u32(&bar_full[stage]);
-        mbar_expect_tx(full, stage_bytes);
-        uint32_t a_dst = tiles_base + (uint32_t)stage * stage_bytes, b_dst = a_dst + a_bytes;
-        int tap = it / p.cblocks, cb = it - tap * p.cblocks;
-        int c_off = cb * p.cb_elems;
+      uint32_t git = 0;  // k-iterations issued so far, across tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
+        const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
+        int q0 = 0, p0 = 0, n0 = 0;
         if (p.a_im2col) {
-          int r = tap / p.S, s = tap - r * p.S;
-          tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(s * p.dw), (uint16_t)(r * p.dh));
-        } else {
-          tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+          q0 = m0 % p.Q;
+          int tt = m0 / p.Q;
+          p0 = tt % p.P;
+          n0 = tt / p.P;
         }
-        tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
+        const int w_base = q0 * p.sw - p.pl, h_base = p0 * p.sh - p.pt;
+        int tap = 0, cb = 0;
+        for (int it = 0; it < k_iters; ++it, ++git) {
+          const uint32_t stage = git % (uint32_t)p.stages;
+          const uint32_t phase = (git / (uint32_t)p.stages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp)) {
+            if (!*abortp) {
+              *abortp = 1;
+              atomicExch(p.err_flag, 1);
+            }
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          mbar_expect_tx(full, stage_bytes);
+          const uint32_t a_dst = tiles_base + stage * stage_bytes, b_dst = a_dst + a_bytes;
+          const int c_off = cb * p.cb_elems;
+          if (p.a_im2col) {
+            const int r = tap / p.S, s = tap - r * p.S;
+            tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(s * p.dw), (uint16_t)(r * p.dh));
+          } else {
+            tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+          }
+          tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
+          if (++cb == p.cblocks) {
+            cb = 0;
+            ++tap;
+          }
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer ----------------
       const int mmas = swz / 32;
+      uint32_t git = 0;
+      uint32_t local = 0;
       bool ok = true;
-      for (int it = 0; it < k_iters && ok; ++it) {
-        int stage = it % p.stages;
-        uint32_t phase = (uint32_t)(it / p.stages) & 1u;
-        if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp)) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const uint32_t buf = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        // the epilogue must have drained this accumulator (free on the first two tiles)
+        if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp)) {
           if (!*abortp) {
             *abortp = 1;
-            atomicExch(p.err_flag, 2);
+            atomicExch(p.err_flag, 4);
           }
-          ok = false;
           break;
         }
         tc_fence_after();
-        uint32_t a_addr = tiles_base + (uint32_t)stage * stage_bytes, b_addr = a_addr + a_bytes;
-        uint64_t da = make_smem_desc(a_addr, swz), db = make_smem_desc(b_addr, swz);
-        for (int kk = 0; kk < mmas; ++kk) {
-          // 32 bytes of K per MMA: advance the (16-byte granular) start address by 2
-          tc_mma<KIND>(tmem_base, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), p.idesc, (it > 0 || kk > 0) ? 1u : 0u);
+        const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+        for (int it = 0; it < k_iters; ++it, ++git) {
+          const uint32_t stage = git % (uint32_t)p.stages;
+          const uint32_t phase = (git / (uint32_t)p.stages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp)) {
+            if (!*abortp) {
+              *abortp = 1;
+              atomicExch(p.err_flag, 2);
+            }
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = tiles_base + stage * stage_bytes, b_addr = a_addr + a_bytes;
+          const uint64_t da = make_smem_desc(a_addr, swz), db = make_smem_desc(b_addr, swz);
+          for (int kk = 0; kk < mmas; ++kk) {
+            // 32 bytes of K per MMA: advance the (16-byte granular) start address by 2
+            tc_mma<KIND>(tmem_d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), p.idesc, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
         }
-        tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
+        if (ok) tc_commit(smem_u32(&bar_acc_full[buf]));  // accumulator complete
       }
-      if (ok) tc_commit(smem_u32(&bar_acc));  // accumulator complete
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
     const int quarter = warp & 3;
-    bool ok = mbar_wait(smem_u32(&bar_acc), 0u, abortp);
-    if (!ok && !*abortp) {
-      *abortp = 1;
-      atomicExch(p.err_flag, 3);
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      tc_fence_after();
-      const int row = quarter * 32 + lane;
-      const long long m = (long long)m0 + row;
-      const bool row_ok = m < p.M;
-      int xz = 0;
-      if (p.x_zp_dev) xz = __float2int_rn(*p.x_zp_dev);
-      const size_t esz = (p.out_dt == (int)DT::F32 || p.out_dt == (int)DT::I32) ? 4 : (p.out_dt == (int)DT::I16 ? 2 : 1);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (oc0 + c0 >= p.OC) break;  // uniform across the CTA
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-        if (!row_ok) continue;
-        const int valid = min(32, p.OC - (oc0 + c0));
-        uint8_t* optr = (uint8_t*)p.out + ((size_t)m * p.OC + oc0 + c0) * esz;
-        if (p.mode == EPI_F32) {
-          float o[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float f = __uint_as_float(v[j]) + s_f[0][c0 + j];
-            if (p.act == 1) f = fmaxf(f, 0.f);
-            else if (p.act == 2) f = fminf(fmaxf(f, p.clip_lo), p.clip_hi);
-            if (p.round_tf32) f = round_tf32(f);
-            o[j] = f;
-          }
-          if (valid == 32 && ((uintptr_t)optr & 15) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) *(float4*)(optr + j * 4) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-          } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) ((float*)optr)[j] = o[j];
-          }
-        } else {
-          int32_t o[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            int32_t acc = (int32_t)v[j] + s_i[0][c0 + j] - xz * s_i[1][c0 + j];
-            if (p.mode == EPI_REQUANT) {
-              // f64 product, f64 add (each rounded once), round-half-even, saturate
-              double scaled = __dadd_rn(__dmul_rn((double)acc, (double)s_f[0][c0 + j]), (double)p.y_zp);
-              int q = __double2int_rn(scaled);
-              acc = min(max(q, p.lo), p.hi);
-            }
-            o[j] = acc;
-          }
-          if (esz == 1) {
-            uint32_t w[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              w[j] = ((uint32_t)o[4 * j] & 0xffu) | (((uint32_t)o[4 * j + 1] & 0xffu) << 8) | (((uint32_t)o[4 * j + 2] & 0xffu) << 16) |
-                     (((uint32_t)o[4 * j + 3] & 0xffu) << 24);
-            if (valid == 32 && ((uintptr_t)optr & 15) == 0) {
-              *(uint4*)(optr) = make_uint4(w[0], w[1], w[2], w[3]);
-              *(uint4*)(optr + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-            } else {
-              _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) optr[j] = (uint8_t)(o[j] & 0xff);
-            }
-          } else if (esz == 4) {
-            if (valid == 32 && ((uintptr_t)optr & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *(int4*)(optr + j * 4) = make_int4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-            } else {
-              _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) ((int32_t*)optr)[j] = o[j];
-            }
-          } else {
-            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < valid) ((int16_t*)optr)[j] = (int16_t)o[j];
-          }
+    const int ew = warp - 2;
+    float* sf = reinterpret_cast<float*>(s_par[ew][0]);
+    int32_t* sb = reinterpret_cast<int32_t*>(s_par[ew][1]);
+    int32_t* sw = reinterpret_cast<int32_t*>(s_par[ew][2]);
+    int xz = 0;
+    if (p.x_zp_dev) xz = __float2int_rn(*p.x_zp_dev);
+    const size_t esz = (p.out_dt == (int)DT::F32 || p.out_dt == (int)DT::I32) ? 4 : (p.out_dt == (int)DT::I16 ? 2 : 1);
+    const int chunk_bytes = 32 * (int)esz;
+    const int pitch = p.out_row_bytes;                 // staged row length: 32, 64 or 128 bytes
+    const int chunks_per_group = p.out_tma ? pitch / chunk_bytes : 1;
+    const uint32_t stage0 = smem_u32(&s_stage[ew][0][0]);
+    uint32_t groups = 0;  // TMA store groups issued by this warp
+    int staged_tile_n = -1;
+    uint32_t local = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
+      const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
+      if (tile_n != staged_tile_n) {
+        // each warp keeps its own copy of the per-channel parameters: no cross-warp barrier
+        __syncwarp();
+        for (int i = lane; i < BN; i += 32) {
+          const int oc = oc0 + i;
+          const bool okc = oc < p.OC;
+          sf[i] = (p.mode == EPI_F32) ? ((okc && p.bias_f) ? p.bias_f[oc] : 0.f) : ((okc && p.combined) ? p.combined[oc] : 0.f);
+          sb[i] = (okc && p.bias_i) ? p.bias_i[oc] : 0;
+          sw[i] = (okc && p.wsum) ? p.wsum[oc] : 0;
         }
+        __syncwarp();
+        staged_tile_n = tile_n;
       }
+      const uint32_t buf = local & 1u;
+      bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local >> 1) & 1u, abortp);
+      if (!ok && !*abortp) {
+        *abortp = 1;
+        atomicExch(p.err_flag, 3);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row_in_tile = quarter * 32 + lane;
+      const long long m = (long long)m0 + row_in_tile;
+      const bool row_ok = m < p.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN;
+      const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;  // uniform across the CTA
+      uint32_t va[32], vb[32], w[32];
+      if (p.dbg == 1) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+        continue;
+      }
+      tmem_ld32_nowait(taddr, va);
+      tmem_ld_wait();
+#pragma unroll 1
+      for (int ch = 0; ch < n_chunks; ++ch) {
+        // software pipeline: the next chunk's TMEM read is in flight while this one is processed
+        const bool odd = ch & 1;
+        if (ch + 1 < n_chunks) {
+          if (odd) tmem_ld32_nowait(taddr + (uint32_t)(ch + 1) * 32u, va);
+          else tmem_ld32_nowait(taddr + (uint32_t)(ch + 1) * 32u, vb);
+        }
+        const int c0 = ch * 32;
+        if (p.dbg == 2) {
+          if (va[0] == 0x7fc12345u && vb[3] == 0x7fc12345u) atomicExch(p.err_flag, 9);
+          tmem_ld_wait();
+          continue;
+        }
+        if (odd) epilogue_math(p, vb, sf, sb, sw, xz, c0, esz, w);
+        else epilogue_math(p, va, sf, sb, sw, xz, c0, esz, w);
+        if (p.dbg == 3) {
+          if (w[0] == 0x7fc12345u && w[5] == 0x7fc12345u && w[31] == 0x7fc12345u) atomicExch(p.err_flag, 9);
+          tmem_ld_wait();
+          continue;
+        }
+        if (p.out_tma) {
+          const int in_group = ch % chunks_per_group;
+          const uint32_t sbuf = stage0 + (groups & 1u) * (uint32_t)(32 * 128);
+          if (in_group == 0) {
+            // the staging buffer about to be rewritten must have been read by its previous store
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+          }
+          store_staged(w, sbuf, lane, pitch, in_group * chunk_bytes, chunk_bytes);
+          if (in_group == chunks_per_group - 1 || ch == n_chunks - 1) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              const int col = oc0 + (ch - in_group) * 32;
+              tma_store_2d(&p.tmO, sbuf, col, m0 + quarter * 32);
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            ++groups;
+          }
+        } else if (row_ok) {
+          store_direct(w, (uint8_t*)p.out + ((size_t)m * p.OC + oc0 + c0) * esz, esz, min(32, p.OC - (oc0 + c0)));
+        }
+        tmem_ld_wait();
+      }
+      // hand the accumulator back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
     }
+    if (p.out_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ---------------- teardown ----------------
@@ -402,6 +582,16 @@ void load_encoders() {
       g_encode_im2col = (EncodeIm2colFn)fn;
     (void)cudaGetLastError();
   });
+}
+
+int sm_count() {
+  static int cached = 0;
+  if (cached == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) cached = n;
+    else cached = 148;
+  }
+  return cached;
 }
 
 CUtensorMapSwizzle swizzle_enum(int bytes) {
@@ -494,9 +684,15 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   }
   if (e.x_zp_rows || e.n_w_zp > 0) return no("per-row or weight zero points need the direct kernel");
 
-  int bn = cs.OC <= 32 ? 32 : (cs.OC <= 64 ? 64 : 128);
-  if (kind == 0 && bn == 128 && cs.OC >= 256 && M >= 148LL * 128 * 4) bn = 256;
-  const int64_t m_tiles = ceil_div(M, BLOCK_M), n_tiles = ceil_div(cs.OC, bn);
+  // Tile width: as wide as the channel count allows (fewer re-reads of the activation tile), but
+  // narrowed while the tile count cannot occupy every SM; GEMV-like problems (one row tile) may go
+  // down to 32 columns so that the weight stream is spread over many SMs.
+  const int sms = sm_count();
+  const int64_t m_tiles = ceil_div(M, BLOCK_M);
+  int bn = cs.OC <= 32 ? 32 : (cs.OC <= 64 ? 64 : (cs.OC <= 128 ? 128 : 256));
+  const int bn_floor = m_tiles <= 2 ? 32 : 64;
+  while (bn > bn_floor && m_tiles * ceil_div(cs.OC, bn) < sms) bn /= 2;
+  const int64_t n_tiles = ceil_div(cs.OC, bn);
   if (m_tiles * n_tiles > 0x7fffffffLL) return no("grid too large");
 
   UmmaPlan* pl = new UmmaPlan();
@@ -547,6 +743,32 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
       return no("weight tensor map rejected by the driver");
     }
   }
+  {
+    // output tile store through TMA when rows are 16-byte granular
+    const size_t oes = dt_size(e.out_dt);
+    const size_t row_bytes = std::min<size_t>(128, (size_t)bn * oes);
+    kp.out_tma = 0;
+    kp.out_row_bytes = (int)row_bytes;
+    if (((size_t)cs.OC * oes) % 16 == 0 && ((uintptr_t)out & 15) == 0 && row_bytes >= 32 && (row_bytes & (row_bytes - 1)) == 0) {
+      CUtensorMapDataType odt = oes == 4 ? (e.out_dt == DT::F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_INT32)
+                                         : (oes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+      cuuint64_t gdim[2] = {(cuuint64_t)cs.OC, (cuuint64_t)M};
+      cuuint64_t gstr[1] = {(cuuint64_t)cs.OC * oes};
+      cuuint32_t box[2] = {(cuuint32_t)(row_bytes / oes), 32};
+      cuuint32_t estr[2] = {1, 1};
+      CUresult ro = g_encode_tiled(&kp.tmO, odt, 2, out, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum((int)row_bytes),
+                                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (ro == CUDA_SUCCESS) kp.out_tma = 1;
+    }
+  }
+  {
+    const char* dbg = std::getenv("OXB200_UMMA_DEBUG");
+    kp.dbg = dbg ? std::atoi(dbg) : 0;
+    if (dbg && std::atoi(dbg) == 4) {
+      kp.dbg = 0;
+      kp.out_tma = 0;
+    }
+  }
   kp.M = (int)M;
   kp.OC = cs.OC;
   kp.P = cs.P;
@@ -563,14 +785,14 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.cb_elems = cb;
   kp.swizzle_bytes = swz;
   kp.n_tiles = (int)n_tiles;
+  kp.m_tiles = (int)m_tiles;
   kp.idesc = make_idesc(kind, x_dt == DT::I8, w_dt == DT::I8, bn);
   const size_t stage_bytes = (size_t)(BLOCK_M + bn) * swz;
-  const size_t budget = 96 * 1024;  // two CTAs per SM overlap one tile's epilogue with another's main loop
+  // one persistent CTA per SM: the ring may use most of the 227 KB and runs on across tiles
+  const size_t budget = 160 * 1024;
   int stages = (int)(budget / stage_bytes);
-  const int k_iters = kp.taps * kp.cblocks;
-  if (stages > k_iters) stages = k_iters;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
-  if (stages < 2) stages = k_iters < 2 ? 1 : 2;
+  if (stages < 2) stages = 2;
   kp.stages = stages;
   kp.mode = e.mode;
   kp.bias_f = e.bias_f;
@@ -590,7 +812,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.err_flag = nullptr;
   pl->bn = bn;
   pl->kind = kind;
-  pl->grid = (int)(m_tiles * n_tiles);
+  pl->grid = (int)std::min<int64_t>(m_tiles * n_tiles, sms);
   pl->smem = (size_t)stages * stage_bytes + 1024;
   snprintf(pl->desc, sizeof pl->desc, "umma_%s M=%lld N=%d K=%lld tile=128x%dx%dB stages=%d %s", kind == 0 ? "i8" : "tf32", (long long)M, cs.OC,
            (long long)cs.K(), bn, swz, stages, gemm_like ? "tiled" : "im2col");

@@ -96,12 +96,15 @@ void* Context::resident_form(const std::string& name, const std::string& form, s
   void* dev = alloc_device(bytes);
   OXB_CUDA(cudaMemcpyAsync(dev, host.data(), bytes, cudaMemcpyHostToDevice, stream_));
   OXB_CUDA(cudaStreamSynchronize(stream_));
-  counters.weight_uploads += 1;
   if (cacheable) {
+    counters.weight_uploads += 1;
     forms_[key] = DeviceBuffer{dev, bytes};
     counters.weight_bytes_resident += bytes;
     resident_names_.insert(name);
   } else {
+    // an operand of a one-node dispatch: activation traffic, not a resident weight
+    counters.uploads += 1;
+    counters.upload_bytes += bytes;
     temp_forms_.push_back(dev);
   }
   return dev;
