@@ -46,6 +46,19 @@ void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scal
 // device); `scratch` is 2 floats used for the min/max reduction.
 void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s);
 
+// The residual join of a quantised network in one pass:
+//   y = Q( relu?( DQ(a) + DQ(b) ) )  with per-tensor parameters,
+// performing the same f32 operations in the same order as the separate DequantizeLinear, Add,
+// Relu and QuantizeLinear nodes (subtract, multiply, add, max, divide, round-half-even, add,
+// clamp; none fused), so the lanes are bit-identical while the f32 intermediates never reach
+// memory: 3 bytes of traffic per element instead of 27.  a, b and y are 8-bit tensors of the
+// same shape and memory order.
+struct ResidualParams {
+  float a_scale, a_zp, b_scale, b_zp, y_scale, y_zp, lo, hi;
+  int relu;
+};
+void residual_requant(const void* a, DT a_dt, const void* b, DT b_dt, void* y, DT y_dt, int64_t n, const ResidualParams& rp, cudaStream_t s);
+
 // ---- element-wise -----------------------------------------------------------------------
 enum BinOp { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_DIV = 3 };
 enum UnOp { UN_RELU = 0, UN_TANH = 1, UN_SIGMOID = 2, UN_SILU = 3, UN_COPY = 4 };
@@ -78,6 +91,13 @@ void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, 
 // Copies `x` into the channel range [c_off, c_off + x.C) of `y` (Concat on the channel axis)
 // or, axis 0/2/3, the matching range of that axis.
 void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s);
+
+// Space-to-depth packing for stride-2 convolutions over very few channels (the 3-channel
+// stem): dst[n][y][x][(bh*2+bw)*C + c] = src[n][c][2y+bh][2x+bw] - sub, channels padded with
+// zeros up to c_pad, so that the convolution becomes a stride-1 one over 4*C channels whose
+// rows are long enough for the tensor-core path.  src may be channels-first f32 lanes (a graph
+// input) or a channels-last activation; dst is channels-last [N, H/2, W/2, c_pad].
+void s2d_pack(const TensorRef& src, void* dst, DT dst_dt, int c_pad, int sub, cudaStream_t s);
 
 // ---- contractions -----------------------------------------------------------------------
 struct ConvShape {

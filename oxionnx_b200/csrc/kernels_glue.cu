@@ -344,6 +344,45 @@ __global__ void max_pool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y,
   }
 }
 
+// 16 bytes of channels per thread: four floats, or sixteen 8-bit lanes reduced with the SIMD
+// byte-max instructions.  KIND 0 = f32, 1 = u8, 2 = i8.
+template <int KIND>
+__global__ void max_pool_nhwc_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, Dims4 xd, PoolShape ps, int64_t cvec, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t c = o % cvec;
+    int64_t t = o / cvec;
+    int64_t q = t % ps.Q;
+    t /= ps.Q;
+    int64_t p = t % ps.P;
+    int64_t n = t / ps.P;
+    uint4 best;
+    if (KIND == 0) best = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);  // -inf
+    else if (KIND == 1) best = make_uint4(0u, 0u, 0u, 0u);
+    else best = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+    for (int r = 0; r < ps.kh; ++r) {
+      int64_t ih = p * ps.sh + (int64_t)r * ps.dh - ps.pt;
+      if (ih < 0 || ih >= xd.H) continue;
+      for (int s = 0; s < ps.kw; ++s) {
+        int64_t iw = q * ps.sw + (int64_t)s * ps.dw - ps.pl;
+        if (iw < 0 || iw >= xd.W) continue;
+        const uint4 v = x[((n * xd.H + ih) * xd.W + iw) * cvec + c];
+        if (KIND == 0) {
+          // `v > best` keeps the reference's behaviour for NaN lanes (a NaN never replaces the maximum)
+          if (__uint_as_float(v.x) > __uint_as_float(best.x)) best.x = v.x;
+          if (__uint_as_float(v.y) > __uint_as_float(best.y)) best.y = v.y;
+          if (__uint_as_float(v.z) > __uint_as_float(best.z)) best.z = v.z;
+          if (__uint_as_float(v.w) > __uint_as_float(best.w)) best.w = v.w;
+        } else if (KIND == 1) {
+          best = make_uint4(__vmaxu4(best.x, v.x), __vmaxu4(best.y, v.y), __vmaxu4(best.z, v.z), __vmaxu4(best.w, v.w));
+        } else {
+          best = make_uint4(__vmaxs4(best.x, v.x), __vmaxs4(best.y, v.y), __vmaxs4(best.z, v.z), __vmaxs4(best.w, v.w));
+        }
+      }
+    }
+    y[o] = best;
+  }
+}
+
 // One thread per (n, c): the sum runs over the plane in (h, w) order exactly like the
 // reference loop; consecutive threads read consecutive channels, so loads are coalesced.
 __global__ void global_avg_pool_nhwc_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 d, int rtf32) {
@@ -493,6 +532,88 @@ __global__ void concat_kernel(const void* x, void* y, DT dt, Layout L, Dims4 xd,
   }
 }
 
+__device__ __forceinline__ float lane8(uint32_t word, int e, bool is_signed) {
+  uint32_t b = (word >> (8 * e)) & 0xffu;
+  return is_signed ? (float)(int)(int8_t)b : (float)b;
+}
+
+__device__ __forceinline__ uint32_t residual_one(float av, float bv, const ResidualParams& rp) {
+  float va = __fmul_rn(__fsub_rn(av, rp.a_zp), rp.a_scale);
+  float vb = __fmul_rn(__fsub_rn(bv, rp.b_zp), rp.b_scale);
+  float sum = __fadd_rn(va, vb);
+  if (rp.relu) sum = fmaxf(sum, 0.f);
+  float q = __fadd_rn(rintf(__fdiv_rn(sum, rp.y_scale)), rp.y_zp);
+  q = fminf(fmaxf(q, rp.lo), rp.hi);
+  return (uint32_t)__float2int_rn(q) & 0xffu;
+}
+
+// 16 lanes per thread: two 16-byte loads, one 16-byte store.
+__global__ void residual_requant_kernel(const uint4* __restrict__ a, bool a_signed, const uint4* __restrict__ b, bool b_signed, uint4* __restrict__ y,
+                                        int64_t n16, ResidualParams rp) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 av = a[i], bv = b[i];
+    const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) w |= residual_one(lane8(aw[j], e, a_signed), lane8(bw[j], e, b_signed), rp) << (8 * e);
+      out[j] = w;
+    }
+    y[i] = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
+__global__ void residual_requant_tail_kernel(const uint8_t* a, bool a_signed, const uint8_t* b, bool b_signed, uint8_t* y, int64_t begin, int64_t n,
+                                             ResidualParams rp) {
+  for (int64_t i = begin + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float av = a_signed ? (float)(int8_t)a[i] : (float)a[i];
+    float bv = b_signed ? (float)(int8_t)b[i] : (float)b[i];
+    y[i] = (uint8_t)residual_one(av, bv, rp);
+  }
+}
+
+// Four consecutive packed channels per thread, written as one 4-byte or 16-byte store.
+__global__ void s2d_pack_kernel(const void* src, DT sdt, Layout sl, Dims4 d, void* dst, DT ddt, int c_pad, int sub, int64_t total4) {
+  const int64_t H2 = d.H / 2, W2 = d.W / 2;
+  const int c4n = c_pad / 4;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total4; o += (int64_t)gridDim.x * blockDim.x) {
+    const int cq = (int)(o % c4n);
+    int64_t t = o / c4n;
+    const int64_t x = t % W2;
+    t /= W2;
+    const int64_t y = t % H2;
+    const int64_t n = t / H2;
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int cp = cq * 4 + e;
+      v[e] = 0.f;
+      if (cp < 4 * d.C) {
+        const int blk = cp / (int)d.C;
+        Coord q;
+        q.n = n;
+        q.c = cp - blk * (int)d.C;
+        q.h = 2 * y + (blk >> 1);
+        q.w = 2 * x + (blk & 1);
+        v[e] = load_as_f32(src, sdt, encode(q, sl, d)) - (float)sub;
+      }
+    }
+    if (ddt == DT::F32) {
+      ((float4*)dst)[o] = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      uint32_t w = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = ddt == DT::U8 ? 0.f : -128.f, hi = ddt == DT::U8 ? 255.f : 127.f;
+        w |= ((uint32_t)__float2int_rn(fminf(fmaxf(v[e], lo), hi)) & 0xffu) << (8 * e);
+      }
+      ((uint32_t*)dst)[o] = w;
+    }
+  }
+}
+
 }  // namespace
 
 // =========================================================================================
@@ -527,6 +648,24 @@ void convert(const TensorRef& src, const TensorRef& dst, cudaStream_t s) {
     }
   }
   convert_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, dst.ptr, dst.dt, dst.layout, d, total);
+}
+
+void residual_requant(const void* a, DT a_dt, const void* b, DT b_dt, void* y, DT y_dt, int64_t n, const ResidualParams& rp, cudaStream_t s) {
+  (void)y_dt;
+  if (n == 0) return;
+  const bool as = a_dt == DT::I8, bs = b_dt == DT::I8;
+  int64_t n16 = 0;
+  if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) & 15) == 0) n16 = n / 16;
+  if (n16 > 0) residual_requant_kernel<<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
+  if (n16 * 16 < n)
+    residual_requant_tail_kernel<<<grid_for(n - n16 * 16), kThreads, 0, s>>>((const uint8_t*)a, as, (const uint8_t*)b, bs, (uint8_t*)y, n16 * 16, n, rp);
+}
+
+void s2d_pack(const TensorRef& src, void* dst, DT dst_dt, int c_pad, int sub, cudaStream_t s) {
+  int64_t total4 = src.d.N * (src.d.H / 2) * (src.d.W / 2) * (c_pad / 4);
+  if (total4 == 0) return;
+  if (!(dst_dt == DT::F32 || dst_dt == DT::U8 || dst_dt == DT::I8)) OXB_FAIL("s2d_pack: unsupported storage type");
+  s2d_pack_kernel<<<grid_for(total4), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, c_pad, sub, total4);
 }
 
 void quantize_linear(const TensorRef& x, const TensorRef& y, const float* scale, int64_t n_scale, const float* zp, int64_t n_zp, float lo,
@@ -599,6 +738,15 @@ void prelu(const TensorRef& x, const TensorRef& y, const float* slope, int64_t n
 void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaStream_t s) {
   int64_t total = y.d.numel();
   if (total == 0) return;
+  const int64_t per = x.dt == DT::F32 ? 4 : 16;
+  if (x.d.C % per == 0 && (((uintptr_t)x.ptr | (uintptr_t)y.ptr) & 15) == 0 && (x.dt == DT::F32 || x.dt == DT::U8 || x.dt == DT::I8)) {
+    const int64_t cvec = x.d.C / per, tv = total / per;
+    const int gv = grid_for(tv);
+    if (x.dt == DT::F32) max_pool_nhwc_vec_kernel<0><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, ps, cvec, tv);
+    else if (x.dt == DT::U8) max_pool_nhwc_vec_kernel<1><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, ps, cvec, tv);
+    else max_pool_nhwc_vec_kernel<2><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, ps, cvec, tv);
+    return;
+  }
   int g = grid_for(total);
   if (x.dt == DT::F32) max_pool_nhwc_kernel<float><<<g, kThreads, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, ps, total, -INFINITY);
   else if (x.dt == DT::U8) max_pool_nhwc_kernel<uint8_t><<<g, kThreads, 0, s>>>((const uint8_t*)x.ptr, (uint8_t*)y.ptr, x.d, ps, total, 0);

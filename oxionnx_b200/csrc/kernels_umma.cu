@@ -24,6 +24,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -57,6 +58,7 @@ struct alignas(64) KParams {
   uint32_t idesc;
   // epilogue
   int mode;
+  int variant;  // which epilogue_math instantiation runs
   const float* bias_f;
   int act;
   float clip_lo, clip_hi;
@@ -84,7 +86,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -195,50 +197,86 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// ONNX requantisation of one accumulator, bit-identical to the reference's
-//   clamp(round_half_even(f64(acc) * f64(combined) + f64(zero_point)), lo, hi).
-// The FP64 pipe of this part is far too narrow for an epilogue, so the value is first formed
-// in f32: a = (float)acc, r = fma(a, c, zp) with |r - exact| <= (|acc*c| + |r|) * 2^-24.  For
-// |r| <= 1024 that is below 2^-12, so whenever r is further than 2^-10 from every half-integer
-// the f32 and the f64 values round to the same integer; for |r| > 1024 both saturate on the
-// same side.  Only the few lanes that land within 2^-10 of a tie take the exact f64 path.
-__device__ __forceinline__ int requant_exact(int32_t acc, float c, float zpf, int zp, int lo, int hi) {
-  const float r = fmaf(__int2float_rn(acc), c, zpf);
-  const float q = rintf(r);
-  const bool near_tie = fabsf(r - q) > 0.4990234375f && fabsf(r) <= 1024.0f;
-  int out;
-  if (!near_tie) {
-    out = __float2int_rn(r);
-  } else {
-    const double scaled = __dadd_rn(__dmul_rn((double)acc, (double)c), (double)zp);
-    out = __double2int_rn(scaled);
+// ---- fused epilogue math ------------------------------------------------------------------
+// One variant per (mode, activation, rounding) combination, chosen once per chunk, so that
+// the 32 per-channel computations inside are straight-line code with full instruction-level
+// parallelism (one epilogue warp per scheduler has nothing else to hide latency with).
+// Per-channel parameters are read with 16-byte read-only loads; the host pads every
+// parameter vector to a multiple of 256 channels, so no bounds checks are needed here.
+enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9 };
+
+template <int ACT, int RT>
+__device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias, uint32_t (&w)[32]) {
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const float4 b = __ldg(reinterpret_cast<const float4*>(bias) + j4);
+    const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float f = __uint_as_float(v[4 * j4 + e]) + bb[e];
+      if (ACT == 1) f = fmaxf(f, 0.f);
+      if (ACT == 2) f = fminf(fmaxf(f, p.clip_lo), p.clip_hi);
+      if (RT) f = round_tf32(f);
+      w[4 * j4 + e] = __float_as_uint(f);
+    }
   }
-  return min(max(out, lo), hi);
 }
 
-// Fused epilogue of one 32-channel run of one output pixel: bias / zero-point correction,
-// requantisation or activation, packed into 32-bit words (8 for 8-bit outputs, 16 for 16-bit,
-// 32 for 32-bit).
-__device__ __forceinline__ void epilogue_math(const KParams& p, const uint32_t (&v)[32], const float* sf, const int32_t* sb, const int32_t* sw, int xz,
-                                              int c0, size_t esz, uint32_t (&w)[32]) {
-  if (p.mode == EPI_F32) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float f = __uint_as_float(v[j]) + sf[c0 + j];
-      if (p.act == 1) f = fmaxf(f, 0.f);
-      else if (p.act == 2) f = fminf(fmaxf(f, p.clip_lo), p.clip_hi);
-      if (p.round_tf32) f = round_tf32(f);
-      w[j] = __float_as_uint(f);
-    }
-    return;
-  }
+// ONNX requantisation, bit-identical to the reference's
+//   clamp(round_half_even(f64(acc) * f64(combined) + f64(zero_point)), lo, hi)
+// without touching the (very narrow) FP64 pipe on the common path.  The value is formed in f32:
+// a = (float)acc, r = fma(a, c, zp).  With |zp| <= 255, |r - exact| <= (2|r| + 255) * 2^-24 =: E.
+// If r is further than T = (2|r| + 256) * 2^-23 >= 2E from every half-integer, the f32 value, the
+// exact value and the reference's f64 value (within 2^-40 of exact) all round to the same integer.
+// For |r| >= 1024 all three saturate on the same side.  Lanes within T of a tie (about one in ten
+// thousand) are redone with the reference's own f64 operations in a second pass.
+template <bool REQ, bool DYN>
+__device__ __forceinline__ void math_int(const KParams& p, const uint32_t (&v)[32], const int32_t* __restrict__ bias, const int32_t* __restrict__ wsum,
+                                         const float* __restrict__ comb, int xz, size_t esz, uint32_t (&w)[32]) {
   int32_t o[32];
+  uint32_t slow = 0;
   const float zpf = (float)p.y_zp;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    int32_t acc = (int32_t)v[j] + sb[c0 + j] - xz * sw[c0 + j];
-    if (p.mode == EPI_REQUANT) acc = requant_exact(acc, sf[c0 + j], zpf, p.y_zp, p.lo, p.hi);
-    o[j] = acc;
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const int4 b = __ldg(reinterpret_cast<const int4*>(bias) + j4);
+    const int bb[4] = {b.x, b.y, b.z, b.w};
+    int ss[4] = {0, 0, 0, 0};
+    if (DYN) {
+      const int4 sv = __ldg(reinterpret_cast<const int4*>(wsum) + j4);
+      ss[0] = sv.x, ss[1] = sv.y, ss[2] = sv.z, ss[3] = sv.w;
+    }
+    float cc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (REQ) {
+      const float4 c = __ldg(reinterpret_cast<const float4*>(comb) + j4);
+      cc[0] = c.x, cc[1] = c.y, cc[2] = c.z, cc[3] = c.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = 4 * j4 + e;
+      int32_t acc = (int32_t)v[j] + bb[e];
+      if (DYN) acc -= xz * ss[e];
+      if (REQ) {
+        const float r = fmaf(__int2float_rn(acc), cc[e], zpf);
+        const float q = rintf(r);
+        const float t = fmaf(fabsf(r), 2.384185791015625e-07f, 3.0517578125e-05f);  // |r| * 2^-22 + 2^-15
+        const bool near_tie = (fabsf(r - q) > 0.5f - t) && (fabsf(r) < 1024.0f);
+        slow |= (near_tie ? 1u : 0u) << j;
+        acc = min(max(__float2int_rn(r), p.lo), p.hi);
+      }
+      o[j] = acc;
+    }
+  }
+  if (REQ && slow != 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if ((slow >> j) & 1u) {
+        int32_t acc = (int32_t)v[j] + __ldg(bias + j);
+        if (DYN) acc -= xz * __ldg(wsum + j);
+        // f64 product and f64 add, each rounded once; round-half-even; saturate
+        const double scaled = __dadd_rn(__dmul_rn((double)acc, (double)__ldg(comb + j)), (double)p.y_zp);
+        o[j] = min(max(__double2int_rn(scaled), p.lo), p.hi);
+      }
+    }
   }
   if (esz == 1) {
 #pragma unroll
@@ -251,6 +289,24 @@ __device__ __forceinline__ void epilogue_math(const KParams& p, const uint32_t (
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) w[j] = (uint32_t)o[j];
+  }
+}
+
+// Fused epilogue of one 32-channel run of one output pixel: bias / zero-point correction,
+// requantisation or activation, packed into 32-bit words (8 for 8-bit outputs, 16 for 16-bit,
+// 32 for 32-bit).  `oc` is the first channel of the run.
+__device__ __forceinline__ void epilogue_math(const KParams& p, const uint32_t (&v)[32], int xz, int oc, size_t esz, uint32_t (&w)[32]) {
+  switch (p.variant) {
+    case 0: math_f32<0, 0>(p, v, p.bias_f + oc, w); break;
+    case 1: math_f32<0, 1>(p, v, p.bias_f + oc, w); break;
+    case 2: math_f32<1, 0>(p, v, p.bias_f + oc, w); break;
+    case 3: math_f32<1, 1>(p, v, p.bias_f + oc, w); break;
+    case 4: math_f32<2, 0>(p, v, p.bias_f + oc, w); break;
+    case 5: math_f32<2, 1>(p, v, p.bias_f + oc, w); break;
+    case V_REQUANT: math_int<true, false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w); break;
+    case V_REQUANT_DYN: math_int<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w); break;
+    case V_INT32: math_int<false, false>(p, v, p.bias_i + oc, nullptr, nullptr, xz, esz, w); break;
+    default: math_int<false, true>(p, v, p.bias_i + oc, p.wsum + oc, nullptr, xz, esz, w); break;
   }
 }
 
@@ -309,8 +365,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  // per epilogue warp: [0] bias_f or combined (f32), [1] bias_i, [2] wsum
-  __shared__ uint32_t s_par[4][3][BN];
   // per epilogue warp: two staging buffers of 32 rows x up to 128 bytes for the TMA stores
   __shared__ __align__(1024) uint8_t s_stage[4][2][32 * 128];
 
@@ -346,102 +400,134 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
 
+  // The producer and the MMA issuer run their loops with the whole warp (every lane polls the
+  // barrier, one lane issues): a lone lane looping while its 31 siblings sit at the teardown
+  // barrier gets only a fraction of the warp's issue slots.
   if (warp == 0) {
-    if (lane == 0) {
-      // ---------------- TMA producer ----------------
-      uint32_t git = 0;  // k-iterations issued so far, across tiles
-      bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
-        const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
-        int q0 = 0, p0 = 0, n0 = 0;
-        if (p.a_im2col) {
-          q0 = m0 % p.Q;
-          int tt = m0 / p.Q;
-          p0 = tt % p.P;
-          n0 = tt / p.P;
+    // ---------------- TMA producer ----------------
+    uint32_t stage = 0, phase = 0;  // ring position, carried across tiles
+    bool ok = true;
+    const int dbg = p.dbg >= 16 ? p.dbg - 16 : 0;  // timing experiments: 1 no B load, 2 no loads at all
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
+      const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
+      int q0 = 0, p0 = 0, n0 = 0;
+      if (p.a_im2col) {
+        q0 = m0 % p.Q;
+        int tt = m0 / p.Q;
+        p0 = tt % p.P;
+        n0 = tt / p.P;
+      }
+      const int w_base = q0 * p.sw - p.pl, h_base = p0 * p.sh - p.pt;
+      int r = 0, sx = 0, cb = 0;
+      for (int it = 0; it < k_iters; ++it) {
+        bool got = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0 && !*abortp) {
+            *abortp = 1;
+            atomicExch(p.err_flag, 1);
+          }
+          ok = false;
+          break;
         }
-        const int w_base = q0 * p.sw - p.pl, h_base = p0 * p.sh - p.pt;
-        int tap = 0, cb = 0;
-        for (int it = 0; it < k_iters; ++it, ++git) {
-          const uint32_t stage = git % (uint32_t)p.stages;
-          const uint32_t phase = (git / (uint32_t)p.stages) & 1u;
-          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp)) {
-            if (!*abortp) {
-              *abortp = 1;
-              atomicExch(p.err_flag, 1);
-            }
-            ok = false;
-            break;
-          }
+        if (lane == 0) {
           const uint32_t full = smem_u32(&bar_full[stage]);
-          mbar_expect_tx(full, stage_bytes);
-          const uint32_t a_dst = tiles_base + stage * stage_bytes, b_dst = a_dst + a_bytes;
-          const int c_off = cb * p.cb_elems;
-          if (p.a_im2col) {
-            const int r = tap / p.S, s = tap - r * p.S;
-            tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(s * p.dw), (uint16_t)(r * p.dh));
+          if (dbg == 2) {
+            mbar_arrive(full);
           } else {
-            tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+            mbar_expect_tx(full, dbg == 1 ? a_bytes : stage_bytes);
+            const uint32_t a_dst = tiles_base + stage * stage_bytes, b_dst = a_dst + a_bytes;
+            const int c_off = cb * p.cb_elems;
+            if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
+            else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+            if (dbg != 1) tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
           }
-          tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
-          if (++cb == p.cblocks) {
-            cb = 0;
-            ++tap;
+        }
+        __syncwarp();
+        if (++cb == p.cblocks) {
+          cb = 0;
+          if (++sx == p.S) {
+            sx = 0;
+            ++r;
           }
+        }
+        if (++stage == (uint32_t)p.stages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---------------- MMA issuer ----------------
-      const int mmas = swz / 32;
-      uint32_t git = 0;
-      uint32_t local = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-        const uint32_t buf = local & 1u;
-        const uint32_t acc_phase = (local >> 1) & 1u;
-        // the epilogue must have drained this accumulator (free on the first two tiles)
-        if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp)) {
-          if (!*abortp) {
+    // ---------------- MMA issuer ----------------
+    const int mmas = swz / 32;
+    const uint64_t desc_rest = make_smem_desc(0, swz);
+    const uint32_t idesc = p.idesc;
+    uint32_t stage = 0, phase = 0;
+    uint32_t local = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      const uint32_t buf = local & 1u;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      // the epilogue must have drained this accumulator (free on the first two tiles)
+      bool got = mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0 && !*abortp) {
+          *abortp = 1;
+          atomicExch(p.err_flag, 4);
+        }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+      for (int it = 0; it < k_iters; ++it) {
+        got = mbar_wait(smem_u32(&bar_full[stage]), phase, abortp);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0 && !*abortp) {
             *abortp = 1;
-            atomicExch(p.err_flag, 4);
+            atomicExch(p.err_flag, 2);
           }
+          ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
-        for (int it = 0; it < k_iters; ++it, ++git) {
-          const uint32_t stage = git % (uint32_t)p.stages;
-          const uint32_t phase = (git / (uint32_t)p.stages) & 1u;
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp)) {
-            if (!*abortp) {
-              *abortp = 1;
-              atomicExch(p.err_flag, 2);
+        if (lane == 0) {
+          // descriptors differ between stages only in the 16-byte granular start address
+          const uint32_t a16 = (tiles_base + stage * stage_bytes) >> 4;
+          const uint64_t da = desc_rest | (uint64_t)(a16 & 0x3fffu), db = desc_rest | (uint64_t)((a16 + (a_bytes >> 4)) & 0x3fffu);
+          if (p.dbg != 32) {
+            // 32 bytes of K per MMA: each step advances the start address by 2 units of 16 bytes
+            tc_mma<KIND>(tmem_d, da, db, idesc, it > 0 ? 1u : 0u);
+            if (mmas >= 2) tc_mma<KIND>(tmem_d, da + 2, db + 2, idesc, 1u);
+            if (mmas == 4) {
+              tc_mma<KIND>(tmem_d, da + 4, db + 4, idesc, 1u);
+              tc_mma<KIND>(tmem_d, da + 6, db + 6, idesc, 1u);
             }
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t a_addr = tiles_base + stage * stage_bytes, b_addr = a_addr + a_bytes;
-          const uint64_t da = make_smem_desc(a_addr, swz), db = make_smem_desc(b_addr, swz);
-          for (int kk = 0; kk < mmas; ++kk) {
-            // 32 bytes of K per MMA: advance the (16-byte granular) start address by 2
-            tc_mma<KIND>(tmem_d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), p.idesc, (it > 0 || kk > 0) ? 1u : 0u);
+            if (p.dbg == 33) {
+              // timing experiment: the same MMAs again into the other accumulator (an independent chain)
+              const uint32_t tmem_o = tmem_base + (buf ^ 1u) * (uint32_t)BN;
+              tc_mma<KIND>(tmem_o, da, db, idesc, it > 0 ? 1u : 0u);
+              if (mmas >= 2) tc_mma<KIND>(tmem_o, da + 2, db + 2, idesc, 1u);
+              if (mmas == 4) {
+                tc_mma<KIND>(tmem_o, da + 4, db + 4, idesc, 1u);
+                tc_mma<KIND>(tmem_o, da + 6, db + 6, idesc, 1u);
+              }
+            }
           }
           tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
         }
-        if (ok) tc_commit(smem_u32(&bar_acc_full[buf]));  // accumulator complete
+        __syncwarp();
+        if (++stage == (uint32_t)p.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
+      if (ok && lane == 0) tc_commit(smem_u32(&bar_acc_full[buf]));  // accumulator complete
+      __syncwarp();
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
     const int quarter = warp & 3;
     const int ew = warp - 2;
-    float* sf = reinterpret_cast<float*>(s_par[ew][0]);
-    int32_t* sb = reinterpret_cast<int32_t*>(s_par[ew][1]);
-    int32_t* sw = reinterpret_cast<int32_t*>(s_par[ew][2]);
     int xz = 0;
     if (p.x_zp_dev) xz = __float2int_rn(*p.x_zp_dev);
     const size_t esz = (p.out_dt == (int)DT::F32 || p.out_dt == (int)DT::I32) ? 4 : (p.out_dt == (int)DT::I16 ? 2 : 1);
@@ -450,24 +536,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     const int chunks_per_group = p.out_tma ? pitch / chunk_bytes : 1;
     const uint32_t stage0 = smem_u32(&s_stage[ew][0][0]);
     uint32_t groups = 0;  // TMA store groups issued by this warp
-    int staged_tile_n = -1;
     uint32_t local = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
       const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
       const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
-      if (tile_n != staged_tile_n) {
-        // each warp keeps its own copy of the per-channel parameters: no cross-warp barrier
-        __syncwarp();
-        for (int i = lane; i < BN; i += 32) {
-          const int oc = oc0 + i;
-          const bool okc = oc < p.OC;
-          sf[i] = (p.mode == EPI_F32) ? ((okc && p.bias_f) ? p.bias_f[oc] : 0.f) : ((okc && p.combined) ? p.combined[oc] : 0.f);
-          sb[i] = (okc && p.bias_i) ? p.bias_i[oc] : 0;
-          sw[i] = (okc && p.wsum) ? p.wsum[oc] : 0;
-        }
-        __syncwarp();
-        staged_tile_n = tile_n;
-      }
       const uint32_t buf = local & 1u;
       bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local >> 1) & 1u, abortp);
       if (!ok && !*abortp) {
@@ -483,7 +555,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN;
       const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;  // uniform across the CTA
       uint32_t va[32], vb[32], w[32];
-      if (p.dbg == 1) {
+      if (p.dbg == 1 || p.dbg >= 16) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
@@ -494,25 +566,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
 #pragma unroll 1
       for (int ch = 0; ch < n_chunks; ++ch) {
         // software pipeline: the next chunk's TMEM read is in flight while this one is processed
-        const bool odd = ch & 1;
-        if (ch + 1 < n_chunks) {
-          if (odd) tmem_ld32_nowait(taddr + (uint32_t)(ch + 1) * 32u, va);
-          else tmem_ld32_nowait(taddr + (uint32_t)(ch + 1) * 32u, vb);
-        }
+        if (ch + 1 < n_chunks) tmem_ld32_nowait(taddr + (uint32_t)(ch + 1) * 32u, vb);
         const int c0 = ch * 32;
-        if (p.dbg == 2) {
-          if (va[0] == 0x7fc12345u && vb[3] == 0x7fc12345u) atomicExch(p.err_flag, 9);
-          tmem_ld_wait();
-          continue;
-        }
-        if (odd) epilogue_math(p, vb, sf, sb, sw, xz, c0, esz, w);
-        else epilogue_math(p, va, sf, sb, sw, xz, c0, esz, w);
-        if (p.dbg == 3) {
-          if (w[0] == 0x7fc12345u && w[5] == 0x7fc12345u && w[31] == 0x7fc12345u) atomicExch(p.err_flag, 9);
-          tmem_ld_wait();
-          continue;
-        }
-        if (p.out_tma) {
+        if (p.dbg != 2) epilogue_math(p, va, xz, oc0 + c0, esz, w);
+        if (p.dbg == 2 || p.dbg == 3) {
+          if (va[0] == 0x7fc12345u && w[5] == 0x7fc12345u && w[31] == 0x7fc12345u) atomicExch(p.err_flag, 9);
+        } else if (p.out_tma) {
           const int in_group = ch % chunks_per_group;
           const uint32_t sbuf = stage0 + (groups & 1u) * (uint32_t)(32 * 128);
           if (in_group == 0) {
@@ -535,6 +594,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
           store_direct(w, (uint8_t*)p.out + ((size_t)m * p.OC + oc0 + c0) * esz, esz, min(32, p.OC - (oc0 + c0)));
         }
         tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) va[j] = vb[j];
       }
       // hand the accumulator back to the MMA issuer
       tc_fence_before();
@@ -684,14 +745,30 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   }
   if (e.x_zp_rows || e.n_w_zp > 0) return no("per-row or weight zero points need the direct kernel");
 
-  // Tile width: as wide as the channel count allows (fewer re-reads of the activation tile), but
-  // narrowed while the tile count cannot occupy every SM; GEMV-like problems (one row tile) may go
-  // down to 32 columns so that the weight stream is spread over many SMs.
+  // Tile width.  Measured on B200: one tcgen05.mma of 32 bytes of K costs about 150 ns whatever
+  // its N, and one SM fills its shared memory from L2 at about 70 GB/s.  A tile therefore takes
+  // max(k_steps * 150 ns, tile_bytes / 70 GB/s); the kernel runs ceil(tiles / SMs) rounds of
+  // tiles, and the last tile's epilogue (about 5 ns per column) is not hidden.  Pick the width
+  // that minimises that estimate; ties go to the wider tile (fewer re-reads of the activations).
   const int sms = sm_count();
   const int64_t m_tiles = ceil_div(M, BLOCK_M);
-  int bn = cs.OC <= 32 ? 32 : (cs.OC <= 64 ? 64 : (cs.OC <= 128 ? 128 : 256));
-  const int bn_floor = m_tiles <= 2 ? 32 : 64;
-  while (bn > bn_floor && m_tiles * ceil_div(cs.OC, bn) < sms) bn /= 2;
+  const int bn_max = cs.OC <= 32 ? 32 : (cs.OC <= 64 ? 64 : (cs.OC <= 128 ? 128 : 256));
+  int bn = bn_max;
+  {
+    const double k_bytes = (double)cs.K() * es;
+    const double k_steps = k_bytes / 32.0;
+    double best = 1e30;
+    for (int cand = bn_max; cand >= 32; cand /= 2) {
+      const double tiles = (double)m_tiles * (double)ceil_div(cs.OC, cand);
+      const double rounds = std::ceil(tiles / sms);
+      const double t_tile = std::max(k_steps * 150e-9, (double)(BLOCK_M + cand) * k_bytes / 70e9);
+      const double t = rounds * t_tile + cand * 5e-9;
+      if (t < best * 0.97) {
+        best = t;
+        bn = cand;
+      }
+    }
+  }
   const int64_t n_tiles = ceil_div(cs.OC, bn);
   if (m_tiles * n_tiles > 0x7fffffffLL) return no("grid too large");
 
@@ -795,6 +872,13 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   if (stages < 2) stages = 2;
   kp.stages = stages;
   kp.mode = e.mode;
+  if (e.mode == EPI_F32) kp.variant = e.act * 2 + (e.round_tf32 ? 1 : 0);
+  else if (e.mode == EPI_REQUANT) kp.variant = e.x_zp_dev ? V_REQUANT_DYN : V_REQUANT;
+  else kp.variant = e.x_zp_dev ? V_INT32_DYN : V_INT32;
+  if (e.mode == EPI_F32 ? e.bias_f == nullptr : e.bias_i == nullptr) {
+    delete pl;
+    return no("the tensor-core epilogue needs a (padded) bias vector");
+  }
   kp.bias_f = e.bias_f;
   kp.act = e.act;
   kp.clip_lo = e.clip_lo;

@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <deque>
 #include <limits>
 
 #include "runtime.hpp"
@@ -266,7 +267,9 @@ class Planner {
     st.writes = std::move(writes);
     S.steps_.push_back(std::move(st));
     int idx = (int)S.steps_.size() - 1;
-    for (int w : S.steps_[idx].writes) V(w).producer = idx;
+    // a value written by several steps (Concat) is born at the first of them
+    for (int w : S.steps_[idx].writes)
+      if (V(w).producer < 0) V(w).producer = idx;
     return S.steps_[idx];
   }
 
@@ -379,10 +382,14 @@ class Planner {
     std::vector<float> bias_f;    // empty or OC
     std::vector<float> combined;  // OC
     float w_scale_mul = 1.0f;     // Gemm alpha folded into the packed weights
+    double algorithmic_ops = 0;   // ops of the node as written (a rewritten stem pads its reduction)
+    int w_cacheable = -1;         // whether the packed weights may stay resident (-1: decide from the name)
   };
   void emit_contraction(const NodeDef& n, Contraction& c);
 
   void finalize_lifetimes_and_arena();
+  bool try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi);
+  std::deque<HostTensor> made_consts_;  // weights rewritten by the planner (space-to-depth stems)
 };
 
 // -----------------------------------------------------------------------------------------
@@ -463,7 +470,10 @@ void Planner::run(const std::vector<std::pair<std::string, std::vector<int64_t>>
 void Planner::finalize_lifetimes_and_arena() {
   const int n_steps = (int)S.steps_.size();
   for (int si = 0; si < n_steps; ++si)
+  {
     for (int r : S.steps_[si].reads) V(r).last_use = std::max(V(r).last_use, si);
+    for (int w : S.steps_[si].writes) V(w).last_use = std::max(V(w).last_use, si);
+  }
   // aliases extend the life of the storage they share
   for (int i = (int)S.values_.size() - 1; i >= 0; --i) {
     Value& v = V(i);
@@ -726,7 +736,7 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
   const int OC = cs.OC, cg = cs.C / cs.group;
   const int64_t taps = (int64_t)cs.R * cs.S;
   const HostTensor* w = c.w;
-  const bool cache_w = cacheable_const(c.w_name);
+  const bool cache_w = c.w_cacheable >= 0 ? c.w_cacheable != 0 : cacheable_const(c.w_name);
 
   auto w_at = [&](int oc, int ic, int64_t tap) -> float {
     if (c.w_is_kn) return w->data[(size_t)ic * OC + oc];  // B[K][N]
@@ -813,14 +823,29 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
         if (b < INT32_MIN || b > INT32_MAX) OXB_DECLINE("%s '%s': folded bias leaves the int32 range", n.op.c_str(), n.name.c_str());
         bias_eff[oc] = (int32_t)b;
       }
+      // parameter vectors are padded to a multiple of 256 channels: the kernel reads them in
+      // 16-byte pieces without bounds checks
+      const size_t padded = align_up((size_t)OC, 256);
+      bias_eff.resize(padded, 0);
       epi.bias_i = upload_vec(bias_eff);
-      epi.wsum = c.x_zp_static ? nullptr : upload_vec(wsum);
-      if (epi.mode == k::EPI_REQUANT) epi.combined = upload_vec(c.combined);
+      if (c.x_zp_static) {
+        epi.wsum = nullptr;
+      } else {
+        wsum.resize(padded, 0);
+        epi.wsum = upload_vec(wsum);
+      }
+      if (epi.mode == k::EPI_REQUANT) {
+        std::vector<float> comb = c.combined;
+        comb.resize(padded, 0.f);
+        epi.combined = upload_vec(comb);
+      }
     } else {
-      epi.bias_f = c.bias_f.empty() ? nullptr : upload_vec(c.bias_f);
+      std::vector<float> bias = c.bias_f;
+      bias.resize(align_up((size_t)OC, 256), 0.f);
+      epi.bias_f = upload_vec(bias);
     }
     Step& st = add_step(n, "umma", 0, reads, {out_vi});
-    st.work = cs.ops();
+    st.work = c.algorithmic_ops > 0 ? c.algorithmic_ops : cs.ops();
     st.work_is_bytes = false;
     const DT xdt = xv.dt, wdt = c.is_int ? c.w_dt : DT::F32;
     Step* stp = &st;
@@ -924,6 +949,97 @@ static DT int_storage_for(const Value& v, bool* ok) {
   return narrowest_int(lo, hi);
 }
 
+// A stride-2 convolution over very few channels (the 3-channel 7x7 stem) cannot feed the
+// tensor cores directly: its channel rows are a few bytes long.  With ih = 2*oh - pt + r, shift
+// the tap index by e = pt mod 2 so that ih = 2*(oh - (pt+e)/2 + a) + b with r + e = 2a + b: the
+// same sums as a stride-1 convolution with ceil((R+e)/2) taps over the 2x2 space-to-depth copy
+// P[n, y, x, (b_h, b_w, c)] = X[n, c, 2y+b_h, 2x+b_w], whose 4*C channels (padded) give rows of
+// 32..128 bytes.  Taps that the shift invents carry zero weights; rows and columns outside P are
+// exactly the original padding, so the tensor-map zero fill stays correct.  For integer inputs
+// the copy stores x - x_zero_point, which makes the fill value equal to the zero point.
+bool Planner::try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi) {
+  k::ConvShape& cs = c.cs;
+  const Value xv = V(src_vi);
+  if (cs.group != 1 || cs.sh != 2 || cs.sw != 2 || cs.dh != 1 || cs.dw != 1) return false;
+  if (cs.C > 8 || (cs.H & 1) || (cs.W & 1) || xv.shape.size() != 4) return false;
+  if (k::umma_channel_block(cs.C, c.is_int ? 0 : 1) != 0) return false;  // already eligible as it is
+  int sub = 0;
+  DT pdt = DT::F32;
+  if (c.is_int) {
+    if (!c.x_zp_static || !c.x_zp_rows.empty()) return false;
+    for (int32_t z : c.w_zp)
+      if (z != 0) return false;
+    if (xv.dt == DT::U8 && c.x_zp == 128) sub = 128, pdt = DT::I8;
+    else if ((xv.dt == DT::U8 || xv.dt == DT::I8) && c.x_zp == 0) pdt = xv.dt;
+    else return false;
+  } else if (xv.dt != DT::F32) {
+    return false;
+  }
+  const int eh = cs.pt & 1, ew = cs.pl & 1;
+  const int R2 = (cs.R + eh + 1) / 2, S2 = (cs.S + ew + 1) / 2;
+  const int H2 = cs.H / 2, W2 = cs.W / 2;
+  const int pt2 = (cs.pt + eh) / 2, pl2 = (cs.pl + ew) / 2;
+  const int pb2 = cs.P - 1 + R2 - H2 - pt2, pr2 = cs.Q - 1 + S2 - W2 - pl2;
+  if (pb2 < 0 || pr2 < 0) return false;
+  const int c4 = 4 * cs.C;
+  const int es = c.is_int ? 1 : 4;
+  int c_pad = 0;
+  for (int bytes : {32, 64, 128})
+    if (c4 * es <= bytes) {
+      c_pad = bytes / es;
+      break;
+    }
+  if (c_pad == 0) return false;
+  // rewritten filter in ONNX order [OC, c_pad, R2, S2]
+  const HostTensor* w = c.w;
+  made_consts_.emplace_back();
+  HostTensor& w2 = made_consts_.back();
+  w2.shape = {cs.OC, c_pad, R2, S2};
+  w2.data.assign((size_t)cs.OC * c_pad * R2 * S2, 0.f);
+  for (int oc = 0; oc < cs.OC; ++oc)
+    for (int bh = 0; bh < 2; ++bh)
+      for (int bw = 0; bw < 2; ++bw)
+        for (int ch = 0; ch < cs.C; ++ch)
+          for (int a = 0; a < R2; ++a)
+            for (int b = 0; b < S2; ++b) {
+              const int r = 2 * a + bh - eh, s = 2 * b + bw - ew;
+              if (r < 0 || r >= cs.R || s < 0 || s >= cs.S) continue;
+              const int cp = (bh * 2 + bw) * cs.C + ch;
+              w2.data[(((size_t)oc * c_pad + cp) * R2 + a) * S2 + b] = w->data[(((size_t)oc * cs.C + ch) * cs.R + r) * cs.S + s];
+            }
+  // the packed activation
+  std::vector<int64_t> pshape = {cs.N, c_pad, H2, W2};
+  int pv = add_value(xv.name + "@s2d", pshape, pdt, Layout::NHWC);
+  k::TensorRef src{nullptr, xv.dt, effective_layout(xv), dims_of(xv)};
+  if (order_free(xv)) src.layout = Layout::NHWC;
+  Step& st = add_step(n, "s2d_pack", 2, {src_vi}, {pv});
+  st.work = (double)xv.bytes + (double)V(pv).bytes;
+  const DT pdt_c = pdt;
+  st.launch = [this, src, src_vi, pv, pdt_c, c_pad, sub](cudaStream_t s) {
+    k::s2d_pack(bound(src, src_vi), V(pv).ptr, pdt_c, c_pad, sub, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+  c.algorithmic_ops = cs.ops();
+  c.w_cacheable = cacheable_const(c.w_name) ? 1 : 0;
+  c.w = &w2;
+  c.w_name = c.w_name + "@s2d";
+  c.x_vi = pv;
+  c.x_plain_nchw = false;
+  c.x_zp = 0;
+  cs.C = c_pad;
+  cs.H = H2;
+  cs.W = W2;
+  cs.R = R2;
+  cs.S = S2;
+  cs.sh = cs.sw = 1;
+  cs.pt = pt2;
+  cs.pl = pl2;
+  cs.pb = pb2;
+  cs.pr = pr2;
+  return true;
+}
+
 void Planner::plan_conv_family(const NodeDef& n, int ni) {
   (void)ni;
   const std::string& op = n.op;
@@ -1002,7 +1118,9 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
     c.epi.out_dt = DT::F32;
     // a stem that reads a channels-first graph input directly skips the layout pass
     bool direct_nchw = xv.layout == Layout::PLAIN && !order_free(xv) && k::umma_channel_block(cs.C, 1) == 0;
-    if (direct_nchw) {
+    if (C.cfg().kernel_path == 0 && k::umma_available() && try_s2d_stem(n, c, xi)) {
+      // the stride-2 few-channel stem became a stride-1 convolution over a space-to-depth copy
+    } else if (direct_nchw) {
       c.x_plain_nchw = true;
       c.x_vi = xi;
     } else {
@@ -1058,6 +1176,7 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
     xq = ensure_layout(n, xi, Layout::NHWC);
   }
   c.x_vi = xq;
+  if (C.cfg().kernel_path == 0 && k::umma_available()) try_s2d_stem(n, c, xq);
 
   if (is_ci) {
     c.epi.mode = k::EPI_INT32;
@@ -1090,7 +1209,8 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
     c.combined[oc] = comb;
     if (!std::isfinite(c.combined[oc])) OXB_DECLINE("QLinearConv: combined scale is not finite");
   }
-  Range r = sat_infer(y_zp_l, {c.x_zp});
+  // the node's own zero point decides the range (a rewritten stem carries an effective zero point of 0)
+  Range r = sat_infer(y_zp_l, {x_zp_l.empty() ? 0 : x_zp_l[0]});
   c.epi.mode = k::EPI_REQUANT;
   c.epi.y_zp = y_zp_l.empty() ? 0 : y_zp_l[0];
   c.epi.lo = r.lo;
@@ -1786,9 +1906,86 @@ void Planner::plan_alias(const NodeDef& n) {
 // operations in the same order, so the lanes equal the unfused chain's bit for bit; the
 // float intermediates never reach memory.
 bool Planner::try_plan_residual_chain(const NodeDef& n, int ni) {
-  (void)n;
-  (void)ni;
-  return false;
+  // per-tensor parameters held by initializers: scale at slot 1, optional zero point at slot 2
+  auto per_tensor = [&](const NodeDef& d, float* scale, float* zp, bool* has_zp) -> bool {
+    for (const std::string& a : d.attrs.names())
+      if (a != "axis") return false;
+    const HostTensor* sc = const_in(d, 1);
+    if (!sc || sc->data.size() != 1 || !std::isfinite(sc->data[0]) || sc->data[0] == 0.f) return false;
+    *scale = sc->data[0];
+    *zp = 0.f;
+    *has_zp = false;
+    if (has_in(d, 2)) {
+      const HostTensor* z = const_in(d, 2);
+      if (!z || z->data.size() != 1 || !std::isfinite(z->data[0]) || z->data[0] != std::nearbyint(z->data[0])) return false;
+      *zp = z->data[0];
+      *has_zp = true;
+    }
+    return true;
+  };
+  auto only_consumer = [&](const std::string& name, int* node, int* slot) -> bool {
+    if (graph_outputs_.count(name)) return false;
+    auto it = consumers_.find(name);
+    if (it == consumers_.end() || it->second.size() != 1) return false;
+    *node = it->second[0].first;
+    *slot = it->second[0].second;
+    return !skipped_[*node];
+  };
+  k::ResidualParams rp{};
+  bool hz;
+  if (!per_tensor(n, &rp.a_scale, &rp.a_zp, &hz)) return false;
+  auto x1 = S.index_.find(in_name(n, 0));
+  if (x1 == S.index_.end()) return false;
+  int add_i, add_slot;
+  if (!only_consumer(n.outputs[0], &add_i, &add_slot) || nodes_[add_i].op != "Add" || add_slot > 1 || !nodes_[add_i].attrs.names().empty()) return false;
+  const NodeDef& add = nodes_[add_i];
+  if (add.inputs.size() != 2) return false;
+  const std::string& other = add.inputs[1 - add_slot];
+  if (S.index_.count(other)) return false;  // already materialised by an earlier node
+  int d2_i = -1;
+  for (int j = ni + 1; j < add_i; ++j)
+    if (!skipped_[j] && nodes_[j].op == "DequantizeLinear" && !nodes_[j].outputs.empty() && nodes_[j].outputs[0] == other) d2_i = j;
+  if (d2_i < 0) return false;
+  const NodeDef& d2 = nodes_[d2_i];
+  int c2, s2;
+  if (!only_consumer(other, &c2, &s2) || c2 != add_i) return false;
+  if (!per_tensor(d2, &rp.b_scale, &rp.b_zp, &hz)) return false;
+  auto x2 = S.index_.find(in_name(d2, 0));
+  if (x2 == S.index_.end()) return false;
+  const Value va = V(x1->second), vb = V(x2->second);
+  auto eight_bit = [](const Value& v) { return v.dt == DT::U8 || v.dt == DT::I8; };
+  if (!eight_bit(va) || !eight_bit(vb) || va.shape != vb.shape) return false;
+  if (va.shape.size() == 4 && !order_free(va) && va.layout != vb.layout) return false;
+  std::string cur = add.outputs[0];
+  int relu_i = sole_consumer(cur, "Relu");
+  rp.relu = relu_i >= 0 ? 1 : 0;
+  if (relu_i >= 0) cur = nodes_[relu_i].outputs[0];
+  int q_i, q_slot;
+  if (!only_consumer(cur, &q_i, &q_slot) || nodes_[q_i].op != "QuantizeLinear" || q_slot != 0) return false;
+  const NodeDef& q = nodes_[q_i];
+  bool q_has_zp;
+  if (!per_tensor(q, &rp.y_scale, &rp.y_zp, &q_has_zp)) return false;
+  // saturation_range (oxionnx-ops src/indexing/quantize.rs:58-64)
+  const bool u8 = !q_has_zp || rp.y_zp > 127.0f;
+  rp.lo = u8 ? 0.f : -128.f;
+  rp.hi = u8 ? 255.f : 127.f;
+  const DT odt = u8 ? DT::U8 : DT::I8;
+  skipped_[d2_i] = skipped_[add_i] = skipped_[q_i] = 1;
+  if (relu_i >= 0) skipped_[relu_i] = 1;
+  const int ai = x1->second, bi = x2->second;
+  const int yi = add_value(q.outputs[0], va.shape, odt, va.shape.size() == 4 ? va.layout : Layout::PLAIN);
+  const int64_t count = va.numel();
+  const DT adt = va.dt, bdt = vb.dt;
+  Step& st = add_step(n, "residual_requant", 2, {ai, bi}, {yi});
+  st.node_name = add.name;
+  st.op_type = "DequantizeLinear+Add+Relu+QuantizeLinear";
+  st.work = 3.0 * (double)count;
+  st.launch = [this, ai, bi, yi, adt, bdt, odt, count, rp](cudaStream_t s) {
+    k::residual_requant(V(ai).ptr, adt, V(bi).ptr, bdt, V(yi).ptr, odt, count, rp, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+  return true;
 }
 
 // =========================================================================================
