@@ -233,6 +233,28 @@ typedef struct {
 uint32_t oxb200_plan_step_count(const oxb200_ctx* ctx);
 int oxb200_plan_step_info(const oxb200_ctx* ctx, uint32_t index, oxb200_step_info* out);
 
+/* ---- allocation-free entry point -------------------------------------------------------- */
+
+/* DynamicQuantizeLinear for hosts that are not allowed to allocate device memory while running
+ * (a frame loop whose memory was fixed at start-up, another runtime's arena, a sandboxed plug-in).
+ * This entry point has no counterpart in the reference.  It computes exactly what the
+ * DynamicQuantizeLinear node of oxb200_dispatch computes, but everything it touches is either
+ * passed in by the caller or part of the library image: it calls no cudaMalloc, no cudaFree and
+ * no other allocating routine.
+ *   x_device        n f32 lanes on the device
+ *   y_device        n u8 lanes on the device (output)
+ *   scale_zp_device 2 f32 lanes on the device (output: y_scale, y_zero_point)
+ *   cuda_stream     a cudaStream_t of device `device_ordinal` (NULL: the default stream)
+ * The reduction scratch is a 256-byte array inside the library, present on every GPU that loads
+ * it until the process exits.  At most 2^28 lanes per call; larger inputs are rejected with
+ * OXB200_FAILED and a message.  The first call for a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current), so make that first call before any stream
+ * capture.  All calls share the array: each call resets it on its stream first, and calls that
+ * overlap on one GPU race on it -- serialise them.  Returns OXB200_OK_DEVICE once the work is
+ * enqueued; the message of a failure is read with oxb200_last_error(NULL). */
+int oxb200_dynamic_quantize_linear_noalloc(int device_ordinal, const float* x_device, uint64_t n, uint8_t* y_device, float* scale_zp_device,
+                                           void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -96,6 +96,8 @@ SYMBOLS = {
     "oxb200_fetch_value": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(Result)]),
     "oxb200_plan_step_count": (ctypes.c_uint32, [ctypes.c_void_p]),
     "oxb200_plan_step_info": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32, _P(StepInfo)]),
+    "oxb200_dynamic_quantize_linear_noalloc": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p,
+                                                              ctypes.c_void_p]),
 }
 
 _lib = None

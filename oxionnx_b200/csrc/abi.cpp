@@ -21,6 +21,15 @@ namespace {
 
 thread_local std::string g_thread_error;
 
+}  // namespace
+
+namespace oxb {
+void set_thread_error(const std::string& message) { g_thread_error = message; }
+}  // namespace oxb
+
+namespace {
+
+
 // The proved-wrong marker of the reference (oxionnx-cuda src/error.rs:75).
 const char kVerifyPrefix[] = "CUDA VERIFY MISMATCH: ";
 

@@ -74,6 +74,9 @@ struct Error : std::runtime_error {
                                         __FILE__, __LINE__, cudaGetErrorString(_e));                     \
   } while (0)
 
+// Records a message for oxb200_last_error(NULL) on the calling thread (defined in abi.cpp).
+void set_thread_error(const std::string& message);
+
 inline int64_t prod(const std::vector<int64_t>& s) {
   int64_t n = 1;
   for (int64_t d : s) n *= d;

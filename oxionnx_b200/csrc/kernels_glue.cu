@@ -2,6 +2,9 @@
 // once through HBM with vectorised accesses where the layout allows; none of them uses a
 // fused multiply-add (this file is compiled with --fmad=false) because the reference rounds
 // every f32 operation separately and the quantisers sit right at rounding boundaries.
+#include <mutex>
+#include <string>
+
 #include "kernels.hpp"
 
 namespace oxb {
@@ -786,5 +789,82 @@ void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offse
   concat_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, y.ptr, x.dt, x.layout, x.d, y.d, axis, offset, total);
 }
 
+// =========================================================================================
+// DynamicQuantizeLinear for callers that must not allocate.
+//
+// Some hosts of this library run where device allocation is off the table: inside a real-time
+// frame loop whose memory was carved up at start-up, inside another runtime's arena that owns
+// every byte of the device, or in a sandboxed plug-in that is simply not allowed to call the
+// allocator.  The ordinary path keeps its min/max reduction words in memory it allocates; this
+// variant keeps them in a small array that is part of the library image instead, so it calls no
+// cudaMalloc, no cudaFree and no allocating library routine.  Every GPU that loads the library
+// carries the array (256 bytes) until the process exits.
+//
+// The array's name is only a host-side handle in host code: the kernels need its device address,
+// which is looked up once per device with cudaGetSymbolAddress while that device is current.
+// That look-up happens inside the first call made for a device, so the first call should be made
+// before any stream capture begins.  All calls share the one array and it keeps whatever the
+// previous call left there: each call re-initialises the two reduction words on its stream before
+// using them, and two calls that overlap on the same GPU (different streams, or different host
+// threads) race on it and must be serialised by the caller.
+namespace {
+
+constexpr unsigned long long kNoAllocMaxElems = 1ull << 28;  // 268,435,456 lanes (1 GiB of f32 input)
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) unsigned int g_noalloc_scratch[64];
+
+std::mutex g_noalloc_mutex;
+unsigned int* g_noalloc_scratch_addr[kNoAllocMaxDevices] = {};
+
+}  // namespace
 }  // namespace k
 }  // namespace oxb
+
+extern "C" int oxb200_dynamic_quantize_linear_noalloc(int device_ordinal, const float* x_device, uint64_t n, uint8_t* y_device,
+                                                       float* scale_zp_device, void* cuda_stream) {
+  using namespace oxb;
+  using namespace oxb::k;
+  auto fail = [](const std::string& m) {
+    set_thread_error(m);
+    return (int)OXB200_FAILED;
+  };
+  if (!x_device || !y_device || !scale_zp_device) return fail("dynamic_quantize_linear_noalloc: NULL device pointer");
+  if (n == 0) return fail("dynamic_quantize_linear_noalloc: input is empty");
+  if (n > kNoAllocMaxElems) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "dynamic_quantize_linear_noalloc: %llu lanes exceed the maximum of %llu for the allocation-free entry point",
+             (unsigned long long)n, kNoAllocMaxElems);
+    return fail(buf);
+  }
+  if (device_ordinal < 0 || device_ordinal >= kNoAllocMaxDevices) return fail("dynamic_quantize_linear_noalloc: device ordinal out of range");
+  int previous = -1;
+  if (cudaGetDevice(&previous) != cudaSuccess) previous = -1;
+  cudaError_t e = cudaSetDevice(device_ordinal);
+  if (e != cudaSuccess) return fail(std::string("dynamic_quantize_linear_noalloc: cudaSetDevice: ") + cudaGetErrorString(e));
+  unsigned int* scratch = nullptr;
+  {
+    // set-up, once per device, with that device current
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_scratch_addr[device_ordinal]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || !p) {
+        if (previous >= 0) cudaSetDevice(previous);
+        return fail(std::string("dynamic_quantize_linear_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+      }
+      g_noalloc_scratch_addr[device_ordinal] = (unsigned int*)p;
+    }
+    scratch = g_noalloc_scratch_addr[device_ordinal];
+  }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const int64_t count = (int64_t)n;
+  minmax_init_kernel<<<1, 1, 0, s>>>(scratch);  // the shared words start every call from their identity values
+  minmax_kernel<<<grid_for(count / 4 + 1), kThreads, 0, s>>>(x_device, count, scratch);
+  dynq_params_kernel<<<1, 1, 0, s>>>(scratch, scale_zp_device);
+  dynq_apply_kernel<<<grid_for(count / 4 + 1), kThreads, 0, s>>>(x_device, y_device, scale_zp_device, count);
+  e = cudaGetLastError();
+  if (previous >= 0 && previous != device_ordinal) cudaSetDevice(previous);
+  if (e != cudaSuccess) return fail(std::string("dynamic_quantize_linear_noalloc: launch failed: ") + cudaGetErrorString(e));
+  return (int)OXB200_OK_DEVICE;
+}
