@@ -86,7 +86,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -94,6 +94,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 // Bounded wait: false when the barrier did not flip within WAIT_CYCLES or another role aborted.
+// try_wait parks the warp in hardware for a bounded time per attempt, so a waiting role leaves
+// its scheduler's issue slots to the epilogue warp that shares it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   long long start = clock64();
@@ -125,21 +127,33 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// The MMAs of one K block (1, 2 or 4 instructions of 32 bytes of K each) in one asm block: the
+// 64-bit descriptors are assembled from a 32-bit low word that advances by 2 (16-byte units) per
+// instruction and a constant high word, so the issuing thread spends a handful of integer
+// instructions per K block.
+#define OXB_MMA_BLOCK(KINDSTR)                                                                              \
+  asm volatile(                                                                                             \
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"                                 \
+      "setp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, 1, 0;\n\t"                                                   \
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"                                                  \
+      "tcgen05.mma.cta_group::1.kind::" KINDSTR " [%0], da, db, %4, p;\n\t"                                 \
+      "setp.lt.u32 p, %6, 2;\n\t@p bra DONE_%=;\n\t"                                                        \
+      "add.u32 la, %1, 2;\n\tadd.u32 lb, %2, 2;\n\tmov.b64 da, {la, %3};\n\tmov.b64 db, {lb, %3};\n\t"     \
+      "tcgen05.mma.cta_group::1.kind::" KINDSTR " [%0], da, db, %4, q;\n\t"                                 \
+      "setp.lt.u32 p, %6, 4;\n\t@p bra DONE_%=;\n\t"                                                        \
+      "add.u32 la, %1, 4;\n\tadd.u32 lb, %2, 4;\n\tmov.b64 da, {la, %3};\n\tmov.b64 db, {lb, %3};\n\t"     \
+      "tcgen05.mma.cta_group::1.kind::" KINDSTR " [%0], da, db, %4, q;\n\t"                                 \
+      "add.u32 la, %1, 6;\n\tadd.u32 lb, %2, 6;\n\tmov.b64 da, {la, %3};\n\tmov.b64 db, {lb, %3};\n\t"     \
+      "tcgen05.mma.cta_group::1.kind::" KINDSTR " [%0], da, db, %4, q;\n\t"                                 \
+      "DONE_%=:\n\t}" ::"r"(tmem_d),                                                                        \
+      "r"(lo_a), "r"(lo_b), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(mmas)                            \
+      : "memory")
+
 template <int KIND>
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  if (KIND == 0) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
+__device__ __forceinline__ void tc_mma_block(uint32_t tmem_d, uint32_t lo_a, uint32_t lo_b, uint32_t desc_hi, uint32_t idesc, uint32_t accumulate,
+                                             uint32_t mmas) {
+  if (KIND == 0) OXB_MMA_BLOCK("i8");
+  else OXB_MMA_BLOCK("tf32");
 }
 
 // Shared-memory matrix descriptor, K-major operand, swizzled rows of `swz` bytes: start
@@ -203,7 +217,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // parallelism (one epilogue warp per scheduler has nothing else to hide latency with).
 // Per-channel parameters are read with 16-byte read-only loads; the host pads every
 // parameter vector to a multiple of 256 channels, so no bounds checks are needed here.
-enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9 };
+enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9, V_REQUANT_FMA = 10, V_REQUANT_FMA_DYN = 11 };
 
 template <int ACT, int RT>
 __device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias, uint32_t (&w)[32]) {
@@ -292,6 +306,68 @@ __device__ __forceinline__ void math_int(const KParams& p, const uint32_t (&v)[3
   }
 }
 
+// ONNX requantisation in one fused multiply-add per output.  With a = (float)acc exact
+// (|acc| < 2^24) the instruction s = fma(a, c, 1.5 * 2^23 + zp) rounds the exact real number
+// acc * c + zp once, to the integer grid of the binade [2^23, 2^24), ties to even: the low
+// mantissa bits of s are round_half_even(acc * c + zp).  The reference's two f64 operations
+// are exact for these operands (a 24-bit by 24-bit product, and a sum spanning at most 53
+// bits when |c| >= 2^-21, which the host checks before choosing this variant), so both sides
+// round the same real number the same way.  Values beyond +-2^22 leave the binade but stay
+// monotone, and the clamp (done on the float, before the bits are taken) sends them to the
+// same bound as the reference's.  A thread that meets |acc| >= 2^24 redoes its run with the
+// reference's own f64 operations.
+template <bool DYN>
+__device__ __forceinline__ void math_requant_fma(const KParams& p, const uint32_t (&v)[32], const int32_t* __restrict__ bias,
+                                                 const int32_t* __restrict__ wsum, const float* __restrict__ comb, int xz, size_t esz, uint32_t (&w)[32]) {
+  const float magic = 12582912.0f;  // 1.5 * 2^23
+  const float magic_zp = magic + (float)p.y_zp, flo = magic + (float)p.lo, fhi = magic + (float)p.hi;
+  float amax = 0.f;
+  uint32_t sb[32];
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const int4 b = __ldg(reinterpret_cast<const int4*>(bias) + j4);
+    const int bb[4] = {b.x, b.y, b.z, b.w};
+    int ss[4] = {0, 0, 0, 0};
+    if (DYN) {
+      const int4 sv = __ldg(reinterpret_cast<const int4*>(wsum) + j4);
+      ss[0] = sv.x, ss[1] = sv.y, ss[2] = sv.z, ss[3] = sv.w;
+    }
+    const float4 c = __ldg(reinterpret_cast<const float4*>(comb) + j4);
+    const float cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = 4 * j4 + e;
+      int32_t acc = (int32_t)v[j] + bb[e];
+      if (DYN) acc -= xz * ss[e];
+      const float a = __int2float_rn(acc);
+      amax = fmaxf(amax, fabsf(a));
+      const float s = fminf(fmaxf(fmaf(a, cc[e], magic_zp), flo), fhi);
+      sb[j] = __float_as_uint(s);
+    }
+  }
+  // the value sits in the low mantissa bits (two's complement below 2^22): take its low byte,
+  // or its low half-word for the 16-bit lanes of the union range [-128, 255]
+  if (esz == 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j] = __byte_perm(__byte_perm(sb[4 * j], sb[4 * j + 1], 0x0040), __byte_perm(sb[4 * j + 2], sb[4 * j + 3], 0x0040), 0x5410);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = __byte_perm(sb[2 * j], sb[2 * j + 1], 0x5410);
+  }
+  if (amax >= 16777216.0f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      int32_t acc = (int32_t)v[j] + __ldg(bias + j);
+      if (DYN) acc -= xz * __ldg(wsum + j);
+      const double scaled = __dadd_rn(__dmul_rn((double)acc, (double)__ldg(comb + j)), (double)p.y_zp);
+      const uint32_t q = (uint32_t)min(max(__double2int_rn(scaled), p.lo), p.hi);
+      if (esz == 1) w[j >> 2] = (w[j >> 2] & ~(0xffu << (8 * (j & 3)))) | ((q & 0xffu) << (8 * (j & 3)));
+      else w[j >> 1] = (w[j >> 1] & ~(0xffffu << (16 * (j & 1)))) | ((q & 0xffffu) << (16 * (j & 1)));
+    }
+  }
+}
+
 // Fused epilogue of one 32-channel run of one output pixel: bias / zero-point correction,
 // requantisation or activation, packed into 32-bit words (8 for 8-bit outputs, 16 for 16-bit,
 // 32 for 32-bit).  `oc` is the first channel of the run.
@@ -306,6 +382,8 @@ __device__ __forceinline__ void epilogue_math(const KParams& p, const uint32_t (
     case V_REQUANT: math_int<true, false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w); break;
     case V_REQUANT_DYN: math_int<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w); break;
     case V_INT32: math_int<false, false>(p, v, p.bias_i + oc, nullptr, nullptr, xz, esz, w); break;
+    case V_REQUANT_FMA: math_requant_fma<false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w); break;
+    case V_REQUANT_FMA_DYN: math_requant_fma<true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w); break;
     default: math_int<false, true>(p, v, p.bias_i + oc, p.wsum + oc, nullptr, xz, esz, w); break;
   }
 }
@@ -407,7 +485,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     // ---------------- TMA producer ----------------
     uint32_t stage = 0, phase = 0;  // ring position, carried across tiles
     bool ok = true;
-    const int dbg = p.dbg >= 16 ? p.dbg - 16 : 0;  // timing experiments: 1 no B load, 2 no loads at all
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
       const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
@@ -432,16 +509,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         }
         if (lane == 0) {
           const uint32_t full = smem_u32(&bar_full[stage]);
-          if (dbg == 2) {
-            mbar_arrive(full);
-          } else {
-            mbar_expect_tx(full, dbg == 1 ? a_bytes : stage_bytes);
-            const uint32_t a_dst = tiles_base + stage * stage_bytes, b_dst = a_dst + a_bytes;
-            const int c_off = cb * p.cb_elems;
-            if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
-            else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
-            if (dbg != 1) tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
-          }
+          mbar_expect_tx(full, stage_bytes);
+          const uint32_t a_dst = tiles_base + stage * stage_bytes, b_dst = a_dst + a_bytes;
+          const int c_off = cb * p.cb_elems;
+          if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
+          else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+          tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
         }
         __syncwarp();
         if (++cb == p.cblocks) {
@@ -459,10 +532,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    const int mmas = swz / 32;
+    const uint32_t mmas = (uint32_t)(swz / 32);
     const uint64_t desc_rest = make_smem_desc(0, swz);
+    const uint32_t desc_hi = (uint32_t)(desc_rest >> 32), desc_lo = (uint32_t)desc_rest;
     const uint32_t idesc = p.idesc;
-    uint32_t stage = 0, phase = 0;
+    const uint32_t ring16 = tiles_base >> 4, stage16 = stage_bytes >> 4, a16_bytes = a_bytes >> 4;
+    uint32_t stage = 0, phase = 0, a16 = ring16;
     uint32_t local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
@@ -492,33 +567,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         tc_fence_after();
         if (lane == 0) {
           // descriptors differ between stages only in the 16-byte granular start address
-          const uint32_t a16 = (tiles_base + stage * stage_bytes) >> 4;
-          const uint64_t da = desc_rest | (uint64_t)(a16 & 0x3fffu), db = desc_rest | (uint64_t)((a16 + (a_bytes >> 4)) & 0x3fffu);
-          if (p.dbg != 32) {
-            // 32 bytes of K per MMA: each step advances the start address by 2 units of 16 bytes
-            tc_mma<KIND>(tmem_d, da, db, idesc, it > 0 ? 1u : 0u);
-            if (mmas >= 2) tc_mma<KIND>(tmem_d, da + 2, db + 2, idesc, 1u);
-            if (mmas == 4) {
-              tc_mma<KIND>(tmem_d, da + 4, db + 4, idesc, 1u);
-              tc_mma<KIND>(tmem_d, da + 6, db + 6, idesc, 1u);
-            }
-            if (p.dbg == 33) {
-              // timing experiment: the same MMAs again into the other accumulator (an independent chain)
-              const uint32_t tmem_o = tmem_base + (buf ^ 1u) * (uint32_t)BN;
-              tc_mma<KIND>(tmem_o, da, db, idesc, it > 0 ? 1u : 0u);
-              if (mmas >= 2) tc_mma<KIND>(tmem_o, da + 2, db + 2, idesc, 1u);
-              if (mmas == 4) {
-                tc_mma<KIND>(tmem_o, da + 4, db + 4, idesc, 1u);
-                tc_mma<KIND>(tmem_o, da + 6, db + 6, idesc, 1u);
-              }
-            }
-          }
+          tc_mma_block<KIND>(tmem_d, desc_lo | (a16 & 0x3fffu), desc_lo | ((a16 + a16_bytes) & 0x3fffu), desc_hi, idesc, it > 0 ? 1u : 0u, mmas);
           tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
         }
         __syncwarp();
+        a16 += stage16;
         if (++stage == (uint32_t)p.stages) {
           stage = 0;
           phase ^= 1u;
+          a16 = ring16;
         }
       }
       if (ok && lane == 0) tc_commit(smem_u32(&bar_acc_full[buf]));  // accumulator complete
@@ -555,7 +612,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN;
       const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;  // uniform across the CTA
       uint32_t va[32], vb[32], w[32];
-      if (p.dbg == 1 || p.dbg >= 16) {
+      if (p.dbg == 1) {  // timing experiment: no epilogue work at all
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
@@ -866,14 +923,18 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.idesc = make_idesc(kind, x_dt == DT::I8, w_dt == DT::I8, bn);
   const size_t stage_bytes = (size_t)(BLOCK_M + bn) * swz;
   // one persistent CTA per SM: the ring may use most of the 227 KB and runs on across tiles
-  const size_t budget = 160 * 1024;
+  const size_t budget = 192 * 1024;
   int stages = (int)(budget / stage_bytes);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) stages = 2;
   kp.stages = stages;
   kp.mode = e.mode;
   if (e.mode == EPI_F32) kp.variant = e.act * 2 + (e.round_tf32 ? 1 : 0);
-  else if (e.mode == EPI_REQUANT) kp.variant = e.x_zp_dev ? V_REQUANT_DYN : V_REQUANT;
+  else if (e.mode == EPI_REQUANT) {
+    const bool no_fma = std::getenv("OXB200_REQUANT_F64") != nullptr;  // keeps the two-pass variant reachable for tests
+    const bool fma = e.combined_fma_ok && !no_fma;
+    kp.variant = e.x_zp_dev ? (fma ? V_REQUANT_FMA_DYN : V_REQUANT_DYN) : (fma ? V_REQUANT_FMA : V_REQUANT);
+  }
   else kp.variant = e.x_zp_dev ? V_INT32_DYN : V_INT32;
   if (e.mode == EPI_F32 ? e.bias_f == nullptr : e.bias_i == nullptr) {
     delete pl;

@@ -836,6 +836,11 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
       }
       if (epi.mode == k::EPI_REQUANT) {
         std::vector<float> comb = c.combined;
+        epi.combined_fma_ok = 1;
+        for (float v : comb) {
+          const float a = std::fabs(v);
+          if (!(a == 0.f || (a >= 4.76837158203125e-07f && a <= 1099511627776.0f))) epi.combined_fma_ok = 0;
+        }
         comb.resize(padded, 0.f);
         epi.combined = upload_vec(comb);
       }

@@ -164,6 +164,50 @@ def test_qlinear_matmul_bit_exact(ctx):
         assert np.array_equal(got[0], want), f"{(m, k, n)}: {np.sum(got[0] != want)} lanes differ"
 
 
+REQUANT_EDGE = [
+    # name, K, generator, a_scale, b_scale, y_scale, a_zp, y_zp
+    ("exact ties, combined 0.5", 32, ("uniform", (0, 8), (-3, 4)), 1.0, 0.5, 1.0, 0, 0),
+    ("exact ties, combined 0.125 with zero points", 64, ("uniform", (0, 16), (-7, 8)), 0.25, 0.5, 1.0, 3, 131),
+    ("accumulators beyond 2^24", 1024, ("big", 100, 128), 0.001, 0.001, 0.5, 0, 128),
+    ("accumulators beyond 2^24, both signs", 2048, ("big_signed", 100, 128), 0.002, 0.001, 1.0, 0, 128),
+    ("combined scale below 2^-21 (two-pass variant)", 4096, ("big_signed", 64, 128), 1e-4, 1e-4, 0.05, 0, 128),
+    ("combined scale above one", 32, ("uniform", (0, 4), (-2, 3)), 2.0, 1.5, 1.0, 0, 100),
+]
+
+
+def _requant_edge_operands(rng, gen, m, k, n):
+    if gen[0] == "uniform":
+        return rng.integers(*gen[1], (m, k)).astype(np.float32), rng.integers(*gen[2], (k, n)).astype(np.float32)
+    # rows of A at one level each, columns of B of one sign each: |sum| grows to K * 255 * 127
+    a = np.clip(rng.integers(128, 256, (m, 1)) + rng.integers(-2, 3, (m, k)), 0, 255).astype(np.float32)
+    b = rng.integers(gen[1], gen[2], (k, n)).astype(np.float32)
+    if gen[0] == "big_signed":
+        b *= rng.choice(np.float32([-1, 1]), (1, n))
+    return a, b
+
+
+@pytest.mark.parametrize("case", REQUANT_EDGE, ids=[c[0] for c in REQUANT_EDGE])
+@pytest.mark.parametrize("force_f64", [False, True], ids=["fma", "two-pass"])
+def test_requantisation_edge_cases_bit_exact(ctx_auto, case, force_f64, monkeypatch):
+    """The tensor-core epilogue has two requantisation variants (one fused multiply-add per lane
+    when the scales allow it, an f32 estimate with an f64 second pass otherwise); both must equal
+    the reference's f64 arithmetic on ties, on accumulators that f32 cannot hold exactly and on
+    extreme scales (oxionnx-ops/src/quantize/requant.rs)."""
+    name, k, gen, a_scale, b_scale, y_scale, a_zp, y_zp = case
+    if force_f64:
+        monkeypatch.setenv("OXB200_REQUANT_F64", "1")
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    oracle.set_threads(8)
+    m, n = 256, 96
+    a, b = _requant_edge_operands(rng, gen, m, k, n)
+    ins = [a, np.float32([a_scale]), np.float32([a_zp]), b, np.float32([b_scale]), np.float32([0]), np.float32([y_scale]), np.float32([y_zp])]
+    want, = oracle.run_node("QLinearMatMul", ins)
+    got = dispatch(ctx_auto, "QLinearMatMul", ins)
+    assert got is not None, ctx_auto.last_error()
+    assert np.array_equal(got[0], want), f"{name}: {np.sum(got[0] != want)} of {want.size} lanes differ"
+    assert np.unique(want).size > 4, "degenerate test vector"
+
+
 def test_quantize_dequantize_dynamic_bit_exact(ctx):
     rng = np.random.default_rng(29)
     x = (rng.standard_normal((4, 6, 10, 12)) * 3).astype(np.float32)
