@@ -6,7 +6,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "_lib", "liboxb200.so")
+LIB_PATH = os.environ.get("OXB200_LIBRARY") or os.path.join(HERE, "_lib", "liboxb200.so")
 
 MAX_RANK = 8
 OK_HOST, OK_DEVICE, DECLINED, FAILED, VERIFY_MISMATCH = 0, 1, 2, 3, 4

@@ -550,19 +550,48 @@ __device__ __forceinline__ uint32_t residual_one(float av, float bv, const Resid
   return (uint32_t)__float2int_rn(q) & 0xffu;
 }
 
+// The same lane without the conversion and reciprocal units, for parameters that
+// residual_requant_prepare() has proven: the byte is dropped into the mantissa of 2^23 (so that
+// `bits - (2^23 + zp)` is the exact integer difference), the quotient is one multiply by the
+// rounded reciprocal plus one remainder correction, and rounding to the nearest-even integer is an
+// addition of 1.5 * 2^23.  `off_a`/`off_b` are 2^23 + zero point (+128 for signed storage, whose
+// bytes arrive with the sign bit flipped).
+__device__ __forceinline__ float residual_fast(uint32_t a_bits, uint32_t b_bits, float off_a, float off_b, const ResidualParams& rp) {
+  const float va = __fmul_rn(__fsub_rn(__uint_as_float(a_bits), off_a), rp.a_scale);
+  const float vb = __fmul_rn(__fsub_rn(__uint_as_float(b_bits), off_b), rp.b_scale);
+  float sum = __fadd_rn(va, vb);
+  if (rp.relu) sum = fmaxf(sum, 0.f);
+  const float q0 = __fmul_rn(sum, rp.y_rcp);
+  const float q = __fmaf_rn(__fmaf_rn(-q0, rp.y_scale, sum), rp.y_rcp, q0);
+  const float t = __fadd_rn(__fadd_rn(q, 12582912.0f), rp.y_zp);
+  return fminf(fmaxf(t, 12582912.0f + rp.lo), 12582912.0f + rp.hi);  // the lane is the low byte of these bits
+}
+
 // 16 lanes per thread: two 16-byte loads, one 16-byte store.
+template <bool FAST>
 __global__ void residual_requant_kernel(const uint4* __restrict__ a, bool a_signed, const uint4* __restrict__ b, bool b_signed, uint4* __restrict__ y,
                                         int64_t n16, ResidualParams rp) {
+  const float off_a = 8388608.0f + rp.a_zp + (a_signed ? 128.f : 0.f), off_b = 8388608.0f + rp.b_zp + (b_signed ? 128.f : 0.f);
+  const uint32_t flip_a = a_signed ? 0x80808080u : 0u, flip_b = b_signed ? 0x80808080u : 0u;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
-    const uint4 av = a[i], bv = b[i];
+    const uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
     const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
     uint32_t out[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      uint32_t w = 0;
+      if (FAST) {
+        const uint32_t wa = aw[j] ^ flip_a, wb = bw[j] ^ flip_b;
+        uint32_t r[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) w |= residual_one(lane8(aw[j], e, a_signed), lane8(bw[j], e, b_signed), rp) << (8 * e);
-      out[j] = w;
+        for (int e = 0; e < 4; ++e)
+          r[e] = __float_as_uint(residual_fast(__byte_perm(wa, 0x4B000000u, 0x7440 + e), __byte_perm(wb, 0x4B000000u, 0x7440 + e), off_a, off_b, rp));
+        out[j] = __byte_perm(__byte_perm(r[0], r[1], 0x0040), __byte_perm(r[2], r[3], 0x0040), 0x5410);
+      } else {
+        uint32_t w = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w |= residual_one(lane8(aw[j], e, a_signed), lane8(bw[j], e, b_signed), rp) << (8 * e);
+        out[j] = w;
+      }
     }
     y[i] = make_uint4(out[0], out[1], out[2], out[3]);
   }
@@ -659,9 +688,47 @@ void residual_requant(const void* a, DT a_dt, const void* b, DT b_dt, void* y, D
   const bool as = a_dt == DT::I8, bs = b_dt == DT::I8;
   int64_t n16 = 0;
   if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) & 15) == 0) n16 = n / 16;
-  if (n16 > 0) residual_requant_kernel<<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
+  if (n16 > 0) {
+    if (rp.proven_fast) residual_requant_kernel<true><<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
+    else residual_requant_kernel<false><<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
+  }
   if (n16 * 16 < n)
     residual_requant_tail_kernel<<<grid_for(n - n16 * 16), kThreads, 0, s>>>((const uint8_t*)a, as, (const uint8_t*)b, bs, (uint8_t*)y, n16 * 16, n, rp);
+}
+
+// Host restatement of both device formulas (IEEE single precision, one rounding per operation,
+// fused multiply-add through fmaf), compared over every pair of input bytes.
+void residual_requant_prepare(ResidualParams& rp, DT a_dt, DT b_dt) {
+  rp.proven_fast = 0;
+  rp.y_rcp = 0.f;
+  auto sane = [](float v) { return std::isfinite(v) && std::fabs(v) >= 9.5367431640625e-07f && std::fabs(v) <= 1048576.0f; };  // 2^-20 .. 2^20
+  if (!sane(rp.a_scale) || !sane(rp.b_scale) || !sane(rp.y_scale)) return;
+  if (!(std::fabs(rp.a_zp) <= 255.f && std::fabs(rp.b_zp) <= 255.f && std::fabs(rp.y_zp) <= 255.f)) return;
+  const float y_rcp = (float)(1.0 / (double)rp.y_scale);
+  const int a_lo = a_dt == DT::I8 ? -128 : 0, b_lo = b_dt == DT::I8 ? -128 : 0;
+  const float magic = 12582912.0f;
+  for (int ia = a_lo; ia < a_lo + 256; ++ia) {
+    volatile float va = ((float)ia - rp.a_zp) * rp.a_scale;
+    for (int ib = b_lo; ib < b_lo + 256; ++ib) {
+      volatile float vb = ((float)ib - rp.b_zp) * rp.b_scale;
+      volatile float sum = va + vb;
+      if (rp.relu) sum = std::fmax(sum, 0.f);
+      // reference: round_ties_even(sum / y_scale) + zero point, clamped
+      volatile float quot = sum / rp.y_scale;
+      volatile float ref = std::nearbyintf(quot) + rp.y_zp;
+      const float want = std::fmin(std::fmax(ref, rp.lo), rp.hi);
+      // fast path
+      volatile float q0 = sum * y_rcp;
+      volatile float rem = std::fmaf(-q0, rp.y_scale, sum);
+      volatile float q = std::fmaf(rem, y_rcp, q0);
+      volatile float t1 = q + magic;
+      volatile float t = t1 + rp.y_zp;
+      const float got = std::fmin(std::fmax(t, magic + rp.lo), magic + rp.hi) - magic;
+      if (!(got == want)) return;
+    }
+  }
+  rp.y_rcp = y_rcp;
+  rp.proven_fast = 1;
 }
 
 void s2d_pack(const TensorRef& src, void* dst, DT dst_dt, int c_pad, int sub, cudaStream_t s) {

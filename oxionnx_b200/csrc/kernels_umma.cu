@@ -71,7 +71,21 @@ struct alignas(64) KParams {
   int out_dt;
   void* out;
   int* err_flag;
+#ifdef OXB_UMMA_TRACE
+  long long* trace;  // diagnostics build only: per-tile role timestamps of CTA 0
+#endif
 };
+
+#ifdef OXB_UMMA_TRACE
+#define OXB_TRACE(tile, slot)                                                             \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && (tile) < 64 && lane == 0) p.trace[(tile) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define OXB_TRACE(tile, slot) \
+  do {                        \
+  } while (0)
+#endif
 
 // ---- PTX wrappers -----------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -485,7 +499,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     // ---------------- TMA producer ----------------
     uint32_t stage = 0, phase = 0;  // ring position, carried across tiles
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    int ptile = 0;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++ptile) {
+      OXB_TRACE(ptile, 0);
       const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
       const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
       int q0 = 0, p0 = 0, n0 = 0;
@@ -529,6 +545,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
           phase ^= 1u;
         }
       }
+      OXB_TRACE(ptile, 1);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -543,6 +560,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
       const uint32_t buf = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
+      OXB_TRACE(local, 2);
       // the epilogue must have drained this accumulator (free on the first two tiles)
       bool got = mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp);
       if (!__all_sync(0xffffffffu, got)) {
@@ -553,9 +571,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         break;
       }
       tc_fence_after();
+      OXB_TRACE(local, 3);
       const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
       for (int it = 0; it < k_iters; ++it) {
         got = mbar_wait(smem_u32(&bar_full[stage]), phase, abortp);
+        if (it == 0) OXB_TRACE(local, 4);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0 && !*abortp) {
             *abortp = 1;
@@ -580,6 +600,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       }
       if (ok && lane == 0) tc_commit(smem_u32(&bar_acc_full[buf]));  // accumulator complete
       __syncwarp();
+      OXB_TRACE(local, 5);
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
@@ -598,7 +619,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
       const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
       const uint32_t buf = local & 1u;
+      if (ew == 0) OXB_TRACE(local, 6);
       bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local >> 1) & 1u, abortp);
+      if (ew == 0) OXB_TRACE(local, 7);
       if (!ok && !*abortp) {
         *abortp = 1;
         atomicExch(p.err_flag, 3);
@@ -654,6 +677,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
 #pragma unroll
         for (int j = 0; j < 32; ++j) va[j] = vb[j];
       }
+      if (ew == 0) OXB_TRACE(local, 8);
+      if (ew == 3) OXB_TRACE(local, 9);
       // hand the accumulator back to the MMA issuer
       tc_fence_before();
       __syncwarp();
@@ -970,6 +995,12 @@ const char* umma_plan_desc(const UmmaPlan* p) { return p->desc; }
 void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {
   KParams kp = p->kp;
   kp.err_flag = err_flag;
+#ifdef OXB_UMMA_TRACE
+  static long long* trace_dev = nullptr;
+  if (!trace_dev) OXB_CUDA(cudaMalloc(&trace_dev, 64 * 16 * sizeof(long long)));
+  OXB_CUDA(cudaMemsetAsync(trace_dev, 0, 64 * 16 * sizeof(long long), s));
+  kp.trace = trace_dev;
+#endif
 #define OXB_UMMA_CASE(BN)                                             \
   case BN:                                                            \
     if (p->kind == 0) launch_t<BN, 0>(kp, p->grid, p->smem, s);       \
@@ -984,6 +1015,21 @@ void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {
   }
 #undef OXB_UMMA_CASE
   OXB_CUDA(cudaGetLastError());
+#ifdef OXB_UMMA_TRACE
+  if (std::getenv("OXB200_UMMA_TRACE")) {
+    static long long host[64 * 16];
+    OXB_CUDA(cudaStreamSynchronize(s));
+    OXB_CUDA(cudaMemcpy(host, trace_dev, sizeof host, cudaMemcpyDeviceToHost));
+    long long t0 = host[0];
+    fprintf(stderr, "trace %s\n tile:  prod0 prod1 | mma0 accfree full0 issued | epi0 accfull done0 done3\n", p->desc);
+    for (int t = 0; t < 40; ++t) {
+      if (!host[t * 16 + 0] && !host[t * 16 + 2]) break;
+      fprintf(stderr, " %3d:", t);
+      for (int k = 0; k < 10; ++k) fprintf(stderr, " %7lld%s", host[t * 16 + k] ? host[t * 16 + k] - t0 : -1, (k == 1 || k == 5) ? " |" : "");
+      fprintf(stderr, "\n");
+    }
+  }
+#endif
 }
 
 }  // namespace k

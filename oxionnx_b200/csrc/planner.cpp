@@ -1981,9 +1981,11 @@ bool Planner::try_plan_residual_chain(const NodeDef& n, int ni) {
   const int yi = add_value(q.outputs[0], va.shape, odt, va.shape.size() == 4 ? va.layout : Layout::PLAIN);
   const int64_t count = va.numel();
   const DT adt = va.dt, bdt = vb.dt;
+  k::residual_requant_prepare(rp, adt, bdt);
   Step& st = add_step(n, "residual_requant", 2, {ai, bi}, {yi});
   st.node_name = add.name;
   st.op_type = "DequantizeLinear+Add+Relu+QuantizeLinear";
+  st.kernel = rp.proven_fast ? "residual_requant (division-free, proven per parameter set)" : "residual_requant";
   st.work = 3.0 * (double)count;
   st.launch = [this, ai, bi, yi, adt, bdt, odt, count, rp](cudaStream_t s) {
     k::residual_requant(V(ai).ptr, adt, V(bi).ptr, bdt, V(yi).ptr, odt, count, rp, s);

@@ -131,3 +131,53 @@ def test_full_size_properties_resnet_qlinear():
     assert np.array_equal(yb, ya[:2])
     b.close()
     assert np.unique(ya).size > 100
+
+
+RESIDUAL_SETS = [
+    # a storage, a (scale, zp), b storage, b (scale, zp), y (scale, zp or None), relu
+    ("u8", (0.02, 0), "u8", (0.05, 0), (0.02, 0), True),           # the ResNet blocks
+    ("u8", (0.031, 128), "i8", (0.0173, -3), (0.043, 131), False),  # mixed storage, odd scales, no Relu
+    ("i8", (0.5, 0), "i8", (0.25, 5), (0.125, -7), True),           # powers of two: every quotient is exact, many ties
+    ("u8", (3.1e-7, 7), "u8", (2.9e-7, 0), (4.4e-7, None), False),  # scales outside the proven range: general kernel
+]
+
+
+@pytest.mark.parametrize("case", RESIDUAL_SETS, ids=[str(i) for i in range(len(RESIDUAL_SETS))])
+def test_residual_requantisation_chain_bit_exact(case):
+    """DequantizeLinear x2 -> Add -> [Relu] -> QuantizeLinear is planned as one kernel; its
+    division-free form is used only for parameter sets proven pair by pair on the host.  Both
+    forms must reproduce the node-by-node reference (oxionnx-ops src/indexing/quantize.rs)."""
+    from oxionnx_b200.graph import Graph, Node
+    a_st, (a_s, a_z), b_st, (b_s, b_z), (y_s, y_z), relu = case
+    rng = np.random.default_rng(5)
+    shape = (2, 48, 9, 7)
+    rng_of = {"u8": (0, 256), "i8": (-128, 128)}
+    a = rng.integers(*rng_of[a_st], shape).astype(np.float32)
+    b = rng.integers(*rng_of[b_st], shape).astype(np.float32)
+    # every pair of lanes at least once
+    grid = np.stack(np.meshgrid(np.arange(*rng_of[a_st]), np.arange(*rng_of[b_st]), indexing="ij"), 0).astype(np.float32)
+    weights = {"as": np.float32([a_s]), "az": np.float32([a_z]), "bs": np.float32([b_s]), "bz": np.float32([b_z]), "ys": np.float32([y_s]),
+               "one": np.float32([1.0])}
+    q_in = ["r", "ys"]
+    if y_z is not None:
+        weights["yz"] = np.float32([y_z])
+        q_in.append("yz")
+    # the operands reach the chain as 8-bit device tensors: quantise them with scale 1 first
+    weights["azq"] = np.float32([128 if a_st == "u8" else 0])
+    weights["bzq"] = np.float32([128 if b_st == "u8" else 0])
+    nodes = [Node("QuantizeLinear", "qa", ["a", "one", "azq"], ["aq"], {}), Node("QuantizeLinear", "qb", ["b", "one", "bzq"], ["bq"], {}),
+             Node("DequantizeLinear", "da", ["aq", "as", "az"], ["af"], {}), Node("DequantizeLinear", "db", ["bq", "bs", "bz"], ["bf"], {}),
+             Node("Add", "add", ["af", "bf"], ["s"], {})]
+    if relu:
+        nodes.append(Node("Relu", "relu", ["s"], ["r"], {}))
+    else:
+        q_in[0] = "s"
+    nodes += [Node("QuantizeLinear", "q", q_in, ["yq"], {}), Node("DequantizeLinear", "dq", ["yq", "ys"] + (["yz"] if y_z is not None else []), ["y"], {})]
+    graph = Graph(nodes=nodes, input_names=["a", "b"], output_names=["y"])
+    off_a, off_b = weights["azq"][0], weights["bzq"][0]
+    for feeds in ({"a": a - off_a, "b": b - off_b}, {"a": grid[0].reshape(1, 256, 16, 16) - off_a, "b": grid[1].reshape(1, 256, 16, 16) - off_b}):
+        sess, out, ref = run_both(graph, weights, feeds)
+        assert any(s["kernel"].startswith("residual_requant") for s in sess.steps()), [s["kernel"] for s in sess.steps()]
+        assert np.array_equal(sess.fetch_value("yq"), ref["yq"]), f"{np.sum(sess.fetch_value('yq') != ref['yq'])} lanes differ"
+        assert np.array_equal(out["y"], ref["y"])
+        sess.close()
