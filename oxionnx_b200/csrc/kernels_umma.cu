@@ -37,7 +37,11 @@ namespace k {
 namespace {
 
 constexpr int BLOCK_M = 128;
-constexpr int NUM_THREADS = 192;  // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2-5: epilogue
+// Eight epilogue warps, two per scheduler (one warp alone fills about half of its issue slots).
+// Ten warps put three on two of the four schedulers, whose register files hold 16384 registers
+// each: 168 registers per thread is the most this block shape can have.
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;  // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2-9: epilogue
 constexpr int MAX_STAGES = 12;
 constexpr long long WAIT_CYCLES = 2000000000LL;  // ~1 s at 2 GHz
 
@@ -46,7 +50,7 @@ struct alignas(64) KParams {
   CUtensorMap tmB;
   CUtensorMap tmO;
   int out_tma, out_row_bytes;
-  int dbg;  // timing experiments only: 1 skip the epilogue work, 2 TMEM reads only, 3 reads + math, 0 normal
+  int dbg;  // timing experiment only: 1 skips the epilogue work, 0 normal
   int a_im2col;
   int M, OC;
   int P, Q, S;
@@ -384,22 +388,18 @@ __device__ __forceinline__ void math_requant_fma(const KParams& p, const uint32_
 
 // Fused epilogue of one 32-channel run of one output pixel: bias / zero-point correction,
 // requantisation or activation, packed into 32-bit words (8 for 8-bit outputs, 16 for 16-bit,
-// 32 for 32-bit).  `oc` is the first channel of the run.
-__device__ __forceinline__ void epilogue_math(const KParams& p, const uint32_t (&v)[32], int xz, int oc, size_t esz, uint32_t (&w)[32]) {
-  switch (p.variant) {
-    case 0: math_f32<0, 0>(p, v, p.bias_f + oc, w); break;
-    case 1: math_f32<0, 1>(p, v, p.bias_f + oc, w); break;
-    case 2: math_f32<1, 0>(p, v, p.bias_f + oc, w); break;
-    case 3: math_f32<1, 1>(p, v, p.bias_f + oc, w); break;
-    case 4: math_f32<2, 0>(p, v, p.bias_f + oc, w); break;
-    case 5: math_f32<2, 1>(p, v, p.bias_f + oc, w); break;
-    case V_REQUANT: math_int<true, false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w); break;
-    case V_REQUANT_DYN: math_int<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w); break;
-    case V_INT32: math_int<false, false>(p, v, p.bias_i + oc, nullptr, nullptr, xz, esz, w); break;
-    case V_REQUANT_FMA: math_requant_fma<false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w); break;
-    case V_REQUANT_FMA_DYN: math_requant_fma<true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w); break;
-    default: math_int<false, true>(p, v, p.bias_i + oc, p.wsum + oc, nullptr, xz, esz, w); break;
-  }
+// 32 for 32-bit).  `oc` is the first channel of the run.  The variant is a template argument:
+// the whole tile loop of an epilogue warp is instantiated per variant, so the code a warp runs
+// is one straight body without a dispatch inside the loop.
+template <int VARIANT>
+__device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t (&v)[32], int xz, int oc, size_t esz, uint32_t (&w)[32]) {
+  if constexpr (VARIANT < V_REQUANT) math_f32<VARIANT / 2, VARIANT & 1>(p, v, p.bias_f + oc, w);
+  else if constexpr (VARIANT == V_REQUANT) math_int<true, false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w);
+  else if constexpr (VARIANT == V_REQUANT_DYN) math_int<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
+  else if constexpr (VARIANT == V_INT32) math_int<false, false>(p, v, p.bias_i + oc, nullptr, nullptr, xz, esz, w);
+  else if constexpr (VARIANT == V_INT32_DYN) math_int<false, true>(p, v, p.bias_i + oc, p.wsum + oc, nullptr, xz, esz, w);
+  else if constexpr (VARIANT == V_REQUANT_FMA) math_requant_fma<false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w);
+  else math_requant_fma<true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
 }
 
 // Direct store of a packed 32-channel run (ragged channel counts, unaligned rows).
@@ -448,6 +448,114 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                : "memory");
 }
 
+// ---- epilogue role ------------------------------------------------------------------------
+// Eight warps drain an accumulator: warp w may read the TMEM lanes 32 * (w % 4) .. + 31 (output
+// rows of the tile), and the two warps of a lane quarter split the tile's channel runs in two
+// contiguous halves.  Per run: TMEM read of the following run in flight, fused math, then
+// either a swizzled copy into this warp's 4 KB staging rows followed by one TMA store per
+// `pitch` bytes of row, or direct 16-byte stores.  The accumulator is handed back to the MMA
+// issuer as soon as this warp's last TMEM read has landed, before the last run's math.
+template <int BN, int VARIANT>
+__device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int lane, uint32_t tmem_base, uint64_t* bar_acc_full,
+                                              uint64_t* bar_acc_empty, uint32_t stage_addr, volatile int* abortp, int total_tiles) {
+  constexpr int CPW = BN >= 64 ? BN / 64 : 1;  // channel runs per warp and tile
+  const int quarter = warp & 3;
+  const int ew = warp - 2;
+  const int first = (ew >> 2) * CPW;
+  int xz = 0;
+  if (p.x_zp_dev) xz = __float2int_rn(*p.x_zp_dev);
+  const size_t esz = (p.out_dt == (int)DT::F32 || p.out_dt == (int)DT::I32) ? 4 : (p.out_dt == (int)DT::I16 ? 2 : 1);
+  const int chunk_bytes = 32 * (int)esz;
+  const int pitch = p.out_row_bytes;  // staged row length: 32, 64 or 128 bytes, at most one warp's share of a row
+  const int cpg = p.out_tma ? pitch / chunk_bytes : 1;
+  uint32_t local = 0;
+  for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+    const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
+    const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
+    const uint32_t buf = local & 1u;
+    if (ew == 0) OXB_TRACE(local, 6);
+    bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local >> 1) & 1u, abortp);
+    if (ew == 0) OXB_TRACE(local, 7);
+    if (!ok && !*abortp) {
+      *abortp = 1;
+      atomicExch(p.err_flag, 3);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    tc_fence_after();
+    const long long m = (long long)m0 + quarter * 32 + lane;
+    const bool row_ok = m < p.M;
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN;
+    const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;  // uniform across the CTA
+    const int end = min(first + CPW, n_chunks);           // this warp's runs: [first, end)
+    uint32_t va[32], vb[32], w[32];
+
+    auto release = [&]() {  // every TMEM read of this warp for this tile has landed
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+    };
+    auto emit = [&](const uint32_t(&v)[32], int ch) {
+      epilogue_chunk<VARIANT>(p, v, xz, oc0 + ch * 32, esz, w);
+      if (p.out_tma) {
+        const int in_group = (ch - first) % cpg;
+        if (in_group == 0) {
+          // the staging rows are rewritten: their previous store must have read them
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+        }
+        store_staged(w, stage_addr, lane, pitch, in_group * chunk_bytes, chunk_bytes);
+        if (in_group == cpg - 1 || ch == end - 1) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&p.tmO, stage_addr, oc0 + (ch - in_group) * 32, m0 + quarter * 32);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      } else if (row_ok) {
+        store_direct(w, (uint8_t*)p.out + ((size_t)m * p.OC + oc0 + ch * 32) * esz, esz, min(32, p.OC - (oc0 + ch * 32)));
+      }
+    };
+
+    if (p.dbg == 1 || first >= end) {  // timing experiment without epilogue work, or no run of this tile is ours
+      release();
+      continue;
+    }
+    tmem_ld32_nowait(taddr + (uint32_t)first * 32u, va);
+    tmem_ld_wait();
+    if constexpr (CPW == 1) {
+      release();
+      emit(va, first);
+    } else {
+#pragma unroll 1
+      for (int c = first; c < end; c += 2) {
+        // va holds run c; runs c+1 and c+2 are fetched while their predecessors are processed
+        if (c + 1 < end) {
+          tmem_ld32_nowait(taddr + (uint32_t)(c + 1) * 32u, vb);
+          emit(va, c);
+          tmem_ld_wait();
+          if (c + 2 < end) {
+            tmem_ld32_nowait(taddr + (uint32_t)(c + 2) * 32u, va);
+            emit(vb, c + 1);
+            tmem_ld_wait();
+          } else {
+            release();
+            emit(vb, c + 1);
+          }
+        } else {
+          release();
+          emit(va, c);
+        }
+      }
+    }
+    if (ew == 0) OXB_TRACE(local, 8);
+    if (ew == EPI_WARPS - 1) OXB_TRACE(local, 9);
+  }
+  if (p.out_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+
 template <int BN, int KIND>
 __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -457,8 +565,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  // per epilogue warp: two staging buffers of 32 rows x up to 128 bytes for the TMA stores
-  __shared__ __align__(1024) uint8_t s_stage[4][2][32 * 128];
+  // per epilogue warp: staging rows (32 x up to 128 bytes) for the TMA stores
+  __shared__ __align__(1024) uint8_t s_stage[EPI_WARPS][32 * 128];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int swz = p.swizzle_bytes;
@@ -477,7 +585,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bar_acc_full[i]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[i]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&bar_acc_empty[i]), EPI_WARPS);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -603,88 +711,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       OXB_TRACE(local, 5);
     }
   } else {
-    // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
-    const int quarter = warp & 3;
-    const int ew = warp - 2;
-    int xz = 0;
-    if (p.x_zp_dev) xz = __float2int_rn(*p.x_zp_dev);
-    const size_t esz = (p.out_dt == (int)DT::F32 || p.out_dt == (int)DT::I32) ? 4 : (p.out_dt == (int)DT::I16 ? 2 : 1);
-    const int chunk_bytes = 32 * (int)esz;
-    const int pitch = p.out_row_bytes;                 // staged row length: 32, 64 or 128 bytes
-    const int chunks_per_group = p.out_tma ? pitch / chunk_bytes : 1;
-    const uint32_t stage0 = smem_u32(&s_stage[ew][0][0]);
-    uint32_t groups = 0;  // TMA store groups issued by this warp
-    uint32_t local = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
-      const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
-      const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
-      const uint32_t buf = local & 1u;
-      if (ew == 0) OXB_TRACE(local, 6);
-      bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local >> 1) & 1u, abortp);
-      if (ew == 0) OXB_TRACE(local, 7);
-      if (!ok && !*abortp) {
-        *abortp = 1;
-        atomicExch(p.err_flag, 3);
+    // ---------------- epilogue: warps 2..9 ----------------
+    const uint32_t stage_addr = smem_u32(&s_stage[warp - 2][0]);
+#define OXB_EPI(V) \
+  case V: epilogue_role<BN, V>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
+    if constexpr (KIND == 0) {
+      switch (p.variant) {
+        OXB_EPI(V_REQUANT)
+        OXB_EPI(V_REQUANT_DYN)
+        OXB_EPI(V_INT32)
+        OXB_EPI(V_INT32_DYN)
+        OXB_EPI(V_REQUANT_FMA)
+        default: epilogue_role<BN, V_REQUANT_FMA_DYN>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
       }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const int row_in_tile = quarter * 32 + lane;
-      const long long m = (long long)m0 + row_in_tile;
-      const bool row_ok = m < p.M;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN;
-      const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;  // uniform across the CTA
-      uint32_t va[32], vb[32], w[32];
-      if (p.dbg == 1) {  // timing experiment: no epilogue work at all
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
-        continue;
+    } else {
+      switch (p.variant) {
+        OXB_EPI(0)
+        OXB_EPI(1)
+        OXB_EPI(2)
+        OXB_EPI(3)
+        OXB_EPI(4)
+        default: epilogue_role<BN, 5>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
       }
-      tmem_ld32_nowait(taddr, va);
-      tmem_ld_wait();
-#pragma unroll 1
-      for (int ch = 0; ch < n_chunks; ++ch) {
-        // software pipeline: the next chunk's TMEM read is in flight while this one is processed
-        if (ch + 1 < n_chunks) tmem_ld32_nowait(taddr + (uint32_t)(ch + 1) * 32u, vb);
-        const int c0 = ch * 32;
-        if (p.dbg != 2) epilogue_math(p, va, xz, oc0 + c0, esz, w);
-        if (p.dbg == 2 || p.dbg == 3) {
-          if (va[0] == 0x7fc12345u && w[5] == 0x7fc12345u && w[31] == 0x7fc12345u) atomicExch(p.err_flag, 9);
-        } else if (p.out_tma) {
-          const int in_group = ch % chunks_per_group;
-          const uint32_t sbuf = stage0 + (groups & 1u) * (uint32_t)(32 * 128);
-          if (in_group == 0) {
-            // the staging buffer about to be rewritten must have been read by its previous store
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            __syncwarp();
-          }
-          store_staged(w, sbuf, lane, pitch, in_group * chunk_bytes, chunk_bytes);
-          if (in_group == chunks_per_group - 1 || ch == n_chunks - 1) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-              const int col = oc0 + (ch - in_group) * 32;
-              tma_store_2d(&p.tmO, sbuf, col, m0 + quarter * 32);
-              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-            ++groups;
-          }
-        } else if (row_ok) {
-          store_direct(w, (uint8_t*)p.out + ((size_t)m * p.OC + oc0 + c0) * esz, esz, min(32, p.OC - (oc0 + c0)));
-        }
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) va[j] = vb[j];
-      }
-      if (ew == 0) OXB_TRACE(local, 8);
-      if (ew == 3) OXB_TRACE(local, 9);
-      // hand the accumulator back to the MMA issuer
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
     }
-    if (p.out_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+#undef OXB_EPI
   }
 
   // ---------------- teardown ----------------
@@ -905,7 +955,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   {
     // output tile store through TMA when rows are 16-byte granular
     const size_t oes = dt_size(e.out_dt);
-    const size_t row_bytes = std::min<size_t>(128, (size_t)bn * oes);
+    const size_t row_bytes = std::min<size_t>(128, (size_t)std::max(bn / 64, 1) * 32 * oes);  // at most one epilogue warp's share of a row
     kp.out_tma = 0;
     kp.out_row_bytes = (int)row_bytes;
     if (((size_t)cs.OC * oes) % 16 == 0 && ((uintptr_t)out & 15) == 0 && row_bytes >= 32 && (row_bytes & (row_bytes - 1)) == 0) {
