@@ -136,6 +136,7 @@ struct Epilogue {
   int n_w_zp = 0;
   // EPI_REQUANT: q = clamp(rne(f64(acc) * f64(combined[oc]) + y_zp), lo, hi)
   const float* combined = nullptr;
+  int64_t acc_abs_bound = 0;  // when > 0: no |raw + bias - x_zp * wsum| of this layer can exceed it (from the weights)
   int combined_fma_ok = 0;  // every combined[oc] is 0 or has 2^-21 <= |c| <= 2^40: the one-FMA requantisation is exact
   int y_zp = 0;
   int lo = 0, hi = 255;

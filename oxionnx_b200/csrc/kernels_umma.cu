@@ -235,7 +235,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // parallelism (one epilogue warp per scheduler has nothing else to hide latency with).
 // Per-channel parameters are read with 16-byte read-only loads; the host pads every
 // parameter vector to a multiple of 256 channels, so no bounds checks are needed here.
-enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9, V_REQUANT_FMA = 10, V_REQUANT_FMA_DYN = 11 };
+enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9, V_REQUANT_FMA = 10, V_REQUANT_FMA_DYN = 11, V_REQUANT_LEAN = 12, V_REQUANT_LEAN_DYN = 13 };
 
 template <int ACT, int RT>
 __device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias, uint32_t (&w)[32]) {
@@ -332,56 +332,62 @@ __device__ __forceinline__ void math_int(const KParams& p, const uint32_t (&v)[3
 // bits when |c| >= 2^-21, which the host checks before choosing this variant), so both sides
 // round the same real number the same way.  Values beyond +-2^22 leave the binade but stay
 // monotone, and the clamp (done on the float, before the bits are taken) sends them to the
-// same bound as the reference's.  A thread that meets |acc| >= 2^24 redoes its run with the
-// reference's own f64 operations.
-template <bool DYN>
+// same bound as the reference's.  A thread that meets |acc| >= 2^24 redoes those eight channels
+// with the reference's own f64 operations; when the host can bound every accumulator of the layer
+// below 2^24 from the weights, the variant without that check and second pass is used.
+template <bool DYN, bool FALLBACK>
 __device__ __forceinline__ void math_requant_fma(const KParams& p, const uint32_t (&v)[32], const int32_t* __restrict__ bias,
-                                                 const int32_t* __restrict__ wsum, const float* __restrict__ comb, int xz, size_t esz, uint32_t (&w)[32]) {
+                                                 const int32_t* __restrict__ wsum, const float* __restrict__ comb, int xz, size_t esz,
+                                                 uint32_t (&w)[32]) {
   const float magic = 12582912.0f;  // 1.5 * 2^23
   const float magic_zp = magic + (float)p.y_zp, flo = magic + (float)p.lo, fhi = magic + (float)p.hi;
-  float amax = 0.f;
-  uint32_t sb[32];
+  // eight channels at a time, packed at once: few values are live together, so that two runs can
+  // be in flight per warp (one in TMEM transit) inside the register budget of a ten-warp block
 #pragma unroll
-  for (int j4 = 0; j4 < 8; ++j4) {
-    const int4 b = __ldg(reinterpret_cast<const int4*>(bias) + j4);
-    const int bb[4] = {b.x, b.y, b.z, b.w};
-    int ss[4] = {0, 0, 0, 0};
-    if (DYN) {
-      const int4 sv = __ldg(reinterpret_cast<const int4*>(wsum) + j4);
-      ss[0] = sv.x, ss[1] = sv.y, ss[2] = sv.z, ss[3] = sv.w;
+  for (int g = 0; g < 4; ++g) {
+    float amax = 0.f;
+    uint32_t sb[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int j4 = 2 * g + h;
+      const int4 b = __ldg(reinterpret_cast<const int4*>(bias) + j4);
+      const int bb[4] = {b.x, b.y, b.z, b.w};
+      int ss[4] = {0, 0, 0, 0};
+      if (DYN) {
+        const int4 sv = __ldg(reinterpret_cast<const int4*>(wsum) + j4);
+        ss[0] = sv.x, ss[1] = sv.y, ss[2] = sv.z, ss[3] = sv.w;
+      }
+      const float4 c = __ldg(reinterpret_cast<const float4*>(comb) + j4);
+      const float cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        int32_t acc = (int32_t)v[4 * j4 + e] + bb[e];
+        if (DYN) acc -= xz * ss[e];
+        const float a = __int2float_rn(acc);
+        if (FALLBACK) amax = fmaxf(amax, fabsf(a));
+        sb[4 * h + e] = __float_as_uint(fminf(fmaxf(fmaf(a, cc[e], magic_zp), flo), fhi));
+      }
     }
-    const float4 c = __ldg(reinterpret_cast<const float4*>(comb) + j4);
-    const float cc[4] = {c.x, c.y, c.z, c.w};
+    // the value sits in the low mantissa bits (two's complement below 2^22): take its low byte,
+    // or its low half-word for the 16-bit lanes of the union range [-128, 255]
+    if (esz == 1) {
+      w[2 * g] = __byte_perm(__byte_perm(sb[0], sb[1], 0x0040), __byte_perm(sb[2], sb[3], 0x0040), 0x5410);
+      w[2 * g + 1] = __byte_perm(__byte_perm(sb[4], sb[5], 0x0040), __byte_perm(sb[6], sb[7], 0x0040), 0x5410);
+    } else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int j = 4 * j4 + e;
-      int32_t acc = (int32_t)v[j] + bb[e];
-      if (DYN) acc -= xz * ss[e];
-      const float a = __int2float_rn(acc);
-      amax = fmaxf(amax, fabsf(a));
-      const float s = fminf(fmaxf(fmaf(a, cc[e], magic_zp), flo), fhi);
-      sb[j] = __float_as_uint(s);
+      for (int k = 0; k < 4; ++k) w[4 * g + k] = __byte_perm(sb[2 * k], sb[2 * k + 1], 0x5410);
     }
-  }
-  // the value sits in the low mantissa bits (two's complement below 2^22): take its low byte,
-  // or its low half-word for the 16-bit lanes of the union range [-128, 255]
-  if (esz == 1) {
+    if (FALLBACK && amax >= 16777216.0f) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      w[j] = __byte_perm(__byte_perm(sb[4 * j], sb[4 * j + 1], 0x0040), __byte_perm(sb[4 * j + 2], sb[4 * j + 3], 0x0040), 0x5410);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) w[j] = __byte_perm(sb[2 * j], sb[2 * j + 1], 0x5410);
-  }
-  if (amax >= 16777216.0f) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      int32_t acc = (int32_t)v[j] + __ldg(bias + j);
-      if (DYN) acc -= xz * __ldg(wsum + j);
-      const double scaled = __dadd_rn(__dmul_rn((double)acc, (double)__ldg(comb + j)), (double)p.y_zp);
-      const uint32_t q = (uint32_t)min(max(__double2int_rn(scaled), p.lo), p.hi);
-      if (esz == 1) w[j >> 2] = (w[j >> 2] & ~(0xffu << (8 * (j & 3)))) | ((q & 0xffu) << (8 * (j & 3)));
-      else w[j >> 1] = (w[j >> 1] & ~(0xffffu << (16 * (j & 1)))) | ((q & 0xffffu) << (16 * (j & 1)));
+      for (int k = 0; k < 8; ++k) {
+        const int j = 8 * g + k;
+        int32_t acc = (int32_t)v[j] + __ldg(bias + j);
+        if (DYN) acc -= xz * __ldg(wsum + j);
+        const double scaled = __dadd_rn(__dmul_rn((double)acc, (double)__ldg(comb + j)), (double)p.y_zp);
+        const uint32_t q = (uint32_t)min(max(__double2int_rn(scaled), p.lo), p.hi);
+        if (esz == 1) w[j >> 2] = (w[j >> 2] & ~(0xffu << (8 * (j & 3)))) | ((q & 0xffu) << (8 * (j & 3)));
+        else w[j >> 1] = (w[j >> 1] & ~(0xffffu << (16 * (j & 1)))) | ((q & 0xffffu) << (16 * (j & 1)));
+      }
     }
   }
 }
@@ -398,8 +404,10 @@ __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t 
   else if constexpr (VARIANT == V_REQUANT_DYN) math_int<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
   else if constexpr (VARIANT == V_INT32) math_int<false, false>(p, v, p.bias_i + oc, nullptr, nullptr, xz, esz, w);
   else if constexpr (VARIANT == V_INT32_DYN) math_int<false, true>(p, v, p.bias_i + oc, p.wsum + oc, nullptr, xz, esz, w);
-  else if constexpr (VARIANT == V_REQUANT_FMA) math_requant_fma<false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w);
-  else math_requant_fma<true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
+  else if constexpr (VARIANT == V_REQUANT_FMA) math_requant_fma<false, true>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w);
+  else if constexpr (VARIANT == V_REQUANT_FMA_DYN) math_requant_fma<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
+  else if constexpr (VARIANT == V_REQUANT_LEAN) math_requant_fma<false, false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w);
+  else math_requant_fma<true, false>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
 }
 
 // Direct store of a packed 32-channel run (ragged channel counts, unaligned rows).
@@ -722,7 +730,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         OXB_EPI(V_INT32)
         OXB_EPI(V_INT32_DYN)
         OXB_EPI(V_REQUANT_FMA)
-        default: epilogue_role<BN, V_REQUANT_FMA_DYN>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
+        OXB_EPI(V_REQUANT_FMA_DYN)
+        OXB_EPI(V_REQUANT_LEAN)
+        default: epilogue_role<BN, V_REQUANT_LEAN_DYN>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
       }
     } else {
       switch (p.variant) {
@@ -1008,7 +1018,9 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   else if (e.mode == EPI_REQUANT) {
     const bool no_fma = std::getenv("OXB200_REQUANT_F64") != nullptr;  // keeps the two-pass variant reachable for tests
     const bool fma = e.combined_fma_ok && !no_fma;
-    kp.variant = e.x_zp_dev ? (fma ? V_REQUANT_FMA_DYN : V_REQUANT_DYN) : (fma ? V_REQUANT_FMA : V_REQUANT);
+    const bool lean = fma && e.acc_abs_bound > 0 && e.acc_abs_bound < 16777216;
+    if (e.x_zp_dev) kp.variant = lean ? V_REQUANT_LEAN_DYN : (fma ? V_REQUANT_FMA_DYN : V_REQUANT_DYN);
+    else kp.variant = lean ? V_REQUANT_LEAN : (fma ? V_REQUANT_FMA : V_REQUANT);
   }
   else kp.variant = e.x_zp_dev ? V_INT32_DYN : V_INT32;
   if (e.mode == EPI_F32 ? e.bias_f == nullptr : e.bias_i == nullptr) {

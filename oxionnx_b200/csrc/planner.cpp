@@ -782,13 +782,22 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
   // ---- epilogue parameter vectors ----
   k::Epilogue epi = c.epi;
   std::vector<int32_t> wsum(OC, 0);
+  int64_t acc_abs_bound = 0;  // max over channels of 255 * sum|w| + |bias| + 255 * |sum w|
   if (c.is_int)
     for (int oc = 0; oc < OC; ++oc) {
-      int64_t s = 0;
+      int64_t s = 0, sabs = 0;
       for (int ic = 0; ic < cg; ++ic)
-        for (int64_t t = 0; t < taps; ++t) s += wi_at(oc, ic, t);
+        for (int64_t t = 0; t < taps; ++t) {
+          const int64_t wv = wi_at(oc, ic, t);
+          s += wv;
+          sabs += wv < 0 ? -wv : wv;
+        }
       wsum[oc] = (int32_t)s;
+      const int64_t b = c.bias_i.empty() ? 0 : c.bias_i[oc];
+      const int64_t bound = 255 * sabs + (b < 0 ? -b : b) + 255 * (s < 0 ? -s : s);
+      acc_abs_bound = std::max(acc_abs_bound, bound);
     }
+  epi.acc_abs_bound = acc_abs_bound;
 
   const int x_vi = c.x_vi, out_vi = c.out_vi, xzp_vi = c.x_zp_vi;
   std::vector<int> reads = {x_vi};
