@@ -105,12 +105,28 @@ void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offse
 // input) or a channels-last activation; dst is channels-last [N, H/2, W/2, c_pad].
 void s2d_pack(const TensorRef& src, void* dst, DT dst_dt, int c_pad, int sub, cudaStream_t s);
 
+// The same packing laid out for row windows: dst is [N][H/2][wp][16] with `pad_left` zero pixels
+// in front of every row and zeros behind it, 16 lanes per pixel (4*C values, then zeros).  A
+// window of s consecutive pixels is then s*16 contiguous lanes, which the tensor-core kernel
+// reads as the "channels" of one filter-row tap (ConvShape::x_pixel_stride).  When `quantize` is
+// set the source is f32 and each value is first quantised exactly as QuantizeLinear does,
+// clamp(round_half_even(x / scale) + zp, lo, hi); `sub` is subtracted last.
+struct S2dQuant {
+  int quantize = 0;
+  float scale = 1.f, zp = 0.f, lo = 0.f, hi = 255.f;
+};
+void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, int wp, int sub, const S2dQuant& q, cudaStream_t s);
+
 // ---- contractions -----------------------------------------------------------------------
 struct ConvShape {
   int N, C, H, W;     // input (per group channels = C / group)
   int OC, R, S;       // filter
   int P, Q;           // output spatial
   int sh, sw, pt, pl, pb, pr, dh, dw, group;
+  // Tensor-core path only.  When non-zero, consecutive W positions of the stored activation are
+  // x_pixel_stride elements apart (less than C: neighbouring positions overlap) and a stored row
+  // holds x_row_pixels of them; zero means the dense layout (C and W).
+  int x_pixel_stride = 0, x_row_pixels = 0;
   int64_t M() const { return (int64_t)N * P * Q; }
   int64_t K() const { return (int64_t)(C / group) * R * S; }
   double ops() const { return 2.0 * (double)M() * (double)OC * (double)K(); }
@@ -155,6 +171,10 @@ void conv_direct(const void* x, DT x_dt, int x_plain_nchw, const void* w, DT w_d
 // side (stride 0), used for activation x activation products.
 void matmul_f32_direct(const float* a, const float* b, float* c, int64_t batch, int64_t M, int64_t K, int64_t N, int64_t a_bstride,
                        int64_t b_bstride, cudaStream_t s);
+
+// True when the driver accepts an im2col tensor map whose W stride is shorter than its channel
+// extent (overlapping positions), which the row-window stem layout needs.
+bool umma_overlapping_positions_ok();
 
 // tcgen05 implicit-GEMM plan (tensor maps are built once at plan time).
 struct UmmaPlan;

@@ -646,6 +646,50 @@ __global__ void s2d_pack_kernel(const void* src, DT sdt, Layout sl, Dims4 d, voi
   }
 }
 
+// One packed pixel (16 lanes) per thread.
+__global__ void s2d_window_pack_kernel(const void* src, DT sdt, Layout sl, Dims4 d, void* dst, DT ddt, int pad_left, int wp, int sub, S2dQuant q,
+                                       int64_t total) {
+  const int64_t H2 = d.H / 2, W2 = d.W / 2;
+  const int c4 = 4 * (int)d.C;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t xw = o % wp;
+    int64_t t = o / wp;
+    const int64_t y = t % H2;
+    const int64_t n = t / H2;
+    const int64_t x2 = xw - pad_left;
+    float v[16];
+#pragma unroll
+    for (int cp = 0; cp < 16; ++cp) {
+      v[cp] = 0.f;
+      if (cp < c4 && x2 >= 0 && x2 < W2) {
+        const int blk = cp / (int)d.C;
+        Coord qd;
+        qd.n = n;
+        qd.c = cp - blk * (int)d.C;
+        qd.h = 2 * y + (blk >> 1);
+        qd.w = 2 * x2 + (blk & 1);
+        float f = load_as_f32(src, sdt, encode(qd, sl, d));
+        if (q.quantize) f = fminf(fmaxf(__fadd_rn(rintf(__fdiv_rn(f, q.scale)), q.zp), q.lo), q.hi);
+        v[cp] = f - (float)sub;
+      }
+    }
+    if (ddt == DT::F32) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ((float4*)dst)[o * 4 + j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      const float lo = ddt == DT::U8 ? 0.f : -128.f, hi = ddt == DT::U8 ? 255.f : 127.f;
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w[j] = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[j] |= ((uint32_t)__float2int_rn(fminf(fmaxf(v[4 * j + e], lo), hi)) & 0xffu) << (8 * e);
+      }
+      ((uint4*)dst)[o] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 }  // namespace
 
 // =========================================================================================
@@ -736,6 +780,14 @@ void s2d_pack(const TensorRef& src, void* dst, DT dst_dt, int c_pad, int sub, cu
   if (total4 == 0) return;
   if (!(dst_dt == DT::F32 || dst_dt == DT::U8 || dst_dt == DT::I8)) OXB_FAIL("s2d_pack: unsupported storage type");
   s2d_pack_kernel<<<grid_for(total4), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, c_pad, sub, total4);
+}
+
+void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, int wp, int sub, const S2dQuant& q, cudaStream_t s) {
+  const int64_t total = src.d.N * (src.d.H / 2) * wp;
+  if (total == 0) return;
+  if (!(dst_dt == DT::F32 || dst_dt == DT::U8 || dst_dt == DT::I8) || 4 * src.d.C > 16) OXB_FAIL("s2d_window_pack: unsupported operand");
+  if (q.quantize && src.dt != DT::F32) OXB_FAIL("s2d_window_pack: quantisation needs an f32 source");
+  s2d_window_pack_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, pad_left, wp, sub, q, total);
 }
 
 void quantize_linear(const TensorRef& x, const TensorRef& y, const float* scale, int64_t n_scale, const float* zp, int64_t n_zp, float lo,

@@ -532,29 +532,18 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     }
     tmem_ld32_nowait(taddr + (uint32_t)first * 32u, va);
     tmem_ld_wait();
-    if constexpr (CPW == 1) {
-      release();
-      emit(va, first);
-    } else {
+    // one copy of the run's code in the loop (the instruction cache, not the 32 register moves, is
+    // what this loop is short of): the next run is in TMEM transit while this one is processed
 #pragma unroll 1
-      for (int c = first; c < end; c += 2) {
-        // va holds run c; runs c+1 and c+2 are fetched while their predecessors are processed
-        if (c + 1 < end) {
-          tmem_ld32_nowait(taddr + (uint32_t)(c + 1) * 32u, vb);
-          emit(va, c);
-          tmem_ld_wait();
-          if (c + 2 < end) {
-            tmem_ld32_nowait(taddr + (uint32_t)(c + 2) * 32u, va);
-            emit(vb, c + 1);
-            tmem_ld_wait();
-          } else {
-            release();
-            emit(vb, c + 1);
-          }
-        } else {
-          release();
-          emit(va, c);
-        }
+    for (int c = first; c < end; ++c) {
+      const bool more = c + 1 < end;
+      if (more) tmem_ld32_nowait(taddr + (uint32_t)(c + 1) * 32u, vb);
+      else release();
+      emit(va, c);
+      if (more) {
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) va[j] = vb[j];
       }
     }
     if (ew == 0) OXB_TRACE(local, 8);
@@ -846,6 +835,25 @@ bool umma_available() {
   return g_encode_tiled != nullptr && g_encode_im2col != nullptr;
 }
 
+bool umma_overlapping_positions_ok() {
+  static int state = -1;
+  if (state >= 0) return state == 1;
+  load_encoders();
+  state = 0;
+  if (!g_encode_im2col) return false;
+  // the shape of the 8-bit stem: 64-lane windows 16 lanes apart; nothing is read through this map
+  CUtensorMap tm;
+  cuuint64_t gdim[4] = {64, 112, 112, 2};
+  cuuint64_t gstr[3] = {16, 115 * 16, 112 * 115 * 16};
+  int lower[2] = {0, -2}, upper[2] = {0, -2};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult rc = g_encode_im2col(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, reinterpret_cast<void*>(uintptr_t(1) << 30), gdim, gstr, lower, upper, 64, BLOCK_M,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  state = rc == CUDA_SUCCESS ? 1 : 0;
+  return state == 1;
+}
+
 int umma_channel_block(int C, int kind) {
   int es = kind == 0 ? 1 : 4;
   int64_t row = (int64_t)C * es;
@@ -877,7 +885,8 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   const int64_t M = cs.M();
   if (M <= 0 || M > 0x7fffffffLL || cs.OC <= 0) return no("empty or oversized problem");
   if (((uintptr_t)x & 127) || ((uintptr_t)w_packed & 127) || ((uintptr_t)out & 15)) return no("operand base address is not aligned");
-  const bool gemm_like = cs.R == 1 && cs.S == 1 && cs.sh == 1 && cs.sw == 1 && cs.pt == 0 && cs.pl == 0 && cs.pb == 0 && cs.pr == 0;
+  const bool gemm_like = cs.R == 1 && cs.S == 1 && cs.sh == 1 && cs.sw == 1 && cs.pt == 0 && cs.pl == 0 && cs.pb == 0 && cs.pr == 0 &&
+                         cs.x_pixel_stride == 0 && cs.x_row_pixels == 0;
   if (!gemm_like) {
     // im2col corners and offsets are 8-bit quantities for two spatial dimensions
     int up_w = cs.pr - (cs.S - 1) * cs.dw, up_h = cs.pb - (cs.R - 1) * cs.dh;
@@ -928,8 +937,9 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     kp.a_im2col = 0;
   } else {
+    const int64_t pix = cs.x_pixel_stride > 0 ? cs.x_pixel_stride : cs.C, row = (cs.x_row_pixels > 0 ? cs.x_row_pixels : cs.W) * pix;
     cuuint64_t gdim[4] = {(cuuint64_t)cs.C, (cuuint64_t)cs.W, (cuuint64_t)cs.H, (cuuint64_t)cs.N};
-    cuuint64_t gstr[3] = {(cuuint64_t)cs.C * es, (cuuint64_t)cs.W * cs.C * es, (cuuint64_t)cs.H * cs.W * cs.C * es};
+    cuuint64_t gstr[3] = {(cuuint64_t)pix * es, (cuuint64_t)row * es, (cuuint64_t)cs.H * row * es};
     int lower[2] = {-cs.pl, -cs.pt};
     int upper[2] = {cs.pr - (cs.S - 1) * cs.dw, cs.pb - (cs.R - 1) * cs.dh};
     cuuint32_t estr[4] = {1, (cuuint32_t)cs.sw, (cuuint32_t)cs.sh, 1};
@@ -941,7 +951,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
     // published workaround clears bit 21 of the second descriptor word.
     int drv = 0;
     if (rc == CUDA_SUCCESS && cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010) {
-      size_t bytes = (size_t)cs.N * cs.H * cs.W * cs.C * es;
+      size_t bytes = (size_t)cs.N * cs.H * row * es;
       if (bytes < 131072) reinterpret_cast<uint64_t*>(&kp.tmA)[1] &= ~(1ull << 21);
     }
   }

@@ -642,6 +642,12 @@ void Planner::plan_quantize(const NodeDef& n) {
   float s0 = scale->data[0], z0 = zp ? zp->data[0] : 0.f;
   bool scalar = ns == 1 && nz <= 1;
   Step& st = add_step(n, "quantize_linear", 2, {xi}, {yi});
+  if (scalar) {
+    Value& yv = V(yi);
+    yv.q_src = xi;
+    yv.q_step = (int)S.steps_.size() - 1;
+    yv.q_scale = s0, yv.q_zp = z0, yv.q_lo = lo, yv.q_hi = hi;
+  }
   st.work = (double)V(xi).bytes + (double)V(yi).bytes;
   st.launch = [this, xr, yr, xi, yi, dscale, ns, dzp, nz, lo, hi, scalar, s0, z0](cudaStream_t s) {
     TensorRef a = bound(xr, xi), b = bound(yr, yi);
@@ -885,6 +891,7 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
   }
 
   // ---- direct kernel ----
+  if (cs.x_pixel_stride != 0) OXB_DECLINE("%s '%s': the row-window stem layout needs the tensor-core kernel (%s)", n.op.c_str(), n.name.c_str(), why.c_str());
   {
     const size_t es = c.is_int ? dt_size(c.w_dt) : 4;
     const size_t wbytes = (size_t)taps * cg * OC * es;
@@ -997,6 +1004,76 @@ bool Planner::try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi) {
   if (pb2 < 0 || pr2 < 0) return false;
   const int c4 = 4 * cs.C;
   const int es = c.is_int ? 1 : 4;
+  if (c4 <= 16 && S2 <= 8 && k::umma_overlapping_positions_ok()) {
+    // Row-window layout: 16 lanes per packed pixel, a zero halo on both sides of every row, and
+    // one filter-row tap = S2p neighbouring pixels = S2p * 16 contiguous lanes.  The convolution
+    // the kernel sees has R2 taps of S2p * 16 "channels" each (positions overlap, 16 lanes apart).
+    const int S2p = S2 <= 2 ? 2 : (S2 <= 4 ? 4 : 8);
+    const int CP = 16, Cw = S2p * CP;
+    const int wp = pl2 + W2 + pr2 + (S2p - S2);
+    const HostTensor* w = c.w;
+    made_consts_.emplace_back();
+    HostTensor& w2 = made_consts_.back();
+    w2.shape = {cs.OC, Cw, R2, 1};
+    w2.data.assign((size_t)cs.OC * Cw * R2, 0.f);
+    for (int oc = 0; oc < cs.OC; ++oc)
+      for (int bh = 0; bh < 2; ++bh)
+        for (int bw = 0; bw < 2; ++bw)
+          for (int ch = 0; ch < cs.C; ++ch)
+            for (int a = 0; a < R2; ++a)
+              for (int b = 0; b < S2; ++b) {
+                const int r = 2 * a + bh - eh, s = 2 * b + bw - ew;
+                if (r < 0 || r >= cs.R || s < 0 || s >= cs.S) continue;
+                const int lane = b * CP + (bh * 2 + bw) * cs.C + ch;
+                w2.data[((size_t)oc * Cw + lane) * R2 + a] = w->data[(((size_t)oc * cs.C + ch) * cs.R + r) * cs.S + s];
+              }
+    // quantise on the way when the activation is the sole product of the QuantizeLinear just planned
+    k::S2dQuant q;
+    int read_vi = src_vi;
+    if (c.is_int && xv.q_src >= 0 && xv.q_step == (int)S.steps_.size() - 1 && !C.cfg().keep_intermediates && !graph_outputs_.count(xv.name) &&
+        V(xv.q_src).shape.size() == 4) {
+      auto it = consumers_.find(xv.name);
+      if (it != consumers_.end() && it->second.size() == 1) {
+        q.quantize = 1;
+        q.scale = xv.q_scale, q.zp = xv.q_zp, q.lo = xv.q_lo, q.hi = xv.q_hi;
+        read_vi = xv.q_src;
+        S.steps_.pop_back();
+        V(src_vi).producer = -1;
+      }
+    }
+    const Value rv = V(read_vi);
+    std::vector<int64_t> pshape = {cs.N, CP, H2, wp};
+    int pv = add_value(xv.name + "@s2dw", pshape, pdt, Layout::NHWC);
+    k::TensorRef src{nullptr, rv.dt, effective_layout(rv), dims_of(rv)};
+    if (order_free(rv)) src.layout = Layout::NHWC;
+    Step& st = add_step(n, q.quantize ? "quantize+s2d_window_pack" : "s2d_window_pack", 2, {read_vi}, {pv});
+    st.work = (double)rv.bytes + (double)V(pv).bytes;
+    const DT pdt_c = pdt;
+    st.launch = [this, src, read_vi, pv, pdt_c, pl2, wp, sub, q](cudaStream_t s) {
+      k::s2d_window_pack(bound(src, read_vi), V(pv).ptr, pdt_c, pl2, wp, sub, q, s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    c.algorithmic_ops = cs.ops();
+    c.w_cacheable = cacheable_const(c.w_name) ? 1 : 0;
+    c.w = &w2;
+    c.w_name = c.w_name + "@s2dw";
+    c.x_vi = pv;
+    c.x_plain_nchw = false;
+    c.x_zp = 0;
+    cs.C = Cw;
+    cs.H = H2;
+    cs.W = cs.Q;  // window start positions per row
+    cs.R = R2;
+    cs.S = 1;
+    cs.sh = cs.sw = 1;
+    cs.pt = pt2;
+    cs.pb = pb2;
+    cs.pl = cs.pr = 0;
+    cs.x_pixel_stride = CP;
+    cs.x_row_pixels = wp;
+    return true;
+  }
   int c_pad = 0;
   for (int bytes : {32, 64, 128})
     if (c4 * es <= bytes) {

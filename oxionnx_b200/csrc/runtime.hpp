@@ -72,6 +72,10 @@ struct Value {
   size_t bytes = 0;
   int slot = -1;
   void* ptr = nullptr;
+  // produced by a per-tensor QuantizeLinear of the f32 value q_src in step q_step (planner use:
+  // a consumer that repacks the tensor anyway may quantise on the way and drop that step)
+  int q_src = -1, q_step = -1;
+  float q_scale = 1.f, q_zp = 0.f, q_lo = 0.f, q_hi = 255.f;
   int64_t numel() const { return prod(shape); }
 };
 
