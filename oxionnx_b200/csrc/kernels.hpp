@@ -141,6 +141,9 @@ struct Epilogue {
   int act = 0;
   float clip_lo = 0.f, clip_hi = 0.f;
   int round_tf32 = 0;
+  // EPI_F32 with a fused residual: out = act((acc + bias_f[oc]) + residual[m * OC + oc]); the two
+  // additions round as the separate Conv and Add nodes do
+  const float* residual = nullptr;
   // integer modes.  Direct kernels subtract zero points per element; the tensor-core kernel
   // computes raw = sum(x*w) and applies acc = raw + bias_i[oc] - x_zp * wsum[oc].
   const int32_t* bias_i = nullptr;

@@ -56,7 +56,8 @@ struct alignas(64) KParams {
   int P, Q, S;
   int sh, sw, pt, pl, dh, dw;
   int taps, cblocks, cb_elems;
-  int swizzle_bytes;  // 128, 64 or 32: bytes of K per stage row
+  int swizzle_bytes;  // 128, 64 or 32: bytes of K per shared-memory row (one K block)
+  int kpb;            // K blocks per ring stage: one barrier round trip moves this many
   int stages;
   int n_tiles, m_tiles;
   uint32_t idesc;
@@ -64,6 +65,7 @@ struct alignas(64) KParams {
   int mode;
   int variant;  // which epilogue_math instantiation runs
   const float* bias_f;
+  const float* residual;  // f32 [M, OC] added after the bias, or null
   int act;
   float clip_lo, clip_hi;
   int round_tf32;
@@ -85,7 +87,14 @@ struct alignas(64) KParams {
   do {                                                                                   \
     if (blockIdx.x == 0 && (tile) < 64 && lane == 0) p.trace[(tile) * 16 + (slot)] = clock64(); \
   } while (0)
+#define OXB_TRACE_K(tile, it, slot)                                                                              \
+  do {                                                                                                          \
+    if (blockIdx.x == 0 && (tile) == 3 && (it) < 24 && lane == 0) p.trace[(40 + (it)) * 16 + (slot)] = clock64(); \
+  } while (0)
 #else
+#define OXB_TRACE_K(tile, it, slot) \
+  do {                              \
+  } while (0)
 #define OXB_TRACE(tile, slot) \
   do {                        \
   } while (0)
@@ -235,17 +244,24 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // parallelism (one epilogue warp per scheduler has nothing else to hide latency with).
 // Per-channel parameters are read with 16-byte read-only loads; the host pads every
 // parameter vector to a multiple of 256 channels, so no bounds checks are needed here.
-enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9, V_REQUANT_FMA = 10, V_REQUANT_FMA_DYN = 11, V_REQUANT_LEAN = 12, V_REQUANT_LEAN_DYN = 13 };
+enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9, V_REQUANT_FMA = 10, V_REQUANT_FMA_DYN = 11, V_REQUANT_LEAN = 12, V_REQUANT_LEAN_DYN = 13, V_F32_RES = 14 };  // 14..19: the float variants with a residual
 
-template <int ACT, int RT>
-__device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias, uint32_t (&w)[32]) {
+template <int ACT, int RT, bool RES>
+__device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias, const float* __restrict__ res,
+                                         uint32_t (&w)[32]) {
 #pragma unroll
   for (int j4 = 0; j4 < 8; ++j4) {
     const float4 b = __ldg(reinterpret_cast<const float4*>(bias) + j4);
     const float bb[4] = {b.x, b.y, b.z, b.w};
+    float rr[4] = {0.f, 0.f, 0.f, 0.f};
+    if (RES && res != nullptr) {  // this pixel's 32 channels of the residual: one full 128-byte line per thread
+      const float4 r = __ldg(reinterpret_cast<const float4*>(res) + j4);
+      rr[0] = r.x, rr[1] = r.y, rr[2] = r.z, rr[3] = r.w;
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float f = __uint_as_float(v[4 * j4 + e]) + bb[e];
+      if (RES) f = __fadd_rn(f, rr[e]);
       if (ACT == 1) f = fmaxf(f, 0.f);
       if (ACT == 2) f = fminf(fmaxf(f, p.clip_lo), p.clip_hi);
       if (RT) f = round_tf32(f);
@@ -398,8 +414,9 @@ __device__ __forceinline__ void math_requant_fma(const KParams& p, const uint32_
 // the whole tile loop of an epilogue warp is instantiated per variant, so the code a warp runs
 // is one straight body without a dispatch inside the loop.
 template <int VARIANT>
-__device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t (&v)[32], int xz, int oc, size_t esz, uint32_t (&w)[32]) {
-  if constexpr (VARIANT < V_REQUANT) math_f32<VARIANT / 2, VARIANT & 1>(p, v, p.bias_f + oc, w);
+__device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t (&v)[32], int xz, int oc, size_t esz, const float* res, uint32_t (&w)[32]) {
+  if constexpr (VARIANT < V_REQUANT) math_f32<VARIANT / 2, VARIANT & 1, false>(p, v, p.bias_f + oc, nullptr, w);
+  else if constexpr (VARIANT >= V_F32_RES) math_f32<(VARIANT - V_F32_RES) / 2, (VARIANT - V_F32_RES) & 1, true>(p, v, p.bias_f + oc, res, w);
   else if constexpr (VARIANT == V_REQUANT) math_int<true, false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w);
   else if constexpr (VARIANT == V_REQUANT_DYN) math_int<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
   else if constexpr (VARIANT == V_INT32) math_int<false, false>(p, v, p.bias_i + oc, nullptr, nullptr, xz, esz, w);
@@ -504,7 +521,8 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
     };
     auto emit = [&](const uint32_t(&v)[32], int ch) {
-      epilogue_chunk<VARIANT>(p, v, xz, oc0 + ch * 32, esz, w);
+      const float* res = (VARIANT >= V_F32_RES && row_ok) ? p.residual + (size_t)m * p.OC + oc0 + ch * 32 : nullptr;
+      epilogue_chunk<VARIANT>(p, v, xz, oc0 + ch * 32, esz, res, w);
       if (p.out_tma) {
         const int in_group = (ch - first) % cpg;
         if (in_group == 0) {
@@ -568,7 +586,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int swz = p.swizzle_bytes;
   const uint32_t a_bytes = (uint32_t)BLOCK_M * swz, b_bytes = (uint32_t)BN * swz;
-  const uint32_t stage_bytes = a_bytes + b_bytes;
+  const uint32_t kb_bytes = a_bytes + b_bytes;           // one K block: activations, then weights
+  const uint32_t stage_bytes = kb_bytes * (uint32_t)p.kpb;  // one ring stage
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int k_iters = p.taps * p.cblocks;
   const int total_tiles = p.m_tiles * p.n_tiles;
@@ -618,8 +637,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       }
       const int w_base = q0 * p.sw - p.pl, h_base = p0 * p.sh - p.pt;
       int r = 0, sx = 0, cb = 0;
-      for (int it = 0; it < k_iters; ++it) {
+      // A barrier round trip, an expect_tx and each TMA instruction cost the issuing thread on the
+      // order of a hundred cycles, whatever the box size: a stage carries several K blocks when
+      // they are small, so that those costs are paid once per stage.
+      for (int it = 0; it < k_iters; it += p.kpb) {
+        OXB_TRACE_K(ptile, it, 0);
         bool got = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp);
+        OXB_TRACE_K(ptile, it, 1);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0 && !*abortp) {
             *abortp = 1;
@@ -628,23 +652,36 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
           ok = false;
           break;
         }
-        if (lane == 0) {
-          const uint32_t full = smem_u32(&bar_full[stage]);
-          mbar_expect_tx(full, stage_bytes);
-          const uint32_t a_dst = tiles_base + stage * stage_bytes, b_dst = a_dst + a_bytes;
-          const int c_off = cb * p.cb_elems;
-          if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
+        const int blocks = min(p.kpb, k_iters - it);
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        if (lane == 0) mbar_expect_tx(full, kb_bytes * (uint32_t)blocks);
+        // Lane g issues the loads of the stage's K block g: the copies of one thread are worked
+        // off one after the other, those of different threads side by side.
+        if (lane < blocks) {
+          int cb_l = cb + lane, sx_l = sx, r_l = r;  // (channel block, tap column, tap row) of K block it + lane
+          while (cb_l >= p.cblocks) {
+            cb_l -= p.cblocks;
+            if (++sx_l == p.S) {
+              sx_l = 0;
+              ++r_l;
+            }
+          }
+          const uint32_t a_dst = tiles_base + stage * stage_bytes + (uint32_t)lane * kb_bytes;
+          const int c_off = cb_l * p.cb_elems;
+          if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx_l * p.dw), (uint16_t)(r_l * p.dh));
           else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
-          tma_load_2d(b_dst, &p.tmB, full, it * p.cb_elems, oc0);
+          tma_load_2d(a_dst + a_bytes, &p.tmB, full, (it + lane) * p.cb_elems, oc0);
         }
-        __syncwarp();
-        if (++cb == p.cblocks) {
-          cb = 0;
+        cb += blocks;
+        while (cb >= p.cblocks) {
+          cb -= p.cblocks;
           if (++sx == p.S) {
             sx = 0;
             ++r;
           }
         }
+        OXB_TRACE_K(ptile, it, 2);
+        __syncwarp();
         if (++stage == (uint32_t)p.stages) {
           stage = 0;
           phase ^= 1u;
@@ -658,7 +695,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     const uint64_t desc_rest = make_smem_desc(0, swz);
     const uint32_t desc_hi = (uint32_t)(desc_rest >> 32), desc_lo = (uint32_t)desc_rest;
     const uint32_t idesc = p.idesc;
-    const uint32_t ring16 = tiles_base >> 4, stage16 = stage_bytes >> 4, a16_bytes = a_bytes >> 4;
+    const uint32_t ring16 = tiles_base >> 4, stage16 = stage_bytes >> 4, kb16 = kb_bytes >> 4, a16_bytes = a_bytes >> 4;
     uint32_t stage = 0, phase = 0, a16 = ring16;
     uint32_t local = 0;
     bool ok = true;
@@ -678,8 +715,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       tc_fence_after();
       OXB_TRACE(local, 3);
       const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
-      for (int it = 0; it < k_iters; ++it) {
+      for (int it = 0; it < k_iters; it += p.kpb) {
+        OXB_TRACE_K((int)local, it, 3);
         got = mbar_wait(smem_u32(&bar_full[stage]), phase, abortp);
+        OXB_TRACE_K((int)local, it, 4);
         if (it == 0) OXB_TRACE(local, 4);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0 && !*abortp) {
@@ -691,10 +730,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         }
         tc_fence_after();
         if (lane == 0) {
-          // descriptors differ between stages only in the 16-byte granular start address
-          tc_mma_block<KIND>(tmem_d, desc_lo | (a16 & 0x3fffu), desc_lo | ((a16 + a16_bytes) & 0x3fffu), desc_hi, idesc, it > 0 ? 1u : 0u, mmas);
+          // descriptors differ between K blocks only in the 16-byte granular start address
+          const int blocks = min(p.kpb, k_iters - it);
+          uint32_t b16 = a16;
+          for (int g = 0; g < blocks; ++g, b16 += kb16)
+            tc_mma_block<KIND>(tmem_d, desc_lo | (b16 & 0x3fffu), desc_lo | ((b16 + a16_bytes) & 0x3fffu), desc_hi, idesc, (it + g) > 0 ? 1u : 0u, mmas);
           tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
         }
+        OXB_TRACE_K((int)local, it, 5);
         __syncwarp();
         a16 += stage16;
         if (++stage == (uint32_t)p.stages) {
@@ -730,7 +773,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         OXB_EPI(2)
         OXB_EPI(3)
         OXB_EPI(4)
-        default: epilogue_role<BN, 5>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
+        OXB_EPI(5)
+        OXB_EPI(14)
+        OXB_EPI(15)
+        OXB_EPI(16)
+        OXB_EPI(17)
+        OXB_EPI(18)
+        default: epilogue_role<BN, 19>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
       }
     }
 #undef OXB_EPI
@@ -896,11 +945,14 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   }
   if (e.x_zp_rows || e.n_w_zp > 0) return no("per-row or weight zero points need the direct kernel");
 
-  // Tile width.  Measured on B200: one tcgen05.mma of 32 bytes of K costs about 150 ns whatever
-  // its N, and one SM fills its shared memory from L2 at about 70 GB/s.  A tile therefore takes
-  // max(k_steps * 150 ns, tile_bytes / 70 GB/s); the kernel runs ceil(tiles / SMs) rounds of
-  // tiles, and the last tile's epilogue (about 5 ns per column) is not hidden.  Pick the width
-  // that minimises that estimate; ties go to the wider tile (fewer re-reads of the activations).
+  // Tile width.  Measured on B200 (1.965 GHz): a tcgen05.mma of 32 bytes of K takes N/2 cycles
+  // of the tensor pipe but cannot be issued faster than one per ~56 cycles; one SM fills its
+  // shared memory from L2 at about 95 GB/s when all SMs do so; the fused epilogue costs about
+  // 0.08 ns per output for requantisation and 0.03 ns for the float variants, spread over eight
+  // warps.  The three overlap (ring of stages, two accumulators), so a tile takes the longest of
+  // them, the kernel runs ceil(tiles / SMs) rounds of tiles, and the last tile's epilogue is
+  // not hidden.  Pick the width that minimises that estimate; ties go to the wider tile (fewer
+  // re-reads of the activations).
   const int sms = sm_count();
   const int64_t m_tiles = ceil_div(M, BLOCK_M);
   const int bn_max = cs.OC <= 32 ? 32 : (cs.OC <= 64 ? 64 : (cs.OC <= 128 ? 128 : 256));
@@ -908,12 +960,15 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   {
     const double k_bytes = (double)cs.K() * es;
     const double k_steps = k_bytes / 32.0;
+    const double ns_out = e.mode == EPI_F32 ? 0.03e-9 : 0.08e-9;
     double best = 1e30;
     for (int cand = bn_max; cand >= 32; cand /= 2) {
       const double tiles = (double)m_tiles * (double)ceil_div(cs.OC, cand);
       const double rounds = std::ceil(tiles / sms);
-      const double t_tile = std::max(k_steps * 150e-9, (double)(BLOCK_M + cand) * k_bytes / 70e9);
-      const double t = rounds * t_tile + cand * 5e-9;
+      const double t_mma = k_steps * std::max(56.0, cand / 2.0) / 1.965e9;
+      const double t_feed = (double)(BLOCK_M + cand) * k_bytes / 95e9;
+      const double t_epi = (double)BLOCK_M * cand * ns_out;
+      const double t = rounds * std::max(t_mma, std::max(t_feed, t_epi)) + t_epi;
       if (t < best * 0.97) {
         best = t;
         bn = cand;
@@ -1016,7 +1071,15 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.n_tiles = (int)n_tiles;
   kp.m_tiles = (int)m_tiles;
   kp.idesc = make_idesc(kind, x_dt == DT::I8, w_dt == DT::I8, bn);
-  const size_t stage_bytes = (size_t)(BLOCK_M + bn) * swz;
+  // K blocks per stage: up to four small ones share a barrier round trip, as long as a stage stays
+  // within 64 KB (the ring then still has three stages)
+  const size_t kb_bytes = (size_t)(BLOCK_M + bn) * swz;
+  const int64_t k_iters_host = (int64_t)cs.R * cs.S * (cs.C / cb);
+  int kpb = 1;
+  while (kpb < 4 && (size_t)(kpb * 2) * kb_bytes <= 64 * 1024 && kpb * 2 <= k_iters_host) kpb *= 2;
+  if (const char* env = std::getenv("OXB200_UMMA_KPB")) kpb = std::max(1, std::min(4, std::atoi(env)));
+  kp.kpb = kpb;
+  const size_t stage_bytes = kb_bytes * kpb;
   // one persistent CTA per SM: the ring may use most of the 227 KB and runs on across tiles
   const size_t budget = 192 * 1024;
   int stages = (int)(budget / stage_bytes);
@@ -1024,7 +1087,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   if (stages < 2) stages = 2;
   kp.stages = stages;
   kp.mode = e.mode;
-  if (e.mode == EPI_F32) kp.variant = e.act * 2 + (e.round_tf32 ? 1 : 0);
+  if (e.mode == EPI_F32) kp.variant = e.act * 2 + (e.round_tf32 ? 1 : 0) + (e.residual ? V_F32_RES : 0);
   else if (e.mode == EPI_REQUANT) {
     const bool no_fma = std::getenv("OXB200_REQUANT_F64") != nullptr;  // keeps the two-pass variant reachable for tests
     const bool fma = e.combined_fma_ok && !no_fma;
@@ -1038,6 +1101,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
     return no("the tensor-core epilogue needs a (padded) bias vector");
   }
   kp.bias_f = e.bias_f;
+  kp.residual = e.residual;
   kp.act = e.act;
   kp.clip_lo = e.clip_lo;
   kp.clip_hi = e.clip_hi;
@@ -1056,8 +1120,8 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   pl->kind = kind;
   pl->grid = (int)std::min<int64_t>(m_tiles * n_tiles, sms);
   pl->smem = (size_t)stages * stage_bytes + 1024;
-  snprintf(pl->desc, sizeof pl->desc, "umma_%s M=%lld N=%d K=%lld tile=128x%dx%dB stages=%d %s", kind == 0 ? "i8" : "tf32", (long long)M, cs.OC,
-           (long long)cs.K(), bn, swz, stages, gemm_like ? "tiled" : "im2col");
+  snprintf(pl->desc, sizeof pl->desc, "umma_%s M=%lld N=%d K=%lld tile=128x%dx%dB stages=%dx%d %s", kind == 0 ? "i8" : "tf32", (long long)M, cs.OC,
+           (long long)cs.K(), bn, swz, stages, kpb, gemm_like ? "tiled" : "im2col");
   return pl;
 }
 
@@ -1098,6 +1162,13 @@ void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {
       if (!host[t * 16 + 0] && !host[t * 16 + 2]) break;
       fprintf(stderr, " %3d:", t);
       for (int k = 0; k < 10; ++k) fprintf(stderr, " %7lld%s", host[t * 16 + k] ? host[t * 16 + k] - t0 : -1, (k == 1 || k == 5) ? " |" : "");
+      fprintf(stderr, "\n");
+    }
+    fprintf(stderr, " tile 3 per K block: prod_wait0 prod_wait1 prod_issued | mma_wait0 mma_wait1 mma_issued\n");
+    for (int t = 40; t < 64; ++t) {
+      if (!host[t * 16 + 0] && !host[t * 16 + 3]) break;
+      fprintf(stderr, " %3d:", t - 40);
+      for (int k = 0; k < 6; ++k) fprintf(stderr, " %7lld%s", host[t * 16 + k] ? host[t * 16 + k] - t0 : -1, k == 2 ? " |" : "");
       fprintf(stderr, "\n");
     }
   }

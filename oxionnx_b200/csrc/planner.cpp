@@ -377,6 +377,7 @@ class Planner {
     bool x_zp_static = true;
     int x_zp = 0;
     int x_zp_vi = -1;            // device lane (dynamic)
+    int res_vi = -1;             // f32 residual added in the epilogue (a fused Add), or -1
     std::vector<int32_t> x_zp_rows;
     std::vector<int32_t> bias_i;  // empty or OC
     std::vector<float> bias_f;    // empty or OC
@@ -805,9 +806,10 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
     }
   epi.acc_abs_bound = acc_abs_bound;
 
-  const int x_vi = c.x_vi, out_vi = c.out_vi, xzp_vi = c.x_zp_vi;
+  const int x_vi = c.x_vi, out_vi = c.out_vi, xzp_vi = c.x_zp_vi, res_vi = c.res_vi;
   std::vector<int> reads = {x_vi};
   if (xzp_vi >= 0) reads.push_back(xzp_vi);
+  if (res_vi >= 0) reads.push_back(res_vi);
 
   if (want_umma) {
     const int kind = c.is_int ? 0 : 1;
@@ -870,15 +872,16 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
     const DT xdt = xv.dt, wdt = c.is_int ? c.w_dt : DT::F32;
     Step* stp = &st;
     const int step_index = (int)S.steps_.size() - 1;
-    st.finalize = [this, step_index, x_vi, out_vi, xzp_vi, wdev, xdt, wdt, cs, epi, kind, n]() mutable {
+    st.finalize = [this, step_index, x_vi, out_vi, xzp_vi, res_vi, wdev, xdt, wdt, cs, epi, kind, n]() mutable {
       k::Epilogue e = epi;
       if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
+      if (res_vi >= 0) e.residual = (const float*)V(res_vi).ptr;
       std::string why2;
       k::UmmaPlan* plan = k::umma_plan_create(V(x_vi).ptr, xdt, wdev, wdt, V(out_vi).ptr, cs, e, kind, &why2);
       if (!plan) OXB_FAIL("%s '%s': tensor-core plan rejected after selection: %s", n.op.c_str(), n.name.c_str(), why2.c_str());
       S.umma_plans_.push_back(plan);
       Step& me = S.steps_[step_index];
-      me.kernel = k::umma_plan_desc(plan);
+      me.kernel = std::string(k::umma_plan_desc(plan)) + (res_vi >= 0 ? " +residual" : "");
       int* err = S.err_flag_;
       me.launch = [this, plan, err](cudaStream_t s) {
         k::umma_launch(plan, err, s);
@@ -941,9 +944,10 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
     st.work_is_bytes = false;
     const DT xdt = xv.dt;
     const int plain = c.x_plain_nchw ? 1 : 0;
-    st.launch = [this, x_vi, out_vi, xzp_vi, wdev, xdt, wdt, cs, epi, plain](cudaStream_t s) {
+    st.launch = [this, x_vi, out_vi, xzp_vi, res_vi, wdev, xdt, wdt, cs, epi, plain](cudaStream_t s) {
       k::Epilogue e = epi;
       if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
+      if (res_vi >= 0) e.residual = (const float*)V(res_vi).ptr;
       k::conv_direct(V(x_vi).ptr, xdt, plain, wdev, wdt, V(out_vi).ptr, cs, e, s);
       C.counters.simt_launches++;
       C.counters.kernel_launches++;
@@ -1216,6 +1220,33 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
       c.x_vi = xi;
     } else {
       c.x_vi = ensure_layout(n, xi, Layout::NHWC);
+    }
+    // Conv -> Add(other) [-> Relu] with `other` already on the device in the same layout: the
+    // addition (and the Relu) move into this convolution's epilogue; the two float additions
+    // round exactly as the separate nodes would.
+    if (c.epi.act == 0 && !C.cfg().keep_intermediates && cs.OC % 32 == 0 && !graph_outputs_.count(out_name)) {
+      auto it = consumers_.find(out_name);
+      if (it != consumers_.end() && it->second.size() == 1) {
+        const int add_i = it->second[0].first, slot = it->second[0].second;
+        const NodeDef& add = nodes_[add_i];
+        if (!skipped_[add_i] && add.op == "Add" && add.inputs.size() == 2 && slot <= 1 && add.attrs.names().empty() && add.inputs[0] != add.inputs[1]) {
+          auto other = S.index_.find(add.inputs[1 - slot]);
+          if (other != S.index_.end()) {
+            const Value& ov = V(other->second);
+            if (ov.dt == DT::F32 && ov.shape == out_shape && ov.layout == Layout::NHWC && ov.host == nullptr) {
+              c.res_vi = other->second;
+              skipped_[add_i] = 1;
+              out_name = add.outputs[0];
+              const int relu_i = sole_consumer(out_name, "Relu");
+              if (relu_i >= 0) {
+                skipped_[relu_i] = 1;
+                c.epi.act = 1;
+                out_name = nodes_[relu_i].outputs[0];
+              }
+            }
+          }
+        }
+      }
     }
     c.out_vi = add_value(out_name, out_shape, DT::F32, Layout::NHWC);
     c.epi.round_tf32 = feeds_contraction(out_name) ? 1 : 0;

@@ -82,6 +82,11 @@ def test_resnet_f32_arena_reuse_matches_private_slots():
     assert np.array_equal(ya, yb)
     ca, cb = a.cuda_cache_counters(), b.cuda_cache_counters()
     assert cb["arena_bytes"] < ca["arena_bytes"] and cb["arena_slots"] < ca["arena_slots"]
+    # without the per-node copies the residual Add (+Relu) of every block runs inside a convolution's epilogue,
+    # with the same two roundings: the logits above are bit-identical to the node-by-node session's
+    kb = [s["kernel"] for s in b.steps()]
+    assert sum(k.endswith("+residual") for k in kb) == 16 and not any(k.startswith("binary") for k in kb), kb
+    assert sum(s["kernel"].startswith("binary") for s in a.steps()) == 16
     # a second run re-uploads activations only: weights stay resident, one fence per run
     before = b.cuda_cache_counters()
     yb2 = b.run(f)["logits"]
