@@ -17,6 +17,9 @@ One JSON line is printed by rank 0:
              CUDA-event durations, against the measured peak
   cpu_baseline  the CPU oracle (a port of the reference's CPU operators) timed on this host's
              cores on a bounded sample of the same workload
+  int8       (default workload, one GPU) the INT8 half of the headline metric measured in the same run:
+             the QLinearConv ResNet-50 at batch 128, images/s and the contraction kernel's TOP/s
+             against twice the measured bf16 rate
 
 `--impl reference` times that CPU port alone on all host threads (the reference itself is a Rust
 project and cannot be built in this environment).
@@ -51,6 +54,12 @@ def measured_peaks():
             p = json.load(fh)
         return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"], source="measured")
     return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+# DRAM bytes (read + written) per launch of the tensor-core kernel, averaged over the launches of one
+# step: dram__bytes_read.sum + dram__bytes_write.sum from the ncu launch lists summarised under profiles/
+# (launch_list_resnet50_f32_b32.md, launch_list_resnet50_int8_b128.md).  None: not captured.
+NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.41e6, "c5": 28.32e6, "c1": None}
 
 
 def build_workload(key, batch):
@@ -134,6 +143,35 @@ def cpu_baseline(key, graph_builder_batch, sample, threads):
     return sample / dt, dt
 
 
+def int8_companion(args, local_rank, flush_l2, peaks):
+    """The INT8 half of the headline metric, measured in the same run: the QLinearConv ResNet-50 at batch
+    128, inputs resident, L2 flushed between steps; images/s and the contraction kernel's TOP/s."""
+    from oxionnx_b200.session import Session
+    key = "c5"
+    w = WORKLOADS[key]
+    batch = w["batch"]
+    graph, weights, feeds, info = build_workload(key, batch)
+    sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).build_from_graph(graph, weights)
+    sess.upload(feeds(batch, "c5_companion"))
+    for _ in range(3):
+        sess.run_resident(1)
+    steps = min(args.steps, 10)
+    total_ms, conv_ms, conv_ops = 0.0, 0.0, 0.0
+    for _ in range(steps):
+        flush_l2()
+        total_ms += sess.run_resident(1)
+        for s in sess.steps():
+            if s["ms"] >= 0 and s["kernel"].startswith("umma"):
+                conv_ms += s["ms"]
+                conv_ops += s["work"]
+    sess.close()
+    tops = conv_ops / (conv_ms / 1000.0) / 1e12 if conv_ms > 0 else 0.0
+    peak = 2.0 * peaks["bf16_sustained"]
+    return {"workload": w["name"], "value": batch * steps / (total_ms / 1000.0), "unit": "images/s", "steps": steps, "ms_per_step": total_ms / steps,
+            "contraction_tops": tops, "peak_tops": peak, "frac": tops / peak, "peak_basis": f"2 x bf16_tflops_sustained of {peaks['source']}",
+            "traffic": NCU_TRAFFIC_PER_LAUNCH[key]}
+
+
 def run_reference(args, rank, world):
     """The reference arm: the CPU port of the reference's operators, all host threads."""
     if rank != 0:
@@ -171,6 +209,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-int8", action="store_true", help="skip the INT8 ResNet-50 companion measurement of the default workload")
     ap.add_argument("--kernel-path", default="auto", choices=["auto", "direct"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -286,7 +325,8 @@ def main():
         achieved = (conv_ops / (conv_ms / 1000.0) / 1e12) if conv_ms > 0 else 0.0
         roofline = {
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s" if kind == "i8" else "TFLOP/s",
-            "frac": achieved / peak if peak else None, "traffic": None,
+            "frac": achieved / peak if peak else None, "traffic": NCU_TRAFFIC_PER_LAUNCH.get(args.workload),
+            "traffic_note": "DRAM bytes per launch from the committed ncu launch list (profiles/), not measured in this run",
             "kernel": "umma_conv_kernel (tcgen05 implicit GEMM)", "launches_per_step": conv_launches // max(args.steps, 1),
             "avg_launch_ms": conv_ms / max(conv_launches, 1), "share_of_step": conv_ms / total_ms if world == 1 else None,
             "peak_basis": f"{factor} x bf16_tflops_sustained of {peaks['source']} ({peaks['bf16_sustained']})",
@@ -305,6 +345,8 @@ def main():
                            "glue": int(c1["glue_launches"] - c0["glue_launches"])},
             "roofline": roofline,
         }
+        if args.workload == "c2" and world == 1 and not args.no_int8:
+            line["int8"] = int8_companion(args, local_rank, flush_l2, peaks)
         if not args.no_cpu_baseline and world == 1:
             sample = {"c2": 2, "c5": 1, "c1": 64}[args.workload]
             cores = os.cpu_count() or 1

@@ -652,32 +652,42 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
           ok = false;
           break;
         }
-        const int blocks = min(p.kpb, k_iters - it);
-        const uint32_t full = smem_u32(&bar_full[stage]);
-        if (lane == 0) mbar_expect_tx(full, kb_bytes * (uint32_t)blocks);
-        // Lane g issues the loads of the stage's K block g: the copies of one thread are worked
-        // off one after the other, those of different threads side by side.
-        if (lane < blocks) {
-          int cb_l = cb + lane, sx_l = sx, r_l = r;  // (channel block, tap column, tap row) of K block it + lane
-          while (cb_l >= p.cblocks) {
-            cb_l -= p.cblocks;
-            if (++sx_l == p.S) {
-              sx_l = 0;
-              ++r_l;
+        if (p.kpb == 1) {
+          if (lane == 0) {  // one thread issues: every operand of the copies is warp-uniform
+            const uint32_t full = smem_u32(&bar_full[stage]);
+            mbar_expect_tx(full, kb_bytes);
+            const uint32_t a_dst = tiles_base + stage * stage_bytes;
+            const int c_off = cb * p.cb_elems;
+            if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
+            else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+            tma_load_2d(a_dst + a_bytes, &p.tmB, full, it * p.cb_elems, oc0);
+          }
+          if (++cb == p.cblocks) {
+            cb = 0;
+            if (++sx == p.S) {
+              sx = 0;
+              ++r;
             }
           }
-          const uint32_t a_dst = tiles_base + stage * stage_bytes + (uint32_t)lane * kb_bytes;
-          const int c_off = cb_l * p.cb_elems;
-          if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx_l * p.dw), (uint16_t)(r_l * p.dh));
-          else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
-          tma_load_2d(a_dst + a_bytes, &p.tmB, full, (it + lane) * p.cb_elems, oc0);
-        }
-        cb += blocks;
-        while (cb >= p.cblocks) {
-          cb -= p.cblocks;
-          if (++sx == p.S) {
-            sx = 0;
-            ++r;
+        } else {
+          const int blocks = min(p.kpb, k_iters - it);
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          if (lane == 0) mbar_expect_tx(full, kb_bytes * (uint32_t)blocks);
+          uint32_t a_dst = tiles_base + stage * stage_bytes;
+          for (int g = 0; g < blocks; ++g, a_dst += kb_bytes) {
+            if (lane == 0) {
+              const int c_off = cb * p.cb_elems;
+              if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
+              else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
+              tma_load_2d(a_dst + a_bytes, &p.tmB, full, (it + g) * p.cb_elems, oc0);
+            }
+            if (++cb == p.cblocks) {
+              cb = 0;
+              if (++sx == p.S) {
+                sx = 0;
+                ++r;
+              }
+            }
           }
         }
         OXB_TRACE_K(ptile, it, 2);
@@ -699,6 +709,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     uint32_t stage = 0, phase = 0, a16 = ring16;
     uint32_t local = 0;
     bool ok = true;
+    const bool one_block = p.kpb == 1;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
       const uint32_t buf = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
@@ -731,10 +742,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         tc_fence_after();
         if (lane == 0) {
           // descriptors differ between K blocks only in the 16-byte granular start address
-          const int blocks = min(p.kpb, k_iters - it);
-          uint32_t b16 = a16;
-          for (int g = 0; g < blocks; ++g, b16 += kb16)
-            tc_mma_block<KIND>(tmem_d, desc_lo | (b16 & 0x3fffu), desc_lo | ((b16 + a16_bytes) & 0x3fffu), desc_hi, idesc, (it + g) > 0 ? 1u : 0u, mmas);
+          if (one_block) {
+            tc_mma_block<KIND>(tmem_d, desc_lo | (a16 & 0x3fffu), desc_lo | ((a16 + a16_bytes) & 0x3fffu), desc_hi, idesc, it > 0 ? 1u : 0u, mmas);
+          } else {
+            const int blocks = min(p.kpb, k_iters - it);
+            uint32_t b16 = a16;
+            for (int g = 0; g < blocks; ++g, b16 += kb16)
+              tc_mma_block<KIND>(tmem_d, desc_lo | (b16 & 0x3fffu), desc_lo | ((b16 + a16_bytes) & 0x3fffu), desc_hi, idesc, (it + g) > 0 ? 1u : 0u, mmas);
+          }
           tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
         }
         OXB_TRACE_K((int)local, it, 5);
