@@ -4,7 +4,8 @@
 
 A step is one pass of the hot path over one batch of seeded synthetic input.  The default
 workload is ResNet-50 v1.5, f32 graph, batch 32 (TF32 tensor-core contractions); `c5` is the
-QLinearConv INT8 ResNet-50 at batch 128 per GPU, `c1` the INT8 MLP.  With N > 1 (launched by
+QLinearConv INT8 ResNet-50 at batch 128 per GPU, `c1` the INT8 MLP, `c3` the InSwapper-shaped f32
+generator at batch 16.  With N > 1 (launched by
 torchrun, one rank per GPU) every rank holds a full weight replica and runs its own batch:
 the path shards along the batch only, there is no data-path collective, and the scaling is weak.
 
@@ -44,6 +45,7 @@ WORKLOADS = {
     "c2": dict(name="resnet50_v1.5_f32_b32", metric="images_per_s", unit="images/s", dtype="tf32", batch=32),
     "c5": dict(name="resnet50_qlinearconv_int8_b128_per_gpu", metric="images_per_s", unit="images/s", dtype="i8", batch=128),
     "c1": dict(name="int8_mlp_64x1024-4096-4096-1024", metric="rows_per_s", unit="rows/s", dtype="i8", batch=64),
+    "c3": dict(name="inswapper128_shaped_f32_b16", metric="images_per_s", unit="images/s", dtype="tf32", batch=16),
 }
 
 
@@ -59,7 +61,7 @@ def measured_peaks():
 # DRAM bytes (read + written) per launch of the tensor-core kernel, averaged over the launches of one
 # step: dram__bytes_read.sum + dram__bytes_write.sum from the ncu launch lists summarised under profiles/
 # (launch_list_resnet50_f32_b32.md, launch_list_resnet50_int8_b128.md).  None: not captured.
-NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.41e6, "c5": 28.32e6, "c1": None}
+NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.41e6, "c5": 28.32e6, "c1": None, "c3": None}
 
 
 def build_workload(key, batch):
@@ -68,6 +70,8 @@ def build_workload(key, batch):
         return models.build_resnet50_f32(batch=batch)
     if key == "c5":
         return models.build_resnet50_qlinear(batch=batch)
+    if key == "c3":
+        return models.build_inswapper_f32(batch=batch)
     return models.build_int8_mlp(rows=batch)
 
 
@@ -178,7 +182,7 @@ def run_reference(args, rank, world):
         return
     w = WORKLOADS[args.workload]
     cores = os.cpu_count() or 1
-    sample = {"c2": 2, "c5": 1, "c1": 64}[args.workload]
+    sample = {"c2": 2, "c5": 1, "c1": 64, "c3": 1}[args.workload]
     times = []
     for i in range(args.warmup + args.steps):
         v, dt = cpu_baseline(args.workload, w["batch"], sample, cores)
@@ -190,7 +194,7 @@ def run_reference(args, rank, world):
     value = sample * steps / sum(times)
     line = {
         "impl": "reference", "metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
-        "ms_per_step": 1000.0 * sum(times) / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32" if args.workload == "c2" else "i64",
+        "ms_per_step": 1000.0 * sum(times) / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32" if args.workload in ("c2", "c3") else "i64",
         "data": "synthetic", "config": {"workload": w["name"], "sample": f"{sample} {w['unit'].split('/')[0]} per step"},
         "cpu_baseline": {"value": value, "unit": w["unit"], "cores": cores, "kind": "port",
                          "sample": f"{sample} {w['unit'].split('/')[0]} per step through the CPU oracle; the Rust reference cannot be built here"},
@@ -239,10 +243,12 @@ def main():
     sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).build_from_graph(graph, weights)
 
     # pinned host staging for the end-to-end leg
-    in_name = graph.input_names[0]
-    host_in, in_ptr = pinned_array(f[in_name].shape, lib)
-    host_in[...] = f[in_name]
-    feeds_pinned = {in_name: host_in}
+    feeds_pinned, pinned_ptrs = {}, []
+    for in_name in graph.input_names:
+        host_in, in_ptr = pinned_array(f[in_name].shape, lib)
+        host_in[...] = f[in_name]
+        feeds_pinned[in_name] = host_in
+        pinned_ptrs.append(in_ptr)
     sess.ensure_planned(feeds_pinned)
 
     # L2 flush between timed steps: a 256 MiB memset (L2 is 126 MB)
@@ -312,7 +318,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_total = float(t.item())
     e2e_value = world * batch * args.steps / (e2e_total / 1000.0)
-    h2d = int(host_in.size * 4)
+    h2d = int(sum(v.size for v in feeds_pinned.values()) * 4)
     d2h = int(sum(v.size for v in out.values()) * 4)
 
     if rank == 0:
@@ -348,13 +354,14 @@ def main():
         if args.workload == "c2" and world == 1 and not args.no_int8:
             line["int8"] = int8_companion(args, local_rank, flush_l2, peaks)
         if not args.no_cpu_baseline and world == 1:
-            sample = {"c2": 2, "c5": 1, "c1": 64}[args.workload]
+            sample = {"c2": 2, "c5": 1, "c1": 64, "c3": 1}[args.workload]
             cores = os.cpu_count() or 1
             v, dt = cpu_baseline(args.workload, batch, sample, cores)
             line["cpu_baseline"] = {"value": v, "unit": w["unit"], "cores": cores, "kind": "port",
                                     "sample": f"{sample} {w['unit'].split('/')[0]} through the CPU oracle in {dt:.1f} s"}
         print(json.dumps(line), flush=True)
-    lib.oxb200_host_free(in_ptr)
+    for ptr in pinned_ptrs:
+        lib.oxb200_host_free(ptr)
     sess.close()
     if dist is not None:
         dist.barrier()

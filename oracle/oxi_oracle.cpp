@@ -1094,6 +1094,69 @@ void op_concat(Ctx& c) {
   }
 }
 
+// Slice (oxionnx-ops src/registry/shape_ops/concat_slice_ops.rs:27-53, src/shape/sequence.rs:52-150):
+// starts/ends/axes/steps arrive as f32 lanes cast to i64 (saturating); negative start/end count
+// from the end of the axis, then clamp to [0, dim] (positive step) or [-1, dim-1] (negative
+// step); axes not named pass through whole.
+int64_t lane_as_i64(float v) {
+  if (std::isnan(v)) return 0;
+  if (v >= 9.2233720368547758e18f) return INT64_MAX;
+  if (v <= -9.2233720368547758e18f) return INT64_MIN;
+  return (int64_t)v;
+}
+
+void op_slice(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  const oxo_tensor& st = c.input(1);
+  const oxo_tensor& en = c.input(2);
+  const oxo_tensor* ax = c.optional(3);
+  const oxo_tensor* sp = c.optional(4);
+  const int64_t n = st.len;
+  if (en.len != n || (ax && ax->len != n) || (sp && sp->len != n)) fail(OXO_ERR_SHAPE_MISMATCH, "slice: starts/ends/axes/steps length mismatch");
+  const int rank = x.rank;
+  std::vector<int64_t> ds(rank, 0), de(rank), dp(rank, 1);
+  for (int d = 0; d < rank; ++d) de[d] = x.shape[d];
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t a = ax ? lane_as_i64(ax->data[i]) : i;
+    if (a < 0) a += rank;
+    if (a < 0 || a >= rank) fail(OXO_ERR_INVALID_MODEL, "slice: axis out of range");
+    const int64_t dim = x.shape[a];
+    const int64_t step = sp ? lane_as_i64(sp->data[i]) : 1;
+    if (step == 0) fail(OXO_ERR_INVALID_MODEL, "slice: steps must not be 0");
+    if (step == INT64_MIN) fail(OXO_ERR_INVALID_MODEL, "slice: steps out of range");
+    int64_t s0 = lane_as_i64(st.data[i]), e0 = lane_as_i64(en.data[i]);
+    if (s0 < 0) s0 += dim;  // a negative value plus a dimension cannot overflow
+    if (e0 < 0) e0 += dim;
+    if (step > 0) {
+      s0 = std::min(std::max<int64_t>(s0, 0), dim);
+      e0 = std::min(std::max<int64_t>(e0, 0), dim);
+    } else {
+      s0 = std::min(std::max<int64_t>(s0, -1), dim - 1);
+      e0 = std::min(std::max<int64_t>(e0, -1), dim - 1);
+    }
+    ds[a] = s0, de[a] = e0, dp[a] = step;
+  }
+  std::vector<int64_t> os(rank);
+  for (int d = 0; d < rank; ++d) {
+    if (dp[d] > 0) os[d] = de[d] <= ds[d] ? 0 : (de[d] - ds[d] + dp[d] - 1) / dp[d];
+    else os[d] = ds[d] <= de[d] ? 0 : (ds[d] - de[d] + (-dp[d]) - 1) / (-dp[d]);
+  }
+  alloc_out(c.out[0], os);
+  const int64_t total = c.out[0].len;
+  std::vector<int64_t> xs(rank, 1);
+  for (int d = rank - 2; d >= 0; --d) xs[d] = xs[d + 1] * x.shape[d + 1];
+  std::vector<int64_t> idx(rank, 0);
+  for (int64_t o = 0; o < total; ++o) {
+    int64_t src = 0;
+    for (int d = 0; d < rank; ++d) src += (ds[d] + idx[d] * dp[d]) * xs[d];
+    c.out[0].data[o] = x.data[src];
+    for (int d = rank - 1; d >= 0; --d) {
+      if (++idx[d] < os[d]) break;
+      idx[d] = 0;
+    }
+  }
+}
+
 void op_pad(Ctx& c) {
   const oxo_tensor& x = c.input(0);
   std::vector<int64_t> pads;
@@ -1257,6 +1320,7 @@ const OpEntry kOps[] = {
     {"Reshape", op_reshape, 1},
     {"Concat", op_concat, 1},
     {"Pad", op_pad, 1},
+    {"Slice", op_slice, 1},
     {"Resize", op_resize, 1},
     {"Cast", op_identity, 1},
     {"Identity", op_identity, 1},

@@ -86,7 +86,8 @@ void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaS
 void global_avg_pool(const TensorRef& x, const TensorRef& y, int round_tf32, cudaStream_t s);
 // OxiInstanceNorm over (n, c) planes, two-pass variance about the mean; optional fused
 // per-sample modulation y = norm * scale[n,c] + shift[n,c] (both may be NULL).
-void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const float* scale_nc, const float* shift_nc, cudaStream_t s);
+void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const float* scale_nc, const float* shift_nc, int relu, int round_tf32,
+                   cudaStream_t s);
 
 // ---- spatial glue -----------------------------------------------------------------------
 // mode 0 nearest, 1 linear; coord 0 half_pixel, 1 pytorch_half_pixel, 2 asymmetric,
@@ -97,6 +98,8 @@ void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, 
 // Copies `x` into the channel range [c_off, c_off + x.C) of `y` (Concat on the channel axis)
 // or, axis 0/2/3, the matching range of that axis.
 void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s);
+// Slice with unit steps over logical (row-major) axes padded to four: y[i] = x[i + start], dims as (N, C, H, W).
+void slice_rows(const void* x, void* y, DT dt, const Dims4& xd, const Dims4& yd, const Dims4& start, cudaStream_t s);
 
 // Space-to-depth packing for stride-2 convolutions over very few channels (the 3-channel
 // stem): dst[n][y][x][(bh*2+bw)*C + c] = src[n][c][2y+bh][2x+bw] - sub, channels padded with
@@ -116,6 +119,8 @@ struct S2dQuant {
   float scale = 1.f, zp = 0.f, lo = 0.f, hi = 255.f;
 };
 void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, int wp, int sub, const S2dQuant& q, cudaStream_t s);
+// The row-window layout for a stride-1 convolution over up to four f32 channels: [N][H][wp][4].
+void window_pack_f32(const TensorRef& src, void* dst, int pad_left, int wp, cudaStream_t s);
 
 // ---- contractions -----------------------------------------------------------------------
 struct ConvShape {

@@ -404,7 +404,7 @@ __global__ void global_avg_pool_nhwc_kernel(const float* __restrict__ x, float* 
 // Instance norm on NHWC: one block per (n, 32-channel group); 32 lanes across channels
 // (coalesced 128-byte rows), 8 warps striding over the pixels.
 __global__ void instance_norm_nhwc_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 d, float eps, const float* scale_nc,
-                                          const float* shift_nc) {
+                                          const float* shift_nc, int relu, int round_tf32_flag) {
   int64_t cgroups = (d.C + 31) / 32;
   int64_t n = blockIdx.x / cgroups, cg = blockIdx.x % cgroups;
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -442,7 +442,9 @@ __global__ void instance_norm_nhwc_kernel(const float* __restrict__ x, float* __
   if (valid)
     for (int64_t i = warp; i < hw; i += nwarps) {
       float v = (px[i * d.C] - mean) * inv_std;
-      if (mod) v = v * sc + sf;
+      if (mod) v = v * sc + sf;  // two roundings, as the separate Mul and Add nodes (this file is built without contraction)
+      if (relu) v = fmaxf(v, 0.f);
+      if (round_tf32_flag) v = round_tf32(v);
       py[i * d.C] = v;
     }
 }
@@ -690,6 +692,48 @@ __global__ void s2d_window_pack_kernel(const void* src, DT sdt, Layout sl, Dims4
   }
 }
 
+// y = x[start0 : start0 + Y0, start1 : ..., ...] over up to four logical (row-major) axes, unit steps.
+__global__ void slice_kernel(const void* x, void* y, int es, Dims4 xd, Dims4 yd, Dims4 start, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t t = o;
+    const int64_t i3 = t % yd.W;
+    t /= yd.W;
+    const int64_t i2 = t % yd.H;
+    t /= yd.H;
+    const int64_t i1 = t % yd.C;
+    const int64_t i0 = t / yd.C;
+    const int64_t src = (((i0 + start.N) * xd.C + (i1 + start.C)) * xd.H + (i2 + start.H)) * xd.W + (i3 + start.W);
+    if (es == 4) ((uint32_t*)y)[o] = ((const uint32_t*)x)[src];
+    else if (es == 2) ((uint16_t*)y)[o] = ((const uint16_t*)x)[src];
+    else ((uint8_t*)y)[o] = ((const uint8_t*)x)[src];
+  }
+}
+
+// Row-window packing without space-to-depth (stride-1 convolutions over up to four f32 channels):
+// dst is [N][H][wp][4], four lanes per pixel (C values, then zeros), `pad_left` zero pixels in front of
+// every row and zeros behind it.  One pixel (16 bytes) per thread.
+__global__ void window_pack_f32_kernel(const float* __restrict__ src, Layout sl, Dims4 d, float4* __restrict__ dst, int pad_left, int wp,
+                                       int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t xw = o % wp;
+    int64_t t = o / wp;
+    const int64_t y = t % d.H;
+    const int64_t n = t / d.H;
+    const int64_t x = xw - pad_left;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (x >= 0 && x < d.W) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (c < d.C) {
+          Coord q;
+          q.n = n, q.c = c, q.h = y, q.w = x;
+          v[c] = src[encode(q, sl, d)];
+        }
+    }
+    dst[o] = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
 }  // namespace
 
 // =========================================================================================
@@ -790,6 +834,13 @@ void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, i
   s2d_window_pack_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, pad_left, wp, sub, q, total);
 }
 
+void window_pack_f32(const TensorRef& src, void* dst, int pad_left, int wp, cudaStream_t s) {
+  const int64_t total = src.d.N * src.d.H * wp;
+  if (total == 0) return;
+  if (src.dt != DT::F32 || src.d.C > 4) OXB_FAIL("window_pack_f32: unsupported operand");
+  window_pack_f32_kernel<<<grid_for(total), kThreads, 0, s>>>((const float*)src.ptr, src.layout, src.d, (float4*)dst, pad_left, wp, total);
+}
+
 void quantize_linear(const TensorRef& x, const TensorRef& y, const float* scale, int64_t n_scale, const float* zp, int64_t n_zp, float lo,
                      float hi, cudaStream_t s) {
   int64_t total = y.d.numel();
@@ -882,11 +933,12 @@ void global_avg_pool(const TensorRef& x, const TensorRef& y, int round_tf32_flag
   global_avg_pool_nhwc_kernel<<<grid_for(total, 128), 128, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, round_tf32_flag);
 }
 
-void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const float* scale_nc, const float* shift_nc, cudaStream_t s) {
+void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const float* scale_nc, const float* shift_nc, int relu, int round_tf32_flag,
+                   cudaStream_t s) {
   int64_t cgroups = (x.d.C + 31) / 32;
   int64_t blocks = x.d.N * cgroups;
   if (blocks == 0) return;
-  instance_norm_nhwc_kernel<<<(unsigned)blocks, 256, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, eps, scale_nc, shift_nc);
+  instance_norm_nhwc_kernel<<<(unsigned)blocks, 256, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, eps, scale_nc, shift_nc, relu, round_tf32_flag);
 }
 
 void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, cudaStream_t s) {
@@ -900,6 +952,13 @@ void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, 
   int64_t total = y.d.numel();
   if (total == 0) return;
   pad_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, y.ptr, x.dt, x.layout, x.d, y.d, mode, value, pn, pc, ph, pw, total);
+}
+
+void slice_rows(const void* x, void* y, DT dt, const Dims4& xd, const Dims4& yd, const Dims4& start, cudaStream_t s) {
+  const int64_t total = yd.numel();
+  if (total == 0) return;
+  const int es = dt == DT::F32 || dt == DT::I32 ? 4 : (dt == DT::I16 ? 2 : 1);
+  slice_kernel<<<grid_for(total), kThreads, 0, s>>>(x, y, es, xd, yd, start, total);
 }
 
 void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s) {

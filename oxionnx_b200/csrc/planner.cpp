@@ -26,7 +26,8 @@ using k::TensorRef;
 const char* kSupportedOps[] = {"Conv",       "Gemm",     "MatMul",  "QLinearConv", "QLinearMatMul", "MatMulInteger",     "ConvInteger",
                                "QuantizeLinear", "DequantizeLinear", "DynamicQuantizeLinear", "Relu", "Tanh", "Sigmoid",    "PRelu",
                                "Add",        "Sub",      "Mul",     "Div",         "MaxPool",       "GlobalAveragePool", "OxiInstanceNorm",
-                               "Resize",     "Pad",      "Concat",  "Flatten",     "Reshape",       "Identity",          "Cast"};
+                               "Resize",     "Pad",      "Concat",  "Flatten",     "Reshape",       "Identity",          "Cast",
+                               "Slice"};
 
 // ---- scalar helpers that must agree with the reference bit for bit -----------------------
 double round_ties_even(double v) { return std::nearbyint(v); }  // default rounding mode: ties to even
@@ -359,6 +360,7 @@ class Planner {
   void plan_resize(const NodeDef& n);
   void plan_pad(const NodeDef& n);
   void plan_concat(const NodeDef& n);
+  void plan_slice(const NodeDef& n);
   void plan_alias(const NodeDef& n);
   bool try_plan_residual_chain(const NodeDef& n, int ni);
 
@@ -390,6 +392,7 @@ class Planner {
 
   void finalize_lifetimes_and_arena();
   bool try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi);
+  bool try_window_stem(const NodeDef& n, Contraction& c, int src_vi);
   std::deque<HostTensor> made_consts_;  // weights rewritten by the planner (space-to-depth stems)
 };
 
@@ -547,6 +550,7 @@ void Planner::plan_node(int ni) {
   const NodeDef& n = nodes_[ni];
   const std::string& op = n.op;
   if (!is_supported_op(op)) OXB_DECLINE("operator '%s' (node '%s') is not claimed by this provider", op.c_str(), n.name.c_str());
+  if (op == "Slice") return plan_slice(n);
   if (op == "QuantizeLinear") return plan_quantize(n);
   if (op == "DequantizeLinear") {
     if (try_plan_residual_chain(n, ni)) return;
@@ -1135,6 +1139,56 @@ bool Planner::try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi) {
   return true;
 }
 
+// A stride-1 float convolution over at most four channels (an image-space 7x7): four lanes per
+// pixel, and one filter-row tap = the S (rounded up to 2, 4 or 8) neighbouring pixels of a row, read
+// through a tensor map whose positions overlap, exactly as the space-to-depth stem does.
+bool Planner::try_window_stem(const NodeDef& n, Contraction& c, int src_vi) {
+  k::ConvShape& cs = c.cs;
+  const Value xv = V(src_vi);
+  if (c.is_int || xv.dt != DT::F32 || xv.shape.size() != 4) return false;
+  if (cs.group != 1 || cs.sh != 1 || cs.sw != 1 || cs.dh != 1 || cs.dw != 1 || cs.C > 4 || cs.S > 8 || cs.S < 2) return false;
+  if (!k::umma_overlapping_positions_ok()) return false;
+  const int Sp = cs.S <= 2 ? 2 : (cs.S <= 4 ? 4 : 8);
+  const int CP = 4, Cw = Sp * CP;
+  if (k::umma_channel_block(Cw, 1) == 0) return false;
+  const int wp = cs.pl + cs.W + cs.pr + (Sp - cs.S);
+  const HostTensor* w = c.w;
+  made_consts_.emplace_back();
+  HostTensor& w2 = made_consts_.back();
+  w2.shape = {cs.OC, Cw, cs.R, 1};
+  w2.data.assign((size_t)cs.OC * Cw * cs.R, 0.f);
+  for (int oc = 0; oc < cs.OC; ++oc)
+    for (int ch = 0; ch < cs.C; ++ch)
+      for (int r = 0; r < cs.R; ++r)
+        for (int sx = 0; sx < cs.S; ++sx)
+          w2.data[((size_t)oc * Cw + sx * CP + ch) * cs.R + r] = w->data[(((size_t)oc * cs.C + ch) * cs.R + r) * cs.S + sx];
+  std::vector<int64_t> pshape = {cs.N, CP, cs.H, wp};
+  int pv = add_value(xv.name + "@window", pshape, DT::F32, Layout::NHWC);
+  k::TensorRef src{nullptr, xv.dt, effective_layout(xv), dims_of(xv)};
+  if (order_free(xv)) src.layout = Layout::NHWC;
+  Step& st = add_step(n, "window_pack", 2, {src_vi}, {pv});
+  st.work = (double)xv.bytes + (double)V(pv).bytes;
+  const int pl = cs.pl;
+  st.launch = [this, src, src_vi, pv, pl, wp](cudaStream_t s) {
+    k::window_pack_f32(bound(src, src_vi), V(pv).ptr, pl, wp, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+  c.algorithmic_ops = cs.ops();
+  c.w_cacheable = cacheable_const(c.w_name) ? 1 : 0;
+  c.w = &w2;
+  c.w_name = c.w_name + "@window";
+  c.x_vi = pv;
+  c.x_plain_nchw = false;
+  cs.C = Cw;
+  cs.W = cs.Q;
+  cs.S = 1;
+  cs.pl = cs.pr = 0;
+  cs.x_pixel_stride = CP;
+  cs.x_row_pixels = wp;
+  return true;
+}
+
 void Planner::plan_conv_family(const NodeDef& n, int ni) {
   (void)ni;
   const std::string& op = n.op;
@@ -1215,6 +1269,8 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
     bool direct_nchw = xv.layout == Layout::PLAIN && !order_free(xv) && k::umma_channel_block(cs.C, 1) == 0;
     if (C.cfg().kernel_path == 0 && k::umma_available() && try_s2d_stem(n, c, xi)) {
       // the stride-2 few-channel stem became a stride-1 convolution over a space-to-depth copy
+    } else if (C.cfg().kernel_path == 0 && k::umma_available() && try_window_stem(n, c, xi)) {
+      // a stride-1 few-channel convolution reads row windows of a four-lane copy
     } else if (direct_nchw) {
       c.x_plain_nchw = true;
       c.x_vi = xi;
@@ -1806,13 +1862,51 @@ void Planner::plan_instance_norm(const NodeDef& n) {
   xi = ensure_layout(n, xi, Layout::NHWC);
   const Value xv = V(xi);
   float eps = n.attrs.f("epsilon", 1e-5f);
-  int yi = add_value(n.outputs[0], xv.shape, DT::F32, Layout::NHWC);
+  // AdaIN: OxiInstanceNorm -> Mul(scale[N,C,1,1]) -> Add(shift[N,C,1,1]) [-> Relu], the per-sample
+  // modulation the optimizer leaves as separate nodes (src/optimizer/fusion/instance_norm.rs:23-26),
+  // runs inside the normalisation's third pass with the same roundings.
+  std::string out_name = n.outputs[0];
+  int scale_vi = -1, shift_vi = -1, relu = 0;
+  if (!C.cfg().keep_intermediates) {
+    auto modulator = [&](const char* op) -> int {
+      if (graph_outputs_.count(out_name)) return -1;
+      auto it = consumers_.find(out_name);
+      if (it == consumers_.end() || it->second.size() != 1) return -1;
+      const int ni = it->second[0].first, slot = it->second[0].second;
+      const NodeDef& m = nodes_[ni];
+      if (skipped_[ni] || m.op != op || m.inputs.size() != 2 || slot > 1 || !m.attrs.names().empty()) return -1;
+      auto other = S.index_.find(m.inputs[1 - slot]);
+      if (other == S.index_.end()) return -1;
+      const Value& ov = V(other->second);
+      const std::vector<int64_t> want = {xv.shape[0], xv.shape[1], 1, 1};
+      if (ov.dt != DT::F32 || ov.shape != want || ov.host != nullptr) return -1;
+      skipped_[ni] = 1;
+      out_name = m.outputs[0];
+      return other->second;
+    };
+    scale_vi = modulator("Mul");
+    if (scale_vi >= 0) shift_vi = modulator("Add");
+    if (scale_vi >= 0) {
+      const int relu_i = sole_consumer(out_name, "Relu");
+      if (relu_i >= 0) {
+        skipped_[relu_i] = 1;
+        relu = 1;
+        out_name = nodes_[relu_i].outputs[0];
+      }
+    }
+  }
+  const int rt = scale_vi >= 0 && feeds_contraction(out_name) ? 1 : 0;
+  int yi = add_value(out_name, xv.shape, DT::F32, Layout::NHWC);
   TensorRef xr = ref_of(xi), yr = ref_of(yi);
   xr.layout = yr.layout = Layout::NHWC;
-  Step& st = add_step(n, "instance_norm", 2, {xi}, {yi});
+  std::vector<int> reads = {xi};
+  if (scale_vi >= 0) reads.push_back(scale_vi);
+  if (shift_vi >= 0) reads.push_back(shift_vi);
+  Step& st = add_step(n, scale_vi >= 0 ? "instance_norm+adain" : "instance_norm", 2, reads, {yi});
   st.work = 3.0 * (double)xv.bytes;
-  st.launch = [this, xr, yr, xi, yi, eps](cudaStream_t s) {
-    k::instance_norm(bound(xr, xi), bound(yr, yi), eps, nullptr, nullptr, s);
+  st.launch = [this, xr, yr, xi, yi, eps, scale_vi, shift_vi, relu, rt](cudaStream_t s) {
+    k::instance_norm(bound(xr, xi), bound(yr, yi), eps, scale_vi >= 0 ? (const float*)V(scale_vi).ptr : nullptr,
+                     shift_vi >= 0 ? (const float*)V(shift_vi).ptr : nullptr, relu, rt, s);
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };
@@ -1944,6 +2038,61 @@ void Planner::plan_concat(const NodeDef& n) {
     };
     off += V(xi).shape[axis];
   }
+}
+
+// Slice (shape_ops/concat_slice_ops.rs:27, shape/sequence.rs:52): initializer starts/ends/axes,
+// unit steps, rank <= 4; runs in the logical order, the output is a plain row-major tensor.
+void Planner::plan_slice(const NodeDef& n) {
+  check_attrs(n, {});
+  const HostTensor* st = const_in(n, 1);
+  const HostTensor* en = const_in(n, 2);
+  const HostTensor* ax = has_in(n, 3) ? const_in(n, 3) : nullptr;
+  const HostTensor* sp = has_in(n, 4) ? const_in(n, 4) : nullptr;
+  if (!st || !en || (has_in(n, 3) && !ax) || (has_in(n, 4) && !sp)) OXB_DECLINE("Slice '%s': starts / ends / axes / steps are not initializers", n.name.c_str());
+  int xi = value_of(in_name(n, 0));
+  const int rank = (int)V(xi).shape.size();
+  if (rank < 1 || rank > 4) OXB_DECLINE("Slice '%s': only ranks 1..4 are claimed", n.name.c_str());
+  const size_t cnt = st->data.size();
+  if (en->data.size() != cnt || (ax && ax->data.size() != cnt) || (sp && sp->data.size() != cnt)) OXB_DECLINE("slice: starts/ends/axes/steps length mismatch");
+  auto lane = [](float v) -> int64_t {
+    if (std::isnan(v)) return 0;
+    if (v >= 9.2233720368547758e18f) return INT64_MAX;
+    if (v <= -9.2233720368547758e18f) return INT64_MIN;
+    return (int64_t)v;
+  };
+  std::vector<int64_t> ds(rank, 0), de = V(xi).shape;
+  for (size_t i = 0; i < cnt; ++i) {
+    int64_t a = ax ? lane(ax->data[i]) : (int64_t)i;
+    if (a < 0) a += rank;
+    if (a < 0 || a >= rank) OXB_DECLINE("Slice '%s': axis out of range", n.name.c_str());
+    if (sp && lane(sp->data[i]) != 1) OXB_DECLINE("Slice '%s': only unit steps are claimed", n.name.c_str());
+    const int64_t dim = V(xi).shape[a];
+    int64_t s0 = lane(st->data[i]), e0 = lane(en->data[i]);
+    if (s0 < 0) s0 += dim;
+    if (e0 < 0) e0 += dim;
+    ds[a] = std::min(std::max<int64_t>(s0, 0), dim);
+    de[a] = std::min(std::max<int64_t>(e0, 0), dim);
+  }
+  std::vector<int64_t> os(rank);
+  for (int d = 0; d < rank; ++d) os[d] = de[d] <= ds[d] ? 0 : de[d] - ds[d];
+  if (rank == 4 && V(xi).layout == Layout::NHWC && !order_free(V(xi))) xi = ensure_layout(n, xi, Layout::PLAIN);
+  const Value xv = V(xi);
+  int yi = add_value(n.outputs[0], os, xv.dt, Layout::PLAIN);
+  auto pad4 = [&](const std::vector<int64_t>& v, int64_t fill) {
+    Dims4 d{fill, fill, fill, fill};
+    int64_t* f[4] = {&d.N, &d.C, &d.H, &d.W};
+    for (int i = 0; i < rank; ++i) *f[4 - rank + i] = v[i];
+    return d;
+  };
+  const Dims4 xd = pad4(xv.shape, 1), yd = pad4(os, 1), sd = pad4(ds, 0);
+  const DT dt = xv.dt;
+  Step& stp = add_step(n, "slice", 2, {xi}, {yi});
+  stp.work = 2.0 * (double)V(yi).bytes;
+  stp.launch = [this, xi, yi, dt, xd, yd, sd](cudaStream_t s) {
+    k::slice_rows(V(xi).ptr, V(yi).ptr, dt, xd, yd, sd, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
 }
 
 // Flatten / Reshape / Identity / Cast: the logical row-major order is untouched, so the output

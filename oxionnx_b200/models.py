@@ -244,3 +244,93 @@ def build_resnet50_qlinear(batch=128, image=224, base=64, blocks=(3, 4, 6, 3), c
         return {"input": _rng(seed_tag).standard_normal((b, 3, image, image)).astype(np.float32)}
 
     return graph, g.weights, feeds, dict(ops=2.0 * macs[0] * batch, macs_per_image=macs[0], batch=batch)
+
+
+# ---------------------------------------------------------------------------------------------
+# C3: InSwapper-128-shaped face-swap generator (float)
+# ---------------------------------------------------------------------------------------------
+def build_inswapper_f32(batch=16, size=128, widths=(128, 256, 512, 1024), blocks=6, latent=512):
+    """Encoder, `blocks` residual style blocks, decoder, 7x7 + Tanh, in the form the reference's
+    optimizer hands to an execution provider: the layer inventory of its own InSwapper parity
+    test (oxionnx-gpu/tests/c3_conv2d_parity.rs:80-164: 7x7 3->128 on the reflect-padded 134^2
+    image, 3x3 128->256, 3x3 stride 2 to 512 and to 1024, twelve pad-free 3x3 1024->1024 on
+    reflect-padded 34^2 maps, 3x3 1024->512 at 64^2, 512->256 and 256->128 at 128^2, 7x7 128->3),
+    every instance normalisation already fused into `OxiInstanceNorm` (epsilon 1e-8,
+    src/optimizer/fusion/instance_norm.rs:17,199) and followed by separate per-sample
+    Mul(scale[N,C,1,1]) and Add(shift[N,C,1,1]) nodes (instance_norm.rs:23-26) whose operands
+    come from one Gemm(latent -> 2*C) per normalisation.  Inputs: target image ~U[0,1], latent
+    ~N(0,1) L2-normalised per row.  Random-initialised weights stand in for the real model."""
+    g = _G()
+    r = _rng("c3")
+    macs = [0]
+    w0, w1, w2, w3 = widths
+
+    def conv(x, cin, cout, ksz, stride, pad, relu, hw, name):
+        fan_in = cin * ksz * ksz
+        g.w(f"{name}_w", r.standard_normal((cout, cin, ksz, ksz)).astype(np.float32) * np.float32(np.sqrt(2.0 / fan_in)))
+        g.w(f"{name}_b", (r.standard_normal(cout) * 0.05).astype(np.float32))
+        attrs = dict(strides=[stride, stride], pads=[pad] * 4, dilations=[1, 1], group=1, kernel_shape=[ksz, ksz])
+        if relu:
+            attrs["activation"] = "relu"
+        out_hw = _conv_out(hw, ksz, stride, pad)
+        macs[0] += out_hw * out_hw * cout * fan_in
+        return g.node("Conv", [x, f"{name}_w", f"{name}_b"], [f"{name}_out"], name=name, **attrs), out_hw
+
+    def reflect(x, p, name):
+        g.w(f"{name}_pads", [0, 0, p, p, 0, 0, p, p])
+        return g.node("Pad", [x, f"{name}_pads"], [f"{name}_out"], name=name, mode="reflect")
+
+    def adain(x, c, name):
+        """OxiInstanceNorm -> Mul(scale) -> Add(shift), scale/shift from one Gemm on the latent."""
+        g.w(f"{name}_fc_w", r.standard_normal((2 * c, latent)).astype(np.float32) * np.float32(np.sqrt(1.0 / latent)))
+        fc_b = np.concatenate([np.ones(c, np.float32), np.zeros(c, np.float32)]) + (r.standard_normal(2 * c) * 0.02).astype(np.float32)
+        g.w(f"{name}_fc_b", fc_b)
+        macs[0] += 2 * c * latent
+        style = g.node("Gemm", ["latent", f"{name}_fc_w", f"{name}_fc_b"], [f"{name}_style"], name=f"{name}_fc", alpha=1.0, beta=1.0, transB=1)
+        g.w(f"{name}_s0", [0]), g.w(f"{name}_s1", [c]), g.w(f"{name}_e1", [2 * c]), g.w(f"{name}_ax", [1]), g.w(f"{name}_shape", [-1, c, 1, 1])
+        sc = g.node("Slice", [style, f"{name}_s0", f"{name}_s1", f"{name}_ax"], [f"{name}_scale2d"], name=f"{name}_slice_scale")
+        sh = g.node("Slice", [style, f"{name}_s1", f"{name}_e1", f"{name}_ax"], [f"{name}_shift2d"], name=f"{name}_slice_shift")
+        sc = g.node("Reshape", [sc, f"{name}_shape"], [f"{name}_scale"], name=f"{name}_reshape_scale")
+        sh = g.node("Reshape", [sh, f"{name}_shape"], [f"{name}_shift"], name=f"{name}_reshape_shift")
+        y = g.node("OxiInstanceNorm", [x], [f"{name}_norm"], name=f"{name}_in", epsilon=1e-8)
+        y = g.node("Mul", [y, sc], [f"{name}_mul"], name=f"{name}_mul")
+        return g.node("Add", [y, sh], [f"{name}_mod"], name=f"{name}_add")
+
+    hw = size
+    x = reflect("target", 3, "enc0_pad")
+    x, hw = conv(x, 3, w0, 7, 1, 0, True, hw + 6, "enc0")
+    x, hw = conv(x, w0, w1, 3, 1, 1, True, hw, "enc1")
+    x, hw = conv(x, w1, w2, 3, 2, 1, True, hw, "enc2")
+    x, hw = conv(x, w2, w3, 3, 2, 1, True, hw, "enc3")
+    for bi in range(blocks):
+        name = f"s{bi}"
+        y = reflect(x, 1, f"{name}_pad1")
+        y, _ = conv(y, w3, w3, 3, 1, 0, False, hw + 2, f"{name}_c1")
+        y = adain(y, w3, f"{name}_a1")
+        y = g.node("Relu", [y], [f"{name}_relu"], name=f"{name}_act")
+        y = reflect(y, 1, f"{name}_pad2")
+        y, _ = conv(y, w3, w3, 3, 1, 0, False, hw + 2, f"{name}_c2")
+        y = adain(y, w3, f"{name}_a2")
+        x = g.node("Add", [y, x], [f"{name}_sum"], name=f"{name}_res")
+    g.w("up_scales", [1, 1, 2, 2])
+    up = dict(mode="linear", coordinate_transformation_mode="half_pixel")
+    x = g.node("Resize", [x, "", "up_scales"], ["up1"], name="up1", **up)
+    hw *= 2
+    x, hw = conv(x, w3, w2, 3, 1, 1, True, hw, "dec1")
+    x = g.node("Resize", [x, "", "up_scales"], ["up2"], name="up2", **up)
+    hw *= 2
+    x, hw = conv(x, w2, w1, 3, 1, 1, True, hw, "dec2")
+    x, hw = conv(x, w1, w0, 3, 1, 1, True, hw, "dec3")
+    x = reflect(x, 3, "out_pad")
+    x, hw = conv(x, w0, 3, 7, 1, 0, False, hw + 6, "out_conv")
+    g.node("Tanh", [x], ["image"], name="out_tanh")
+    graph = Graph(nodes=g.nodes, input_names=["target", "latent"], output_names=["image"])
+
+    def feeds(b=batch, seed_tag="c3_in"):
+        rr = _rng(seed_tag)
+        target = rr.uniform(0.0, 1.0, (b, 3, size, size)).astype(np.float32)
+        z = rr.standard_normal((b, latent)).astype(np.float32)
+        z /= np.sqrt(np.sum(z.astype(np.float64) ** 2, axis=1, keepdims=True)).astype(np.float32)
+        return {"target": target, "latent": z}
+
+    return graph, g.weights, feeds, dict(ops=2.0 * macs[0] * batch, macs_per_image=macs[0], batch=batch)

@@ -186,3 +186,30 @@ def test_residual_requantisation_chain_bit_exact(case):
         assert np.array_equal(sess.fetch_value("yq"), ref["yq"]), f"{np.sum(sess.fetch_value('yq') != ref['yq'])} lanes differ"
         assert np.array_equal(out["y"], ref["y"])
         sess.close()
+
+
+def test_inswapper_f32_small_per_node_and_final():
+    """Config 3 at reduced width: reflect Pad, pad-free 3x3 convolutions, OxiInstanceNorm with per-sample
+    Mul/Add modulation from Gemm + Slice heads, residual joins, Resize x2 decoder, 7x7 + Tanh."""
+    graph, weights, feeds, _ = models.build_inswapper_f32(batch=3, size=32, widths=(32, 64, 96, 128), blocks=2, latent=64)
+    sess, out, ref = run_both(graph, weights, feeds(3))
+    for node in graph.nodes:
+        name = node.outputs[0]
+        if not sess.has_value(name):
+            continue
+        got, want = sess.fetch_value(name), ref[name]
+        assert got.shape == want.shape, name
+        err = float(np.max(np.abs(got - want)) / (np.max(np.abs(want)) + 1e-30))
+        # teacher-free drift: TF32 rounding of every layer before it compounds, and each instance normalisation
+        # rescales it; the bound is 2.5x the per-operator tolerance inside the network and 5x (1e-2 of the
+        # tensor's magnitude) behind the last, heavily cancelling 7x7 convolution
+        bound = (5.0 if name in ("out_conv_out", "image") else 2.5) * RTOL
+        assert err <= bound, f"{name}: relative-to-max error {err}"
+    assert close_tf32(out["image"], ref["image"], scale=5.0)
+    kernels = [s["kernel"] for s in sess.steps()]
+    assert any(k.startswith("umma_tf32") for k in kernels) and any(k.startswith("instance_norm") for k in kernels), kernels
+    sess.close()
+    # the planned-for-speed session (no per-node copies, residual joins inside the convolutions) gives the same image
+    fast = Session.builder().build_from_graph(graph, weights)
+    assert close_tf32(fast.run(feeds(3))["image"], ref["image"], scale=5.0)
+    fast.close()

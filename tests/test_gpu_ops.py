@@ -244,7 +244,10 @@ FCONV_SHAPES = [
     (2, 32, 14, 14, 64, 3, 2, 1, "relu"),    # 128-byte block, stride 2
     (1, 64, 7, 7, 256, 1, 2, 0, ""),         # projection shortcut
     (2, 64, 8, 8, 64, 3, 1, 1, "clip"),
-    (2, 3, 32, 32, 16, 7, 2, 3, "relu"),     # stem (direct kernel reading channels-first input)
+    (2, 3, 32, 32, 16, 7, 2, 3, "relu"),     # stride-2 stem: space-to-depth row windows
+    (2, 3, 20, 18, 40, 7, 1, 3, "relu"),     # stride-1 image-space 7x7 with its own padding: four-lane row windows
+    (2, 3, 19, 19, 32, 7, 1, 0, ""),         # the same behind an explicit reflect Pad (no padding of its own)
+    (1, 4, 12, 12, 16, 3, 1, 1, ""),         # four channels, 3x3 (windows of four pixels)
     (1, 6, 10, 10, 6, 3, 1, 1, ""),          # depthwise-like groups below
 ]
 
@@ -335,6 +338,13 @@ def test_glue_ops_match_oracle(ctx_auto):
     assert np.array_equal(dispatch(ctx, "Concat", [x, z], {"axis": 1})[0], want)
     want, = oracle.run_node("Flatten", [x], {"axis": 1})
     assert np.array_equal(dispatch(ctx, "Flatten", [x], {"axis": 1})[0], want)
+    for ins in ([x, np.float32([1, 2]), np.float32([3, 9.3e18]), np.float32([1, 3])], [x, np.float32([-3]), np.float32([-1]), np.float32([2])],
+                [x[0, 0], np.float32([0, 4]), np.float32([5, 4])]):
+        want, = oracle.run_node("Slice", ins)
+        got = dispatch(ctx, "Slice", ins)
+        assert got is not None, ctx.last_error()
+        assert np.array_equal(got[0], want), ins[1:]
+    assert dispatch(ctx, "Slice", [x, np.float32([0]), np.float32([4]), np.float32([3]), np.float32([2])]) is None  # strided: declined
 
 
 def test_decline_and_failure_contract(ctx_auto):

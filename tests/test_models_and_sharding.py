@@ -49,6 +49,39 @@ def test_full_size_graph_arithmetic():
     assert info1["ops"] == 2 * 64 * (1024 * 4096 + 4096 * 4096 + 4096 * 1024)
 
 
+def test_inswapper_shaped_graph_matches_the_reference_inventory():
+    """Config 3: the builder's arithmetic equals what the reference states for the real model (349 GFLOP per
+    frame, oxionnx-cuda/src/reference.rs:45-49), and every sample is modulated by its own latent row."""
+    _, w, _, info = models.build_inswapper_f32(batch=1)
+    assert abs(2 * info["macs_per_image"] / 1e9 - 349.0) < 1.0
+    assert 480e6 < sum(v.size for v in w.values()) * 4 < 600e6
+    oracle.set_threads(4)
+    g, w, f, _ = models.build_inswapper_f32(batch=2, size=16, widths=(8, 16, 24, 32), blocks=2, latent=32)
+    feeds = f(2)
+    assert np.allclose(np.sum(feeds["latent"].astype(np.float64) ** 2, axis=1), 1.0, atol=1e-5)
+    full = oracle.run_graph(g, w, feeds)
+    assert full["image"].shape == (2, 3, 16, 16) and np.all(np.abs(full["image"]) <= 1.0)
+    one = oracle.run_graph(g, w, {k: v[1:2] for k, v in feeds.items()})
+    assert np.allclose(one["image"][0], full["image"][1], atol=1e-6)   # batch independence: what sharding relies on
+    swapped = dict(feeds, latent=feeds["latent"][::-1].copy())
+    assert not np.allclose(oracle.run_graph(g, w, swapped)["image"], full["image"], atol=1e-3)
+    oracle.set_threads(1)
+
+
+def test_slice_matches_numpy_on_the_oracle():
+    x = np.arange(3 * 5 * 7, dtype=np.float32).reshape(3, 5, 7)
+    cases = [((1, 2), (3, 9.3e18), (0, 2), None, x[1:3, :, 2:]), ((-2,), (-9.3e18,), (1,), (-1,), x[:, -2::-1]),
+             ((0, 1, 6), (2, 4, 0), None, (1, 2, -3), x[0:2, 1:4:2, 6:0:-3]), ((4,), (2,), (2,), None, x[:, :, 4:2])]
+    for starts, ends, axes, steps, want in cases:
+        ins = [x, np.float32(starts), np.float32(ends)]
+        if axes is not None or steps is not None:
+            ins.append(np.float32(axes) if axes is not None else None)
+        if steps is not None:
+            ins.append(np.float32(steps))
+        got, = oracle.run_node("Slice", ins)
+        assert got.shape == want.shape and np.array_equal(got, want), (starts, ends, axes, steps)
+
+
 def test_two_gloo_ranks_shard_and_gather_bit_exact(tmp_path):
     """world_size 2 on CPU: each rank runs its slice of the batch through the oracle (standing
     in for its GPU replica), results are gathered on the host and must equal the unsharded run."""
