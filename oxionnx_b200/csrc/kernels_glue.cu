@@ -2,6 +2,8 @@
 // once through HBM with vectorised accesses where the layout allows; none of them uses a
 // fused multiply-add (this file is compiled with --fmad=false) because the reference rounds
 // every f32 operation separately and the quantisers sit right at rounding boundaries.
+#include <cmath>
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -497,6 +499,43 @@ __global__ void resize_nhwc_kernel(const float* __restrict__ x, float* __restric
   }
 }
 
+// Four channels per thread (NHWC f32, C % 4 == 0): the same arithmetic per lane as the scalar kernel.
+__global__ void resize_nhwc_vec4_kernel(const float4* __restrict__ x, float4* __restrict__ y, Dims4 xd, Dims4 yd, int mode, int coord, int rule,
+                                        float sh, float sw, int64_t total4) {
+  const int64_t c4n = yd.C / 4;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total4; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c4 = o % c4n;
+    int64_t t = o / c4n;
+    const int64_t ox = t % yd.W;
+    t /= yd.W;
+    const int64_t oy = t % yd.H;
+    const int64_t n = t / yd.H;
+    const float sy = src_coord(coord, oy, sh, xd.H, yd.H), sx = src_coord(coord, ox, sw, xd.W, yd.W);
+    const float4* base = x + n * xd.H * xd.W * c4n + c4;
+    if (mode == 0) {
+      y[o] = base[(nearest_index(rule, sy, xd.H) * xd.W + nearest_index(rule, sx, xd.W)) * c4n];
+    } else {
+      const float cy = fminf(fmaxf(sy, 0.f), (float)(xd.H - 1)), cx = fminf(fmaxf(sx, 0.f), (float)(xd.W - 1));
+      const int64_t y0 = (int64_t)floorf(cy), x0 = (int64_t)floorf(cx);
+      const int64_t y1 = y0 + 1 < xd.H ? y0 + 1 : xd.H - 1, x1 = x0 + 1 < xd.W ? x0 + 1 : xd.W - 1;
+      const float fy = __fsub_rn(cy, (float)y0), fx = __fsub_rn(cx, (float)x0);
+      const float gx = __fsub_rn(1.f, fx), gy = __fsub_rn(1.f, fy);
+      const float4 v00 = base[(y0 * xd.W + x0) * c4n], v01 = base[(y0 * xd.W + x1) * c4n];
+      const float4 v10 = base[(y1 * xd.W + x0) * c4n], v11 = base[(y1 * xd.W + x1) * c4n];
+      float4 r;
+#define OXB_LERP(f)                                                                          \
+  {                                                                                          \
+    const float top = __fadd_rn(__fmul_rn(v00.f, gx), __fmul_rn(v01.f, fx));                 \
+    const float bot = __fadd_rn(__fmul_rn(v10.f, gx), __fmul_rn(v11.f, fx));                 \
+    r.f = __fadd_rn(__fmul_rn(top, gy), __fmul_rn(bot, fy));                                 \
+  }
+      OXB_LERP(x) OXB_LERP(y) OXB_LERP(z) OXB_LERP(w)
+#undef OXB_LERP
+      y[o] = r;
+    }
+  }
+}
+
 __device__ __forceinline__ int64_t pad_src(int64_t idx, int64_t ext, int mode, bool& outside) {
   if (idx >= 0 && idx < ext) return idx;
   if (mode == 0) {
@@ -519,6 +558,22 @@ __global__ void pad_kernel(const void* x, void* y, DT dt, Layout L, Dims4 xd, Di
     sq.w = pad_src(q.w - pw, xd.W, mode, outside);
     float v = outside ? value : load_as_f32(x, dt, encode(sq, L, xd));
     store_from_f32(y, dt, o, v);
+  }
+}
+
+// Spatial padding of an NHWC tensor in 16-byte pieces (any storage type whose pixel is a multiple of 16 bytes).
+__global__ void pad_nhwc_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, Dims4 xd, Dims4 yd, int64_t vec_per_pixel, int mode, uint4 fill,
+                                    int ph, int pw, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t v = o % vec_per_pixel;
+    int64_t t = o / vec_per_pixel;
+    const int64_t ow = t % yd.W;
+    t /= yd.W;
+    const int64_t oh = t % yd.H;
+    const int64_t n = t / yd.H;
+    bool outside = false;
+    const int64_t ih = pad_src(oh - ph, xd.H, mode, outside), iw = pad_src(ow - pw, xd.W, mode, outside);
+    y[o] = outside ? fill : x[((n * xd.H + ih) * xd.W + iw) * vec_per_pixel + v];
   }
 }
 
@@ -944,6 +999,11 @@ void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const floa
 void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, cudaStream_t s) {
   int64_t total = y.d.numel();
   if (total == 0) return;
+  if (y.d.C % 4 == 0 && ((uintptr_t)x.ptr & 15) == 0 && ((uintptr_t)y.ptr & 15) == 0) {
+    resize_nhwc_vec4_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((const float4*)x.ptr, (float4*)y.ptr, x.d, y.d, mode, coord, nearest_rule, scale_h,
+                                                                    scale_w, total / 4);
+    return;
+  }
   resize_nhwc_kernel<<<grid_for(total), kThreads, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, y.d, mode, coord, nearest_rule, scale_h,
                                                           scale_w, total);
 }
@@ -951,6 +1011,29 @@ void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nea
 void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, int pc, int ph, int pw, cudaStream_t s) {
   int64_t total = y.d.numel();
   if (total == 0) return;
+  const size_t es = x.dt == DT::F32 || x.dt == DT::I32 ? 4 : (x.dt == DT::I16 ? 2 : 1);
+  if (x.layout == Layout::NHWC && pn == 0 && pc == 0 && (x.d.C * es) % 16 == 0 && ((uintptr_t)x.ptr & 15) == 0 && ((uintptr_t)y.ptr & 15) == 0) {
+    // the fill value in the tensor's storage type, replicated over 16 bytes
+    uint32_t word;  // rounded to nearest even and saturated like store_from_f32
+    auto sat = [&](float lo, float hi) { return (int32_t)std::nearbyint(std::fmin(std::fmax(value, lo), hi)); };
+    if (x.dt == DT::F32) {
+      std::memcpy(&word, &value, 4);
+    } else if (x.dt == DT::I32) {
+      const int32_t iv = (int32_t)std::nearbyint(std::fmin(std::fmax(value, -2147483648.0f), 2147483520.0f));
+      std::memcpy(&word, &iv, 4);
+    } else if (x.dt == DT::I16) {
+      const uint16_t hv = (uint16_t)(int16_t)sat(-32768.f, 32767.f);
+      word = (uint32_t)hv | ((uint32_t)hv << 16);
+    } else {
+      const uint8_t bv = x.dt == DT::U8 ? (uint8_t)sat(0.f, 255.f) : (uint8_t)(int8_t)sat(-128.f, 127.f);
+      word = bv * 0x01010101u;
+    }
+    const int64_t vpp = (int64_t)(x.d.C * es / 16);
+    const int64_t total_v = y.d.N * y.d.H * y.d.W * vpp;
+    pad_nhwc_vec_kernel<<<grid_for(total_v), kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, y.d, vpp, mode, make_uint4(word, word, word, word), ph,
+                                                              pw, total_v);
+    return;
+  }
   pad_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, y.ptr, x.dt, x.layout, x.d, y.d, mode, value, pn, pc, ph, pw, total);
 }
 
