@@ -5,7 +5,7 @@
 A step is one pass of the hot path over one batch of seeded synthetic input.  The default
 workload is ResNet-50 v1.5, f32 graph, batch 32 (TF32 tensor-core contractions); `c5` is the
 QLinearConv INT8 ResNet-50 at batch 128 per GPU, `c1` the INT8 MLP, `c3` the InSwapper-shaped f32
-generator at batch 16.  With N > 1 (launched by
+generator at batch 16, `c4` the BERT-base-shaped dynamic-INT8 encoder at 64 x 128 tokens (tokens/s).  With N > 1 (launched by
 torchrun, one rank per GPU) every rank holds a full weight replica and runs its own batch:
 the path shards along the batch only, there is no data-path collective, and the scaling is weak.
 
@@ -46,6 +46,7 @@ WORKLOADS = {
     "c5": dict(name="resnet50_qlinearconv_int8_b128_per_gpu", metric="images_per_s", unit="images/s", dtype="i8", batch=128),
     "c1": dict(name="int8_mlp_64x1024-4096-4096-1024", metric="rows_per_s", unit="rows/s", dtype="i8", batch=64),
     "c3": dict(name="inswapper128_shaped_f32_b16", metric="images_per_s", unit="images/s", dtype="tf32", batch=16),
+    "c4": dict(name="bert_base_dynamic_int8_b64_s128", metric="tokens_per_s", unit="tokens/s", dtype="i8", batch=64, per_item=128),
 }
 
 
@@ -61,7 +62,7 @@ def measured_peaks():
 # DRAM bytes (read + written) per launch of the tensor-core kernel, averaged over the launches of one
 # step: dram__bytes_read.sum + dram__bytes_write.sum from the ncu launch lists summarised under profiles/
 # (launch_list_resnet50_f32_b32.md, launch_list_resnet50_int8_b128.md).  None: not captured.
-NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.41e6, "c5": 28.32e6, "c1": None, "c3": None}
+NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.41e6, "c5": 28.32e6, "c1": None, "c3": None, "c4": None}
 
 
 def build_workload(key, batch):
@@ -72,6 +73,8 @@ def build_workload(key, batch):
         return models.build_resnet50_qlinear(batch=batch)
     if key == "c3":
         return models.build_inswapper_f32(batch=batch)
+    if key == "c4":
+        return models.build_bert_dynamic_int8(batch=batch)
     return models.build_int8_mlp(rows=batch)
 
 
@@ -144,7 +147,7 @@ def cpu_baseline(key, graph_builder_batch, sample, threads):
     dt = time.time() - t0
     oracle.set_float_accum(0)
     oracle.set_threads(1)
-    return sample / dt, dt
+    return sample * WORKLOADS[key].get("per_item", 1) / dt, dt
 
 
 def int8_companion(args, local_rank, flush_l2, peaks):
@@ -182,7 +185,7 @@ def run_reference(args, rank, world):
         return
     w = WORKLOADS[args.workload]
     cores = os.cpu_count() or 1
-    sample = {"c2": 2, "c5": 1, "c1": 64, "c3": 1}[args.workload]
+    sample = {"c2": 2, "c5": 1, "c1": 64, "c3": 1, "c4": 1}[args.workload]
     times = []
     for i in range(args.warmup + args.steps):
         v, dt = cpu_baseline(args.workload, w["batch"], sample, cores)
@@ -191,7 +194,7 @@ def run_reference(args, rank, world):
         if sum(times) > 150:
             break
     steps = len(times)
-    value = sample * steps / sum(times)
+    value = sample * w.get("per_item", 1) * steps / sum(times)
     line = {
         "impl": "reference", "metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
         "ms_per_step": 1000.0 * sum(times) / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32" if args.workload in ("c2", "c3") else "i64",
@@ -299,7 +302,8 @@ def main():
         t = torch.tensor([total_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
-    value = world * batch * args.steps / (total_ms / 1000.0)
+    per_item = w.get("per_item", 1)  # tokens per sequence for the encoder, 1 otherwise
+    value = world * batch * per_item * args.steps / (total_ms / 1000.0)
 
     # ---- end-to-end leg: pinned host buffers through the public run call ----
     out = sess.run(feeds_pinned)
@@ -317,7 +321,7 @@ def main():
         t = torch.tensor([e2e_total], dtype=torch.float64, device=f"cuda:{local_rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_total = float(t.item())
-    e2e_value = world * batch * args.steps / (e2e_total / 1000.0)
+    e2e_value = world * batch * per_item * args.steps / (e2e_total / 1000.0)
     h2d = int(sum(v.size for v in feeds_pinned.values()) * 4)
     d2h = int(sum(v.size for v in out.values()) * 4)
 
@@ -354,7 +358,7 @@ def main():
         if args.workload == "c2" and world == 1 and not args.no_int8:
             line["int8"] = int8_companion(args, local_rank, flush_l2, peaks)
         if not args.no_cpu_baseline and world == 1:
-            sample = {"c2": 2, "c5": 1, "c1": 64, "c3": 1}[args.workload]
+            sample = {"c2": 2, "c5": 1, "c1": 64, "c3": 1, "c4": 1}[args.workload]
             cores = os.cpu_count() or 1
             v, dt = cpu_baseline(args.workload, batch, sample, cores)
             line["cpu_baseline"] = {"value": v, "unit": w["unit"], "cores": cores, "kind": "port",

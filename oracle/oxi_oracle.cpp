@@ -1157,6 +1157,152 @@ void op_slice(Ctx& c) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Transformer glue for the dynamic-INT8 encoder (float, tolerance-checked).
+// Gather: oxionnx-ops/src/indexing/gather.rs:12-44 (negative indices wrap, out of range is an error).
+// Transpose: src/shape/basic.rs:146-230 (empty perm reverses; perm must be a permutation).
+// Softmax: src/nn/normalization.rs:300-360 (max, exp(v - max) summed in order, multiply by 1/sum).
+// LayerNormalization: src/nn/normalization.rs layer_norm_into (mean and variance as sequential f32
+//   sums over the normalised group, inv_std = 1/sqrt(var + eps), (x - mean) * inv_std * scale, + bias).
+// Gelu: src/registry/nn_ops/activations.rs:357-386 (approximate="tanh" -> 0.5 x (1 + tanh(0.7978846 (x +
+//   0.044715 x^3))); otherwise x * 0.5 * (1 + erf(x / sqrt 2)) with the Abramowitz-Stegun 7.1.26
+//   polynomial of erf_approx :578-586).  Erf uses the same polynomial.
+// ---------------------------------------------------------------------------------------
+float erf_poly(float x) {
+  const float sign = x >= 0.0f ? 1.0f : -1.0f;
+  x = std::fabs(x);
+  const float t = 1.0f / (1.0f + 0.3275911f * x);
+  const float poly = t * (0.2548296f + t * (-0.28449672f + t * (1.4214138f + t * (-1.4531521f + t * 1.0614054f))));
+  return sign * (1.0f - poly * std::exp(-x * x));
+}
+
+void op_gelu(Ctx& c) {
+  if (c.attrs.s("approximate") == "tanh") {
+    unary_op(c, [](float x) {
+      const float inner = 0.7978846f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + std::tanh(inner));
+    });
+  } else {
+    unary_op(c, [](float x) { return x * 0.5f * (1.0f + erf_poly(x * 0.70710678118654752440f)); });
+  }
+}
+
+void op_gather(Ctx& c) {
+  const oxo_tensor& data = c.input(0);
+  const oxo_tensor& idx = c.input(1);
+  int64_t axis = c.attrs.i("axis", 0);
+  if (axis < 0) axis += data.rank;
+  if (axis < 0 || axis >= data.rank) fail(OXO_ERR_INVALID_MODEL, "gather: axis out of range");
+  std::vector<int64_t> os;
+  for (int d = 0; d < axis; ++d) os.push_back(data.shape[d]);
+  for (int d = 0; d < idx.rank; ++d) os.push_back(idx.shape[d]);
+  for (int d = (int)axis + 1; d < data.rank; ++d) os.push_back(data.shape[d]);
+  int64_t outer = 1, inner = 1;
+  for (int d = 0; d < axis; ++d) outer *= data.shape[d];
+  for (int d = (int)axis + 1; d < data.rank; ++d) inner *= data.shape[d];
+  const int64_t axis_size = data.shape[axis], idx_n = idx.len;
+  alloc_out(c.out[0], os);
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t ii = 0; ii < idx_n; ++ii) {
+      int64_t iv = (int64_t)idx.data[ii];
+      if (iv < 0) iv += axis_size;
+      if (iv < 0 || iv >= axis_size) fail(OXO_ERR_INVALID_MODEL, "gather: index out of range");
+      std::copy(data.data + (o * axis_size + iv) * inner, data.data + (o * axis_size + iv + 1) * inner, c.out[0].data + (o * idx_n + ii) * inner);
+    }
+}
+
+void op_transpose(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  const int rank = x.rank;
+  std::vector<int64_t> perm = c.attrs.ints("perm");
+  if (perm.empty())
+    for (int d = rank - 1; d >= 0; --d) perm.push_back(d);
+  if ((int)perm.size() != rank) fail(OXO_ERR_INVALID_MODEL, "transpose: perm length differs from the rank");
+  std::vector<char> seen(rank, 0);
+  for (int64_t pv : perm) {
+    if (pv < 0 || pv >= rank) fail(OXO_ERR_INVALID_MODEL, "transpose: perm entry out of range");
+    if (seen[pv]) fail(OXO_ERR_INVALID_MODEL, "transpose: perm entry repeated");
+    seen[pv] = 1;
+  }
+  std::vector<int64_t> os(rank), xs(rank, 1);
+  for (int d = rank - 2; d >= 0; --d) xs[d] = xs[d + 1] * x.shape[d + 1];
+  for (int d = 0; d < rank; ++d) os[d] = x.shape[perm[d]];
+  alloc_out(c.out[0], os);
+  std::vector<int64_t> idx(rank, 0);
+  for (int64_t o = 0; o < c.out[0].len; ++o) {
+    int64_t src = 0;
+    for (int d = 0; d < rank; ++d) src += idx[d] * xs[perm[d]];
+    c.out[0].data[o] = x.data[src];
+    for (int d = rank - 1; d >= 0; --d) {
+      if (++idx[d] < os[d]) break;
+      idx[d] = 0;
+    }
+  }
+}
+
+void op_softmax(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  int64_t axis = c.attrs.i("axis", -1);
+  if (axis < 0) axis += x.rank;
+  if (axis < 0 || axis >= x.rank) fail(OXO_ERR_INVALID_MODEL, "softmax: axis out of range");
+  int64_t outer = 1, inner = 1;
+  for (int d = 0; d < axis; ++d) outer *= x.shape[d];
+  for (int d = (int)axis + 1; d < x.rank; ++d) inner *= x.shape[d];
+  const int64_t n = x.shape[axis];
+  alloc_out(c.out[0], shape_of(x));
+  float* out = c.out[0].data;
+#pragma omp parallel for collapse(2) schedule(static) if (outer * inner * n > 65536)
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const float* px = x.data + o * n * inner + i;
+      float* py = out + o * n * inner + i;
+      float mx = -INFINITY;
+      for (int64_t k = 0; k < n; ++k) mx = px[k * inner] > mx ? px[k * inner] : mx;
+      float sum = 0.0f;
+      for (int64_t k = 0; k < n; ++k) {
+        const float e = std::exp(px[k * inner] - mx);
+        py[k * inner] = e;
+        sum += e;
+      }
+      const float inv = 1.0f / sum;
+      for (int64_t k = 0; k < n; ++k) py[k * inner] *= inv;
+    }
+}
+
+void op_layer_norm(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  const oxo_tensor& scale = c.input(1);
+  const oxo_tensor* bias = c.optional(2);
+  int64_t axis = c.attrs.i("axis", -1);
+  const float eps = c.attrs.f("epsilon", 1e-5f);
+  if (axis < 0) axis += x.rank;
+  if (axis < 0 || axis >= x.rank) fail(OXO_ERR_INVALID_MODEL, "layer_norm: axis out of range");
+  int64_t outer = 1, norm = 1;
+  for (int d = 0; d < axis; ++d) outer *= x.shape[d];
+  for (int d = (int)axis; d < x.rank; ++d) norm *= x.shape[d];
+  if (norm == 0 || scale.len == 0 || (bias && bias->len == 0)) fail(OXO_ERR_SHAPE_MISMATCH, "layer_norm: empty operand");
+  alloc_out(c.out[0], shape_of(x));
+  float* out = c.out[0].data;
+#pragma omp parallel for schedule(static) if (outer * norm > 65536)
+  for (int64_t o = 0; o < outer; ++o) {
+    const float* in = x.data + o * norm;
+    float* dst = out + o * norm;
+    float sum = 0.0f;
+    for (int64_t j = 0; j < norm; ++j) sum += in[j];
+    const float mean = sum / (float)norm;
+    float vs = 0.0f;
+    for (int64_t j = 0; j < norm; ++j) {
+      const float d = in[j] - mean;
+      vs += d * d;
+    }
+    const float var = vs / (float)norm;
+    const float inv_std = 1.0f / std::sqrt(var + eps);
+    for (int64_t j = 0; j < norm; ++j) dst[j] = (in[j] - mean) * inv_std * scale.data[j % scale.len];
+    if (bias)
+      for (int64_t j = 0; j < norm; ++j) dst[j] += bias->data[j % bias->len];
+  }
+}
+
 void op_pad(Ctx& c) {
   const oxo_tensor& x = c.input(0);
   std::vector<int64_t> pads;
@@ -1321,6 +1467,13 @@ const OpEntry kOps[] = {
     {"Concat", op_concat, 1},
     {"Pad", op_pad, 1},
     {"Slice", op_slice, 1},
+    {"Gather", op_gather, 1},
+    {"Transpose", op_transpose, 1},
+    {"Softmax", op_softmax, 1},
+    {"LayerNormalization", op_layer_norm, 1},
+    {"LayerNorm", op_layer_norm, 1},
+    {"Gelu", op_gelu, 1},
+    {"Erf", [](Ctx& c) { unary_op(c, [](float v) { return erf_poly(v); }); }, 1},
     {"Resize", op_resize, 1},
     {"Cast", op_identity, 1},
     {"Identity", op_identity, 1},

@@ -312,7 +312,7 @@ int oxb200_dispatch(oxb200_ctx* ctx, const oxb200_node* node, const oxb200_opera
       if (flag) {
         cudaFree(t->h.ptr);
         delete t;
-        raise(OXB200_FAILED, "a tensor-core kernel gave up on a bounded wait (code %d)", flag);
+        raise(OXB200_FAILED, flag == 20 ? "Gather: an index is out of range (device code %d)" : "a tensor-core kernel gave up on a bounded wait (code %d)", flag);
       }
       results[0].resident = t;
       results[0].rank = (uint32_t)v->shape.size();
@@ -428,7 +428,7 @@ int oxb200_run_resident(oxb200_ctx* ctx, uint32_t iters, float* elapsed_ms) {
           if (cudaEventElapsedTime(&t, st.ev0, st.ev1) == cudaSuccess) st.last_ms = t;
         }
     int flag = s.check_error_flag();
-    if (flag) raise(OXB200_FAILED, "a tensor-core kernel gave up on a bounded wait (code %d); results are not valid", flag);
+    if (flag) raise(OXB200_FAILED, flag == 20 ? "Gather: an index is out of range (device code %d); results are not valid" : "a tensor-core kernel gave up on a bounded wait (code %d); results are not valid", flag);
     return (int)OXB200_OK_DEVICE;
   });
 }

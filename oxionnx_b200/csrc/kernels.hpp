@@ -67,7 +67,7 @@ void residual_requant(const void* a, DT a_dt, const void* b, DT b_dt, void* y, D
 
 // ---- element-wise -----------------------------------------------------------------------
 enum BinOp { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_DIV = 3 };
-enum UnOp { UN_RELU = 0, UN_TANH = 1, UN_SIGMOID = 2, UN_SILU = 3, UN_COPY = 4 };
+enum UnOp { UN_RELU = 0, UN_TANH = 1, UN_SIGMOID = 2, UN_SILU = 3, UN_COPY = 4, UN_GELU_ERF = 5, UN_GELU_TANH = 6, UN_ERF = 7 };
 // out = op(a, b) with numpy broadcasting expressed through per-axis extents of 1 in the
 // views; optional fused relu afterwards; round_tf32 rounds the f32 result to TF32
 // (round-to-nearest, ties away) for a following tensor-core contraction.
@@ -98,6 +98,15 @@ void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, 
 // Copies `x` into the channel range [c_off, c_off + x.C) of `y` (Concat on the channel axis)
 // or, axis 0/2/3, the matching range of that axis.
 void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s);
+// Transformer glue (f32, logical row-major order).  gather_rows: out[i, :] = table[idx[i], :] with index lanes
+// as f32 (negative counts from the end; out of range records code 20 in *err).  transpose_perm: y of shape yd
+// reads x through the strides xstride (the input stride of each output axis).  softmax_rows / layer_norm_rows:
+// over the last axis of a [rows, n] view.
+void gather_rows(const float* table, const float* idx, float* out, int64_t n_idx, int64_t rows, int64_t inner, int* err, cudaStream_t s);
+void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstride, cudaStream_t s);
+// softmax_rows optionally applies x * scale[0] and + mask[row / rows_per_mask][:] first (fused Mul / Add producers).
+void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, cudaStream_t s);
+void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s);
 // Slice with unit steps over logical (row-major) axes padded to four: y[i] = x[i + start], dims as (N, C, H, W).
 void slice_rows(const void* x, void* y, DT dt, const Dims4& xd, const Dims4& yd, const Dims4& start, cudaStream_t s);
 
@@ -137,7 +146,7 @@ struct ConvShape {
   double ops() const { return 2.0 * (double)M() * (double)OC * (double)K(); }
 };
 
-enum EpiMode { EPI_F32 = 0, EPI_REQUANT = 1, EPI_INT32 = 2 };
+enum EpiMode { EPI_F32 = 0, EPI_REQUANT = 1, EPI_INT32 = 2, EPI_DEQUANT = 3 };
 
 struct Epilogue {
   int mode = EPI_F32;
@@ -165,6 +174,13 @@ struct Epilogue {
   int y_zp = 0;
   int lo = 0, hi = 255;
   int relu_fused = 0;  // integer: clamp below at max(lo, 0) (a following Relu node)
+  // EPI_DEQUANT (MatMulInteger -> Cast -> Mul(x_scale * w_scale[oc]) -> Add(bias[oc]) [-> Gelu], the chain a
+  // dynamically quantised linear is exported as): out = f32(acc) * (x_scale * w_scale[oc]) + bias[oc], every
+  // product and sum rounded separately as the unfused nodes do; dq_act 1 = exact Gelu, 2 = tanh Gelu
+  const float* dq_w_scale = nullptr;      // [OC], padded like the other parameter vectors
+  const float* dq_x_scale_dev = nullptr;  // one device lane (a DynamicQuantizeLinear scale)
+  const float* dq_bias = nullptr;         // [OC], padded
+  int dq_act = 0;
   DT out_dt = DT::F32;
 };
 

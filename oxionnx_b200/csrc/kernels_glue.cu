@@ -300,6 +300,19 @@ __global__ void binary_vec4_kernel(const float4* __restrict__ a, const float4* _
   }
 }
 
+// erf by the polynomial the reference uses (Abramowitz-Stegun 7.1.26, nn_ops/activations.rs:578), same operation order.
+__device__ __forceinline__ float erf_poly(float x) {
+  const float sign = x >= 0.0f ? 1.0f : -1.0f;
+  x = fabsf(x);
+  const float t = __fdiv_rn(1.0f, __fadd_rn(1.0f, __fmul_rn(0.3275911f, x)));
+  float p = __fadd_rn(-1.4531521f, __fmul_rn(t, 1.0614054f));
+  p = __fadd_rn(1.4214138f, __fmul_rn(t, p));
+  p = __fadd_rn(-0.28449672f, __fmul_rn(t, p));
+  p = __fadd_rn(0.2548296f, __fmul_rn(t, p));
+  const float poly = __fmul_rn(t, p);
+  return __fmul_rn(sign, __fsub_rn(1.0f, __fmul_rn(poly, expf(__fmul_rn(-x, x)))));
+}
+
 __global__ void unary_kernel(const void* x, DT xdt, void* y, DT ydt, int op, int64_t total) {
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
     float v = load_as_f32(x, xdt, o);
@@ -309,6 +322,13 @@ __global__ void unary_kernel(const void* x, DT xdt, void* y, DT ydt, int op, int
       case UN_TANH: r = tanhf(v); break;
       case UN_SIGMOID: r = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))); break;
       case UN_SILU: r = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v))); break;
+      case UN_GELU_ERF: r = __fmul_rn(__fmul_rn(v, 0.5f), __fadd_rn(1.0f, erf_poly(__fmul_rn(v, 0.70710678118654752440f)))); break;
+      case UN_GELU_TANH: {
+        const float inner = __fmul_rn(0.7978846f, __fadd_rn(v, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v)));
+        r = __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner)));
+        break;
+      }
+      case UN_ERF: r = erf_poly(v); break;
       default: r = v; break;
     }
     store_from_f32(y, ydt, o, r);
@@ -789,6 +809,111 @@ __global__ void window_pack_f32_kernel(const float* __restrict__ src, Layout sl,
   }
 }
 
+// ---- transformer glue ---------------------------------------------------------------------
+// Gather along axis 0 of a [rows, inner] table: one output row per index lane (an f32 lane holding
+// an integer; negative values count from the end).  An index outside the table records code 20.
+__global__ void gather_rows_kernel(const float* __restrict__ table, const float* __restrict__ idx, float* __restrict__ out, int64_t n_idx, int64_t rows,
+                                   int64_t inner, int* err) {
+  const int64_t total = n_idx * inner;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = o / inner, j = o - i * inner;
+    long long r = (long long)idx[i];
+    if (r < 0) r += rows;
+    if (r < 0 || r >= rows) {
+      if (j == 0) atomicExch(err, 20);
+      out[o] = 0.f;
+      continue;
+    }
+    out[o] = table[r * inner + j];
+  }
+}
+
+// Permutation of up to four logical axes: yd is the output shape, xstride[d] the input stride of output axis d.
+__global__ void transpose_perm_kernel(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, Dims4 yd, Dims4 xstride, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t t = o;
+    const int64_t i3 = t % yd.W;
+    t /= yd.W;
+    const int64_t i2 = t % yd.H;
+    t /= yd.H;
+    const int64_t i1 = t % yd.C;
+    const int64_t i0 = t / yd.C;
+    y[o] = x[i0 * xstride.N + i1 * xstride.C + i2 * xstride.H + i3 * xstride.W];
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Softmax over the last axis, one warp per row: max, exp(v - max), sum, multiply by 1 / sum
+// (nn/normalization.rs softmax_into; the sums are reassociated across lanes: float tolerance).
+__global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int64_t n, const float* __restrict__ scale,
+                                    const float* __restrict__ mask, int64_t rows_per_mask) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const float* px = x + r * n;
+    float* py = y + r * n;
+    // optional fused producers: v = x * scale[0] (a Mul by a scalar) and v += mask[row / rows_per_mask][k] (an Add
+    // of a mask that broadcasts over heads and query rows), each rounded as the separate nodes would
+    const float sc = scale ? scale[0] : 1.f;
+    const float* pm = mask ? mask + (r / rows_per_mask) * n : nullptr;
+    auto value = [&](int64_t k) {
+      float v = px[k];
+      if (scale) v = __fmul_rn(v, sc);
+      if (pm) v = __fadd_rn(v, pm[k]);
+      return v;
+    };
+    float mx = -INFINITY;
+    for (int64_t k = lane; k < n; k += 32) mx = fmaxf(mx, value(k));
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int64_t k = lane; k < n; k += 32) {
+      const float e = expf(__fsub_rn(value(k), mx));
+      py[k] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    const float inv = __frcp_rn(sum);
+    for (int64_t k = lane; k < n; k += 32) py[k] = __fmul_rn(py[k], inv);
+  }
+}
+
+// LayerNormalization over the last axis, one warp per row (nn/normalization.rs layer_norm_into):
+// mean = sum / n, var = sum((x - mean)^2) / n, inv_std = 1 / sqrt(var + eps), (x - mean) * inv_std * scale [+ bias].
+__global__ void layer_norm_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int64_t n, const float* __restrict__ scale,
+                                       const float* __restrict__ bias, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const float* px = x + r * n;
+    float* py = y + r * n;
+    float sum = 0.f;
+    for (int64_t k = lane; k < n; k += 32) sum += px[k];
+    const float mean = __fdiv_rn(warp_sum(sum), (float)n);
+    float vs = 0.f;
+    for (int64_t k = lane; k < n; k += 32) {
+      const float d = __fsub_rn(px[k], mean);
+      vs += __fmul_rn(d, d);
+    }
+    const float var = __fdiv_rn(warp_sum(vs), (float)n);
+    const float inv_std = __frcp_rn(__fsqrt_rn(__fadd_rn(var, eps)));
+    for (int64_t k = lane; k < n; k += 32) {
+      float v = __fmul_rn(__fmul_rn(__fsub_rn(px[k], mean), inv_std), scale[k]);
+      if (bias) v = __fadd_rn(v, bias[k]);
+      py[k] = v;
+    }
+  }
+}
+
 }  // namespace
 
 // =========================================================================================
@@ -1042,6 +1167,27 @@ void slice_rows(const void* x, void* y, DT dt, const Dims4& xd, const Dims4& yd,
   if (total == 0) return;
   const int es = dt == DT::F32 || dt == DT::I32 ? 4 : (dt == DT::I16 ? 2 : 1);
   slice_kernel<<<grid_for(total), kThreads, 0, s>>>(x, y, es, xd, yd, start, total);
+}
+
+void gather_rows(const float* table, const float* idx, float* out, int64_t n_idx, int64_t rows, int64_t inner, int* err, cudaStream_t s) {
+  if (n_idx * inner == 0) return;
+  gather_rows_kernel<<<grid_for(n_idx * inner), kThreads, 0, s>>>(table, idx, out, n_idx, rows, inner, err);
+}
+
+void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstride, cudaStream_t s) {
+  const int64_t total = yd.numel();
+  if (total == 0) return;
+  transpose_perm_kernel<<<grid_for(total), kThreads, 0, s>>>((const uint32_t*)x, (uint32_t*)y, yd, xstride, total);
+}
+
+void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, cudaStream_t s) {
+  if (rows * n == 0) return;
+  softmax_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, mask, rows_per_mask > 0 ? rows_per_mask : 1);
+}
+
+void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s) {
+  if (rows * n == 0) return;
+  layer_norm_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, bias, eps);
 }
 
 void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s) {

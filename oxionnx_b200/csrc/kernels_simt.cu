@@ -42,6 +42,10 @@ struct EpiDev {
   const float* combined;
   int y_zp, lo, hi;
   DT out_dt;
+  const float* dq_w_scale;
+  const float* dq_x_scale;
+  const float* dq_bias;
+  int dq_act;
 };
 
 __device__ __forceinline__ void store_int(void* out, DT dt, int64_t idx, int32_t q) {
@@ -54,7 +58,29 @@ __device__ __forceinline__ void store_int(void* out, DT dt, int64_t idx, int32_t
   }
 }
 
+__device__ __forceinline__ float erf_poly(float x) {  // nn_ops/activations.rs:578, same operation order
+  const float sign = x >= 0.0f ? 1.0f : -1.0f;
+  x = fabsf(x);
+  const float t = __fdiv_rn(1.0f, __fadd_rn(1.0f, __fmul_rn(0.3275911f, x)));
+  float p = __fadd_rn(-1.4531521f, __fmul_rn(t, 1.0614054f));
+  p = __fadd_rn(1.4214138f, __fmul_rn(t, p));
+  p = __fadd_rn(-0.28449672f, __fmul_rn(t, p));
+  p = __fadd_rn(0.2548296f, __fmul_rn(t, p));
+  return __fmul_rn(sign, __fsub_rn(1.0f, __fmul_rn(__fmul_rn(t, p), expf(__fmul_rn(-x, x)))));
+}
+
 __device__ __forceinline__ void finish_int(const EpiDev& e, void* out, int64_t idx, int oc, long long acc) {
+  if (e.mode == EPI_DEQUANT) {
+    const long long c = acc < -2147483648LL ? -2147483648LL : (acc > 2147483647LL ? 2147483647LL : acc);
+    float y = __fadd_rn(__fmul_rn(__int2float_rn((int)c), __fmul_rn(*e.dq_x_scale, e.dq_w_scale[oc])), e.dq_bias[oc]);
+    if (e.dq_act == 1) y = __fmul_rn(__fmul_rn(y, 0.5f), __fadd_rn(1.0f, erf_poly(__fmul_rn(y, 0.70710678118654752440f))));
+    if (e.dq_act == 2) {
+      const float inner = __fmul_rn(0.7978846f, __fadd_rn(y, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, y), y), y)));
+      y = __fmul_rn(__fmul_rn(0.5f, y), __fadd_rn(1.0f, tanhf(inner)));
+    }
+    ((float*)out)[idx] = y;
+    return;
+  }
   if (e.mode == EPI_INT32) {
     long long c = acc < -2147483648LL ? -2147483648LL : (acc > 2147483647LL ? 2147483647LL : acc);
     store_int(out, e.out_dt, idx, (int32_t)c);
@@ -179,7 +205,7 @@ void launch_conv(const void* x, const void* w, void* out, const ConvShape& cs, c
 void conv_direct(const void* x, DT x_dt, int x_plain_nchw, const void* w, DT w_dt, void* out, const ConvShape& cs, const Epilogue& ep,
                  cudaStream_t s) {
   EpiDev e{ep.mode,     ep.bias_f,    ep.act,  ep.clip_lo, ep.clip_hi,  ep.round_tf32, ep.residual, ep.bias_i, ep.x_zp, ep.x_zp_dev,
-           ep.x_zp_rows, ep.w_zp,     ep.n_w_zp, ep.combined, ep.y_zp,  ep.relu_fused && ep.lo < 0 ? 0 : ep.lo, ep.hi, ep.out_dt};
+           ep.x_zp_rows, ep.w_zp,     ep.n_w_zp, ep.combined, ep.y_zp,  ep.relu_fused && ep.lo < 0 ? 0 : ep.lo, ep.hi, ep.out_dt, ep.dq_w_scale, ep.dq_x_scale_dev, ep.dq_bias, ep.dq_act};
   if (ep.mode == EPI_F32) {
     if (x_dt != DT::F32 || w_dt != DT::F32) OXB_FAIL("conv_direct: float epilogue needs f32 operands");
     launch_conv<float, float, false>(x, w, out, cs, e, x_plain_nchw, s);

@@ -73,6 +73,9 @@ struct alignas(64) KParams {
   const int32_t* wsum;
   const float* x_zp_dev;
   const float* combined;
+  const float* dq_w_scale;   // dequantising epilogue: per-channel weight scale,
+  const float* dq_x_scale;   // the activation's scale (one device lane),
+  const float* dq_bias;      // per-channel f32 bias
   int y_zp, lo, hi;
   int out_dt;
   void* out;
@@ -244,7 +247,8 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // parallelism (one epilogue warp per scheduler has nothing else to hide latency with).
 // Per-channel parameters are read with 16-byte read-only loads; the host pads every
 // parameter vector to a multiple of 256 channels, so no bounds checks are needed here.
-enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9, V_REQUANT_FMA = 10, V_REQUANT_FMA_DYN = 11, V_REQUANT_LEAN = 12, V_REQUANT_LEAN_DYN = 13, V_F32_RES = 14 };  // 14..19: the float variants with a residual
+enum { V_F32_BASE = 0, V_REQUANT = 6, V_REQUANT_DYN = 7, V_INT32 = 8, V_INT32_DYN = 9, V_REQUANT_FMA = 10, V_REQUANT_FMA_DYN = 11, V_REQUANT_LEAN = 12, V_REQUANT_LEAN_DYN = 13, V_F32_RES = 14,  // 14..19: the float variants with a residual
+       V_DEQUANT = 20 };  // 20..25: dequantising variants, + (dynamic zero point ? 1 : 0) + 2 * activation
 
 template <int ACT, int RT, bool RES>
 __device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias, const float* __restrict__ res,
@@ -408,6 +412,53 @@ __device__ __forceinline__ void math_requant_fma(const KParams& p, const uint32_
   }
 }
 
+// erf by the reference's polynomial (Abramowitz-Stegun 7.1.26, nn_ops/activations.rs:578), same operation order.
+__device__ __forceinline__ float erf_poly(float x) {
+  const float sign = x >= 0.0f ? 1.0f : -1.0f;
+  x = fabsf(x);
+  const float t = __fdiv_rn(1.0f, __fadd_rn(1.0f, __fmul_rn(0.3275911f, x)));
+  float p = __fadd_rn(-1.4531521f, __fmul_rn(t, 1.0614054f));
+  p = __fadd_rn(1.4214138f, __fmul_rn(t, p));
+  p = __fadd_rn(-0.28449672f, __fmul_rn(t, p));
+  p = __fadd_rn(0.2548296f, __fmul_rn(t, p));
+  return __fmul_rn(sign, __fsub_rn(1.0f, __fmul_rn(__fmul_rn(t, p), expf(__fmul_rn(-x, x)))));
+}
+
+// Dequantising epilogue of a dynamically quantised linear: the integer accumulator becomes an f32 lane
+// (round to nearest even above 2^24, as `saturate_i32(acc) as f32`), is multiplied by x_scale * w_scale[oc]
+// and gets bias[oc] added, each operation rounded on its own, then optionally Gelu.
+template <bool DYN, int ACT>
+__device__ __forceinline__ void math_dequant(const KParams& p, const uint32_t (&v)[32], const int32_t* __restrict__ bias_i,
+                                             const int32_t* __restrict__ wsum, const float* __restrict__ wscale, const float* __restrict__ bias_f, int xz,
+                                             float xs, uint32_t (&w)[32]) {
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const int4 b = __ldg(reinterpret_cast<const int4*>(bias_i) + j4);
+    const int bb[4] = {b.x, b.y, b.z, b.w};
+    int ss[4] = {0, 0, 0, 0};
+    if (DYN) {
+      const int4 sv = __ldg(reinterpret_cast<const int4*>(wsum) + j4);
+      ss[0] = sv.x, ss[1] = sv.y, ss[2] = sv.z, ss[3] = sv.w;
+    }
+    const float4 c = __ldg(reinterpret_cast<const float4*>(wscale) + j4);
+    const float cc[4] = {c.x, c.y, c.z, c.w};
+    const float4 f = __ldg(reinterpret_cast<const float4*>(bias_f) + j4);
+    const float ff[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int32_t acc = (int32_t)v[4 * j4 + e] + bb[e];
+      if (DYN) acc -= xz * ss[e];
+      float y = __fadd_rn(__fmul_rn(__int2float_rn(acc), __fmul_rn(xs, cc[e])), ff[e]);
+      if (ACT == 1) y = __fmul_rn(__fmul_rn(y, 0.5f), __fadd_rn(1.0f, erf_poly(__fmul_rn(y, 0.70710678118654752440f))));
+      if (ACT == 2) {
+        const float inner = __fmul_rn(0.7978846f, __fadd_rn(y, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, y), y), y)));
+        y = __fmul_rn(__fmul_rn(0.5f, y), __fadd_rn(1.0f, tanhf(inner)));
+      }
+      w[4 * j4 + e] = __float_as_uint(y);
+    }
+  }
+}
+
 // Fused epilogue of one 32-channel run of one output pixel: bias / zero-point correction,
 // requantisation or activation, packed into 32-bit words (8 for 8-bit outputs, 16 for 16-bit,
 // 32 for 32-bit).  `oc` is the first channel of the run.  The variant is a template argument:
@@ -416,7 +467,10 @@ __device__ __forceinline__ void math_requant_fma(const KParams& p, const uint32_
 template <int VARIANT>
 __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t (&v)[32], int xz, int oc, size_t esz, const float* res, uint32_t (&w)[32]) {
   if constexpr (VARIANT < V_REQUANT) math_f32<VARIANT / 2, VARIANT & 1, false>(p, v, p.bias_f + oc, nullptr, w);
-  else if constexpr (VARIANT >= V_F32_RES) math_f32<(VARIANT - V_F32_RES) / 2, (VARIANT - V_F32_RES) & 1, true>(p, v, p.bias_f + oc, res, w);
+  else if constexpr (VARIANT >= V_DEQUANT) {
+    const float xs = __ldg(p.dq_x_scale);
+    math_dequant<((VARIANT - V_DEQUANT) & 1) != 0, (VARIANT - V_DEQUANT) / 2>(p, v, p.bias_i + oc, p.wsum + oc, p.dq_w_scale + oc, p.dq_bias + oc, xz, xs, w);
+  } else if constexpr (VARIANT >= V_F32_RES) math_f32<(VARIANT - V_F32_RES) / 2, (VARIANT - V_F32_RES) & 1, true>(p, v, p.bias_f + oc, res, w);
   else if constexpr (VARIANT == V_REQUANT) math_int<true, false>(p, v, p.bias_i + oc, nullptr, p.combined + oc, xz, esz, w);
   else if constexpr (VARIANT == V_REQUANT_DYN) math_int<true, true>(p, v, p.bias_i + oc, p.wsum + oc, p.combined + oc, xz, esz, w);
   else if constexpr (VARIANT == V_INT32) math_int<false, false>(p, v, p.bias_i + oc, nullptr, nullptr, xz, esz, w);
@@ -521,7 +575,7 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
     };
     auto emit = [&](const uint32_t(&v)[32], int ch) {
-      const float* res = (VARIANT >= V_F32_RES && row_ok) ? p.residual + (size_t)m * p.OC + oc0 + ch * 32 : nullptr;
+      const float* res = (VARIANT >= V_F32_RES && VARIANT < V_DEQUANT && row_ok) ? p.residual + (size_t)m * p.OC + oc0 + ch * 32 : nullptr;
       epilogue_chunk<VARIANT>(p, v, xz, oc0 + ch * 32, esz, res, w);
       if (p.out_tma) {
         const int in_group = (ch - first) % cpg;
@@ -779,7 +833,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         OXB_EPI(V_REQUANT_FMA)
         OXB_EPI(V_REQUANT_FMA_DYN)
         OXB_EPI(V_REQUANT_LEAN)
-        default: epilogue_role<BN, V_REQUANT_LEAN_DYN>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
+        OXB_EPI(V_REQUANT_LEAN_DYN)
+        OXB_EPI(20)
+        OXB_EPI(21)
+        OXB_EPI(22)
+        OXB_EPI(23)
+        OXB_EPI(24)
+        default: epilogue_role<BN, 25>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
       }
     } else {
       switch (p.variant) {
@@ -1110,6 +1170,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
     if (e.x_zp_dev) kp.variant = lean ? V_REQUANT_LEAN_DYN : (fma ? V_REQUANT_FMA_DYN : V_REQUANT_DYN);
     else kp.variant = lean ? V_REQUANT_LEAN : (fma ? V_REQUANT_FMA : V_REQUANT);
   }
+  else if (e.mode == EPI_DEQUANT) kp.variant = V_DEQUANT + (e.x_zp_dev ? 1 : 0) + 2 * e.dq_act;
   else kp.variant = e.x_zp_dev ? V_INT32_DYN : V_INT32;
   if (e.mode == EPI_F32 ? e.bias_f == nullptr : e.bias_i == nullptr) {
     delete pl;
@@ -1117,6 +1178,9 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   }
   kp.bias_f = e.bias_f;
   kp.residual = e.residual;
+  kp.dq_w_scale = e.dq_w_scale;
+  kp.dq_x_scale = e.dq_x_scale_dev;
+  kp.dq_bias = e.dq_bias;
   kp.act = e.act;
   kp.clip_lo = e.clip_lo;
   kp.clip_hi = e.clip_hi;

@@ -27,7 +27,8 @@ const char* kSupportedOps[] = {"Conv",       "Gemm",     "MatMul",  "QLinearConv
                                "QuantizeLinear", "DequantizeLinear", "DynamicQuantizeLinear", "Relu", "Tanh", "Sigmoid",    "PRelu",
                                "Add",        "Sub",      "Mul",     "Div",         "MaxPool",       "GlobalAveragePool", "OxiInstanceNorm",
                                "Resize",     "Pad",      "Concat",  "Flatten",     "Reshape",       "Identity",          "Cast",
-                               "Slice"};
+                               "Slice",      "Gather",   "Transpose", "Softmax",   "LayerNormalization", "LayerNorm",    "Gelu",
+                               "Erf"};
 
 // ---- scalar helpers that must agree with the reference bit for bit -----------------------
 double round_ties_even(double v) { return std::nearbyint(v); }  // default rounding mode: ties to even
@@ -361,6 +362,11 @@ class Planner {
   void plan_pad(const NodeDef& n);
   void plan_concat(const NodeDef& n);
   void plan_slice(const NodeDef& n);
+  void plan_gather(const NodeDef& n);
+  void plan_transpose(const NodeDef& n);
+  void plan_softmax(const NodeDef& n);
+  bool try_plan_scaled_masked_softmax(const NodeDef& n);
+  void plan_layer_norm(const NodeDef& n);
   void plan_alias(const NodeDef& n);
   bool try_plan_residual_chain(const NodeDef& n, int ni);
 
@@ -380,6 +386,8 @@ class Planner {
     int x_zp = 0;
     int x_zp_vi = -1;            // device lane (dynamic)
     int res_vi = -1;             // f32 residual added in the epilogue (a fused Add), or -1
+    int dq_xs_vi = -1;           // dequantising epilogue: the device lane holding the activation scale
+    std::vector<float> dq_w_scale, dq_bias;  // ... and its per-channel weight scales and bias
     std::vector<int32_t> x_zp_rows;
     std::vector<int32_t> bias_i;  // empty or OC
     std::vector<float> bias_f;    // empty or OC
@@ -551,6 +559,11 @@ void Planner::plan_node(int ni) {
   const std::string& op = n.op;
   if (!is_supported_op(op)) OXB_DECLINE("operator '%s' (node '%s') is not claimed by this provider", op.c_str(), n.name.c_str());
   if (op == "Slice") return plan_slice(n);
+  if (op == "Gather") return plan_gather(n);
+  if (op == "Transpose") return plan_transpose(n);
+  if (op == "Softmax") return plan_softmax(n);
+  if (op == "LayerNormalization" || op == "LayerNorm") return plan_layer_norm(n);
+  if (op == "Gelu" || op == "Erf") return plan_unary(n);
   if (op == "QuantizeLinear") return plan_quantize(n);
   if (op == "DequantizeLinear") {
     if (try_plan_residual_chain(n, ni)) return;
@@ -810,10 +823,19 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
     }
   epi.acc_abs_bound = acc_abs_bound;
 
-  const int x_vi = c.x_vi, out_vi = c.out_vi, xzp_vi = c.x_zp_vi, res_vi = c.res_vi;
+  const int x_vi = c.x_vi, out_vi = c.out_vi, xzp_vi = c.x_zp_vi, res_vi = c.res_vi, dq_vi = c.dq_xs_vi;
   std::vector<int> reads = {x_vi};
   if (xzp_vi >= 0) reads.push_back(xzp_vi);
   if (res_vi >= 0) reads.push_back(res_vi);
+  if (dq_vi >= 0) reads.push_back(dq_vi);
+  if (epi.mode == k::EPI_DEQUANT) {
+    const size_t padded = align_up((size_t)OC, 256);
+    std::vector<float> ws = c.dq_w_scale, bs = c.dq_bias;
+    ws.resize(padded, 0.f);
+    bs.resize(padded, 0.f);
+    epi.dq_w_scale = upload_vec(ws);
+    epi.dq_bias = upload_vec(bs);
+  }
 
   if (want_umma) {
     const int kind = c.is_int ? 0 : 1;
@@ -876,16 +898,17 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
     const DT xdt = xv.dt, wdt = c.is_int ? c.w_dt : DT::F32;
     Step* stp = &st;
     const int step_index = (int)S.steps_.size() - 1;
-    st.finalize = [this, step_index, x_vi, out_vi, xzp_vi, res_vi, wdev, xdt, wdt, cs, epi, kind, n]() mutable {
+    st.finalize = [this, step_index, x_vi, out_vi, xzp_vi, res_vi, dq_vi, wdev, xdt, wdt, cs, epi, kind, n]() mutable {
       k::Epilogue e = epi;
       if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
       if (res_vi >= 0) e.residual = (const float*)V(res_vi).ptr;
+      if (dq_vi >= 0) e.dq_x_scale_dev = (const float*)V(dq_vi).ptr;
       std::string why2;
       k::UmmaPlan* plan = k::umma_plan_create(V(x_vi).ptr, xdt, wdev, wdt, V(out_vi).ptr, cs, e, kind, &why2);
       if (!plan) OXB_FAIL("%s '%s': tensor-core plan rejected after selection: %s", n.op.c_str(), n.name.c_str(), why2.c_str());
       S.umma_plans_.push_back(plan);
       Step& me = S.steps_[step_index];
-      me.kernel = std::string(k::umma_plan_desc(plan)) + (res_vi >= 0 ? " +residual" : "");
+      me.kernel = std::string(k::umma_plan_desc(plan)) + (res_vi >= 0 ? " +residual" : "") + (dq_vi >= 0 ? " +dequant" : "");
       int* err = S.err_flag_;
       me.launch = [this, plan, err](cudaStream_t s) {
         k::umma_launch(plan, err, s);
@@ -948,10 +971,11 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
     st.work_is_bytes = false;
     const DT xdt = xv.dt;
     const int plain = c.x_plain_nchw ? 1 : 0;
-    st.launch = [this, x_vi, out_vi, xzp_vi, res_vi, wdev, xdt, wdt, cs, epi, plain](cudaStream_t s) {
+    st.launch = [this, x_vi, out_vi, xzp_vi, res_vi, dq_vi, wdev, xdt, wdt, cs, epi, plain](cudaStream_t s) {
       k::Epilogue e = epi;
       if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
       if (res_vi >= 0) e.residual = (const float*)V(res_vi).ptr;
+      if (dq_vi >= 0) e.dq_x_scale_dev = (const float*)V(dq_vi).ptr;
       k::conv_direct(V(x_vi).ptr, xdt, plain, wdev, wdt, V(out_vi).ptr, cs, e, s);
       C.counters.simt_launches++;
       C.counters.kernel_launches++;
@@ -1640,6 +1664,66 @@ void Planner::plan_matmul_family(const NodeDef& n, int ni) {
   if (is_mi) {
     c.epi.mode = k::EPI_INT32;
     c.epi.out_dt = DT::I32;
+    // The chain a dynamically quantised linear is exported as,
+    //   MatMulInteger -> Cast(to float) -> Mul(Mul(x_scale, w_scale[N])) -> Add(bias[N]) [-> Gelu],
+    // runs inside the contraction's epilogue with the same roundings (each product and sum on its own).
+    if (!C.cfg().keep_intermediates && os.size() == 2) {
+      auto only_user = [&](const std::string& name, const char* opn) -> int {
+        if (graph_outputs_.count(name)) return -1;
+        auto it = consumers_.find(name);
+        if (it == consumers_.end() || it->second.size() != 1) return -1;
+        const int ni2 = it->second[0].first;
+        return (!skipped_[ni2] && nodes_[ni2].op == opn) ? ni2 : -1;
+      };
+      auto producer_of = [&](const std::string& name) -> int {
+        for (size_t j = 0; j < nodes_.size(); ++j)
+          for (const std::string& o : nodes_[j].outputs)
+            if (o == name) return (int)j;
+        return -1;
+      };
+      const int cast_i = only_user(n.outputs[0], "Cast");
+      const int mul_i = cast_i >= 0 && nodes_[cast_i].attrs.i("to", 1) == 1 ? only_user(nodes_[cast_i].outputs[0], "Mul") : -1;
+      const int add_i = mul_i >= 0 ? only_user(nodes_[mul_i].outputs[0], "Add") : -1;
+      if (add_i >= 0 && nodes_[mul_i].inputs.size() == 2 && nodes_[add_i].inputs.size() == 2) {
+        const NodeDef& mul = nodes_[mul_i];
+        const NodeDef& add = nodes_[add_i];
+        const std::string& sc_name = mul.inputs[0] == nodes_[cast_i].outputs[0] ? mul.inputs[1] : mul.inputs[0];
+        const std::string& bias_name = add.inputs[0] == mul.outputs[0] ? add.inputs[1] : add.inputs[0];
+        const HostTensor* bias = const_of(bias_name);
+        const int sc_i = producer_of(sc_name);
+        int sc_user = -1;
+        if (sc_i >= 0 && !skipped_[sc_i] && nodes_[sc_i].op == "Mul" && nodes_[sc_i].inputs.size() == 2) sc_user = only_user(sc_name, "Mul");
+        if (bias && (int64_t)bias->data.size() == N && S.index_.find(bias_name) == S.index_.end() && sc_user == mul_i) {
+          const NodeDef& scn = nodes_[sc_i];
+          for (int slot = 0; slot < 2; ++slot) {
+            auto xs = S.index_.find(scn.inputs[slot]);
+            const HostTensor* ws = const_of(scn.inputs[1 - slot]);
+            if (xs == S.index_.end() || !ws || (int64_t)ws->data.size() != N || S.index_.count(scn.inputs[1 - slot])) continue;
+            const Value& xv2 = V(xs->second);
+            if (xv2.dt != DT::F32 || xv2.numel() != 1 || xv2.host != nullptr) continue;
+            c.dq_xs_vi = xs->second;
+            c.dq_w_scale = ws->data;
+            c.dq_bias = bias->data;
+            break;
+          }
+        }
+        if (c.dq_xs_vi >= 0) {
+          skipped_[cast_i] = skipped_[mul_i] = skipped_[add_i] = skipped_[sc_i] = 1;
+          std::string out_name = add.outputs[0];
+          c.epi.mode = k::EPI_DEQUANT;
+          c.epi.out_dt = DT::F32;
+          const int gelu_i = only_user(out_name, "Gelu");
+          if (gelu_i >= 0 && nodes_[gelu_i].inputs.size() == 1) {
+            skipped_[gelu_i] = 1;
+            c.epi.dq_act = nodes_[gelu_i].attrs.s("approximate") == "tanh" ? 2 : 1;
+            out_name = nodes_[gelu_i].outputs[0];
+          }
+          c.out_vi = add_value(out_name, os, DT::F32, Layout::PLAIN);
+          emit_contraction(n, c);
+          return;
+        }
+      }
+    }
     c.out_vi = add_value(n.outputs[0], os, DT::I32, Layout::PLAIN);
     emit_contraction(n, c);
     return;
@@ -1682,10 +1766,14 @@ void Planner::plan_matmul_family(const NodeDef& n, int ni) {
 
 // ---- element-wise ----------------------------------------------------------------------------
 void Planner::plan_unary(const NodeDef& n) {
-  check_attrs(n, {});
+  if (n.op == "Gelu") check_attrs(n, {"approximate"});
+  else check_attrs(n, {});
   int xi = value_of(in_name(n, 0));
   const Value xv = V(xi);
   int op = n.op == "Relu" ? k::UN_RELU : (n.op == "Tanh" ? k::UN_TANH : k::UN_SIGMOID);
+  // Gelu: exact unless approximate == "tanh" (nn_ops/activations.rs:357-386); Erf: the same polynomial
+  if (n.op == "Gelu") op = n.attrs.s("approximate") == "tanh" ? k::UN_GELU_TANH : k::UN_GELU_ERF;
+  if (n.op == "Erf") op = k::UN_ERF;
   if (op != k::UN_RELU && xv.dt != DT::F32) OXB_DECLINE("%s '%s': input is not a float tensor", n.op.c_str(), n.name.c_str());
   DT odt = xv.dt;
   if (op == k::UN_RELU && xv.dt == DT::I16) odt = DT::I16;
@@ -1704,6 +1792,7 @@ void Planner::plan_unary(const NodeDef& n) {
 void Planner::plan_binary(const NodeDef& n, int ni) {
   (void)ni;
   check_attrs(n, {});
+  if (try_plan_scaled_masked_softmax(n)) return;
   int ai = value_of(in_name(n, 0)), bi = value_of(in_name(n, 1));
   Value av = V(ai), bv = V(bi);
   if (av.dt != DT::F32 && av.dt != DT::I32) OXB_DECLINE("%s '%s': operand A is a quantised tensor", n.op.c_str(), n.name.c_str());
@@ -2090,6 +2179,185 @@ void Planner::plan_slice(const NodeDef& n) {
   stp.work = 2.0 * (double)V(yi).bytes;
   stp.launch = [this, xi, yi, dt, xd, yd, sd](cudaStream_t s) {
     k::slice_rows(V(xi).ptr, V(yi).ptr, dt, xd, yd, sd, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+// Gather along axis 0 of a rank-2 initializer (an embedding table) with device-resident index lanes
+// (indexing/gather.rs:12-44).  Other forms are declined.
+void Planner::plan_gather(const NodeDef& n) {
+  check_attrs(n, {"axis"});
+  const HostTensor* table = const_in(n, 0);
+  if (!table || table->shape.size() != 2) OXB_DECLINE("Gather '%s': only a rank-2 initializer table is claimed", n.name.c_str());
+  int64_t axis = n.attrs.i("axis", 0);
+  if (axis < 0) axis += 2;
+  if (axis != 0) OXB_DECLINE("Gather '%s': only axis 0 is claimed", n.name.c_str());
+  int ii = value_of(in_name(n, 1));
+  if (V(ii).dt != DT::F32) OXB_DECLINE("Gather '%s': indices are not f32 lanes", n.name.c_str());
+  if (V(ii).shape.size() == 4 && V(ii).layout == Layout::NHWC && !order_free(V(ii))) ii = ensure_layout(n, ii, Layout::PLAIN);
+  const int64_t rows = table->shape[0], inner = table->shape[1];
+  std::vector<int64_t> os = V(ii).shape;
+  os.push_back(inner);
+  if (os.size() > 4) OXB_DECLINE("Gather '%s': output rank above 4", n.name.c_str());
+  const float* dtable = (const float*)C.resident_form(in_name(n, 0), "raw_f32", table->data.size() * 4,
+                                                      [table](void* p) { std::memcpy(p, table->data.data(), table->data.size() * 4); },
+                                                      cacheable_const(in_name(n, 0)));
+  int yi = add_value(n.outputs[0], os, DT::F32, Layout::PLAIN);
+  const int64_t n_idx = V(ii).numel();
+  int* err = S.err_flag_;
+  Step& st = add_step(n, "gather_rows", 2, {ii}, {yi});
+  st.work = 2.0 * (double)V(yi).bytes;
+  st.launch = [this, ii, yi, dtable, n_idx, rows, inner, err](cudaStream_t s) {
+    k::gather_rows(dtable, (const float*)V(ii).ptr, (float*)V(yi).ptr, n_idx, rows, inner, err, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+// Transpose (shape/basic.rs:146): any permutation of up to four logical axes of a 32-bit tensor.
+void Planner::plan_transpose(const NodeDef& n) {
+  check_attrs(n, {"perm"});
+  int xi = value_of(in_name(n, 0));
+  const int rank = (int)V(xi).shape.size();
+  if (rank < 1 || rank > 4) OXB_DECLINE("Transpose '%s': only ranks 1..4 are claimed", n.name.c_str());
+  if (dt_size(V(xi).dt) != 4) OXB_DECLINE("Transpose '%s': only 32-bit storage is claimed", n.name.c_str());
+  std::vector<int64_t> perm = n.attrs.int_list("perm");
+  if (perm.empty())
+    for (int d = rank - 1; d >= 0; --d) perm.push_back(d);
+  if ((int)perm.size() != rank) OXB_DECLINE("transpose: perm len %zu != ndim %d", perm.size(), rank);
+  std::vector<char> seen(rank, 0);
+  for (int64_t pv : perm) {
+    if (pv < 0 || pv >= rank || seen[pv]) OXB_DECLINE("transpose: perm is not a permutation");
+    seen[pv] = 1;
+  }
+  if (rank == 4 && V(xi).layout == Layout::NHWC && !order_free(V(xi))) xi = ensure_layout(n, xi, Layout::PLAIN);
+  const Value xv = V(xi);
+  std::vector<int64_t> xs(rank, 1), os(rank);
+  for (int d = rank - 2; d >= 0; --d) xs[d] = xs[d + 1] * xv.shape[d + 1];
+  for (int d = 0; d < rank; ++d) os[d] = xv.shape[perm[d]];
+  int yi = add_value(n.outputs[0], os, xv.dt, Layout::PLAIN);
+  Dims4 yd{1, 1, 1, 1}, st4{0, 0, 0, 0};
+  int64_t* yf[4] = {&yd.N, &yd.C, &yd.H, &yd.W};
+  int64_t* sf[4] = {&st4.N, &st4.C, &st4.H, &st4.W};
+  for (int d = 0; d < rank; ++d) {
+    *yf[4 - rank + d] = os[d];
+    *sf[4 - rank + d] = xs[perm[d]];
+  }
+  Step& st = add_step(n, "transpose_perm", 2, {xi}, {yi});
+  st.work = 2.0 * (double)xv.bytes;
+  st.launch = [this, xi, yi, yd, st4](cudaStream_t s) {
+    k::transpose_perm(V(xi).ptr, V(yi).ptr, yd, st4, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+// Softmax over the last axis (nn/normalization.rs softmax_into); other axes are declined.
+// Mul(x, scalar) -> Add(., mask[B,1,1,S]) -> Softmax(last axis) over x[B,H,Q,S]: the attention-score chain.  The
+// softmax kernel applies the product and the sum (rounded as the nodes would) while it reads its input.
+bool Planner::try_plan_scaled_masked_softmax(const NodeDef& n) {
+  if (C.cfg().keep_intermediates || n.op != "Mul" || n.inputs.size() != 2 || !n.attrs.names().empty()) return false;
+  int slot = -1;
+  for (int sl = 0; sl < 2; ++sl) {
+    auto it = S.index_.find(n.inputs[sl]);
+    const HostTensor* sc = const_of(n.inputs[1 - sl]);
+    if (it != S.index_.end() && sc && sc->data.size() == 1 && !S.index_.count(n.inputs[1 - sl]) && V(it->second).shape.size() == 4 && V(it->second).dt == DT::F32 &&
+        V(it->second).host == nullptr)
+      slot = sl;
+  }
+  if (slot < 0) return false;
+  const int xi0 = S.index_.find(n.inputs[slot])->second;
+  if (V(xi0).layout == Layout::NHWC && !order_free(V(xi0))) return false;
+  auto only_user = [&](const std::string& name, const char* opn) -> int {
+    if (graph_outputs_.count(name)) return -1;
+    auto it = consumers_.find(name);
+    if (it == consumers_.end() || it->second.size() != 1) return -1;
+    const int ni2 = it->second[0].first;
+    return (!skipped_[ni2] && nodes_[ni2].op == opn) ? ni2 : -1;
+  };
+  const int add_i = only_user(n.outputs[0], "Add");
+  if (add_i < 0 || nodes_[add_i].inputs.size() != 2) return false;
+  const NodeDef& add = nodes_[add_i];
+  const std::string& mask_name = add.inputs[0] == n.outputs[0] ? add.inputs[1] : add.inputs[0];
+  auto mit = S.index_.find(mask_name);
+  if (mit == S.index_.end()) return false;
+  const std::vector<int64_t>& xs = V(xi0).shape;
+  const std::vector<int64_t> want = {xs[0], 1, 1, xs[3]};
+  if (V(mit->second).shape != want || V(mit->second).dt != DT::F32) return false;
+  const int sm_i = only_user(add.outputs[0], "Softmax");
+  if (sm_i < 0) return false;
+  int64_t axis = nodes_[sm_i].attrs.i("axis", -1);
+  if (axis < 0) axis += 4;
+  if (axis != 3) return false;
+  const float* dscale = (const float*)C.resident_form(n.inputs[1 - slot], "raw_f32", 4, [sc = const_of(n.inputs[1 - slot])](void* p) { std::memcpy(p, sc->data.data(), 4); },
+                                                      cacheable_const(n.inputs[1 - slot]));
+  skipped_[add_i] = skipped_[sm_i] = 1;
+  const int mi = mit->second;
+  const int64_t len = xs[3], rows = V(xi0).numel() / len, rows_per_mask = xs[1] * xs[2];
+  int yi = add_value(nodes_[sm_i].outputs[0], xs, DT::F32, Layout::PLAIN);
+  Step& st = add_step(nodes_[sm_i], "softmax_rows+scale+mask", 2, {xi0, mi}, {yi});
+  st.work = 2.0 * (double)V(xi0).bytes;
+  st.launch = [this, xi0, mi, yi, rows, len, dscale, rows_per_mask](cudaStream_t s) {
+    k::softmax_rows((const float*)V(xi0).ptr, (float*)V(yi).ptr, rows, len, dscale, (const float*)V(mi).ptr, rows_per_mask, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+  return true;
+}
+
+void Planner::plan_softmax(const NodeDef& n) {
+  check_attrs(n, {"axis"});
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).dt != DT::F32) OXB_DECLINE("Softmax '%s': input is not a float tensor", n.name.c_str());
+  const int rank = (int)V(xi).shape.size();
+  int64_t axis = n.attrs.i("axis", -1);
+  if (axis < 0) axis += rank;
+  if (rank < 1 || axis != rank - 1) OXB_DECLINE("Softmax '%s': only the last axis is claimed", n.name.c_str());
+  if (rank == 4 && V(xi).layout == Layout::NHWC && !order_free(V(xi))) xi = ensure_layout(n, xi, Layout::PLAIN);
+  const Value xv = V(xi);
+  const int64_t len = xv.shape[rank - 1], rows = len ? xv.numel() / len : 0;
+  int yi = add_value(n.outputs[0], xv.shape, DT::F32, Layout::PLAIN);
+  Step& st = add_step(n, "softmax_rows", 2, {xi}, {yi});
+  st.work = 2.0 * (double)xv.bytes;
+  st.launch = [this, xi, yi, rows, len](cudaStream_t s) {
+    k::softmax_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, nullptr, nullptr, 1, s);
+    C.counters.glue_launches++;
+    C.counters.kernel_launches++;
+  };
+}
+
+// LayerNormalization over the last axis with initializer scale (and bias) of that length
+// (nn/normalization.rs layer_norm_into, the ONNX-conformant case); other forms are declined.
+void Planner::plan_layer_norm(const NodeDef& n) {
+  check_attrs(n, {"axis", "epsilon", "stash_type"});
+  int xi = value_of(in_name(n, 0));
+  if (V(xi).dt != DT::F32) OXB_DECLINE("LayerNormalization '%s': input is not a float tensor", n.name.c_str());
+  const int rank = (int)V(xi).shape.size();
+  int64_t axis = n.attrs.i("axis", -1);
+  if (axis < 0) axis += rank;
+  if (rank < 1 || axis != rank - 1) OXB_DECLINE("LayerNormalization '%s': only the last axis is claimed", n.name.c_str());
+  if (n.outputs.size() > 1 && !n.outputs[1].empty()) OXB_DECLINE("LayerNormalization '%s': mean / inv-std outputs are not produced", n.name.c_str());
+  const HostTensor* scale = const_in(n, 1);
+  const HostTensor* bias = has_in(n, 2) ? const_in(n, 2) : nullptr;
+  if (!scale || (has_in(n, 2) && !bias)) OXB_DECLINE("LayerNormalization '%s': scale / bias are not initializers", n.name.c_str());
+  if (rank == 4 && V(xi).layout == Layout::NHWC && !order_free(V(xi))) xi = ensure_layout(n, xi, Layout::PLAIN);
+  const Value xv = V(xi);
+  const int64_t len = xv.shape[rank - 1], rows = len ? xv.numel() / len : 0;
+  if ((int64_t)scale->data.size() != len || (bias && (int64_t)bias->data.size() != len)) OXB_DECLINE("LayerNormalization '%s': scale / bias length differs from the axis", n.name.c_str());
+  const float eps = n.attrs.f("epsilon", 1e-5f);
+  const float* dscale = (const float*)C.resident_form(in_name(n, 1), "raw_f32", scale->data.size() * 4,
+                                                      [scale](void* p) { std::memcpy(p, scale->data.data(), scale->data.size() * 4); },
+                                                      cacheable_const(in_name(n, 1)));
+  const float* dbias = nullptr;
+  if (bias)
+    dbias = (const float*)C.resident_form(in_name(n, 2), "raw_f32", bias->data.size() * 4, [bias](void* p) { std::memcpy(p, bias->data.data(), bias->data.size() * 4); },
+                                          cacheable_const(in_name(n, 2)));
+  int yi = add_value(n.outputs[0], xv.shape, DT::F32, Layout::PLAIN);
+  Step& st = add_step(n, "layer_norm_rows", 2, {xi}, {yi});
+  st.work = 2.0 * (double)xv.bytes;
+  st.launch = [this, xi, yi, rows, len, dscale, dbias, eps](cudaStream_t s) {
+    k::layer_norm_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, dscale, dbias, eps, s);
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };

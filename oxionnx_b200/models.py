@@ -334,3 +334,88 @@ def build_inswapper_f32(batch=16, size=128, widths=(128, 256, 512, 1024), blocks
         return {"target": target, "latent": z}
 
     return graph, g.weights, feeds, dict(ops=2.0 * macs[0] * batch, macs_per_image=macs[0], batch=batch)
+
+
+# ---------------------------------------------------------------------------------------------
+# C4: BERT-base-shaped encoder, dynamic INT8 linears
+# ---------------------------------------------------------------------------------------------
+def build_bert_dynamic_int8(batch=64, seq=128, hidden=768, heads=12, ffn=3072, layers=12, vocab=30522):
+    """Token ids uniform in [0, vocab), attention mask all ones.  Every linear is
+    DynamicQuantizeLinear (u8, per tensor: quant_ops/dynamic_quantize.rs:40-94) -> MatMulInteger
+    (i8 per-output-channel weights ~ round(N(0, 40)) clipped to +-127, zero point 0;
+    qlinear_matmul.rs:181-199) -> Cast -> Mul(x_scale * w_scale[n]) -> Add(bias), the chain a
+    dynamically quantised export spells; LayerNormalization, Softmax, Gelu and the two attention
+    products stay in f32.  Returns the last hidden state [batch, seq, hidden]."""
+    g = _G()
+    r = _rng("c4")
+    macs = [0]
+    d_head = hidden // heads
+    g.w("word_emb", (r.standard_normal((vocab, hidden)) * 0.05).astype(np.float32))
+    g.w("pos_emb", (r.standard_normal((seq, hidden)) * 0.05).astype(np.float32))
+    g.w("type_emb", (r.standard_normal(hidden) * 0.05).astype(np.float32))
+    g.w("one", [1.0]), g.w("mask_scale", [-10000.0]), g.w("mask_shape", [batch, 1, 1, seq]), g.w("att_scale", [1.0 / np.sqrt(d_head)])
+    g.w("rows_shape", [batch * seq, hidden]), g.w("heads_shape", [batch, seq, heads, d_head]), g.w("out_shape", [batch, seq, hidden])
+
+    def layer_norm(x, name):
+        g.w(f"{name}_g", r.uniform(0.8, 1.2, hidden).astype(np.float32))
+        g.w(f"{name}_b", (r.standard_normal(hidden) * 0.05).astype(np.float32))
+        return g.node("LayerNormalization", [x, f"{name}_g", f"{name}_b"], [f"{name}_out"], name=name, axis=-1, epsilon=1e-12)
+
+    def quantise(x, name):
+        g.node("DynamicQuantizeLinear", [x], [f"{name}_q", f"{name}_s", f"{name}_z"], name=name)
+        return f"{name}_q", f"{name}_s", f"{name}_z"
+
+    def linear(xq, xs, xz, k, n, name):
+        wq = np.clip(np.rint(r.standard_normal((k, n)) * 40.0), -127, 127).astype(np.float32)
+        g.w(f"{name}_w", wq)
+        g.w(f"{name}_ws", r.uniform(0.0005, 0.002, n).astype(np.float32) * np.float32(np.sqrt(768.0 / k)))
+        g.w(f"{name}_bias", (r.standard_normal(n) * 0.02).astype(np.float32))
+        macs[0] += seq * k * n
+        acc = g.node("MatMulInteger", [xq, f"{name}_w", xz], [f"{name}_acc"], name=f"{name}_mmi")
+        accf = g.node("Cast", [acc], [f"{name}_accf"], name=f"{name}_cast", to=1)
+        sc = g.node("Mul", [xs, f"{name}_ws"], [f"{name}_scale"], name=f"{name}_scales")
+        y = g.node("Mul", [accf, sc], [f"{name}_scaled"], name=f"{name}_rescale")
+        return g.node("Add", [y, f"{name}_bias"], [f"{name}_out"], name=f"{name}_addb")
+
+    emb = g.node("Gather", ["word_emb", "input_ids"], ["emb_word"], name="emb_gather", axis=0)
+    emb = g.node("Add", [emb, "pos_emb"], ["emb_pos"], name="emb_add_pos")
+    emb = g.node("Add", [emb, "type_emb"], ["emb_sum"], name="emb_add_type")
+    x = layer_norm(emb, "emb_ln")
+    x = g.node("Reshape", [x, "rows_shape"], ["x0"], name="rows")
+    m = g.node("Sub", ["one", "attention_mask"], ["mask_inv"], name="mask_inv")
+    m = g.node("Mul", [m, "mask_scale"], ["mask_add"], name="mask_scale_mul")
+    mask = g.node("Reshape", [m, "mask_shape"], ["mask4"], name="mask_reshape")
+    for li in range(layers):
+        p = f"l{li}"
+        xq, xs, xz = quantise(x, f"{p}_qx")
+        q = linear(xq, xs, xz, hidden, hidden, f"{p}_q")
+        k = linear(xq, xs, xz, hidden, hidden, f"{p}_k")
+        v = linear(xq, xs, xz, hidden, hidden, f"{p}_v")
+        q4 = g.node("Transpose", [g.node("Reshape", [q, "heads_shape"], [f"{p}_q4r"], name=f"{p}_q_split")], [f"{p}_q4"], name=f"{p}_q_t", perm=[0, 2, 1, 3])
+        k4 = g.node("Transpose", [g.node("Reshape", [k, "heads_shape"], [f"{p}_k4r"], name=f"{p}_k_split")], [f"{p}_k4t"], name=f"{p}_k_t", perm=[0, 2, 3, 1])
+        v4 = g.node("Transpose", [g.node("Reshape", [v, "heads_shape"], [f"{p}_v4r"], name=f"{p}_v_split")], [f"{p}_v4"], name=f"{p}_v_t", perm=[0, 2, 1, 3])
+        s = g.node("MatMul", [q4, k4], [f"{p}_scores"], name=f"{p}_qk")
+        s = g.node("Mul", [s, "att_scale"], [f"{p}_scores_scaled"], name=f"{p}_scale")
+        s = g.node("Add", [s, mask], [f"{p}_scores_masked"], name=f"{p}_mask")
+        pr = g.node("Softmax", [s], [f"{p}_probs"], name=f"{p}_softmax", axis=-1)
+        c = g.node("MatMul", [pr, v4], [f"{p}_ctx4"], name=f"{p}_av")
+        macs[0] += 2 * heads * seq * seq * d_head
+        c = g.node("Transpose", [c], [f"{p}_ctx_t"], name=f"{p}_ctx_merge_t", perm=[0, 2, 1, 3])
+        c = g.node("Reshape", [c, "rows_shape"], [f"{p}_ctx"], name=f"{p}_ctx_merge")
+        cq, cs, cz = quantise(c, f"{p}_qc")
+        o = linear(cq, cs, cz, hidden, hidden, f"{p}_o")
+        x1 = layer_norm(g.node("Add", [o, x], [f"{p}_res1"], name=f"{p}_add1"), f"{p}_ln1")
+        hq, hs, hz = quantise(x1, f"{p}_qh")
+        h = linear(hq, hs, hz, hidden, ffn, f"{p}_f1")
+        h = g.node("Gelu", [h], [f"{p}_gelu"], name=f"{p}_act")
+        fq, fs, fz = quantise(h, f"{p}_qf")
+        f2 = linear(fq, fs, fz, ffn, hidden, f"{p}_f2")
+        x = layer_norm(g.node("Add", [f2, x1], [f"{p}_res2"], name=f"{p}_add2"), f"{p}_ln2")
+    g.node("Reshape", [x, "out_shape"], ["hidden"], name="out_reshape")
+    graph = Graph(nodes=g.nodes, input_names=["input_ids", "attention_mask"], output_names=["hidden"])
+
+    def feeds(b=batch, seed_tag="c4_in"):
+        rr = _rng(seed_tag)
+        return {"input_ids": rr.integers(0, vocab, (b, seq)).astype(np.float32), "attention_mask": np.ones((b, seq), np.float32)}
+
+    return graph, g.weights, feeds, dict(ops=2.0 * macs[0] * batch, macs_per_sequence=macs[0], batch=batch, tokens=batch * seq)
