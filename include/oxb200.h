@@ -158,6 +158,9 @@ const char* oxb200_last_error(const oxb200_ctx* ctx); /* ctx may be NULL: last e
 void oxb200_get_counters(const oxb200_ctx* ctx, oxb200_counters* out);
 /* CudaContext::release_device_caches */
 int oxb200_release_device_caches(oxb200_ctx* ctx);
+/* Switches the per-node CUDA-event timing of planned runs (oxb200_config.profile) on or off for later runs;
+ * the reference has no counterpart (its profiler wraps whole nodes on the host, src/session/profiling.rs). */
+int oxb200_set_profile(oxb200_ctx* ctx, int on);
 
 /* Page-locked host memory for feeds and fetches (the reference's pinned staging,
  * src/residency.rs:1147-1312, handed to the caller so no extra host copy is needed). */

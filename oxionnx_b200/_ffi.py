@@ -76,6 +76,7 @@ SYMBOLS = {
     "oxb200_last_error": (ctypes.c_char_p, [ctypes.c_void_p]),
     "oxb200_get_counters": (None, [ctypes.c_void_p, _P(Counters)]),
     "oxb200_release_device_caches": (ctypes.c_int, [ctypes.c_void_p]),
+    "oxb200_set_profile": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "oxb200_host_alloc": (ctypes.c_void_p, [ctypes.c_size_t]),
     "oxb200_host_free": (None, [ctypes.c_void_p]),
     "oxb200_weight_register": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(ctypes.c_float), ctypes.c_uint64, _P(ctypes.c_uint64),

@@ -172,6 +172,13 @@ int oxb200_release_device_caches(oxb200_ctx* ctx) {
   });
 }
 
+int oxb200_set_profile(oxb200_ctx* ctx, int on) {
+  if (!ctx) return OXB200_FAILED;
+  std::lock_guard<std::mutex> lock(ctx->impl.mu);
+  ctx->impl.set_profile(on);
+  return OXB200_OK_HOST;
+}
+
 void* oxb200_host_alloc(size_t bytes) {
   void* p = nullptr;
   if (cudaMallocHost(&p, bytes ? bytes : 1) != cudaSuccess) {

@@ -669,6 +669,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
+  // let the next grid in the stream start its own prologue, then wait for the previous grid's results
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // The producer and the MMA issuer run their loops with the whole warp (every lane polls the
   // barrier, one lane issues): a lone lane looping while its 31 siblings sit at the teardown
@@ -940,7 +943,21 @@ void launch_t(const KParams& kp, int grid, size_t smem, cudaStream_t s) {
     attr_set = true;
     attr_smem = smem;
   }
-  umma_conv_kernel<BN, KIND><<<grid, NUM_THREADS, smem, s>>>(kp);
+  // Programmatic dependent launch: this grid may be scheduled while its predecessor in the stream drains, so
+  // that its prologue (barrier setup, TMEM allocation) overlaps the predecessor's tail; it touches no global
+  // memory before griddepcontrol.wait, which returns only once the predecessor has completed and flushed.
+  static const bool pdl = std::getenv("OXB200_NO_PDL") == nullptr;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  OXB_CUDA(cudaLaunchKernelEx(&cfg, umma_conv_kernel<BN, KIND>, kp));
 }
 
 }  // namespace

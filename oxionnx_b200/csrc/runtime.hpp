@@ -149,6 +149,7 @@ class Context {
   int device() const { return device_; }
   cudaStream_t stream() const { return stream_; }
   const oxb200_config& cfg() const { return cfg_; }
+  void set_profile(int on) { cfg_.profile = on ? 1 : 0; }
   void make_current();
 
   void register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank);

@@ -171,6 +171,10 @@ class CudaContext:
     def release_device_caches(self):
         _raise_for(_ffi.lib().oxb200_release_device_caches(self.handle), self.last_error())
 
+    def set_profiling(self, on: bool):
+        """Per-node CUDA-event timing of planned runs, on or off, for the runs that follow."""
+        _raise_for(_ffi.lib().oxb200_set_profile(self.handle, int(bool(on))), self.last_error())
+
     def shadow_verify(self, op: str, device_result: np.ndarray, cpu_result: np.ndarray):
         a = np.ascontiguousarray(device_result, dtype=np.float32).ravel()
         b = np.ascontiguousarray(cpu_result, dtype=np.float32).ravel()
