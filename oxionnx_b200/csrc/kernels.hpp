@@ -105,7 +105,8 @@ void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offse
 void gather_rows(const float* table, const float* idx, float* out, int64_t n_idx, int64_t rows, int64_t inner, int* err, cudaStream_t s);
 void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstride, cudaStream_t s);
 // softmax_rows optionally applies x * scale[0] and + mask[row / rows_per_mask][:] first (fused Mul / Add producers).
-void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, cudaStream_t s);
+void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, int round_tf32,
+                  cudaStream_t s);
 void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s);
 // Slice with unit steps over logical (row-major) axes padded to four: y[i] = x[i + start], dims as (N, C, H, W).
 void slice_rows(const void* x, void* y, DT dt, const Dims4& xd, const Dims4& yd, const Dims4& start, cudaStream_t s);
@@ -195,6 +196,23 @@ void conv_direct(const void* x, DT x_dt, int x_plain_nchw, const void* w, DT w_d
 // side (stride 0), used for activation x activation products.
 void matmul_f32_direct(const float* a, const float* b, float* c, int64_t batch, int64_t M, int64_t K, int64_t N, int64_t a_bstride,
                        int64_t b_bstride, cudaStream_t s);
+
+// Batched TF32 products over strided windows of row-major f32 matrices (see umma_plan_create_batched).
+struct BatchedGemm {
+  const void* a = nullptr;
+  int64_t a_rows = 0, a_cols = 0;
+  const void* b = nullptr;  // [N][K] per item, K contiguous
+  int64_t b_rows = 0, b_cols = 0;
+  void* out = nullptr;
+  int64_t o_rows = 0, o_cols = 0;
+  int outer = 1, inner = 1;  // items = outer * inner
+  int M = 0, N = 0, K = 0;   // per item
+  int a_rb = 0, a_rh = 0, a_ch = 0, b_rb = 0, b_rh = 0, b_ch = 0, o_rb = 0, o_rh = 0, o_ch = 0;
+  const float* zero_bias = nullptr;  // at least align_up(N, 256) zeros
+  int round_tf32 = 0;
+};
+struct UmmaPlan;
+UmmaPlan* umma_plan_create_batched(const BatchedGemm& g, std::string* why);
 
 // True when the driver accepts an im2col tensor map whose W stride is shorter than its channel
 // extent (overlapping positions), which the row-window stem layout needs.

@@ -856,7 +856,7 @@ __device__ __forceinline__ float warp_max(float v) {
 // Softmax over the last axis, one warp per row: max, exp(v - max), sum, multiply by 1 / sum
 // (nn/normalization.rs softmax_into; the sums are reassociated across lanes: float tolerance).
 __global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int64_t n, const float* __restrict__ scale,
-                                    const float* __restrict__ mask, int64_t rows_per_mask) {
+                                    const float* __restrict__ mask, int64_t rows_per_mask, int round_tf32_flag) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -883,7 +883,10 @@ __global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restri
     }
     sum = warp_sum(sum);
     const float inv = __frcp_rn(sum);
-    for (int64_t k = lane; k < n; k += 32) py[k] = __fmul_rn(py[k], inv);
+    for (int64_t k = lane; k < n; k += 32) {
+      const float v = __fmul_rn(py[k], inv);
+      py[k] = round_tf32_flag ? round_tf32(v) : v;
+    }
   }
 }
 
@@ -1180,9 +1183,10 @@ void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstrid
   transpose_perm_kernel<<<grid_for(total), kThreads, 0, s>>>((const uint32_t*)x, (uint32_t*)y, yd, xstride, total);
 }
 
-void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, cudaStream_t s) {
+void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, int round_tf32_flag,
+                  cudaStream_t s) {
   if (rows * n == 0) return;
-  softmax_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, mask, rows_per_mask > 0 ? rows_per_mask : 1);
+  softmax_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, mask, rows_per_mask > 0 ? rows_per_mask : 1, round_tf32_flag);
 }
 
 void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s) {

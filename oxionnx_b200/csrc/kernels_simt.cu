@@ -78,6 +78,7 @@ __device__ __forceinline__ void finish_int(const EpiDev& e, void* out, int64_t i
       const float inner = __fmul_rn(0.7978846f, __fadd_rn(y, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, y), y), y)));
       y = __fmul_rn(__fmul_rn(0.5f, y), __fadd_rn(1.0f, tanhf(inner)));
     }
+    if (e.round_tf32) y = round_tf32(y);
     ((float*)out)[idx] = y;
     return;
   }

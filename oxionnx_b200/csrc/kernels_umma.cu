@@ -60,6 +60,10 @@ struct alignas(64) KParams {
   int kpb;            // K blocks per ring stage: one barrier round trip moves this many
   int stages;
   int n_tiles, m_tiles;
+  // batched products (attention): tile t belongs to item t / (m_tiles * n_tiles) = (outer, inner); each operand
+  // and the output start at row outer * rb + inner * rh and column inner * ch of their matrices
+  int batched, items, items_inner;
+  int a_rb, a_rh, a_ch, b_rb, b_rh, b_ch, o_rb, o_rh, o_ch;
   uint32_t idesc;
   // epilogue
   int mode;
@@ -454,6 +458,7 @@ __device__ __forceinline__ void math_dequant(const KParams& p, const uint32_t (&
         const float inner = __fmul_rn(0.7978846f, __fadd_rn(y, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, y), y), y)));
         y = __fmul_rn(__fmul_rn(0.5f, y), __fadd_rn(1.0f, tanhf(inner)));
       }
+      if (p.round_tf32) y = round_tf32(y);  // the lane feeds a TF32 product
       w[4 * j4 + e] = __float_as_uint(y);
     }
   }
@@ -549,7 +554,15 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
   const int cpg = p.out_tma ? pitch / chunk_bytes : 1;
   uint32_t local = 0;
   for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
-    const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
+    int tt = t, o_row0 = 0, o_col0 = 0;
+    if (p.batched) {
+      const int per = p.m_tiles * p.n_tiles, item = t / per;
+      tt = t - item * per;
+      const int outer = item / p.items_inner, inner = item - outer * p.items_inner;
+      o_row0 = outer * p.o_rb + inner * p.o_rh;
+      o_col0 = inner * p.o_ch;
+    }
+    const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
     const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
     const uint32_t buf = local & 1u;
     if (ew == 0) OXB_TRACE(local, 6);
@@ -589,7 +602,7 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&p.tmO, stage_addr, oc0 + (ch - in_group) * 32, m0 + quarter * 32);
+            tma_store_2d(&p.tmO, stage_addr, o_col0 + oc0 + (ch - in_group) * 32, o_row0 + m0 + quarter * 32);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
@@ -644,7 +657,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   const uint32_t stage_bytes = kb_bytes * (uint32_t)p.kpb;  // one ring stage
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int k_iters = p.taps * p.cblocks;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_tiles = p.m_tiles * p.n_tiles * (p.batched ? p.items : 1);
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
 
   if (threadIdx.x == 0) {
@@ -683,7 +696,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     int ptile = 0;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++ptile) {
       OXB_TRACE(ptile, 0);
-      const int tile_n = t % p.n_tiles, tile_m = t / p.n_tiles;
+      int tt = t, a_row0 = 0, a_col0 = 0, b_row0 = 0, b_col0 = 0;
+      if (p.batched) {
+        const int per = p.m_tiles * p.n_tiles, item = t / per;
+        tt = t - item * per;
+        const int outer = item / p.items_inner, inner = item - outer * p.items_inner;
+        a_row0 = outer * p.a_rb + inner * p.a_rh;
+        a_col0 = inner * p.a_ch;
+        b_row0 = outer * p.b_rb + inner * p.b_rh;
+        b_col0 = inner * p.b_ch;
+      }
+      const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
       const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
       int q0 = 0, p0 = 0, n0 = 0;
       if (p.a_im2col) {
@@ -716,8 +739,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
             const uint32_t a_dst = tiles_base + stage * stage_bytes;
             const int c_off = cb * p.cb_elems;
             if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
-            else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
-            tma_load_2d(a_dst + a_bytes, &p.tmB, full, it * p.cb_elems, oc0);
+            else tma_load_2d(a_dst, &p.tmA, full, a_col0 + c_off, a_row0 + m0);
+            tma_load_2d(a_dst + a_bytes, &p.tmB, full, b_col0 + it * p.cb_elems, b_row0 + oc0);
           }
           if (++cb == p.cblocks) {
             cb = 0;
@@ -735,8 +758,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
             if (lane == 0) {
               const int c_off = cb * p.cb_elems;
               if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
-              else tma_load_2d(a_dst, &p.tmA, full, c_off, m0);
-              tma_load_2d(a_dst + a_bytes, &p.tmB, full, (it + g) * p.cb_elems, oc0);
+              else tma_load_2d(a_dst, &p.tmA, full, a_col0 + c_off, a_row0 + m0);
+              tma_load_2d(a_dst + a_bytes, &p.tmB, full, b_col0 + (it + g) * p.cb_elems, b_row0 + oc0);
             }
             if (++cb == p.cblocks) {
               cb = 0;
@@ -1218,6 +1241,108 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   pl->smem = (size_t)stages * stage_bytes + 1024;
   snprintf(pl->desc, sizeof pl->desc, "umma_%s M=%lld N=%d K=%lld tile=128x%dx%dB stages=%dx%d %s", kind == 0 ? "i8" : "tf32", (long long)M, cs.OC,
            (long long)cs.K(), bn, swz, stages, kpb, gemm_like ? "tiled" : "im2col");
+  return pl;
+}
+
+// Batched f32 (TF32) products whose operands are strided windows of larger row-major matrices: item
+// (outer, inner) multiplies A rows [outer*a_rb + inner*a_rh, +M) x columns [inner*a_ch, +K) by B rows
+// [outer*b_rb + inner*b_rh, +N) x columns [inner*b_ch, +K) (B is [N][K], K contiguous) into out rows
+// [outer*o_rb + inner*o_rh, +M) x columns [inner*o_ch, +N).  This is how attention reads Q, K and V straight
+// out of the [tokens, hidden] outputs of their linears and writes the context back in that layout.
+UmmaPlan* umma_plan_create_batched(const BatchedGemm& g, std::string* why) {
+  auto no = [&](const char* msg) -> UmmaPlan* {
+    if (why) *why = msg;
+    return nullptr;
+  };
+  load_encoders();
+  if (!g_encode_tiled) return no("tensor-map encoders unavailable in this driver");
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.outer <= 0 || g.inner <= 0) return no("empty problem");
+  if (g.M % BLOCK_M != 0) return no("rows per item are not a multiple of 128");
+  const int cb = umma_channel_block(g.K, 1);
+  if (cb == 0) return no("K is not a multiple of a 32-byte block");
+  if (g.N % 32 != 0) return no("columns per item are not a multiple of 32");
+  int bn = 256;
+  while (bn > 32 && g.N % bn != 0) bn /= 2;
+  if (g.N % bn != 0) return no("columns per item do not tile");
+  if ((g.a_ch % 4) || (g.b_ch % 4) || (g.o_ch % 4) || (g.a_cols % 4) || (g.b_cols % 4) || (g.o_cols % 4)) return no("column offsets are not 16-byte granular");
+  if (((uintptr_t)g.a & 127) || ((uintptr_t)g.b & 127) || ((uintptr_t)g.out & 15)) return no("operand base address is not aligned");
+  const int swz = cb * 4;
+  const int64_t items = (int64_t)g.outer * g.inner, m_tiles = g.M / BLOCK_M, n_tiles = g.N / bn;
+  if (items * m_tiles * n_tiles > 0x7fffffffLL) return no("grid too large");
+  UmmaPlan* pl = new UmmaPlan();
+  std::memset(&pl->kp, 0, sizeof(KParams));
+  KParams& kp = pl->kp;
+  const CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint32_t estr[2] = {1, 1};
+  {
+    cuuint64_t gdim[2] = {(cuuint64_t)g.a_cols, (cuuint64_t)g.a_rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)g.a_cols * 4};
+    cuuint32_t box[2] = {(cuuint32_t)cb, (cuuint32_t)BLOCK_M};
+    if (g_encode_tiled(&kp.tmA, dtype, 2, const_cast<void*>(g.a), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum(swz),
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      delete pl;
+      return no("A tensor map rejected by the driver");
+    }
+  }
+  {
+    cuuint64_t gdim[2] = {(cuuint64_t)g.b_cols, (cuuint64_t)g.b_rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)g.b_cols * 4};
+    cuuint32_t box[2] = {(cuuint32_t)cb, (cuuint32_t)bn};
+    if (g_encode_tiled(&kp.tmB, dtype, 2, const_cast<void*>(g.b), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum(swz),
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      delete pl;
+      return no("B tensor map rejected by the driver");
+    }
+  }
+  {
+    const size_t row_bytes = std::min<size_t>(128, (size_t)std::max(bn / 64, 1) * 32 * 4);
+    kp.out_row_bytes = (int)row_bytes;
+    cuuint64_t gdim[2] = {(cuuint64_t)g.o_cols, (cuuint64_t)g.o_rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)g.o_cols * 4};
+    cuuint32_t box[2] = {(cuuint32_t)(row_bytes / 4), 32};
+    if (g_encode_tiled(&kp.tmO, dtype, 2, g.out, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum((int)row_bytes),
+                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      delete pl;
+      return no("output tensor map rejected by the driver");
+    }
+    kp.out_tma = 1;  // the only store path of the batched form
+  }
+  kp.M = g.M;
+  kp.OC = g.N;
+  kp.P = kp.Q = kp.S = 1;
+  kp.sh = kp.sw = kp.dh = kp.dw = 1;
+  kp.taps = 1;
+  kp.cblocks = g.K / cb;
+  kp.cb_elems = cb;
+  kp.swizzle_bytes = swz;
+  kp.n_tiles = (int)n_tiles;
+  kp.m_tiles = (int)m_tiles;
+  kp.batched = 1;
+  kp.items = (int)items;
+  kp.items_inner = g.inner;
+  kp.a_rb = g.a_rb, kp.a_rh = g.a_rh, kp.a_ch = g.a_ch;
+  kp.b_rb = g.b_rb, kp.b_rh = g.b_rh, kp.b_ch = g.b_ch;
+  kp.o_rb = g.o_rb, kp.o_rh = g.o_rh, kp.o_ch = g.o_ch;
+  kp.idesc = make_idesc(1, false, false, bn);
+  const size_t kb_bytes = (size_t)(BLOCK_M + bn) * swz;
+  int kpb = 1;
+  while (kpb < 4 && (size_t)(kpb * 2) * kb_bytes <= 64 * 1024 && kpb * 2 <= kp.cblocks) kpb *= 2;
+  kp.kpb = kpb;
+  const size_t stage_bytes = kb_bytes * kpb;
+  int stages = (int)((192 * 1024) / stage_bytes);
+  stages = std::max(2, std::min(stages, MAX_STAGES));
+  kp.stages = stages;
+  kp.mode = EPI_F32;
+  kp.variant = g.round_tf32 ? 1 : 0;
+  kp.bias_f = g.zero_bias;
+  kp.round_tf32 = g.round_tf32;
+  kp.out_dt = (int)DT::F32;
+  kp.out = g.out;
+  pl->bn = bn;
+  pl->kind = 1;
+  pl->grid = (int)std::min<int64_t>(items * m_tiles * n_tiles, sm_count());
+  pl->smem = (size_t)stages * stage_bytes + 1024;
+  snprintf(pl->desc, sizeof pl->desc, "umma_tf32 batched %lldx(M=%d N=%d K=%d) tile=128x%dx%dB stages=%dx%d", (long long)items, g.M, g.N, g.K, bn, swz, stages, kpb);
   return pl;
 }
 

@@ -339,7 +339,7 @@ class Planner {
       if (op == "Conv" || op == "Gemm" || op == "MatMul") return true;
       // look through nodes that only move or select values
       if (op == "MaxPool" || op == "Flatten" || op == "Reshape" || op == "Identity" || op == "Relu" || op == "Pad" || op == "Resize" ||
-          op == "Concat")
+          op == "Concat" || op == "Transpose")
         if (!nodes_[c.first].outputs.empty() && feeds_contraction(nodes_[c.first].outputs[0])) return true;
     }
     return false;
@@ -364,6 +364,20 @@ class Planner {
   void plan_slice(const NodeDef& n);
   void plan_gather(const NodeDef& n);
   void plan_transpose(const NodeDef& n);
+  void emit_transpose(const NodeDef& n, int xi, const std::vector<int64_t>& perm, int yi);
+  // A head split Transpose(Reshape(x2d [B*S, H*D] -> [B,S,H,D])) whose only reader is a MatMul is not run when
+  // planned: the tensor-core product reads the heads straight out of x2d through strided tensor maps.
+  struct LazyHeads {
+    int src_vi, root_vi;
+    int64_t B, S, H, D;
+    int kind;  // 0: [B,H,S,D] (perm 0,2,1,3), 1: [B,H,D,S] (perm 0,2,3,1)
+    int node;
+    std::vector<int64_t> perm;
+    bool materialised;
+  };
+  std::map<int, LazyHeads> lazy_heads_;
+  void materialise_heads(int yi);
+  bool try_plan_attention_product(const NodeDef& n, int ai, int bi);
   void plan_softmax(const NodeDef& n);
   bool try_plan_scaled_masked_softmax(const NodeDef& n);
   void plan_layer_norm(const NodeDef& n);
@@ -1466,6 +1480,9 @@ void Planner::plan_matmul_family(const NodeDef& n, int ni) {
     // activation x activation product: float MatMul only
     if (op != "MatMul") OXB_DECLINE("%s '%s': the B operand is not an initializer", op.c_str(), n.name.c_str());
     int bi = value_of(in_name(n, 1));
+    if (try_plan_attention_product(n, ai, bi)) return;
+    materialise_heads(ai);
+    materialise_heads(bi);
     const Value bv = V(bi);
     if (av.dt != DT::F32 || bv.dt != DT::F32) OXB_DECLINE("MatMul '%s': operands are not float tensors", n.name.c_str());
     if (av.shape.size() < 2 || bv.shape.size() < 2) OXB_DECLINE("MatMul '%s': 1-D operands with a non-constant B", n.name.c_str());
@@ -1719,6 +1736,7 @@ void Planner::plan_matmul_family(const NodeDef& n, int ni) {
             out_name = nodes_[gelu_i].outputs[0];
           }
           c.out_vi = add_value(out_name, os, DT::F32, Layout::PLAIN);
+          c.epi.round_tf32 = feeds_contraction(out_name) ? 1 : 0;
           emit_contraction(n, c);
           return;
         }
@@ -2233,10 +2251,31 @@ void Planner::plan_transpose(const NodeDef& n) {
   }
   if (rank == 4 && V(xi).layout == Layout::NHWC && !order_free(V(xi))) xi = ensure_layout(n, xi, Layout::PLAIN);
   const Value xv = V(xi);
-  std::vector<int64_t> xs(rank, 1), os(rank);
-  for (int d = rank - 2; d >= 0; --d) xs[d] = xs[d + 1] * xv.shape[d + 1];
+  std::vector<int64_t> os(rank);
   for (int d = 0; d < rank; ++d) os[d] = xv.shape[perm[d]];
   int yi = add_value(n.outputs[0], os, xv.dt, Layout::PLAIN);
+  // head split in front of an attention product: defer (see LazyHeads)
+  if (rank == 4 && xv.dt == DT::F32 && !C.cfg().keep_intermediates && C.cfg().kernel_path == 0 && k::umma_available() && !graph_outputs_.count(n.outputs[0])) {
+    const bool p0 = perm == std::vector<int64_t>{0, 2, 1, 3}, p1 = perm == std::vector<int64_t>{0, 2, 3, 1};
+    int root = xi;
+    while (V(root).alias_of >= 0) root = V(root).alias_of;
+    auto it = consumers_.find(n.outputs[0]);
+    const bool to_matmul = it != consumers_.end() && it->second.size() == 1 && nodes_[it->second[0].first].op == "MatMul";
+    const int64_t B = xv.shape[0], Sq = xv.shape[1], H = xv.shape[2], D = xv.shape[3];
+    if ((p0 || p1) && to_matmul && root != xi && V(root).shape == std::vector<int64_t>{B * Sq, H * D} && V(root).host == nullptr && Sq % 128 == 0 && D % 8 == 0) {
+      lazy_heads_[yi] = LazyHeads{xi, root, B, Sq, H, D, p0 ? 0 : 1, cur_node_, perm, false};
+      return;
+    }
+  }
+  emit_transpose(n, xi, perm, yi);
+}
+
+void Planner::emit_transpose(const NodeDef& n, int xi, const std::vector<int64_t>& perm, int yi) {
+  const Value xv = V(xi);
+  const int rank = (int)xv.shape.size();
+  std::vector<int64_t> xs(rank, 1);
+  for (int d = rank - 2; d >= 0; --d) xs[d] = xs[d + 1] * xv.shape[d + 1];
+  const std::vector<int64_t> os = V(yi).shape;
   Dims4 yd{1, 1, 1, 1}, st4{0, 0, 0, 0};
   int64_t* yf[4] = {&yd.N, &yd.C, &yd.H, &yd.W};
   int64_t* sf[4] = {&st4.N, &st4.C, &st4.H, &st4.W};
@@ -2251,6 +2290,105 @@ void Planner::plan_transpose(const NodeDef& n) {
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };
+}
+
+void Planner::materialise_heads(int yi) {
+  auto it = lazy_heads_.find(yi);
+  if (it == lazy_heads_.end() || it->second.materialised) return;
+  it->second.materialised = true;
+  emit_transpose(nodes_[it->second.node], it->second.src_vi, it->second.perm, yi);
+}
+
+// The two products of an attention layer on the tensor cores (TF32), batched over (batch, head):
+//   scores[b,h] = Q[b,h] (S x D) . K[b,h]^T         Q and K read as column windows of their [B*S, H*D] matrices
+//   ctx[b,h]    = probs[b,h] (S x S) . V[b,h] (S x D)  V transposed once to [B,H,D,S]; the context is written
+//                                                      straight into [B*S, H*D] when a head merge follows
+bool Planner::try_plan_attention_product(const NodeDef& n, int ai, int bi) {
+  auto la = lazy_heads_.find(ai), lb = lazy_heads_.find(bi);
+  const bool a_lazy = la != lazy_heads_.end() && !la->second.materialised, b_lazy = lb != lazy_heads_.end() && !lb->second.materialised;
+  if (!b_lazy) return false;
+  const LazyHeads hb = lb->second;
+  const int64_t B = hb.B, Sq = hb.S, H = hb.H, D = hb.D;
+  if (B * H * Sq > 0x7fffffffLL || H * D > 0x7fffffffLL) return false;
+  k::BatchedGemm g;
+  g.outer = (int)B, g.inner = (int)H;
+  std::vector<int> reads;
+  int out_vi = -1;
+  std::string label;
+  if (a_lazy && la->second.kind == 0 && hb.kind == 1 && la->second.B == B && la->second.S == Sq && la->second.H == H && la->second.D == D) {
+    // scores
+    g.M = (int)Sq, g.N = (int)Sq, g.K = (int)D;
+    g.a_rows = B * Sq, g.a_cols = H * D, g.a_rb = (int)Sq, g.a_rh = 0, g.a_ch = (int)D;
+    g.b_rows = B * Sq, g.b_cols = H * D, g.b_rb = (int)Sq, g.b_rh = 0, g.b_ch = (int)D;
+    g.o_rows = B * H * Sq, g.o_cols = Sq, g.o_rb = (int)(H * Sq), g.o_rh = (int)Sq, g.o_ch = 0;
+    out_vi = add_value(n.outputs[0], {B, H, Sq, Sq}, DT::F32, Layout::PLAIN);
+    g.round_tf32 = feeds_contraction(n.outputs[0]) ? 1 : 0;
+    reads = {la->second.root_vi, hb.root_vi};
+    label = "scores";
+  } else if (!a_lazy && hb.kind == 0 && V(ai).dt == DT::F32 && V(ai).shape == std::vector<int64_t>{B, H, Sq, Sq} && V(ai).layout == Layout::PLAIN &&
+             V(ai).host == nullptr) {
+    // context: V^T per head first
+    const int vt = add_value(V(hb.src_vi).name + "@heads_t", {B, H, D, Sq}, DT::F32, Layout::PLAIN);
+    emit_transpose(nodes_[hb.node], hb.src_vi, {0, 2, 3, 1}, vt);
+    g.M = (int)Sq, g.N = (int)D, g.K = (int)Sq;
+    g.a_rows = B * H * Sq, g.a_cols = Sq, g.a_rb = (int)(H * Sq), g.a_rh = (int)Sq, g.a_ch = 0;
+    g.b_rows = B * H * D, g.b_cols = Sq, g.b_rb = (int)(H * D), g.b_rh = (int)D, g.b_ch = 0;
+    // a head merge Transpose(0,2,1,3) -> Reshape([B*S, H*D]) behind the product is absorbed into the store
+    std::string out_name = n.outputs[0];
+    std::vector<int64_t> oshape = {B, H, Sq, D};
+    g.o_rows = B * H * Sq, g.o_cols = D, g.o_rb = (int)(H * Sq), g.o_rh = (int)Sq, g.o_ch = 0;
+    auto only_user = [&](const std::string& name, const char* opn) -> int {
+      if (graph_outputs_.count(name)) return -1;
+      auto it = consumers_.find(name);
+      if (it == consumers_.end() || it->second.size() != 1) return -1;
+      const int ni2 = it->second[0].first;
+      return (!skipped_[ni2] && nodes_[ni2].op == opn && it->second[0].second == 0) ? ni2 : -1;
+    };
+    const int t_i = only_user(out_name, "Transpose");
+    if (t_i >= 0 && nodes_[t_i].attrs.int_list("perm") == std::vector<int64_t>{0, 2, 1, 3}) {
+      const int r_i = only_user(nodes_[t_i].outputs[0], "Reshape");
+      const HostTensor* sh = r_i >= 0 ? const_in(nodes_[r_i], 1) : nullptr;
+      if (sh && sh->data.size() == 2 && (int64_t)sh->data[0] == B * Sq && (int64_t)sh->data[1] == H * D) {
+        skipped_[t_i] = skipped_[r_i] = 1;
+        out_name = nodes_[r_i].outputs[0];
+        oshape = {B * Sq, H * D};
+        g.o_rows = B * Sq, g.o_cols = H * D, g.o_rb = (int)Sq, g.o_rh = 0, g.o_ch = (int)D;
+      }
+    }
+    out_vi = add_value(out_name, oshape, DT::F32, Layout::PLAIN);
+    g.round_tf32 = feeds_contraction(out_name) ? 1 : 0;
+    reads = {ai, vt};
+    lb->second.materialised = true;  // consumed through its transposed copy
+    label = "context";
+  } else {
+    return false;
+  }
+  if (label == "scores") la->second.materialised = lb->second.materialised = true;
+  g.zero_bias = upload_vec(std::vector<float>(align_up((size_t)g.N, 256), 0.f));
+  Step& st = add_step(n, "umma", 0, reads, {out_vi});
+  st.work = 2.0 * (double)B * H * g.M * g.N * g.K;
+  st.work_is_bytes = false;
+  const int step_index = (int)S.steps_.size() - 1;
+  const int ra = reads[0], rb = reads[1];
+  st.finalize = [this, step_index, g, ra, rb, out_vi, n]() mutable {
+    k::BatchedGemm gg = g;
+    gg.a = V(ra).ptr;
+    gg.b = V(rb).ptr;
+    gg.out = V(out_vi).ptr;
+    std::string why2;
+    k::UmmaPlan* plan = k::umma_plan_create_batched(gg, &why2);
+    if (!plan) OXB_FAIL("MatMul '%s': batched tensor-core plan rejected: %s", n.name.c_str(), why2.c_str());
+    S.umma_plans_.push_back(plan);
+    Step& me = S.steps_[step_index];
+    me.kernel = k::umma_plan_desc(plan);
+    int* err = S.err_flag_;
+    me.launch = [this, plan, err](cudaStream_t s) {
+      k::umma_launch(plan, err, s);
+      C.counters.umma_launches++;
+      C.counters.kernel_launches++;
+    };
+  };
+  return true;
 }
 
 // Softmax over the last axis (nn/normalization.rs softmax_into); other axes are declined.
@@ -2296,10 +2434,11 @@ bool Planner::try_plan_scaled_masked_softmax(const NodeDef& n) {
   const int mi = mit->second;
   const int64_t len = xs[3], rows = V(xi0).numel() / len, rows_per_mask = xs[1] * xs[2];
   int yi = add_value(nodes_[sm_i].outputs[0], xs, DT::F32, Layout::PLAIN);
+  const int rt = feeds_contraction(nodes_[sm_i].outputs[0]) ? 1 : 0;
   Step& st = add_step(nodes_[sm_i], "softmax_rows+scale+mask", 2, {xi0, mi}, {yi});
   st.work = 2.0 * (double)V(xi0).bytes;
-  st.launch = [this, xi0, mi, yi, rows, len, dscale, rows_per_mask](cudaStream_t s) {
-    k::softmax_rows((const float*)V(xi0).ptr, (float*)V(yi).ptr, rows, len, dscale, (const float*)V(mi).ptr, rows_per_mask, s);
+  st.launch = [this, xi0, mi, yi, rows, len, dscale, rows_per_mask, rt](cudaStream_t s) {
+    k::softmax_rows((const float*)V(xi0).ptr, (float*)V(yi).ptr, rows, len, dscale, (const float*)V(mi).ptr, rows_per_mask, rt, s);
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };
@@ -2318,10 +2457,11 @@ void Planner::plan_softmax(const NodeDef& n) {
   const Value xv = V(xi);
   const int64_t len = xv.shape[rank - 1], rows = len ? xv.numel() / len : 0;
   int yi = add_value(n.outputs[0], xv.shape, DT::F32, Layout::PLAIN);
+  const int rt = feeds_contraction(n.outputs[0]) ? 1 : 0;
   Step& st = add_step(n, "softmax_rows", 2, {xi}, {yi});
   st.work = 2.0 * (double)xv.bytes;
-  st.launch = [this, xi, yi, rows, len](cudaStream_t s) {
-    k::softmax_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, nullptr, nullptr, 1, s);
+  st.launch = [this, xi, yi, rows, len, rt](cudaStream_t s) {
+    k::softmax_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, nullptr, nullptr, 1, rt, s);
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };

