@@ -4,10 +4,11 @@
 
 A step is one pass of the hot path over one batch of seeded synthetic input.  The default
 workload is ResNet-50 v1.5, f32 graph, batch 32 (TF32 tensor-core contractions); `c5` is the
-QLinearConv INT8 ResNet-50 at batch 128 per GPU, `c1` the INT8 MLP, `c3` the InSwapper-shaped f32
+QLinearConv INT8 ResNet-50 at a global batch of 1024 split over the GPUs of the run, `c1` the INT8 MLP, `c3` the InSwapper-shaped f32
 generator at batch 16, `c4` the BERT-base-shaped dynamic-INT8 encoder at 64 x 128 tokens (tokens/s).  With N > 1 (launched by
 torchrun, one rank per GPU) every rank holds a full weight replica and runs its own batch:
-the path shards along the batch only, there is no data-path collective, and the scaling is weak.
+the path shards along the batch only, there is no data-path collective; the scaling is weak (per-GPU
+batch fixed) except for `c5`, whose global batch is fixed (strong).
 
 One JSON line is printed by rank 0:
   value      images/s (rows/s for c1) with inputs resident in HBM, device time from CUDA events on
@@ -19,7 +20,7 @@ One JSON line is printed by rank 0:
   cpu_baseline  the CPU oracle (a port of the reference's CPU operators) timed on this host's
              cores on a bounded sample of the same workload
   int8       (default workload, one GPU) the INT8 half of the headline metric measured in the same run:
-             the QLinearConv ResNet-50 at batch 128, images/s and the contraction kernel's TOP/s
+             the QLinearConv ResNet-50 at batch 1024, images/s and the contraction kernel's TOP/s
              against twice the measured bf16 rate
 
 `--impl reference` times that CPU port alone on all host threads (the reference itself is a Rust
@@ -43,7 +44,8 @@ import numpy as np  # noqa: E402
 
 WORKLOADS = {
     "c2": dict(name="resnet50_v1.5_f32_b32", metric="images_per_s", unit="images/s", dtype="tf32", batch=32),
-    "c5": dict(name="resnet50_qlinearconv_int8_b128_per_gpu", metric="images_per_s", unit="images/s", dtype="i8", batch=128),
+    # global batch 1024 split over the GPUs of the run (BASELINE.json configs[4]): 1024 / N images per GPU
+    "c5": dict(name="resnet50_qlinearconv_int8_b1024_global", metric="images_per_s", unit="images/s", dtype="i8", batch=1024, global_batch=True),
     "c1": dict(name="int8_mlp_64x1024-4096-4096-1024", metric="rows_per_s", unit="rows/s", dtype="i8", batch=64),
     "c3": dict(name="inswapper128_shaped_f32_b16", metric="images_per_s", unit="images/s", dtype="tf32", batch=16),
     "c4": dict(name="bert_base_dynamic_int8_b64_s128", metric="tokens_per_s", unit="tokens/s", dtype="i8", batch=64, per_item=128),
@@ -61,8 +63,8 @@ def measured_peaks():
 
 # DRAM bytes (read + written) per launch of the tensor-core kernel, averaged over the launches of one
 # step: dram__bytes_read.sum + dram__bytes_write.sum from the ncu launch lists summarised under profiles/
-# (launch_list_resnet50_f32_b32.md, launch_list_resnet50_int8_b128.md).  None: not captured.
-NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.41e6, "c5": 28.32e6, "c1": None, "c3": None, "c4": None}
+# (launch_list_resnet50_f32_b32.md, launch_list_resnet50_int8_b1024.md).  None: not captured.
+NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.33e6, "c5": 351.58e6, "c1": None, "c3": None, "c4": None}
 
 
 def build_workload(key, batch):
@@ -152,7 +154,8 @@ def cpu_baseline(key, graph_builder_batch, sample, threads):
 
 def int8_companion(args, local_rank, flush_l2, peaks):
     """The INT8 half of the headline metric, measured in the same run: the QLinearConv ResNet-50 at batch
-    128, inputs resident, L2 flushed between steps; images/s and the contraction kernel's TOP/s."""
+    1024 (the configuration's global batch on one GPU), inputs resident, L2 flushed between steps; images/s
+    and the contraction kernel's TOP/s."""
     from oxionnx_b200.session import Session
     key = "c5"
     w = WORKLOADS[key]
@@ -216,7 +219,7 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -246,7 +249,7 @@ def main():
     from oxionnx_b200.session import Session
     lib = _ffi.lib()
     w = WORKLOADS[args.workload]
-    batch = args.batch or w["batch"]
+    batch = args.batch or (max(w["batch"] // world, 1) if w.get("global_batch") else w["batch"])
     graph, weights, feeds, info = build_workload(args.workload, batch)
     f = feeds(batch, f"{args.workload}_in_rank{rank}") if args.workload != "c1" else feeds()
     sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).build_from_graph(graph, weights)
@@ -290,6 +293,7 @@ def main():
     for _ in range(args.steps):
         flush_l2()
         step_ms.append(sess.run_resident(1))
+    c1 = sess.cuda_cache_counters()
     # ... and the same K steps again with a CUDA-event pair around every kernel, for the roofline figures
     sess.ctx.set_profiling(True)
     prof_ms = 0.0
@@ -311,7 +315,7 @@ def main():
     barrier()
     t_end = time.time()
     clocks = sampler.stop(t_begin, t_end)
-    c1 = sess.cuda_cache_counters()
+    sess.ctx.set_profiling(False)
     total_ms = sum(step_ms)
     if dist is not None:
         t = torch.tensor([total_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
@@ -360,11 +364,11 @@ def main():
         }
         line = {
             "metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong" if (w.get("global_batch") and not args.batch) else "weak", "vs_baseline": None, "dtype": kind,
             "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu_batch": batch, "global_batch": batch * world, "parallelism": f"batch-sharded replicas x{world}, no collective",
                        "l2": "flushed between timed steps (256 MiB memset)", "algorithmic_ops_per_step": info["ops"], "kernel_path": args.kernel_path},
-            "clocks": clocks,
+            "clocks": dict(clocks, window="the timed K steps and the profiled K steps that follow them"),
             "e2e": {"value": e2e_value, "unit": w["unit"], "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_total / args.steps},
             "gpu_launches": int(c1["kernel_launches"] - c0["kernel_launches"]),
             "launch_mix": {"umma": int(c1["umma_launches"] - c0["umma_launches"]), "direct": int(c1["simt_launches"] - c0["simt_launches"]),

@@ -45,6 +45,8 @@ void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scal
 // DynamicQuantizeLinear: params[0] = y_scale, params[1] = y_zero_point (f32 lanes on the
 // device); `scratch` is 2 floats used for the min/max reduction.
 void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s);
+// Puts a freshly allocated scratch block (at least 12 bytes) into the state dynamic_quantize_linear expects.
+void dynamic_quantize_scratch_init(float* scratch);
 
 // The residual join of a quantised network in one pass:
 //   y = Q( relu?( DQ(a) + DQ(b) ) )  with per-tensor parameters,

@@ -262,6 +262,50 @@ __global__ void dynq_apply_kernel(const float* __restrict__ x, uint8_t* __restri
   }
 }
 
+// The apply pass of the session path: every block derives scale and zero point from the min/max keys (the same
+// operations as dynq_params_kernel, so every block gets the same two values), block 0 publishes them for the
+// consumers, and the last block to finish puts the keys back to their identity values for the next call: two
+// launches per DynamicQuantizeLinear instead of four.  keys[2] is the arrival counter.
+__global__ void dynq_apply_fused_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, uint32_t* keys, float* params, int64_t n) {
+  const float max_x = fmaxf(key_float(keys[1]), 0.f);
+  const float min_x = fminf(key_float(keys[0]), 0.f);
+  const float span = (max_x == min_x) ? 1.0f : __fsub_rn(max_x, min_x);
+  const float s = __fdiv_rn(span, 255.0f);
+  const float z = rintf(fminf(fmaxf(__fsub_rn(0.0f, __fdiv_rn(min_x, s)), 0.f), 255.f));
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    params[0] = s;
+    params[1] = z;
+  }
+  const int64_t n4 = n / 4;
+  const float4* x4 = (const float4*)x;
+  uint32_t* y4 = (uint32_t*)y;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 v = x4[i];
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    uint32_t w = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float r = __fadd_rn(rintf(__fdiv_rn(f[e], s)), z);
+      r = fminf(fmaxf(r, 0.f), 255.f);
+      w |= ((uint32_t)__float2int_rn(r) & 0xffu) << (8 * e);
+    }
+    y4[i] = w;
+  }
+  for (int64_t i = n4 * 4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float r = __fadd_rn(rintf(__fdiv_rn(x[i], s)), z);
+    y[i] = (uint8_t)__float2int_rn(fminf(fmaxf(r, 0.f), 255.f));
+  }
+  __syncthreads();  // every thread of this block has read the keys
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&keys[2], 1u) == gridDim.x - 1) {
+      keys[0] = 0xffffffffu;
+      keys[1] = 0u;
+      keys[2] = 0u;
+    }
+  }
+}
+
 // ---- element-wise ---------------------------------------------------------------------
 __device__ __forceinline__ float apply_bin(int op, float a, float b) {
   switch (op) {
@@ -1057,12 +1101,17 @@ void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scal
 }
 
 void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s) {
+  // `scratch` holds {min key, max key, arrival counter}, set to {0xffffffff, 0, 0} when it was allocated
+  // (dynamic_quantize_scratch_init) and put back to that by the last block of every apply pass
   int64_t n = x.d.numel();
   uint32_t* keys = (uint32_t*)scratch;
-  minmax_init_kernel<<<1, 1, 0, s>>>(keys);
   minmax_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, n, keys);
-  dynq_params_kernel<<<1, 1, 0, s>>>(keys, params);
-  dynq_apply_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, params, n);
+  dynq_apply_fused_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n);
+}
+
+void dynamic_quantize_scratch_init(float* scratch) {
+  const uint32_t init[3] = {0xffffffffu, 0u, 0u};
+  OXB_CUDA(cudaMemcpy(scratch, init, sizeof init, cudaMemcpyHostToDevice));
 }
 
 void binary(const TensorRef& a, const TensorRef& b, const TensorRef& out, int op, int relu_after, int round_tf32_flag, cudaStream_t s) {

@@ -746,6 +746,7 @@ void Planner::plan_dynamic_quantize(const NodeDef& n) {
     V(zi).alias_of = pi;
   }
   float* scratch = (float*)owned_buffer(256);
+  k::dynamic_quantize_scratch_init(scratch);
   Dims4 d{V(xi).numel(), 1, 1, 1};
   TensorRef xr{nullptr, DT::F32, Layout::PLAIN, d}, yr{nullptr, DT::U8, Layout::PLAIN, d};
   std::vector<int> writes = {yi, pi};
