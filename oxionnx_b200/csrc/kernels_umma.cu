@@ -14,11 +14,21 @@
 //  * B tiles (BN output channels x the same K slice) are 2-D tiled TMA loads.
 //  * No load uses cluster multicast: every CTA fetches its own tiles.
 //  * One elected thread issues tcgen05.mma (kind::i8 with s32 accumulation, or kind::tf32 with
-//    f32 accumulation) from shared-memory descriptors into a TMEM accumulator of BN columns.
-//  * Four epilogue warps read the accumulator with tcgen05.ld (one output pixel per thread,
-//    32 channels per load), apply the fused epilogue in registers (bias; ONNX requantisation
-//    in f64 with round-half-even and saturation; ReLU/clip; int32 saturation) and write each
-//    pixel's channel run with 16-byte stores.
+//    f32 accumulation) from shared-memory descriptors into one of two TMEM accumulators of BN
+//    columns; a ring stage carries up to four K blocks when they are small, so that the
+//    barrier round trip and the fixed cost of each asynchronous instruction are paid per stage.
+//  * Eight epilogue warps (two per scheduler; the two of a TMEM lane quarter split the channel
+//    runs) read the accumulator with tcgen05.ld (one output pixel per thread, 32 channels per
+//    load), apply the fused epilogue in registers and hand the tile to TMA stores through
+//    swizzled staging rows.  Epilogue variants, one tile loop instantiated per variant: float
+//    bias / ReLU / clip / TF32 rounding, optionally with a fused residual; exact ONNX
+//    requantisation in one fused multiply-add per output (and an f64 two-pass form for scales
+//    outside its proven range); int32 saturation; the dequantising chain of a dynamically
+//    quantised linear (scale, bias, Gelu).
+//  * Batched products (attention) address each item's operands and output as windows of larger
+//    row-major matrices, so heads are read and written in place.
+//  * The grid is launched with programmatic stream serialization and waits for its predecessor
+//    (griddepcontrol.wait) only after its own prologue.
 //  * Every mbarrier wait is bounded; on a timeout the kernel records an error code, lets its
 //    copies land, frees its TMEM and returns, so the context stays usable.
 #include <cuda.h>
