@@ -213,6 +213,13 @@ int oxb200_session_plan(oxb200_ctx* ctx, const oxb200_node* nodes, uint32_t n_no
 int oxb200_run(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds, oxb200_result* fetches, uint32_t n_fetches);
 /* Device time of the last oxb200_run in milliseconds, taken with CUDA events on the context's
  * stream from before the first host-to-device copy to after the last device-to-host copy. */
+/* Pipelined form of oxb200_run for throughput: submit enqueues the upload of one set of feeds (host lanes,
+ * ideally page-locked) on a copy stream, the run, and the download of the outputs, and returns at once; collect
+ * waits for the oldest submission and writes its outputs.  Up to two submissions may be in flight, so the copy
+ * of the next batch overlaps the run of the current one.  The reference has no counterpart (its run is
+ * synchronous, src/session/run/sequential.rs:468). */
+int oxb200_run_submit(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds);
+int oxb200_run_collect(oxb200_ctx* ctx, oxb200_result* fetches, uint32_t n_fetches);
 float oxb200_last_run_ms(const oxb200_ctx* ctx);
 /* The same run split for measurement: stage feeds, run the planned launches `iters`
  * times with everything resident (no host traffic), read fetches. */

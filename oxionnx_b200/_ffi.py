@@ -90,6 +90,8 @@ SYMBOLS = {
     "oxb200_session_plan": (ctypes.c_int, [ctypes.c_void_p, _P(CNode), ctypes.c_uint32, _P(ValueInfo), ctypes.c_uint32, _P(ctypes.c_char_p),
                                            ctypes.c_uint32]),
     "oxb200_run": (ctypes.c_int, [ctypes.c_void_p, _P(Operand), ctypes.c_uint32, _P(Result), ctypes.c_uint32]),
+    "oxb200_run_submit": (ctypes.c_int, [ctypes.c_void_p, _P(Operand), ctypes.c_uint32]),
+    "oxb200_run_collect": (ctypes.c_int, [ctypes.c_void_p, _P(Result), ctypes.c_uint32]),
     "oxb200_last_run_ms": (ctypes.c_float, [ctypes.c_void_p]),
     "oxb200_upload_feeds": (ctypes.c_int, [ctypes.c_void_p, _P(Operand), ctypes.c_uint32]),
     "oxb200_run_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32, _P(ctypes.c_float)]),

@@ -395,6 +395,28 @@ int oxb200_run(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds, o
   });
 }
 
+int oxb200_run_submit(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds) {
+  if (!ctx) return fail_with(ctx, OXB200_FAILED, "run_submit: ctx is NULL");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    ctx->impl.make_current();
+    Session& s = planned(ctx);
+    s.submit(feeds, n_feeds, ctx->impl.cfg().profile != 0);
+    return (int)OXB200_OK_HOST;
+  });
+}
+
+int oxb200_run_collect(oxb200_ctx* ctx, oxb200_result* fetches, uint32_t n_fetches) {
+  if (!ctx) return fail_with(ctx, OXB200_FAILED, "run_collect: ctx is NULL");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    ctx->impl.make_current();
+    Session& s = planned(ctx);
+    s.collect(fetches, n_fetches);
+    return (int)OXB200_OK_HOST;
+  });
+}
+
 float oxb200_last_run_ms(const oxb200_ctx* ctx) { return ctx ? ctx->impl.last_run_ms : -1.f; }
 
 int oxb200_upload_feeds(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds) {

@@ -138,6 +138,17 @@ Session::~Session() {
   if (arena_.ptr) cudaFree(arena_.ptr);
   for (auto& b : owned_) cudaFree(b.ptr);
   if (err_flag_) cudaFree(err_flag_);
+  for (int f = 0; f < 2; ++f) {
+    Flight& fl = flight_[f];
+    if (fl.up) cudaEventDestroy(fl.up);
+    if (fl.done) cudaEventDestroy(fl.done);
+    if (fl.down) cudaEventDestroy(fl.down);
+    if (f == 1 && pipe_double_)
+      for (void* p : fl.in_dev) cudaFree(p);
+    for (float* p : fl.out_host) cudaFreeHost(p);
+    if (fl.err_host) cudaFreeHost(fl.err_host);
+  }
+  if (copy_stream_) cudaStreamDestroy(copy_stream_);
 }
 
 Value* Session::find_value(const std::string& name) {
@@ -255,6 +266,116 @@ void Session::fetch_value(const std::string& name, oxb200_result* out) {
   ctx_->free_device(tmp);
   ctx_->counters.downloads += 1;
   ctx_->counters.download_bytes += (uint64_t)n * 4;
+}
+
+// ---- pipelined runs ---------------------------------------------------------------------------
+void Session::rebind_input(int value_index, void* ptr) {
+  values_[value_index].ptr = ptr;
+  for (Value& v : values_) {  // values that share the input's storage (Reshape, Flatten, Identity)
+    int root = v.alias_of;
+    while (root >= 0 && values_[root].alias_of >= 0) root = values_[root].alias_of;
+    if (root == value_index) v.ptr = ptr;
+  }
+}
+
+void Session::prepare_pipeline() {
+  if (pipe_ready_) return;
+  OXB_CUDA(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+  // A second input buffer is only safe when no step has the input's address built into a tensor map:
+  // the tensor-core steps are the ones that do, so none of them may read an input (or an alias of one).
+  pipe_double_ = external_bind_.empty();
+  for (const Step& st : steps_) {
+    if (st.family != 0) continue;
+    for (int r : st.reads) {
+      int root = r;
+      while (values_[root].alias_of >= 0) root = values_[root].alias_of;
+      for (auto& in : input_staging_)
+        if (in.second == root) pipe_double_ = false;
+    }
+  }
+  for (int f = 0; f < 2; ++f) {
+    Flight& fl = flight_[f];
+    OXB_CUDA(cudaEventCreateWithFlags(&fl.up, cudaEventDisableTiming));
+    OXB_CUDA(cudaEventCreateWithFlags(&fl.done, cudaEventDisableTiming));
+    OXB_CUDA(cudaEventCreateWithFlags(&fl.down, cudaEventDisableTiming));
+    for (auto& in : input_staging_) {
+      void* p = values_[in.second].ptr;
+      if (f == 1 && pipe_double_) OXB_CUDA(cudaMalloc(&p, std::max<size_t>((size_t)values_[in.second].numel() * 4, 256)));
+      fl.in_dev.push_back(p);
+    }
+    for (auto& out : output_staging_) {
+      float* p = nullptr;
+      OXB_CUDA(cudaMallocHost(&p, std::max<size_t>((size_t)values_[out.second].numel() * 4, 4)));
+      fl.out_host.push_back(p);
+    }
+    OXB_CUDA(cudaMallocHost(&fl.err_host, sizeof(int)));
+  }
+  pipe_ready_ = true;
+}
+
+void Session::submit(const oxb200_operand* feeds, uint32_t n, bool profile) {
+  prepare_pipeline();
+  Flight& fl = flight_[submit_idx_];
+  Flight& prev = flight_[submit_idx_ ^ 1];
+  if (fl.busy) raise(OXB200_FAILED, "submit: two runs are already in flight; collect one first");
+  cudaStream_t main = ctx_->stream();
+  // without a second input buffer the upload must wait until the previous run has read the inputs
+  if (!pipe_double_ && prev.busy) OXB_CUDA(cudaStreamWaitEvent(copy_stream_, prev.done, 0));
+  for (size_t i = 0; i < input_staging_.size(); ++i) {
+    const auto& in = input_staging_[i];
+    const oxb200_operand* f = nullptr;
+    for (uint32_t k2 = 0; k2 < n; ++k2)
+      if (feeds[k2].name && in.first == feeds[k2].name) f = &feeds[k2];
+    Value& v = values_[in.second];
+    if (!f || !f->lanes) raise(OXB200_FAILED, "submit: no host lanes for graph input '%s'", in.first.c_str());
+    if ((int64_t)f->len != v.numel()) raise(OXB200_FAILED, "submit: feed '%s' has %llu lanes, the plan expects %lld", in.first.c_str(), (unsigned long long)f->len, (long long)v.numel());
+    OXB_CUDA(cudaMemcpyAsync(fl.in_dev[i], f->lanes, (size_t)v.numel() * 4, cudaMemcpyHostToDevice, copy_stream_));
+    ctx_->counters.uploads += 1;
+    ctx_->counters.upload_bytes += (uint64_t)v.numel() * 4;
+    rebind_input(in.second, fl.in_dev[i]);
+  }
+  OXB_CUDA(cudaEventRecord(fl.up, copy_stream_));
+  OXB_CUDA(cudaStreamWaitEvent(main, fl.up, 0));
+  // the previous run's outputs must have left their device buffers before this run overwrites them
+  if (prev.busy) OXB_CUDA(cudaStreamWaitEvent(main, prev.down, 0));
+  run_steps(profile);
+  OXB_CUDA(cudaEventRecord(fl.done, main));
+  OXB_CUDA(cudaStreamWaitEvent(copy_stream_, fl.done, 0));
+  for (size_t i = 0; i < output_staging_.size(); ++i) {
+    const Value& v = values_[output_staging_[i].second];
+    if (v.numel() > 0) OXB_CUDA(cudaMemcpyAsync(fl.out_host[i], v.ptr, (size_t)v.numel() * 4, cudaMemcpyDeviceToHost, copy_stream_));
+    ctx_->counters.downloads += 1;
+    ctx_->counters.download_bytes += (uint64_t)v.numel() * 4;
+  }
+  OXB_CUDA(cudaMemcpyAsync(fl.err_host, err_flag_, sizeof(int), cudaMemcpyDeviceToHost, copy_stream_));
+  OXB_CUDA(cudaEventRecord(fl.down, copy_stream_));
+  fl.busy = true;
+  submit_idx_ ^= 1;
+}
+
+void Session::collect(oxb200_result* fetches, uint32_t n) {
+  Flight& fl = flight_[collect_idx_];
+  if (!fl.busy) raise(OXB200_FAILED, "collect: no run is in flight");
+  if (n != outputs_.size()) raise(OXB200_FAILED, "collect: %u fetch slots for %zu graph outputs", n, outputs_.size());
+  for (uint32_t i = 0; i < n; ++i) {
+    const Value& v = values_[output_staging_[i].second];
+    if (fetches[i].lanes && fetches[i].cap < (uint64_t)v.numel())
+      raise(OXB200_FAILED, "collect: fetch buffer for '%s' holds %llu lanes, %lld needed", outputs_[i].c_str(), (unsigned long long)fetches[i].cap, (long long)v.numel());
+  }
+  OXB_CUDA(cudaEventSynchronize(fl.down));
+  ctx_->counters.fences += 1;
+  fl.busy = false;
+  collect_idx_ ^= 1;
+  if (*fl.err_host != 0) {
+    const int flag = *fl.err_host, zero = 0;
+    OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    raise(OXB200_FAILED, "a kernel reported code %d during a pipelined run; results are not valid", flag);
+  }
+  for (uint32_t i = 0; i < n; ++i) {
+    const Value& v = values_[output_staging_[i].second];
+    write_result_shape(v, &fetches[i]);
+    if (fetches[i].lanes && v.numel() > 0) std::memcpy(fetches[i].lanes, fl.out_host[i], (size_t)v.numel() * 4);
+  }
 }
 
 void Session::bind_external(const std::string& name, void* ptr, DT dt, Layout layout) { external_bind_[name] = {ptr, {dt, layout}}; }

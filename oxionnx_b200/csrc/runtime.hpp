@@ -123,6 +123,12 @@ class Session {
   // After a run, detach the storage of an output so it can outlive the session.
   Value* find_value(const std::string& name);
   int check_error_flag();
+  // Pipelined runs: submit() enqueues the upload of one set of feeds (on a copy stream, into the input buffer
+  // that is not being read), the steps, and the download of the outputs into pinned staging; collect() waits
+  // for the oldest submission and hands its outputs over.  At most two submissions are in flight.
+  void submit(const oxb200_operand* feeds, uint32_t n, bool profile);
+  void collect(oxb200_result* fetches, uint32_t n);
+  int in_flight() const { return (flight_[0].busy ? 1 : 0) + (flight_[1].busy ? 1 : 0); }
 
  private:
   friend class Planner;
@@ -140,6 +146,19 @@ class Session {
   int* err_flag_ = nullptr;
   std::map<std::string, std::pair<void*, std::pair<DT, Layout>>> external_bind_;
   std::shared_ptr<void> planner_;  // keeps the objects the step closures refer to alive
+  struct Flight {
+    bool busy = false;
+    cudaEvent_t up = nullptr, done = nullptr, down = nullptr;
+    std::vector<void*> in_dev;       // this slot's device buffer per graph input
+    std::vector<float*> out_host;    // pinned staging per graph output
+    int* err_host = nullptr;         // pinned copy of the kernels' error word
+  };
+  Flight flight_[2];
+  int submit_idx_ = 0, collect_idx_ = 0;
+  cudaStream_t copy_stream_ = nullptr;
+  bool pipe_ready_ = false, pipe_double_ = false;
+  void prepare_pipeline();
+  void rebind_input(int value_index, void* ptr);
 };
 
 class Context {

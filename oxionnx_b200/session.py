@@ -349,6 +349,42 @@ class Session:
         _raise_for(st, self.ctx.last_error())
         return {name: _ffi.result_array(res[i], self._out_bufs[i]) for i, name in enumerate(self.graph.output_names)}
 
+    # ---- pipelined runs: the upload of the next batch overlaps the run of the current one ----
+    def submit(self, feeds: Dict[str, np.ndarray]):
+        """Enqueues one run (upload, steps, download) and returns at once; at most two may be in flight.
+        The feed arrays must stay unchanged until the matching collect()."""
+        self.ensure_planned(feeds)
+        keep = _ffi.Keep()
+        ops = self._operands(feeds, keep)
+        _raise_for(_ffi.lib().oxb200_run_submit(self.ctx.handle, ops, len(self.graph.input_names)), self.ctx.last_error())
+        if not hasattr(self, "_in_flight"):
+            self._in_flight = []
+        self._in_flight.append(keep)
+
+    def collect(self) -> Dict[str, np.ndarray]:
+        """Waits for the oldest submitted run and returns its outputs."""
+        keep = _ffi.Keep()
+        res = self._results(keep)
+        st = _ffi.lib().oxb200_run_collect(self.ctx.handle, res, len(self.graph.output_names))
+        if getattr(self, "_in_flight", None):
+            self._in_flight.pop(0)
+        _raise_for(st, self.ctx.last_error())
+        return {name: _ffi.result_array(res[i], self._out_bufs[i]) for i, name in enumerate(self.graph.output_names)}
+
+    def run_pipelined(self, batches):
+        """Runs a sequence of feed dictionaries with one batch in flight behind the one being awaited."""
+        out, pending = [], 0
+        for feeds in batches:
+            self.submit(feeds)
+            pending += 1
+            if pending == 2:
+                out.append(self.collect())
+                pending -= 1
+        while pending:
+            out.append(self.collect())
+            pending -= 1
+        return out
+
     # ---- measurement helpers: the same run split into stage / resident launches / read ----
     def upload(self, feeds):
         self.ensure_planned(feeds)
