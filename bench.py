@@ -283,7 +283,8 @@ def main():
         sess.run_resident(1)
     c0 = sess.cuda_cache_counters()
     sampler = ClockSampler(int(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[local_rank]) if os.environ.get("CUDA_VISIBLE_DEVICES") else local_rank)
-    sampler.start()
+    if rank == 0:  # one sampler per job: eight nvidia-smi loops would compete with the ranks' launch threads
+        sampler.start()
     barrier()
     t_begin = time.time()
     # the timed K steps run without per-kernel events (an event record between two launches keeps the second
@@ -314,7 +315,7 @@ def main():
                 glue_bytes += s["work"]
     barrier()
     t_end = time.time()
-    clocks = sampler.stop(t_begin, t_end)
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     sess.ctx.set_profiling(False)
     total_ms = sum(step_ms)
     if dist is not None:
