@@ -161,7 +161,7 @@ def int8_companion(args, local_rank, flush_l2, peaks):
     w = WORKLOADS[key]
     batch = w["batch"]
     graph, weights, feeds, info = build_workload(key, batch)
-    sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).build_from_graph(graph, weights)
+    sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).with_cuda_graph(args.cuda_graph != 0).build_from_graph(graph, weights)
     sess.upload(feeds(batch, "c5_companion"))
     for _ in range(3):
         sess.run_resident(1)
@@ -227,6 +227,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-int8", action="store_true", help="skip the INT8 ResNet-50 companion measurement of the default workload")
     ap.add_argument("--kernel-path", default="auto", choices=["auto", "direct"])
+    ap.add_argument("--cuda-graph", type=int, default=0, help="1: replay the planned step list as one CUDA graph (OXIONNX_CUDA_GRAPH)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -252,7 +253,7 @@ def main():
     batch = args.batch or (max(w["batch"] // world, 1) if w.get("global_batch") else w["batch"])
     graph, weights, feeds, info = build_workload(args.workload, batch)
     f = feeds(batch, f"{args.workload}_in_rank{rank}") if args.workload != "c1" else feeds()
-    sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).build_from_graph(graph, weights)
+    sess = Session.builder().with_device(local_rank).with_profiling(True).with_kernel_path(args.kernel_path).with_cuda_graph(args.cuda_graph != 0).build_from_graph(graph, weights)
 
     # pinned host staging for the end-to-end leg
     feeds_pinned, pinned_ptrs = {}, []
@@ -377,7 +378,8 @@ def main():
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong" if (w.get("global_batch") and not args.batch) else "weak", "vs_baseline": None, "dtype": kind,
             "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu_batch": batch, "global_batch": batch * world, "parallelism": f"batch-sharded replicas x{world}, no collective",
-                       "l2": "flushed between timed steps (256 MiB memset)", "algorithmic_ops_per_step": info["ops"], "kernel_path": args.kernel_path},
+                       "l2": "flushed between timed steps (256 MiB memset)", "algorithmic_ops_per_step": info["ops"], "kernel_path": args.kernel_path,
+                       "cuda_graph": bool(args.cuda_graph)},
             "clocks": dict(clocks, window="the timed K steps and the profiled K steps that follow them"),
             "e2e": {"value": e2e_value, "unit": w["unit"], "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_total / args.steps,
                     "call": "oxb200_run_submit / oxb200_run_collect, two runs in flight, L2 not flushed between steps (the uploads replace the flush)"},

@@ -128,6 +128,7 @@ typedef struct {
   uint64_t kernel_launches;
   uint64_t umma_launches, simt_launches, glue_launches;
   uint64_t dispatches, declines, failures;
+  uint64_t graph_captures, graph_replays, graph_poisoned; /* graph_cache.rs: recordings made, replays, keys demoted */
 } oxb200_counters;
 
 /* ---- pure predicates (no device) ---------------------------------------------------- */

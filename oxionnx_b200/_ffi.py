@@ -50,7 +50,7 @@ class Counters(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in (
         "uploads", "upload_bytes", "downloads", "download_bytes", "fences", "weight_uploads", "weight_bytes_resident", "arena_bytes",
         "arena_peak_bytes", "arena_slots", "kernel_launches", "umma_launches", "simt_launches", "glue_launches", "dispatches", "declines",
-        "failures")]
+        "failures", "graph_captures", "graph_replays", "graph_poisoned")]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}

@@ -362,6 +362,7 @@ int oxb200_session_plan(oxb200_ctx* ctx, const oxb200_node* nodes, uint32_t n_no
     auto sess = std::make_unique<Session>(&C);
     std::map<std::string, const HostTensor*> none;
     sess->plan(nd, in, none, outs);
+    sess->allow_graph(true);
     C.session = std::move(sess);
     return (int)OXB200_OK_DEVICE;
   });

@@ -306,6 +306,128 @@ __global__ void dynq_apply_fused_kernel(const float* __restrict__ x, uint8_t* __
   }
 }
 
+// ---- DynamicQuantizeLinear, session path: wide passes ---------------------------------------------------
+// First pass: four independent 16-byte loads per thread and iteration, one pair of atomics per block.
+__global__ void __launch_bounds__(kThreads) minmax_wide_kernel(const float* __restrict__ x, int64_t n, uint32_t* keys) {
+  float mn = INFINITY, mx = -INFINITY;
+  const int64_t n4 = n / 4;
+  const float4* x4 = (const float4*)x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += 4 * stride) {
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t k = i + j * stride;
+      v[j] = x4[k < n4 ? k : i];  // a lane past the end re-reads a valid one: neutral for both extremes
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      mn = fminf(fminf(mn, v[j].x), fminf(v[j].y, fminf(v[j].z, v[j].w)));
+      mx = fmaxf(fmaxf(mx, v[j].x), fmaxf(v[j].y, fmaxf(v[j].z, v[j].w)));
+    }
+  }
+  if (blockIdx.x == 0)
+    for (int64_t i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      mn = fminf(mn, x[i]);
+      mx = fmaxf(mx, x[i]);
+    }
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  __shared__ float smn[kThreads / 32], smx[kThreads / 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    smn[warp] = mn;
+    smx[warp] = mx;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    mn = lane < kThreads / 32 ? smn[lane] : INFINITY;
+    mx = lane < kThreads / 32 ? smx[lane] : -INFINITY;
+    for (int off = 4; off > 0; off >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    if (lane == 0) {
+      if (mn != INFINITY) atomicMin(&keys[0], float_key(mn));
+      if (mx != -INFINITY) atomicMax(&keys[1], float_key(mx));
+    }
+  }
+}
+
+// saturate(round_ties_even(x / s) + z) as one byte.  With `safe` (s a normal number well inside the exponent
+// range, so that no product below under- or overflows for |x / s| <= 256) the quotient comes from the
+// reciprocal computed once per thread: q0 = x*r, one exact-remainder correction q = q0 + (x - s*q0)*r, which is
+// within one unit in the last place of the correctly rounded x / s.  Rounding to an integer can then differ
+// from the reference only when q lies within 2^-16 of k + 0.5; every q closer than 2^-13 to such a tie is
+// recomputed with the IEEE division.  The integer rounding and the byte extraction use the 1.5 * 2^23 addend
+// (an addition in round-to-nearest-even is the rounding), which keeps the conversion pipe out of the loop.
+__device__ __forceinline__ uint32_t dynq_byte(float x, float s, float r, float z, bool safe) {
+  const float M = 12582912.0f;
+  float ri;
+  if (safe) {
+    const float q0 = __fmul_rn(x, r);
+    const float q = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+    ri = __fsub_rn(__fadd_rn(q, M), M);
+    if (fabsf(__fsub_rn(q, ri)) > 0.49987793f) ri = rintf(__fdiv_rn(x, s));
+  } else {
+    ri = rintf(__fdiv_rn(x, s));
+  }
+  const float v = fminf(fmaxf(__fadd_rn(ri, z), 0.f), 255.f);
+  return __float_as_uint(__fadd_rn(v, M)) & 0xffu;
+}
+
+// Second pass: every block derives scale and zero point from the keys (the operations of dynq_params_kernel, so
+// every block gets the same two values), block 0 publishes them, and the last block to finish puts the keys
+// back to their identity values for the next call.  keys[2] is the arrival counter.  A warp covers 512
+// consecutive lanes per iteration: four coalesced 16-byte loads and four coalesced 4-byte stores per thread.
+__global__ void __launch_bounds__(kThreads) dynq_apply_wide_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, uint32_t* keys, float* params,
+                                                                   int64_t n) {
+  const float max_x = fmaxf(key_float(keys[1]), 0.f);
+  const float min_x = fminf(key_float(keys[0]), 0.f);
+  const float span = (max_x == min_x) ? 1.0f : __fsub_rn(max_x, min_x);
+  const float s = __fdiv_rn(span, 255.0f);
+  const float z = rintf(fminf(fmaxf(__fsub_rn(0.0f, __fdiv_rn(min_x, s)), 0.f), 255.f));
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    params[0] = s;
+    params[1] = z;
+  }
+  const bool safe = s >= 7.8886090522101181e-31f && s <= 1.2676506002282294e+30f;  // 2^-100 .. 2^100
+  const float r = safe ? __frcp_rn(s) : 0.f;
+  const int64_t n4 = n / 4;
+  const float4* x4 = (const float4*)x;
+  uint32_t* y4 = (uint32_t*)y;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t base = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * 128; base < n4; base += warps * 128) {
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t k = base + j * 32 + lane;
+      v[j] = k < n4 ? x4[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t k = base + j * 32 + lane;
+      const uint32_t w = dynq_byte(v[j].x, s, r, z, safe) | (dynq_byte(v[j].y, s, r, z, safe) << 8) | (dynq_byte(v[j].z, s, r, z, safe) << 16) |
+                         (dynq_byte(v[j].w, s, r, z, safe) << 24);
+      if (k < n4) y4[k] = w;
+    }
+  }
+  if (blockIdx.x == 0)
+    for (int64_t i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) y[i] = (uint8_t)dynq_byte(x[i], s, r, z, safe);
+  __syncthreads();  // every thread of this block has read the keys
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&keys[2], 1u) == gridDim.x - 1) {
+      keys[0] = 0xffffffffu;
+      keys[1] = 0u;
+      keys[2] = 0u;
+    }
+  }
+}
+
 // ---- element-wise ---------------------------------------------------------------------
 __device__ __forceinline__ float apply_bin(int op, float a, float b) {
   switch (op) {
@@ -1105,8 +1227,16 @@ void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* para
   // (dynamic_quantize_scratch_init) and put back to that by the last block of every apply pass
   int64_t n = x.d.numel();
   uint32_t* keys = (uint32_t*)scratch;
-  minmax_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, n, keys);
-  dynq_apply_fused_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n);
+  if ((((uintptr_t)x.ptr) & 15) != 0 || (((uintptr_t)y.ptr) & 3) != 0) {
+    minmax_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, n, keys);
+    dynq_apply_fused_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n);
+    return;
+  }
+  const int64_t cap = 148 * 8;
+  const int64_t b_mm = std::min<int64_t>(cap, std::max<int64_t>(1, (n / 4 + kThreads * 4 - 1) / (kThreads * 4)));
+  const int64_t b_ap = std::min<int64_t>(cap, std::max<int64_t>(1, (n / 4 + (kThreads / 32) * 128 - 1) / ((kThreads / 32) * 128)));
+  minmax_wide_kernel<<<(int)b_mm, kThreads, 0, s>>>((const float*)x.ptr, n, keys);
+  dynq_apply_wide_kernel<<<(int)b_ap, kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n);
 }
 
 void dynamic_quantize_scratch_init(float* scratch) {

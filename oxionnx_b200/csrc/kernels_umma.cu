@@ -74,6 +74,14 @@ struct alignas(64) KParams {
   // and the output start at row outer * rb + inner * rh and column inner * ch of their matrices
   int batched, items, items_inner;
   int a_rb, a_rh, a_ch, b_rb, b_rh, b_ch, o_rb, o_rh, o_ch;
+  // split K (few output tiles, long K): work item t is (tile t / splits, slice t % splits); slice s runs K
+  // blocks [s * k_per, (s + 1) * k_per) and leaves its raw accumulators in ws[tile][s][128 x BN]; per run of an
+  // epilogue warp, the slice that arrives last (ws_count) adds the slices in order 0 .. splits-1 and runs the
+  // fused epilogue.  Nobody waits for anybody, and the sum does not depend on the arrival order.  Counters are
+  // kept per tile, epilogue warp and 32-channel run.
+  int splits, k_per;
+  uint32_t* ws;
+  unsigned int* ws_count;
   uint32_t idesc;
   // epilogue
   int mode;
@@ -542,6 +550,21 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                : "memory");
 }
 
+// L2 prefetch of one warp's share of a tile's residual lanes (32 rows, `cpw` runs of 128 bytes each).
+template <int BN>
+__device__ __forceinline__ void prefetch_residual_rows(const KParams& p, int tt, int quarter, int lane, int first, int cpw) {
+  const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
+  const long long m = (long long)tile_m * BLOCK_M + quarter * 32 + lane;
+  const int oc0 = tile_n * BN;
+  if (m >= p.M) return;
+  const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;
+  const int end = min(first + cpw, n_chunks);
+  for (int c = first; c < end; ++c) {
+    const float* line = p.residual + (size_t)m * p.OC + oc0 + c * 32;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+  }
+}
+
 // ---- epilogue role ------------------------------------------------------------------------
 // Eight warps drain an accumulator: warp w may read the TMEM lanes 32 * (w % 4) .. + 31 (output
 // rows of the tile), and the two warps of a lane quarter split the tile's channel runs in two
@@ -549,7 +572,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 // either a swizzled copy into this warp's 4 KB staging rows followed by one TMA store per
 // `pitch` bytes of row, or direct 16-byte stores.  The accumulator is handed back to the MMA
 // issuer as soon as this warp's last TMEM read has landed, before the last run's math.
-template <int BN, int VARIANT>
+template <int BN, int VARIANT, bool SPLIT>
 __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int lane, uint32_t tmem_base, uint64_t* bar_acc_full,
                                               uint64_t* bar_acc_empty, uint32_t stage_addr, volatile int* abortp, int total_tiles) {
   constexpr int CPW = BN >= 64 ? BN / 64 : 1;  // channel runs per warp and tile
@@ -571,10 +594,20 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
       const int outer = item / p.items_inner, inner = item - outer * p.items_inner;
       o_row0 = outer * p.o_rb + inner * p.o_rh;
       o_col0 = inner * p.o_ch;
+    } else if (p.splits > 1) {
+      tt = t / p.splits;
     }
     const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
     const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
     const uint32_t buf = local & 1u;
+    if constexpr (VARIANT >= V_F32_RES && VARIANT < V_DEQUANT) {
+      // The residual lanes are read with plain loads right before their use, one 128-byte line per thread and
+      // run: bring the lines of this CTA's next tile (and, at the start, of this one) into L2 a whole tile
+      // ahead, so that those loads pay the L2 latency instead of the DRAM latency.
+      if (local == 0) prefetch_residual_rows<BN>(p, tt, quarter, lane, first, CPW);
+      const int tn = t + (int)gridDim.x;
+      if (tn < total_tiles) prefetch_residual_rows<BN>(p, p.splits > 1 ? tn / p.splits : tn, quarter, lane, first, CPW);
+    }
     if (ew == 0) OXB_TRACE(local, 6);
     bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local >> 1) & 1u, abortp);
     if (ew == 0) OXB_TRACE(local, 7);
@@ -625,6 +658,55 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
       release();
       continue;
     }
+    if constexpr (SPLIT) {
+      // Runs are taken in an order rotated by the slice index and each run has its own arrival counter, so the
+      // slices of a tile finish different runs last and share the summing and the fused epilogue between them.
+      constexpr bool kFloatAcc = VARIANT < V_REQUANT || (VARIANT >= V_F32_RES && VARIANT < V_DEQUANT);
+      const int split = t - tt * p.splits;
+      // workspace of one slice: [lane quarter][run][16-byte piece j][lane], so that every store and load of a
+      // warp covers 512 contiguous bytes (only warps with the same index in the other slices read it back)
+      const uint4* tile_ws = reinterpret_cast<const uint4*>(p.ws + (size_t)tt * p.splits * (BLOCK_M * BN)) + (size_t)quarter * (BN / 32) * 256 + lane;
+      constexpr size_t kSlice = (size_t)BLOCK_M * BN / 4;  // 16-byte pieces per slice
+      uint4* mine = const_cast<uint4*>(tile_ws) + (size_t)split * kSlice;
+      unsigned int* counters = p.ws_count + ((size_t)tt * EPI_WARPS + ew) * 4;
+      const int runs = end - first;
+      for (int i = 0; i < runs; ++i) {
+        const int c = first + (i + split) % runs;
+        tmem_ld32_nowait(taddr + (uint32_t)c * 32u, va);
+        tmem_ld_wait();
+        if (i == runs - 1) release();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) __stcg(mine + (c * 8 + j) * 32, make_uint4(va[4 * j], va[4 * j + 1], va[4 * j + 2], va[4 * j + 3]));
+        __threadfence();
+        __syncwarp();
+        unsigned int arrived = 0;
+        if (lane == 0) arrived = atomicAdd(counters + (c - first), 1u);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (arrived != (unsigned int)p.splits - 1u) continue;  // a later slice finishes this run
+        if (lane == 0) counters[c - first] = 0u;               // ready for the next launch
+        __threadfence();
+        for (int sl = 0; sl < p.splits; ++sl) {
+          const uint4* src = tile_ws + (size_t)sl * kSlice + c * 256;
+          uint4 xv[8];  // the eight loads of a slice are issued together
+#pragma unroll
+          for (int j = 0; j < 8; ++j) xv[j] = __ldcg(src + j * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t xs[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (sl == 0) va[4 * j + e] = xs[e];
+              else if (kFloatAcc) va[4 * j + e] = __float_as_uint(__fadd_rn(__uint_as_float(va[4 * j + e]), __uint_as_float(xs[e])));
+              else va[4 * j + e] += xs[e];
+            }
+          }
+        }
+        emit(va, c);
+      }
+      if (ew == 0) OXB_TRACE(local, 8);
+      continue;
+    }
+    if constexpr (SPLIT) continue;  // (not reached)
     tmem_ld32_nowait(taddr + (uint32_t)first * 32u, va);
     tmem_ld_wait();
     // one copy of the run's code in the loop (the instruction cache, not the 32 register moves, is
@@ -667,7 +749,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   const uint32_t stage_bytes = kb_bytes * (uint32_t)p.kpb;  // one ring stage
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int k_iters = p.taps * p.cblocks;
-  const int total_tiles = p.m_tiles * p.n_tiles * (p.batched ? p.items : 1);
+  const int total_tiles = p.m_tiles * p.n_tiles * (p.batched ? p.items : p.splits);
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
 
   if (threadIdx.x == 0) {
@@ -707,6 +789,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++ptile) {
       OXB_TRACE(ptile, 0);
       int tt = t, a_row0 = 0, a_col0 = 0, b_row0 = 0, b_col0 = 0;
+      int it_begin = 0, it_end = k_iters;
       if (p.batched) {
         const int per = p.m_tiles * p.n_tiles, item = t / per;
         tt = t - item * per;
@@ -715,6 +798,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         a_col0 = inner * p.a_ch;
         b_row0 = outer * p.b_rb + inner * p.b_rh;
         b_col0 = inner * p.b_ch;
+      } else if (p.splits > 1) {
+        tt = t / p.splits;
+        it_begin = (t - tt * p.splits) * p.k_per;
+        it_end = min(k_iters, it_begin + p.k_per);
       }
       const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
       const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
@@ -726,11 +813,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         n0 = tt / p.P;
       }
       const int w_base = q0 * p.sw - p.pl, h_base = p0 * p.sh - p.pt;
-      int r = 0, sx = 0, cb = 0;
+      int cb = it_begin % p.cblocks, sx = (it_begin / p.cblocks) % p.S, r = (it_begin / p.cblocks) / p.S;
       // A barrier round trip, an expect_tx and each TMA instruction cost the issuing thread on the
       // order of a hundred cycles, whatever the box size: a stage carries several K blocks when
       // they are small, so that those costs are paid once per stage.
-      for (int it = 0; it < k_iters; it += p.kpb) {
+      for (int it = it_begin; it < it_end; it += p.kpb) {
         OXB_TRACE_K(ptile, it, 0);
         bool got = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp);
         OXB_TRACE_K(ptile, it, 1);
@@ -760,7 +847,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
             }
           }
         } else {
-          const int blocks = min(p.kpb, k_iters - it);
+          const int blocks = min(p.kpb, it_end - it);
           const uint32_t full = smem_u32(&bar_full[stage]);
           if (lane == 0) mbar_expect_tx(full, kb_bytes * (uint32_t)blocks);
           uint32_t a_dst = tiles_base + stage * stage_bytes;
@@ -816,11 +903,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
       tc_fence_after();
       OXB_TRACE(local, 3);
       const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
-      for (int it = 0; it < k_iters; it += p.kpb) {
+      int it_begin = 0, it_end = k_iters;
+      if (!p.batched && p.splits > 1) {
+        it_begin = (t % p.splits) * p.k_per;
+        it_end = min(k_iters, it_begin + p.k_per);
+      }
+      for (int it = it_begin; it < it_end; it += p.kpb) {
         OXB_TRACE_K((int)local, it, 3);
         got = mbar_wait(smem_u32(&bar_full[stage]), phase, abortp);
         OXB_TRACE_K((int)local, it, 4);
-        if (it == 0) OXB_TRACE(local, 4);
+        if (it == it_begin) OXB_TRACE(local, 4);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0 && !*abortp) {
             *abortp = 1;
@@ -833,12 +925,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         if (lane == 0) {
           // descriptors differ between K blocks only in the 16-byte granular start address
           if (one_block) {
-            tc_mma_block<KIND>(tmem_d, desc_lo | (a16 & 0x3fffu), desc_lo | ((a16 + a16_bytes) & 0x3fffu), desc_hi, idesc, it > 0 ? 1u : 0u, mmas);
+            tc_mma_block<KIND>(tmem_d, desc_lo | (a16 & 0x3fffu), desc_lo | ((a16 + a16_bytes) & 0x3fffu), desc_hi, idesc, it > it_begin ? 1u : 0u, mmas);
           } else {
-            const int blocks = min(p.kpb, k_iters - it);
+            const int blocks = min(p.kpb, it_end - it);
             uint32_t b16 = a16;
             for (int g = 0; g < blocks; ++g, b16 += kb16)
-              tc_mma_block<KIND>(tmem_d, desc_lo | (b16 & 0x3fffu), desc_lo | ((b16 + a16_bytes) & 0x3fffu), desc_hi, idesc, (it + g) > 0 ? 1u : 0u, mmas);
+              tc_mma_block<KIND>(tmem_d, desc_lo | (b16 & 0x3fffu), desc_lo | ((b16 + a16_bytes) & 0x3fffu), desc_hi, idesc, (it + g) > it_begin ? 1u : 0u, mmas);
           }
           tc_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
         }
@@ -858,8 +950,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
   } else {
     // ---------------- epilogue: warps 2..9 ----------------
     const uint32_t stage_addr = smem_u32(&s_stage[warp - 2][0]);
-#define OXB_EPI(V) \
-  case V: epilogue_role<BN, V>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
+    const bool split = !p.batched && p.splits > 1;
+#define OXB_EPI(V)                                                                                                                  \
+  case V:                                                                                                                           \
+    if (split) epilogue_role<BN, V, true>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles);   \
+    else epilogue_role<BN, V, false>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles);        \
+    break;
     if constexpr (KIND == 0) {
       switch (p.variant) {
         OXB_EPI(V_REQUANT)
@@ -875,7 +971,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         OXB_EPI(22)
         OXB_EPI(23)
         OXB_EPI(24)
-        default: epilogue_role<BN, 25>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
+        default:
+          if (split) epilogue_role<BN, 25, true>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles);
+          else epilogue_role<BN, 25, false>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles);
+          break;
       }
     } else {
       switch (p.variant) {
@@ -890,7 +989,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) umma_conv_kernel(const __grid_
         OXB_EPI(16)
         OXB_EPI(17)
         OXB_EPI(18)
-        default: epilogue_role<BN, 19>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles); break;
+        default:
+          if (split) epilogue_role<BN, 19, true>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles);
+          else epilogue_role<BN, 19, false>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles);
+          break;
       }
     }
 #undef OXB_EPI
@@ -1002,6 +1104,8 @@ struct UmmaPlan {
   int grid;
   size_t smem;
   char desc[160];
+  void* ws = nullptr;        // split-K workspace and arrival counters, owned by the plan
+  void* ws_count = nullptr;
 };
 
 bool umma_available() {
@@ -1078,25 +1182,38 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   // them, the kernel runs ceil(tiles / SMs) rounds of tiles, and the last tile's epilogue is
   // not hidden.  Pick the width that minimises that estimate; ties go to the wider tile (fewer
   // re-reads of the activations).
+  // Split K: when even the narrowest useful tiling leaves most SMs without a tile and K is long, `splits`
+  // CTAs share a (wider) tile, each running a slice of K; the slices meet in an L2-resident workspace.  It is
+  // only considered when every slice gets its own SM in one round and at least eight K blocks.
   const int sms = sm_count();
   const int64_t m_tiles = ceil_div(M, BLOCK_M);
   const int bn_max = cs.OC <= 32 ? 32 : (cs.OC <= 64 ? 64 : (cs.OC <= 128 ? 128 : 256));
-  int bn = bn_max;
+  const int64_t k_iters_host = (int64_t)cs.R * cs.S * (cs.C / cb);
+  int bn = bn_max, splits = 1;
   {
     const double k_bytes = (double)cs.K() * es;
     const double k_steps = k_bytes / 32.0;
     const double ns_out = e.mode == EPI_F32 ? 0.03e-9 : 0.08e-9;
+    const char* env_split = std::getenv("OXB200_UMMA_SPLITK");  // upper bound on the slices; "1": never split (for comparisons)
+    const int max_split = env_split ? std::max(1, std::atoi(env_split)) : 8;
     double best = 1e30;
     for (int cand = bn_max; cand >= 32; cand /= 2) {
       const double tiles = (double)m_tiles * (double)ceil_div(cs.OC, cand);
-      const double rounds = std::ceil(tiles / sms);
-      const double t_mma = k_steps * std::max(56.0, cand / 2.0) / 1.965e9;
-      const double t_feed = (double)(BLOCK_M + cand) * k_bytes / 95e9;
-      const double t_epi = (double)BLOCK_M * cand * ns_out;
-      const double t = rounds * std::max(t_mma, std::max(t_feed, t_epi)) + t_epi;
-      if (t < best * 0.97) {
-        best = t;
-        bn = cand;
+      for (int sp = 1; sp <= max_split; ++sp) {
+        if (sp > 1 && (tiles * sp > sms || k_iters_host / sp < 8)) break;
+        const double rounds = std::ceil(tiles * sp / sms);
+        const double t_mma = k_steps * std::max(56.0, cand / 2.0) / 1.965e9 / sp;
+        const double t_feed = (double)(BLOCK_M + cand) * k_bytes / 95e9 / sp;
+        const double t_epi = (double)BLOCK_M * cand * ns_out;
+        // measured: a split launch costs about 10 us more than an unsplit one before its first K block pays
+        // back (the slices' accumulators go through the workspace, and the finishing epilogues are not overlapped)
+        const double t_split = sp > 1 ? 10e-6 : 0.0;
+        const double t = rounds * std::max(t_mma, std::max(t_feed, t_epi)) + t_epi + t_split;
+        if (t < best * 0.97) {
+          best = t;
+          bn = cand;
+          splits = sp;
+        }
       }
     }
   }
@@ -1155,7 +1272,8 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   {
     // output tile store through TMA when rows are 16-byte granular
     const size_t oes = dt_size(e.out_dt);
-    const size_t row_bytes = std::min<size_t>(128, (size_t)std::max(bn / 64, 1) * 32 * oes);  // at most one epilogue warp's share of a row
+    // at most one epilogue warp's share of a row; one run when K is split (any slice may finish any run)
+    const size_t row_bytes = splits > 1 ? 32 * oes : std::min<size_t>(128, (size_t)std::max(bn / 64, 1) * 32 * oes);
     kp.out_tma = 0;
     kp.out_row_bytes = (int)row_bytes;
     if (((size_t)cs.OC * oes) % 16 == 0 && ((uintptr_t)out & 15) == 0 && row_bytes >= 32 && (row_bytes & (row_bytes - 1)) == 0) {
@@ -1199,11 +1317,30 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   // K blocks per stage: up to four small ones share a barrier round trip, as long as a stage stays
   // within 64 KB (the ring then still has three stages)
   const size_t kb_bytes = (size_t)(BLOCK_M + bn) * swz;
-  const int64_t k_iters_host = (int64_t)cs.R * cs.S * (cs.C / cb);
   int kpb = 1;
   while (kpb < 4 && (size_t)(kpb * 2) * kb_bytes <= 64 * 1024 && kpb * 2 <= k_iters_host) kpb *= 2;
   if (const char* env = std::getenv("OXB200_UMMA_KPB")) kpb = std::max(1, std::min(4, std::atoi(env)));
   kp.kpb = kpb;
+  // slices of K: whole stages each, none empty
+  kp.splits = 1;
+  kp.k_per = (int)k_iters_host;
+  if (splits > 1) {
+    const int64_t k_per = ceil_div(ceil_div(k_iters_host, (int64_t)splits), (int64_t)kpb) * kpb;
+    const int64_t eff = ceil_div(k_iters_host, k_per);
+    if (eff > 1) {
+      const size_t ws_words = (size_t)m_tiles * n_tiles * eff * BLOCK_M * bn;
+      const size_t cnt = (size_t)m_tiles * n_tiles * EPI_WARPS * 4;
+      if (cudaMalloc(&pl->ws, ws_words * 4) == cudaSuccess && cudaMalloc(&pl->ws_count, cnt * sizeof(unsigned int)) == cudaSuccess &&
+          cudaMemset(pl->ws_count, 0, cnt * sizeof(unsigned int)) == cudaSuccess) {
+        kp.splits = (int)eff;
+        kp.k_per = (int)k_per;
+        kp.ws = (uint32_t*)pl->ws;
+        kp.ws_count = (unsigned int*)pl->ws_count;
+      } else {
+        (void)cudaGetLastError();  // no workspace: run unsplit
+      }
+    }
+  }
   const size_t stage_bytes = kb_bytes * kpb;
   // one persistent CTA per SM: the ring may use most of the 227 KB and runs on across tiles
   const size_t budget = 192 * 1024;
@@ -1223,6 +1360,8 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   else if (e.mode == EPI_DEQUANT) kp.variant = V_DEQUANT + (e.x_zp_dev ? 1 : 0) + 2 * e.dq_act;
   else kp.variant = e.x_zp_dev ? V_INT32_DYN : V_INT32;
   if (e.mode == EPI_F32 ? e.bias_f == nullptr : e.bias_i == nullptr) {
+    if (pl->ws) cudaFree(pl->ws);
+    if (pl->ws_count) cudaFree(pl->ws_count);
     delete pl;
     return no("the tensor-core epilogue needs a (padded) bias vector");
   }
@@ -1247,10 +1386,12 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.err_flag = nullptr;
   pl->bn = bn;
   pl->kind = kind;
-  pl->grid = (int)std::min<int64_t>(m_tiles * n_tiles, sms);
+  pl->grid = (int)std::min<int64_t>(m_tiles * n_tiles * kp.splits, sms);
   pl->smem = (size_t)stages * stage_bytes + 1024;
-  snprintf(pl->desc, sizeof pl->desc, "umma_%s M=%lld N=%d K=%lld tile=128x%dx%dB stages=%dx%d %s", kind == 0 ? "i8" : "tf32", (long long)M, cs.OC,
-           (long long)cs.K(), bn, swz, stages, kpb, gemm_like ? "tiled" : "im2col");
+  char split_note[24] = "";
+  if (kp.splits > 1) snprintf(split_note, sizeof split_note, " splitK=%d", kp.splits);
+  snprintf(pl->desc, sizeof pl->desc, "umma_%s M=%lld N=%d K=%lld tile=128x%dx%dB stages=%dx%d %s%s", kind == 0 ? "i8" : "tf32", (long long)M, cs.OC,
+           (long long)cs.K(), bn, swz, stages, kpb, gemm_like ? "tiled" : "im2col", split_note);
   return pl;
 }
 
@@ -1328,6 +1469,7 @@ UmmaPlan* umma_plan_create_batched(const BatchedGemm& g, std::string* why) {
   kp.n_tiles = (int)n_tiles;
   kp.m_tiles = (int)m_tiles;
   kp.batched = 1;
+  kp.splits = 1;
   kp.items = (int)items;
   kp.items_inner = g.inner;
   kp.a_rb = g.a_rb, kp.a_rh = g.a_rh, kp.a_ch = g.a_ch;
@@ -1356,7 +1498,12 @@ UmmaPlan* umma_plan_create_batched(const BatchedGemm& g, std::string* why) {
   return pl;
 }
 
-void umma_plan_destroy(UmmaPlan* p) { delete p; }
+void umma_plan_destroy(UmmaPlan* p) {
+  if (!p) return;
+  if (p->ws) cudaFree(p->ws);
+  if (p->ws_count) cudaFree(p->ws_count);
+  delete p;
+}
 const char* umma_plan_desc(const UmmaPlan* p) { return p->desc; }
 
 void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {
@@ -1393,6 +1540,7 @@ void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {
       if (!host[t * 16 + 0] && !host[t * 16 + 2]) break;
       fprintf(stderr, " %3d:", t);
       for (int k = 0; k < 10; ++k) fprintf(stderr, " %7lld%s", host[t * 16 + k] ? host[t * 16 + k] - t0 : -1, (k == 1 || k == 5) ? " |" : "");
+      if (t == 0 && host[10]) fprintf(stderr, "  last slice of tile 0: loads of run 0 %lld, its epilogue %lld, all runs %lld cycles", host[11] - host[10], host[12] - host[11], host[13] - host[10]);
       fprintf(stderr, "\n");
     }
     fprintf(stderr, " tile 3 per K block: prod_wait0 prod_wait1 prod_issued | mma_wait0 mma_wait1 mma_issued\n");

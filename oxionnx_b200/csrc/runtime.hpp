@@ -159,6 +159,24 @@ class Session {
   bool pipe_ready_ = false, pipe_double_ = false;
   void prepare_pipeline();
   void rebind_input(int value_index, void* ptr);
+  // CUDA-graph replay of the step list (graph_cache.rs of the reference's provider: off unless
+  // OXIONNX_CUDA_GRAPH is set, never together with shadow verification, a failed capture demotes its key
+  // for good).  A recording stores device addresses, so the key is every address that can differ between
+  // two runs of one plan: the graph inputs' buffers.  Everything else a step touches (arena, weights,
+  // parameter vectors, the error word) is owned by the session or the context and never moves.
+  struct GraphSlot {
+    std::vector<void*> key;
+    cudaGraphExec_t exec = nullptr;
+    bool warmed = false, poisoned = false;
+    uint64_t d_kernel = 0, d_umma = 0, d_simt = 0, d_glue = 0;  // launches one replay stands for
+  };
+  std::vector<GraphSlot> graphs_;
+  bool graph_allowed_ = false;
+  bool replay_graph();
+  bool capture_graph(GraphSlot& g);
+
+ public:
+  void allow_graph(bool on) { graph_allowed_ = on; }
 };
 
 class Context {

@@ -114,13 +114,14 @@ class CudaContext:
     """One device, one stream, session-lifetime weight residency."""
 
     def __init__(self, device: int = 0, *, verify=False, strict=False, residency=True, kernel_path="auto", keep_intermediates=False,
-                 profile=False):
+                 profile=False, cuda_graph=False):
         cfg = _ffi.Config()
         cfg.struct_size = ctypes.sizeof(_ffi.Config)
         cfg.verify, cfg.strict, cfg.residency = int(verify), int(strict), int(residency)
         cfg.kernel_path = 1 if kernel_path == "direct" else 0
         cfg.keep_intermediates = int(keep_intermediates)
         cfg.profile = int(profile)
+        cfg.cuda_graph = int(cuda_graph)
         h = ctypes.c_void_p()
         st = _ffi.lib().oxb200_ctx_create(device, ctypes.byref(cfg), ctypes.byref(h))
         if st != _ffi.OK_HOST:
@@ -263,6 +264,15 @@ class SessionBuilder:
 
     def with_profiling(self, on=True):
         self._ctx_kw["profile"] = on
+        return self
+
+    def with_cuda_graph(self, on=True):
+        """Replay the planned step list as one CUDA graph (OXIONNX_CUDA_GRAPH; oxionnx-cuda src/graph_cache.rs)."""
+        self._ctx_kw["cuda_graph"] = on
+        return self
+
+    def with_verify(self, on=True):
+        self._ctx_kw["verify"] = on
         return self
 
     def with_input_shapes(self, shapes: Dict[str, tuple]):

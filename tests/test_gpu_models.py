@@ -320,3 +320,85 @@ def test_pipelined_runs_match_synchronous_runs():
     for g_, w_ in zip(s2.run_pipelined(b2), want2):
         assert np.array_equal(g_["y"], w_)
     s2.close()
+
+
+def test_cuda_graph_replay_is_bit_identical_and_counted():
+    """OXIONNX_CUDA_GRAPH (oxionnx-cuda src/graph_cache.rs; tests/graph_cache_gpu.rs checks replays bit for bit):
+    the first run on a set of input addresses launches the ordinary way, the second records, later ones replay;
+    every run gives exactly the lanes of a session without graphs; launch counters advance as if each step had
+    been launched; pipelined runs record one graph per input buffer; with shadow verification on nothing is
+    recorded."""
+    graph, weights, feeds, _ = models.build_resnet50_qlinear(batch=2, image=32, base=8, classes=10)
+    batches = [feeds(2, f"graph{i}") for i in range(4)]
+    plain = Session.builder().build_from_graph(graph, weights)
+    want = [plain.run(b)["logits"].copy() for b in batches]
+    per_run = plain.cuda_cache_counters()["kernel_launches"] // len(batches)
+    plain.close()
+
+    sess = Session.builder().with_cuda_graph().build_from_graph(graph, weights)
+    for b, w in zip(batches, want):
+        assert np.array_equal(sess.run(b)["logits"], w)
+    c = sess.cuda_cache_counters()
+    assert (c["graph_captures"], c["graph_replays"], c["graph_poisoned"]) == (1, 3, 0)
+    assert c["kernel_launches"] == per_run * len(batches)
+    for g_, w_ in zip(sess.run_pipelined(batches), want):
+        assert np.array_equal(g_["logits"], w_)
+    c = sess.cuda_cache_counters()
+    assert c["graph_poisoned"] == 0 and c["graph_captures"] in (1, 2) and c["graph_replays"] >= 5
+    sess.upload(batches[2])
+    sess.run_resident(3)
+    assert np.array_equal(sess.download()["logits"], want[2])
+    sess.close()
+
+    # float graph with tensor-core steps launched as programmatic dependents
+    g2, w2, f2, _ = models.build_resnet50_f32(batch=2, image=32, base=16, classes=10)
+    feeds2 = f2(2, "graph-f32")
+    s_plain = Session.builder().build_from_graph(g2, w2)
+    want2 = s_plain.run(feeds2)["logits"].copy()
+    s_plain.close()
+    s_graph = Session.builder().with_cuda_graph().build_from_graph(g2, w2)
+    for _ in range(4):
+        assert np.array_equal(s_graph.run(feeds2)["logits"], want2)
+    assert s_graph.cuda_cache_counters()["graph_replays"] == 3
+    s_graph.close()
+
+    verified = Session.builder().with_cuda_graph().with_verify().build_from_graph(graph, weights)
+    for b, w in zip(batches, want):
+        assert np.array_equal(verified.run(b)["logits"], w)
+    c = verified.cuda_cache_counters()
+    assert (c["graph_captures"], c["graph_replays"]) == (0, 0)
+    verified.close()
+
+
+def test_split_k_is_used_and_agrees_with_the_unsplit_kernel(monkeypatch):
+    """Layers with few output tiles and a long K run as several K slices per tile that meet in a workspace.  The
+    integer form must equal the unsplit kernel bit for bit; the float form adds the slices in a fixed order, so
+    it is reproducible run to run and agrees with the unsplit kernel within the TF32 tolerance."""
+    from oxionnx_b200.graph import Graph, Node
+    rng = np.random.default_rng(77)
+    wq = {"w": rng.integers(-127, 128, (256, 512, 3, 3)).astype(np.float32), "ws": rng.uniform(0.001, 0.01, 256).astype(np.float32),
+          "wz": np.zeros(256, np.float32), "b": rng.integers(-1000, 1000, 256).astype(np.float32), "xs": np.float32([0.02]), "z0": np.float32([0]),
+          "z128": np.float32([128]), "ys": np.float32([1.5]), "qs": np.float32([0.02])}
+    gq = Graph(nodes=[Node("QuantizeLinear", "q", ["x", "qs", "z0"], ["xq"], {}),
+                      Node("QLinearConv", "conv", ["xq", "xs", "z0", "w", "ws", "wz", "ys", "z128", "b"], ["yq"], {"pads": [1, 1, 1, 1]}),
+                      Node("DequantizeLinear", "dq", ["yq", "ys", "z128"], ["y"], {})], input_names=["x"], output_names=["y"])
+    xq = np.abs(rng.standard_normal((2, 512, 7, 7))).astype(np.float32)
+    wf = {"w": (rng.standard_normal((512, 256, 3, 3)) * 0.02).astype(np.float32), "b": rng.standard_normal(512).astype(np.float32)}
+    gf = Graph(nodes=[Node("Relu", "pre", ["x"], ["x1"], {}), Node("Conv", "conv", ["x1", "w", "b"], ["y"], {"pads": [1, 1, 1, 1], "activation": "relu"})],
+               input_names=["x"], output_names=["y"])
+    xf = rng.standard_normal((2, 256, 7, 7)).astype(np.float32)
+    results = {}
+    for mode in ("split", "unsplit"):
+        monkeypatch.setenv("OXB200_UMMA_SPLITK", "8" if mode == "split" else "1")
+        for name, graph, weights, x in (("int8", gq, wq, xq), ("f32", gf, wf, xf)):
+            sess = Session.builder().build_from_graph(graph, weights)
+            first = sess.run({"x": x})["y"].copy()
+            again = sess.run({"x": x})["y"].copy()
+            assert np.array_equal(first, again), "a split-K sum must not depend on the arrival order"
+            kernel = [s_["kernel"] for s_ in sess.steps() if s_["node"] == "conv" and s_["kernel"].startswith("umma")][0]
+            assert ("splitK" in kernel) == (mode == "split"), kernel
+            results[(mode, name)] = first
+            sess.close()
+    assert np.array_equal(results[("split", "int8")], results[("unsplit", "int8")])
+    assert np.unique(results[("split", "int8")]).size > 8
+    assert close_tf32(results[("split", "f32")], results[("unsplit", "f32")])

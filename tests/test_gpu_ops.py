@@ -90,6 +90,8 @@ QCONV_SHAPES = [
     (5, 64, 16, 16, 64, 3, 1, 1, 128, 0),      # padded with a non-zero zero point: direct kernel
     (2, 3, 20, 20, 16, 7, 2, 3, 128, 0),       # stem geometry: direct kernel
     (1, 512, 4, 4, 1000, 1, 1, 0, 128, 128),   # classifier as a 1x1 convolution
+    (2, 512, 7, 7, 256, 3, 1, 1, 128, 128),    # one row tile, 36 K blocks: K split over several CTAs
+    (3, 256, 9, 9, 96, 3, 1, 1, 0, 0),         # split K with a ragged channel tile and 16-bit lanes
 ]
 
 
@@ -229,7 +231,16 @@ def test_quantize_dequantize_dynamic_bit_exact(ctx):
     want, = oracle.run_node("DequantizeLinear", [q, np.float32([0.037]), np.float32([128])])
     got = dispatch(ctx, "DequantizeLinear", [q, np.float32([0.037]), np.float32([128])])
     assert np.array_equal(got[0], want)
-    for arr in (x.reshape(24, 120), np.zeros((3, 5), np.float32), np.float32([[-0.5, 254.5]]), (rng.standard_normal((1000, 77)) * 5).astype(np.float32)):
+    # quotients on and next to every tie k + 0.5 (scale exactly 1, then a scale with a full mantissa), sizes that
+    # leave ragged ends for the 512-lane warp tiles, and scales at the ends of the exponent range
+    ties = np.concatenate([np.arange(0, 255, 0.5, dtype=np.float32), np.float32([0.0, 255.0])])
+    ties = np.concatenate([ties, np.nextafter(ties, np.float32(300)), np.nextafter(ties, np.float32(-300))]).astype(np.float32)
+    ties = np.clip(ties, 0, 255).astype(np.float32)
+    odd = np.float32(0.7310585975646973)
+    wide = (rng.standard_normal(513 * 41 + 3) * 3).astype(np.float32)
+    for arr in (x.reshape(24, 120), np.zeros((3, 5), np.float32), np.float32([[-0.5, 254.5]]), (rng.standard_normal((1000, 77)) * 5).astype(np.float32),
+                ties.reshape(1, -1), (ties * odd).reshape(1, -1), (ties - np.float32(100.5)).reshape(1, -1), wide.reshape(1, -1),
+                (wide * np.float32(1e-36)).reshape(1, -1), (wide * np.float32(1e33)).reshape(1, -1), wide[:2051].reshape(7, 293)):
         want = oracle.run_node("DynamicQuantizeLinear", [arr], n_outputs=3)
         got = dispatch(ctx, "DynamicQuantizeLinear", [arr], n_out=3)
         assert got is not None, ctx.last_error()
@@ -248,6 +259,8 @@ FCONV_SHAPES = [
     (2, 3, 20, 18, 40, 7, 1, 3, "relu"),     # stride-1 image-space 7x7 with its own padding: four-lane row windows
     (2, 3, 19, 19, 32, 7, 1, 0, ""),         # the same behind an explicit reflect Pad (no padding of its own)
     (1, 4, 12, 12, 16, 3, 1, 1, ""),         # four channels, 3x3 (windows of four pixels)
+    (2, 256, 7, 7, 512, 3, 1, 1, "relu"),    # one row tile, 72 K blocks: K split over several CTAs
+    (4, 1024, 7, 7, 200, 1, 1, 0, ""),       # split K on the 1x1 GEMM path, ragged channel tile
     (1, 6, 10, 10, 6, 3, 1, 1, ""),          # depthwise-like groups below
 ]
 
