@@ -376,13 +376,13 @@ def test_split_k_is_used_and_agrees_with_the_unsplit_kernel(monkeypatch):
     it is reproducible run to run and agrees with the unsplit kernel within the TF32 tolerance."""
     from oxionnx_b200.graph import Graph, Node
     rng = np.random.default_rng(77)
-    wq = {"w": rng.integers(-127, 128, (256, 512, 3, 3)).astype(np.float32), "ws": rng.uniform(0.001, 0.01, 256).astype(np.float32),
+    wq = {"w": rng.integers(-127, 128, (256, 1024, 3, 3)).astype(np.float32), "ws": rng.uniform(0.001, 0.01, 256).astype(np.float32),
           "wz": np.zeros(256, np.float32), "b": rng.integers(-1000, 1000, 256).astype(np.float32), "xs": np.float32([0.02]), "z0": np.float32([0]),
-          "z128": np.float32([128]), "ys": np.float32([1.5]), "qs": np.float32([0.02])}
+          "z128": np.float32([128]), "ys": np.float32([2.0]), "qs": np.float32([0.02])}
     gq = Graph(nodes=[Node("QuantizeLinear", "q", ["x", "qs", "z0"], ["xq"], {}),
                       Node("QLinearConv", "conv", ["xq", "xs", "z0", "w", "ws", "wz", "ys", "z128", "b"], ["yq"], {"pads": [1, 1, 1, 1]}),
                       Node("DequantizeLinear", "dq", ["yq", "ys", "z128"], ["y"], {})], input_names=["x"], output_names=["y"])
-    xq = np.abs(rng.standard_normal((2, 512, 7, 7))).astype(np.float32)
+    xq = np.abs(rng.standard_normal((2, 1024, 7, 7))).astype(np.float32)
     wf = {"w": (rng.standard_normal((512, 256, 3, 3)) * 0.02).astype(np.float32), "b": rng.standard_normal(512).astype(np.float32)}
     gf = Graph(nodes=[Node("Relu", "pre", ["x"], ["x1"], {}), Node("Conv", "conv", ["x1", "w", "b"], ["y"], {"pads": [1, 1, 1, 1], "activation": "relu"})],
                input_names=["x"], output_names=["y"])

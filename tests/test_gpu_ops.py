@@ -90,8 +90,8 @@ QCONV_SHAPES = [
     (5, 64, 16, 16, 64, 3, 1, 1, 128, 0),      # padded with a non-zero zero point: direct kernel
     (2, 3, 20, 20, 16, 7, 2, 3, 128, 0),       # stem geometry: direct kernel
     (1, 512, 4, 4, 1000, 1, 1, 0, 128, 128),   # classifier as a 1x1 convolution
-    (2, 512, 7, 7, 256, 3, 1, 1, 128, 128),    # one row tile, 36 K blocks: K split over several CTAs
-    (3, 256, 9, 9, 96, 3, 1, 1, 0, 0),         # split K with a ragged channel tile and 16-bit lanes
+    (2, 1024, 7, 7, 256, 3, 1, 1, 128, 128),   # one row tile, 72 K blocks: K split over several CTAs
+    (3, 1024, 9, 9, 96, 3, 1, 1, 0, 0),        # split K with a ragged channel tile and 16-bit lanes
 ]
 
 
