@@ -550,21 +550,6 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                : "memory");
 }
 
-// L2 prefetch of one warp's share of a tile's residual lanes (32 rows, `cpw` runs of 128 bytes each).
-template <int BN>
-__device__ __forceinline__ void prefetch_residual_rows(const KParams& p, int tt, int quarter, int lane, int first, int cpw) {
-  const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
-  const long long m = (long long)tile_m * BLOCK_M + quarter * 32 + lane;
-  const int oc0 = tile_n * BN;
-  if (m >= p.M) return;
-  const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;
-  const int end = min(first + cpw, n_chunks);
-  for (int c = first; c < end; ++c) {
-    const float* line = p.residual + (size_t)m * p.OC + oc0 + c * 32;
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
-  }
-}
-
 // ---- epilogue role ------------------------------------------------------------------------
 // Eight warps drain an accumulator: warp w may read the TMEM lanes 32 * (w % 4) .. + 31 (output
 // rows of the tile), and the two warps of a lane quarter split the tile's channel runs in two
@@ -600,14 +585,6 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
     const int m0 = tile_m * BLOCK_M, oc0 = tile_n * BN;
     const uint32_t buf = local & 1u;
-    if constexpr (VARIANT >= V_F32_RES && VARIANT < V_DEQUANT) {
-      // The residual lanes are read with plain loads right before their use, one 128-byte line per thread and
-      // run: bring the lines of this CTA's next tile (and, at the start, of this one) into L2 a whole tile
-      // ahead, so that those loads pay the L2 latency instead of the DRAM latency.
-      if (local == 0) prefetch_residual_rows<BN>(p, tt, quarter, lane, first, CPW);
-      const int tn = t + (int)gridDim.x;
-      if (tn < total_tiles) prefetch_residual_rows<BN>(p, p.splits > 1 ? tn / p.splits : tn, quarter, lane, first, CPW);
-    }
     if (ew == 0) OXB_TRACE(local, 6);
     bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local >> 1) & 1u, abortp);
     if (ew == 0) OXB_TRACE(local, 7);

@@ -146,9 +146,11 @@ Session::~Session() {
     if (f == 1 && pipe_double_)
       for (void* p : fl.in_dev) cudaFree(p);
     for (float* p : fl.out_host) cudaFreeHost(p);
+    for (void* p : fl.out_dev) cudaFree(p);
     if (fl.err_host) cudaFreeHost(fl.err_host);
   }
   if (copy_stream_) cudaStreamDestroy(copy_stream_);
+  if (down_stream_) cudaStreamDestroy(down_stream_);
   for (auto& g : graphs_)
     if (g.exec) cudaGraphExecDestroy(g.exec);
 }
@@ -350,7 +352,10 @@ void Session::rebind_input(int value_index, void* ptr) {
 
 void Session::prepare_pipeline() {
   if (pipe_ready_) return;
+  // uploads and downloads have a stream each: a download waits for its run, and an upload queued behind it
+  // in the same stream would wait for that run too instead of overlapping it
   OXB_CUDA(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+  OXB_CUDA(cudaStreamCreateWithFlags(&down_stream_, cudaStreamNonBlocking));
   // A second input buffer is only safe when no step has the input's address built into a tensor map:
   // the tensor-core steps are the ones that do, so none of them may read an input (or an alias of one).
   pipe_double_ = external_bind_.empty();
@@ -377,6 +382,9 @@ void Session::prepare_pipeline() {
       float* p = nullptr;
       OXB_CUDA(cudaMallocHost(&p, std::max<size_t>((size_t)values_[out.second].numel() * 4, 4)));
       fl.out_host.push_back(p);
+      void* d = nullptr;
+      OXB_CUDA(cudaMalloc(&d, std::max<size_t>((size_t)values_[out.second].numel() * 4, 256)));
+      fl.out_dev.push_back(d);
     }
     OXB_CUDA(cudaMallocHost(&fl.err_host, sizeof(int)));
   }
@@ -406,19 +414,23 @@ void Session::submit(const oxb200_operand* feeds, uint32_t n, bool profile) {
   }
   OXB_CUDA(cudaEventRecord(fl.up, copy_stream_));
   OXB_CUDA(cudaStreamWaitEvent(main, fl.up, 0));
-  // the previous run's outputs must have left their device buffers before this run overwrites them
-  if (prev.busy) OXB_CUDA(cudaStreamWaitEvent(main, prev.down, 0));
   run_steps(profile);
-  OXB_CUDA(cudaEventRecord(fl.done, main));
-  OXB_CUDA(cudaStreamWaitEvent(copy_stream_, fl.done, 0));
+  // the outputs move to this slot's own device buffers (a device-to-device copy, microseconds), so that the next
+  // run may overwrite the arena while the download is still crossing PCIe
   for (size_t i = 0; i < output_staging_.size(); ++i) {
     const Value& v = values_[output_staging_[i].second];
-    if (v.numel() > 0) OXB_CUDA(cudaMemcpyAsync(fl.out_host[i], v.ptr, (size_t)v.numel() * 4, cudaMemcpyDeviceToHost, copy_stream_));
+    if (v.numel() > 0) OXB_CUDA(cudaMemcpyAsync(fl.out_dev[i], v.ptr, (size_t)v.numel() * 4, cudaMemcpyDeviceToDevice, main));
+  }
+  OXB_CUDA(cudaEventRecord(fl.done, main));
+  OXB_CUDA(cudaStreamWaitEvent(down_stream_, fl.done, 0));
+  for (size_t i = 0; i < output_staging_.size(); ++i) {
+    const Value& v = values_[output_staging_[i].second];
+    if (v.numel() > 0) OXB_CUDA(cudaMemcpyAsync(fl.out_host[i], fl.out_dev[i], (size_t)v.numel() * 4, cudaMemcpyDeviceToHost, down_stream_));
     ctx_->counters.downloads += 1;
     ctx_->counters.download_bytes += (uint64_t)v.numel() * 4;
   }
-  OXB_CUDA(cudaMemcpyAsync(fl.err_host, err_flag_, sizeof(int), cudaMemcpyDeviceToHost, copy_stream_));
-  OXB_CUDA(cudaEventRecord(fl.down, copy_stream_));
+  OXB_CUDA(cudaMemcpyAsync(fl.err_host, err_flag_, sizeof(int), cudaMemcpyDeviceToHost, down_stream_));
+  OXB_CUDA(cudaEventRecord(fl.down, down_stream_));
   fl.busy = true;
   submit_idx_ ^= 1;
 }

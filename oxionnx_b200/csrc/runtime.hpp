@@ -151,11 +151,12 @@ class Session {
     cudaEvent_t up = nullptr, done = nullptr, down = nullptr;
     std::vector<void*> in_dev;       // this slot's device buffer per graph input
     std::vector<float*> out_host;    // pinned staging per graph output
+    std::vector<void*> out_dev;      // device copy of each output, so that the next run need not wait for the download
     int* err_host = nullptr;         // pinned copy of the kernels' error word
   };
   Flight flight_[2];
   int submit_idx_ = 0, collect_idx_ = 0;
-  cudaStream_t copy_stream_ = nullptr;
+  cudaStream_t copy_stream_ = nullptr, down_stream_ = nullptr;  // uploads; downloads
   bool pipe_ready_ = false, pipe_double_ = false;
   void prepare_pipeline();
   void rebind_input(int value_index, void* ptr);
