@@ -227,8 +227,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-int8", action="store_true", help="skip the INT8 ResNet-50 companion measurement of the default workload")
     ap.add_argument("--kernel-path", default="auto", choices=["auto", "direct"])
-    ap.add_argument("--cuda-graph", type=int, default=0, help="1: replay the planned step list as one CUDA graph (OXIONNX_CUDA_GRAPH)")
+    ap.add_argument("--cuda-graph", type=int, default=-1,
+                    help="1: replay the planned step list as one CUDA graph (OXIONNX_CUDA_GRAPH); default: on, except for the six-launch MLP "
+                         "(c1), where a graph launch costs more than the launches it replaces")
     args = ap.parse_args()
+    if args.cuda_graph < 0:
+        args.cuda_graph = 0 if args.workload == "c1" else 1
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))

@@ -1,6 +1,7 @@
 """Times one contraction layer through the planned session (the tensor-core kernel in isolation).
 
   python -m oxionnx_b200.layer_bench f32|i8 N C H W OC K STRIDE PAD [ITERS]
+  python -m oxionnx_b200.layer_bench dql ROWS COLS [ITERS]      (DynamicQuantizeLinear of a [ROWS, COLS] activation)
 
 The layer sits between two cheap glue nodes so that its input and output are device-resident
 activations, exactly as inside a network.  Prints the kernel chosen by the planner, its best
@@ -36,8 +37,29 @@ def build(kind, n, c, h, w, oc, k, stride, pad):
     return Graph(nodes=nodes, input_names=["x"], output_names=["z"]), weights, x
 
 
+def main_dql(argv):
+    rows, cols = int(argv[0]), int(argv[1])
+    iters = int(argv[2]) if len(argv) > 2 else 5
+    nodes = [Node("Relu", "pre", ["x"], ["x1"], {}), Node("DynamicQuantizeLinear", "dq", ["x1"], ["y", "s", "z"], {})]
+    graph = Graph(nodes=nodes, input_names=["x"], output_names=["s", "z"])
+    x = np.random.default_rng(0).standard_normal((rows, cols)).astype(np.float32)
+    sess = Session.builder().with_profiling(True).build_from_graph(graph, {})
+    sess.upload({"x": x})
+    for _ in range(3):
+        sess.run_resident(1)
+    best = 1e9
+    for _ in range(iters):
+        sess.run_resident(1)
+        best = min([best] + [s["ms"] for s in sess.steps() if s["node"] == "dq" and s["ms"] >= 0])
+    n = rows * cols
+    print(f"dynamic_quantize_linear [{rows}, {cols}]: best {best * 1000:.1f} us (two launches)  {9 * n / (best / 1e3) / 1e12:.2f} TB/s at 9 bytes per lane")
+    sess.close()
+
+
 def main(argv):
     kind = argv[0]
+    if kind == "dql":
+        return main_dql(argv[1:])
     n, c, h, w, oc, k, stride, pad = [int(a) for a in argv[1:9]]
     iters = int(argv[9]) if len(argv) > 9 else 5
     graph, weights, x = build(kind, n, c, h, w, oc, k, stride, pad)
