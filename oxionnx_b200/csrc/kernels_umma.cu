@@ -262,6 +262,13 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, naming the registers a pending read lands in: nothing that uses them may be scheduled above it.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 
 // ---- fused epilogue math ------------------------------------------------------------------
 // One variant per (mode, activation, rounding) combination, chosen once per chunk, so that
@@ -600,16 +607,18 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN;
     const int n_chunks = min(BN, p.OC - oc0 + 31) / 32;  // uniform across the CTA
     const int end = min(first + CPW, n_chunks);           // this warp's runs: [first, end)
-    uint32_t va[32], vb[32], w[32];
+    uint32_t va[32], w[32];
 
     auto release = [&]() {  // every TMEM read of this warp for this tile has landed
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
     };
-    auto emit = [&](const uint32_t(&v)[32], int ch) {
+    auto math = [&](const uint32_t(&v)[32], int ch) {
       const float* res = (VARIANT >= V_F32_RES && VARIANT < V_DEQUANT && row_ok) ? p.residual + (size_t)m * p.OC + oc0 + ch * 32 : nullptr;
       epilogue_chunk<VARIANT>(p, v, xz, oc0 + ch * 32, esz, res, w);
+    };
+    auto store = [&](int ch) {
       if (p.out_tma) {
         const int in_group = (ch - first) % cpg;
         if (in_group == 0) {
@@ -629,6 +638,10 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
       } else if (row_ok) {
         store_direct(w, (uint8_t*)p.out + ((size_t)m * p.OC + oc0 + ch * 32) * esz, esz, min(32, p.OC - (oc0 + ch * 32)));
       }
+    };
+    auto emit = [&](const uint32_t(&v)[32], int ch) {
+      math(v, ch);
+      store(ch);
     };
 
     if (p.dbg == 1 || first >= end) {  // timing experiment without epilogue work, or no run of this tile is ours
@@ -685,20 +698,18 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     }
     if constexpr (SPLIT) continue;  // (not reached)
     tmem_ld32_nowait(taddr + (uint32_t)first * 32u, va);
-    tmem_ld_wait();
-    // one copy of the run's code in the loop (the instruction cache, not the 32 register moves, is
-    // what this loop is short of): the next run is in TMEM transit while this one is processed
+    tmem_ld_wait_for(va);
+    // one copy of the run's code in the loop (the instruction cache is what this loop is short of); a run's math
+    // leaves its packed words in `w`, so the next run's TMEM read can land in the same registers while the words
+    // are staged and handed to the TMA store (no second register set, no copies between the two)
 #pragma unroll 1
     for (int c = first; c < end; ++c) {
       const bool more = c + 1 < end;
-      if (more) tmem_ld32_nowait(taddr + (uint32_t)(c + 1) * 32u, vb);
+      math(va, c);
+      if (more) tmem_ld32_nowait(taddr + (uint32_t)(c + 1) * 32u, va);
       else release();
-      emit(va, c);
-      if (more) {
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) va[j] = vb[j];
-      }
+      store(c);
+      if (more) tmem_ld_wait_for(va);
     }
     if (ew == 0) OXB_TRACE(local, 8);
     if (ew == EPI_WARPS - 1) OXB_TRACE(local, 9);
