@@ -86,6 +86,9 @@ void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaS
 // Sequential f32 sum over the plane in (h, w) order, then one division: the order the
 // reference's global_avg_pool uses, so the result is bit-identical.
 void global_avg_pool(const TensorRef& x, const TensorRef& y, int round_tf32, cudaStream_t s);
+// The same sum over an 8-bit NHWC tensor dequantised on the fly with per-tensor parameters: (x - zp) * scale per
+// lane, added in (h, w) order, i.e. DequantizeLinear followed by GlobalAveragePool without the f32 tensor between them.
+void global_avg_pool_dequant(const TensorRef& x, const TensorRef& y, float scale, float zp, int round_tf32, cudaStream_t s);
 // OxiInstanceNorm over (n, c) planes, two-pass variance about the mean; optional fused
 // per-sample modulation y = norm * scale[n,c] + shift[n,c] (both may be NULL).
 void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const float* scale_nc, const float* shift_nc, int relu, int round_tf32,

@@ -172,6 +172,26 @@ __global__ void dequantize_kernel(const void* x, DT xdt, Layout xl, void* y, Lay
   }
 }
 
+// Per-tensor parameters, 8-bit lanes, same element order on both sides: four lanes per thread, a 4-byte load and
+// a 16-byte store, both fully coalesced.  The byte is dropped into the mantissa of 2^23 (exact integer to float
+// without the conversion pipe); (v - zp) * scale is rounded as in the generic kernel.
+__global__ void dequantize_vec4_kernel(const uint32_t* __restrict__ x, bool is_signed, float4* __restrict__ y, const float* __restrict__ scale,
+                                       const float* __restrict__ zp, int64_t n4) {
+  const float s = scale[0], z = zp ? zp[0] : 0.f;
+  const uint32_t flip = is_signed ? 0x80808080u : 0u;
+  const float off = is_signed ? 8388736.0f : 8388608.0f;  // 2^23 (+ 128 for the flipped sign bit)
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t w = __ldg(x + i) ^ flip;
+    float f[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float v = __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440 + e)), off);
+      f[e] = __fmul_rn(__fsub_rn(v, z), s);
+    }
+    y[i] = make_float4(f[0], f[1], f[2], f[3]);
+  }
+}
+
 // ---- DynamicQuantizeLinear --------------------------------------------------------------
 // Order-independent min/max: floats are mapped to a monotone unsigned key so atomicMin/Max
 // on integers gives the exact float extrema.
@@ -535,6 +555,48 @@ __global__ void max_pool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y,
   }
 }
 
+// Four channels of one image per thread over 8-bit lanes: every lane is dequantised as DequantizeLinear does,
+// (x - zp) * scale with each operation rounded, and added in (h, w) order as the f32 kernel adds.
+__global__ void global_avg_pool_nhwc_q_kernel(const uint32_t* __restrict__ x, bool is_signed, float scale, float zp, float4* __restrict__ y, Dims4 d,
+                                              int rtf32) {
+  const int64_t c4n = d.C / 4, total = d.N * c4n, hw = d.H * d.W;
+  const uint32_t flip = is_signed ? 0x80808080u : 0u;
+  const float off = is_signed ? 8388736.0f : 8388608.0f;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c4 = o % c4n, n = o / c4n;
+    const uint32_t* p = x + n * hw * c4n + c4;
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    int64_t i = 0;
+    for (; i + 8 <= hw; i += 8) {
+      uint32_t w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w[k] = __ldg(p + (i + k) * c4n) ^ flip;
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float v = __fsub_rn(__uint_as_float(__byte_perm(w[k], 0x4B000000u, 0x7440 + e)), off);
+          sum[e] = __fadd_rn(sum[e], __fmul_rn(__fsub_rn(v, zp), scale));
+        }
+    }
+    for (; i < hw; ++i) {
+      const uint32_t w = __ldg(p + i * c4n) ^ flip;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float v = __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440 + e)), off);
+        sum[e] = __fadd_rn(sum[e], __fmul_rn(__fsub_rn(v, zp), scale));
+      }
+    }
+    float r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      r[e] = __fdiv_rn(sum[e], (float)hw);
+      if (rtf32) r[e] = round_tf32(r[e]);
+    }
+    y[o] = make_float4(r[0], r[1], r[2], r[3]);
+  }
+}
+
 // 16 bytes of channels per thread: four floats, or sixteen 8-bit lanes reduced with the SIMD
 // byte-max instructions.  KIND 0 = f32, 1 = u8, 2 = i8.
 template <int KIND>
@@ -583,7 +645,16 @@ __global__ void global_avg_pool_nhwc_kernel(const float* __restrict__ x, float* 
     const float* p = x + n * d.H * d.W * d.C + c;
     float sum = 0.f;
     int64_t hw = d.H * d.W;
-    for (int64_t i = 0; i < hw; ++i) sum = __fadd_rn(sum, p[i * d.C]);
+    // the additions keep the reference's (h, w) order; the loads of eight positions are issued together
+    int64_t i = 0;
+    for (; i + 8 <= hw; i += 8) {
+      float v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = p[(i + k) * d.C];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) sum = __fadd_rn(sum, v[k]);
+    }
+    for (; i < hw; ++i) sum = __fadd_rn(sum, p[i * d.C]);
     float r = __fdiv_rn(sum, (float)hw);
     y[o] = rtf32 ? round_tf32(r) : r;
   }
@@ -933,6 +1004,74 @@ __global__ void s2d_window_pack_kernel(const void* src, DT sdt, Layout sl, Dims4
   }
 }
 
+// round_ties_even(x / s) without the division on the common path: the quotient from the correctly rounded
+// reciprocal r with one exact-remainder correction is within one unit in the last place of the IEEE quotient
+// (s a normal number in 2^-100 .. 2^100, |q| < 1024, so that a unit is at most 2^-14); only a q closer than
+// 2^-13 to a tie k + 1/2 could round differently, and those lanes, like every lane outside the proven range,
+// take the division.
+__device__ __forceinline__ float quotient_rint(float x, float s, float r, bool safe) {
+  if (safe) {
+    const float q0 = __fmul_rn(x, r);
+    const float q = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+    if (fabsf(q) < 1024.0f) {
+      const float ri = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+      if (fabsf(__fsub_rn(q, ri)) <= 0.49987793f) return ri;
+    }
+  }
+  return rintf(__fdiv_rn(x, s));
+}
+
+// The same packing for the common source: f32 NCHW with an even width.  The two horizontally adjacent pixels of
+// a 2x2 block come from one 8-byte load, and consecutive threads read consecutive blocks (fully coalesced).
+template <int C>
+__global__ void s2d_window_pack_nchw_f32_kernel(const float* __restrict__ src, Dims4 d, void* dst, DT ddt, int pad_left, int wp, int sub, S2dQuant q,
+                                                float rcp, bool safe, int64_t total) {
+  const int64_t H2 = d.H / 2, W2 = d.W / 2;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t xw = o % wp;
+    int64_t t = o / wp;
+    const int64_t y = t % H2;
+    const int64_t n = t / H2;
+    const int64_t x2 = xw - pad_left;
+    float v[16];
+#pragma unroll
+    for (int cp = 0; cp < 16; ++cp) v[cp] = 0.f;
+    if (x2 >= 0 && x2 < W2) {
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const float* plane = src + ((n * C + c) * d.H + 2 * y) * d.W + 2 * x2;
+        const float2 top = __ldg(reinterpret_cast<const float2*>(plane));
+        const float2 bot = __ldg(reinterpret_cast<const float2*>(plane + d.W));
+        v[0 * C + c] = top.x;
+        v[1 * C + c] = top.y;
+        v[2 * C + c] = bot.x;
+        v[3 * C + c] = bot.y;
+      }
+#pragma unroll
+      for (int cp = 0; cp < 4 * C; ++cp) {
+        float f = v[cp];
+        if (q.quantize) f = fminf(fmaxf(__fadd_rn(quotient_rint(f, q.scale, rcp, safe), q.zp), q.lo), q.hi);
+        v[cp] = f - (float)sub;
+      }
+    }
+    if (ddt == DT::F32) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ((float4*)dst)[o * 4 + j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      const float lo = ddt == DT::U8 ? 0.f : -128.f, hi = ddt == DT::U8 ? 255.f : 127.f;
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w[j] = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          w[j] |= (__float_as_uint(__fadd_rn(fminf(fmaxf(v[4 * j + e], lo), hi), 12582912.0f)) & 0xffu) << (8 * e);
+      }
+      ((uint4*)dst)[o] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 // y = x[start0 : start0 + Y0, start1 : ..., ...] over up to four logical (row-major) axes, unit steps.
 __global__ void slice_kernel(const void* x, void* y, int es, Dims4 xd, Dims4 yd, Dims4 start, int64_t total) {
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
@@ -1180,6 +1319,19 @@ void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, i
   if (total == 0) return;
   if (!(dst_dt == DT::F32 || dst_dt == DT::U8 || dst_dt == DT::I8) || 4 * src.d.C > 16) OXB_FAIL("s2d_window_pack: unsupported operand");
   if (q.quantize && src.dt != DT::F32) OXB_FAIL("s2d_window_pack: quantisation needs an f32 source");
+  if (src.dt == DT::F32 && src.layout == Layout::PLAIN && src.d.W % 2 == 0 && ((uintptr_t)src.ptr & 7) == 0 && src.d.C >= 1 && src.d.C <= 4) {
+    const bool safe = q.quantize && q.scale >= 7.8886090522101181e-31f && q.scale <= 1.2676506002282294e+30f;
+    const float rcp = safe ? 1.0f / q.scale : 0.f;
+    const int g = grid_for(total);
+    const float* x = (const float*)src.ptr;
+    switch ((int)src.d.C) {
+      case 1: s2d_window_pack_nchw_f32_kernel<1><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
+      case 2: s2d_window_pack_nchw_f32_kernel<2><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
+      case 3: s2d_window_pack_nchw_f32_kernel<3><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
+      default: s2d_window_pack_nchw_f32_kernel<4><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
+    }
+    return;
+  }
   s2d_window_pack_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, pad_left, wp, sub, q, total);
 }
 
@@ -1219,6 +1371,12 @@ void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scal
                        cudaStream_t s) {
   int64_t total = y.d.numel();
   if (total == 0) return;
+  const bool same_order = x.layout == y.layout || y.d.C == 1 || y.d.H * y.d.W == 1;
+  if ((x.dt == DT::U8 || x.dt == DT::I8) && n_scale == 1 && n_zp <= 1 && same_order && total % 4 == 0 && ((uintptr_t)x.ptr & 3) == 0 &&
+      ((uintptr_t)y.ptr & 15) == 0) {
+    dequantize_vec4_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((const uint32_t*)x.ptr, x.dt == DT::I8, (float4*)y.ptr, scale, zp, total / 4);
+    return;
+  }
   dequantize_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, x.dt, x.layout, y.ptr, y.layout, y.d, scale, n_scale, zp, n_zp, total);
 }
 
@@ -1287,6 +1445,14 @@ void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaS
   else if (x.dt == DT::U8) max_pool_nhwc_kernel<uint8_t><<<g, kThreads, 0, s>>>((const uint8_t*)x.ptr, (uint8_t*)y.ptr, x.d, ps, total, 0);
   else if (x.dt == DT::I8) max_pool_nhwc_kernel<int8_t><<<g, kThreads, 0, s>>>((const int8_t*)x.ptr, (int8_t*)y.ptr, x.d, ps, total, -128);
   else OXB_FAIL("max_pool: unsupported storage type");
+}
+
+void global_avg_pool_dequant(const TensorRef& x, const TensorRef& y, float scale, float zp, int round_tf32_flag, cudaStream_t s) {
+  if (!(x.dt == DT::U8 || x.dt == DT::I8) || x.d.C % 4 != 0 || ((uintptr_t)x.ptr & 3) != 0 || ((uintptr_t)y.ptr & 15) != 0)
+    OXB_FAIL("global_avg_pool_dequant: unsupported operand");
+  const int64_t total4 = x.d.N * x.d.C / 4;
+  if (total4 == 0) return;
+  global_avg_pool_nhwc_q_kernel<<<grid_for(total4, 128), 128, 0, s>>>((const uint32_t*)x.ptr, x.dt == DT::I8, scale, zp, (float4*)y.ptr, x.d, round_tf32_flag);
 }
 
 void global_avg_pool(const TensorRef& x, const TensorRef& y, int round_tf32_flag, cudaStream_t s) {

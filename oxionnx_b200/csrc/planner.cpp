@@ -715,6 +715,13 @@ void Planner::plan_dequantize(const NodeDef& n) {
     dzp = (const float*)C.resident_form(in_name(n, 2), "raw_f32", zp->data.size() * 4, [zp](void* p) { std::memcpy(p, zp->data.data(), zp->data.size() * 4); },
                                         cacheable_const(in_name(n, 2)));
   Step& st = add_step(n, "dequantize_linear", 2, {xi}, {yi});
+  if (ns == 1 && nz <= 1 && native4 && V(xi).shape.size() == 4 && (V(xi).dt == DT::U8 || V(xi).dt == DT::I8)) {
+    Value& yv = V(yi);
+    yv.dq_src = xi;
+    yv.dq_step = (int)S.steps_.size() - 1;
+    yv.dq_scale = scale->data[0];
+    yv.dq_zp = zp ? zp->data[0] : 0.f;
+  }
   st.work = (double)V(xi).bytes + (double)V(yi).bytes;
   st.launch = [this, xr, yr, xi, yi, dscale, ns, dzp, nz](cudaStream_t s) {
     k::dequantize_linear(bound(xr, xi), bound(yr, yi), dscale, ns, dzp, nz, s);
@@ -1947,6 +1954,33 @@ void Planner::plan_global_avg_pool(const NodeDef& n) {
   check_attrs(n, {});
   int xi = value_of(in_name(n, 0));
   if (V(xi).shape.size() != 4 || V(xi).dt != DT::F32) OXB_DECLINE("GlobalAveragePool '%s': needs a rank-4 float input", n.name.c_str());
+  {
+    // DequantizeLinear (per tensor) -> GlobalAveragePool with no other reader of the f32 tensor: the pool reads the
+    // 8-bit lanes and dequantises on the fly, same operations in the same order, and the f32 tensor is never written
+    const Value dv = V(xi);
+    auto it = consumers_.find(dv.name);
+    if (dv.dq_src >= 0 && dv.dq_step == (int)S.steps_.size() - 1 && !C.cfg().keep_intermediates && !graph_outputs_.count(dv.name) &&
+        it != consumers_.end() && it->second.size() == 1 && effective_layout(V(dv.dq_src)) == Layout::NHWC && V(dv.dq_src).shape[1] % 4 == 0) {
+      const int src = dv.dq_src;
+      S.steps_.pop_back();
+      V(xi).producer = -1;
+      const Value sv = V(src);
+      std::vector<int64_t> os = {sv.shape[0], sv.shape[1], 1, 1};
+      int yi = add_value(n.outputs[0], os, DT::F32, Layout::NHWC);
+      int rt = feeds_contraction(n.outputs[0]) ? 1 : 0;
+      TensorRef xr = ref_of(src), yr = ref_of(yi);
+      xr.layout = Layout::NHWC;
+      const float sc = dv.dq_scale, zp = dv.dq_zp;
+      Step& st = add_step(n, "dequantize+global_avg_pool", 2, {src}, {yi});
+      st.work = (double)sv.bytes + (double)V(yi).bytes;
+      st.launch = [this, xr, yr, src, yi, sc, zp, rt](cudaStream_t s) {
+        k::global_avg_pool_dequant(bound(xr, src), bound(yr, yi), sc, zp, rt, s);
+        C.counters.glue_launches++;
+        C.counters.kernel_launches++;
+      };
+      return;
+    }
+  }
   xi = ensure_layout(n, xi, Layout::NHWC);
   const Value xv = V(xi);
   std::vector<int64_t> os = {xv.shape[0], xv.shape[1], 1, 1};

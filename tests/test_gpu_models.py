@@ -119,6 +119,22 @@ def test_resnet_qlinear_small_bit_exact_per_node(path):
     sess.close()
 
 
+def test_resnet_qlinear_fused_session_equals_the_oracle_bit_for_bit():
+    """The session a user gets (no per-node copies): QuantizeLinear inside the stem packing, the residual chains as
+    one kernel each, DequantizeLinear inside GlobalAveragePool; the logits must still be the oracle's, lane for lane."""
+    graph, weights, feeds, _ = models.build_resnet50_qlinear(batch=3, image=64, base=32, classes=48)
+    sess = Session.builder().build_from_graph(graph, weights)
+    f = feeds(3)
+    out = sess.run(f)
+    oracle.set_threads(8)
+    ref = oracle.run_graph(graph, weights, f)
+    assert np.array_equal(out["logits"], ref["logits"])
+    kernels = [s["kernel"] for s in sess.steps()]
+    assert "dequantize+global_avg_pool" in kernels and "quantize+s2d_window_pack" in kernels, kernels
+    assert not any(k == "global_avg_pool" for k in kernels)
+    sess.close()
+
+
 def test_full_size_properties_resnet_qlinear():
     """At the benchmark's per-image size the oracle is too slow for a full comparison, so the
     run is pinned through size-independent properties: the tensor-core path and the direct
