@@ -44,7 +44,8 @@ void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scal
                        cudaStream_t s);
 // DynamicQuantizeLinear: params[0] = y_scale, params[1] = y_zero_point (f32 lanes on the
 // device); `scratch` is 2 floats used for the min/max reduction.
-void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s);
+// `have_minmax`: the producer of x has already merged x's extrema into the scratch keys; only the second pass runs.
+void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s, bool have_minmax = false);
 // Puts a freshly allocated scratch block (at least 12 bytes) into the state dynamic_quantize_linear expects.
 void dynamic_quantize_scratch_init(float* scratch);
 
@@ -112,7 +113,7 @@ void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstrid
 // softmax_rows optionally applies x * scale[0] and + mask[row / rows_per_mask][:] first (fused Mul / Add producers).
 void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, int round_tf32,
                   cudaStream_t s);
-void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s);
+void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s, unsigned int* minmax_keys = nullptr);
 // Slice with unit steps over logical (row-major) axes padded to four: y[i] = x[i + start], dims as (N, C, H, W).
 void slice_rows(const void* x, void* y, DT dt, const Dims4& xd, const Dims4& yd, const Dims4& start, cudaStream_t s);
 

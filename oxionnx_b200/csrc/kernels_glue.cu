@@ -1198,8 +1198,9 @@ __global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restri
 // LayerNormalization over the last axis, one warp per row (nn/normalization.rs layer_norm_into):
 // mean = sum / n, var = sum((x - mean)^2) / n, inv_std = 1 / sqrt(var + eps), (x - mean) * inv_std * scale [+ bias].
 __global__ void layer_norm_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int64_t n, const float* __restrict__ scale,
-                                       const float* __restrict__ bias, float eps) {
+                                       const float* __restrict__ bias, float eps, uint32_t* minmax_keys) {
   const int lane = threadIdx.x & 31;
+  float mn = INFINITY, mx = -INFINITY;  // extrema of what this thread writes (for a DynamicQuantizeLinear reader)
   const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
     const float* px = x + r * n;
@@ -1218,6 +1219,33 @@ __global__ void layer_norm_rows_kernel(const float* __restrict__ x, float* __res
       float v = __fmul_rn(__fmul_rn(__fsub_rn(px[k], mean), inv_std), scale[k]);
       if (bias) v = __fadd_rn(v, bias[k]);
       py[k] = v;
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+  }
+  if (minmax_keys) {  // uniform across the grid
+    for (int off = 16; off > 0; off >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    __shared__ float smn[kThreads / 32], smx[kThreads / 32];
+    const int warp = threadIdx.x >> 5;
+    if (lane == 0) {
+      smn[warp] = mn;
+      smx[warp] = mx;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      mn = lane < kThreads / 32 ? smn[lane] : INFINITY;
+      mx = lane < kThreads / 32 ? smx[lane] : -INFINITY;
+      for (int off = 4; off > 0; off >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      }
+      if (lane == 0) {
+        if (mn != INFINITY) atomicMin(&minmax_keys[0], float_key(mn));
+        if (mx != -INFINITY) atomicMax(&minmax_keys[1], float_key(mx));
+      }
     }
   }
 }
@@ -1380,20 +1408,20 @@ void dequantize_linear(const TensorRef& x, const TensorRef& y, const float* scal
   dequantize_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, x.dt, x.layout, y.ptr, y.layout, y.d, scale, n_scale, zp, n_zp, total);
 }
 
-void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s) {
+void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* params, float* scratch, cudaStream_t s, bool have_minmax) {
   // `scratch` holds {min key, max key, arrival counter}, set to {0xffffffff, 0, 0} when it was allocated
   // (dynamic_quantize_scratch_init) and put back to that by the last block of every apply pass
   int64_t n = x.d.numel();
   uint32_t* keys = (uint32_t*)scratch;
   if ((((uintptr_t)x.ptr) & 15) != 0 || (((uintptr_t)y.ptr) & 3) != 0) {
-    minmax_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, n, keys);
+    if (!have_minmax) minmax_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, n, keys);
     dynq_apply_fused_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n);
     return;
   }
   const int64_t cap = 148 * 8;
   const int64_t b_mm = std::min<int64_t>(cap, std::max<int64_t>(1, (n / 4 + kThreads * 4 - 1) / (kThreads * 4)));
   const int64_t b_ap = std::min<int64_t>(cap, std::max<int64_t>(1, (n / 4 + (kThreads / 32) * 128 - 1) / ((kThreads / 32) * 128)));
-  minmax_wide_kernel<<<(int)b_mm, kThreads, 0, s>>>((const float*)x.ptr, n, keys);
+  if (!have_minmax) minmax_wide_kernel<<<(int)b_mm, kThreads, 0, s>>>((const float*)x.ptr, n, keys);
   dynq_apply_wide_kernel<<<(int)b_ap, kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n);
 }
 
@@ -1534,9 +1562,10 @@ void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float
   softmax_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, mask, rows_per_mask > 0 ? rows_per_mask : 1, round_tf32_flag);
 }
 
-void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s) {
+void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s,
+                     unsigned int* minmax_keys) {
   if (rows * n == 0) return;
-  layer_norm_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, bias, eps);
+  layer_norm_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, bias, eps, minmax_keys);
 }
 
 void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s) {

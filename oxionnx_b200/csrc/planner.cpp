@@ -757,12 +757,21 @@ void Planner::plan_dynamic_quantize(const NodeDef& n) {
   Dims4 d{V(xi).numel(), 1, 1, 1};
   TensorRef xr{nullptr, DT::F32, Layout::PLAIN, d}, yr{nullptr, DT::U8, Layout::PLAIN, d};
   std::vector<int> writes = {yi, pi};
-  Step& st = add_step(n, "dynamic_quantize_linear", 2, {xi}, writes);
-  st.work = 2.0 * (double)V(xi).bytes + (double)V(yi).bytes;
-  st.launch = [this, xr, yr, xi, yi, pi, scratch](cudaStream_t s) {
-    k::dynamic_quantize_linear(bound(xr, xi), bound(yr, yi), (float*)V(pi).ptr, scratch, s);
-    C.counters.glue_launches += 4;
-    C.counters.kernel_launches += 4;
+  // A LayerNormalization that writes x can take x's extrema while it writes (one pass over the tensor saved):
+  // it merges them into this node's keys, which the apply pass resets for the next run as always.
+  bool have_minmax = false;
+  if (!C.cfg().keep_intermediates && V(xi).alias_of < 0 && V(xi).producer >= 0 && V(xi).producer < (int)S.steps_.size() &&
+      S.steps_[V(xi).producer].kernel == "layer_norm_rows" && V(xi).minmax_keys == nullptr) {
+    V(xi).minmax_keys = scratch;
+    have_minmax = true;
+  }
+  Step& st = add_step(n, have_minmax ? "dynamic_quantize_linear (extrema from the producer)" : "dynamic_quantize_linear", 2, {xi}, writes);
+  st.work = (have_minmax ? 1.0 : 2.0) * (double)V(xi).bytes + (double)V(yi).bytes;
+  st.launch = [this, xr, yr, xi, yi, pi, scratch, have_minmax](cudaStream_t s) {
+    k::dynamic_quantize_linear(bound(xr, xi), bound(yr, yi), (float*)V(pi).ptr, scratch, s, have_minmax);
+    const uint64_t launched = have_minmax ? 1 : 2;
+    C.counters.glue_launches += launched;
+    C.counters.kernel_launches += launched;
   };
   // the zero-point alias points one lane further
   if (zi >= 0) {
@@ -2532,7 +2541,7 @@ void Planner::plan_layer_norm(const NodeDef& n) {
   Step& st = add_step(n, "layer_norm_rows", 2, {xi}, {yi});
   st.work = 2.0 * (double)xv.bytes;
   st.launch = [this, xi, yi, rows, len, dscale, dbias, eps](cudaStream_t s) {
-    k::layer_norm_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, dscale, dbias, eps, s);
+    k::layer_norm_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, dscale, dbias, eps, s, (unsigned int*)V(yi).minmax_keys);
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };

@@ -78,6 +78,9 @@ struct Value {
   float q_scale = 1.f, q_zp = 0.f, q_lo = 0.f, q_hi = 255.f;
   // set on the output of a per-tensor DequantizeLinear of an 8-bit rank-4 value: a consumer that can read the
   // 8-bit lanes itself may drop that step (dq_step) and read dq_src
+  // when set: the step that writes this value also merges the value's minimum and maximum into these two ordered
+  // keys (the scratch of the DynamicQuantizeLinear that reads it, which then skips its own first pass)
+  void* minmax_keys = nullptr;
   int dq_src = -1, dq_step = -1;
   float dq_scale = 1.f, dq_zp = 0.f;
   int64_t numel() const { return prod(shape); }
