@@ -64,7 +64,7 @@ def measured_peaks():
 # DRAM bytes (read + written) per launch of the tensor-core kernel, averaged over the launches of one
 # step: dram__bytes_read.sum + dram__bytes_write.sum from the ncu launch lists summarised under profiles/
 # (launch_list_resnet50_f32_b32.md, launch_list_resnet50_int8_b1024.md).  None: not captured.
-NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.33e6, "c5": 351.58e6, "c1": None, "c3": None, "c4": None}
+NCU_TRAFFIC_PER_LAUNCH = {"c2": 43.35e6, "c5": 351.83e6, "c1": None, "c3": None, "c4": None}
 
 
 def build_workload(key, batch):
