@@ -231,6 +231,9 @@ struct UmmaPlan;
 UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt, void* out, const ConvShape& cs, const Epilogue& e, int kind,
                            std::string* why);
 void umma_plan_destroy(UmmaPlan* p);
+// After a launch that gave up (error word set): puts a split-K plan's arrival counters back to zero, so that the
+// next launch does not inherit a half-counted tile.  A no-op for plans that do not split K.
+void umma_plan_reset_after_error(UmmaPlan* p);
 void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s);
 const char* umma_plan_desc(const UmmaPlan* p);
 // Re-point a plan at new buffers (arena moved) is not supported: plans are rebuilt.

@@ -1492,6 +1492,11 @@ void umma_plan_destroy(UmmaPlan* p) {
   if (p->ws_count) cudaFree(p->ws_count);
   delete p;
 }
+void umma_plan_reset_after_error(UmmaPlan* p) {
+  if (!p || !p->ws_count) return;
+  const size_t cnt = (size_t)p->kp.m_tiles * p->kp.n_tiles * EPI_WARPS * 4;
+  (void)cudaMemset(p->ws_count, 0, cnt * sizeof(unsigned int));
+}
 const char* umma_plan_desc(const UmmaPlan* p) { return p->desc; }
 
 void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {

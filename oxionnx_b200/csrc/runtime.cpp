@@ -171,6 +171,7 @@ int Session::check_error_flag() {
   if (flag != 0) {
     int zero = 0;
     OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    for (auto* p : umma_plans_) k::umma_plan_reset_after_error(p);
   }
   return flag;
 }
@@ -451,6 +452,8 @@ void Session::collect(oxb200_result* fetches, uint32_t n) {
   if (*fl.err_host != 0) {
     const int flag = *fl.err_host, zero = 0;
     OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    OXB_CUDA(cudaStreamSynchronize(ctx_->stream()));
+    for (auto* p : umma_plans_) k::umma_plan_reset_after_error(p);
     raise(OXB200_FAILED, "a kernel reported code %d during a pipelined run; results are not valid", flag);
   }
   for (uint32_t i = 0; i < n; ++i) {
