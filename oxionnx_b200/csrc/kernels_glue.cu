@@ -490,7 +490,7 @@ __global__ void binary_vec4_kernel(const float4* __restrict__ a, const float4* _
 __device__ __forceinline__ float erf_poly(float x) {
   const float sign = x >= 0.0f ? 1.0f : -1.0f;
   x = fabsf(x);
-  const float t = __fdiv_rn(1.0f, __fadd_rn(1.0f, __fmul_rn(0.3275911f, x)));
+  const float t = __frcp_rn(__fadd_rn(1.0f, __fmul_rn(0.3275911f, x)));  // the correctly rounded 1 / d, as the division gives
   float p = __fadd_rn(-1.4531521f, __fmul_rn(t, 1.0614054f));
   p = __fadd_rn(1.4214138f, __fmul_rn(t, p));
   p = __fadd_rn(-0.28449672f, __fmul_rn(t, p));
