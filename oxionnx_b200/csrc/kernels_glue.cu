@@ -209,9 +209,10 @@ __global__ void minmax_init_kernel(uint32_t* keys) {
   keys[1] = 0u;           // running max key
 }
 
-__global__ void minmax_kernel(const float* __restrict__ x, int64_t n, uint32_t* keys) {
+// `vec` = 0: x is not 16-byte aligned, every lane goes through the scalar loop.
+__global__ void minmax_kernel(const float* __restrict__ x, int64_t n, uint32_t* keys, int vec) {
   float mn = INFINITY, mx = -INFINITY;
-  int64_t n4 = n / 4;
+  int64_t n4 = vec ? n / 4 : 0;
   const float4* x4 = (const float4*)x;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
     float4 v = x4[i];
@@ -261,7 +262,7 @@ __global__ void dynq_params_kernel(const uint32_t* keys, float* params) {
 
 __global__ void dynq_apply_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, const float* params, int64_t n) {
   float s = params[0], z = params[1];
-  int64_t n4 = n / 4;
+  int64_t n4 = n / 4;  // the entry point that launches this kernel has checked the alignment of x (16) and y (4)
   const float4* x4 = (const float4*)x;
   uint32_t* y4 = (uint32_t*)y;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
@@ -286,7 +287,7 @@ __global__ void dynq_apply_kernel(const float* __restrict__ x, uint8_t* __restri
 // operations as dynq_params_kernel, so every block gets the same two values), block 0 publishes them for the
 // consumers, and the last block to finish puts the keys back to their identity values for the next call: two
 // launches per DynamicQuantizeLinear instead of four.  keys[2] is the arrival counter.
-__global__ void dynq_apply_fused_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, uint32_t* keys, float* params, int64_t n) {
+__global__ void dynq_apply_fused_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, uint32_t* keys, float* params, int64_t n, int vec) {
   const float max_x = fmaxf(key_float(keys[1]), 0.f);
   const float min_x = fminf(key_float(keys[0]), 0.f);
   const float span = (max_x == min_x) ? 1.0f : __fsub_rn(max_x, min_x);
@@ -296,7 +297,7 @@ __global__ void dynq_apply_fused_kernel(const float* __restrict__ x, uint8_t* __
     params[0] = s;
     params[1] = z;
   }
-  const int64_t n4 = n / 4;
+  const int64_t n4 = vec ? n / 4 : 0;  // vec = 0: x or y is not aligned for vector accesses, the scalar loop takes every lane
   const float4* x4 = (const float4*)x;
   uint32_t* y4 = (uint32_t*)y;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
@@ -1414,8 +1415,9 @@ void dynamic_quantize_linear(const TensorRef& x, const TensorRef& y, float* para
   int64_t n = x.d.numel();
   uint32_t* keys = (uint32_t*)scratch;
   if ((((uintptr_t)x.ptr) & 15) != 0 || (((uintptr_t)y.ptr) & 3) != 0) {
-    if (!have_minmax) minmax_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, n, keys);
-    dynq_apply_fused_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n);
+    // operands that are not aligned for 16-byte loads / 4-byte stores: the same arithmetic, one lane per access
+    if (!have_minmax) minmax_kernel<<<grid_for(n), kThreads, 0, s>>>((const float*)x.ptr, n, keys, 0);
+    dynq_apply_fused_kernel<<<grid_for(n), kThreads, 0, s>>>((const float*)x.ptr, (uint8_t*)y.ptr, keys, params, n, 0);
     return;
   }
   const int64_t cap = 148 * 8;
@@ -1623,6 +1625,10 @@ extern "C" int oxb200_dynamic_quantize_linear_noalloc(int device_ordinal, const 
     return fail(buf);
   }
   if (device_ordinal < 0 || device_ordinal >= kNoAllocMaxDevices) return fail("dynamic_quantize_linear_noalloc: device ordinal out of range");
+  // the kernels read x in 16-byte pieces and write y in 4-byte words: a sub-buffer at an odd offset would fault on the device
+  if (((uintptr_t)x_device & 15) != 0) return fail("dynamic_quantize_linear_noalloc: x_device must be 16-byte aligned");
+  if (((uintptr_t)y_device & 3) != 0) return fail("dynamic_quantize_linear_noalloc: y_device must be 4-byte aligned");
+  if (((uintptr_t)scale_zp_device & 3) != 0) return fail("dynamic_quantize_linear_noalloc: scale_zp_device must be 4-byte aligned");
   int previous = -1;
   if (cudaGetDevice(&previous) != cudaSuccess) previous = -1;
   cudaError_t e = cudaSetDevice(device_ordinal);
@@ -1645,7 +1651,7 @@ extern "C" int oxb200_dynamic_quantize_linear_noalloc(int device_ordinal, const 
   cudaStream_t s = (cudaStream_t)cuda_stream;
   const int64_t count = (int64_t)n;
   minmax_init_kernel<<<1, 1, 0, s>>>(scratch);  // the shared words start every call from their identity values
-  minmax_kernel<<<grid_for(count / 4 + 1), kThreads, 0, s>>>(x_device, count, scratch);
+  minmax_kernel<<<grid_for(count / 4 + 1), kThreads, 0, s>>>(x_device, count, scratch, 1);
   dynq_params_kernel<<<1, 1, 0, s>>>(scratch, scale_zp_device);
   dynq_apply_kernel<<<grid_for(count / 4 + 1), kThreads, 0, s>>>(x_device, y_device, scale_zp_device, count);
   e = cudaGetLastError();

@@ -5,7 +5,8 @@ inside another runtime's arena) call oxb200_dynamic_quantize_linear_noalloc with
 already own; its reduction scratch is a static array inside the library.  The test calls it
 twice in a row through the C ABI -- the second call with different data, which would expose
 stale contents of the shared scratch -- and requires the quantised lanes, the scale and the zero
-point to equal, bit for bit, what the DynamicQuantizeLinear node of oxb200_dispatch produces.
+point to equal, bit for bit, what the DynamicQuantizeLinear node of oxb200_dispatch produces and
+what the CPU oracle (the restatement of the reference's operator) produces.
 This file is named so that pytest collects it last.
 """
 import ctypes
@@ -13,6 +14,7 @@ import ctypes
 import numpy as np
 import pytest
 
+import oracle
 from oxionnx_b200 import _ffi
 from oxionnx_b200.graph import Node
 from oxionnx_b200 import session as S
@@ -50,6 +52,10 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         got_p = pd.cpu().numpy()
         assert np.array_equal(got_y, want_y)
         assert got_p[0] == np.float32(want_scale) and got_p[1] == np.float32(want_zp)
+        # and against the CPU oracle (quant_ops/dynamic_quantize.rs:51-93 restated)
+        o_y, o_scale, o_zp = oracle.run_node("DynamicQuantizeLinear", [x], {}, n_outputs=3)
+        assert np.array_equal(got_y, o_y)
+        assert got_p[0] == np.float32(o_scale) and got_p[1] == np.float32(o_zp)
     ctx.close()
 
 
@@ -60,3 +66,14 @@ def test_no_alloc_entry_point_rejects_oversized_and_null_arguments():
     assert "exceed the maximum" in lib.oxb200_last_error(None).decode()
     st = lib.oxb200_dynamic_quantize_linear_noalloc(0, None, 16, ctypes.c_void_p(256), ctypes.c_void_p(256), None)
     assert st == _ffi.FAILED
+
+
+def test_no_alloc_entry_point_rejects_misaligned_buffers_before_any_launch():
+    """x is read in 16-byte pieces and y written in 4-byte words: a sub-buffer at an odd offset is refused on the
+    host (nothing is launched, so the dummy addresses are never touched)."""
+    lib = _ffi.lib()
+    for x, y, p, word in ((256 + 4, 256, 256, "x_device"), (256, 256 + 1, 256, "y_device"), (256, 256, 256 + 2, "scale_zp_device")):
+        st = lib.oxb200_dynamic_quantize_linear_noalloc(0, ctypes.c_void_p(x), 64, ctypes.c_void_p(y), ctypes.c_void_p(p), None)
+        assert st == _ffi.FAILED
+        msg = lib.oxb200_last_error(None).decode()
+        assert word in msg and "aligned" in msg
