@@ -15,6 +15,9 @@
 #ifdef _OPENMP
 #include <omp.h>
 #endif
+#if defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+#endif
 
 namespace {
 
@@ -738,6 +741,221 @@ void apply_fused_activation(const Attrs& at, float* data, int64_t n) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The reference's float contraction ALGORITHM (float mode 2): what the timed CPU baseline runs.
+//
+// Conv: oxionnx-ops/src/conv/conv2d.rs:246-546 -- a 1x1 / stride-1 / unpadded convolution is one
+// sgemm per (batch, group) over the input viewed as [C, H*W] (conv2d_1x1_into, :1071); every other
+// shape gathers an im2col column matrix [C/g*kH*kW, OH*OW] in blocks of at most 64 MiB
+// (IM2COL_WORKSPACE_MAX_BYTES :119, im2col_block_cols :135) and multiplies the filter matrix into
+// it; with more than one (batch, group) job the jobs run in parallel, each with a sequential
+// sgemm (:468-546), otherwise the one job's sgemm is split by rows of the filter matrix
+// (parallel_sgemm :1132, taken when m*k*n >= 64^3 and m >= 2 * threads, :896).  Bias is a separate
+// pass (:441-449), the fused activation another (registry/conv_ops/conv.rs:124-156).  The
+// Winograd branch (:325-346) only takes layers below 4096 work units and is not restated.
+// MatMul / Gemm: one sgemm per batch item, items in parallel from four on (math_typed.rs:334-420).
+//
+// sgemm itself is the third-party crate matrixmultiply 0.3 (Cargo.toml:43, not vendored).  Its
+// published algorithm is restated here: Goto-style blocking (kc = 256, mc = 64, nc = 1024), both
+// operands packed into panels, an 8 x 8 register tile updated with fused multiply-adds (AVX2 + FMA,
+// which that crate selects at run time on x86-64), the K blocks of an output element added in
+// order.  The summation order inside a tile is this file's own, so the result agrees with the
+// reference's to rounding (about 1e-6 relative), not bit for bit.
+// ---------------------------------------------------------------------------------------
+constexpr int64_t kGemmMR = 8, kGemmNR = 8, kGemmKC = 256, kGemmMC = 64, kGemmNC = 1024;
+
+// acc[8][8] += sum_p ap[p][0..8] (x) bp[p][0..8]; ap and bp are packed panels of kc steps.
+inline void gemm_micro_8x8(int64_t kc, const float* ap, const float* bp, float* acc /* 64 */) {
+#if defined(__AVX2__) && defined(__FMA__)
+  __m256 r0 = _mm256_setzero_ps(), r1 = r0, r2 = r0, r3 = r0, r4 = r0, r5 = r0, r6 = r0, r7 = r0;
+  for (int64_t p = 0; p < kc; ++p) {
+    const __m256 b = _mm256_loadu_ps(bp + p * 8);
+    const float* a = ap + p * 8;
+    r0 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 0), b, r0);
+    r1 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 1), b, r1);
+    r2 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 2), b, r2);
+    r3 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 3), b, r3);
+    r4 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 4), b, r4);
+    r5 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 5), b, r5);
+    r6 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 6), b, r6);
+    r7 = _mm256_fmadd_ps(_mm256_broadcast_ss(a + 7), b, r7);
+  }
+  _mm256_storeu_ps(acc + 0, r0);
+  _mm256_storeu_ps(acc + 8, r1);
+  _mm256_storeu_ps(acc + 16, r2);
+  _mm256_storeu_ps(acc + 24, r3);
+  _mm256_storeu_ps(acc + 32, r4);
+  _mm256_storeu_ps(acc + 40, r5);
+  _mm256_storeu_ps(acc + 48, r6);
+  _mm256_storeu_ps(acc + 56, r7);
+#else
+  for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+  for (int64_t p = 0; p < kc; ++p)
+    for (int i = 0; i < 8; ++i)
+      for (int j = 0; j < 8; ++j) acc[i * 8 + j] = std::fma(ap[p * 8 + i], bp[p * 8 + j], acc[i * 8 + j]);
+#endif
+}
+
+// C[m, n] (row stride ldc) = A[m, k] * B[k, n], general strides for A and B, beta = 0, one thread.
+void sgemm_sequential(int64_t m, int64_t k, int64_t n, const float* a, int64_t rsa, int64_t csa, const float* b, int64_t rsb, int64_t csb, float* c,
+                      int64_t ldc) {
+  if (m <= 0 || n <= 0) return;
+  if (k <= 0) {
+    for (int64_t i = 0; i < m; ++i) std::fill(c + i * ldc, c + i * ldc + n, 0.f);
+    return;
+  }
+  std::vector<float> bpack((size_t)(kGemmKC * ((std::min(n, kGemmNC) + kGemmNR - 1) / kGemmNR) * kGemmNR));
+  std::vector<float> apack((size_t)(kGemmKC * kGemmMC));
+  float acc[64];
+  for (int64_t jc = 0; jc < n; jc += kGemmNC) {
+    const int64_t nc = std::min(kGemmNC, n - jc);
+    for (int64_t pc = 0; pc < k; pc += kGemmKC) {
+      const int64_t kc = std::min(kGemmKC, k - pc);
+      // pack B[pc..pc+kc, jc..jc+nc] into panels of 8 columns: panel-major, then k, then the 8 columns
+      for (int64_t jr = 0; jr < nc; jr += kGemmNR) {
+        float* dst = bpack.data() + (jr / kGemmNR) * kc * kGemmNR;
+        const int64_t w = std::min(kGemmNR, nc - jr);
+        for (int64_t p = 0; p < kc; ++p) {
+          const float* src = b + (pc + p) * rsb + (jc + jr) * csb;
+          for (int64_t j = 0; j < w; ++j) dst[p * kGemmNR + j] = src[j * csb];
+          for (int64_t j = w; j < kGemmNR; ++j) dst[p * kGemmNR + j] = 0.f;
+        }
+      }
+      for (int64_t ic = 0; ic < m; ic += kGemmMC) {
+        const int64_t mc = std::min(kGemmMC, m - ic);
+        for (int64_t ir = 0; ir < mc; ir += kGemmMR) {
+          float* dst = apack.data() + (ir / kGemmMR) * kc * kGemmMR;
+          const int64_t h = std::min(kGemmMR, mc - ir);
+          for (int64_t p = 0; p < kc; ++p) {
+            const float* src = a + (ic + ir) * rsa + (pc + p) * csa;
+            for (int64_t i = 0; i < h; ++i) dst[p * kGemmMR + i] = src[i * rsa];
+            for (int64_t i = h; i < kGemmMR; ++i) dst[p * kGemmMR + i] = 0.f;
+          }
+        }
+        for (int64_t jr = 0; jr < nc; jr += kGemmNR) {
+          const float* bp = bpack.data() + (jr / kGemmNR) * kc * kGemmNR;
+          const int64_t w = std::min(kGemmNR, nc - jr);
+          for (int64_t ir = 0; ir < mc; ir += kGemmMR) {
+            const float* ap = apack.data() + (ir / kGemmMR) * kc * kGemmMR;
+            const int64_t h = std::min(kGemmMR, mc - ir);
+            gemm_micro_8x8(kc, ap, bp, acc);
+            float* ct = c + (ic + ir) * ldc + jc + jr;
+            if (pc == 0) {
+              for (int64_t i = 0; i < h; ++i)
+                for (int64_t j = 0; j < w; ++j) ct[i * ldc + j] = acc[i * 8 + j];
+            } else {
+              for (int64_t i = 0; i < h; ++i)
+                for (int64_t j = 0; j < w; ++j) ct[i * ldc + j] += acc[i * 8 + j];
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// sgemm_maybe_parallel_ldc (conv2d.rs:884-903): row bands of A over the threads when the product is large.
+void sgemm_maybe_parallel(int64_t m, int64_t k, int64_t n, const float* a, const float* b, float* c, int64_t ldc) {
+  const int threads = g_threads;
+  if (threads > 1 && m * k * n >= 64LL * 64 * 64 && m >= 2 * threads) {
+    const int64_t chunk = std::max<int64_t>((m + threads - 1) / threads, 1);
+#pragma omp parallel for num_threads(threads) schedule(static, 1)
+    for (int64_t t = 0; t < threads; ++t) {
+      const int64_t r0 = t * chunk;
+      if (r0 < m) sgemm_sequential(std::min(chunk, m - r0), k, n, a + r0 * k, k, 1, b, n, 1, c + r0 * ldc, ldc);
+    }
+    return;
+  }
+  sgemm_sequential(m, k, n, a, k, 1, b, n, 1, c, ldc);
+}
+
+// im2col_block_cols (conv2d.rs:135-166)
+int64_t im2col_block_cols(int64_t col_rows, int64_t col_cols, int64_t ow, int64_t cap_bytes) {
+  const int64_t bytes_per_col = col_rows * 4;
+  if (bytes_per_col == 0 || col_cols == 0) return col_cols;
+  if (bytes_per_col * col_cols <= cap_bytes) return col_cols;
+  const int64_t cap_cols = std::max<int64_t>(cap_bytes / bytes_per_col, 1);
+  const int64_t blocks = (col_cols + cap_cols - 1) / cap_cols;
+  const int64_t even = std::min(std::max<int64_t>((col_cols + blocks - 1) / std::max<int64_t>(blocks, 1), 1), cap_cols);
+  if (ow > 0 && even >= ow) {
+    const int64_t up = (even + ow - 1) / ow * ow;
+    if (up <= cap_cols) return std::min(up, col_cols);
+    const int64_t down = (even / ow) * ow;
+    if (down >= 1) return std::min(down, col_cols);
+  }
+  return even;
+}
+
+// Columns [col0, col1) of the im2col matrix of one (batch, group): row (ic, r, s), column (oh, ow).
+void im2col_block(const float* x, int64_t h, int64_t w, int64_t cpg, int64_t kh, int64_t kw, const ConvGeo& g, int64_t ow, int64_t col0, int64_t col1,
+                  float* col) {
+  const int64_t bw = col1 - col0;
+  const int64_t sh = g.strides[0], sw = g.strides[1], dh = g.dilations[0], dw = g.dilations[1], pt = g.pads[0], pl = g.pads[1];
+  for (int64_t ic = 0; ic < cpg; ++ic)
+    for (int64_t r = 0; r < kh; ++r)
+      for (int64_t s = 0; s < kw; ++s) {
+        float* dst = col + ((ic * kh + r) * kw + s) * bw;
+        const float* plane = x + ic * h * w;
+        for (int64_t j = col0; j < col1; ++j) {
+          const int64_t oy = j / ow, ox = j % ow;
+          const int64_t iy = oy * sh - pt + r * dh, ix = ox * sw - pl + s * dw;
+          dst[j - col0] = (iy >= 0 && iy < h && ix >= 0 && ix < w) ? plane[iy * w + ix] : 0.f;
+        }
+      }
+}
+
+void conv2d_reference_algorithm(const oxo_tensor& x, const oxo_tensor& w, const oxo_tensor* bias, const ConvGeo& g, float* y) {
+  const int64_t n = x.shape[0], c_in = x.shape[1], h = x.shape[2], wd = x.shape[3];
+  const int64_t c_out = w.shape[0], cpg = w.shape[1], kh = w.shape[2], kw = w.shape[3];
+  const int64_t oh = g.out_shape[2], ow = g.out_shape[3];
+  const int64_t group = g.group, copg = c_out / group;
+  const int64_t col_rows = cpg * kh * kw, col_cols = oh * ow;
+  const bool no_pad = g.pads[0] == 0 && g.pads[1] == 0 && g.pads[2] == 0 && g.pads[3] == 0;
+  auto add_bias = [&](int64_t batch, int64_t grp) {
+    if (!bias) return;
+    for (int64_t oc = 0; oc < copg; ++oc) {
+      const float bv = bias->data[grp * copg + oc];
+      float* row = y + ((batch * c_out + grp * copg + oc) * col_cols);
+      for (int64_t j = 0; j < col_cols; ++j) row[j] += bv;
+    }
+  };
+  if (kh == 1 && kw == 1 && g.strides[0] == 1 && g.strides[1] == 1 && no_pad && g.dilations[0] == 1 && g.dilations[1] == 1) {
+    const int64_t spatial = h * wd;
+    for (int64_t batch = 0; batch < n; ++batch)
+      for (int64_t grp = 0; grp < group; ++grp) {
+        sgemm_maybe_parallel(copg, cpg, spatial, w.data + grp * copg * cpg, x.data + (batch * c_in + grp * cpg) * spatial,
+                             y + (batch * c_out + grp * copg) * spatial, spatial);
+        add_bias(batch, grp);
+      }
+    return;
+  }
+  const int64_t block_cols = im2col_block_cols(col_rows, col_cols, ow, 64LL * 1024 * 1024);
+  const int64_t jobs = n * group;
+  auto run_job = [&](int64_t batch, int64_t grp, std::vector<float>& col, bool parallel_gemm) {
+    const float* xin = x.data + (batch * c_in + grp * cpg) * h * wd;
+    const float* wm = w.data + grp * copg * col_rows;
+    float* out = y + (batch * c_out + grp * copg) * col_cols;
+    for (int64_t c0 = 0; c0 < col_cols; c0 += block_cols) {
+      const int64_t c1 = std::min(c0 + block_cols, col_cols);
+      im2col_block(xin, h, wd, cpg, kh, kw, g, ow, c0, c1, col.data());
+      if (parallel_gemm) sgemm_maybe_parallel(copg, col_rows, c1 - c0, wm, col.data(), out + c0, col_cols);
+      else sgemm_sequential(copg, col_rows, c1 - c0, wm, col_rows, 1, col.data(), c1 - c0, 1, out + c0, col_cols);
+    }
+    add_bias(batch, grp);
+  };
+  if (jobs <= 1 || g_threads <= 1) {
+    std::vector<float> col((size_t)(col_rows * block_cols));
+    for (int64_t job = 0; job < jobs; ++job) run_job(job / group, job % group, col, jobs <= 1);
+    return;
+  }
+#pragma omp parallel num_threads(g_threads)
+  {
+    std::vector<float> col((size_t)(col_rows * block_cols));  // one workspace per worker (for_each_init, :506)
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t job = 0; job < jobs; ++job) run_job(job / group, job % group, col, false);
+  }
+}
+
 void op_conv(Ctx& c) {
   const char* op = "Conv";
   const oxo_tensor& x = c.input(0);
@@ -755,9 +973,14 @@ void op_conv(Ctx& c) {
     k_volume *= w.shape[d + 2];
   }
   int64_t copg = c_out / g.group;
-  TapTable taps = build_taps(g, x.shape + 2, w.shape + 2);
   alloc_out(c.out[0], g.out_shape);
   float* y = c.out[0].data;
+  if (g_float_accum == 2 && rank == 2) {  // the reference's algorithm (im2col + blocked sgemm), for the timed baseline
+    conv2d_reference_algorithm(x, w, bias, g, y);
+    apply_fused_activation(c.attrs, y, c.out[0].len);
+    return;
+  }
+  TapTable taps = build_taps(g, x.shape + 2, w.shape + 2);
   int64_t jobs = batch * c_out;
   const int accum = g_float_accum;
 #pragma omp parallel for if (g_threads > 1) num_threads(g_threads) schedule(dynamic, 1)
@@ -792,6 +1015,10 @@ void op_conv(Ctx& c) {
 // ---------------------------------------------------------------------------------------
 void raw_matmul(const float* a, int64_t rsa, int64_t csa, const float* b, int64_t rsb, int64_t csb, float* out, int64_t m, int64_t k, int64_t n) {
   const int accum = g_float_accum;
+  if (accum == 2) {  // sgemm_strided (math_typed.rs:45): one sequential blocked sgemm
+    sgemm_sequential(m, k, n, a, rsa, csa, b, rsb, csb, out, n);
+    return;
+  }
 #pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
   for (int64_t i = 0; i < m; ++i) {
     for (int64_t j = 0; j < n; ++j) {
@@ -813,6 +1040,9 @@ void op_matmul(Ctx& c) {
   if (a.len != numel(a) || b.len != numel(b)) fail(OXO_ERR_SHAPE_MISMATCH, "MatMul: data length does not match shape");
   MatMulShape s = resolve_shapes(a, b, "MatMul");
   alloc_out(c.out[0], s.out_shape);
+  // batch items in parallel from four on (matmul_f32_into, math_typed.rs:355); only the timed mode threads here,
+  // the other modes thread inside raw_matmul
+#pragma omp parallel for if (g_float_accum == 2 && g_threads > 1 && s.batch >= 4) num_threads(g_threads)
   for (int64_t bi = 0; bi < s.batch; ++bi) {
     const float* ap = a.data + (s.a_broadcast ? 0 : bi * s.m * s.k);
     const float* bp = b.data + (s.b_broadcast ? 0 : bi * s.k * s.n);
@@ -929,6 +1159,12 @@ void binary_op(Ctx& c, F f) {
   }
   float* y = c.out[0].data;
   int64_t n = c.out[0].len;
+  if (a.len == n && b.len == n) {  // same shape: one straight pass (the reference's simd_add / simd_mul path, math/broadcast.rs:219-249)
+    const float* pa = a.data;
+    const float* pb = b.data;
+    for (int64_t i = 0; i < n; ++i) y[i] = f(pa[i], pb[i]);
+    return;
+  }
 #pragma omp parallel for if (g_threads > 1) num_threads(g_threads)
   for (int64_t flat = 0; flat < n; ++flat) {
     int64_t rem = flat, ia = 0, ib = 0;
@@ -1516,7 +1752,7 @@ void oxo_free_tensor(oxo_tensor* t) {
 const char* oxo_last_error(void) { return g_err.c_str(); }
 void oxo_set_threads(int32_t threads) { g_threads = threads < 1 ? 1 : threads; }
 int32_t oxo_get_threads(void) { return g_threads; }
-void oxo_set_float_accum(int32_t mode) { g_float_accum = mode ? 1 : 0; }
+void oxo_set_float_accum(int32_t mode) { g_float_accum = (mode == 1 || mode == 2) ? mode : 0; }
 double oxo_round_ties_even_f64(double v) { return round_ties_even_f64(v); }
 float oxo_round_ties_even_f32(float v) { return round_ties_even_f32_native(v); }
 float oxo_requantize(int64_t acc, float combined, int32_t zero_point, int64_t lo, int64_t hi) {

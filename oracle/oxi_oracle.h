@@ -68,8 +68,12 @@ const char* oxo_last_error(void);
  * the integer operators). */
 void oxo_set_threads(int32_t threads);
 int32_t oxo_get_threads(void);
-/* 0: accumulate float contractions in f64 then round once (tight yardstick);
- * 1: accumulate in f32, sequentially (closer to what an f32 sgemm produces). */
+/* 0: accumulate float contractions in f64 then round once (tight yardstick, the checker);
+ * 1: accumulate in f32, sequentially (closer to what an f32 sgemm produces);
+ * 2: the reference's algorithm and threading for float Conv / MatMul / Gemm -- im2col in blocks of at most
+ *    64 MiB plus a blocked, packed sgemm with an 8x8 FMA register tile, jobs or row bands over the threads
+ *    (oxionnx-ops src/conv/conv2d.rs:246-546, src/math_typed.rs:45): the TIMED CPU baseline, checked against
+ *    mode 0 to 1e-5. */
 void oxo_set_float_accum(int32_t mode);
 
 /* scalar helpers exposed for unit tests */
