@@ -23,11 +23,15 @@ SOURCES = {
     "kernels_glue.cu": COMMON,
     "kernels_simt.cu": [f for f in COMMON if f != "--fmad=false"],
     "kernels_umma.cu": [f for f in COMMON if f != "--fmad=false"],
+    "umma_i8.cu": [f for f in COMMON if f != "--fmad=false"],
+    "umma_tf32.cu": [f for f in COMMON if f != "--fmad=false"],
+    "umma_f16.cu": [f for f in COMMON if f != "--fmad=false"],
+    "umma_probe.cu": [f for f in COMMON if f != "--fmad=false"],
     "runtime.cpp": COMMON,
     "planner.cpp": COMMON,
     "abi.cpp": COMMON,
 }
-HEADERS = ["common.hpp", "kernels.hpp", "runtime.hpp", os.path.join("..", "..", "include", "oxb200.h")]
+HEADERS = ["common.hpp", "kernels.hpp", "runtime.hpp", "umma_kernel.cuh", "umma_launch.cuh", os.path.join("..", "..", "include", "oxb200.h")]
 
 
 def _nvcc():

@@ -16,7 +16,7 @@ namespace oxb {
 
 // Device storage type of a value.  The boundary speaks f32 lanes; on the device a value is
 // stored in the narrowest type that holds every lane the reference can produce for it.
-enum class DT : int32_t { F32 = 0, U8 = 1, I8 = 2, I32 = 3, I16 = 4 };
+enum class DT : int32_t { F32 = 0, U8 = 1, I8 = 2, I32 = 3, I16 = 4, F16 = 5, BF16 = 6 };
 
 inline size_t dt_size(DT d) {
   switch (d) {
@@ -25,6 +25,8 @@ inline size_t dt_size(DT d) {
     case DT::I8: return 1;
     case DT::I32: return 4;
     case DT::I16: return 2;
+    case DT::F16: return 2;
+    case DT::BF16: return 2;
   }
   return 4;
 }
@@ -35,6 +37,8 @@ inline const char* dt_name(DT d) {
     case DT::I8: return "i8";
     case DT::I32: return "i32";
     case DT::I16: return "i16";
+    case DT::F16: return "f16";
+    case DT::BF16: return "bf16";
   }
   return "?";
 }

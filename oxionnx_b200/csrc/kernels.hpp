@@ -157,8 +157,9 @@ enum EpiMode { EPI_F32 = 0, EPI_REQUANT = 1, EPI_INT32 = 2, EPI_DEQUANT = 3 };
 
 struct Epilogue {
   int mode = EPI_F32;
-  // EPI_F32: out = act(acc + bias_f[oc]); act 0 none, 1 relu, 2 clip
+  // EPI_F32: out = act(acc + bias_f[oc]); act 0 none, 1 relu, 2 clip, 3 silu, 4 prelu (per-channel slope)
   const float* bias_f = nullptr;
+  const float* slope = nullptr;  // act 4: [OC] padded like the bias
   int act = 0;
   float clip_lo = 0.f, clip_hi = 0.f;
   int round_tf32 = 0;
@@ -168,6 +169,7 @@ struct Epilogue {
   // integer modes.  Direct kernels subtract zero points per element; the tensor-core kernel
   // computes raw = sum(x*w) and applies acc = raw + bias_i[oc] - x_zp * wsum[oc].
   const int32_t* bias_i = nullptr;
+  const float* bias_if = nullptr;  // tensor-core kernel: the folded integer bias as f32 lanes (every entry below 2^24), or null
   const int32_t* wsum = nullptr;
   int x_zp = 0;
   const float* x_zp_dev = nullptr;  // when set, the zero point is read from this device f32 lane
@@ -226,10 +228,18 @@ bool umma_overlapping_positions_ok();
 
 // tcgen05 implicit-GEMM plan (tensor maps are built once at plan time).
 struct UmmaPlan;
-// kind: 0 = i8 (A u8/s8, B s8/u8, s32 accumulate), 1 = tf32 (f32 storage, f32 accumulate).
-// Returns nullptr with `why` filled when the shape is not eligible.
+// kind: 0 = i8 (A u8/s8, B s8/u8, s32 accumulate), 1 = tf32 (f32 storage, f32 accumulate), 2 = f16, 3 = bf16
+// (16-bit storage, f32 accumulate).  Returns nullptr with `why` filled when the shape is not eligible.
+// Choices a context may override (oxb200_config): `requant_f64` keeps the two-pass f64 requantisation even where
+// the one-FMA form is proven; `split_k_max` bounds the slices of a split reduction (0: the default of 8, 1: never
+// split); `cta_pairs` 0 lets the tile model decide, 1 never pairs CTAs, 2 pairs them wherever the shape allows.
+struct UmmaTuning {
+  int requant_f64 = 0;
+  int split_k_max = 0;
+  int cta_pairs = 0;
+};
 UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt, void* out, const ConvShape& cs, const Epilogue& e, int kind,
-                           std::string* why);
+                           const UmmaTuning& tune, std::string* why);
 void umma_plan_destroy(UmmaPlan* p);
 // After a launch that gave up (error word set): puts a split-K plan's arrival counters back to zero, so that the
 // next launch does not inherit a half-counted tile.  A no-op for plans that do not split K.
@@ -241,7 +251,11 @@ const char* umma_plan_desc(const UmmaPlan* p);
 // Packed weight size helpers for the tensor-core path: weights are laid out [OC][R*S*Cpad]
 // (K-major rows), Cpad = C rounded up to the channel block.
 int umma_channel_block(int C, int kind);  // 0 when C is not eligible
+inline int umma_elem_bytes(int kind) { return kind == 0 ? 1 : (kind == 1 ? 4 : 2); }
 bool umma_available();                    // driver entry point for tensor-map encoding found
+// Issue-rate probe: operations per second the tensor pipe reaches for `kind` (0 i8, 1 tf32, 2 f16, 3 bf16) on the
+// current device with nothing to wait for; `err_flag` is a device word that records a wait that ran out.
+double umma_probe_peak(int kind, int* err_flag, cudaStream_t s);
 
 }  // namespace k
 }  // namespace oxb

@@ -388,7 +388,7 @@ def test_cuda_graph_replay_is_bit_identical_and_counted():
     verified.close()
 
 
-def test_split_k_is_used_and_agrees_with_the_unsplit_kernel(monkeypatch):
+def test_split_k_is_used_and_agrees_with_the_unsplit_kernel():
     """Layers with few output tiles and a long K run as several K slices per tile that meet in a workspace.  The
     integer form must equal the unsplit kernel bit for bit; the float form adds the slices in a fixed order, so
     it is reproducible run to run and agrees with the unsplit kernel within the TF32 tolerance."""
@@ -407,9 +407,8 @@ def test_split_k_is_used_and_agrees_with_the_unsplit_kernel(monkeypatch):
     xf = rng.standard_normal((2, 256, 7, 7)).astype(np.float32)
     results = {}
     for mode in ("split", "unsplit"):
-        monkeypatch.setenv("OXB200_UMMA_SPLITK", "8" if mode == "split" else "1")
         for name, graph, weights, x in (("int8", gq, wq, xq), ("f32", gf, wf, xf)):
-            sess = Session.builder().build_from_graph(graph, weights)
+            sess = Session.builder().with_tuning(split_k_max=8 if mode == "split" else 1).build_from_graph(graph, weights)
             first = sess.run({"x": x})["y"].copy()
             again = sess.run({"x": x})["y"].copy()
             assert np.array_equal(first, again), "a split-K sum must not depend on the arrival order"

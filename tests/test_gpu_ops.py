@@ -117,6 +117,74 @@ def test_qlinear_conv_bit_exact(ctx, shape):
     assert np.unique(want).size > 8, "degenerate test vector"
 
 
+PAIR_SHAPES = [
+    # N, C, H, W, OC, k, stride, pad: shapes the CTA-pair form (tcgen05 cta_group::2, one 256 x 256 tile per two CTAs) must get right
+    (2, 256, 16, 16, 256, 3, 1, 1),     # two full pair tiles, 18 K blocks, halo rows
+    (3, 128, 11, 13, 512, 3, 1, 1),     # M = 429: the second CTA of the last pair is mostly past the end; two channel tiles
+    (1, 256, 9, 9, 320, 1, 1, 0),       # M = 81 (< 128: the odd CTA has no rows at all), ragged second channel tile
+    (5, 64, 14, 14, 256, 3, 2, 1),      # stride 2, 64-byte K blocks
+    (2, 512, 20, 20, 256, 1, 1, 0),     # plain GEMM form (2-D tiled loads), M = 800
+]
+
+
+@pytest.mark.parametrize("shape", PAIR_SHAPES, ids=[str(s) for s in PAIR_SHAPES])
+def test_cta_pair_kernel_matches_oracle_and_lone_cta_kernel(shape):
+    """The pair form against the oracle (bit-exact for QLinearConv, TF32 tolerance for Conv) and against the
+    one-CTA-per-tile form of the same layer (bit-exact for the integers; the float forms may sum the K blocks
+    in different orders, e.g. when the lone-CTA form splits K, so they are held to the tolerance)."""
+    n, c, h, w, oc, k, stride, pad = shape
+    rng = np.random.default_rng(zlib.crc32(repr(("pair",) + shape).encode()))
+    oracle.set_threads(8)
+    attrs = {"strides": [stride, stride], "pads": [pad] * 4, "kernel_shape": [k, k]}
+    x = rng.integers(0, 128, (n, c, h, w)).astype(np.float32)
+    wt = rng.integers(-127, 128, (oc, c, k, k)).astype(np.float32)
+    ws = rng.uniform(0.001, 0.01, oc).astype(np.float32)
+    bias = rng.integers(-1000, 1001, oc).astype(np.float32)
+    y_scale = np.float32(0.005 * 73.0 * np.sqrt(c * k * k) * 0.02)
+    qins = [x, np.float32([0.02]), np.float32([0]), wt, ws, np.zeros(oc, np.float32), np.float32([y_scale]), np.float32([128]), bias]
+    xf = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wf = (rng.standard_normal((oc, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    bf = rng.standard_normal(oc).astype(np.float32)
+    fattrs = dict(attrs, activation="relu")
+    results = {}
+    for mode in ("always", "never"):
+        ctx = S.CudaContext(0, cta_pairs=mode)
+        got_q = dispatch(ctx, "QLinearConv", qins, attrs)
+        got_f = dispatch(ctx, "Conv", [xf, wf, bf], fattrs)
+        assert got_q is not None and got_f is not None, ctx.last_error()
+        results[mode] = (got_q[0], got_f[0])
+        ctx.close()
+    want_q, = oracle.run_node("QLinearConv", qins, attrs)
+    want_f, = oracle.run_node("Conv", [xf, wf, bf], fattrs)
+    assert np.array_equal(results["always"][0], want_q), f"{np.sum(results['always'][0] != want_q)} of {want_q.size} lanes differ"
+    assert np.array_equal(results["never"][0], want_q)
+    assert np.unique(want_q).size > 8, "degenerate test vector"
+    assert_close_tf32(results["always"][1], want_f, "pair Conv")
+    assert_close_tf32(results["never"][1], want_f, "lone-CTA Conv")
+
+
+def test_cta_pair_kernel_is_the_one_that_runs_when_forced():
+    from oxionnx_b200.graph import Graph
+    rng = np.random.default_rng(5)
+    weights = {"w": rng.integers(-127, 128, (256, 256, 3, 3)).astype(np.float32), "ws": rng.uniform(0.001, 0.01, 256).astype(np.float32),
+               "wz": np.zeros(256, np.float32), "b": rng.integers(-1000, 1000, 256).astype(np.float32), "xs": np.float32([0.02]), "z0": np.float32([0]),
+               "ys": np.float32([0.5]), "qs": np.float32([0.02])}
+    graph = Graph(nodes=[Node("QuantizeLinear", "q", ["x", "qs", "z0"], ["xq"], {}),
+                         Node("QLinearConv", "conv", ["xq", "xs", "z0", "w", "ws", "wz", "ys", "z0", "b"], ["yq"], {"pads": [1, 1, 1, 1]}),
+                         Node("DequantizeLinear", "dq", ["yq", "ys", "z0"], ["y"], {})], input_names=["x"], output_names=["y"])
+    x = np.abs(rng.standard_normal((2, 256, 12, 12))).astype(np.float32)
+    outs = {}
+    for mode in ("always", "never"):
+        sess = S.Session.builder().with_tuning(cta_pairs=mode).build_from_graph(graph, weights)
+        outs[mode] = sess.run({"x": x})["y"]
+        kernel = [s_["kernel"] for s_ in sess.steps() if s_["node"] == "conv"][0]
+        assert ("cta-pair" in kernel) == (mode == "always"), kernel
+        sess.close()
+    oracle.set_threads(8)
+    want = oracle.run_graph(graph, weights, {"x": x}, keep_all=False)["y"]
+    assert np.array_equal(outs["always"], want) and np.array_equal(outs["never"], want)
+
+
 def test_conv_integer_and_matmul_integer_bit_exact(ctx):
     rng = np.random.default_rng(17)
     oracle.set_threads(8)
@@ -190,14 +258,13 @@ def _requant_edge_operands(rng, gen, m, k, n):
 
 @pytest.mark.parametrize("case", REQUANT_EDGE, ids=[c[0] for c in REQUANT_EDGE])
 @pytest.mark.parametrize("force_f64", [False, True], ids=["fma", "two-pass"])
-def test_requantisation_edge_cases_bit_exact(ctx_auto, case, force_f64, monkeypatch):
+def test_requantisation_edge_cases_bit_exact(case, force_f64):
     """The tensor-core epilogue has two requantisation variants (one fused multiply-add per lane
     when the scales allow it, an f32 estimate with an f64 second pass otherwise); both must equal
     the reference's f64 arithmetic on ties, on accumulators that f32 cannot hold exactly and on
-    extreme scales (oxionnx-ops/src/quantize/requant.rs)."""
+    extreme scales (SatRange::requantize, oxionnx-ops/src/registry/quant_ops/mod.rs:229-233)."""
     name, k, gen, a_scale, b_scale, y_scale, a_zp, y_zp = case
-    if force_f64:
-        monkeypatch.setenv("OXB200_REQUANT_F64", "1")
+    ctx_auto = S.CudaContext(0, requant_f64=force_f64)
     rng = np.random.default_rng(zlib.crc32(name.encode()))
     oracle.set_threads(8)
     m, n = 256, 96
@@ -206,6 +273,7 @@ def test_requantisation_edge_cases_bit_exact(ctx_auto, case, force_f64, monkeypa
     want, = oracle.run_node("QLinearMatMul", ins)
     got = dispatch(ctx_auto, "QLinearMatMul", ins)
     assert got is not None, ctx_auto.last_error()
+    ctx_auto.close()
     assert np.array_equal(got[0], want), f"{name}: {np.sum(got[0] != want)} of {want.size} lanes differ"
     assert np.unique(want).size > 4, "degenerate test vector"
 
