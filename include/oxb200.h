@@ -75,15 +75,23 @@ typedef struct {
   uint32_t n_attrs;
 } oxb200_node;
 
+/* Element types a typed buffer may have (DType, oxionnx-core src/dtype.rs:8-24; the subset this path stores). */
+enum { OXB200_DT_F32 = 0, OXB200_DT_U8 = 1, OXB200_DT_I8 = 2, OXB200_DT_I32 = 3, OXB200_DT_F16 = 5, OXB200_DT_BF16 = 6 };
+
 /* InputBinding (oxionnx-cuda src/activation.rs:285): a host tensor (f32 lanes) or a value
- * that already lives on the device. */
+ * that already lives on the device.  A graph input that was declared with an 8-bit type
+ * (oxb200_value_info.dtype) is fed through `typed` instead of `lanes`: `len` elements of
+ * `dtype` in the logical (row-major) order, a quarter of the bytes of f32 lanes
+ * (TypedTensor feeds of Session::run_typed, root crate src/session/run/entry.rs). */
 typedef struct {
   const char* name;
-  const float* lanes; /* host f32 lanes, NULL when `resident` is set */
+  const float* lanes; /* host f32 lanes, NULL when `resident` or `typed` is set */
   uint64_t len;
   const uint64_t* shape;
   uint32_t rank;
   oxb200_tensor* resident;
+  int32_t dtype;      /* OXB200_DT_* of `typed`; ignored when `typed` is NULL */
+  const void* typed;  /* typed host lanes, or NULL */
 } oxb200_operand;
 
 /* One output of a dispatch or a fetch of a run. */
@@ -96,11 +104,15 @@ typedef struct {
   oxb200_tensor* resident; /* out: device tensor when the outcome is OK_DEVICE */
 } oxb200_result;
 
-/* Declared shape of a graph input (TensorInfo, oxionnx-core src/graph.rs:862). */
+/* Declared shape and element type of a graph input (TensorInfo, oxionnx-core src/graph.rs:862).
+ * dtype 0 (f32 lanes) is the reference's dtype-erased convention; U8 / I8 declare a quantised
+ * input whose feeds arrive as typed 8-bit lanes and whose saturation is exact per type
+ * (SatRange::for_dtype, oxionnx-ops src/registry/quant_ops/mod.rs:216-222). */
 typedef struct {
   const char* name;
   const uint64_t* shape;
   uint32_t rank;
+  int32_t dtype;
 } oxb200_value_info;
 
 /* Context options.  Zero-initialise, set struct_size, then override.  The environment
@@ -115,7 +127,10 @@ typedef struct {
   int32_t kernel_path;        /* 0 auto (tcgen05 where eligible), 1 force the direct CUDA-core kernels */
   int32_t keep_intermediates; /* 1: every value keeps a private arena slot (per-node inspection) */
   int32_t profile;            /* 1: record per-node CUDA-event timings during runs */
-  int32_t reserved[8];
+  int32_t requant_f64;        /* 1: requantise with the two-pass f64 form even where the one-FMA form is proven exact */
+  int32_t split_k_max;        /* most slices a long reduction may be split into (0: default 8, 1: never split) */
+  int32_t cta_pairs;          /* 0 the tile model decides, 1 never pair CTAs (cta_group::2), 2 pair wherever the shape allows */
+  int32_t reserved[5];
 } oxb200_config;
 
 /* CacheCounters (oxionnx-cuda src/residency.rs:141-240) plus arena figures. */
@@ -151,7 +166,10 @@ void oxb200_config_from_env(oxb200_config* cfg);
 /* ---- context ------------------------------------------------------------------------- */
 
 int oxb200_device_count(void);
-/* CudaContext::try_new_with (src/context.rs:362-467): one context, one stream, one device. */
+/* CudaContext::try_new_with (src/context.rs:362-467): one context, one stream, one device.
+ * A process may hold several contexts, on one device or on several (one per GPU for a batch split over
+ * GPUs); calls on different contexts may run on different host threads at the same time, calls on one
+ * context are serialised by the context's own lock. */
 int oxb200_ctx_create(int device_ordinal, const oxb200_config* cfg, oxb200_ctx** out);
 void oxb200_ctx_destroy(oxb200_ctx* ctx);
 const char* oxb200_last_error(const oxb200_ctx* ctx); /* ctx may be NULL: last error of the calling thread */
@@ -162,6 +180,13 @@ int oxb200_release_device_caches(oxb200_ctx* ctx);
 /* Switches the per-node CUDA-event timing of planned runs (oxb200_config.profile) on or off for later runs;
  * the reference has no counterpart (its profiler wraps whole nodes on the host, src/session/profiling.rs). */
 int oxb200_set_profile(oxb200_ctx* ctx, int on);
+
+/* Peak rate of the tensor pipe on the context's device for one contraction kind (0 = kind::i8, 1 = kind::tf32,
+ * 2 = kind::f16 with f16 operands, 3 = with bf16 operands): every SM issues a long run of tcgen05.mma
+ * instructions on operands that are never refilled, and the call returns operations (two per multiply-add)
+ * per second.  It is what the benchmark's roofline fractions are quoted against beside the cuBLAS-derived
+ * figures; the reference has no counterpart.  Takes a few milliseconds. */
+int oxb200_probe_tensor_peak(oxb200_ctx* ctx, int32_t kind, double* ops_per_second);
 
 /* Page-locked host memory for feeds and fetches (the reference's pinned staging,
  * src/residency.rs:1147-1312, handed to the caller so no extra host copy is needed). */
@@ -175,6 +200,12 @@ void oxb200_host_free(void* p);
  * life, and are uploaded/packed on first use by a planned session or a dispatch
  * (initializer_id, src/dispatch_helpers.rs:21-64). The lanes are copied. */
 int oxb200_weight_register(oxb200_ctx* ctx, const char* name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank);
+/* The same with the element type the initializer was declared with in the model (TensorProto.data_type,
+ * oxionnx-proto src/types.rs:9-24).  The lanes are still f32; the type is kept beside them and is what lets a
+ * quantised operator whose y_zero_point is a uint8 / int8 initializer saturate to exactly that type
+ * (SatRange::for_dtype, oxionnx-ops src/registry/quant_ops/mod.rs:216-222; pinned by the reference's
+ * tests/qlinear_run_typed_e2e.rs:91-134) instead of the value-based union range. */
+int oxb200_weight_register_typed(oxb200_ctx* ctx, const char* name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank, int32_t dtype);
 /* CudaContext::is_weight_resident */
 int oxb200_is_weight_resident(const oxb200_ctx* ctx, const char* name);
 
@@ -212,8 +243,6 @@ int oxb200_session_plan(oxb200_ctx* ctx, const oxb200_node* nodes, uint32_t n_no
  * every intermediate stays in HBM.  Copies are asynchronous on the context's stream and
  * the call returns after one fence. */
 int oxb200_run(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds, oxb200_result* fetches, uint32_t n_fetches);
-/* Device time of the last oxb200_run in milliseconds, taken with CUDA events on the context's
- * stream from before the first host-to-device copy to after the last device-to-host copy. */
 /* Pipelined form of oxb200_run for throughput: submit enqueues the upload of one set of feeds (host lanes,
  * ideally page-locked) on a copy stream, the run, and the download of the outputs, and returns at once; collect
  * waits for the oldest submission and writes its outputs.  Up to two submissions may be in flight, so the copy
@@ -221,7 +250,36 @@ int oxb200_run(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds, o
  * synchronous, src/session/run/sequential.rs:468). */
 int oxb200_run_submit(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds);
 int oxb200_run_collect(oxb200_ctx* ctx, oxb200_result* fetches, uint32_t n_fetches);
+/* Device time of the last oxb200_run in milliseconds, taken with CUDA events on the context's
+ * stream from before the first host-to-device copy to after the last device-to-host copy. */
 float oxb200_last_run_ms(const oxb200_ctx* ctx);
+
+/* ---- device I/O binding -------------------------------------------------------------- */
+
+/* IoBinding::bind_input / bind_output and Session::run_with_binding (root crate
+ * src/io_binding.rs:42-58, src/session/run/entry.rs:109-139) extended to device memory, which
+ * the reference's binding (host tensors only) cannot hold: a graph input or output of the
+ * planned session is bound to a device buffer, so that consecutive runs exchange no bytes with
+ * the host.
+ *   bind_input_device   the input is read from `device_ptr` (`len` elements of the input's
+ *                       declared dtype, logical row-major order, 16-byte aligned) by every
+ *                       following run until it is bound again or the bindings are cleared;
+ *                       the buffer stays the caller's and must outlive those runs.
+ *   bind_output_device  the output's f32 lanes (logical order) are also written to
+ *                       `device_ptr` (capacity `cap` elements) at the end of every run.
+ *   output_device_ptr   the library-owned device buffer that holds an output's f32 lanes after
+ *                       a run; it keeps its address for the life of the plan, so it can be bound
+ *                       as the input of another plan or of the next run.
+ *   run_bound           one run that touches the host only for inputs that are not bound
+ *                       (`feeds` may be NULL when every input is bound) and fetches that are not
+ *                       NULL; with everything bound it moves no bytes across PCIe and returns
+ *                       after one fence.
+ *   clear_bindings      forgets every binding; later runs upload and download as before. */
+int oxb200_bind_input_device(oxb200_ctx* ctx, const char* name, const void* device_ptr, int32_t dtype, uint64_t len);
+int oxb200_bind_output_device(oxb200_ctx* ctx, const char* name, void* device_ptr, uint64_t cap);
+int oxb200_output_device_ptr(oxb200_ctx* ctx, const char* name, void** device_ptr, uint64_t* len);
+int oxb200_run_bound(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds, oxb200_result* fetches, uint32_t n_fetches);
+int oxb200_clear_bindings(oxb200_ctx* ctx);
 /* The same run split for measurement: stage feeds, run the planned launches `iters`
  * times with everything resident (no host traffic), read fetches. */
 int oxb200_upload_feeds(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds);
@@ -252,9 +310,11 @@ int oxb200_plan_step_info(const oxb200_ctx* ctx, uint32_t index, oxb200_step_inf
  * DynamicQuantizeLinear node of oxb200_dispatch computes, but everything it touches is either
  * passed in by the caller or part of the library image: it calls no cudaMalloc, no cudaFree and
  * no other allocating routine.
- *   x_device        n f32 lanes on the device
- *   y_device        n u8 lanes on the device (output)
- *   scale_zp_device 2 f32 lanes on the device (output: y_scale, y_zero_point)
+ *   x_device        n f32 lanes on the device, 16-byte aligned (the kernels read four lanes per load)
+ *   y_device        n u8 lanes on the device (output), 4-byte aligned (four lanes per store)
+ *   scale_zp_device 2 f32 lanes on the device (output: y_scale, y_zero_point), 4-byte aligned
+ * A pointer that misses its alignment (a slice of a larger buffer at an odd offset) is rejected with
+ * OXB200_FAILED before anything is launched.
  *   cuda_stream     a cudaStream_t of device `device_ordinal` (NULL: the default stream)
  * The reduction scratch is a 256-byte array inside the library, present on every GPU that loads
  * it until the process exits.  At most 2^28 lanes per call; larger inputs are rejected with

@@ -9,6 +9,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("OXB200_LIBRARY") or os.path.join(HERE, "_lib", "liboxb200.so")
 
 MAX_RANK = 8
+DT_F32, DT_U8, DT_I8, DT_I32, DT_F16, DT_BF16 = 0, 1, 2, 3, 5, 6
+# numpy element types that cross the boundary as typed lanes
+TYPED = {np.dtype(np.uint8): DT_U8, np.dtype(np.int8): DT_I8}
 OK_HOST, OK_DEVICE, DECLINED, FAILED, VERIFY_MISMATCH = 0, 1, 2, 3, 4
 PLACE_HOST, PLACE_DEVICE = 0, 1
 STATUS_NAMES = {0: "OK_HOST", 1: "OK_DEVICE", 2: "DECLINED", 3: "FAILED", 4: "VERIFY_MISMATCH"}
@@ -28,7 +31,8 @@ class CNode(ctypes.Structure):
 
 class Operand(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("lanes", ctypes.POINTER(ctypes.c_float)), ("len", ctypes.c_uint64),
-                ("shape", ctypes.POINTER(ctypes.c_uint64)), ("rank", ctypes.c_uint32), ("resident", ctypes.c_void_p)]
+                ("shape", ctypes.POINTER(ctypes.c_uint64)), ("rank", ctypes.c_uint32), ("resident", ctypes.c_void_p),
+                ("dtype", ctypes.c_int32), ("typed", ctypes.c_void_p)]
 
 
 class Result(ctypes.Structure):
@@ -37,13 +41,14 @@ class Result(ctypes.Structure):
 
 
 class ValueInfo(ctypes.Structure):
-    _fields_ = [("name", ctypes.c_char_p), ("shape", ctypes.POINTER(ctypes.c_uint64)), ("rank", ctypes.c_uint32)]
+    _fields_ = [("name", ctypes.c_char_p), ("shape", ctypes.POINTER(ctypes.c_uint64)), ("rank", ctypes.c_uint32), ("dtype", ctypes.c_int32)]
 
 
 class Config(ctypes.Structure):
     _fields_ = [("struct_size", ctypes.c_uint32), ("verify", ctypes.c_int32), ("strict", ctypes.c_int32), ("residency", ctypes.c_int32),
                 ("cuda_graph", ctypes.c_int32), ("kernel_path", ctypes.c_int32), ("keep_intermediates", ctypes.c_int32),
-                ("profile", ctypes.c_int32), ("reserved", ctypes.c_int32 * 8)]
+                ("profile", ctypes.c_int32), ("requant_f64", ctypes.c_int32), ("split_k_max", ctypes.c_int32), ("cta_pairs", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 5)]
 
 
 class Counters(ctypes.Structure):
@@ -77,10 +82,13 @@ SYMBOLS = {
     "oxb200_get_counters": (None, [ctypes.c_void_p, _P(Counters)]),
     "oxb200_release_device_caches": (ctypes.c_int, [ctypes.c_void_p]),
     "oxb200_set_profile": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "oxb200_probe_tensor_peak": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, _P(ctypes.c_double)]),
     "oxb200_host_alloc": (ctypes.c_void_p, [ctypes.c_size_t]),
     "oxb200_host_free": (None, [ctypes.c_void_p]),
     "oxb200_weight_register": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(ctypes.c_float), ctypes.c_uint64, _P(ctypes.c_uint64),
                                               ctypes.c_uint32]),
+    "oxb200_weight_register_typed": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(ctypes.c_float), ctypes.c_uint64, _P(ctypes.c_uint64),
+                                                    ctypes.c_uint32, ctypes.c_int32]),
     "oxb200_is_weight_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
     "oxb200_dispatch": (ctypes.c_int, [ctypes.c_void_p, _P(CNode), _P(Operand), ctypes.c_uint32, ctypes.c_int, _P(Result), ctypes.c_uint32]),
     "oxb200_shadow_verify": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(ctypes.c_float), _P(ctypes.c_float), ctypes.c_uint64]),
@@ -93,6 +101,11 @@ SYMBOLS = {
     "oxb200_run_submit": (ctypes.c_int, [ctypes.c_void_p, _P(Operand), ctypes.c_uint32]),
     "oxb200_run_collect": (ctypes.c_int, [ctypes.c_void_p, _P(Result), ctypes.c_uint32]),
     "oxb200_last_run_ms": (ctypes.c_float, [ctypes.c_void_p]),
+    "oxb200_bind_input_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint64]),
+    "oxb200_bind_output_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_uint64]),
+    "oxb200_output_device_ptr": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(ctypes.c_void_p), _P(ctypes.c_uint64)]),
+    "oxb200_run_bound": (ctypes.c_int, [ctypes.c_void_p, _P(Operand), ctypes.c_uint32, _P(Result), ctypes.c_uint32]),
+    "oxb200_clear_bindings": (ctypes.c_int, [ctypes.c_void_p]),
     "oxb200_upload_feeds": (ctypes.c_int, [ctypes.c_void_p, _P(Operand), ctypes.c_uint32]),
     "oxb200_run_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32, _P(ctypes.c_float)]),
     "oxb200_download_fetches": (ctypes.c_int, [ctypes.c_void_p, _P(Result), ctypes.c_uint32]),
@@ -177,6 +190,15 @@ def pack_operand(op, name, array, keep, resident=None):
         op.resident = resident
         return
     if array is None:
+        return
+    if isinstance(array, np.ndarray) and array.dtype in TYPED:
+        # 8-bit lanes of a graph input that was declared with that type
+        a = keep.add(np.ascontiguousarray(array))
+        op.typed = a.ctypes.data_as(ctypes.c_void_p)
+        op.dtype = TYPED[a.dtype]
+        op.len = a.size
+        op.shape = keep.add((ctypes.c_uint64 * max(a.ndim, 1))(*a.shape))
+        op.rank = a.ndim
         return
     a = keep.add(np.ascontiguousarray(np.asarray(array, dtype=np.float32)))
     op.lanes = a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))

@@ -179,6 +179,31 @@ int oxb200_set_profile(oxb200_ctx* ctx, int on) {
   return OXB200_OK_HOST;
 }
 
+int oxb200_probe_tensor_peak(oxb200_ctx* ctx, int32_t kind, double* ops_per_second) {
+  if (!ctx || !ops_per_second) return fail_with(ctx, OXB200_FAILED, "probe_tensor_peak: NULL argument");
+  if (kind < 0 || kind > 3) return fail_with(ctx, OXB200_FAILED, "probe_tensor_peak: kind must be 0 (i8), 1 (tf32), 2 (f16) or 3 (bf16)");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    Context& C = ctx->impl;
+    C.make_current();
+    int* err = (int*)C.alloc_device(256);
+    OXB_CUDA(cudaMemsetAsync(err, 0, 256, C.stream()));
+    double rate = 0.0;
+    int flag = 0;
+    try {
+      rate = k::umma_probe_peak(kind, err, C.stream());
+      OXB_CUDA(cudaMemcpy(&flag, err, sizeof(int), cudaMemcpyDeviceToHost));
+    } catch (...) {
+      C.free_device(err);
+      throw;
+    }
+    C.free_device(err);
+    if (flag != 0) raise(OXB200_FAILED, "probe_tensor_peak: a bounded wait ran out (code %d)", flag);
+    *ops_per_second = rate;
+    return (int)OXB200_OK_HOST;
+  });
+}
+
 void* oxb200_host_alloc(size_t bytes) {
   void* p = nullptr;
   if (cudaMallocHost(&p, bytes ? bytes : 1) != cudaSuccess) {
@@ -197,6 +222,24 @@ int oxb200_weight_register(oxb200_ctx* ctx, const char* name, const float* lanes
   return guarded(ctx, [&]() {
     std::lock_guard<std::mutex> lock(ctx->impl.mu);
     ctx->impl.register_weight(name, lanes, len, shape, rank);
+    return (int)OXB200_OK_HOST;
+  });
+}
+
+int oxb200_weight_register_typed(oxb200_ctx* ctx, const char* name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank, int32_t dtype) {
+  if (!ctx || !name || (!lanes && len)) return fail_with(ctx, OXB200_FAILED, "weight_register_typed: NULL argument");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    DT declared = DT::F32;
+    switch (dtype) {
+      case OXB200_DT_U8: declared = DT::U8; break;
+      case OXB200_DT_I8: declared = DT::I8; break;
+      case OXB200_DT_I32: declared = DT::I32; break;
+      case OXB200_DT_F16: declared = DT::F16; break;
+      case OXB200_DT_BF16: declared = DT::BF16; break;
+      default: declared = DT::F32; break;
+    }
+    ctx->impl.register_weight(name, lanes, len, shape, rank, declared);
     return (int)OXB200_OK_HOST;
   });
 }
@@ -273,6 +316,18 @@ int oxb200_dispatch(oxb200_ctx* ctx, const oxb200_node* node, const oxb200_opera
         if (!accepts_resident_slot(nd.op, i)) raise(OXB200_DECLINED, "%s: operand %u cannot be bound from the device", nd.op.c_str(), i);
         inputs.push_back({nm, o.resident->h.shape});
         sess.bind_external(nm, o.resident->h.ptr, o.resident->h.dt, o.resident->h.layout);
+        continue;
+      }
+      if (!o.lanes && o.typed && (o.dtype == OXB200_DT_U8 || o.dtype == OXB200_DT_I8)) {
+        // a typed 8-bit operand (TypedTensor): exact integers as f32 lanes, the declared type kept beside them
+        HostTensor t;
+        t.shape.assign(o.shape, o.shape + o.rank);
+        if ((uint64_t)prod(t.shape) != o.len) raise(OXB200_DECLINED, "%s: operand %u data length %llu does not match its shape", nd.op.c_str(), i, (unsigned long long)o.len);
+        t.data.resize(o.len);
+        for (uint64_t e = 0; e < o.len; ++e) t.data[e] = o.dtype == OXB200_DT_U8 ? (float)((const uint8_t*)o.typed)[e] : (float)((const int8_t*)o.typed)[e];
+        t.declared = o.dtype == OXB200_DT_U8 ? DT::U8 : DT::I8;
+        temps.push_back(std::move(t));
+        vconsts[nm] = &temps.back();
         continue;
       }
       if (!o.lanes) {
@@ -357,9 +412,18 @@ int oxb200_session_plan(oxb200_ctx* ctx, const oxb200_node* nodes, uint32_t n_no
       std::vector<int64_t> sh(inputs[i].shape, inputs[i].shape + inputs[i].rank);
       in.push_back({inputs[i].name, sh});
     }
+    auto declared_dt = [](int32_t d, const char* name) -> DT {
+      switch (d) {
+        case OXB200_DT_F32: return DT::F32;
+        case OXB200_DT_U8: return DT::U8;
+        case OXB200_DT_I8: return DT::I8;
+        default: raise(OXB200_DECLINED, "graph input '%s': element type %d is not taken at the boundary", name, (int)d);
+      }
+    };
     std::vector<std::string> outs;
     for (uint32_t i = 0; i < n_outputs; ++i) outs.push_back(outputs[i]);
     auto sess = std::make_unique<Session>(&C);
+    for (uint32_t i = 0; i < n_inputs; ++i) sess->declare_input_type(inputs[i].name, declared_dt(inputs[i].dtype, inputs[i].name));
     std::map<std::string, const HostTensor*> none;
     sess->plan(nd, in, none, outs);
     sess->allow_graph(true);
@@ -419,6 +483,63 @@ int oxb200_run_collect(oxb200_ctx* ctx, oxb200_result* fetches, uint32_t n_fetch
 }
 
 float oxb200_last_run_ms(const oxb200_ctx* ctx) { return ctx ? ctx->impl.last_run_ms : -1.f; }
+
+// ---- device I/O binding (IoBinding / run_with_binding over device memory) ----
+int oxb200_bind_input_device(oxb200_ctx* ctx, const char* name, const void* device_ptr, int32_t dtype, uint64_t len) {
+  if (!ctx || !name) return fail_with(ctx, OXB200_FAILED, "bind_input_device: NULL argument");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    ctx->impl.make_current();
+    DT dt;
+    switch (dtype) {
+      case OXB200_DT_F32: dt = DT::F32; break;
+      case OXB200_DT_U8: dt = DT::U8; break;
+      case OXB200_DT_I8: dt = DT::I8; break;
+      default: raise(OXB200_FAILED, "bind_input_device: element type %d is not taken at the boundary", (int)dtype);
+    }
+    planned(ctx).bind_input_device(name, device_ptr, dt, len);
+    return (int)OXB200_OK_HOST;
+  });
+}
+
+int oxb200_bind_output_device(oxb200_ctx* ctx, const char* name, void* device_ptr, uint64_t cap) {
+  if (!ctx || !name) return fail_with(ctx, OXB200_FAILED, "bind_output_device: NULL argument");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    ctx->impl.make_current();
+    planned(ctx).bind_output_device(name, device_ptr, cap);
+    return (int)OXB200_OK_HOST;
+  });
+}
+
+int oxb200_output_device_ptr(oxb200_ctx* ctx, const char* name, void** device_ptr, uint64_t* len) {
+  if (!ctx || !name) return fail_with(ctx, OXB200_FAILED, "output_device_ptr: NULL argument");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    planned(ctx).output_device_ptr(name, device_ptr, len);
+    return (int)OXB200_OK_HOST;
+  });
+}
+
+int oxb200_run_bound(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds, oxb200_result* fetches, uint32_t n_fetches) {
+  if (!ctx) return fail_with(ctx, OXB200_FAILED, "run_bound: ctx is NULL");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    ctx->impl.make_current();
+    planned(ctx).run_bound(feeds, n_feeds, fetches, n_fetches, ctx->impl.cfg().profile != 0);
+    return (int)OXB200_OK_DEVICE;
+  });
+}
+
+int oxb200_clear_bindings(oxb200_ctx* ctx) {
+  if (!ctx) return fail_with(ctx, OXB200_FAILED, "clear_bindings: ctx is NULL");
+  return guarded(ctx, [&]() {
+    std::lock_guard<std::mutex> lock(ctx->impl.mu);
+    ctx->impl.make_current();
+    planned(ctx).clear_bindings();
+    return (int)OXB200_OK_HOST;
+  });
+}
 
 int oxb200_upload_feeds(oxb200_ctx* ctx, const oxb200_operand* feeds, uint32_t n_feeds) {
   if (!ctx) return fail_with(ctx, OXB200_FAILED, "upload_feeds: ctx is NULL");

@@ -64,6 +64,13 @@ Range sat_infer(const std::vector<int32_t>& y_zp, const std::vector<int32_t>& x_
   return {-128, 255};
 }
 
+// SatRange::for_dtype (quant_ops/mod.rs:216-222) where the zero point kept its declared type, else SatRange::infer.
+Range sat_range(const HostTensor* y_zp_tensor, const std::vector<int32_t>& y_zp, const std::vector<int32_t>& x_zp) {
+  if (y_zp_tensor && y_zp_tensor->declared == DT::U8) return {0, 255};
+  if (y_zp_tensor && y_zp_tensor->declared == DT::I8) return {-128, 127};
+  return sat_infer(y_zp, x_zp);
+}
+
 DT narrowest_int(int64_t lo, int64_t hi) {
   if (lo >= 0 && hi <= 255) return DT::U8;
   if (lo >= -128 && hi <= 127) return DT::I8;
@@ -432,7 +439,11 @@ void Planner::run(const std::vector<std::pair<std::string, std::vector<int64_t>>
 
   // graph inputs: raw f32 lanes in logical order, uploaded into persistent staging
   for (auto& in : inputs) {
-    int vi = add_value(in.first, in.second, DT::F32, Layout::PLAIN);
+    // declared element type (TensorInfo): 8-bit inputs are stored, fed and bound as 8-bit lanes
+    auto declared = S.input_types_.find(in.first);
+    const DT in_dt = declared == S.input_types_.end() ? DT::F32 : declared->second;
+    if (!(in_dt == DT::F32 || in_dt == DT::U8 || in_dt == DT::I8)) OXB_DECLINE("graph input '%s': declared element type %s is not one this provider takes at the boundary", in.first.c_str(), dt_name(in_dt));
+    int vi = add_value(in.first, in.second, in_dt, Layout::PLAIN);
     V(vi).is_graph_input = true;
     V(vi).external = true;
     auto vc = vconsts_.find(in.first);
@@ -902,6 +913,13 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
       const size_t padded = align_up((size_t)OC, 256);
       bias_eff.resize(padded, 0);
       epi.bias_i = upload_vec(bias_eff);
+      // the same bias as f32 lanes, exact below 2^24, for the epilogue variant that adds it after the conversion
+      bool bias_fits = c.x_zp_static;
+      for (int32_t b : bias_eff) bias_fits = bias_fits && b > -16777216 && b < 16777216;
+      if (bias_fits && epi.mode == k::EPI_REQUANT) {
+        std::vector<float> bias_as_f(bias_eff.begin(), bias_eff.end());
+        epi.bias_if = upload_vec(bias_as_f);
+      }
       if (c.x_zp_static) {
         epi.wsum = nullptr;
       } else {
@@ -935,7 +953,11 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
       if (res_vi >= 0) e.residual = (const float*)V(res_vi).ptr;
       if (dq_vi >= 0) e.dq_x_scale_dev = (const float*)V(dq_vi).ptr;
       std::string why2;
-      k::UmmaPlan* plan = k::umma_plan_create(V(x_vi).ptr, xdt, wdev, wdt, V(out_vi).ptr, cs, e, kind, &why2);
+      k::UmmaTuning tune;
+      tune.requant_f64 = C.cfg().requant_f64;
+      tune.split_k_max = C.cfg().split_k_max;
+      tune.cta_pairs = C.cfg().cta_pairs;
+      k::UmmaPlan* plan = k::umma_plan_create(V(x_vi).ptr, xdt, wdev, wdt, V(out_vi).ptr, cs, e, kind, tune, &why2);
       if (!plan) OXB_FAIL("%s '%s': tensor-core plan rejected after selection: %s", n.op.c_str(), n.name.c_str(), why2.c_str());
       S.umma_plans_.push_back(plan);
       Step& me = S.steps_[step_index];
@@ -1443,7 +1465,7 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
     if (!std::isfinite(c.combined[oc])) OXB_DECLINE("QLinearConv: combined scale is not finite");
   }
   // the node's own zero point decides the range (a rewritten stem carries an effective zero point of 0)
-  Range r = sat_infer(y_zp_l, {x_zp_l.empty() ? 0 : x_zp_l[0]});
+  Range r = sat_range(has_in(n, 7) ? const_in(n, 7) : nullptr, y_zp_l, {x_zp_l.empty() ? 0 : x_zp_l[0]});
   c.epi.mode = k::EPI_REQUANT;
   c.epi.y_zp = y_zp_l.empty() ? 0 : y_zp_l[0];
   c.epi.lo = r.lo;
@@ -1781,7 +1803,7 @@ void Planner::plan_matmul_family(const NodeDef& n, int ni) {
   volatile float comb = ab / y_scale;
   if (!std::isfinite((float)comb)) OXB_DECLINE("QLinearMatMul: combined scale is not finite");
   c.combined.assign((size_t)N, (float)comb);
-  Range r = sat_infer(y_zp, a_zp);
+  Range r = sat_range(has_in(n, 7) ? const_in(n, 7) : nullptr, y_zp, a_zp);
   c.epi.mode = k::EPI_REQUANT;
   c.epi.y_zp = y_zp.empty() ? 0 : y_zp[0];
   c.epi.lo = r.lo;

@@ -47,8 +47,9 @@ Context::~Context() {
 
 void Context::make_current() { OXB_CUDA(cudaSetDevice(device_)); }
 
-void Context::register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank) {
+void Context::register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank, DT declared) {
   HostTensor t;
+  t.declared = declared;
   t.shape.assign(shape, shape + rank);
   if ((uint64_t)prod(t.shape) != len) raise(OXB200_FAILED, "weight '%s': %llu lanes do not match its shape", name.c_str(), (unsigned long long)len);
   t.data.assign(lanes, lanes + len);
@@ -176,6 +177,23 @@ int Session::check_error_flag() {
   return flag;
 }
 
+// The host lanes of a feed for graph input `v`, checked against the plan: f32 lanes for an input declared f32, typed
+// lanes of the declared type otherwise.
+static const void* feed_lanes(const oxb200_operand& f, const Value& v, const char* name) {
+  if ((int64_t)f.len != v.numel()) raise(OXB200_FAILED, "run: feed '%s' has %llu lanes, the plan expects %lld", name, (unsigned long long)f.len, (long long)v.numel());
+  if (f.rank != v.shape.size()) raise(OXB200_FAILED, "run: feed '%s' rank differs from the planned shape", name);
+  for (uint32_t d = 0; d < f.rank; ++d)
+    if ((int64_t)f.shape[d] != v.shape[d]) raise(OXB200_FAILED, "run: feed '%s' shape differs from the planned shape", name);
+  if (v.dt == DT::F32) {
+    if (f.lanes) return f.lanes;
+    if (f.typed && f.dtype == OXB200_DT_F32) return f.typed;
+    raise(OXB200_FAILED, "run: feed '%s' has no f32 host lanes", name);
+  }
+  if (!f.typed || f.dtype != (int32_t)v.dt)
+    raise(OXB200_FAILED, "run: graph input '%s' was declared %s; its feed must carry typed lanes of that type", name, dt_name(v.dt));
+  return f.typed;
+}
+
 void Session::upload(const oxb200_operand* feeds, uint32_t n) {
   for (auto& in : input_staging_) {
     const oxb200_operand* f = nullptr;
@@ -184,14 +202,10 @@ void Session::upload(const oxb200_operand* feeds, uint32_t n) {
     if (!f) raise(OXB200_FAILED, "run: no feed for graph input '%s'", in.first.c_str());
     Value& v = values_[in.second];
     if (external_bind_.count(in.first)) continue;  // bound to a value that already lives on the device
-    if (!f->lanes) raise(OXB200_FAILED, "run: feed '%s' has no host lanes", in.first.c_str());
-    if ((int64_t)f->len != v.numel()) raise(OXB200_FAILED, "run: feed '%s' has %llu lanes, the plan expects %lld", in.first.c_str(), (unsigned long long)f->len, (long long)v.numel());
-    if (f->rank != v.shape.size()) raise(OXB200_FAILED, "run: feed '%s' rank differs from the planned shape", in.first.c_str());
-    for (uint32_t d = 0; d < f->rank; ++d)
-      if ((int64_t)f->shape[d] != v.shape[d]) raise(OXB200_FAILED, "run: feed '%s' shape differs from the planned shape", in.first.c_str());
-    OXB_CUDA(cudaMemcpyAsync(v.ptr, f->lanes, (size_t)v.numel() * 4, cudaMemcpyHostToDevice, ctx_->stream()));
+    const void* src = feed_lanes(*f, v, in.first.c_str());
+    OXB_CUDA(cudaMemcpyAsync(v.ptr, src, (size_t)v.numel() * dt_size(v.dt), cudaMemcpyHostToDevice, ctx_->stream()));
     ctx_->counters.uploads += 1;
-    ctx_->counters.upload_bytes += (uint64_t)v.numel() * 4;
+    ctx_->counters.upload_bytes += (uint64_t)v.numel() * dt_size(v.dt);
   }
 }
 
@@ -376,7 +390,7 @@ void Session::prepare_pipeline() {
     OXB_CUDA(cudaEventCreateWithFlags(&fl.down, cudaEventDisableTiming));
     for (auto& in : input_staging_) {
       void* p = values_[in.second].ptr;
-      if (f == 1 && pipe_double_) OXB_CUDA(cudaMalloc(&p, std::max<size_t>((size_t)values_[in.second].numel() * 4, 256)));
+      if (f == 1 && pipe_double_) OXB_CUDA(cudaMalloc(&p, std::max<size_t>((size_t)values_[in.second].numel() * dt_size(values_[in.second].dt), 256)));
       fl.in_dev.push_back(p);
     }
     for (auto& out : output_staging_) {
@@ -399,18 +413,23 @@ void Session::submit(const oxb200_operand* feeds, uint32_t n, bool profile) {
   if (fl.busy) raise(OXB200_FAILED, "submit: two runs are already in flight; collect one first");
   cudaStream_t main = ctx_->stream();
   // without a second input buffer the upload must wait until the previous run has read the inputs
-  if (!pipe_double_ && prev.busy) OXB_CUDA(cudaStreamWaitEvent(copy_stream_, prev.done, 0));
+  // validate every feed before the first input is re-pointed: a rejected submission leaves the plan as it was
+  std::vector<const void*> srcs(input_staging_.size(), nullptr);
   for (size_t i = 0; i < input_staging_.size(); ++i) {
     const auto& in = input_staging_[i];
     const oxb200_operand* f = nullptr;
     for (uint32_t k2 = 0; k2 < n; ++k2)
       if (feeds[k2].name && in.first == feeds[k2].name) f = &feeds[k2];
+    if (!f) raise(OXB200_FAILED, "submit: no feed for graph input '%s'", in.first.c_str());
+    srcs[i] = feed_lanes(*f, values_[in.second], in.first.c_str());
+  }
+  if (!pipe_double_ && prev.busy) OXB_CUDA(cudaStreamWaitEvent(copy_stream_, prev.done, 0));
+  for (size_t i = 0; i < input_staging_.size(); ++i) {
+    const auto& in = input_staging_[i];
     Value& v = values_[in.second];
-    if (!f || !f->lanes) raise(OXB200_FAILED, "submit: no host lanes for graph input '%s'", in.first.c_str());
-    if ((int64_t)f->len != v.numel()) raise(OXB200_FAILED, "submit: feed '%s' has %llu lanes, the plan expects %lld", in.first.c_str(), (unsigned long long)f->len, (long long)v.numel());
-    OXB_CUDA(cudaMemcpyAsync(fl.in_dev[i], f->lanes, (size_t)v.numel() * 4, cudaMemcpyHostToDevice, copy_stream_));
+    OXB_CUDA(cudaMemcpyAsync(fl.in_dev[i], srcs[i], (size_t)v.numel() * dt_size(v.dt), cudaMemcpyHostToDevice, copy_stream_));
     ctx_->counters.uploads += 1;
-    ctx_->counters.upload_bytes += (uint64_t)v.numel() * 4;
+    ctx_->counters.upload_bytes += (uint64_t)v.numel() * dt_size(v.dt);
     rebind_input(in.second, fl.in_dev[i]);
   }
   OXB_CUDA(cudaEventRecord(fl.up, copy_stream_));
@@ -449,12 +468,18 @@ void Session::collect(oxb200_result* fetches, uint32_t n) {
   ctx_->counters.fences += 1;
   fl.busy = false;
   collect_idx_ ^= 1;
-  if (*fl.err_host != 0) {
+  if (*fl.err_host != 0 || fl.poisoned) {
+    // The error word is shared by the runs in flight: let the other run finish before the word is cleared (its
+    // kernels may still write it, and its own snapshot may already hold this run's code), and fail it as well.
     const int flag = *fl.err_host, zero = 0;
-    OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    fl.poisoned = false;
+    Flight& other = flight_[collect_idx_];
     OXB_CUDA(cudaStreamSynchronize(ctx_->stream()));
+    OXB_CUDA(cudaStreamSynchronize(down_stream_));
+    if (other.busy) other.poisoned = true;
+    OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
     for (auto* p : umma_plans_) k::umma_plan_reset_after_error(p);
-    raise(OXB200_FAILED, "a kernel reported code %d during a pipelined run; results are not valid", flag);
+    raise(OXB200_FAILED, "a kernel reported code %d during a pipelined run (or the run before it failed while this one was in flight); results are not valid", flag);
   }
   for (uint32_t i = 0; i < n; ++i) {
     const Value& v = values_[output_staging_[i].second];
@@ -464,5 +489,125 @@ void Session::collect(oxb200_result* fetches, uint32_t n) {
 }
 
 void Session::bind_external(const std::string& name, void* ptr, DT dt, Layout layout) { external_bind_[name] = {ptr, {dt, layout}}; }
+
+// ---- device I/O binding -------------------------------------------------------------------------
+bool Session::input_in_tensor_map(int value_index) const {
+  // the tensor-core steps build their operands' addresses into tensor maps at plan time
+  for (const Step& st : steps_) {
+    if (st.family != 0) continue;
+    for (int r : st.reads) {
+      int root = r;
+      while (values_[root].alias_of >= 0) root = values_[root].alias_of;
+      if (root == value_index) return true;
+    }
+  }
+  return false;
+}
+
+void Session::bind_input_device(const std::string& name, const void* ptr, DT dt, uint64_t len) {
+  if (in_flight() > 0) raise(OXB200_FAILED, "bind_input_device: pipelined runs are in flight; collect them first");
+  for (size_t i = 0; i < input_staging_.size(); ++i) {
+    if (input_staging_[i].first != name) continue;
+    const Value& v = values_[input_staging_[i].second];
+    if (external_bind_.count(name)) raise(OXB200_FAILED, "bind_input_device: '%s' is a resident dispatch operand", name.c_str());
+    if (dt != v.dt) raise(OXB200_FAILED, "bind_input_device: '%s' was planned as %s, the buffer is %s", name.c_str(), dt_name(v.dt), dt_name(dt));
+    if ((int64_t)len != v.numel()) raise(OXB200_FAILED, "bind_input_device: '%s' has %lld elements, the buffer %llu", name.c_str(), (long long)v.numel(), (unsigned long long)len);
+    if (!ptr || ((uintptr_t)ptr & 15) != 0) raise(OXB200_FAILED, "bind_input_device: the buffer of '%s' must be a 16-byte aligned device address", name.c_str());
+    if (own_in_ptr_.empty())
+      for (auto& in : input_staging_) own_in_ptr_.push_back(values_[in.second].ptr);
+    bound_in_[(int)i] = ptr;
+    return;
+  }
+  raise(OXB200_FAILED, "bind_input_device: '%s' is not an input of the planned graph", name.c_str());
+}
+
+void Session::bind_output_device(const std::string& name, void* ptr, uint64_t cap) {
+  for (size_t i = 0; i < output_staging_.size(); ++i) {
+    if (output_staging_[i].first != name) continue;
+    const Value& v = values_[output_staging_[i].second];
+    if (cap < (uint64_t)v.numel()) raise(OXB200_FAILED, "bind_output_device: '%s' has %lld lanes, the buffer holds %llu", name.c_str(), (long long)v.numel(), (unsigned long long)cap);
+    if (!ptr || ((uintptr_t)ptr & 3) != 0) raise(OXB200_FAILED, "bind_output_device: the buffer of '%s' must be a 4-byte aligned device address", name.c_str());
+    bound_out_[(int)i] = {ptr, cap};
+    return;
+  }
+  raise(OXB200_FAILED, "bind_output_device: '%s' is not an output of the planned graph", name.c_str());
+}
+
+void Session::output_device_ptr(const std::string& name, void** ptr, uint64_t* len) {
+  for (size_t i = 0; i < output_staging_.size(); ++i) {
+    if (output_staging_[i].first != name) continue;
+    const Value& v = values_[output_staging_[i].second];
+    if (ptr) *ptr = v.ptr;
+    if (len) *len = (uint64_t)v.numel();
+    return;
+  }
+  raise(OXB200_FAILED, "output_device_ptr: '%s' is not an output of the planned graph", name.c_str());
+}
+
+void Session::clear_bindings() {
+  if (!own_in_ptr_.empty())
+    for (size_t i = 0; i < input_staging_.size(); ++i) rebind_input(input_staging_[i].second, own_in_ptr_[i]);
+  bound_in_.clear();
+  bound_out_.clear();
+}
+
+// A bound input is read in place when no tensor map holds its buffer's address; otherwise its lanes are copied
+// device-to-device into the buffer the maps were built for (no host traffic either way).
+void Session::apply_input_bindings() {
+  for (auto& kv : bound_in_) {
+    const int vi = input_staging_[kv.first].second;
+    Value& v = values_[vi];
+    if (input_in_tensor_map(vi)) {
+      if (v.ptr != own_in_ptr_[kv.first]) rebind_input(vi, own_in_ptr_[kv.first]);
+      OXB_CUDA(cudaMemcpyAsync(v.ptr, kv.second, (size_t)v.numel() * dt_size(v.dt), cudaMemcpyDeviceToDevice, ctx_->stream()));
+    } else {
+      rebind_input(vi, const_cast<void*>(kv.second));
+    }
+  }
+}
+
+void Session::run_bound(const oxb200_operand* feeds, uint32_t n, oxb200_result* fetches, uint32_t nf, bool profile) {
+  if (in_flight() > 0) raise(OXB200_FAILED, "run_bound: pipelined runs are in flight; collect them first");
+  if (fetches && nf != outputs_.size()) raise(OXB200_FAILED, "run_bound: %u fetch slots for %zu graph outputs", nf, outputs_.size());
+  // unbound inputs come from the host as in run()
+  for (size_t i = 0; i < input_staging_.size(); ++i) {
+    if (bound_in_.count((int)i)) continue;
+    const auto& in = input_staging_[i];
+    if (external_bind_.count(in.first)) continue;
+    const oxb200_operand* f = nullptr;
+    for (uint32_t k2 = 0; k2 < n; ++k2)
+      if (feeds && feeds[k2].name && in.first == feeds[k2].name) f = &feeds[k2];
+    if (!f) raise(OXB200_FAILED, "run_bound: graph input '%s' is neither bound nor fed", in.first.c_str());
+    Value& v = values_[in.second];
+    const void* src = feed_lanes(*f, v, in.first.c_str());
+    OXB_CUDA(cudaMemcpyAsync(v.ptr, src, (size_t)v.numel() * dt_size(v.dt), cudaMemcpyHostToDevice, ctx_->stream()));
+    ctx_->counters.uploads += 1;
+    ctx_->counters.upload_bytes += (uint64_t)v.numel() * dt_size(v.dt);
+  }
+  apply_input_bindings();
+  run_steps(profile);
+  for (auto& kv : bound_out_) {
+    const Value& v = values_[output_staging_[kv.first].second];
+    if (v.numel() > 0 && kv.second.first != v.ptr)
+      OXB_CUDA(cudaMemcpyAsync(kv.second.first, v.ptr, (size_t)v.numel() * 4, cudaMemcpyDeviceToDevice, ctx_->stream()));
+  }
+  if (fetches) {
+    for (uint32_t i = 0; i < nf; ++i) {
+      const Value& v = values_[output_staging_[i].second];
+      if (fetches[i].lanes && fetches[i].cap < (uint64_t)v.numel())
+        raise(OXB200_FAILED, "run_bound: fetch buffer for '%s' holds %llu lanes, %lld needed", outputs_[i].c_str(), (unsigned long long)fetches[i].cap, (long long)v.numel());
+    }
+    for (uint32_t i = 0; i < nf; ++i) {
+      const Value& v = values_[output_staging_[i].second];
+      write_result_shape(v, &fetches[i]);
+      if (fetches[i].lanes && v.numel() > 0) {
+        OXB_CUDA(cudaMemcpyAsync(fetches[i].lanes, v.ptr, (size_t)v.numel() * 4, cudaMemcpyDeviceToHost, ctx_->stream()));
+        ctx_->counters.downloads += 1;
+        ctx_->counters.download_bytes += (uint64_t)v.numel() * 4;
+      }
+    }
+  }
+  finish_download();
+}
 
 }  // namespace oxb

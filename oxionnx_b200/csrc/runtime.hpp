@@ -19,6 +19,10 @@ namespace oxb {
 struct HostTensor {
   std::vector<float> data;
   std::vector<int64_t> shape;
+  // Element type the tensor was declared with where it came from (an ONNX initializer, a typed operand); F32 is
+  // the reference's dtype-erased default.  Only the quantised operators' y_zero_point reads it, to resolve the
+  // saturation range exactly (SatRange::for_dtype, quant_ops/mod.rs:216-222).
+  DT declared = DT::F32;
   int64_t numel() const { return prod(shape); }
 };
 
@@ -127,6 +131,16 @@ class Session {
   size_t arena_slots() const { return n_slots_; }
   // Bind a graph input to storage that already lives on the device (resident dispatch operand).
   void bind_external(const std::string& name, void* ptr, DT dt, Layout layout);
+  // Declared element type of a graph input (before plan()): 8-bit inputs are stored and fed as 8-bit lanes.
+  void declare_input_type(const std::string& name, DT dt) { input_types_[name] = dt; }
+  // Device I/O binding (after plan()): inputs read from, outputs also written to, caller-owned device buffers.
+  void bind_input_device(const std::string& name, const void* ptr, DT dt, uint64_t len);
+  void bind_output_device(const std::string& name, void* ptr, uint64_t cap);
+  void output_device_ptr(const std::string& name, void** ptr, uint64_t* len);
+  void clear_bindings();
+  // run_with_binding: uploads the unbound inputs, runs, copies bound outputs device-to-device, downloads the
+  // fetches that have host lanes; one fence
+  void run_bound(const oxb200_operand* feeds, uint32_t n, oxb200_result* fetches, uint32_t nf, bool profile);
   // After a run, detach the storage of an output so it can outlive the session.
   Value* find_value(const std::string& name);
   int check_error_flag();
@@ -152,9 +166,18 @@ class Session {
   size_t n_slots_ = 0;
   int* err_flag_ = nullptr;
   std::map<std::string, std::pair<void*, std::pair<DT, Layout>>> external_bind_;
+  std::map<std::string, DT> input_types_;
+  // device bindings: input index -> caller's buffer (copied into the input's own buffer when a tensor map holds
+  // that buffer's address, read in place otherwise); output index -> caller's buffer and capacity
+  std::map<int, const void*> bound_in_;
+  std::map<int, std::pair<void*, uint64_t>> bound_out_;
+  std::vector<void*> own_in_ptr_;  // the session's own buffer of each graph input (what an unbound input reads)
+  bool input_in_tensor_map(int value_index) const;
+  void apply_input_bindings();
   std::shared_ptr<void> planner_;  // keeps the objects the step closures refer to alive
   struct Flight {
     bool busy = false;
+    bool poisoned = false;           // the other run in flight failed while this one was running: its results are not trusted
     cudaEvent_t up = nullptr, done = nullptr, down = nullptr;
     std::vector<void*> in_dev;       // this slot's device buffer per graph input
     std::vector<float*> out_host;    // pinned staging per graph output
@@ -197,7 +220,7 @@ class Context {
   void set_profile(int on) { cfg_.profile = on ? 1 : 0; }
   void make_current();
 
-  void register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank);
+  void register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank, DT declared = DT::F32);
   const HostTensor* weight(const std::string& name) const;
   bool weight_resident(const std::string& name) const;
 

@@ -165,12 +165,16 @@ def build_resnet50_f32(batch=32, image=224, base=64, blocks=(3, 4, 6, 3), classe
     return graph, g.weights, feeds, dict(ops=2.0 * macs[0] * batch, macs_per_image=macs[0], batch=batch)
 
 
-def build_resnet50_qlinear(batch=128, image=224, base=64, blocks=(3, 4, 6, 3), classes=1000):
+def build_resnet50_qlinear(batch=128, image=224, base=64, blocks=(3, 4, 6, 3), classes=1000, typed_input=False):
     """The same topology as QLinearConv nodes: u8 activations (first scale fitted to N(0,1),
     zero point 128), i8 per-output-channel weights U[-127,127] with scales U[0.001,0.01], int32
     biases, output zero point 0 behind a ReLU (spelled as an explicit Relu node on the quantised
     lanes, so the reference's value-based saturation inference and the ONNX typed semantics
-    agree), residual joins as DequantizeLinear -> Add -> Relu -> QuantizeLinear."""
+    agree), residual joins as DequantizeLinear -> Add -> Relu -> QuantizeLinear.
+
+    typed_input: the graph input is the already quantised image, declared and fed as u8 lanes
+    (`input_q`, a quarter of the bytes of the f32 image); the QuantizeLinear of the f32 form is
+    then done by the feed generator with the same arithmetic, so both forms see the same lanes."""
     g = _G()
     r = _rng("c5")
     macs = [0]
@@ -200,7 +204,10 @@ def build_resnet50_qlinear(batch=128, image=224, base=64, blocks=(3, 4, 6, 3), c
         return y, f"{name}_ys", out_hw, (out_std * 0.6 if relu else out_std)
 
     g.w("in_scale", [np.float32(4.0 / 127.0)])
-    x = g.node("QuantizeLinear", ["input", "in_scale", "zp128"], ["input_q"], name="quantize_input")
+    if typed_input:
+        x = "input_q"
+    else:
+        x = g.node("QuantizeLinear", ["input", "in_scale", "zp128"], ["input_q"], name="quantize_input")
     hw = image
     x, xs, hw, std = qconv(x, "in_scale", "zp128", 1.0, 3, base, 7, 2, 3, True, hw, "stem")
     x = g.node("MaxPool", [x], ["pool_q"], name="pool", kernel_shape=[3, 3], strides=[2, 2], pads=[1, 1, 1, 1])
@@ -238,10 +245,15 @@ def build_resnet50_qlinear(batch=128, image=224, base=64, blocks=(3, 4, 6, 3), c
     fc, fcs, _, _ = qconv(q, "gap_scale", "zp128", std / 2.0, feat, classes, 1, 1, 0, False, 1, "fc")
     o = g.node("DequantizeLinear", [fc, fcs, "zp128"], ["fc_dq"], name="fc_dq")
     g.node("Flatten", [o], ["logits"], name="flatten", axis=1)
-    graph = Graph(nodes=g.nodes, input_names=["input"], output_names=["logits"])
+    graph = Graph(nodes=g.nodes, input_names=["input_q" if typed_input else "input"], output_names=["logits"])
 
     def feeds(b=batch, seed_tag="c5_in"):
-        return {"input": _rng(seed_tag).standard_normal((b, 3, image, image)).astype(np.float32)}
+        x = _rng(seed_tag).standard_normal((b, 3, image, image)).astype(np.float32)
+        if not typed_input:
+            return {"input": x}
+        # QuantizeLinear(scale 4/127, zero point 128) in f32: divide, round half to even, add, saturate
+        q = np.rint(x / np.float32(4.0 / 127.0)).astype(np.float32) + np.float32(128.0)
+        return {"input_q": np.clip(q, 0.0, 255.0).astype(np.uint8)}
 
     return graph, g.weights, feeds, dict(ops=2.0 * macs[0] * batch, macs_per_image=macs[0], batch=batch)
 

@@ -114,7 +114,7 @@ class CudaContext:
     """One device, one stream, session-lifetime weight residency."""
 
     def __init__(self, device: int = 0, *, verify=False, strict=False, residency=True, kernel_path="auto", keep_intermediates=False,
-                 profile=False, cuda_graph=False):
+                 profile=False, cuda_graph=False, requant_f64=False, split_k_max=0, cta_pairs="auto"):
         cfg = _ffi.Config()
         cfg.struct_size = ctypes.sizeof(_ffi.Config)
         cfg.verify, cfg.strict, cfg.residency = int(verify), int(strict), int(residency)
@@ -122,6 +122,9 @@ class CudaContext:
         cfg.keep_intermediates = int(keep_intermediates)
         cfg.profile = int(profile)
         cfg.cuda_graph = int(cuda_graph)
+        cfg.requant_f64 = int(requant_f64)
+        cfg.split_k_max = int(split_k_max)
+        cfg.cta_pairs = {"auto": 0, "never": 1, "always": 2}[cta_pairs]
         h = ctypes.c_void_p()
         st = _ffi.lib().oxb200_ctx_create(device, ctypes.byref(cfg), ctypes.byref(h))
         if st != _ffi.OK_HOST:
@@ -153,11 +156,14 @@ class CudaContext:
             pass
 
     def register_weights(self, weights: Dict[str, np.ndarray]):
+        """Initializers as f32 lanes.  An array that arrives as uint8 / int8 keeps that declared type beside its
+        lanes (an ONNX initializer's data_type), which makes a quantised operator saturate exactly to it."""
         for name, w in weights.items():
+            declared = _ffi.TYPED.get(np.asarray(w).dtype, _ffi.DT_F32)
             a = np.ascontiguousarray(np.asarray(w, dtype=np.float32))
             shape = (ctypes.c_uint64 * max(a.ndim, 1))(*a.shape)
-            st = _ffi.lib().oxb200_weight_register(self.handle, name.encode(), a.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), a.size, shape,
-                                                   a.ndim)
+            st = _ffi.lib().oxb200_weight_register_typed(self.handle, name.encode(), a.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), a.size, shape,
+                                                         a.ndim, declared)
             _raise_for(st, self.last_error())
             self._weights[name] = a.shape
 
@@ -171,6 +177,13 @@ class CudaContext:
 
     def release_device_caches(self):
         _raise_for(_ffi.lib().oxb200_release_device_caches(self.handle), self.last_error())
+
+    def probe_tensor_peak(self, kind: str) -> float:
+        """Operations per second of the tensor pipe for "i8" | "tf32" | "f16" | "bf16", measured on this device."""
+        rate = ctypes.c_double()
+        code = {"i8": 0, "tf32": 1, "f16": 2, "bf16": 3}[kind]
+        _raise_for(_ffi.lib().oxb200_probe_tensor_peak(self.handle, code, ctypes.byref(rate)), self.last_error())
+        return float(rate.value)
 
     def set_profiling(self, on: bool):
         """Per-node CUDA-event timing of planned runs, on or off, for the runs that follow."""
@@ -244,6 +257,7 @@ class SessionBuilder:
         self._device = 0
         self._ctx_kw = {}
         self._input_shapes = {}
+        self._input_types = {}
 
     def with_device(self, device: int):
         self._device = device
@@ -271,6 +285,11 @@ class SessionBuilder:
         self._ctx_kw["cuda_graph"] = on
         return self
 
+    def with_tuning(self, **kw):
+        """Kernel choices of the context: requant_f64, split_k_max, cta_pairs ("auto" | "never" | "always")."""
+        self._ctx_kw.update(kw)
+        return self
+
     def with_verify(self, on=True):
         self._ctx_kw["verify"] = on
         return self
@@ -279,8 +298,14 @@ class SessionBuilder:
         self._input_shapes = dict(shapes)
         return self
 
+    def with_input_types(self, types: Dict[str, object]):
+        """Declared element types of graph inputs (TensorInfo.dtype): np.uint8 / np.int8 inputs are stored, fed and
+        bound as 8-bit lanes instead of f32 lanes."""
+        self._input_types = dict(types)
+        return self
+
     def build_from_graph(self, graph: Graph, weights: Dict[str, np.ndarray]):
-        return Session(graph, weights, self._device, self._input_shapes, self._ctx_kw)
+        return Session(graph, weights, self._device, self._input_shapes, self._ctx_kw, getattr(self, "_input_types", None))
 
 
 class Session:
@@ -290,11 +315,12 @@ class Session:
     def builder() -> SessionBuilder:
         return SessionBuilder()
 
-    def __init__(self, graph, weights, device, input_shapes, ctx_kw):
+    def __init__(self, graph, weights, device, input_shapes, ctx_kw, input_types=None):
         self.graph = graph
         self.ctx = CudaContext(device, **ctx_kw)
         self.ctx.register_weights(weights)
         self._input_shapes = dict(input_shapes)
+        self._input_types = dict(input_types or {})  # name -> np.uint8 / np.int8 for inputs declared 8-bit
         self._planned_for = None
         self._out_bufs = None
 
@@ -310,6 +336,7 @@ class Session:
             sh = shapes[name]
             ins[i].shape = keep.add((ctypes.c_uint64 * max(len(sh), 1))(*sh))
             ins[i].rank = len(sh)
+            ins[i].dtype = _ffi.TYPED.get(np.dtype(self._input_types[name]), _ffi.DT_F32) if name in self._input_types else _ffi.DT_F32
         outs = keep.add((ctypes.c_char_p * max(len(self.graph.output_names), 1))(*[s.encode() for s in self.graph.output_names]))
         st = lib.oxb200_session_plan(self.ctx.handle, nodes, len(self.graph.nodes), ins, len(self.graph.input_names), outs,
                                      len(self.graph.output_names))
@@ -321,6 +348,10 @@ class Session:
         shapes = dict(self._input_shapes)
         if feeds is not None:
             shapes.update({k: tuple(np.asarray(v).shape) for k, v in feeds.items()})
+            if self._planned_for is None:  # a feed that arrives as 8-bit lanes declares its input 8-bit
+                for k, v in feeds.items():
+                    if isinstance(v, np.ndarray) and v.dtype in _ffi.TYPED:
+                        self._input_types.setdefault(k, v.dtype)
         if self._planned_for != {k: tuple(shapes[k]) for k in self.graph.input_names}:
             self._plan({k: tuple(shapes[k]) for k in self.graph.input_names})
 
@@ -394,6 +425,43 @@ class Session:
             out.append(self.collect())
             pending -= 1
         return out
+
+    # ---- device I/O binding (IoBinding / run_with_binding, extended to device memory) ----
+    def bind_input_device(self, name: str, device_ptr: int, dtype, count: int):
+        """Graph input `name` is read from the caller's device buffer by the following runs."""
+        code = _ffi.TYPED.get(np.dtype(dtype), _ffi.DT_F32)
+        _raise_for(_ffi.lib().oxb200_bind_input_device(self.ctx.handle, name.encode(), ctypes.c_void_p(device_ptr), code, count), self.ctx.last_error())
+
+    def bind_output_device(self, name: str, device_ptr: int, capacity: int):
+        """Graph output `name` (f32 lanes, logical order) is also written to the caller's device buffer."""
+        _raise_for(_ffi.lib().oxb200_bind_output_device(self.ctx.handle, name.encode(), ctypes.c_void_p(device_ptr), capacity), self.ctx.last_error())
+
+    def output_device_ptr(self, name: str):
+        """(device address, element count) of the library-owned buffer holding an output's f32 lanes after a run."""
+        p, n = ctypes.c_void_p(), ctypes.c_uint64()
+        _raise_for(_ffi.lib().oxb200_output_device_ptr(self.ctx.handle, name.encode(), ctypes.byref(p), ctypes.byref(n)), self.ctx.last_error())
+        return int(p.value or 0), int(n.value)
+
+    def run_with_binding(self, feeds: Optional[Dict[str, np.ndarray]] = None, fetch: bool = True) -> Optional[Dict[str, np.ndarray]]:
+        """One run with the current bindings: bound inputs are read on the device, unbound ones come from `feeds`;
+        with fetch=False nothing is read back (the outputs stay in their device buffers)."""
+        feeds = feeds or {}
+        keep = _ffi.Keep()
+        names = [n for n in self.graph.input_names if n in feeds]
+        ops = keep.add((_ffi.Operand * max(len(names), 1))())
+        for i, name in enumerate(names):
+            _ffi.pack_operand(ops[i], name, feeds[name], keep)
+        if not fetch:
+            st = _ffi.lib().oxb200_run_bound(self.ctx.handle, ops, len(names), None, 0)
+            _raise_for(st, self.ctx.last_error())
+            return None
+        res = self._results(keep)
+        st = _ffi.lib().oxb200_run_bound(self.ctx.handle, ops, len(names), res, len(self.graph.output_names))
+        _raise_for(st, self.ctx.last_error())
+        return {name: _ffi.result_array(res[i], self._out_bufs[i]) for i, name in enumerate(self.graph.output_names)}
+
+    def clear_bindings(self):
+        _raise_for(_ffi.lib().oxb200_clear_bindings(self.ctx.handle), self.ctx.last_error())
 
     # ---- measurement helpers: the same run split into stage / resident launches / read ----
     def upload(self, feeds):
