@@ -127,7 +127,8 @@ typedef struct {
   int32_t kernel_path;        /* 0 auto (tcgen05 where eligible), 1 force the direct CUDA-core kernels */
   int32_t keep_intermediates; /* 1: every value keeps a private arena slot (per-node inspection) */
   int32_t profile;            /* 1: record per-node CUDA-event timings during runs */
-  int32_t requant_f64;        /* 1: requantise with the two-pass f64 form even where the one-FMA form is proven exact */
+  int32_t requant_f64;        /* 1: requantise with the two-pass f64 form even where the one-FMA form is proven exact;
+                                 2: the one-FMA form, but never its packed 16-bit saturation */
   int32_t split_k_max;        /* most slices a long reduction may be split into (0: default 8, 1: never split) */
   int32_t cta_pairs;          /* 0 the tile model decides, 1 never pair CTAs (cta_group::2), 2 pair wherever the shape allows */
   int32_t reserved[5];
@@ -301,6 +302,43 @@ typedef struct {
 } oxb200_step_info;
 uint32_t oxb200_plan_step_count(const oxb200_ctx* ctx);
 int oxb200_plan_step_info(const oxb200_ctx* ctx, uint32_t index, oxb200_step_info* out);
+
+/* ---- ONNX models ------------------------------------------------------------------------ */
+
+/* What oxionnx_proto::load and the optimizer become on the host side of this provider (oxionnx-proto
+ * src/model.rs:45-355, src/reader.rs, src/parser.rs; root crate src/optimizer/mod.rs:134-167): a model file is
+ * parsed (protobuf wire format, no external dependency) into topologically sorted nodes, initializers as f32
+ * lanes with their declared element types, and graph inputs / outputs; `optimize` runs the reference's fusions
+ * for this path in its order -- MatMul+Add -> Gemm, Conv+BatchNormalization fold
+ * (src/optimizer/fusion/conv/batchnorm.rs:17-188), Conv+Relu / Conv+Clip (relu.rs:69-179), Conv+Clip(0,6)
+ * (relu6.rs:30), Mul(x, Sigmoid(x)) -> SiLU, the InstanceNorm-style chain -> OxiInstanceNorm
+ * (src/optimizer/fusion/instance_norm.rs:199-268), Conv+Add+Relu -> ConvAddRelu (conv/add_relu.rs:27-156) --
+ * and `session_plan_model` registers the initializers as the context's weights and plans the graph.  Features
+ * the provider does not take (external data files, subgraph attributes, sparse initializers, string tensors)
+ * are DECLINED with a message. */
+typedef struct oxb200_model oxb200_model;
+int oxb200_model_load(const void* bytes, uint64_t len, oxb200_model** out);
+int oxb200_model_load_file(const char* path, oxb200_model** out);
+void oxb200_model_free(oxb200_model* model);
+/* level 0: nothing; 1: the passes above.  `removed` (optional) receives the number of nodes fused away. */
+int oxb200_model_optimize(oxb200_model* model, int32_t level, uint32_t* removed);
+/* One pass by the reference's function name ("fuse_conv_batchnorm", "fuse_conv_relu", "fuse_conv_clip_to_conv_relu6",
+ * "fuse_instance_norm", "fuse_matmul_add", "fuse_mul_sigmoid_to_silu", "fuse_conv_add_relu"). */
+int oxb200_model_run_pass(oxb200_model* model, const char* pass, uint32_t* removed);
+/* Views into the model; they stay valid until the model is optimised again or freed.  A symbolic or missing input
+ * dimension reads as UINT64_MAX; an input's dtype is an OXB200_DT_* code, or -1 for a type the boundary does not take. */
+uint32_t oxb200_model_node_count(const oxb200_model* model);
+int oxb200_model_node(oxb200_model* model, uint32_t index, oxb200_node* out);
+uint32_t oxb200_model_input_count(const oxb200_model* model);
+int oxb200_model_input(oxb200_model* model, uint32_t index, oxb200_value_info* out);
+uint32_t oxb200_model_output_count(const oxb200_model* model);
+const char* oxb200_model_output_name(const oxb200_model* model, uint32_t index);
+uint32_t oxb200_model_initializer_count(const oxb200_model* model);
+int oxb200_model_initializer(oxb200_model* model, uint32_t index, oxb200_operand* out); /* name, f32 lanes, shape, declared dtype */
+/* Session::from_file + build (root crate src/session/loading.rs:181): the model's initializers become the
+ * context's weights (typed), its graph is planned.  `shapes` supplies the concrete shape of every input that has
+ * a symbolic dimension (and may override the others). */
+int oxb200_session_plan_model(oxb200_ctx* ctx, oxb200_model* model, const oxb200_value_info* shapes, uint32_t n_shapes);
 
 /* ---- allocation-free entry point -------------------------------------------------------- */
 

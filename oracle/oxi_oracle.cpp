@@ -1669,6 +1669,47 @@ void op_resize(Ctx& c) {
   }
 }
 
+// BatchNormalization, inference form: oxionnx-ops/src/nn/normalization.rs:132-166 --
+// out = (x - mean) * (1 / sqrt(var + eps)) * scale + bias, each step rounded to f32 in that order.
+void op_batch_norm(Ctx& c) {
+  const oxo_tensor& x = c.input(0);
+  if (x.rank < 2) fail(OXO_ERR_SHAPE_MISMATCH, "batch_norm: need at least 2D");
+  const oxo_tensor &scale = c.input(1), &bias = c.input(2), &mean = c.input(3), &var = c.input(4);
+  const int64_t n = x.shape[0], ch = x.shape[1];
+  for (const oxo_tensor* t : {&scale, &bias, &mean, &var})
+    if (t->len < ch) fail(OXO_ERR_SHAPE_MISMATCH, "batch_norm: a parameter has %lld entries, expected %lld", (long long)t->len, (long long)ch);
+  int64_t spatial = 1;
+  for (int d = 2; d < x.rank; ++d) spatial *= x.shape[d];
+  const float eps = c.attrs.f("epsilon", 1e-5f);
+  alloc_out(c.out[0], std::vector<int64_t>(x.shape, x.shape + x.rank));
+  float* y = c.out[0].data;
+  for (int64_t ni = 0; ni < n; ++ni)
+    for (int64_t ci = 0; ci < ch; ++ci) {
+      const float inv_std = 1.0f / std::sqrt(var.data[ci] + eps);
+      const float s = scale.data[ci], b = bias.data[ci], m = mean.data[ci];
+      const int64_t base = (ni * ch + ci) * spatial;
+      for (int64_t si = 0; si < spatial; ++si) {
+        volatile float d = x.data[base + si] - m;
+        volatile float t = d * inv_std;
+        volatile float u = t * s;
+        y[base + si] = u + b;
+      }
+    }
+}
+
+// ConvAddRelu, the node fuse_conv_add_relu emits (src/optimizer/fusion/conv/add_relu.rs:27-156): inputs
+// (x, w, bias or "", residual) and the Conv's attributes; its value is the unfused chain's,
+// relu(conv(x, w, bias) + residual), every step rounded to f32.
+void op_conv_add_relu(Ctx& c) {
+  if (c.n_in < 4) fail(OXO_ERR_SHAPE_MISMATCH, "ConvAddRelu: expected inputs (x, w, bias, residual)");
+  Ctx conv{c.op, c.in, 3, c.attrs, c.out, c.n_out};
+  op_conv(conv);
+  const oxo_tensor& r = c.input(3);
+  oxo_tensor& y = c.out[0];
+  if (r.len != y.len) fail(OXO_ERR_SHAPE_MISMATCH, "ConvAddRelu: residual has %lld entries, the convolution %lld", (long long)r.len, (long long)y.len);
+  for (int64_t i = 0; i < y.len; ++i) y.data[i] = std::max(y.data[i] + r.data[i], 0.0f);
+}
+
 struct OpEntry {
   const char* name;
   void (*fn)(Ctx&);
@@ -1695,7 +1736,10 @@ const OpEntry kOps[] = {
     {"Tanh", [](Ctx& c) { unary_op(c, [](float v) { return std::tanh(v); }); }, 1},
     {"Sigmoid", [](Ctx& c) { unary_op(c, [](float v) { return 1.0f / (1.0f + std::exp(-v)); }); }, 1},
     {"Silu", [](Ctx& c) { unary_op(c, [](float v) { return v / (1.0f + std::exp(-v)); }); }, 1},
+    {"SiLU", [](Ctx& c) { unary_op(c, [](float v) { return v / (1.0f + std::exp(-v)); }); }, 1},
     {"PRelu", op_prelu, 1},
+    {"BatchNormalization", op_batch_norm, 1},
+    {"ConvAddRelu", op_conv_add_relu, 1},
     {"MaxPool", op_max_pool, 1},
     {"GlobalAveragePool", op_global_average_pool, 1},
     {"Flatten", op_flatten, 1},

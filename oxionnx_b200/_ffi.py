@@ -112,6 +112,20 @@ SYMBOLS = {
     "oxb200_fetch_value": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(Result)]),
     "oxb200_plan_step_count": (ctypes.c_uint32, [ctypes.c_void_p]),
     "oxb200_plan_step_info": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32, _P(StepInfo)]),
+    "oxb200_model_load": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint64, _P(ctypes.c_void_p)]),
+    "oxb200_model_load_file": (ctypes.c_int, [ctypes.c_char_p, _P(ctypes.c_void_p)]),
+    "oxb200_model_free": (None, [ctypes.c_void_p]),
+    "oxb200_model_optimize": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, _P(ctypes.c_uint32)]),
+    "oxb200_model_run_pass": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, _P(ctypes.c_uint32)]),
+    "oxb200_model_node_count": (ctypes.c_uint32, [ctypes.c_void_p]),
+    "oxb200_model_node": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32, _P(CNode)]),
+    "oxb200_model_input_count": (ctypes.c_uint32, [ctypes.c_void_p]),
+    "oxb200_model_input": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32, _P(ValueInfo)]),
+    "oxb200_model_output_count": (ctypes.c_uint32, [ctypes.c_void_p]),
+    "oxb200_model_output_name": (ctypes.c_char_p, [ctypes.c_void_p, ctypes.c_uint32]),
+    "oxb200_model_initializer_count": (ctypes.c_uint32, [ctypes.c_void_p]),
+    "oxb200_model_initializer": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32, _P(Operand)]),
+    "oxb200_session_plan_model": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, _P(ValueInfo), ctypes.c_uint32]),
     "oxb200_dynamic_quantize_linear_noalloc": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p,
                                                               ctypes.c_void_p]),
 }

@@ -30,8 +30,10 @@ SOURCES = {
     "runtime.cpp": COMMON,
     "planner.cpp": COMMON,
     "abi.cpp": COMMON,
+    "onnx_model.cpp": COMMON,
+    "model_abi.cpp": COMMON,
 }
-HEADERS = ["common.hpp", "kernels.hpp", "runtime.hpp", "umma_kernel.cuh", "umma_launch.cuh", os.path.join("..", "..", "include", "oxb200.h")]
+HEADERS = ["common.hpp", "kernels.hpp", "runtime.hpp", "umma_kernel.cuh", "umma_launch.cuh", "model.hpp", "abi_internal.hpp", os.path.join("..", "..", "include", "oxb200.h")]
 
 
 def _nvcc():

@@ -9,13 +9,7 @@
 
 using namespace oxb;
 
-struct oxb200_ctx {
-  Context impl;
-  oxb200_ctx(int device, const oxb200_config& cfg) : impl(device, cfg) {}
-};
-struct oxb200_tensor {
-  DeviceTensorHandle h;
-};
+#include "abi_internal.hpp"
 
 namespace {
 

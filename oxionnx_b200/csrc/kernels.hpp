@@ -180,6 +180,7 @@ struct Epilogue {
   const float* combined = nullptr;
   int64_t acc_abs_bound = 0;  // when > 0: no |raw + bias - x_zp * wsum| of this layer can exceed it (from the weights)
   int combined_fma_ok = 0;  // every combined[oc] is 0 or has 2^-21 <= |c| <= 2^40: the one-FMA requantisation is exact
+  double q_abs_bound = 0;   // when > 0: no |acc * combined[oc] + y_zp| of this layer can exceed it (from acc_abs_bound and the scales)
   int y_zp = 0;
   int lo = 0, hi = 255;
   int relu_fused = 0;  // integer: clamp below at max(lo, 0) (a following Relu node)
@@ -230,8 +231,8 @@ bool umma_overlapping_positions_ok();
 struct UmmaPlan;
 // kind: 0 = i8 (A u8/s8, B s8/u8, s32 accumulate), 1 = tf32 (f32 storage, f32 accumulate), 2 = f16, 3 = bf16
 // (16-bit storage, f32 accumulate).  Returns nullptr with `why` filled when the shape is not eligible.
-// Choices a context may override (oxb200_config): `requant_f64` keeps the two-pass f64 requantisation even where
-// the one-FMA form is proven; `split_k_max` bounds the slices of a split reduction (0: the default of 8, 1: never
+// Choices a context may override (oxb200_config): `requant_f64` 1 keeps the two-pass f64 requantisation even where
+// the one-FMA form is proven, 2 keeps the one-FMA form without the packed 16-bit saturation; `split_k_max` bounds the slices of a split reduction (0: the default of 8, 1: never
 // split); `cta_pairs` 0 lets the tile model decide, 1 never pairs CTAs, 2 pairs them wherever the shape allows.
 struct UmmaTuning {
   int requant_f64 = 0;

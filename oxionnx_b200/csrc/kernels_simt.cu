@@ -31,6 +31,7 @@ struct EpiDev {
   const float* bias_f;
   int act;
   float clip_lo, clip_hi;
+  const float* slope;  // act 4 (PRelu): one slope per output channel
   int round_tf32;
   const float* residual;
   const int32_t* bias_i;
@@ -152,6 +153,8 @@ __global__ void conv_direct_kernel(const TX* __restrict__ x, const TW* __restric
       if (e.residual) v = __fadd_rn(v, e.residual[idx]);
       if (e.act == 1) v = fmaxf(v, 0.f);
       else if (e.act == 2) v = fminf(fmaxf(v, e.clip_lo), e.clip_hi);
+      else if (e.act == 3) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));  // silu
+      else if (e.act == 4) v = v >= 0.f ? v : __fmul_rn(v, e.slope[oc]);  // prelu
       if (e.round_tf32) v = round_tf32(v);
       ((float*)out)[idx] = v;
     }
@@ -205,7 +208,7 @@ void launch_conv(const void* x, const void* w, void* out, const ConvShape& cs, c
 
 void conv_direct(const void* x, DT x_dt, int x_plain_nchw, const void* w, DT w_dt, void* out, const ConvShape& cs, const Epilogue& ep,
                  cudaStream_t s) {
-  EpiDev e{ep.mode,     ep.bias_f,    ep.act,  ep.clip_lo, ep.clip_hi,  ep.round_tf32, ep.residual, ep.bias_i, ep.x_zp, ep.x_zp_dev,
+  EpiDev e{ep.mode,     ep.bias_f,    ep.act,  ep.clip_lo, ep.clip_hi,  ep.slope, ep.round_tf32, ep.residual, ep.bias_i, ep.x_zp, ep.x_zp_dev,
            ep.x_zp_rows, ep.w_zp,     ep.n_w_zp, ep.combined, ep.y_zp,  ep.relu_fused && ep.lo < 0 ? 0 : ep.lo, ep.hi, ep.out_dt, ep.dq_w_scale, ep.dq_x_scale_dev, ep.dq_bias, ep.dq_act};
   if (ep.mode == EPI_F32) {
     if (x_dt != DT::F32 || w_dt != DT::F32) OXB_FAIL("conv_direct: float epilogue needs f32 operands");

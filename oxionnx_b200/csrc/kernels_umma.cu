@@ -409,10 +409,12 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.mode = e.mode;
   if (e.mode == EPI_F32) kp.variant = (e.residual ? V_F32_RES : V_F32_BASE) + e.act * 2 + (e.round_tf32 ? 1 : 0);
   else if (e.mode == EPI_REQUANT) {
-    const bool fma = e.combined_fma_ok && !tune.requant_f64;
+    const bool fma = e.combined_fma_ok && tune.requant_f64 != 1;
     const bool lean = fma && e.acc_abs_bound > 0 && e.acc_abs_bound < 16777216;
+    // packed saturation: 8-bit lanes, every result provably inside int16 (margin for the rounding and the clamp bounds)
+    const bool packed = lean && e.bias_if && tune.requant_f64 == 0 && dt_size(e.out_dt) == 1 && e.q_abs_bound > 0 && e.q_abs_bound < 32000.0;
     if (e.x_zp_dev) kp.variant = lean ? V_REQUANT_LEAN_DYN : (fma ? V_REQUANT_FMA_DYN : V_REQUANT_DYN);
-    else kp.variant = lean ? (e.bias_if ? V_REQUANT_FBIAS : V_REQUANT_LEAN) : (fma ? V_REQUANT_FMA : V_REQUANT);
+    else kp.variant = lean ? (packed ? V_REQUANT_PACKED : (e.bias_if ? V_REQUANT_FBIAS : V_REQUANT_LEAN)) : (fma ? V_REQUANT_FMA : V_REQUANT);
   }
   else if (e.mode == EPI_DEQUANT) kp.variant = V_DEQUANT + (e.x_zp_dev ? 1 : 0) + 2 * e.dq_act;
   else kp.variant = e.x_zp_dev ? V_INT32_DYN : V_INT32;

@@ -28,7 +28,7 @@ const char* kSupportedOps[] = {"Conv",       "Gemm",     "MatMul",  "QLinearConv
                                "Add",        "Sub",      "Mul",     "Div",         "MaxPool",       "GlobalAveragePool", "OxiInstanceNorm",
                                "Resize",     "Pad",      "Concat",  "Flatten",     "Reshape",       "Identity",          "Cast",
                                "Slice",      "Gather",   "Transpose", "Softmax",   "LayerNormalization", "LayerNorm",    "Gelu",
-                               "Erf"};
+                               "Erf",        "ConvAddRelu", "Silu",  "SiLU"};
 
 // ---- scalar helpers that must agree with the reference bit for bit -----------------------
 double round_ties_even(double v) { return std::nearbyint(v); }  // default rounding mode: ties to even
@@ -166,6 +166,7 @@ bool accepts_resident_slot(const std::string& op, uint32_t slot) {
   if (op == "QLinearMatMul") return slot == 0;
   if (op == "MatMulInteger") return slot == 0 || slot == 2;  // A and the dynamic a_zero_point
   if (op == "ConvInteger" || op == "Conv") return slot == 0;
+  if (op == "ConvAddRelu") return slot == 0 || slot == 3;  // the activation and the residual
   if (op == "Gemm") return slot == 0;
   if (op == "MatMul" || op == "Add" || op == "Sub" || op == "Mul" || op == "Div") return slot <= 1;
   if (op == "Concat") return true;
@@ -412,6 +413,7 @@ class Planner {
     std::vector<int32_t> x_zp_rows;
     std::vector<int32_t> bias_i;  // empty or OC
     std::vector<float> bias_f;    // empty or OC
+    std::vector<float> slope;     // PRelu epilogue: OC slopes
     std::vector<float> combined;  // OC
     float w_scale_mul = 1.0f;     // Gemm alpha folded into the packed weights
     double algorithmic_ops = 0;   // ops of the node as written (a rewritten stem pads its reduction)
@@ -595,9 +597,9 @@ void Planner::plan_node(int ni) {
     return plan_dequantize(n);
   }
   if (op == "DynamicQuantizeLinear") return plan_dynamic_quantize(n);
-  if (op == "Conv" || op == "QLinearConv" || op == "ConvInteger") return plan_conv_family(n, ni);
+  if (op == "Conv" || op == "QLinearConv" || op == "ConvInteger" || op == "ConvAddRelu") return plan_conv_family(n, ni);
   if (op == "Gemm" || op == "MatMul" || op == "QLinearMatMul" || op == "MatMulInteger") return plan_matmul_family(n, ni);
-  if (op == "Relu" || op == "Tanh" || op == "Sigmoid") return plan_unary(n);
+  if (op == "Relu" || op == "Tanh" || op == "Sigmoid" || op == "Silu" || op == "SiLU") return plan_unary(n);
   if (op == "Add" || op == "Sub" || op == "Mul" || op == "Div") return plan_binary(n, ni);
   if (op == "PRelu") return plan_prelu(n);
   if (op == "MaxPool") return plan_max_pool(n);
@@ -933,6 +935,9 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
           const float a = std::fabs(v);
           if (!(a == 0.f || (a >= 4.76837158203125e-07f && a <= 1099511627776.0f))) epi.combined_fma_ok = 0;
         }
+        double cmax = 0.0;
+        for (float v : comb) cmax = std::max(cmax, (double)std::fabs(v));
+        epi.q_abs_bound = (double)acc_abs_bound * cmax * 1.0001 + std::fabs((double)epi.y_zp) + 1.0;
         comb.resize(padded, 0.f);
         epi.combined = upload_vec(comb);
       }
@@ -940,6 +945,11 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
       std::vector<float> bias = c.bias_f;
       bias.resize(align_up((size_t)OC, 256), 0.f);
       epi.bias_f = upload_vec(bias);
+      if (epi.act == 4) {
+        std::vector<float> sl = c.slope;
+        sl.resize(align_up((size_t)OC, 256), 0.f);
+        epi.slope = upload_vec(sl);
+      }
     }
     Step& st = add_step(n, "umma", 0, reads, {out_vi});
     st.work = c.algorithmic_ops > 0 ? c.algorithmic_ops : cs.ops();
@@ -1017,6 +1027,7 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
       if (epi.mode == k::EPI_REQUANT) epi.combined = upload_vec(c.combined);
     } else {
       epi.bias_f = c.bias_f.empty() ? nullptr : upload_vec(c.bias_f);
+      if (epi.act == 4) epi.slope = upload_vec(c.slope);
     }
     Step& st = add_step(n, "direct", 1, reads, {out_vi});
     st.kernel = std::string("direct_") + (c.is_int ? "int" : "f32") + (why.empty() ? "" : (" (" + why + ")"));
@@ -1269,8 +1280,15 @@ bool Planner::try_window_stem(const NodeDef& n, Contraction& c, int src_vi) {
 void Planner::plan_conv_family(const NodeDef& n, int ni) {
   (void)ni;
   const std::string& op = n.op;
-  const bool is_q = op == "QLinearConv", is_ci = op == "ConvInteger", is_f = op == "Conv";
-  if (is_f) check_attrs(n, {"strides", "pads", "dilations", "group", "auto_pad", "kernel_shape", "activation", "activation_min", "activation_max"});
+  // ConvAddRelu (src/optimizer/fusion/conv/add_relu.rs:114-156): inputs (x, w, bias or "", residual), the Conv's
+  // attributes plus fused_ops = "Add,Relu"; relu(conv(x, w, bias) + residual)
+  const bool is_car = op == "ConvAddRelu";
+  const bool is_q = op == "QLinearConv", is_ci = op == "ConvInteger", is_f = op == "Conv" || is_car;
+  if (is_car) {
+    check_attrs(n, {"strides", "pads", "dilations", "group", "auto_pad", "kernel_shape", "fused_ops"});
+    if (n.attrs.s("fused_ops") != "Add,Relu") OXB_DECLINE("ConvAddRelu '%s': fused_ops is not \"Add,Relu\"", n.name.c_str());
+    if (!has_in(n, 3)) OXB_DECLINE("ConvAddRelu '%s': no residual operand", n.name.c_str());
+  } else if (is_f) check_attrs(n, {"strides", "pads", "dilations", "group", "auto_pad", "kernel_shape", "activation", "activation_min", "activation_max"});
   else check_attrs(n, {"strides", "pads", "dilations", "group", "auto_pad", "kernel_shape"});
   const size_t w_slot = is_q ? 3 : 1;
   const HostTensor* w = const_in(n, w_slot);
@@ -1354,10 +1372,19 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
     } else {
       c.x_vi = ensure_layout(n, xi, Layout::NHWC);
     }
+    if (is_car) {
+      // the residual rides in the epilogue when it is a device-resident f32 tensor of the output's shape (brought
+      // to channels-last first if need be); the sum and the Relu round as the separate nodes would
+      int ri = value_of(in_name(n, 3));
+      if (V(ri).dt != DT::F32 || V(ri).shape != out_shape) OXB_DECLINE("ConvAddRelu '%s': the residual is not an f32 tensor of the output's shape", n.name.c_str());
+      ri = ensure_layout(n, ri, Layout::NHWC);
+      c.res_vi = ri;
+      c.epi.act = 1;
+    }
     // Conv -> Add(other) [-> Relu] with `other` already on the device in the same layout: the
     // addition (and the Relu) move into this convolution's epilogue; the two float additions
     // round exactly as the separate nodes would.
-    if (c.epi.act == 0 && !C.cfg().keep_intermediates && cs.OC % 32 == 0 && !graph_outputs_.count(out_name)) {
+    if (!is_car && c.epi.act == 0 && !C.cfg().keep_intermediates && cs.OC % 32 == 0 && !graph_outputs_.count(out_name)) {
       auto it = consumers_.find(out_name);
       if (it != consumers_.end() && it->second.size() == 1) {
         const int add_i = it->second[0].first, slot = it->second[0].second;
@@ -1376,6 +1403,39 @@ void Planner::plan_conv_family(const NodeDef& n, int ni) {
                 c.epi.act = 1;
                 out_name = nodes_[relu_i].outputs[0];
               }
+            }
+          }
+        }
+      }
+    }
+    // Conv -> SiLU and Conv -> PRelu(constant slope, scalar or per channel): these activations have no fused-Conv
+    // spelling in the reference's optimizer; they arrive as separate nodes and move into the epilogue here, the
+    // value at the activation's output being what the separate node would give.
+    if (c.epi.act == 0 && c.res_vi < 0 && !C.cfg().keep_intermediates && !graph_outputs_.count(out_name)) {
+      int silu_i = sole_consumer(out_name, "Silu");
+      if (silu_i < 0) silu_i = sole_consumer(out_name, "SiLU");
+      if (silu_i >= 0 && nodes_[silu_i].inputs.size() == 1) {
+        skipped_[silu_i] = 1;
+        c.epi.act = 3;
+        out_name = nodes_[silu_i].outputs[0];
+      } else {
+        auto it = consumers_.find(out_name);
+        if (it != consumers_.end() && it->second.size() == 1 && it->second[0].second == 0) {
+          const int pi = it->second[0].first;
+          const NodeDef& pr = nodes_[pi];
+          const HostTensor* slope = (pr.op == "PRelu" && !skipped_[pi] && pr.inputs.size() == 2 && pr.attrs.names().empty()) ? const_of(pr.inputs[1]) : nullptr;
+          if (slope && S.index_.find(pr.inputs[1]) == S.index_.end()) {
+            const int64_t ns = slope->numel();
+            int64_t nontrivial = 0;
+            for (int64_t d : slope->shape) nontrivial += d != 1;
+            // scalar, or one value per channel shaped [C,1,1] / [1,C,1,1] (numpy broadcasting against [N,C,H,W])
+            const bool per_channel = ns == cs.OC && ns > 1 && nontrivial == 1 && slope->shape.size() >= 3 && slope->shape[slope->shape.size() - 3] == ns;
+            if (ns == 1 || per_channel) {
+              c.slope.assign((size_t)cs.OC, slope->data[0]);
+              if (per_channel) c.slope = slope->data;
+              skipped_[pi] = 1;
+              c.epi.act = 4;
+              out_name = pr.outputs[0];
             }
           }
         }
@@ -1827,7 +1887,7 @@ void Planner::plan_unary(const NodeDef& n) {
   else check_attrs(n, {});
   int xi = value_of(in_name(n, 0));
   const Value xv = V(xi);
-  int op = n.op == "Relu" ? k::UN_RELU : (n.op == "Tanh" ? k::UN_TANH : k::UN_SIGMOID);
+  int op = n.op == "Relu" ? k::UN_RELU : (n.op == "Tanh" ? k::UN_TANH : ((n.op == "Silu" || n.op == "SiLU") ? k::UN_SILU : k::UN_SIGMOID));
   // Gelu: exact unless approximate == "tanh" (nn_ops/activations.rs:357-386); Erf: the same polynomial
   if (n.op == "Gelu") op = n.attrs.s("approximate") == "tanh" ? k::UN_GELU_TANH : k::UN_GELU_ERF;
   if (n.op == "Erf") op = k::UN_ERF;

@@ -301,6 +301,7 @@ enum {
   V_REQUANT_LEAN = 26,
   V_REQUANT_LEAN_DYN = 27,
   V_REQUANT_FBIAS = 28,  // LEAN with the bias added as a float after the conversion
+  V_REQUANT_PACKED = 29, // FBIAS with the saturation done on packed 16-bit lanes (8-bit outputs of bounded magnitude)
   V_DEQUANT = 30         // 30..35: dequantising variants, + (dynamic zero point ? 1 : 0) + 2 * activation
 };
 
@@ -510,6 +511,59 @@ __device__ __forceinline__ void math_requant_fma(const KParams& p, const uint32_
   }
 }
 
+// Two f32 operations in one instruction (add.rn.f32x2 / fma.rn.f32x2): the same IEEE results lane by lane, half
+// the issue slots.
+__device__ __forceinline__ void add2(float& x0, float& x1, float y0, float y1) {
+  uint64_t a, b, d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(x0), "f"(x1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(y0), "f"(y1));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(d));
+}
+__device__ __forceinline__ void fma2(float& x0, float& x1, float y0, float y1, float z) {
+  uint64_t a, b, c, d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(x0), "f"(x1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(y0), "f"(y1));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c) : "f"(z));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(d));
+}
+
+// The one-FMA requantisation (see math_requant_fma; the float-bias form) for 8-bit outputs whose magnitude the
+// host has bounded below 2^15 from the weights and the scales: the rounded result sits in the low mantissa bits
+// of s = fma(a, c, 1.5 * 2^23 + zp), and because 1.5 * 2^23 has sixteen zero low bits, the low half-word of s is
+// the result itself as a two's-complement int16.  Two results are packed into one register and saturated together
+// with one packed min/max (a single instruction when the lower bound is 0, as behind a fused Relu), then four
+// are packed into a word: 2.25 integer-pipe instructions per output instead of 3.75.  Bit-identical to the
+// unpacked form wherever that bound holds, which is checked per layer at plan time.
+template <bool RELU>
+__device__ __forceinline__ void math_requant_packed(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias_f,
+                                                    const float* __restrict__ comb, uint32_t (&w)[32]) {
+  const float magic_zp = 12582912.0f + (float)p.y_zp;
+  const uint32_t lo2 = ((uint32_t)p.lo & 0xffffu) * 0x00010001u, hi2 = ((uint32_t)p.hi & 0xffffu) * 0x00010001u;
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const float4 b = __ldg(reinterpret_cast<const float4*>(bias_f) + j4);
+    const float4 c = __ldg(reinterpret_cast<const float4*>(comb) + j4);
+    float a0 = __int2float_rn((int32_t)v[4 * j4]), a1 = __int2float_rn((int32_t)v[4 * j4 + 1]);
+    float a2 = __int2float_rn((int32_t)v[4 * j4 + 2]), a3 = __int2float_rn((int32_t)v[4 * j4 + 3]);
+    add2(a0, a1, b.x, b.y);
+    add2(a2, a3, b.z, b.w);
+    fma2(a0, a1, c.x, c.y, magic_zp);
+    fma2(a2, a3, c.z, c.w, magic_zp);
+    uint32_t p01 = __byte_perm(__float_as_uint(a0), __float_as_uint(a1), 0x5410);
+    uint32_t p23 = __byte_perm(__float_as_uint(a2), __float_as_uint(a3), 0x5410);
+    if (RELU) {
+      p01 = __vimin_s16x2_relu(p01, hi2);
+      p23 = __vimin_s16x2_relu(p23, hi2);
+    } else {
+      p01 = __vmins2(__vmaxs2(p01, lo2), hi2);
+      p23 = __vmins2(__vmaxs2(p23, lo2), hi2);
+    }
+    w[j4] = __byte_perm(p01, p23, 0x6420);
+  }
+}
+
 // erf by the reference's polynomial (Abramowitz-Stegun 7.1.26, nn_ops/activations.rs:578), same operation order.
 __device__ __forceinline__ float erf_poly(float x) {
   const float sign = x >= 0.0f ? 1.0f : -1.0f;
@@ -578,7 +632,11 @@ __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t 
   else if constexpr (VARIANT == V_REQUANT_FMA_DYN) math_requant_fma<true, true, false>(p, v, p.bias_i + oc, nullptr, p.wsum + oc, p.combined + oc, xz, esz, w);
   else if constexpr (VARIANT == V_REQUANT_LEAN) math_requant_fma<false, false, false>(p, v, p.bias_i + oc, nullptr, nullptr, p.combined + oc, xz, esz, w);
   else if constexpr (VARIANT == V_REQUANT_LEAN_DYN) math_requant_fma<true, false, false>(p, v, p.bias_i + oc, nullptr, p.wsum + oc, p.combined + oc, xz, esz, w);
-  else math_requant_fma<false, false, true>(p, v, nullptr, p.bias_if + oc, nullptr, p.combined + oc, xz, esz, w);
+  else if constexpr (VARIANT == V_REQUANT_FBIAS) math_requant_fma<false, false, true>(p, v, nullptr, p.bias_if + oc, nullptr, p.combined + oc, xz, esz, w);
+  else {
+    if (p.lo == 0) math_requant_packed<true>(p, v, p.bias_if + oc, p.combined + oc, w);
+    else math_requant_packed<false>(p, v, p.bias_if + oc, p.combined + oc, w);
+  }
 }
 
 // Direct store of a packed 32-channel run (ragged channel counts, unaligned rows).
@@ -1056,6 +1114,7 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
         OXB_EPI(V_REQUANT_LEAN)
         OXB_EPI(V_REQUANT_LEAN_DYN)
         OXB_EPI(V_REQUANT_FBIAS)
+        OXB_EPI(V_REQUANT_PACKED)
         OXB_EPI(30)
         OXB_EPI(31)
         OXB_EPI(32)

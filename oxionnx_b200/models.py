@@ -111,6 +111,16 @@ def _conv_out(size, k, s, p):
     return (size + 2 * p - k) // s + 1
 
 
+def fold_batchnorm(w, b, gamma, beta, mean, var, eps):
+    """fuse_conv_batchnorm's arithmetic (src/optimizer/fusion/conv/batchnorm.rs:126-144), in f32 like the reference:
+    inv_std = 1 / sqrt(var + eps); factor = gamma * inv_std; W' = W * factor per output channel; b' = (b - mean) * factor + beta, with b = 0
+    when the convolution has no bias."""
+    f32 = np.float32
+    factor = (gamma.astype(f32) * (f32(1.0) / np.sqrt(var.astype(f32) + f32(eps)))).astype(f32)
+    b = np.zeros(w.shape[0], f32) if b is None else b.astype(f32)
+    return (w.astype(f32) * factor.reshape((-1,) + (1,) * (w.ndim - 1))).astype(f32), ((b - mean.astype(f32)) * factor + beta.astype(f32)).astype(f32)
+
+
 def build_resnet50_f32(batch=32, image=224, base=64, blocks=(3, 4, 6, 3), classes=1000):
     """ResNet-50 v1.5, BatchNorm folded into the convolutions, fused ReLU."""
     g = _G()
@@ -124,10 +134,9 @@ def build_resnet50_f32(batch=32, image=224, base=64, blocks=(3, 4, 6, 3), classe
         beta = (r.standard_normal(cout) * 0.1).astype(np.float32)
         mean = (r.standard_normal(cout) * 0.1).astype(np.float32)
         var = r.uniform(0.5, 1.5, cout).astype(np.float32)
-        # fuse_conv_batchnorm: factor = gamma / sqrt(var + eps); W' = W * factor; b' = (b - mean) * factor + beta
-        factor = (gamma / np.sqrt(var + np.float32(1e-5))).astype(np.float32)
-        g.w(f"{name}_out_fused_weight", w * factor[:, None, None, None])
-        g.w(f"{name}_out_fused_bias", (np.float32(0.0) - mean) * factor + beta)
+        fw, fb = fold_batchnorm(w, None, gamma, beta, mean, var, 1e-5)
+        g.w(f"{name}_out_fused_weight", fw)
+        g.w(f"{name}_out_fused_bias", fb)
         attrs = dict(strides=[stride, stride], pads=[pad, pad, pad, pad], dilations=[1, 1], group=1, kernel_shape=[ksz, ksz])
         if relu:
             attrs["activation"] = "relu"

@@ -122,7 +122,7 @@ class CudaContext:
         cfg.keep_intermediates = int(keep_intermediates)
         cfg.profile = int(profile)
         cfg.cuda_graph = int(cuda_graph)
-        cfg.requant_f64 = int(requant_f64)
+        cfg.requant_f64 = int(requant_f64)  # False/0 auto, True/1 two-pass f64, 2 one-FMA without the packed saturation
         cfg.split_k_max = int(split_k_max)
         cfg.cta_pairs = {"auto": 0, "never": 1, "always": 2}[cta_pairs]
         h = ctypes.c_void_p()
@@ -263,9 +263,13 @@ class SessionBuilder:
         self._device = device
         return self
 
-    def with_optimization_level(self, _level):
-        """Accepted for source compatibility: graphs reach this provider already optimised
-        (the fused Conv / OxiInstanceNorm node contract), nothing is rewritten here."""
+    def with_optimization_level(self, level):
+        """SessionBuilder::with_optimization_level (root crate src/session/builder/options.rs): 0 runs the nodes as
+        given; from 1 on the reference's fusion passes for this path run first (Conv+BatchNormalization,
+        Conv+Relu/Clip, Conv+Add+Relu, the InstanceNorm chain, MatMul+Add, x*Sigmoid(x)).  Without this call a
+        graph passed to build_from_graph is run as given (it is taken to be optimised already); a model file is
+        optimised at level 1."""
+        self._opt_level = int(level)
         return self
 
     def with_kernel_path(self, path: str):
@@ -305,7 +309,29 @@ class SessionBuilder:
         return self
 
     def build_from_graph(self, graph: Graph, weights: Dict[str, np.ndarray]):
+        level = getattr(self, "_opt_level", None)
+        if level:
+            # the passes live behind the model ABI: hand the graph over as ONNX bytes
+            from .onnx_io import write_onnx
+            missing = [n for n in graph.input_names if n not in self._input_shapes]
+            if missing:
+                raise OnnxError(f"optimising a graph needs the shapes of its inputs; missing: {missing}")
+            types = getattr(self, "_input_types", {})
+            data = write_onnx(graph, weights, {n: (self._input_shapes[n], types.get(n, np.float32)) for n in graph.input_names})
+            return self.load_from_bytes(data)
         return Session(graph, weights, self._device, self._input_shapes, self._ctx_kw, getattr(self, "_input_types", None))
+
+    def load_from_bytes(self, data: bytes):
+        """SessionBuilder::load_from_bytes (src/session/loading.rs): an ONNX ModelProto held in memory."""
+        from .onnx_io import Model
+        level = getattr(self, "_opt_level", None)
+        return Session.from_model(Model.from_bytes(data), self._device, 1 if level is None else level, self._input_shapes, **self._ctx_kw)
+
+    def load(self, path: str):
+        """SessionBuilder::load: an ONNX file."""
+        from .onnx_io import Model
+        level = getattr(self, "_opt_level", None)
+        return Session.from_model(Model.from_file(path), self._device, 1 if level is None else level, self._input_shapes, **self._ctx_kw)
 
 
 class Session:
@@ -324,7 +350,42 @@ class Session:
         self._planned_for = None
         self._out_bufs = None
 
+    @classmethod
+    def from_file(cls, path: str, device: int = 0, optimization_level: int = 1, input_shapes: Optional[Dict[str, tuple]] = None, **ctx_kw):
+        """Session::from_file (root crate src/session/loading.rs:181): parses the ONNX file, runs the reference's
+        fusion passes for this path, registers the initializers (with their declared element types) as the context's
+        weights and plans the graph at the first run.  `input_shapes` gives the concrete shape of every input that
+        has a symbolic dimension."""
+        from .onnx_io import Model
+        model = Model.from_file(path)
+        return cls.from_model(model, device, optimization_level, input_shapes, **ctx_kw)
+
+    @classmethod
+    def from_model(cls, model, device: int = 0, optimization_level: int = 1, input_shapes: Optional[Dict[str, tuple]] = None, **ctx_kw):
+        if optimization_level > 0:
+            model.optimize(optimization_level)
+        graph = Graph(nodes=model.nodes(), input_names=[n for n, _, _ in model.inputs()], output_names=model.output_names())
+        self = cls.__new__(cls)
+        self.graph = graph
+        self.ctx = CudaContext(device, **ctx_kw)
+        self._model = model
+        self._input_shapes = dict(input_shapes or {})
+        for name, shape, _ in model.inputs():
+            if name not in self._input_shapes and all(d is not None for d in shape):
+                self._input_shapes[name] = tuple(shape)
+        self._input_types = {name: (np.uint8 if code == _ffi.DT_U8 else np.int8) for name, _, code in model.inputs() if code in (_ffi.DT_U8, _ffi.DT_I8)}
+        self._planned_for = None
+        self._out_bufs = None
+        return self
+
     def _plan(self, shapes):
+        if getattr(self, "_model", None) is not None:
+            from .onnx_io import plan_model
+            st, msg = plan_model(self.ctx, self._model, shapes)
+            _raise_for(st, msg)
+            self._planned_for = {k: tuple(v) for k, v in shapes.items()}
+            self._out_bufs = None
+            return
         lib = _ffi.lib()
         keep = _ffi.Keep()
         nodes = keep.add((_ffi.CNode * max(len(self.graph.nodes), 1))())

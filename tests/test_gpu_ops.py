@@ -185,6 +185,36 @@ def test_cta_pair_kernel_is_the_one_that_runs_when_forced():
     assert np.array_equal(outs["always"], want) and np.array_equal(outs["never"], want)
 
 
+@pytest.mark.parametrize("form", [0, 1, 2], ids=["auto (packed saturation)", "two-pass f64", "one FMA, unpacked"])
+@pytest.mark.parametrize("relu", [False, True], ids=["i8 range", "relu"])
+def test_every_requantisation_form_of_the_tensor_core_epilogue_is_bit_exact(form, relu):
+    """The requantising epilogue has three forms (f32 estimate + f64 second pass; one fused multiply-add per lane;
+    the same with the saturation done on packed 16-bit lanes): each, forced through the context's tuning, must
+    give the reference's lanes on the same layer, with and without a Relu folded into the saturation."""
+    from oxionnx_b200.graph import Graph
+    rng = np.random.default_rng(31 + int(relu))
+    c, oc = 128, 192
+    weights = {"w": rng.integers(-127, 128, (oc, c, 3, 3)).astype(np.float32), "ws": rng.uniform(0.001, 0.01, oc).astype(np.float32),
+               "wz": np.zeros(oc, np.float32), "b": rng.integers(-1000, 1000, oc).astype(np.float32), "xs": np.float32([0.02]), "z0": np.float32([0]),
+               "yz": np.float32([0 if relu else -3]), "ys": np.float32([0.35]), "qs": np.float32([0.02])}
+    nodes = [Node("QuantizeLinear", "q", ["x", "qs", "z0"], ["xq"], {}),
+             Node("QLinearConv", "conv", ["xq", "xs", "z0", "w", "ws", "wz", "ys", "yz", "b"], ["yq"], {"pads": [1, 1, 1, 1]})]
+    last = "yq"
+    if relu:
+        nodes.append(Node("Relu", "r", ["yq"], ["yr"], {}))
+        last = "yr"
+    nodes.append(Node("DequantizeLinear", "dq", [last, "ys", "yz"], ["y"], {}))
+    graph = Graph(nodes=nodes, input_names=["x"], output_names=["y"])
+    x = np.abs(rng.standard_normal((3, c, 10, 10))).astype(np.float32)
+    sess = S.Session.builder().with_tuning(requant_f64=form).build_from_graph(graph, weights)
+    got = sess.run({"x": x})["y"]
+    sess.close()
+    oracle.set_threads(8)
+    want = oracle.run_graph(graph, weights, {"x": x}, keep_all=False)["y"]
+    assert np.array_equal(got, want), f"{np.sum(got != want)} of {want.size} lanes differ"
+    assert np.unique(want).size > 16, "degenerate test vector"
+
+
 def test_conv_integer_and_matmul_integer_bit_exact(ctx):
     rng = np.random.default_rng(17)
     oracle.set_threads(8)
