@@ -25,7 +25,9 @@ class OracleError(RuntimeError):
 
 class _Tensor(ctypes.Structure):
     _fields_ = [("data", ctypes.POINTER(ctypes.c_float)), ("shape", ctypes.c_int64 * MAX_RANK), ("rank", ctypes.c_int32),
-                ("present", ctypes.c_int32), ("len", ctypes.c_int64)]
+                ("present", ctypes.c_int32), ("len", ctypes.c_int64), ("dtype", ctypes.c_int32)]
+
+DT_UNTYPED, DT_U8, DT_I8 = 0, 1, 2
 
 
 class _Attr(ctypes.Structure):
@@ -120,8 +122,9 @@ def _pack_attrs(attrs):
 
 
 def run_node(op, inputs, attrs=None, n_outputs=1):
-    """Execute one operator.  `inputs` is a list of float32 arrays (None = omitted optional
-    input).  Returns a list of n_outputs float32 arrays."""
+    """Execute one operator.  `inputs` is a list of arrays (None = omitted optional input); a uint8 or int8 array
+    is a typed tensor (its lanes are widened to f32, its declared type travels with it, as on the reference's
+    execute_typed path), anything else is plain f32 lanes.  Returns a list of n_outputs float32 arrays."""
     lib = _load()
     n_in = len(inputs)
     tin = (_Tensor * max(n_in, 1))()
@@ -130,6 +133,8 @@ def run_node(op, inputs, attrs=None, n_outputs=1):
         if x is None:
             tin[i].present = 0
             continue
+        declared = getattr(x, "dtype", None)
+        tin[i].dtype = DT_U8 if declared == np.uint8 else (DT_I8 if declared == np.int8 else DT_UNTYPED)
         arr = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
         keep.append(arr)
         if arr.ndim > MAX_RANK:
@@ -164,9 +169,13 @@ def run_graph(graph, weights, feeds, keep_all=True):
     """Execute `graph.nodes` in order (they must be topologically sorted), the way
     Session::run does with OptLevel::None (src/session/run/sequential.rs:505).  Returns a
     dict holding every value (feeds, intermediates, outputs) when keep_all, else only the
-    graph outputs."""
-    state = {k: np.asarray(v, dtype=np.float32) for k, v in weights.items()}
-    state.update({k: np.asarray(v, dtype=np.float32) for k, v in feeds.items()})
+    graph outputs.  uint8 / int8 weights and feeds stay typed tensors (run_typed: the declared type of a
+    y_zero_point then fixes the saturation range); every other array is f32 lanes."""
+    def lanes(v):
+        v = np.asarray(v)
+        return v if v.dtype in (np.uint8, np.int8) else v.astype(np.float32)
+    state = {k: lanes(v) for k, v in weights.items()}
+    state.update({k: lanes(v) for k, v in feeds.items()})
     for node in graph.nodes:
         ins = [state[name] if name else None for name in node.inputs]
         outs = run_node(node.op, ins, node.attrs, n_outputs=len(node.outputs))

@@ -185,6 +185,14 @@ SatRange sat_infer(const std::vector<int32_t>& y_zp, const std::vector<int32_t>&
   return {-128, 255};
 }
 
+// execute_typed (quant_ops/qlinear_matmul.rs, qlinear_conv.rs): SatRange::for_dtype (mod.rs:216-222) of the declared
+// type of y_zero_point when it is U8 or I8, otherwise the value cascade of infer.
+SatRange sat_range(const oxo_tensor* y_zp_tensor, const std::vector<int32_t>& y_zp, const std::vector<int32_t>& x_zp) {
+  if (y_zp_tensor && y_zp_tensor->dtype == OXO_DT_U8) return SatRange{0, 255};
+  if (y_zp_tensor && y_zp_tensor->dtype == OXO_DT_I8) return SatRange{-128, 127};
+  return sat_infer(y_zp, x_zp);
+}
+
 // SatRange::requantize: quant_ops/mod.rs:229-233
 float requantize(int64_t acc, float combined, int32_t zp, SatRange r) {
   volatile double prod = (double)acc * (double)combined;  // separately rounded multiply
@@ -444,7 +452,7 @@ void op_qlinear_matmul(Ctx& c) {
   auto bi = tensor_to_i32(b, "QLinearMatMul: b");
   auto acc = integer_matmul(ai, bi, a_zp, b_zp, s);
   int32_t y_zp = y_zp_l.empty() ? 0 : y_zp_l[0];
-  SatRange r = sat_infer(y_zp_l, a_zp);
+  SatRange r = sat_range(c.optional(7), y_zp_l, a_zp);
   volatile float ab = a_scale * b_scale;
   float combined = ab / y_scale;
   alloc_out(c.out[0], s.out_shape);
@@ -689,7 +697,7 @@ void op_qlinear_conv(Ctx& c) {
     fail(OXO_ERR_SHAPE_MISMATCH, "QLinearConv: w_scale has %lld entries, expected 1 or %lld (per output channel)", (long long)w_scale.len, (long long)c_out);
   for (int64_t i = 0; i < w_scale.len; ++i)
     if (!std::isfinite(w_scale.data[i])) fail(OXO_ERR_INVALID_MODEL, "QLinearConv: w_scale[%lld] must be finite", (long long)i);
-  SatRange r = sat_infer(y_zp_l, {x_zp});
+  SatRange r = sat_range(c.optional(7), y_zp_l, {x_zp});
   int64_t spatial = 1;
   for (size_t d = 2; d < g.out_shape.size(); ++d) spatial *= g.out_shape[d];
   alloc_out(c.out[0], g.out_shape);

@@ -41,7 +41,11 @@ typedef struct {
   int32_t rank;
   int32_t present;
   int64_t len;                 /* number of lanes in data */
+  int32_t dtype;               /* declared element type when it survived to the operator (TypedTensor): OXO_DT_* */
 } oxo_tensor;
+
+/* lanes are always f32; dtype only records what the tensor was declared as (oxionnx-core src/dtype.rs:8) */
+enum { OXO_DT_UNTYPED = 0, OXO_DT_U8 = 1, OXO_DT_I8 = 2 };
 
 enum { OXO_ATTR_INT = 0, OXO_ATTR_FLOAT = 1, OXO_ATTR_STRING = 2, OXO_ATTR_INTS = 3, OXO_ATTR_FLOATS = 4 };
 

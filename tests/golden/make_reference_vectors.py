@@ -28,7 +28,26 @@ def s(v):
     return t([v], [1])
 
 
+def tt(data, shape, dtype):
+    """A typed tensor (TypedTensor with U8 / I8 storage): the declared element type travels with the lanes."""
+    return dict(t(data, shape), dtype=dtype)
+
+
+def iota(n, shape):
+    """Written in the source as iota(n, shape) = 0, 1, ..., n-1."""
+    return dict(t(range(n), shape), gen={"kind": "iota", "n": n})
+
+
+def fill(v, n, shape):
+    """Written in the source as vec![v; n] / &[v; n]."""
+    return dict(t([v] * n, shape), gen={"kind": "fill", "v": v, "n": n})
+
+
 W2 = "tests/w2_quantized_ops_e2e.rs"
+ND = "oxionnx-ops/tests/qlinear_native_dtype_test.rs"
+CC = "tests/conformance_conv.rs"
+OC = "tests/op_conv_tests.rs"
+W1 = "oxionnx-ops/tests/w1_conv_pool.rs"
 
 CASES = [
     dict(name="matmul_integer_u8_with_zero_point", source=f"{W2}:119-144", op="MatMulInteger",
@@ -138,6 +157,94 @@ CASES = [
                     -0.598, -0.309, -0.062, 0.812, 0.395, -0.321, -0.966, -0.68, 0.993], [2, 3, 4])],
          attrs={}, expected=[t([-0.484872, 0.769199, 1.237093, -1.245648, 0.005295, -0.139934, -0.331534, 0.085718], [2, 1, 4])],
          exact=1e-4),
+    # ---- typed execution: the declared type of y_zero_point fixes the saturation range exactly ----
+    dict(name="typed_qlinear_matmul_f32_zero_point_union", source=f"{ND}:164-174", op="QLinearMatMul",
+         inputs=[t([10, 0, 0, 10], [2, 2]), s(1.0), s(0.0), t([10, -15, 0, 0], [2, 2]), s(1.0), s(0.0), s(1.0), s(100.0)],
+         attrs={}, expected=[t([200, -50, 100, 100], [2, 2])], exact=True),
+    dict(name="typed_qlinear_matmul_i8_zero_point", source=f"{ND}:178-186", op="QLinearMatMul",
+         inputs=[tt([10, 0, 0, 10], [2, 2], "i8"), s(1.0), s(0.0), tt([10, -15, 0, 0], [2, 2], "i8"), s(1.0), s(0.0), s(1.0), tt([100], [1], "i8")],
+         attrs={}, expected=[t([127, -50, 100, 100], [2, 2])], exact=True),
+    dict(name="typed_qlinear_matmul_u8_zero_point", source=f"{ND}:194-202", op="QLinearMatMul",
+         inputs=[tt([10, 0, 0, 10], [2, 2], "u8"), s(1.0), s(0.0), tt([10, -15, 0, 0], [2, 2], "i8"), s(1.0), s(0.0), s(1.0), tt([100], [1], "u8")],
+         attrs={}, expected=[t([200, 0, 100, 100], [2, 2])], exact=True),
+    dict(name="typed_qlinear_conv_f32_zero_point_union", source=f"{ND}:207-217", op="QLinearConv",
+         inputs=[t([10, -15], [1, 1, 1, 2]), s(1.0), s(0.0), t([10], [1, 1, 1, 1]), s(1.0), s(0.0), s(1.0), s(100.0)],
+         attrs={}, expected=[t([200, -50], [1, 1, 1, 2])], exact=True),
+    dict(name="typed_qlinear_conv_i8_zero_point", source=f"{ND}:220-228", op="QLinearConv",
+         inputs=[tt([10, -15], [1, 1, 1, 2], "i8"), s(1.0), s(0.0), tt([10], [1, 1, 1, 1], "i8"), s(1.0), s(0.0), s(1.0), tt([100], [1], "i8")],
+         attrs={}, expected=[t([127, -50], [1, 1, 1, 2])], exact=True),
+    dict(name="typed_qlinear_conv_u8_zero_point", source=f"{ND}:231-239", op="QLinearConv",
+         inputs=[tt([10, -15], [1, 1, 1, 2], "i8"), s(1.0), s(0.0), tt([10], [1, 1, 1, 1], "i8"), s(1.0), s(0.0), s(1.0), tt([100], [1], "u8")],
+         attrs={}, expected=[t([200, 0], [1, 1, 1, 2])], exact=True),
+    # the same table through Session::run_typed (typed graph inputs)
+    dict(name="run_typed_qlinear_matmul_u8", source="tests/qlinear_run_typed_e2e.rs:63-104", op="QLinearMatMul",
+         inputs=[tt([10, 0, 0, 10], [2, 2], "u8"), s(1.0), s(0.0), tt([10, -15, 0, 0], [2, 2], "i8"), s(1.0), s(0.0), s(1.0), tt([100], [1], "u8")],
+         attrs={}, expected=[t([200.0, 0.0, 100.0, 100.0], [2, 2])], exact=True),
+    dict(name="run_typed_qlinear_matmul_i8", source="tests/qlinear_run_typed_e2e.rs:63-119", op="QLinearMatMul",
+         inputs=[tt([10, 0, 0, 10], [2, 2], "u8"), s(1.0), s(0.0), tt([10, -15, 0, 0], [2, 2], "i8"), s(1.0), s(0.0), s(1.0), tt([100], [1], "i8")],
+         attrs={}, expected=[t([127.0, -50.0, 100.0, 100.0], [2, 2])], exact=True),
+    dict(name="run_typed_qlinear_matmul_f32_zero_point_union", source="tests/qlinear_run_typed_e2e.rs:63-134", op="QLinearMatMul",
+         inputs=[tt([10, 0, 0, 10], [2, 2], "u8"), s(1.0), s(0.0), tt([10, -15, 0, 0], [2, 2], "i8"), s(1.0), s(0.0), s(1.0), s(100.0)],
+         attrs={}, expected=[t([200.0, -50.0, 100.0, 100.0], [2, 2])], exact=True),
+    # ---- float Conv and MaxPool: geometry, auto_pad, typed errors ----
+    dict(name="conformance_conv2d_1x1", source=f"{CC}:15-54", op="Conv",
+         inputs=[t([1, 2, 3, 4, 5, 6, 7, 8], [1, 2, 2, 2]), t([1, 0, 0, 1, 1, 1], [3, 2, 1, 1])],
+         attrs={"strides": [1, 1], "pads": [0, 0, 0, 0], "dilations": [1, 1], "group": 1},
+         expected=[t([1, 2, 3, 4, 5, 6, 7, 8, 6, 8, 10, 12], [1, 3, 2, 2])], exact=1e-5),
+    dict(name="conformance_conv2d_3x3_pad1", source=f"{CC}:57-91", op="Conv",
+         inputs=[fill(1.0, 9, [1, 1, 3, 3]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"strides": [1, 1], "pads": [1, 1, 1, 1], "dilations": [1, 1], "group": 1},
+         expected=[t([4, 6, 4, 6, 9, 6, 4, 6, 4], [1, 1, 3, 3])], exact=1e-5),
+    dict(name="conformance_maxpool_2x2", source=f"{CC}:94-125", op="MaxPool", inputs=[t(range(1, 17), [1, 1, 4, 4])],
+         attrs={"kernel_shape": [2, 2], "strides": [2, 2], "pads": [0, 0, 0, 0]}, expected=[t([6, 8, 14, 16], [1, 1, 2, 2])], exact=1e-5),
+    dict(name="conv2d_dilated", source=f"{OC}:15-44", op="Conv", inputs=[fill(1.0, 25, [1, 1, 5, 5]), fill(1.0, 4, [1, 1, 2, 2])],
+         attrs={"strides": [1, 1], "pads": [0, 0, 0, 0], "dilations": [2, 2], "group": 1}, expected=[fill(4.0, 9, [1, 1, 3, 3])], exact=1e-5),
+    dict(name="conv2d_grouped", source=f"{OC}:47-76", op="Conv", inputs=[fill(1.0, 36, [1, 4, 3, 3]), fill(1.0, 8, [4, 2, 1, 1])],
+         attrs={"strides": [1, 1], "pads": [0, 0, 0, 0], "dilations": [1, 1], "group": 2}, expected=[fill(2.0, 36, [1, 4, 3, 3])], exact=1e-5),
+    dict(name="conv2d_stride2", source=f"{OC}:79-109", op="Conv", inputs=[t(range(1, 17), [1, 1, 4, 4]), fill(1.0, 4, [1, 1, 2, 2])],
+         attrs={"strides": [2, 2], "pads": [0, 0, 0, 0], "dilations": [1, 1], "group": 1}, expected=[t([14, 22, 46, 54], [1, 1, 2, 2])], exact=1e-5),
+    dict(name="conv2d_batch_n", source=f"{OC}:144-170", op="Conv", inputs=[fill(1.0, 36, [4, 1, 3, 3]), fill(1.0, 4, [1, 1, 2, 2])],
+         attrs={"strides": [1, 1], "pads": [0, 0, 0, 0], "dilations": [1, 1], "group": 1}, expected=[fill(4.0, 16, [4, 1, 2, 2])], exact=1e-5),
+    dict(name="conv_auto_pad_same_upper", source=f"{W1}:89-108", op="Conv", inputs=[iota(25, [1, 1, 5, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"auto_pad": "SAME_UPPER"},
+         expected=[t([12, 21, 27, 33, 24, 33, 54, 63, 72, 51, 63, 99, 108, 117, 81, 93, 144, 153, 162, 111, 72, 111, 117, 123, 84], [1, 1, 5, 5])],
+         exact=1e-4),
+    dict(name="conv_auto_pad_same_upper_stride2", source=f"{W1}:110-127", op="Conv", inputs=[iota(36, [1, 1, 6, 6]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"auto_pad": "SAME_UPPER", "strides": [2, 2]}, expected=[t([63, 81, 63, 171, 189, 135, 168, 180, 126], [1, 1, 3, 3])], exact=1e-4),
+    dict(name="conv_auto_pad_same_lower_stride2", source=f"{W1}:110-139", op="Conv", inputs=[iota(36, [1, 1, 6, 6]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"auto_pad": "SAME_LOWER", "strides": [2, 2]}, expected=[t([14, 30, 42, 75, 126, 144, 147, 234, 252], [1, 1, 3, 3])], exact=1e-4),
+    dict(name="conv_auto_pad_valid_overrides_pads", source=f"{W1}:142-158", op="Conv", inputs=[iota(25, [1, 1, 5, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"auto_pad": "VALID", "pads": [1, 1, 1, 1]}, expected=[t([54, 63, 72, 99, 108, 117, 144, 153, 162], [1, 1, 3, 3])], exact=1e-4),
+    dict(name="conv_rejects_unknown_auto_pad", source=f"{W1}:161-174", op="Conv", inputs=[iota(25, [1, 1, 5, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"auto_pad": "SAME"}, error_kind="Unsupported"),
+    dict(name="conv_zero_stride_is_typed_error", source=f"{W1}:179-192", op="Conv", inputs=[iota(25, [1, 1, 5, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"strides": [0, 0]}, error_kind="ShapeMismatch"),
+    dict(name="conv_zero_group_is_typed_error", source=f"{W1}:195-208", op="Conv", inputs=[iota(25, [1, 1, 5, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"group": 0}, error_kind="ShapeMismatch"),
+    dict(name="conv_kernel_larger_than_padded_input", source=f"{W1}:211-227", op="Conv", inputs=[t([1.0], [1, 1, 1, 1]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={}, error_kind="ShapeMismatch"),
+    dict(name="conv_dilation_beyond_input_extent", source=f"{W1}:230-244", op="Conv", inputs=[iota(25, [1, 1, 5, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"dilations": [4, 4]}, error_kind="ShapeMismatch"),
+    dict(name="conv_negative_pads", source=f"{W1}:247-260", op="Conv", inputs=[iota(25, [1, 1, 5, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={"pads": [-1, 0, 0, 0]}, error_kind="ShapeMismatch"),
+    dict(name="conv_non_4d_input", source=f"{W1}:263-275", op="Conv", inputs=[iota(5, [1, 1, 5]), fill(1.0, 9, [1, 1, 3, 3])],
+         attrs={}, error_kind="ShapeMismatch"),
+    dict(name="max_pool_ceil_mode_1", source=f"{W1}:280-297", op="MaxPool", inputs=[iota(25, [1, 1, 5, 5])],
+         attrs={"kernel_shape": [2, 2], "strides": [2, 2], "ceil_mode": 1}, expected=[t([6, 8, 9, 16, 18, 19, 21, 23, 24], [1, 1, 3, 3])], exact=1e-4),
+    dict(name="max_pool_ceil_mode_0", source=f"{W1}:280-309", op="MaxPool", inputs=[iota(25, [1, 1, 5, 5])],
+         attrs={"kernel_shape": [2, 2], "strides": [2, 2]}, expected=[t([6, 8, 16, 18], [1, 1, 2, 2])], exact=1e-4),
+    dict(name="max_pool_h4_k3_s2_ceil", source=f"{W1}:312-329", op="MaxPool", inputs=[iota(16, [1, 1, 4, 4])],
+         attrs={"kernel_shape": [3, 3], "strides": [2, 2], "ceil_mode": 1}, expected=[t([10, 11, 14, 15], [1, 1, 2, 2])], exact=1e-4),
+    dict(name="max_pool_h4_k3_s2_floor", source=f"{W1}:312-336", op="MaxPool", inputs=[iota(16, [1, 1, 4, 4])],
+         attrs={"kernel_shape": [3, 3], "strides": [2, 2]}, expected=[t([10.0], [1, 1, 1, 1])], exact=1e-4),
+    dict(name="max_pool_ceil_mode_drops_window_in_right_padding", source=f"{W1}:339-359", op="MaxPool", inputs=[iota(25, [1, 1, 5, 5])],
+         attrs={"kernel_shape": [3, 3], "strides": [3, 3], "pads": [0, 0, 2, 2], "ceil_mode": 1}, expected=[t([12, 14, 22, 24], [1, 1, 2, 2])],
+         exact=1e-4),
+    dict(name="max_pool_dilations", source=f"{W1}:362-377", op="MaxPool", inputs=[iota(16, [1, 1, 4, 4])],
+         attrs={"kernel_shape": [2, 2], "dilations": [2, 2]}, expected=[t([10, 11, 14, 15], [1, 1, 2, 2])], exact=1e-4),
+    dict(name="max_pool_auto_pad_same_upper", source=f"{W1}:380-397", op="MaxPool", inputs=[iota(25, [1, 1, 5, 5])],
+         attrs={"kernel_shape": [3, 3], "auto_pad": "SAME_UPPER"},
+         expected=[t([6, 7, 8, 9, 9, 11, 12, 13, 14, 14, 16, 17, 18, 19, 19, 21, 22, 23, 24, 24, 21, 22, 23, 24, 24], [1, 1, 5, 5])], exact=1e-4),
 ]
 
 
@@ -173,9 +280,19 @@ def verify_against_reference():
         with open(os.path.join(REF, path)) as fh:
             lines = fh.readlines()
         # a generous window: helpers such as (1..=32) ranges are written as ranges there
-        nums = _numbers("".join(lines[max(lo - 12, 0):hi + 4]))
+        window = "".join(lines[max(lo - 12, 0):hi + 4])
+        nums = _numbers(window)
         for tensor in case["inputs"] + case.get("expected", []):
             data = tensor["data"]
+            gen = tensor.get("gen")
+            if gen:  # written as a generator expression there, not as literals
+                if gen["kind"] == "iota":
+                    pat = rf"iota\({gen['n']}\b"
+                else:
+                    pat = rf"\[{gen['v']:.1f}(?:_f32)?; {gen['n']}\]"
+                if not re.search(pat, window):
+                    problems.append(f"{case['name']}: generator {gen} not found in {case['source']}")
+                continue
             if len(data) <= 1:
                 continue
             is_range = all(abs(data[i + 1] - data[i] - 1.0) < 1e-12 for i in range(len(data) - 1)) and len(data) > 8

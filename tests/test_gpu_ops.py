@@ -40,7 +40,8 @@ def ctx_auto():
 
 
 def _arr(t):
-    return np.asarray(t["data"], dtype=np.float32).reshape(t["shape"])
+    dtype = {"u8": np.uint8, "i8": np.int8}.get(t.get("dtype"), np.float32)  # a typed tensor keeps its declared type
+    return np.asarray(t["data"], dtype=dtype).reshape(t["shape"])
 
 
 def dispatch(ctx, op, inputs, attrs=None, n_out=1):
@@ -62,6 +63,11 @@ def assert_close_tf32(got, want, what=""):
 @pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
 def test_reference_vector_through_abi(ctx, case):
     ins = [_arr(t) for t in case["inputs"]]
+    if "error_kind" in case:
+        # malformed geometry is not taken: the node falls to the CPU operator, which raises the typed error
+        assert dispatch(ctx, case["op"], ins, case["attrs"]) is None
+        assert ctx.last_error()
+        return
     if "error_contains" in case:
         # malformed quantised nodes decline so that the CPU operator raises its own typed error
         assert dispatch(ctx, case["op"], ins, case["attrs"]) is None

@@ -15,7 +15,8 @@ with open(os.path.join(ROOT, "tests", "golden", "reference_vectors.json")) as _f
 
 
 def _arr(t):
-    return np.asarray(t["data"], dtype=np.float32).reshape(t["shape"])
+    dtype = {"u8": np.uint8, "i8": np.int8}.get(t.get("dtype"), np.float32)  # a typed tensor keeps its declared type
+    return np.asarray(t["data"], dtype=dtype).reshape(t["shape"])
 
 
 @pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
@@ -24,6 +25,11 @@ def test_reference_vector(case, threads):
     oracle.set_threads(threads)
     try:
         ins = [_arr(t) for t in case["inputs"]]
+        if "error_kind" in case:  # the OnnxError variant the reference's test matches on
+            with pytest.raises(oracle.OracleError) as ei:
+                oracle.run_node(case["op"], ins, case["attrs"], n_outputs=1)
+            assert ei.value.kind == case["error_kind"], str(ei.value)
+            return
         if "error_contains" in case:
             with pytest.raises(oracle.OracleError) as ei:
                 oracle.run_node(case["op"], ins, case["attrs"], n_outputs=1)
