@@ -131,7 +131,10 @@ typedef struct {
                                  2: the one-FMA form, but never its packed 16-bit saturation */
   int32_t split_k_max;        /* most slices a long reduction may be split into (0: default 8, 1: never split) */
   int32_t cta_pairs;          /* 0 the tile model decides, 1 never pair CTAs (cta_group::2), 2 pair wherever the shape allows */
-  int32_t reserved[5];
+  int32_t float_precision;    /* float contractions (Conv, Gemm, MatMul on the tensor cores): 0 TF32 operands (f32 storage),
+                                 1 f16 operands, 2 bf16 operands; accumulation is f32 in every case, results are f32 lanes.
+                                 The reference's counterpart is its mixed-precision session (src/session/mixed_precision) */
+  int32_t reserved[4];
 } oxb200_config;
 
 /* CacheCounters (oxionnx-cuda src/residency.rs:141-240) plus arena figures. */

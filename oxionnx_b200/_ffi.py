@@ -48,7 +48,7 @@ class Config(ctypes.Structure):
     _fields_ = [("struct_size", ctypes.c_uint32), ("verify", ctypes.c_int32), ("strict", ctypes.c_int32), ("residency", ctypes.c_int32),
                 ("cuda_graph", ctypes.c_int32), ("kernel_path", ctypes.c_int32), ("keep_intermediates", ctypes.c_int32),
                 ("profile", ctypes.c_int32), ("requant_f64", ctypes.c_int32), ("split_k_max", ctypes.c_int32), ("cta_pairs", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 5)]
+                ("float_precision", ctypes.c_int32), ("reserved", ctypes.c_int32 * 4)]
 
 
 class Counters(ctypes.Structure):

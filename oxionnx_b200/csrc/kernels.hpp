@@ -37,6 +37,12 @@ void quantize_linear(const TensorRef& x, const TensorRef& y, const float* scale,
 // Same arithmetic with host-known per-tensor parameters and identical memory order on both
 // sides: 16 lanes per thread through 16-byte accesses.  Fails if the operand is not eligible
 // (callers check quantize_linear_scalar_ok first).
+// f32 lanes -> f16 / bf16 lanes (round to nearest even), same memory order: the operand copy a 16-bit float
+// contraction reads.  6 B per element.
+void convert_f32_to_half(const float* src, void* dst, DT dst_dt, int64_t n, cudaStream_t s);
+// y = x rounded to TF32 (cvt.rna), lane by lane: the operand copy of a TF32 contraction whose input was not rounded
+// by its producer (a graph input).  8 B per element.
+void round_to_tf32_copy(const float* src, float* dst, int64_t n, cudaStream_t s);
 bool quantize_linear_scalar_ok(const TensorRef& x, const TensorRef& y);
 void quantize_linear_scalar(const TensorRef& x, const TensorRef& y, float scale, float zp, float lo, float hi, cudaStream_t s);
 // y = (x - zp[ch]) * scale[ch], two separately rounded f32 operations.

@@ -7,6 +7,9 @@
 #include <mutex>
 #include <string>
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "kernels.hpp"
 
 namespace oxb {
@@ -1285,6 +1288,49 @@ void convert(const TensorRef& src, const TensorRef& dst, cudaStream_t s) {
     }
   }
   convert_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, dst.ptr, dst.dt, dst.layout, d, total);
+}
+
+// Eight lanes per thread: two 16-byte loads, one 16-byte store; the tail runs lane by lane.
+__global__ void f32_to_half_kernel(const float* __restrict__ src, void* __restrict__ dst, bool bf16, int64_t n8, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src) + 2 * i), b = __ldg(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    uint4 o;
+    if (bf16) {
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w), p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+      o = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1), *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+    } else {
+      __half2 p0 = __floats2half2_rn(a.x, a.y), p1 = __floats2half2_rn(a.z, a.w), p2 = __floats2half2_rn(b.x, b.y), p3 = __floats2half2_rn(b.z, b.w);
+      o = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1), *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+    }
+    reinterpret_cast<uint4*>(dst)[i] = o;
+  }
+  for (int64_t i = n8 * 8 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += stride) {
+    if (bf16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(src[i]);
+    else reinterpret_cast<__half*>(dst)[i] = __float2half_rn(src[i]);
+  }
+}
+
+__global__ void round_to_tf32_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t n4, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src) + i);
+    reinterpret_cast<float4*>(dst)[i] = make_float4(round_tf32(a.x), round_tf32(a.y), round_tf32(a.z), round_tf32(a.w));
+  }
+  for (int64_t i = n4 * 4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = round_tf32(src[i]);
+}
+
+void round_to_tf32_copy(const float* src, float* dst, int64_t n, cudaStream_t s) {
+  if (n == 0) return;
+  const int64_t n4 = ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) ? n / 4 : 0;
+  round_to_tf32_kernel<<<grid_for(std::max<int64_t>(n4, n - n4 * 4)), kThreads, 0, s>>>(src, dst, n4, n);
+}
+
+void convert_f32_to_half(const float* src, void* dst, DT dst_dt, int64_t n, cudaStream_t s) {
+  if (n == 0) return;
+  if (!(dst_dt == DT::F16 || dst_dt == DT::BF16)) OXB_FAIL("convert_f32_to_half: destination is not a 16-bit float type");
+  const int64_t n8 = ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) ? n / 8 : 0;
+  f32_to_half_kernel<<<grid_for(std::max<int64_t>(n8, n - n8 * 8)), kThreads, 0, s>>>(src, dst, dst_dt == DT::BF16, n8, n);
 }
 
 void residual_requant(const void* a, DT a_dt, const void* b, DT b_dt, void* y, DT y_dt, int64_t n, const ResidualParams& rp, cudaStream_t s) {

@@ -233,7 +233,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   // Tile width.  Measured on B200 (1.965 GHz): a tcgen05.mma of 32 bytes of K takes N/2 cycles
   // of the tensor pipe but cannot be issued faster than one per ~56 cycles; one SM fills its
   // shared memory from L2 at about 95 GB/s when all SMs do so; the fused epilogue costs about
-  // 0.05 ns per output for requantisation and 0.03 ns for the float variants.  The three overlap
+  // 0.07 ns per output for requantisation and 0.03 ns for the float variants, plus a fixed cost per tile.  The three overlap
   // (ring of stages, two accumulators), so a tile takes the longest of them, the kernel runs
   // ceil(tiles / SMs) rounds of tiles, and the last tile's epilogue is not hidden.  Pick the
   // width that minimises that estimate; ties go to the wider tile (fewer re-reads of the activations).
@@ -249,7 +249,11 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   {
     const double k_bytes = (double)cs.K() * es;
     const double k_steps = k_bytes / 32.0;
-    const double ns_out = e.mode == EPI_F32 ? 0.03e-9 : 0.05e-9;
+    // epilogue: per output 0.07 ns requantised / 0.03 ns float, plus about 0.5 us per tile whatever its width (the
+    // per-tile handshakes and address arithmetic of the epilogue warps: a 1x1 64 -> 256 layer at M = 802816 takes
+    // 3.0 us per round of 128 x 256 tiles, 1.05 us per round of 128 x 64 tiles, 0.84 us per round of 128 x 32)
+    const double ns_out = e.mode == EPI_F32 ? 0.03e-9 : 0.07e-9;
+    const double t_tile_fixed = 0.5e-6;
     const int max_split = tune.split_k_max > 0 ? tune.split_k_max : 8;
     double best = 1e30;
     for (int cand = bn_max; cand >= 32; cand /= 2) {
@@ -259,7 +263,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
         const double rounds = std::ceil(tiles * sp / sms);
         const double t_mma = k_steps * std::max(56.0, cand / 2.0) / 1.965e9 / sp;
         const double t_feed = (double)(BLOCK_M + cand) * k_bytes / 95e9 / sp;
-        const double t_epi = (double)BLOCK_M * cand * ns_out;
+        const double t_epi = (double)BLOCK_M * cand * ns_out + t_tile_fixed;
         // measured: a split launch costs about 10 us more than an unsplit one before its first K block pays
         // back (the slices' accumulators go through the workspace, and the finishing epilogues are not overlapped)
         const double t_split = sp > 1 ? 10e-6 : 0.0;
@@ -284,9 +288,14 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   if (tune.cta_pairs != 1 && bn == 256 && splits == 1 && cs.OC >= 256) {
     const int64_t pair_tiles = ceil_div(M, 2 * BLOCK_M) * ceil_div(cs.OC, 256);
     const double k_bytes = (double)cs.K() * es;
-    const bool feed_bound = k_bytes >= 1024.0;  // at least eight 128-byte K blocks per tile
+    // Measured: with 2 KB of K or more per row a pair wins once every pair has at least two tiles (3x3 256->256,
+    // i8, M=100352: 57.7 us against 65.9 us for lone CTAs); from 8 KB of K it also wins with a single partial wave
+    // (TF32 3x3 256->256 at M=25088: 61.9 us against 78.2 us); below 2 KB the extra barrier traffic of a pair costs
+    // more than the halved operand feed saves (1x1 1024->256, i8, M=12544: 18.6 us against 16.7 us).
+    const int64_t pairs_resident = sms / 2;
+    const bool feed_bound = k_bytes >= 2048.0 && (pair_tiles >= 2 * pairs_resident || (k_bytes >= 8192.0 && pair_tiles >= pairs_resident));
     if (tune.cta_pairs == 2) pair = true;
-    else pair = feed_bound && pair_tiles >= sms / 2;
+    else pair = feed_bound;
   }
   const int64_t n_tiles = ceil_div(cs.OC, bn);
   if (m_tiles * n_tiles > 0x7fffffffLL) return no("grid too large");

@@ -78,6 +78,39 @@ DT narrowest_int(int64_t lo, int64_t hi) {
   return DT::I32;
 }
 
+// f32 -> IEEE binary16 bits, round to nearest even (overflow to infinity, subnormals kept, NaN quiet).
+uint16_t f32_to_f16_bits(float f) {
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  const uint32_t mag = x & 0x7fffffffu;
+  if (mag >= 0x7f800000u) return (uint16_t)(sign | (mag > 0x7f800000u ? 0x7e00u : 0x7c00u));
+  if (mag >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);  // rounds to 65520 or above: infinity
+  if (mag < 0x33000001u) return (uint16_t)sign;              // below half of the smallest subnormal
+  const int e = (int)(mag >> 23) - 127;
+  uint32_t man = (mag & 0x7fffffu) | 0x800000u;
+  uint32_t shift, base;
+  if (e < -14) {  // subnormal half: value = man * 2^(e-23), unit 2^-24
+    shift = (uint32_t)(-e - 1);  // 13 + (-14 - e)
+    base = 0;
+  } else {
+    shift = 13;
+    base = ((uint32_t)(e + 15) << 10) - 0x400u;  // the implicit bit of man adds the last exponent step
+  }
+  const uint32_t q = man >> shift, rem = man & ((1u << shift) - 1u), half = 1u << (shift - 1);
+  uint32_t r = base + q;
+  if (rem > half || (rem == half && (q & 1u))) r += 1;
+  return (uint16_t)(sign | r);
+}
+// f32 -> bfloat16 bits, round to nearest even.
+uint16_t f32_to_bf16_bits(float f) {
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  if ((x & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((x >> 16) | 0x40u);
+  x += 0x7fffu + ((x >> 16) & 1u);
+  return (uint16_t)(x >> 16);
+}
+
 float round_to_tf32(float v) {
   if (!std::isfinite(v)) return v;
   uint32_t u;
@@ -191,6 +224,7 @@ class Planner {
   std::vector<char> skipped_;
   std::set<std::string> graph_outputs_;
   std::map<std::pair<int, int>, int> layout_memo_;
+  std::set<std::string> tf32_rounded_names_;
   int cur_node_ = -1;
 
   // ---- value bookkeeping ----
@@ -325,6 +359,26 @@ class Planner {
     layout_memo_[key] = out;
     return out;
   }
+  // The 16-bit float copy of an f32 value in the same memory order: the A operand of a kind::f16 contraction
+  // (context option float_precision).  One copy per value, shared by its consumers.
+  int half_copy(const NodeDef& n, int vi, DT dt16) {
+    auto key = std::make_pair(vi, 100 + (int)dt16);
+    auto it = layout_memo_.find(key);
+    if (it != layout_memo_.end()) return it->second;
+    Value src = V(vi);
+    int out = add_value(src.name + (dt16 == DT::F16 ? "@f16" : "@bf16"), src.shape, dt16, src.layout);
+    V(out).bytes = src.bytes / 2;  // padded layouts (the stem's row windows) keep their padding
+    const int64_t lanes = (int64_t)(src.bytes / 4);
+    Step& st = add_step(n, dt16 == DT::F16 ? "convert_f32_to_f16" : "convert_f32_to_bf16", 2, {vi}, {out});
+    st.work = 1.5 * (double)src.bytes;
+    st.launch = [this, vi, out, dt16, lanes](cudaStream_t s) {
+      k::convert_f32_to_half((const float*)V(vi).ptr, V(out).ptr, dt16, lanes, s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    layout_memo_[key] = out;
+    return out;
+  }
   // For order-free rank-4 values any kernel may treat the bytes as NHWC.
   Layout layout_for_kernel(const Value& v, Layout want) const { return (v.shape.size() == 4 && order_free(v)) ? want : effective_layout(v); }
 
@@ -339,7 +393,51 @@ class Planner {
     return ni;
   }
 
+  // Every producer decides whether to round its output to TF32 by asking this about its output's name; a "yes"
+  // is remembered, so that a contraction can tell whether its operand arrives rounded (tf32_ready).
   bool feeds_contraction(const std::string& name) {
+    const bool yes = feeds_contraction_impl(name);
+    if (yes) tf32_rounded_names_.insert(name);
+    return yes;
+  }
+  // Does the value hold TF32-rounded lanes?  Either its producer rounded it, or it was moved / selected (layout
+  // conversion, pooling by maximum, padding, slicing, concatenation, transposition, the stem's packing) out of
+  // values that were.  A graph input never is: the tensor pipe would truncate its low mantissa bits instead of
+  // rounding them, which doubles the operand error and biases it.
+  bool tf32_ready(int vi, int depth = 0) {
+    while (V(vi).alias_of >= 0) vi = V(vi).alias_of;
+    if (tf32_rounded_names_.count(V(vi).name)) return true;
+    if (V(vi).is_graph_input || V(vi).producer < 0 || depth > 12) return false;
+    const Step& ps = S.steps_[V(vi).producer];
+    static const char* movers[] = {"convert_layout", "max_pool", "pad", "slice", "concat", "transpose_perm", "transpose_a", "s2d_pack", "window_pack"};
+    bool mover = false;
+    for (const char* m : movers) mover = mover || ps.kernel.rfind(m, 0) == 0;
+    if (!mover || ps.reads.empty()) return false;
+    for (int r : ps.reads)
+      if (V(r).dt == DT::F32 && !tf32_ready(r, depth + 1)) return false;
+    return true;
+  }
+  // A TF32-rounded copy of an f32 value in the same memory order (round to nearest, ties away: cvt.rna), made once
+  // per value for the contractions that read it.
+  int tf32_copy(const NodeDef& n, int vi) {
+    auto key = std::make_pair(vi, 200);
+    auto it = layout_memo_.find(key);
+    if (it != layout_memo_.end()) return it->second;
+    Value src = V(vi);
+    int out = add_value(src.name + "@tf32", src.shape, DT::F32, src.layout);
+    V(out).bytes = src.bytes;
+    const int64_t lanes = (int64_t)(src.bytes / 4);
+    Step& st = add_step(n, "round_to_tf32", 2, {vi}, {out});
+    st.work = 2.0 * (double)src.bytes;
+    st.launch = [this, vi, out, lanes](cudaStream_t s) {
+      k::round_to_tf32_copy((const float*)V(vi).ptr, (float*)V(out).ptr, lanes, s);
+      C.counters.glue_launches++;
+      C.counters.kernel_launches++;
+    };
+    layout_memo_[key] = out;
+    return out;
+  }
+  bool feeds_contraction_impl(const std::string& name) {
     auto it = consumers_.find(name);
     if (it == consumers_.end()) return false;
     for (auto& c : it->second) {
@@ -348,7 +446,7 @@ class Planner {
       // look through nodes that only move or select values
       if (op == "MaxPool" || op == "Flatten" || op == "Reshape" || op == "Identity" || op == "Relu" || op == "Pad" || op == "Resize" ||
           op == "Concat" || op == "Transpose")
-        if (!nodes_[c.first].outputs.empty() && feeds_contraction(nodes_[c.first].outputs[0])) return true;
+        if (!nodes_[c.first].outputs.empty() && feeds_contraction_impl(nodes_[c.first].outputs[0])) return true;
     }
     return false;
   }
@@ -844,7 +942,14 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
   } else if (want_umma && xv.dt != DT::F32) {
     want_umma = false;
   }
-  if (want_umma && k::umma_channel_block(cs.C, c.is_int ? 0 : 1) == 0) want_umma = false, why = "channel count not a multiple of the block";
+  // float contractions: TF32 operands unless the context asks for f16 / bf16 operands and the channel count fits
+  // their 32-byte blocks (16 channels); accumulation is f32 either way
+  int float_kind = 1;
+  if (want_umma && !c.is_int && (C.cfg().float_precision == 1 || C.cfg().float_precision == 2)) {
+    const int k16 = C.cfg().float_precision == 1 ? 2 : 3;
+    if (k::umma_channel_block(cs.C, k16) != 0) float_kind = k16;
+  }
+  if (want_umma && k::umma_channel_block(cs.C, c.is_int ? 0 : float_kind) == 0) want_umma = false, why = "channel count not a multiple of the block";
   if (want_umma && cs.group != 1) want_umma = false, why = "grouped";
 
   // ---- epilogue parameter vectors ----
@@ -882,13 +987,14 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
   }
 
   if (want_umma) {
-    const int kind = c.is_int ? 0 : 1;
-    const size_t es = c.is_int ? 1 : 4;
+    const int kind = c.is_int ? 0 : float_kind;
+    const DT f_dt = float_kind == 2 ? DT::F16 : (float_kind == 3 ? DT::BF16 : DT::F32);
+    const size_t es = c.is_int ? 1 : dt_size(f_dt);
     const int64_t ktot = cs.K();
     const size_t wbytes = (size_t)OC * ktot * es;
     char form[96];
-    snprintf(form, sizeof form, "umma_%s_%dx%dx%dx%d_a%.9g%s", c.is_int ? dt_name(c.w_dt) : "tf32", OC, cs.C, cs.R, cs.S, (double)c.w_scale_mul,
-             c.w_is_kn ? "_kn" : "");
+    snprintf(form, sizeof form, "umma_%s_%dx%dx%dx%d_a%.9g%s", c.is_int ? dt_name(c.w_dt) : (float_kind == 1 ? "tf32" : dt_name(f_dt)), OC, cs.C, cs.R, cs.S,
+             (double)c.w_scale_mul, c.w_is_kn ? "_kn" : "");
     const float wmul = c.w_scale_mul;
     void* wdev = C.resident_form(
         c.w_name, form, wbytes,
@@ -897,8 +1003,13 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
             for (int64_t t = 0; t < taps; ++t)
               for (int ic = 0; ic < cs.C; ++ic) {
                 size_t o = (size_t)oc * ktot + (size_t)t * cs.C + ic;
-                if (c.is_int) ((uint8_t*)dst)[o] = (uint8_t)(wi_at(oc, ic, t) & 0xff);
-                else ((float*)dst)[o] = round_to_tf32(wmul == 1.0f ? w_at(oc, ic, t) : w_at(oc, ic, t) * wmul);
+                if (c.is_int) {
+                  ((uint8_t*)dst)[o] = (uint8_t)(wi_at(oc, ic, t) & 0xff);
+                } else {
+                  const float wv = wmul == 1.0f ? w_at(oc, ic, t) : w_at(oc, ic, t) * wmul;
+                  if (float_kind == 1) ((float*)dst)[o] = round_to_tf32(wv);
+                  else ((uint16_t*)dst)[o] = float_kind == 2 ? f32_to_f16_bits(wv) : f32_to_bf16_bits(wv);
+                }
               }
         },
         cache_w);
@@ -951,13 +1062,21 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
         epi.slope = upload_vec(sl);
       }
     }
+    int x_op_vi = x_vi;  // the value the kernel reads as its A operand
+    if (!c.is_int && float_kind != 1) {
+      x_op_vi = half_copy(n, x_vi, f_dt);
+      reads[0] = x_op_vi;
+    } else if (!c.is_int && !tf32_ready(x_vi)) {
+      x_op_vi = tf32_copy(n, x_vi);
+      reads[0] = x_op_vi;
+    }
     Step& st = add_step(n, "umma", 0, reads, {out_vi});
     st.work = c.algorithmic_ops > 0 ? c.algorithmic_ops : cs.ops();
     st.work_is_bytes = false;
-    const DT xdt = xv.dt, wdt = c.is_int ? c.w_dt : DT::F32;
+    const DT xdt = V(x_op_vi).dt, wdt = c.is_int ? c.w_dt : f_dt;
     Step* stp = &st;
     const int step_index = (int)S.steps_.size() - 1;
-    st.finalize = [this, step_index, x_vi, out_vi, xzp_vi, res_vi, dq_vi, wdev, xdt, wdt, cs, epi, kind, n]() mutable {
+    st.finalize = [this, step_index, x_vi = x_op_vi, out_vi, xzp_vi, res_vi, dq_vi, wdev, xdt, wdt, cs, epi, kind, n]() mutable {
       k::Epilogue e = epi;
       if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
       if (res_vi >= 0) e.residual = (const float*)V(res_vi).ptr;

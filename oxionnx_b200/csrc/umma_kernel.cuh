@@ -133,14 +133,30 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// Bounded wait: false when the barrier did not flip within WAIT_CYCLES or another role aborted.
-// try_wait parks the warp in hardware for a bounded time per attempt, so a waiting role leaves
-// its scheduler's issue slots to the epilogue warps that share it.
+// The same test with a suspend-time hint (nanoseconds): the warp may stay parked in hardware that long before the
+// instruction gives up, so a long wait costs few issue slots.
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok;
+}
+// Bounded wait: false when the barrier did not flip within WAIT_CYCLES or another role aborted.  A waiting role
+// shares its scheduler's issue slots with the epilogue warps, so the loop is kept to the parked test and a
+// counter; the abort flag and the clock are looked at once per 32 attempts (an attempt returns within a few
+// microseconds at the latest, so an abort is seen within a fraction of a millisecond and the limit holds).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long start = clock64();
+  const long long start = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int attempt = 0; attempt < 32; ++attempt)
+      if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
     if (*abort_flag) return false;
     if (clock64() - start > WAIT_CYCLES) return false;
   }
@@ -269,16 +285,16 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
         "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
         "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
+      : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The same wait, naming the registers a pending read lands in: nothing that uses them may be scheduled above it.
+// Neither this nor the read itself is a compiler barrier for memory: the per-channel parameter loads of the run's
+// math may be started above the wait, so that their latency (the top stall of the short-K layers) overlaps it.
 __device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
+               :);
 }
 
 // ---- fused epilogue math ------------------------------------------------------------------
@@ -313,8 +329,16 @@ __device__ __forceinline__ float act_f32(int act, float f, float slope, float lo
   return f;
 }
 
-// Packs 32 f32 results into the output type: f32 (32 words), f16 or bf16 (16 words).
+// Packs 32 f32 results into the output type: f32 (32 words), f16 or bf16 (16 words).  The tf32 kind only writes
+// f32: the choice is made at compile time there, so that the packed words of a run have one definition each (a
+// run-time choice between the 32-word and the 16-word form costs a select per word in an issue-bound loop).
+template <int KIND>
 __device__ __forceinline__ void pack_float(const float (&f)[4], int j4, int out_dt, uint32_t (&w)[32]) {
+  if (KIND == KIND_TF32) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) w[4 * j4 + e] = __float_as_uint(f[e]);
+    return;
+  }
   if (out_dt == (int)DT::F16) {
     __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
     w[2 * j4] = *reinterpret_cast<uint32_t*>(&a);
@@ -329,18 +353,22 @@ __device__ __forceinline__ void pack_float(const float (&f)[4], int j4, int out_
   }
 }
 
-template <int ACT, int RT, bool RES>
+template <int KIND, int ACT, int RT, bool RES>
 __device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[32], const float* __restrict__ bias, const float* __restrict__ slope,
                                          const float* __restrict__ res, uint32_t (&w)[32]) {
+  // this pixel's 32 channels of the residual: one full 128-byte line per thread, all eight loads in flight
+  // together before the first is used
+  float4 rv[RES ? 8 : 1];
+  if (RES) {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) rv[j4] = res != nullptr ? __ldg(reinterpret_cast<const float4*>(res) + j4) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 #pragma unroll
   for (int j4 = 0; j4 < 8; ++j4) {
     const float4 b = __ldg(reinterpret_cast<const float4*>(bias) + j4);
     const float bb[4] = {b.x, b.y, b.z, b.w};
     float rr[4] = {0.f, 0.f, 0.f, 0.f};
-    if (RES && res != nullptr) {  // this pixel's 32 channels of the residual: one full 128-byte line per thread
-      const float4 r = __ldg(reinterpret_cast<const float4*>(res) + j4);
-      rr[0] = r.x, rr[1] = r.y, rr[2] = r.z, rr[3] = r.w;
-    }
+    if (RES) rr[0] = rv[j4].x, rr[1] = rv[j4].y, rr[2] = rv[j4].z, rr[3] = rv[j4].w;
     float ss[4] = {0.f, 0.f, 0.f, 0.f};
     if (ACT == 4) {
       const float4 s = __ldg(reinterpret_cast<const float4*>(slope) + j4);
@@ -354,7 +382,7 @@ __device__ __forceinline__ void math_f32(const KParams& p, const uint32_t (&v)[3
       f[e] = act_f32(ACT, f[e], ss[e], p.clip_lo, p.clip_hi);
       if (RT) f[e] = round_tf32(f[e]);
     }
-    pack_float(f, j4, p.out_dt, w);
+    pack_float<KIND>(f, j4, p.out_dt, w);
   }
 }
 
@@ -617,10 +645,10 @@ __device__ __forceinline__ void math_dequant(const KParams& p, const uint32_t (&
 // 32 for 32-bit).  `oc` is the first channel of the run.  The variant is a template argument:
 // the whole tile loop of an epilogue warp is instantiated per variant, so the code a warp runs
 // is one straight body without a dispatch inside the loop.
-template <int VARIANT>
+template <int KIND, int VARIANT>
 __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t (&v)[32], int xz, int oc, size_t esz, const float* res, uint32_t (&w)[32]) {
-  if constexpr (VARIANT < V_F32_RES) math_f32<VARIANT / 2, VARIANT & 1, false>(p, v, p.bias_f + oc, p.slope + oc, nullptr, w);
-  else if constexpr (VARIANT < V_REQUANT) math_f32<(VARIANT - V_F32_RES) / 2, (VARIANT - V_F32_RES) & 1, true>(p, v, p.bias_f + oc, p.slope + oc, res, w);
+  if constexpr (VARIANT < V_F32_RES) math_f32<KIND, VARIANT / 2, VARIANT & 1, false>(p, v, p.bias_f + oc, p.slope + oc, nullptr, w);
+  else if constexpr (VARIANT < V_REQUANT) math_f32<KIND, (VARIANT - V_F32_RES) / 2, (VARIANT - V_F32_RES) & 1, true>(p, v, p.bias_f + oc, p.slope + oc, res, w);
   else if constexpr (VARIANT >= V_DEQUANT) {
     const float xs = __ldg(p.dq_x_scale);
     math_dequant<((VARIANT - V_DEQUANT) & 1) != 0, (VARIANT - V_DEQUANT) / 2>(p, v, p.bias_i + oc, p.wsum + oc, p.dq_w_scale + oc, p.dq_bias + oc, xz, xs, w);
@@ -666,9 +694,9 @@ __device__ __forceinline__ void store_direct(const uint32_t (&w)[32], uint8_t* o
 // Staged store: the run goes into this warp's shared-memory staging rows in the swizzled order a
 // TMA store with the matching swizzle mode expects (16-byte chunk index XOR row-derived bits), so
 // that the tile leaves the SM as full-line writes instead of 32 scattered 16-byte pieces.
-__device__ __forceinline__ void store_staged(const uint32_t (&w)[32], uint32_t stage_addr, int row, int pitch, int byte_off, int bytes) {
-  const uint32_t xor_bits = ((uint32_t)(row * pitch) >> 7) & (uint32_t)(pitch / 16 - 1);
-  const uint32_t row_addr = stage_addr + (uint32_t)(row * pitch);
+// `row_addr` is the lane's staging row, `xor_bits` its swizzle term (((row * pitch) >> 7) & (pitch / 16 - 1)): both
+// are fixed for the life of the warp and computed once by the caller.
+__device__ __forceinline__ void store_staged(const uint32_t (&w)[32], uint32_t row_addr, uint32_t xor_bits, int byte_off, int bytes) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     if (j * 16 < bytes) {
@@ -684,6 +712,27 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)map), "r"(src), "r"(c0), "r"(c1)
                : "memory");
 }
+
+// Tile coordinates of a CTA's walk over the tile list (channel tile fastest) without a division per tile: the
+// step splits once into whole rows of channel tiles and a remainder.  Used for the plain case (one item, no split
+// reduction); the batched and split forms decode the tile number as before.
+struct TileWalk {
+  int m, n, dm, dn, n_tiles;
+  __device__ __forceinline__ TileWalk(int tile0, int step, int n_tiles_) : n_tiles(n_tiles_) {
+    m = tile0 / n_tiles_;
+    n = tile0 - m * n_tiles_;
+    dm = step / n_tiles_;
+    dn = step - dm * n_tiles_;
+  }
+  __device__ __forceinline__ void next() {
+    m += dm;
+    n += dn;
+    if (n >= n_tiles) {
+      n -= n_tiles;
+      ++m;
+    }
+  }
+};
 
 // How the epilogue warps of a block share tiles (see the file header).
 template <int BN, int EW>
@@ -704,10 +753,11 @@ struct EpiShape {
 // stores.  The accumulator is handed back to the MMA issuer as soon as this warp's last TMEM read
 // has landed, before the last run's math.  `acc_empty` is the barrier address to arrive on: the
 // CTA's own, or the even CTA's for a pair (a shared::cluster address).
-template <int BN, int EW, int VARIANT, bool SPLIT, bool PAIR>
+template <int BN, int KIND, int VARIANT, bool SPLIT, bool PAIR>
 __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int lane, uint32_t tmem_base, uint64_t* bar_acc_full,
                                               uint64_t* bar_acc_empty, uint32_t stage_addr, volatile int* abortp, int total_tiles, int tile0, int tile_step,
                                               int pair_rank) {
+  constexpr int EW = epi_warps(KIND);
   using ES = EpiShape<BN, EW>;
   constexpr int CPW = ES::CPW;
   const int quarter = warp & 3;
@@ -720,9 +770,13 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
   const size_t esz = (p.out_dt == (int)DT::F32 || p.out_dt == (int)DT::I32) ? 4 : ((p.out_dt == (int)DT::I16 || p.out_dt == (int)DT::F16 || p.out_dt == (int)DT::BF16) ? 2 : 1);
   const int chunk_bytes = 32 * (int)esz;
   const int pitch = p.out_row_bytes;  // staged row length: 32, 64 or 128 bytes, at most one warp's share of a row
-  const int cpg = p.out_tma ? pitch / chunk_bytes : 1;
+  const int cpg = p.out_tma ? pitch / chunk_bytes : 1;  // runs per staged store: 1, 2 or 4
+  const uint32_t stage_row_addr = stage_addr + (uint32_t)(lane * pitch);
+  const uint32_t stage_xor = ((uint32_t)(lane * pitch) >> 7) & (uint32_t)(pitch / 16 - 1);
   uint32_t local = 0;
-  for (int t = tile0; t < total_tiles; t += tile_step, ++local) {
+  const bool plain = !p.batched && p.splits == 1;
+  TileWalk walk(tile0, tile_step, p.n_tiles);
+  for (int t = tile0; t < total_tiles; t += tile_step, ++local, walk.next()) {
     if (ES::NG > 1 && (int)(local % ES::NG) != group) continue;
     int tt = t, o_row0 = 0, o_col0 = 0;
     if (p.batched) {
@@ -734,7 +788,7 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     } else if (p.splits > 1) {
       tt = t / p.splits;
     }
-    const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
+    const int tile_n = plain ? walk.n : tt % p.n_tiles, tile_m = plain ? walk.m : tt / p.n_tiles;
     const int m0 = tile_m * (PAIR ? 2 * BLOCK_M : BLOCK_M) + (PAIR ? pair_rank * BLOCK_M : 0), oc0 = tile_n * BN;
     const uint32_t buf = local % (uint32_t)ES::NACC;
     bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (local / (uint32_t)ES::NACC) & 1u, abortp);
@@ -762,17 +816,17 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     };
     auto math = [&](const uint32_t(&v)[32], int ch) {
       const float* res = (VARIANT >= V_F32_RES && VARIANT < V_REQUANT && row_ok) ? p.residual + (size_t)m * p.OC + oc0 + ch * 32 : nullptr;
-      epilogue_chunk<VARIANT>(p, v, xz, oc0 + ch * 32, esz, res, w);
+      epilogue_chunk<KIND, VARIANT>(p, v, xz, oc0 + ch * 32, esz, res, w);
     };
     auto store = [&](int ch) {
       if (p.out_tma) {
-        const int in_group = (ch - first) % cpg;
+        const int in_group = (ch - first) & (cpg - 1);
         if (in_group == 0) {
           // the staging rows are rewritten: their previous store must have read them
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           __syncwarp();
         }
-        store_staged(w, stage_addr, lane, pitch, in_group * chunk_bytes, chunk_bytes);
+        store_staged(w, stage_row_addr, stage_xor, in_group * chunk_bytes, chunk_bytes);
         if (in_group == cpg - 1 || ch == end - 1) {
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
@@ -840,18 +894,17 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
         emit(va, c);
       }
     } else {
-      tmem_ld32_nowait(taddr + (uint32_t)first * 32u, va);
-      tmem_ld_wait_for(va);
-      // one copy of the run's code in the loop; a run's math leaves its packed words in `w`, so the next run's
-      // TMEM read can land in the same registers while the words are staged and handed to the TMA store
+      // One copy of the run's code in the loop, each run reading its own accumulator columns first.  Starting the
+      // next run's TMEM read under this run's store was measured and is slower (102.6 us against 96.7 us on a 1x1
+      // 64 -> 256 layer at M = 802816): the other epilogue warps of the scheduler hide the read's latency, and the
+      // conditional read costs register moves at the loop's join.
 #pragma unroll 1
       for (int c = first; c < end; ++c) {
-        const bool more = c + 1 < end;
+        tmem_ld32_nowait(taddr + (uint32_t)c * 32u, va);
+        tmem_ld_wait_for(va);
+        if (c + 1 == end) release();
         math(va, c);
-        if (more) tmem_ld32_nowait(taddr + (uint32_t)(c + 1) * 32u, va);
-        else release();
         store(c);
-        if (more) tmem_ld_wait_for(va);
       }
     }
   }
@@ -934,7 +987,9 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
     bool ok = true;
     // a pair's copies are counted on the even CTA's barrier, which alone announces the bytes of both
     const uint32_t tx_per_kb = PAIR ? 2u * kb_bytes : kb_bytes;
-    for (int t = tile0; t < total_tiles && ok; t += tile_step) {
+    const bool plain = !p.batched && p.splits == 1;
+    TileWalk walk(tile0, tile_step, p.n_tiles);
+    for (int t = tile0; t < total_tiles && ok; t += tile_step, walk.next()) {
       int tt = t, a_row0 = 0, a_col0 = 0, b_row0 = 0, b_col0 = 0;
       int it_begin = 0, it_end = k_iters;
       if (p.batched) {
@@ -950,7 +1005,7 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
         it_begin = (t - tt * p.splits) * p.k_per;
         it_end = min(k_iters, it_begin + p.k_per);
       }
-      const int tile_n = tt % p.n_tiles, tile_m = tt / p.n_tiles;
+      const int tile_n = plain ? walk.n : tt % p.n_tiles, tile_m = plain ? walk.m : tt / p.n_tiles;
       const int m0 = tile_m * (PAIR ? 2 * BLOCK_M : BLOCK_M) + (PAIR ? pair_rank * BLOCK_M : 0);
       const int oc0 = tile_n * BN + (PAIR ? pair_rank * B_ROWS : 0);
       int q0 = 0, p0 = 0, n0 = 0;
@@ -1100,8 +1155,8 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
     const bool split = !p.batched && p.splits > 1;
 #define OXB_EPI(V)                                                                                                                                    \
   case V:                                                                                                                                             \
-    if (!PAIR && split) epilogue_role<BN, EW, V, !PAIR, PAIR>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles, tile0, tile_step, pair_rank); \
-    else epilogue_role<BN, EW, V, false, PAIR>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles, tile0, tile_step, pair_rank); \
+    if (!PAIR && split) epilogue_role<BN, KIND, V, !PAIR, PAIR>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles, tile0, tile_step, pair_rank); \
+    else epilogue_role<BN, KIND, V, false, PAIR>(p, warp, lane, tmem_base, bar_acc_full, bar_acc_empty, stage_addr, abortp, total_tiles, tile0, tile_step, pair_rank); \
     break;
     if constexpr (KIND == KIND_I8) {
       switch (p.variant) {

@@ -114,7 +114,7 @@ class CudaContext:
     """One device, one stream, session-lifetime weight residency."""
 
     def __init__(self, device: int = 0, *, verify=False, strict=False, residency=True, kernel_path="auto", keep_intermediates=False,
-                 profile=False, cuda_graph=False, requant_f64=False, split_k_max=0, cta_pairs="auto"):
+                 profile=False, cuda_graph=False, requant_f64=False, split_k_max=0, cta_pairs="auto", float_precision="tf32"):
         cfg = _ffi.Config()
         cfg.struct_size = ctypes.sizeof(_ffi.Config)
         cfg.verify, cfg.strict, cfg.residency = int(verify), int(strict), int(residency)
@@ -125,6 +125,8 @@ class CudaContext:
         cfg.requant_f64 = int(requant_f64)  # False/0 auto, True/1 two-pass f64, 2 one-FMA without the packed saturation
         cfg.split_k_max = int(split_k_max)
         cfg.cta_pairs = {"auto": 0, "never": 1, "always": 2}[cta_pairs]
+        # operand type of the float contractions on the tensor cores (f32 accumulation and f32 results in every case)
+        cfg.float_precision = {"tf32": 0, "f16": 1, "bf16": 2}[float_precision]
         h = ctypes.c_void_p()
         st = _ffi.lib().oxb200_ctx_create(device, ctypes.byref(cfg), ctypes.byref(h))
         if st != _ffi.OK_HOST:
@@ -290,7 +292,8 @@ class SessionBuilder:
         return self
 
     def with_tuning(self, **kw):
-        """Kernel choices of the context: requant_f64, split_k_max, cta_pairs ("auto" | "never" | "always")."""
+        """Kernel choices of the context: requant_f64, split_k_max, cta_pairs ("auto" | "never" | "always"),
+        float_precision ("tf32" | "f16" | "bf16": the operand type of float contractions)."""
         self._ctx_kw.update(kw)
         return self
 

@@ -1,0 +1,171 @@
+"""Teacher-forced float parity: every float node of the float networks is run through the operator boundary
+(oxb200_dispatch) on the ORACLE's inputs for that node and compared element by element with the oracle's output
+for it, so that no error of an earlier layer can hide or excuse a later one.
+
+Tolerance, per element:  |a - b| <= 2e-3 * |b| + 2e-3 * rms(b).
+The relative part is the TF32 tolerance of the path (operands rounded to 11 significant bits: 2^-11 each, two
+operands).  The absolute part covers lanes that cancel: the rounding error of a K-term product sum does not
+shrink with the sum, it is of the order 2^-11 * sqrt(K) * rms(x) * rms(w), i.e. 2^-11 of the output's own rms.
+Integer and quantised nodes are bit-exact and covered elsewhere; here only float nodes are checked.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from oxionnx_b200 import models, session as S
+from oxionnx_b200.graph import Node
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 2e-3
+EXACT_OPS = {"Relu", "MaxPool", "Flatten", "Reshape", "Transpose", "Concat", "Slice", "Pad", "Gather", "Identity", "Cast", "Resize"}
+SKIP_OPS = {"DynamicQuantizeLinear", "MatMulInteger", "QLinearConv", "QLinearMatMul", "ConvInteger", "QuantizeLinear", "DequantizeLinear"}
+
+
+def per_element_violations(got, want):
+    want64 = want.astype(np.float64)
+    rms = float(np.sqrt(np.mean(want64 * want64))) if want.size else 0.0
+    bound = RTOL * np.abs(want64) + RTOL * rms
+    err = np.abs(got.astype(np.float64) - want64)
+    worst = float(np.max(err / (bound + 1e-300))) if want.size else 0.0
+    return int(np.sum(err > bound)), worst
+
+
+def teacher_forced(graph, weights, feeds):
+    ref = oracle.run_graph(graph, weights, feeds)
+    ctx = S.CudaContext(0)
+    report, failures = {}, []
+    try:
+        for node in graph.nodes:
+            if node.op in SKIP_OPS:
+                continue
+            inter = {n: (weights[n] if n in weights else ref[n]) for n in node.inputs if n}
+            got = S.try_cuda_dispatch(Node(node.op, node.name, node.inputs, node.outputs, node.attrs), {}, inter, ctx)
+            assert got is not None, f"{node.name} ({node.op}) was declined: {ctx.last_error()}"
+            for g_, name in zip(got, node.outputs):
+                want = ref[name]
+                assert g_.shape == want.shape, name
+                if node.op in EXACT_OPS:
+                    if not np.array_equal(g_, want):
+                        failures.append(f"{node.name} ({node.op}): not bit-exact")
+                    continue
+                bad, worst = per_element_violations(g_, want)
+                report[node.op] = max(report.get(node.op, 0.0), worst)
+                if bad:
+                    failures.append(f"{node.name} ({node.op}) -> {name}: {bad} of {want.size} lanes over the bound, worst {worst:.2f}x")
+    finally:
+        ctx.close()
+    assert not failures, "\n".join(failures[:20])
+    return report
+
+
+def test_resnet50_f32_every_float_node_on_the_oracles_inputs():
+    graph, weights, feeds, _ = models.build_resnet50_f32(batch=2, image=64, base=16, classes=40)
+    report = teacher_forced(graph, weights, feeds(2))
+    assert {"Conv", "Gemm", "GlobalAveragePool"} <= set(report), report
+    print("worst error / bound per operator:", {k: round(v, 3) for k, v in report.items()})
+
+
+def test_inswapper_f32_every_float_node_on_the_oracles_inputs():
+    graph, weights, feeds, _ = models.build_inswapper_f32(batch=2, size=32, widths=(32, 64, 96, 128), blocks=2, latent=64)
+    report = teacher_forced(graph, weights, feeds(2))
+    assert {"Conv", "OxiInstanceNorm", "Gemm", "Mul", "Add", "Tanh"} <= set(report), report
+    print("worst error / bound per operator:", {k: round(v, 3) for k, v in report.items()})
+
+
+def test_bert_float_nodes_on_the_oracles_inputs():
+    graph, weights, feeds, _ = models.build_bert_dynamic_int8(batch=2, seq=32, hidden=128, heads=4, ffn=256, layers=2, vocab=500)
+    report = teacher_forced(graph, weights, feeds(2))
+    assert {"LayerNormalization", "Softmax", "MatMul"} <= set(report), report
+    print("worst error / bound per operator:", {k: round(v, 3) for k, v in report.items()})
+
+
+@pytest.mark.parametrize("config", ["c2", "c3", "c4"])
+def test_final_outputs_of_the_float_networks_within_one_percent(config):
+    """Teacher-free, whole network, final output: max |a - b| <= 1e-2 * max |b| (the float tolerance of the
+    path for a network's output; per-node tolerances are the teacher-forced tests above)."""
+    if config == "c2":
+        graph, weights, feeds, _ = models.build_resnet50_f32(batch=2, image=96, base=32, classes=100)
+        out_name = "logits"
+    elif config == "c3":
+        graph, weights, feeds, _ = models.build_inswapper_f32(batch=2, size=32, widths=(32, 64, 96, 128), blocks=2, latent=64)
+        out_name = "image"
+    else:
+        graph, weights, feeds, _ = models.build_bert_dynamic_int8(batch=2, seq=32, hidden=128, heads=4, ffn=256, layers=2, vocab=500)
+        out_name = "hidden"
+    f = feeds(2)
+    want = oracle.run_graph(graph, weights, f, keep_all=False)[out_name]
+    sess = S.Session.builder().build_from_graph(graph, weights)
+    got = sess.run(f)[out_name]
+    sess.close()
+    err = float(np.max(np.abs(got.astype(np.float64) - want)) / np.max(np.abs(want)))
+    print(f"{config}: final-output error {err:.2e} of the output's magnitude")
+    assert err <= 1e-2, err
+
+
+# ---- 16-bit float operands (context option float_precision): same tests, tolerance 1e-2 ---------------------------
+HALF_TOL = {"f16": 1e-2, "bf16": 3e-2}  # f16: 11 significant bits; bf16 keeps 8 (2^-9 per operand), three times the bound
+
+
+def half_close(got, want, what, tol=1e-2):
+    want64 = want.astype(np.float64)
+    rms = float(np.sqrt(np.mean(want64 * want64)))
+    bound = tol * np.abs(want64) + tol * rms
+    err = np.abs(got.astype(np.float64) - want64)
+    assert got.shape == want.shape, what
+    assert np.all(err <= bound), f"{what}: {int(np.sum(err > bound))} of {want.size} lanes over the bound, worst {float(np.max(err / bound)):.2f}x"
+
+
+@pytest.mark.parametrize("precision", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 64, 14, 14, 128, 3, 1, 1), (2, 32, 9, 9, 48, 1, 1, 0), (1, 256, 14, 14, 256, 3, 1, 1), (2, 128, 16, 16, 64, 3, 2, 1), (1, 48, 7, 7, 80, 1, 1, 0)],
+                         ids=["3x3 64->128", "1x1 32->48", "3x3 256->256", "3x3 stride 2", "1x1 48->80"])
+def test_float_conv_with_16_bit_operands(precision, shape):
+    n, c, h, w_, oc, k, stride, pad = shape
+    rng = np.random.default_rng(c * 7 + oc)
+    x = rng.standard_normal((n, c, h, w_)).astype(np.float32)
+    wt = (rng.standard_normal((oc, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    b = rng.standard_normal(oc).astype(np.float32)
+    attrs = dict(pads=[pad] * 4, strides=[stride, stride], activation="relu")
+    want = oracle.run_node("Conv", [x, wt, b], attrs)[0]
+    ctx = S.CudaContext(0, float_precision=precision, profile=True)
+    try:
+        node = Node("Conv", "conv", ["x", "w", "b"], ["y"], attrs)
+        got = S.try_cuda_dispatch(node, {}, {"x": x, "w": wt, "b": b}, ctx)
+        assert got is not None, ctx.last_error()
+        half_close(got[0], want, f"Conv with {precision} operands", HALF_TOL[precision])
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("precision", ["f16", "bf16"])
+def test_gemm_and_matmul_with_16_bit_operands(precision):
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((96, 256)).astype(np.float32)
+    bm = (rng.standard_normal((256, 160)) / 16).astype(np.float32)
+    bias = rng.standard_normal(160).astype(np.float32)
+    ctx = S.CudaContext(0, float_precision=precision)
+    try:
+        got = S.try_cuda_dispatch(Node("Gemm", "g", ["a", "b", "c"], ["y"], {}), {"b": bm, "c": bias}, {"a": a}, ctx)
+        assert got is not None, ctx.last_error()
+        half_close(got[0], oracle.run_node("Gemm", [a, bm, bias], {})[0], f"Gemm {precision}", HALF_TOL[precision])
+        got = S.try_cuda_dispatch(Node("MatMul", "m", ["a", "b"], ["y"], {}), {"b": bm}, {"a": a}, ctx)
+        assert got is not None, ctx.last_error()
+        half_close(got[0], oracle.run_node("MatMul", [a, bm], {})[0], f"MatMul {precision}", HALF_TOL[precision])
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("precision", ["f16", "bf16"])
+def test_resnet50_with_16_bit_operands_runs_on_the_16_bit_kind(precision):
+    graph, weights, feeds, _ = models.build_resnet50_f32(batch=2, image=64, base=16, classes=40)
+    f = feeds(2)
+    want = oracle.run_graph(graph, weights, f, keep_all=False)["logits"]
+    sess = S.Session.builder().with_tuning(float_precision=precision).build_from_graph(graph, weights)
+    got = sess.run(f)["logits"]
+    kernels = [st["kernel"] for st in sess.steps()]
+    sess.close()
+    assert any(k.startswith(f"umma_{precision}") for k in kernels), kernels
+    assert any(k.startswith("convert_f32_to_") for k in kernels), kernels
+    err = float(np.max(np.abs(got.astype(np.float64) - want)) / np.max(np.abs(want)))
+    print(f"{precision}: final-output error {err:.2e} of the output's magnitude")
+    assert err <= (1e-2 if precision == "f16" else 3e-2), err
