@@ -232,6 +232,22 @@ int oxb200_shadow_verify(oxb200_ctx* ctx, const char* op_type, const float* devi
 int oxb200_tensor_shape(const oxb200_tensor* t, uint64_t* shape, uint32_t* rank, uint64_t* len);
 int oxb200_tensor_read_back(oxb200_ctx* ctx, const oxb200_tensor* t, float* dst_lanes, uint64_t cap);
 void oxb200_tensor_release(oxb200_ctx* ctx, oxb200_tensor* t);
+/* CudaDeviceTensor::alias (src/activation.rs:150-163): another handle to the same allocation under another shape
+ * of the same element count (what Reshape / Flatten of a resident value become).  DECLINED -- the reference's
+ * None -- when the counts differ, or when the tensor is stored channels-last and the new shape would read its
+ * bytes in another order.  The allocation lives until the last handle to it is released. */
+int oxb200_tensor_alias(oxb200_ctx* ctx, const oxb200_tensor* t, const uint64_t* shape, uint32_t rank, oxb200_tensor** out);
+/* CudaDeviceTensor::reserved_bytes (src/activation.rs:116-148): device bytes of the allocation behind the handle. */
+uint64_t oxb200_tensor_reserved_bytes(const oxb200_tensor* t);
+/* CudaContext::streams_unified (src/context.rs:384): every launch and copy of a dispatch or a run rides one queue
+ * (always 1 here; the pipelined submit / collect pair orders its copy streams against it with events). */
+int oxb200_streams_unified(const oxb200_ctx* ctx);
+/* CudaContext::cached_device_bytes (src/context.rs:445): device bytes held for reuse (packed weight forms). */
+uint64_t oxb200_cached_device_bytes(oxb200_ctx* ctx);
+/* CudaContext::set_graph_capture / graph_capture_enabled (src/context.rs:416-424): whether later runs of a planned
+ * session replay its step list as a CUDA graph; recordings already made are kept.  Never on under verification. */
+int oxb200_set_graph_capture(oxb200_ctx* ctx, int on);
+int oxb200_graph_capture_enabled(const oxb200_ctx* ctx);
 
 /* ---- planned, device-resident session run --------------------------------------------- */
 

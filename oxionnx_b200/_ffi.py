@@ -76,6 +76,12 @@ SYMBOLS = {
     "oxb200_env_truthy": (ctypes.c_int, [ctypes.c_char_p]),
     "oxb200_config_from_env": (None, [_P(Config)]),
     "oxb200_device_count": (ctypes.c_int, []),
+    "oxb200_tensor_alias": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, _P(ctypes.c_uint64), ctypes.c_uint32, _P(ctypes.c_void_p)]),
+    "oxb200_tensor_reserved_bytes": (ctypes.c_uint64, [ctypes.c_void_p]),
+    "oxb200_streams_unified": (ctypes.c_int, [ctypes.c_void_p]),
+    "oxb200_cached_device_bytes": (ctypes.c_uint64, [ctypes.c_void_p]),
+    "oxb200_set_graph_capture": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "oxb200_graph_capture_enabled": (ctypes.c_int, [ctypes.c_void_p]),
     "oxb200_ctx_create": (ctypes.c_int, [ctypes.c_int, _P(Config), _P(ctypes.c_void_p)]),
     "oxb200_ctx_destroy": (None, [ctypes.c_void_p]),
     "oxb200_last_error": (ctypes.c_char_p, [ctypes.c_void_p]),

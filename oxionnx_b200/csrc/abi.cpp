@@ -280,9 +280,54 @@ void oxb200_tensor_release(oxb200_ctx* ctx, oxb200_tensor* t) {
     cudaSetDevice(ctx->impl.device());
     cudaStreamSynchronize(ctx->impl.stream());
   }
-  if (t->h.ptr) cudaFree(t->h.ptr);
+  // an allocation shared with aliases (oxb200_tensor_alias) lives until its last handle is released
+  if (t->h.ptr && t->h.owners.use_count() == 1) cudaFree(t->h.ptr);
   delete t;
 }
+
+int oxb200_tensor_alias(oxb200_ctx* ctx, const oxb200_tensor* t, const uint64_t* shape, uint32_t rank, oxb200_tensor** out) {
+  if (!t || !out || (!shape && rank) || rank > OXB200_MAX_RANK) return fail_with(ctx, OXB200_FAILED, "tensor_alias: bad argument");
+  *out = nullptr;
+  // CudaDeviceTensor::alias returns None when the element counts differ; so does this (DECLINED)
+  uint64_t len = 1;
+  for (uint32_t d = 0; d < rank; ++d) {
+    if (shape[d] != 0 && len > UINT64_MAX / shape[d]) return fail_with(ctx, OXB200_DECLINED, "tensor_alias: the shape's element count overflows");
+    len *= shape[d];
+  }
+  if (len != (uint64_t)prod(t->h.shape)) return fail_with(ctx, OXB200_DECLINED, "tensor_alias: the shape has another element count");
+  // the lanes of a rank-4 value are stored channels-last: another shape over the same bytes is the same tensor
+  // only when the two orders coincide (one channel, or a 1x1 plane) -- otherwise the caller reads back and reshapes
+  const std::vector<int64_t>& s0 = t->h.shape;
+  const bool order_free = s0.size() != 4 || t->h.layout == Layout::PLAIN || s0[1] == 1 || (s0[2] == 1 && s0[3] == 1);
+  if (!order_free) return fail_with(ctx, OXB200_DECLINED, "tensor_alias: the tensor is stored channels-last; its bytes are not in the order of the new shape");
+  bool new_order_free = rank != 4 || shape[1] == 1 || (shape[2] == 1 && shape[3] == 1);
+  if (!new_order_free && t->h.layout != Layout::PLAIN) return fail_with(ctx, OXB200_DECLINED, "tensor_alias: a rank-4 view of these bytes would be read channels-last");
+  oxb200_tensor* a = new oxb200_tensor();
+  a->h = t->h;  // shares `owners`
+  a->h.shape.assign(shape, shape + rank);
+  if (rank == 4 && !new_order_free) a->h.layout = Layout::PLAIN;
+  *out = a;
+  return OXB200_OK_DEVICE;
+}
+
+uint64_t oxb200_tensor_reserved_bytes(const oxb200_tensor* t) { return t ? (uint64_t)t->h.bytes : 0; }
+
+int oxb200_streams_unified(const oxb200_ctx* ctx) { return ctx ? 1 : 0; }
+
+uint64_t oxb200_cached_device_bytes(oxb200_ctx* ctx) {
+  if (!ctx) return 0;
+  std::lock_guard<std::mutex> lock(ctx->impl.mu);
+  return ctx->impl.cached_bytes();
+}
+
+int oxb200_set_graph_capture(oxb200_ctx* ctx, int on) {
+  if (!ctx) return OXB200_FAILED;
+  std::lock_guard<std::mutex> lock(ctx->impl.mu);
+  ctx->impl.set_graph_capture(on);
+  return OXB200_OK_HOST;
+}
+
+int oxb200_graph_capture_enabled(const oxb200_ctx* ctx) { return ctx && ctx->impl.cfg().cuda_graph && !ctx->impl.cfg().verify ? 1 : 0; }
 
 int oxb200_dispatch(oxb200_ctx* ctx, const oxb200_node* node, const oxb200_operand* operands, uint32_t n_operands, int want_placement,
                     oxb200_result* results, uint32_t n_results) {

@@ -65,8 +65,9 @@ void dynamic_quantize_scratch_init(float* scratch);
 struct ResidualParams {
   float a_scale, a_zp, b_scale, b_zp, y_scale, y_zp, lo, hi;
   int relu;
-  // set by residual_requant_prepare(): the division-free kernel gives the reference's result for
-  // every one of the 256 x 256 input pairs (checked on the host, pair by pair)
+  // set by residual_requant_prepare(): 1 when the division-free lane gives the reference's result for every one of
+  // the 256 x 256 input pairs (checked on the host, pair by pair); 2 when the pairwise form (f32x2 arithmetic, ReLU
+  // folded into the lower clamp bound, packed 16-bit clamp) does so too; 0 otherwise (the IEEE division runs)
   int proven_fast;
   float y_rcp;
 };

@@ -640,6 +640,47 @@ __global__ void max_pool_nhwc_vec_kernel(const uint4* __restrict__ x, uint4* __r
   }
 }
 
+// The 3x3 / stride 2 / pad 1 pool of the ResNet front end on 8-bit lanes: the nine loads of a window are issued
+// together (clamped coordinates; a tap outside the image contributes the identity of max), 32-bit index arithmetic.
+template <bool SIGNED>
+__global__ void max_pool_3x3s2_q_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int H, int W, int P, int Q, int cvec, int total) {
+  const uint32_t ident = SIGNED ? 0x80808080u : 0u;
+  for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < total; o += gridDim.x * blockDim.x) {
+    const int c = o % cvec;
+    int t = o / cvec;
+    const int q = t % Q;
+    t /= Q;
+    const int p = t % P, n = t / P;
+    const int h0 = 2 * p - 1, w0 = 2 * q - 1;
+    uint4 v[9];
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      const int ih = min(max(h0 + r, 0), H - 1);
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        const int iw = min(max(w0 + s, 0), W - 1);
+        v[3 * r + s] = __ldg(x + ((size_t)(n * H + ih) * W + iw) * cvec + c);
+      }
+    }
+    uint4 best = make_uint4(ident, ident, ident, ident);
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        // a clamped coordinate re-reads a pixel of the window itself, which cannot change the maximum -- except
+        // that the window must not reach past the image on the far side (odd extents), where the tap is dropped
+        const bool inside = h0 + r < H && w0 + s < W;
+        const uint4 u = v[3 * r + s];
+        if (inside) {
+          if (SIGNED) best = make_uint4(__vmaxs4(best.x, u.x), __vmaxs4(best.y, u.y), __vmaxs4(best.z, u.z), __vmaxs4(best.w, u.w));
+          else best = make_uint4(__vmaxu4(best.x, u.x), __vmaxu4(best.y, u.y), __vmaxu4(best.z, u.z), __vmaxu4(best.w, u.w));
+        }
+      }
+    }
+    y[o] = best;
+  }
+}
+
 // One thread per (n, c): the sum runs over the plane in (h, w) order exactly like the
 // reference loop; consecutive threads read consecutive channels, so loads are coalesced.
 __global__ void global_avg_pool_nhwc_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 d, int rtf32) {
@@ -886,18 +927,83 @@ __device__ __forceinline__ float residual_fast(uint32_t a_bits, uint32_t b_bits,
 }
 
 // 16 lanes per thread: two 16-byte loads, one 16-byte store.
-template <bool FAST>
-__global__ void residual_requant_kernel(const uint4* __restrict__ a, bool a_signed, const uint4* __restrict__ b, bool b_signed, uint4* __restrict__ y,
-                                        int64_t n16, ResidualParams rp) {
-  const float off_a = 8388608.0f + rp.a_zp + (a_signed ? 128.f : 0.f), off_b = 8388608.0f + rp.b_zp + (b_signed ? 128.f : 0.f);
-  const uint32_t flip_a = a_signed ? 0x80808080u : 0u, flip_b = b_signed ? 0x80808080u : 0u;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
-    const uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
+// ---- the same lane, two at a time (proven_fast == 2) ------------------------------------------------------------
+// f32x2 instructions give the IEEE result of each lane with half the issue slots; the ReLU is folded into the lower
+// clamp bound (the quotient by a positive scale and the rounding are monotone and map 0 to 0, so
+// max(round(sum / s), 0) + zp == round(max(sum, 0) / s) + zp); and because 1.5 * 2^23 has sixteen zero low bits, the
+// low half-word of t = (q + 1.5 * 2^23) + zp is the rounded result itself as an int16, so two results are clamped
+// with one packed max and one packed min.  residual_requant_prepare() evaluates exactly this formula for all
+// 256 x 256 input pairs and enables it only when every pair gives the reference's lane and stays inside int16.
+struct F2 {
+  float x, y;
+};
+__device__ __forceinline__ F2 add2(F2 a, F2 b) {
+  uint64_t ra, rb, rd;
+  F2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ F2 mul2(F2 a, F2 b) {
+  uint64_t ra, rb, rd;
+  F2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ F2 fma2(F2 a, F2 b, F2 c) {
+  uint64_t ra, rb, rc, rd;
+  F2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+// Two lanes (bytes e and e + 1 of the words wa, wb): returns the two clamped results as packed int16.
+__device__ __forceinline__ uint32_t residual_pair(uint32_t wa, uint32_t wb, int e, F2 noff_a, F2 noff_b, F2 sa, F2 sb, F2 rcp, F2 nys, F2 magic, F2 zp,
+                                                  uint32_t lo2, uint32_t hi2) {
+  const F2 abits = {__uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7440 + e)), __uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7441 + e))};
+  const F2 bbits = {__uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7440 + e)), __uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7441 + e))};
+  // The two dequantising products are scalar __fmul_rn: on this toolchain a packed multiply whose result feeds a
+  // packed add came out as if fused (5 * 0.02f + 0.05f gave 0.15f, not 0.14999999f), which moves exact ties.
+  const F2 da = add2(abits, noff_a), db = add2(bbits, noff_b);
+  const F2 va = {__fmul_rn(da.x, sa.x), __fmul_rn(da.y, sa.y)}, vb = {__fmul_rn(db.x, sb.x), __fmul_rn(db.y, sb.y)};
+  const F2 sum = add2(va, vb);
+  const F2 q0 = mul2(sum, rcp);
+  const F2 q = fma2(fma2(q0, nys, sum), rcp, q0);
+  const F2 t = add2(add2(q, magic), zp);
+  const uint32_t p = __byte_perm(__float_as_uint(t.x), __float_as_uint(t.y), 0x5410);
+  return __vmins2(__vmaxs2(p, lo2), hi2);
+}
+
+template <int MODE>
+__device__ __forceinline__ uint4 residual_vec(const uint4 av, const uint4 bv, bool a_signed, bool b_signed, float off_a, float off_b, uint32_t flip_a,
+                                              uint32_t flip_b, const ResidualParams& rp) {
     const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
     uint32_t out[4];
+    if (MODE == 2) {
+      const float lo_eff = rp.relu ? fmaxf(rp.lo, rp.y_zp) : rp.lo;
+      const uint32_t lo2 = ((uint32_t)(int)lo_eff & 0xffffu) * 0x00010001u, hi2 = ((uint32_t)(int)rp.hi & 0xffffu) * 0x00010001u;
+      const F2 noff_a = {-off_a, -off_a}, noff_b = {-off_b, -off_b}, sa = {rp.a_scale, rp.a_scale}, sb = {rp.b_scale, rp.b_scale};
+      const F2 rcp = {rp.y_rcp, rp.y_rcp}, nys = {-rp.y_scale, -rp.y_scale}, magic = {12582912.0f, 12582912.0f}, zp = {rp.y_zp, rp.y_zp};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t wa = aw[j] ^ flip_a, wb = bw[j] ^ flip_b;
+        const uint32_t p01 = residual_pair(wa, wb, 0, noff_a, noff_b, sa, sb, rcp, nys, magic, zp, lo2, hi2);
+        const uint32_t p23 = residual_pair(wa, wb, 2, noff_a, noff_b, sa, sb, rcp, nys, magic, zp, lo2, hi2);
+        out[j] = __byte_perm(p01, p23, 0x6420);
+      }
+      return make_uint4(out[0], out[1], out[2], out[3]);
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (FAST) {
+      if (MODE == 1) {
         const uint32_t wa = aw[j] ^ flip_a, wb = bw[j] ^ flip_b;
         uint32_t r[4];
 #pragma unroll
@@ -911,8 +1017,19 @@ __global__ void residual_requant_kernel(const uint4* __restrict__ a, bool a_sign
         out[j] = w;
       }
     }
-    y[i] = make_uint4(out[0], out[1], out[2], out[3]);
-  }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// 16 lanes per thread and iteration: two 16-byte loads, one 16-byte store.  Two vectors per iteration (four loads
+// in flight) were measured and are slower (4.46 against 4.65 TB/s on 822 MB operands): the grid already keeps
+// enough bytes in flight, and the longer body costs occupancy.
+template <int MODE>
+__global__ void residual_requant_kernel(const uint4* __restrict__ a, bool a_signed, const uint4* __restrict__ b, bool b_signed, uint4* __restrict__ y,
+                                        int64_t n16, ResidualParams rp) {
+  const float off_a = 8388608.0f + rp.a_zp + (a_signed ? 128.f : 0.f), off_b = 8388608.0f + rp.b_zp + (b_signed ? 128.f : 0.f);
+  const uint32_t flip_a = a_signed ? 0x80808080u : 0u, flip_b = b_signed ? 0x80808080u : 0u;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = residual_vec<MODE>(__ldcs(a + i), __ldcs(b + i), a_signed, b_signed, off_a, off_b, flip_a, flip_b, rp);
 }
 
 __global__ void residual_requant_tail_kernel(const uint8_t* a, bool a_signed, const uint8_t* b, bool b_signed, uint8_t* y, int64_t begin, int64_t n,
@@ -1340,8 +1457,9 @@ void residual_requant(const void* a, DT a_dt, const void* b, DT b_dt, void* y, D
   int64_t n16 = 0;
   if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) & 15) == 0) n16 = n / 16;
   if (n16 > 0) {
-    if (rp.proven_fast) residual_requant_kernel<true><<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
-    else residual_requant_kernel<false><<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
+    if (rp.proven_fast == 2) residual_requant_kernel<2><<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
+    else if (rp.proven_fast == 1) residual_requant_kernel<1><<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
+    else residual_requant_kernel<0><<<grid_for(n16), kThreads, 0, s>>>((const uint4*)a, as, (const uint4*)b, bs, (uint4*)y, n16, rp);
   }
   if (n16 * 16 < n)
     residual_requant_tail_kernel<<<grid_for(n - n16 * 16), kThreads, 0, s>>>((const uint8_t*)a, as, (const uint8_t*)b, bs, (uint8_t*)y, n16 * 16, n, rp);
@@ -1358,6 +1476,8 @@ void residual_requant_prepare(ResidualParams& rp, DT a_dt, DT b_dt) {
   const float y_rcp = (float)(1.0 / (double)rp.y_scale);
   const int a_lo = a_dt == DT::I8 ? -128 : 0, b_lo = b_dt == DT::I8 ? -128 : 0;
   const float magic = 12582912.0f;
+  const float lo_eff = rp.relu ? std::fmax(rp.lo, rp.y_zp) : rp.lo;
+  bool packed_ok = rp.y_scale > 0.f && std::fabs(rp.lo) <= 32000.f && std::fabs(rp.hi) <= 32000.f;
   for (int ia = a_lo; ia < a_lo + 256; ++ia) {
     volatile float va = ((float)ia - rp.a_zp) * rp.a_scale;
     for (int ib = b_lo; ib < b_lo + 256; ++ib) {
@@ -1376,10 +1496,22 @@ void residual_requant_prepare(ResidualParams& rp, DT a_dt, DT b_dt) {
       volatile float t = t1 + rp.y_zp;
       const float got = std::fmin(std::fmax(t, magic + rp.lo), magic + rp.hi) - magic;
       if (!(got == want)) return;
+      if (packed_ok) {
+        // the pairwise form: no ReLU on the sum, the same quotient, the low half-word of t clamped as an int16
+        volatile float sum2 = va + vb;
+        volatile float p0 = sum2 * y_rcp;
+        volatile float prem = std::fmaf(p0, -rp.y_scale, sum2);
+        volatile float pq = std::fmaf(prem, y_rcp, p0);
+        volatile float pt1 = pq + magic;
+        volatile float pt = pt1 + rp.y_zp;
+        const float ti = pt - magic;  // exact: pt is an integer of the binade when it is in range
+        if (!(pt >= 8388608.0f && pt < 16777216.0f) || std::fabs(ti) > 32000.f) packed_ok = false;
+        else if (!(std::fmin(std::fmax(ti, lo_eff), rp.hi) == want)) packed_ok = false;
+      }
     }
   }
   rp.y_rcp = y_rcp;
-  rp.proven_fast = 1;
+  rp.proven_fast = packed_ok ? 2 : 1;
 }
 
 void s2d_pack(const TensorRef& src, void* dst, DT dst_dt, int c_pad, int sub, cudaStream_t s) {
@@ -1511,6 +1643,13 @@ void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaS
   if (x.d.C % per == 0 && (((uintptr_t)x.ptr | (uintptr_t)y.ptr) & 15) == 0 && (x.dt == DT::F32 || x.dt == DT::U8 || x.dt == DT::I8)) {
     const int64_t cvec = x.d.C / per, tv = total / per;
     const int gv = grid_for(tv);
+    if (x.dt != DT::F32 && ps.kh == 3 && ps.kw == 3 && ps.sh == 2 && ps.sw == 2 && ps.dh == 1 && ps.dw == 1 && ps.pt == 1 && ps.pl == 1 && tv < 0x7fffffffLL &&
+        x.d.numel() / per < 0x7fffffffLL) {
+      // low-side clamping re-reads row / column 0, which the window contains: exact
+      if (x.dt == DT::U8) max_pool_3x3s2_q_kernel<false><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, (int)x.d.H, (int)x.d.W, ps.P, ps.Q, (int)cvec, (int)tv);
+      else max_pool_3x3s2_q_kernel<true><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, (int)x.d.H, (int)x.d.W, ps.P, ps.Q, (int)cvec, (int)tv);
+      return;
+    }
     if (x.dt == DT::F32) max_pool_nhwc_vec_kernel<0><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, ps, cvec, tv);
     else if (x.dt == DT::U8) max_pool_nhwc_vec_kernel<1><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, ps, cvec, tv);
     else max_pool_nhwc_vec_kernel<2><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, ps, cvec, tv);

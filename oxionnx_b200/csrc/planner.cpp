@@ -2904,7 +2904,8 @@ bool Planner::try_plan_residual_chain(const NodeDef& n, int ni) {
   Step& st = add_step(n, "residual_requant", 2, {ai, bi}, {yi});
   st.node_name = add.name;
   st.op_type = "DequantizeLinear+Add+Relu+QuantizeLinear";
-  st.kernel = rp.proven_fast ? "residual_requant (division-free, proven per parameter set)" : "residual_requant";
+  st.kernel = rp.proven_fast == 2 ? "residual_requant (division-free, packed pairs, proven per parameter set)"
+                                  : (rp.proven_fast ? "residual_requant (division-free, proven per parameter set)" : "residual_requant");
   st.work = 3.0 * (double)count;
   st.launch = [this, ai, bi, yi, adt, bdt, odt, count, rp](cudaStream_t s) {
     k::residual_requant(V(ai).ptr, adt, V(bi).ptr, bdt, V(yi).ptr, odt, count, rp, s);

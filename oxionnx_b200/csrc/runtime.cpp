@@ -116,6 +116,12 @@ void Context::free_temp_forms() {
   temp_forms_.clear();
 }
 
+uint64_t Context::cached_bytes() const {
+  uint64_t total = 0;
+  for (const auto& kv : forms_) total += kv.second.bytes;
+  return total;
+}
+
 void Context::release_caches() {
   for (auto& kv : forms_) cudaFree(kv.second.ptr);
   forms_.clear();

@@ -218,6 +218,9 @@ class Context {
   cudaStream_t stream() const { return stream_; }
   const oxb200_config& cfg() const { return cfg_; }
   void set_profile(int on) { cfg_.profile = on ? 1 : 0; }
+  void set_graph_capture(int on) { cfg_.cuda_graph = on ? 1 : 0; }
+  // device bytes held for reuse: packed weight forms (resident weights) of this context
+  uint64_t cached_bytes() const;
   void make_current();
 
   void register_weight(const std::string& name, const float* lanes, uint64_t len, const uint64_t* shape, uint32_t rank, DT declared = DT::F32);
@@ -252,6 +255,8 @@ class Context {
 
 // Device tensor handed across the ABI (CudaDeviceTensor).
 struct DeviceTensorHandle {
+  // handles that alias one allocation share this count; the last one released frees the memory
+  std::shared_ptr<int> owners = std::make_shared<int>(0);
   void* ptr = nullptr;
   size_t bytes = 0;
   DT dt = DT::F32;

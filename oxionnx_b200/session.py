@@ -104,6 +104,20 @@ class DeviceTensor:
         _raise_for(st, self._ctx.last_error())
         return buf[:n].reshape(shape).copy()
 
+    def alias(self, shape) -> Optional["DeviceTensor"]:
+        """CudaDeviceTensor::alias: the same allocation under another shape of the same element count, or None."""
+        arr = (ctypes.c_uint64 * max(len(shape), 1))(*[int(d) for d in shape])
+        out = ctypes.c_void_p()
+        st = _ffi.lib().oxb200_tensor_alias(self._ctx.handle, self.handle, arr, len(shape), ctypes.byref(out))
+        if st == _ffi.DECLINED:
+            return None
+        _raise_for(st, self._ctx.last_error())
+        return DeviceTensor(self._ctx, out)
+
+    @property
+    def reserved_bytes(self) -> int:
+        return int(_ffi.lib().oxb200_tensor_reserved_bytes(self.handle))
+
     def release(self):
         if self.handle:
             _ffi.lib().oxb200_tensor_release(self._ctx.handle, self.handle)
@@ -179,6 +193,18 @@ class CudaContext:
 
     def release_device_caches(self):
         _raise_for(_ffi.lib().oxb200_release_device_caches(self.handle), self.last_error())
+
+    def streams_unified(self) -> bool:
+        return bool(_ffi.lib().oxb200_streams_unified(self.handle))
+
+    def cached_device_bytes(self) -> int:
+        return int(_ffi.lib().oxb200_cached_device_bytes(self.handle))
+
+    def set_graph_capture(self, on: bool):
+        _ffi.lib().oxb200_set_graph_capture(self.handle, int(on))
+
+    def graph_capture_enabled(self) -> bool:
+        return bool(_ffi.lib().oxb200_graph_capture_enabled(self.handle))
 
     def probe_tensor_peak(self, kind: str) -> float:
         """Operations per second of the tensor pipe for "i8" | "tf32" | "f16" | "bf16", measured on this device."""

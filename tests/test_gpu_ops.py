@@ -513,6 +513,45 @@ def test_device_resident_chain_and_counters():
     ctx.close()
 
 
+def test_device_tensor_alias_reserved_bytes_and_context_queries():
+    """CudaDeviceTensor::alias / reserved_bytes and CudaContext::{streams_unified, cached_device_bytes,
+    set_graph_capture} (oxionnx-cuda src/activation.rs:116-163, src/context.rs:384-447)."""
+    ctx = S.CudaContext(0)
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((6, 32)).astype(np.float32)
+    w = (rng.standard_normal((32, 48)) * 0.1).astype(np.float32)
+    weights = {"w": w}
+    ctx.register_weights(weights)
+    assert ctx.streams_unified() and ctx.cached_device_bytes() == 0
+    y = S.try_cuda_dispatch_resident(Node("MatMul", "mm", ["a", "w"], ["y"], {}), weights, {"a": a}, "device", ctx)
+    assert isinstance(y, S.DeviceTensor) and y.shape == (6, 48) and y.reserved_bytes >= 6 * 48 * 4
+    assert ctx.cached_device_bytes() >= 32 * 48 * 4  # the packed weight stays resident
+    flat = y.alias((2, 144))
+    assert flat is not None and flat.shape == (2, 144)
+    assert y.alias((5, 5)) is None  # another element count: the reference's None
+    want = y.read_back()
+    y.release()  # the alias keeps the allocation alive
+    assert np.array_equal(flat.read_back(), want.reshape(2, 144))
+    # the alias is a usable operand
+    r = S.try_cuda_dispatch_resident(Node("Relu", "r", ["t"], ["z"], {}), {}, {"t": flat}, "host", ctx)[0]
+    assert np.array_equal(r, np.maximum(want, 0).reshape(2, 144))
+    flat.release()
+    # a channels-last rank-4 value does not alias into another order
+    x = rng.standard_normal((1, 32, 4, 4)).astype(np.float32)
+    wc = (rng.standard_normal((64, 32, 1, 1)) * 0.1).astype(np.float32)
+    h = S.try_cuda_dispatch_resident(Node("Conv", "c", ["x", "wc"], ["h"], {}), {"wc": wc}, {"x": x}, "device", ctx)
+    assert h.alias((1, 64 * 16)) is None and "channels-last" in ctx.last_error()
+    h.release()
+    assert not ctx.graph_capture_enabled()
+    ctx.set_graph_capture(True)
+    assert ctx.graph_capture_enabled()
+    ctx.set_graph_capture(False)
+    ctx.close()
+    verify = S.CudaContext(0, verify=True, cuda_graph=True)
+    assert not verify.graph_capture_enabled()  # never under shadow verification
+    verify.close()
+
+
 def test_shadow_verify_contract():
     """A 'wrong kernel' is simulated on the host by handing mismatching vectors to the
     comparator, as the reference's own shadow_verify tests do."""
