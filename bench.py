@@ -2,6 +2,7 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c2|c1|c3|c4] [--impl reference]
   python bench.py --layer "i8|f32 N C H W OC K STRIDE PAD"        (one contraction layer in isolation)
+  python bench.py --layer "dql ROWS COLS"                         (DynamicQuantizeLinear of a [ROWS, COLS] activation)
 
 A step is one pass of the hot path over one batch of seeded synthetic input.  The default
 workload is `c5`: the QLinearConv INT8 ResNet-50 at a GLOBAL batch of 1024 images split over the
@@ -56,7 +57,7 @@ WORKLOADS = {
     "c4": dict(name="bert_base_dynamic_int8_b64_s128", metric="tokens_per_s", unit="tokens/s", dtype="i8", batch=64, per_item=128),
 }
 # units the CPU baseline runs per sample (about 10-30 s of CPU work each)
-CPU_SAMPLE = {"c2": 4, "c5": 1, "c1": 64, "c3": 1, "c4": 1}
+CPU_SAMPLE = {"c2": 4, "c5": 8, "c1": 64, "c3": 1, "c4": 1}
 
 
 def measured_peaks():
@@ -240,6 +241,23 @@ def run_layer(spec, iters, pairs):
     from oxionnx_b200.graph import Graph, Node
     from oxionnx_b200.session import Session
     kind = spec[0]
+    if kind == "dql":  # "dql ROWS COLS": DynamicQuantizeLinear of a [ROWS, COLS] activation
+        rows, cols = int(spec[1]), int(spec[2])
+        nodes = [Node("Relu", "pre", ["x"], ["x1"], {}), Node("DynamicQuantizeLinear", "dq", ["x1"], ["y", "s", "z"], {})]
+        sess = Session.builder().with_profiling(True).build_from_graph(Graph(nodes=nodes, input_names=["x"], output_names=["s", "z"]), {})
+        sess.upload({"x": np.random.default_rng(0).standard_normal((rows, cols)).astype(np.float32)})
+        for _ in range(3):
+            sess.run_resident(1)
+        best = {}
+        for _ in range(iters):
+            sess.run_resident(1)
+            for s in sess.steps():
+                if s["node"] == "dq":
+                    best[s["kernel"]] = min(best.get(s["kernel"], 1e9), s["ms"])
+        for kname, ms in best.items():
+            print(f"{kname}: best {ms * 1000:.1f} us  {rows * cols * 4 / (ms / 1e3) / 1e12:.2f} TB/s of input")
+        sess.close()
+        return
     n, c, h, w, oc, k, stride, pad = [int(a) for a in spec[1:9]]
     rng = np.random.default_rng(0)
     if kind == "f32":

@@ -185,7 +185,7 @@ void layout_smem(KParams& kp, int bn, int kind, bool pair, size_t* smem_total) {
 size_t warp_row_bytes(int bn, int kind, size_t oes, bool one_run) {
   const int ew = epi_warps(kind);
   const int runs = bn / 32, wpq_all = ew / 4;
-  const int wpq = std::min(wpq_all, runs);
+  const int wpq = std::min(wpq_all, std::max(runs / 2, 1));  // EpiShape::WPQ
   const int cpw = one_run ? 1 : runs / wpq;
   return std::min<size_t>(128, (size_t)cpw * 32 * oes);
 }

@@ -26,8 +26,9 @@
 //    accumulator with tcgen05.ld (one output pixel per thread, 32 channels per load), apply the
 //    fused epilogue in registers and hand the tile to TMA stores through swizzled staging rows.
 //    A warp may only read the TMEM lanes 32 * (warp % 4) .. + 31, so the warps of a lane
-//    quarter split a tile's channel runs; when a tile has fewer runs than a quarter has warps
-//    (narrow tiles) the warps form groups and each group drains a tile of its own.
+//    quarter split a tile's channel runs, at least two runs per warp; when that leaves warps
+//    over (tiles narrower than 256 channels) the warps form groups, each group drains a tile of
+//    its own, and there are two accumulators per group (up to eight).
 //  * Epilogue variants, one tile loop instantiated per variant: float bias / ReLU / clip /
 //    SiLU / PRelu / TF32 rounding, optionally with a fused residual; exact ONNX requantisation
 //    in one fused multiply-add per output (and an f64 two-pass form for scales outside its
@@ -739,7 +740,10 @@ template <int BN, int EW>
 struct EpiShape {
   static constexpr int RUNS = BN / 32;                          // 32-channel runs of a tile
   static constexpr int WPQ_ALL = EW / 4;                        // warps per TMEM lane quarter
-  static constexpr int WPQ = WPQ_ALL < RUNS ? WPQ_ALL : RUNS;   // ... that share one tile
+  // ... that share one tile: every warp takes at least two runs of a tile that has them, so that the per-tile
+  // handshakes are paid once per two runs and a warp's staged rows (and its TMA store) are 64 bytes or more
+  static constexpr int HALF_RUNS = RUNS >= 2 ? RUNS / 2 : 1;
+  static constexpr int WPQ = WPQ_ALL < HALF_RUNS ? WPQ_ALL : HALF_RUNS;
   static constexpr int NG = WPQ_ALL / WPQ;                      // groups; tile number i of a CTA goes to group i % NG
   static constexpr int CPW = RUNS / WPQ;                        // runs per warp and tile
   static constexpr int NACC = 2 * NG;                           // accumulators: two per group
