@@ -85,15 +85,15 @@ def captured_traffic(key):
     None when no capture exists for the present kernel sources."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     if not os.path.exists(path):
-        return None, "no capture recorded"
+        return None, "no capture recorded", None
     with open(path) as fh:
         table = json.load(fh)
     rec = table.get(key)
     if not rec:
-        return None, "no capture recorded for this workload"
+        return None, "no capture recorded for this workload", None
     if rec.get("kernel_sha16") != kernel_source_sha():
-        return None, "the recorded capture is of other kernel sources (%s)" % rec.get("kernel_sha16")
-    return rec["dram_bytes_per_launch"], rec.get("note", "")
+        return None, "the recorded capture is of other kernel sources (%s)" % rec.get("kernel_sha16"), None
+    return rec["dram_bytes_per_launch"], rec.get("note", ""), rec.get("batch")
 
 
 def build_workload(key, batch, typed_input=False):
@@ -429,7 +429,12 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
     factor = {"tf32": 0.5, "i8": 2.0}[kind]
     peak = peaks["bf16_sustained"] * factor
     achieved = (conv_ops / (conv_ms / 1000.0) / 1e12) if conv_ms > 0 else 0.0
-    traffic, traffic_note = captured_traffic(key)
+    traffic, traffic_note, traffic_batch = captured_traffic(key)
+    if traffic is not None and traffic_batch and traffic_batch != batch:
+        # the capture was taken at another batch: activations dominate the traffic and grow with the batch, the
+        # weights (25.5 MB in 54 launches for the INT8 network) do not; scale by the units one launch processes
+        traffic = traffic * batch / traffic_batch
+        traffic_note += f" -- scaled by {batch}/{traffic_batch} to this run's per-GPU batch"
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s" if kind == "i8" else "TFLOP/s",
         "frac": achieved / peak if peak else None, "traffic": traffic, "traffic_note": traffic_note,
