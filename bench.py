@@ -330,6 +330,8 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
     # ... and the same K steps again with a CUDA-event pair around every kernel, for the roofline figures
     sess.ctx.set_profiling(True)
     prof_ms, conv_ms, conv_ops, conv_launches, glue_ms, glue_bytes = 0.0, 0.0, 0.0, 0, 0.0, 0.0
+    conv_algo_bytes = 0.0
+    conv_layers = []  # (ops, algorithmic bytes) of every contraction launch of one step: the layer-wise bound below
     slowest = {}
     for _ in range(args.steps):
         flush_l2()
@@ -341,6 +343,9 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
                 conv_ms += s["ms"]
                 conv_ops += s["work"]
                 conv_launches += 1
+                conv_algo_bytes += s["bytes"]
+                if _ == 0:
+                    conv_layers.append((s["work"], s["bytes"]))
             elif s["work_is_bytes"]:
                 glue_ms += s["ms"]
                 glue_bytes += s["work"]
@@ -435,7 +440,19 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
         # weights (25.5 MB in 54 launches for the INT8 network) do not; scale by the units one launch processes
         traffic = traffic * batch / traffic_batch
         traffic_note += f" -- scaled by {batch}/{traffic_batch} to this run's per-GPU batch"
+    # A network is a mix of layers, each with its own roofline: a layer cannot take less than the longer of its
+    # operations at the tensor peak and its algorithmic bytes (operands, weights and result once) at the measured
+    # copy bandwidth.  The sum of those per-layer floors against the measured contraction time says how far the
+    # kernel is from what this layer mix allows; `frac` above is the plain tensor-pipe fraction.
+    floor_ms = sum(max(ops / (peak * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)) for ops, nbytes in conv_layers) * 1000.0
+    conv_ms_per_step = conv_ms / max(args.steps, 1)
+    hbm_bound_layers = sum(1 for ops, nbytes in conv_layers if nbytes / (peaks["hbm_gbs"] * 1e9) > ops / (peak * 1e12))
     roofline = {
+        "layerwise": {"floor_ms_per_step": floor_ms, "measured_ms_per_step": conv_ms_per_step,
+                      "frac": floor_ms / conv_ms_per_step if conv_ms_per_step > 0 else None,
+                      "hbm_bound_layers": hbm_bound_layers, "layers": len(conv_layers),
+                      "algorithmic_bytes_per_launch": conv_algo_bytes / max(conv_launches, 1),
+                      "rule": "sum over the contraction launches of max(ops / tensor peak, algorithmic bytes / measured copy bandwidth)"},
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s" if kind == "i8" else "TFLOP/s",
         "frac": achieved / peak if peak else None, "traffic": traffic, "traffic_note": traffic_note,
         "kernel": "umma_conv_kernel (tcgen05 implicit GEMM)", "launches_per_step": conv_launches // max(args.steps, 1),

@@ -318,6 +318,7 @@ typedef struct {
   int32_t work_is_bytes;
   float last_ms;        /* CUDA-event time of the last profiled run (profile=1), else -1 */
   uint64_t launches;
+  double bytes;         /* algorithmic bytes per launch: every operand and result once, plus a contraction's packed weights */
 } oxb200_step_info;
 uint32_t oxb200_plan_step_count(const oxb200_ctx* ctx);
 int oxb200_plan_step_info(const oxb200_ctx* ctx, uint32_t index, oxb200_step_info* out);

@@ -63,7 +63,7 @@ class Counters(ctypes.Structure):
 
 class StepInfo(ctypes.Structure):
     _fields_ = [("node_name", ctypes.c_char_p), ("op_type", ctypes.c_char_p), ("kernel", ctypes.c_char_p), ("work", ctypes.c_double),
-                ("work_is_bytes", ctypes.c_int32), ("last_ms", ctypes.c_float), ("launches", ctypes.c_uint64)]
+                ("work_is_bytes", ctypes.c_int32), ("last_ms", ctypes.c_float), ("launches", ctypes.c_uint64), ("bytes", ctypes.c_double)]
 
 
 # every symbol include/oxb200.h declares: (restype, argtypes)

@@ -660,6 +660,7 @@ int oxb200_plan_step_info(const oxb200_ctx* ctx, uint32_t index, oxb200_step_inf
   out->work_is_bytes = s.work_is_bytes ? 1 : 0;
   out->last_ms = s.last_ms;
   out->launches = s.launches;
+  out->bytes = s.bytes;
   return OXB200_OK_HOST;
 }
 

@@ -608,8 +608,16 @@ void Planner::finalize_lifetimes_and_arena() {
   const int n_steps = (int)S.steps_.size();
   for (int si = 0; si < n_steps; ++si)
   {
-    for (int r : S.steps_[si].reads) V(r).last_use = std::max(V(r).last_use, si);
-    for (int w : S.steps_[si].writes) V(w).last_use = std::max(V(w).last_use, si);
+    Step& st = S.steps_[si];
+    st.bytes = st.param_bytes;
+    for (int r : st.reads) {
+      V(r).last_use = std::max(V(r).last_use, si);
+      st.bytes += (double)V(r).bytes;
+    }
+    for (int w : st.writes) {
+      V(w).last_use = std::max(V(w).last_use, si);
+      st.bytes += (double)V(w).bytes;
+    }
   }
   // aliases extend the life of the storage they share
   for (int i = (int)S.values_.size() - 1; i >= 0; --i) {
@@ -1073,6 +1081,7 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
     Step& st = add_step(n, "umma", 0, reads, {out_vi});
     st.work = c.algorithmic_ops > 0 ? c.algorithmic_ops : cs.ops();
     st.work_is_bytes = false;
+    st.param_bytes = (double)wbytes;
     const DT xdt = V(x_op_vi).dt, wdt = c.is_int ? c.w_dt : f_dt;
     Step* stp = &st;
     const int step_index = (int)S.steps_.size() - 1;

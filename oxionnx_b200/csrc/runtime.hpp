@@ -95,6 +95,9 @@ struct Step {
   int family = 2;  // 0 tcgen05, 1 direct CUDA-core, 2 glue
   double work = 0;
   bool work_is_bytes = true;
+  // algorithmic bytes of one launch: every value the step reads and writes once, plus `param_bytes` (a
+  // contraction's packed weights); filled when the plan is finalised
+  double param_bytes = 0, bytes = 0;
   std::vector<int> reads, writes;  // value indices
   std::function<void(cudaStream_t)> launch;
   std::function<void()> finalize;  // runs once after the arena is laid out (builds tensor maps)

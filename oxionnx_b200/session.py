@@ -594,7 +594,7 @@ class Session:
             s = _ffi.StepInfo()
             lib.oxb200_plan_step_info(self.ctx.handle, i, ctypes.byref(s))
             out.append(dict(node=s.node_name.decode(), op=s.op_type.decode(), kernel=s.kernel.decode(), work=float(s.work),
-                            work_is_bytes=bool(s.work_is_bytes), ms=float(s.last_ms), launches=int(s.launches)))
+                            work_is_bytes=bool(s.work_is_bytes), ms=float(s.last_ms), launches=int(s.launches), bytes=float(s.bytes)))
         return out
 
     def cuda_cache_counters(self) -> dict:
