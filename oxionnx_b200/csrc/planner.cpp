@@ -952,11 +952,13 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
   }
   // float contractions: TF32 operands unless the context asks for f16 / bf16 operands and the channel count fits
   // their 32-byte blocks (16 channels); accumulation is f32 either way
+  // A weight the model declares as FLOAT16 / BFLOAT16 (the declared type survives loading beside the f32 lanes)
+  // selects that kind for its contraction even without the context option: the graph's own tensors are 16-bit.
   int float_kind = 1;
-  if (want_umma && !c.is_int && (C.cfg().float_precision == 1 || C.cfg().float_precision == 2)) {
-    const int k16 = C.cfg().float_precision == 1 ? 2 : 3;
-    if (k::umma_channel_block(cs.C, k16) != 0) float_kind = k16;
-  }
+  int want16 = C.cfg().float_precision == 1 ? 2 : (C.cfg().float_precision == 2 ? 3 : 0);
+  if (want16 == 0 && w && w->declared == DT::F16) want16 = 2;
+  if (want16 == 0 && w && w->declared == DT::BF16) want16 = 3;
+  if (want_umma && !c.is_int && want16 != 0 && k::umma_channel_block(cs.C, want16) != 0) float_kind = want16;
   if (want_umma && k::umma_channel_block(cs.C, c.is_int ? 0 : float_kind) == 0) want_umma = false, why = "channel count not a multiple of the block";
   if (want_umma && cs.group != 1) want_umma = false, why = "grouped";
 

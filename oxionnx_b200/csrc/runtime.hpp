@@ -20,8 +20,9 @@ struct HostTensor {
   std::vector<float> data;
   std::vector<int64_t> shape;
   // Element type the tensor was declared with where it came from (an ONNX initializer, a typed operand); F32 is
-  // the reference's dtype-erased default.  Only the quantised operators' y_zero_point reads it, to resolve the
-  // saturation range exactly (SatRange::for_dtype, quant_ops/mod.rs:216-222).
+  // the reference's dtype-erased default.  The quantised operators' y_zero_point reads it to resolve the
+  // saturation range exactly (SatRange::for_dtype, quant_ops/mod.rs:216-222); a float contraction whose weight
+  // is declared FLOAT16 / BFLOAT16 runs with 16-bit operands.
   DT declared = DT::F32;
   int64_t numel() const { return prod(shape); }
 };

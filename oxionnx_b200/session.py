@@ -173,9 +173,10 @@ class CudaContext:
 
     def register_weights(self, weights: Dict[str, np.ndarray]):
         """Initializers as f32 lanes.  An array that arrives as uint8 / int8 keeps that declared type beside its
-        lanes (an ONNX initializer's data_type), which makes a quantised operator saturate exactly to it."""
+        lanes (an ONNX initializer's data_type), which makes a quantised operator saturate exactly to it; a float16
+        array is declared FLOAT16, which makes the contraction it feeds run with f16 operands."""
         for name, w in weights.items():
-            declared = _ffi.TYPED.get(np.asarray(w).dtype, _ffi.DT_F32)
+            declared = _ffi.TYPED.get(np.asarray(w).dtype, _ffi.DT_F16 if np.asarray(w).dtype == np.float16 else _ffi.DT_F32)
             a = np.ascontiguousarray(np.asarray(w, dtype=np.float32))
             shape = (ctypes.c_uint64 * max(a.ndim, 1))(*a.shape)
             st = _ffi.lib().oxb200_weight_register_typed(self.handle, name.encode(), a.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), a.size, shape,

@@ -236,3 +236,24 @@ def test_conv_followed_by_silu_or_prelu_runs_in_the_epilogue(kind, geom):
     steps = [st for st in sess.steps() if not st["kernel"].startswith(("convert_", "round_to_tf32"))]
     assert [st["op"] for st in steps] == ["Conv"], steps
     sess.close()
+
+
+def test_model_with_float16_weights_runs_on_the_f16_kind(tmp_path):
+    """A model whose convolution weights are FLOAT16 initializers: the declared type survives loading beside the
+    f32 lanes and selects 16-bit operands (f32 accumulation) for that contraction, without any context option."""
+    rng = np.random.default_rng(21)
+    c, oc = 64, 96
+    w16 = (rng.standard_normal((oc, c, 3, 3)) / np.sqrt(c * 9)).astype(np.float16)
+    weights = {"w": w16, "b": rng.standard_normal(oc).astype(np.float32)}
+    graph = Graph([N("Conv", "conv", ["x", "w", "b"], ["y"], pads=[1, 1, 1, 1], activation="relu")], ["x"], ["y"])
+    path = str(tmp_path / "half.onnx")
+    onnx_io.write_onnx(graph, weights, {"x": ((2, c, 12, 12), np.float32)}, path)
+    x = rng.standard_normal((2, c, 12, 12)).astype(np.float32)
+    want = oracle.run_node("Conv", [x, w16.astype(np.float32), weights["b"]], dict(pads=[1, 1, 1, 1], activation="relu"))[0]
+    sess = S.Session.from_file(path)
+    got = sess.run({"x": x})["y"]
+    kernels = [st["kernel"] for st in sess.steps()]
+    sess.close()
+    assert any(k.startswith("umma_f16") for k in kernels), kernels
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    assert np.all(np.abs(got.astype(np.float64) - want) <= 1e-2 * np.abs(want) + 1e-2 * rms)
