@@ -355,11 +355,8 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
     t_end = time.time()
     clocks = sampler.stop(t_begin, t_end) if sampler else None
     sess.ctx.set_profiling(False)
-    total_ms = sum(step_ms)
-    if dist is not None:
-        t = torch.tensor([total_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    from oxionnx_b200.shard import max_over_ranks
+    total_ms = max_over_ranks(sum(step_ms), world, device=f"cuda:{local_rank}")  # the slowest rank's device time
     per_item = w.get("per_item", 1)  # tokens per sequence for the encoder, 1 otherwise
     value = world * batch * per_item * args.steps / (total_ms / 1000.0)
 
@@ -384,10 +381,7 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
         torch.cuda.synchronize()
         elapsed = (time.perf_counter() - t0) * 1000.0
         barrier()
-        if dist is not None:
-            t = torch.tensor([elapsed], dtype=torch.float64, device=f"cuda:{local_rank}")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            elapsed = float(t.item())
+        elapsed = max_over_ranks(elapsed, world, device=f"cuda:{local_rank}")
         return elapsed, out
 
     e2e_total, out = pipelined(sess, pinned)

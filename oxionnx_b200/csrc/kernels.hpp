@@ -105,7 +105,8 @@ void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const floa
 // ---- spatial glue -----------------------------------------------------------------------
 // mode 0 nearest, 1 linear; coord 0 half_pixel, 1 pytorch_half_pixel, 2 asymmetric,
 // 3 align_corners; nearest_rule 0 round_prefer_floor, 1 floor, 2 ceil, 3 round_prefer_ceil
-void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, cudaStream_t s);
+// `round_tf32`: interpolated lanes (linear mode) are rounded to TF32 when they feed a contraction.
+void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, int round_tf32, cudaStream_t s);
 // mode 0 constant, 1 reflect, 2 edge (spatial and channel pads of a rank-4 view)
 void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, int pc, int ph, int pw, cudaStream_t s);
 // Copies `x` into the channel range [c_off, c_off + x.C) of `y` (Concat on the channel axis)

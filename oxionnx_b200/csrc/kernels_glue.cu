@@ -640,11 +640,10 @@ __global__ void max_pool_nhwc_vec_kernel(const uint4* __restrict__ x, uint4* __r
   }
 }
 
-// The 3x3 / stride 2 / pad 1 pool of the ResNet front end on 8-bit lanes: the nine loads of a window are issued
-// together (clamped coordinates; a tap outside the image contributes the identity of max), 32-bit index arithmetic.
-template <bool SIGNED>
-__global__ void max_pool_3x3s2_q_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int H, int W, int P, int Q, int cvec, int total) {
-  const uint32_t ident = SIGNED ? 0x80808080u : 0u;
+// The 3x3 / stride 2 / pad 1 pool of the ResNet front end, 16 bytes of channels per thread: the nine loads of a
+// window are issued together (clamped coordinates), 32-bit index arithmetic.  KIND 0 = f32, 1 = u8, 2 = i8.
+template <int KIND>
+__global__ void max_pool_3x3s2_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int H, int W, int P, int Q, int cvec, int total) {
   for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < total; o += gridDim.x * blockDim.x) {
     const int c = o % cvec;
     int t = o / cvec;
@@ -662,18 +661,30 @@ __global__ void max_pool_3x3s2_q_kernel(const uint4* __restrict__ x, uint4* __re
         v[3 * r + s] = __ldg(x + ((size_t)(n * H + ih) * W + iw) * cvec + c);
       }
     }
-    uint4 best = make_uint4(ident, ident, ident, ident);
+    uint4 best;
+    if (KIND == 0) best = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);  // -inf
+    else if (KIND == 1) best = make_uint4(0u, 0u, 0u, 0u);
+    else best = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
 #pragma unroll
     for (int r = 0; r < 3; ++r) {
 #pragma unroll
       for (int s = 0; s < 3; ++s) {
-        // a clamped coordinate re-reads a pixel of the window itself, which cannot change the maximum -- except
-        // that the window must not reach past the image on the far side (odd extents), where the tap is dropped
-        const bool inside = h0 + r < H && w0 + s < W;
+        // a coordinate clamped on the low side re-reads a pixel the window holds anyway, which cannot change the
+        // maximum; on the far side (odd extents) the tap lies outside the image and is dropped.  Taps are taken
+        // in the reference's (r, s) order, so a NaN lane behaves as there (it never replaces the maximum).
+        const bool inside = h0 + r < H && w0 + s < W && (h0 + r >= 0) && (w0 + s >= 0);
         const uint4 u = v[3 * r + s];
         if (inside) {
-          if (SIGNED) best = make_uint4(__vmaxs4(best.x, u.x), __vmaxs4(best.y, u.y), __vmaxs4(best.z, u.z), __vmaxs4(best.w, u.w));
-          else best = make_uint4(__vmaxu4(best.x, u.x), __vmaxu4(best.y, u.y), __vmaxu4(best.z, u.z), __vmaxu4(best.w, u.w));
+          if (KIND == 0) {
+            if (__uint_as_float(u.x) > __uint_as_float(best.x)) best.x = u.x;
+            if (__uint_as_float(u.y) > __uint_as_float(best.y)) best.y = u.y;
+            if (__uint_as_float(u.z) > __uint_as_float(best.z)) best.z = u.z;
+            if (__uint_as_float(u.w) > __uint_as_float(best.w)) best.w = u.w;
+          } else if (KIND == 1) {
+            best = make_uint4(__vmaxu4(best.x, u.x), __vmaxu4(best.y, u.y), __vmaxu4(best.z, u.z), __vmaxu4(best.w, u.w));
+          } else {
+            best = make_uint4(__vmaxs4(best.x, u.x), __vmaxs4(best.y, u.y), __vmaxs4(best.z, u.z), __vmaxs4(best.w, u.w));
+          }
         }
       }
     }
@@ -775,7 +786,7 @@ __device__ __forceinline__ int64_t nearest_index(int rule, float s, int64_t in_s
 }
 
 __global__ void resize_nhwc_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 xd, Dims4 yd, int mode, int coord, int rule,
-                                   float sh, float sw, int64_t total) {
+                                   float sh, float sw, int64_t total, int rtf32) {
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
     int64_t c = o % yd.C;
     int64_t t = o / yd.C;
@@ -796,14 +807,15 @@ __global__ void resize_nhwc_kernel(const float* __restrict__ x, float* __restric
       float v10 = base[(y1 * xd.W + x0) * xd.C], v11 = base[(y1 * xd.W + x1) * xd.C];
       float top = __fadd_rn(__fmul_rn(v00, __fsub_rn(1.f, fx)), __fmul_rn(v01, fx));
       float bot = __fadd_rn(__fmul_rn(v10, __fsub_rn(1.f, fx)), __fmul_rn(v11, fx));
-      y[o] = __fadd_rn(__fmul_rn(top, __fsub_rn(1.f, fy)), __fmul_rn(bot, fy));
+      const float r = __fadd_rn(__fmul_rn(top, __fsub_rn(1.f, fy)), __fmul_rn(bot, fy));
+      y[o] = rtf32 ? round_tf32(r) : r;
     }
   }
 }
 
 // Four channels per thread (NHWC f32, C % 4 == 0): the same arithmetic per lane as the scalar kernel.
 __global__ void resize_nhwc_vec4_kernel(const float4* __restrict__ x, float4* __restrict__ y, Dims4 xd, Dims4 yd, int mode, int coord, int rule,
-                                        float sh, float sw, int64_t total4) {
+                                        float sh, float sw, int64_t total4, int rtf32) {
   const int64_t c4n = yd.C / 4;
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total4; o += (int64_t)gridDim.x * blockDim.x) {
     const int64_t c4 = o % c4n;
@@ -833,6 +845,7 @@ __global__ void resize_nhwc_vec4_kernel(const float4* __restrict__ x, float4* __
   }
       OXB_LERP(x) OXB_LERP(y) OXB_LERP(z) OXB_LERP(w)
 #undef OXB_LERP
+      if (rtf32) r = make_float4(round_tf32(r.x), round_tf32(r.y), round_tf32(r.z), round_tf32(r.w));  // the lanes feed a TF32 product
       y[o] = r;
     }
   }
@@ -1643,11 +1656,12 @@ void max_pool(const TensorRef& x, const TensorRef& y, const PoolShape& ps, cudaS
   if (x.d.C % per == 0 && (((uintptr_t)x.ptr | (uintptr_t)y.ptr) & 15) == 0 && (x.dt == DT::F32 || x.dt == DT::U8 || x.dt == DT::I8)) {
     const int64_t cvec = x.d.C / per, tv = total / per;
     const int gv = grid_for(tv);
-    if (x.dt != DT::F32 && ps.kh == 3 && ps.kw == 3 && ps.sh == 2 && ps.sw == 2 && ps.dh == 1 && ps.dw == 1 && ps.pt == 1 && ps.pl == 1 && tv < 0x7fffffffLL &&
+    if (ps.kh == 3 && ps.kw == 3 && ps.sh == 2 && ps.sw == 2 && ps.dh == 1 && ps.dw == 1 && ps.pt == 1 && ps.pl == 1 && tv < 0x7fffffffLL &&
         x.d.numel() / per < 0x7fffffffLL) {
-      // low-side clamping re-reads row / column 0, which the window contains: exact
-      if (x.dt == DT::U8) max_pool_3x3s2_q_kernel<false><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, (int)x.d.H, (int)x.d.W, ps.P, ps.Q, (int)cvec, (int)tv);
-      else max_pool_3x3s2_q_kernel<true><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, (int)x.d.H, (int)x.d.W, ps.P, ps.Q, (int)cvec, (int)tv);
+      const int H = (int)x.d.H, W = (int)x.d.W, cv = (int)cvec, n = (int)tv;
+      if (x.dt == DT::F32) max_pool_3x3s2_kernel<0><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, H, W, ps.P, ps.Q, cv, n);
+      else if (x.dt == DT::U8) max_pool_3x3s2_kernel<1><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, H, W, ps.P, ps.Q, cv, n);
+      else max_pool_3x3s2_kernel<2><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, H, W, ps.P, ps.Q, cv, n);
       return;
     }
     if (x.dt == DT::F32) max_pool_nhwc_vec_kernel<0><<<gv, kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, ps, cvec, tv);
@@ -1684,16 +1698,17 @@ void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const floa
   instance_norm_nhwc_kernel<<<(unsigned)blocks, 256, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, eps, scale_nc, shift_nc, relu, round_tf32_flag);
 }
 
-void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, cudaStream_t s) {
+void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nearest_rule, float scale_h, float scale_w, int round_tf32_flag,
+            cudaStream_t s) {
   int64_t total = y.d.numel();
   if (total == 0) return;
   if (y.d.C % 4 == 0 && ((uintptr_t)x.ptr & 15) == 0 && ((uintptr_t)y.ptr & 15) == 0) {
     resize_nhwc_vec4_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((const float4*)x.ptr, (float4*)y.ptr, x.d, y.d, mode, coord, nearest_rule, scale_h,
-                                                                    scale_w, total / 4);
+                                                                    scale_w, total / 4, round_tf32_flag);
     return;
   }
   resize_nhwc_kernel<<<grid_for(total), kThreads, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, y.d, mode, coord, nearest_rule, scale_h,
-                                                          scale_w, total);
+                                                          scale_w, total, round_tf32_flag);
 }
 
 void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, int pc, int ph, int pw, cudaStream_t s) {

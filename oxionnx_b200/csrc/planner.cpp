@@ -409,7 +409,8 @@ class Planner {
     if (tf32_rounded_names_.count(V(vi).name)) return true;
     if (V(vi).is_graph_input || V(vi).producer < 0 || depth > 12) return false;
     const Step& ps = S.steps_[V(vi).producer];
-    static const char* movers[] = {"convert_layout", "max_pool", "pad", "slice", "concat", "transpose_perm", "transpose_a", "s2d_pack", "window_pack"};
+    static const char* movers[] = {"convert_layout", "max_pool", "pad", "slice", "concat", "transpose_perm", "transpose_a", "s2d_pack", "window_pack",
+                                   "resize_nearest"};
     bool mover = false;
     for (const char* m : movers) mover = mover || ps.kernel.rfind(m, 0) == 0;
     if (!mover || ps.reads.empty()) return false;
@@ -2312,10 +2313,12 @@ void Planner::plan_resize(const NodeDef& n) {
   TensorRef xr = ref_of(xi), yr = ref_of(yi);
   xr.layout = yr.layout = Layout::NHWC;
   float shh = sc[2], sww = sc[3];
-  Step& st = add_step(n, "resize", 2, {xi}, {yi});
+  // nearest-neighbour resizing only selects lanes: a TF32-rounded input stays rounded (tf32_ready looks for the name)
+  Step& st = add_step(n, m == 0 ? "resize_nearest" : "resize", 2, {xi}, {yi});
   st.work = (double)xv.bytes + (double)V(yi).bytes;
-  st.launch = [this, xr, yr, xi, yi, m, cm, nr, shh, sww](cudaStream_t s) {
-    k::resize(bound(xr, xi), bound(yr, yi), m, cm, nr, shh, sww, s);
+  const int rt = (m == 1 && feeds_contraction(n.outputs[0])) ? 1 : 0;  // interpolated lanes are new values: round them here
+  st.launch = [this, xr, yr, xi, yi, m, cm, nr, shh, sww, rt](cudaStream_t s) {
+    k::resize(bound(xr, xi), bound(yr, yi), m, cm, nr, shh, sww, rt, s);
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };
