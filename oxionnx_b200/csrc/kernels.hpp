@@ -142,7 +142,11 @@ struct S2dQuant {
   int quantize = 0;
   float scale = 1.f, zp = 0.f, lo = 0.f, hi = 255.f;
 };
-void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, int wp, int sub, const S2dQuant& q, cudaStream_t s);
+// `pair_top` >= 0 selects the row-pair form for 8-bit destinations: dst is [N][rows_phys][wp][32], physical row j
+// holding the packed blocks of image rows j - pair_top and j - pair_top + 1 (zeros outside the image), so that a
+// window of S2p pixels is 128 contiguous bytes covering two filter rows.
+void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, int wp, int sub, const S2dQuant& q, int pair_top, int rows_phys,
+                     cudaStream_t s);
 // The row-window layout for a stride-1 convolution over up to four f32 channels: [N][H][wp][4].
 void window_pack_f32(const TensorRef& src, void* dst, int pad_left, int wp, cudaStream_t s);
 

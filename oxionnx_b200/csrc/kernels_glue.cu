@@ -1095,21 +1095,34 @@ __global__ void s2d_pack_kernel(const void* src, DT sdt, Layout sl, Dims4 d, voi
 }
 
 // One packed pixel (16 lanes) per thread.
+// Row pairs (8-bit destinations, `pair_top` >= 0): the destination is [N][rows_phys][wp][32] -- physical row j holds
+// the packed block of image row j - pair_top in lanes 0..15 and that of image row j - pair_top + 1 in lanes 16..31
+// (zeros where there is no such row: the vertical padding is physical) -- so that one window of S2p pixels covers two
+// filter rows in 128 contiguous bytes.  A thread makes the block of one (row, pixel) and stores it in both places;
+// the row index runs over rows_phys + 1 values so that every half of every physical row is written exactly once.
+__device__ __forceinline__ void s2d_store_pair(void* dst, uint4 block, int64_t n, int64_t jp, int64_t xw, int rows_phys, int wp) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  if (jp < rows_phys) d4[((n * rows_phys + jp) * wp + xw) * 2] = block;
+  if (jp >= 1) d4[((n * rows_phys + jp - 1) * wp + xw) * 2 + 1] = block;
+}
+
 __global__ void s2d_window_pack_kernel(const void* src, DT sdt, Layout sl, Dims4 d, void* dst, DT ddt, int pad_left, int wp, int sub, S2dQuant q,
-                                       int64_t total) {
+                                       int64_t total, int pair_top, int rows_phys) {
   const int64_t H2 = d.H / 2, W2 = d.W / 2;
   const int c4 = 4 * (int)d.C;
+  const int64_t rows = pair_top >= 0 ? rows_phys + 1 : H2;
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
     const int64_t xw = o % wp;
     int64_t t = o / wp;
-    const int64_t y = t % H2;
-    const int64_t n = t / H2;
+    const int64_t jp = t % rows;
+    const int64_t y = pair_top >= 0 ? jp - pair_top : jp;
+    const int64_t n = t / rows;
     const int64_t x2 = xw - pad_left;
     float v[16];
 #pragma unroll
     for (int cp = 0; cp < 16; ++cp) {
       v[cp] = 0.f;
-      if (cp < c4 && x2 >= 0 && x2 < W2) {
+      if (cp < c4 && x2 >= 0 && x2 < W2 && y >= 0 && y < H2) {
         const int blk = cp / (int)d.C;
         Coord qd;
         qd.n = n;
@@ -1133,7 +1146,8 @@ __global__ void s2d_window_pack_kernel(const void* src, DT sdt, Layout sl, Dims4
 #pragma unroll
         for (int e = 0; e < 4; ++e) w[j] |= ((uint32_t)__float2int_rn(fminf(fmaxf(v[4 * j + e], lo), hi)) & 0xffu) << (8 * e);
       }
-      ((uint4*)dst)[o] = make_uint4(w[0], w[1], w[2], w[3]);
+      if (pair_top >= 0) s2d_store_pair(dst, make_uint4(w[0], w[1], w[2], w[3]), n, jp, xw, rows_phys, wp);
+      else ((uint4*)dst)[o] = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -1159,18 +1173,20 @@ __device__ __forceinline__ float quotient_rint(float x, float s, float r, bool s
 // a 2x2 block come from one 8-byte load, and consecutive threads read consecutive blocks (fully coalesced).
 template <int C>
 __global__ void s2d_window_pack_nchw_f32_kernel(const float* __restrict__ src, Dims4 d, void* dst, DT ddt, int pad_left, int wp, int sub, S2dQuant q,
-                                                float rcp, bool safe, int64_t total) {
+                                                float rcp, bool safe, int64_t total, int pair_top, int rows_phys) {
   const int64_t H2 = d.H / 2, W2 = d.W / 2;
+  const int64_t rows = pair_top >= 0 ? rows_phys + 1 : H2;
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
     const int64_t xw = o % wp;
     int64_t t = o / wp;
-    const int64_t y = t % H2;
-    const int64_t n = t / H2;
+    const int64_t jp = t % rows;
+    const int64_t y = pair_top >= 0 ? jp - pair_top : jp;
+    const int64_t n = t / rows;
     const int64_t x2 = xw - pad_left;
     float v[16];
 #pragma unroll
     for (int cp = 0; cp < 16; ++cp) v[cp] = 0.f;
-    if (x2 >= 0 && x2 < W2) {
+    if (x2 >= 0 && x2 < W2 && y >= 0 && y < H2) {
 #pragma unroll
       for (int c = 0; c < C; ++c) {
         const float* plane = src + ((n * C + c) * d.H + 2 * y) * d.W + 2 * x2;
@@ -1201,7 +1217,8 @@ __global__ void s2d_window_pack_nchw_f32_kernel(const float* __restrict__ src, D
         for (int e = 0; e < 4; ++e)
           w[j] |= (__float_as_uint(__fadd_rn(fminf(fmaxf(v[4 * j + e], lo), hi), 12582912.0f)) & 0xffu) << (8 * e);
       }
-      ((uint4*)dst)[o] = make_uint4(w[0], w[1], w[2], w[3]);
+      if (pair_top >= 0) s2d_store_pair(dst, make_uint4(w[0], w[1], w[2], w[3]), n, jp, xw, rows_phys, wp);
+      else ((uint4*)dst)[o] = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -1534,10 +1551,12 @@ void s2d_pack(const TensorRef& src, void* dst, DT dst_dt, int c_pad, int sub, cu
   s2d_pack_kernel<<<grid_for(total4), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, c_pad, sub, total4);
 }
 
-void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, int wp, int sub, const S2dQuant& q, cudaStream_t s) {
-  const int64_t total = src.d.N * (src.d.H / 2) * wp;
+void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, int wp, int sub, const S2dQuant& q, int pair_top, int rows_phys,
+                     cudaStream_t s) {
+  const int64_t total = src.d.N * (pair_top >= 0 ? (int64_t)rows_phys + 1 : src.d.H / 2) * wp;
   if (total == 0) return;
   if (!(dst_dt == DT::F32 || dst_dt == DT::U8 || dst_dt == DT::I8) || 4 * src.d.C > 16) OXB_FAIL("s2d_window_pack: unsupported operand");
+  if (pair_top >= 0 && dst_dt == DT::F32) OXB_FAIL("s2d_window_pack: row pairs are an 8-bit layout");
   if (q.quantize && src.dt != DT::F32) OXB_FAIL("s2d_window_pack: quantisation needs an f32 source");
   if (src.dt == DT::F32 && src.layout == Layout::PLAIN && src.d.W % 2 == 0 && ((uintptr_t)src.ptr & 7) == 0 && src.d.C >= 1 && src.d.C <= 4) {
     const bool safe = q.quantize && q.scale >= 7.8886090522101181e-31f && q.scale <= 1.2676506002282294e+30f;
@@ -1545,14 +1564,14 @@ void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, i
     const int g = grid_for(total);
     const float* x = (const float*)src.ptr;
     switch ((int)src.d.C) {
-      case 1: s2d_window_pack_nchw_f32_kernel<1><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
-      case 2: s2d_window_pack_nchw_f32_kernel<2><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
-      case 3: s2d_window_pack_nchw_f32_kernel<3><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
-      default: s2d_window_pack_nchw_f32_kernel<4><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total); break;
+      case 1: s2d_window_pack_nchw_f32_kernel<1><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total, pair_top, rows_phys); break;
+      case 2: s2d_window_pack_nchw_f32_kernel<2><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total, pair_top, rows_phys); break;
+      case 3: s2d_window_pack_nchw_f32_kernel<3><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total, pair_top, rows_phys); break;
+      default: s2d_window_pack_nchw_f32_kernel<4><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total, pair_top, rows_phys); break;
     }
     return;
   }
-  s2d_window_pack_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, pad_left, wp, sub, q, total);
+  s2d_window_pack_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, pad_left, wp, sub, q, total, pair_top, rows_phys);
 }
 
 void window_pack_f32(const TensorRef& src, void* dst, int pad_left, int wp, cudaStream_t s) {

@@ -1236,13 +1236,20 @@ bool Planner::try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi) {
     // one filter-row tap = S2p neighbouring pixels = S2p * 16 contiguous lanes.  The convolution
     // the kernel sees has R2 taps of S2p * 16 "channels" each (positions overlap, 16 lanes apart).
     const int S2p = S2 <= 2 ? 2 : (S2 <= 4 ? 4 : 8);
-    const int CP = 16, Cw = S2p * CP;
+    // Row pairs (8-bit stems with an even number of packed filter rows): a packed pixel carries the blocks of two
+    // vertically adjacent rows, 32 lanes, so that one window of S2p pixels is 128 contiguous bytes covering two
+    // filter rows -- half as many, twice as long rows for the TMA unit, whose cost is per row.  The vertical
+    // padding becomes physical (rows of zeros written by the packing kernel) and the taps step two rows.
+    const bool pairs = c.is_int && (R2 % 2 == 0) && S2p * 32 <= 128;
+    const int CP = pairs ? 32 : 16, Cw = S2p * CP;
+    const int RT = pairs ? R2 / 2 : R2;              // taps the kernel sees
+    const int rows_phys = pairs ? cs.P - 2 + R2 : H2;  // stored rows per image
     const int wp = pl2 + W2 + pr2 + (S2p - S2);
     const HostTensor* w = c.w;
     made_consts_.emplace_back();
     HostTensor& w2 = made_consts_.back();
-    w2.shape = {cs.OC, Cw, R2, 1};
-    w2.data.assign((size_t)cs.OC * Cw * R2, 0.f);
+    w2.shape = {cs.OC, Cw, RT, 1};
+    w2.data.assign((size_t)cs.OC * Cw * RT, 0.f);
     for (int oc = 0; oc < cs.OC; ++oc)
       for (int bh = 0; bh < 2; ++bh)
         for (int bw = 0; bw < 2; ++bw)
@@ -1251,8 +1258,9 @@ bool Planner::try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi) {
               for (int b = 0; b < S2; ++b) {
                 const int r = 2 * a + bh - eh, s = 2 * b + bw - ew;
                 if (r < 0 || r >= cs.R || s < 0 || s >= cs.S) continue;
-                const int lane = b * CP + (bh * 2 + bw) * cs.C + ch;
-                w2.data[((size_t)oc * Cw + lane) * R2 + a] = w->data[(((size_t)oc * cs.C + ch) * cs.R + r) * cs.S + s];
+                const int lane = b * CP + (pairs ? (a % 2) * 16 : 0) + (bh * 2 + bw) * cs.C + ch;
+                const int tap = pairs ? a / 2 : a;
+                w2.data[((size_t)oc * Cw + lane) * RT + tap] = w->data[(((size_t)oc * cs.C + ch) * cs.R + r) * cs.S + s];
               }
     // quantise on the way when the activation is the sole product of the QuantizeLinear just planned
     k::S2dQuant q;
@@ -1269,15 +1277,16 @@ bool Planner::try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi) {
       }
     }
     const Value rv = V(read_vi);
-    std::vector<int64_t> pshape = {cs.N, CP, H2, wp};
+    std::vector<int64_t> pshape = {cs.N, CP, rows_phys, wp};
     int pv = add_value(xv.name + "@s2dw", pshape, pdt, Layout::NHWC);
     k::TensorRef src{nullptr, rv.dt, effective_layout(rv), dims_of(rv)};
     if (order_free(rv)) src.layout = Layout::NHWC;
     Step& st = add_step(n, q.quantize ? "quantize+s2d_window_pack" : "s2d_window_pack", 2, {read_vi}, {pv});
     st.work = (double)rv.bytes + (double)V(pv).bytes;
     const DT pdt_c = pdt;
-    st.launch = [this, src, read_vi, pv, pdt_c, pl2, wp, sub, q](cudaStream_t s) {
-      k::s2d_window_pack(bound(src, read_vi), V(pv).ptr, pdt_c, pl2, wp, sub, q, s);
+    const int pair_top = pairs ? pt2 : -1;
+    st.launch = [this, src, read_vi, pv, pdt_c, pl2, wp, sub, q, pair_top, rows_phys](cudaStream_t s) {
+      k::s2d_window_pack(bound(src, read_vi), V(pv).ptr, pdt_c, pl2, wp, sub, q, pair_top, rows_phys, s);
       C.counters.glue_launches++;
       C.counters.kernel_launches++;
     };
@@ -1289,13 +1298,14 @@ bool Planner::try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi) {
     c.x_plain_nchw = false;
     c.x_zp = 0;
     cs.C = Cw;
-    cs.H = H2;
+    cs.H = rows_phys;
     cs.W = cs.Q;  // window start positions per row
-    cs.R = R2;
+    cs.R = RT;
     cs.S = 1;
     cs.sh = cs.sw = 1;
-    cs.pt = pt2;
-    cs.pb = pb2;
+    cs.dh = pairs ? 2 : 1;
+    cs.pt = pairs ? 0 : pt2;
+    cs.pb = pairs ? 0 : pb2;
     cs.pl = cs.pr = 0;
     cs.x_pixel_stride = CP;
     cs.x_row_pixels = wp;
