@@ -166,19 +166,21 @@ int umma_channel_block(int C, int kind) {
 namespace {
 
 // Ring depth and the shared-memory layout [ring | epilogue staging rows] of a plan.
+// Layout: [resident weights, when kp.b_resident_bytes > 0 | ring | staging rows].
 void layout_smem(KParams& kp, int bn, int kind, bool pair, size_t* smem_total) {
   const int ew = epi_warps(kind);
-  const size_t kb_bytes = (size_t)(BLOCK_M + (pair ? bn / 2 : bn)) * kp.swizzle_bytes;
+  const size_t resident = kp.b_resident_bytes;
+  const size_t kb_bytes = (size_t)(BLOCK_M + (resident ? 0 : (pair ? bn / 2 : bn))) * kp.swizzle_bytes;
   const size_t stage_bytes = kb_bytes * kp.kpb;
   const size_t staging = kp.out_tma ? (size_t)ew * 32 * kp.out_row_bytes : 0;
   // one persistent CTA per SM: the ring may use most of the shared memory and runs on across tiles
-  const size_t budget = std::min<size_t>(192 * 1024, kSmemBudget - staging);
+  const size_t budget = std::min<size_t>(192 * 1024, kSmemBudget - staging) - resident;
   int stages = (int)(budget / stage_bytes);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) stages = 2;
   kp.stages = stages;
-  kp.stage_off = (uint32_t)(stages * stage_bytes);
-  *smem_total = (size_t)stages * stage_bytes + staging + 1024;
+  kp.stage_off = (uint32_t)(resident + stages * stage_bytes);
+  *smem_total = resident + (size_t)stages * stage_bytes + staging + 1024;
 }
 
 // Bytes of an output row one epilogue warp stages per TMA store: its share of the row, at most 128.
@@ -386,7 +388,14 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.idesc = make_idesc(kind, x_dt == DT::I8, w_dt == DT::I8, bn, pair ? 2 * BLOCK_M : BLOCK_M);
   // K blocks per stage: up to four small ones share a barrier round trip, as long as a stage stays
   // within 64 KB (the ring then still has three stages)
-  const size_t kb_bytes = (size_t)(BLOCK_M + (pair ? bn / 2 : bn)) * swz;
+  // A layer with one channel tile whose packed weights fit beside the ring keeps them in shared memory for the
+  // life of the CTA: every tile after a CTA's first then fetches activation rows only.
+  {
+    const size_t b_total = (size_t)k_iters_host * bn * swz;
+    // Measured (i8, M=802816): 3x3 64->64 125.1 us against 137.6 us, 1x1 256->64 53.6 against 55.6, 1x1 256->128 215.4 against 221.6.
+    if (!pair && splits == 1 && n_tiles == 1 && b_total <= 48 * 1024 && m_tiles >= 2 * sms) kp.b_resident_bytes = (uint32_t)b_total;
+  }
+  const size_t kb_bytes = (size_t)(BLOCK_M + (kp.b_resident_bytes ? 0 : (pair ? bn / 2 : bn))) * swz;
   int kpb = 1;
   while (kpb < 4 && (size_t)(kpb * 2) * kb_bytes <= 64 * 1024 && kpb * 2 <= k_iters_host) kpb *= 2;
   kp.kpb = kpb;

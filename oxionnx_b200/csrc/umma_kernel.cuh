@@ -91,6 +91,9 @@ struct alignas(64) KParams {
   unsigned int* ws_count;
   uint32_t idesc;
   uint32_t stage_off;  // byte offset of the epilogue staging rows inside the dynamic shared memory (after the ring)
+  // > 0: the layer has one channel tile and its whole packed weight matrix (this many bytes) stays in shared memory
+  // in front of the ring for the life of the CTA; ring stages then hold activation blocks only
+  uint32_t b_resident_bytes;
   // epilogue
   int mode;
   int variant;  // which epilogue_math instantiation runs
@@ -930,6 +933,7 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
   __shared__ __align__(8) uint64_t bar_empty[MAX_STAGES];
   __shared__ __align__(8) uint64_t bar_acc_full[MAX_ACC];
   __shared__ __align__(8) uint64_t bar_acc_empty[MAX_ACC];
+  __shared__ __align__(8) uint64_t bar_b_resident;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -938,9 +942,11 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
   // rows of B a CTA stages per K block: the whole channel tile, or its own half of the pair's
   constexpr int B_ROWS = PAIR ? BN / 2 : BN;
   const uint32_t a_bytes = (uint32_t)BLOCK_M * swz, b_bytes = (uint32_t)B_ROWS * swz;
-  const uint32_t kb_bytes = a_bytes + b_bytes;           // one K block: activations, then weights
-  const uint32_t stage_bytes = kb_bytes * (uint32_t)p.kpb;  // one ring stage
-  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const bool b_res = !PAIR && p.b_resident_bytes != 0;
+  const uint32_t kb_bytes = b_res ? a_bytes : a_bytes + b_bytes;  // one K block of the ring: activations, then weights
+  const uint32_t stage_bytes = kb_bytes * (uint32_t)p.kpb;        // one ring stage
+  const uint32_t b_res_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // resident weights (when used), then the ring
+  const uint32_t tiles_base = b_res_base + (b_res ? p.b_resident_bytes : 0u);
   const int k_iters = p.taps * p.cblocks;
   const int total_tiles = p.m_tiles * p.n_tiles * (p.batched ? p.items : p.splits);
   const int pair_rank = PAIR ? (int)cluster_ctarank() : 0;
@@ -955,6 +961,7 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
       mbar_init(smem_u32(&bar_full[i]), 1);
       mbar_init(smem_u32(&bar_empty[i]), 1);
     }
+    mbar_init(smem_u32(&bar_b_resident), 1);
     for (int i = 0; i < ES::NACC; ++i) {
       mbar_init(smem_u32(&bar_acc_full[i]), 1);
       // one arrival per epilogue warp of the group that drains it (of both CTAs for a pair)
@@ -991,6 +998,12 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
     bool ok = true;
     // a pair's copies are counted on the even CTA's barrier, which alone announces the bytes of both
     const uint32_t tx_per_kb = PAIR ? 2u * kb_bytes : kb_bytes;
+    if (b_res && tile0 < total_tiles && lane == 0) {
+      // the whole weight matrix of the (only) channel tile, once: K block i at b_res_base + i * b_bytes
+      mbar_expect_tx(smem_u32(&bar_b_resident), p.b_resident_bytes);
+      for (int i = 0; i < k_iters; ++i) tma_load_2d(b_res_base + (uint32_t)i * b_bytes, &p.tmB, smem_u32(&bar_b_resident), i * p.cb_elems, 0);
+    }
+    __syncwarp();
     const bool plain = !p.batched && p.splits == 1;
     TileWalk walk(tile0, tile_step, p.n_tiles);
     for (int t = tile0; t < total_tiles && ok; t += tile_step, walk.next()) {
@@ -1049,7 +1062,7 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
             } else {
               if (p.a_im2col) tma_load_im2col_4d(a_dst, &p.tmA, full, c_off, w_base, h_base, n0, (uint16_t)(sx * p.dw), (uint16_t)(r * p.dh));
               else tma_load_2d(a_dst, &p.tmA, full, a_col0 + c_off, a_row0 + m0);
-              tma_load_2d(a_dst + a_bytes, &p.tmB, full, b_col0 + (it + g) * p.cb_elems, b_row0 + oc0);
+              if (!b_res) tma_load_2d(a_dst + a_bytes, &p.tmB, full, b_col0 + (it + g) * p.cb_elems, b_row0 + oc0);
             }
           }
           if (++cb == p.cblocks) {
@@ -1088,6 +1101,18 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
       uint32_t stage = 0, phase = 0, a16 = ring16;
       uint32_t local = 0;
       bool ok = true;
+      const uint32_t bres16 = b_res_base >> 4, b16_bytes = b_bytes >> 4;
+      if (b_res && tile0 < total_tiles) {  // the resident weights have landed
+        const bool got = mbar_wait(smem_u32(&bar_b_resident), 0u, abortp);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0 && !*abortp) {
+            *abortp = 1;
+            atomicExch(p.err_flag, 5);
+          }
+          ok = false;
+        }
+        tc_fence_after();
+      }
       for (int t = tile0; t < total_tiles && ok; t += tile_step, ++local) {
         const uint32_t buf = local % (uint32_t)ES::NACC;
         const uint32_t acc_phase = (local / (uint32_t)ES::NACC) & 1u;
@@ -1122,8 +1147,10 @@ __global__ void __launch_bounds__(64 + 32 * epi_warps(KIND), 1) umma_conv_kernel
             // descriptors differ between K blocks only in the 16-byte granular start address
             const int blocks = min(p.kpb, it_end - it);
             uint32_t b16 = a16;
-            for (int g = 0; g < blocks; ++g, b16 += kb16)
-              tc_mma_block<KIND, PAIR>(tmem_d, desc_lo | (b16 & 0x3fffu), desc_lo | ((b16 + a16_bytes) & 0x3fffu), desc_hi, idesc, (it + g) > it_begin ? 1u : 0u, mmas);
+            for (int g = 0; g < blocks; ++g, b16 += kb16) {
+              const uint32_t w16 = b_res ? bres16 + (uint32_t)(it + g) * b16_bytes : b16 + a16_bytes;
+              tc_mma_block<KIND, PAIR>(tmem_d, desc_lo | (b16 & 0x3fffu), desc_lo | (w16 & 0x3fffu), desc_hi, idesc, (it + g) > it_begin ? 1u : 0u, mmas);
+            }
             // frees the stage, in both CTAs of a pair, once these MMAs have read it
             const uint32_t e = smem_u32(&bar_empty[stage]);
             if (PAIR) {

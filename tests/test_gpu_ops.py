@@ -44,11 +44,13 @@ def _arr(t):
     return np.asarray(t["data"], dtype=dtype).reshape(t["shape"])
 
 
-def dispatch(ctx, op, inputs, attrs=None, n_out=1):
+def dispatch(ctx, op, inputs, attrs=None, n_out=1, initializers=()):
+    """One node through the dispatch entry; the inputs whose positions `initializers` lists are handed over as weights."""
     names = [f"in{i}" if x is not None else "" for i, x in enumerate(inputs)]
     node = Node(op=op, name="op0", inputs=names, outputs=[f"out{i}" for i in range(n_out)], attrs=dict(attrs or {}))
-    inter = {n: x for n, x in zip(names, inputs) if n}
-    return S.try_cuda_dispatch(node, {}, inter, ctx)
+    inter = {n: x for i, (n, x) in enumerate(zip(names, inputs)) if n and i not in initializers}
+    weights = {n: x for i, (n, x) in enumerate(zip(names, inputs)) if n and i in initializers}
+    return S.try_cuda_dispatch(node, weights, inter, ctx)
 
 
 def assert_close_tf32(got, want, what=""):
@@ -462,6 +464,53 @@ def test_glue_ops_match_oracle(ctx_auto):
         assert got is not None, ctx.last_error()
         assert np.array_equal(got[0], want), ins[1:]
     assert dispatch(ctx, "Slice", [x, np.float32([0]), np.float32([4]), np.float32([3]), np.float32([2])]) is None  # strided: declined
+
+
+def test_transformer_glue_ops_match_oracle(ctx_auto):
+    """LayerNormalization, Softmax, Gelu (both forms), Erf, Gather and Transpose, each as one node through the ABI,
+    at the absolute tolerances of the reference's own tests (oxionnx-ops src/nn/normalization.rs:912 layer_norm 1e-4,
+    :1087 softmax 1e-5; the activations at 1e-5); the two movers are exact."""
+    ctx = ctx_auto
+    rng = np.random.default_rng(131)
+    x = (rng.standard_normal((3, 37, 768)) * 2.5 + 0.7).astype(np.float32)
+    gamma = rng.uniform(0.5, 1.5, 768).astype(np.float32)
+    beta = rng.standard_normal(768).astype(np.float32)
+    for ins, attrs in (([x, gamma, beta], {"axis": -1, "epsilon": 1e-5}), ([x, gamma], {"axis": -1, "epsilon": 1e-12}),
+                       ([x[:, :, :96], gamma[:96], beta[:96]], {"axis": 2})):
+        want, = oracle.run_node("LayerNormalization", ins, attrs)
+        got = dispatch(ctx, "LayerNormalization", ins, attrs, initializers=(1, 2))
+        assert got is not None, ctx.last_error()
+        assert got[0].shape == want.shape and np.max(np.abs(got[0] - want)) <= 1e-4, (attrs, np.max(np.abs(got[0] - want)))
+    scores = (rng.standard_normal((2, 12, 37, 37)) * 4).astype(np.float32)
+    scores[0, :, :, 30:] = -10000.0  # an attention mask already added
+    for ins, attrs in (([scores], {"axis": -1}), ([scores], {}), ([scores[0, 0]], {"axis": 1}), ([x[0]], {"axis": -1})):
+        want, = oracle.run_node("Softmax", ins, attrs)
+        got = dispatch(ctx, "Softmax", ins, attrs)
+        assert got is not None, ctx.last_error()
+        assert np.max(np.abs(got[0] - want)) <= 1e-5, attrs
+        assert np.allclose(got[0].sum(-1), 1.0, atol=1e-5)
+    h = (rng.standard_normal((2, 37, 3072)) * 3).astype(np.float32)
+    h[0, 0, :8] = [0.0, -0.0, 1e-8, -1e-8, 12.0, -12.0, 40.0, -40.0]
+    for op, attrs in (("Gelu", {}), ("Gelu", {"approximate": "none"}), ("Gelu", {"approximate": "tanh"}), ("Erf", {})):
+        want, = oracle.run_node(op, [h], attrs)
+        got = dispatch(ctx, op, [h], attrs)
+        assert got is not None, ctx.last_error()
+        assert np.all(np.abs(got[0] - want) <= 1e-5 + 1e-5 * np.abs(want)), (op, attrs, np.max(np.abs(got[0] - want)))
+    table = rng.standard_normal((211, 96)).astype(np.float32)
+    ids = rng.integers(-211, 211, size=(3, 37)).astype(np.float32)  # negative indices wrap (oxionnx-ops src/indexing/gather.rs:12-44)
+    want, = oracle.run_node("Gather", [table, ids], {"axis": 0})
+    got = dispatch(ctx, "Gather", [table, ids], {"axis": 0}, initializers=(0,))
+    assert got is not None, ctx.last_error()
+    assert np.array_equal(got[0], want)
+    # an index outside the table is reported, not clamped: the node falls to the CPU operator, which raises its own error
+    assert dispatch(ctx, "Gather", [table, np.float32([[0, 211]])], {"axis": 0}, initializers=(0,)) is None
+    assert ctx.last_error()
+    t4 = rng.standard_normal((2, 37, 12, 64)).astype(np.float32)
+    for ins, attrs in (([t4], {"perm": [0, 2, 1, 3]}), ([t4], {"perm": [0, 2, 3, 1]}), ([t4[0, :, 0]], {}), ([t4], {"perm": [0, 1, 2, 3]})):
+        want, = oracle.run_node("Transpose", ins, attrs)
+        got = dispatch(ctx, "Transpose", ins, attrs)
+        assert got is not None, (attrs, ctx.last_error())
+        assert np.array_equal(got[0], want), attrs
 
 
 def test_decline_and_failure_contract(ctx_auto):
