@@ -27,13 +27,14 @@ SOURCES = {
     "umma_tf32.cu": [f for f in COMMON if f != "--fmad=false"],
     "umma_f16.cu": [f for f in COMMON if f != "--fmad=false"],
     "umma_probe.cu": [f for f in COMMON if f != "--fmad=false"],
+    "umma_chain.cu": [f for f in COMMON if f != "--fmad=false"],
     "runtime.cpp": COMMON,
     "planner.cpp": COMMON,
     "abi.cpp": COMMON,
     "onnx_model.cpp": COMMON,
     "model_abi.cpp": COMMON,
 }
-HEADERS = ["common.hpp", "kernels.hpp", "runtime.hpp", "umma_kernel.cuh", "umma_launch.cuh", "model.hpp", "abi_internal.hpp", os.path.join("..", "..", "include", "oxb200.h")]
+HEADERS = ["common.hpp", "kernels.hpp", "runtime.hpp", "umma_kernel.cuh", "umma_launch.cuh", "umma_chain.cuh", "model.hpp", "abi_internal.hpp", os.path.join("..", "..", "include", "oxb200.h")]
 
 
 def _nvcc():

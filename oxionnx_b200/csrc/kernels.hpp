@@ -261,6 +261,31 @@ void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s);
 const char* umma_plan_desc(const UmmaPlan* p);
 // Re-point a plan at new buffers (arena moved) is not supported: plans are rebuilt.
 
+// A chain of quantised linear layers over at most 64 rows as one cooperative tcgen05 kernel: layer i reads
+// [rows][K] 8-bit lanes at `x`, multiplies by the packed [N][K] 8-bit weights at `w`, requantises
+// (q = clamp(rne(f64(acc + bias_i[ch]) * f64(combined[ch]) + y_zp), lo, hi)) and writes [rows][N] 8-bit lanes at
+// `out`, which must be layer i+1's `x`.  Returns nullptr with `why` filled when the chain is not eligible (then
+// every layer runs as its own plan).
+struct UmmaChainLayer {
+  const void* x = nullptr;
+  DT x_dt = DT::U8;
+  const void* w = nullptr;
+  DT w_dt = DT::I8;
+  void* out = nullptr;
+  int K = 0, N = 0;
+  const int32_t* bias_i = nullptr;
+  const float* combined = nullptr;
+  int y_zp = 0, lo = 0, hi = 255;
+  int fma_exact = 0;  // every combined[ch] is 0 or within [2^-21, 2^40]: fma(acc, c, 1.5 * 2^23 + zp) is the exact requantisation for |acc| < 2^24
+};
+struct UmmaChain;
+UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int rows, std::string* why);
+void umma_chain_destroy(UmmaChain* c);
+// After a launch that gave up: clears the arrival counters and the grid barrier's counter.
+void umma_chain_reset_after_error(UmmaChain* c);
+void umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s);
+const char* umma_chain_desc(const UmmaChain* c);
+
 // Packed weight size helpers for the tensor-core path: weights are laid out [OC][R*S*Cpad]
 // (K-major rows), Cpad = C rounded up to the channel block.
 int umma_channel_block(int C, int kind);  // 0 when C is not eligible

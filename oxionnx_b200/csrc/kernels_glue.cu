@@ -490,6 +490,22 @@ __global__ void binary_vec4_kernel(const float4* __restrict__ a, const float4* _
   }
 }
 
+// a[i] op b[i % nb]: the second operand is the trailing axes of the first (a bias row, a position table added to every
+// sample), f32 in the logical order; 16-byte accesses, 32-bit index arithmetic.
+__global__ void binary_suffix_vec4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out, int op, int relu_after,
+                                          int rtf32, uint32_t n4, uint32_t nb4) {
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    const float4 x = a[i], y = __ldg(b + i % nb4);
+    float r[4] = {apply_bin(op, x.x, y.x), apply_bin(op, x.y, y.y), apply_bin(op, x.z, y.z), apply_bin(op, x.w, y.w)};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (relu_after) r[e] = fmaxf(r[e], 0.f);
+      if (rtf32) r[e] = round_tf32(r[e]);
+    }
+    out[i] = make_float4(r[0], r[1], r[2], r[3]);
+  }
+}
+
 // erf by the polynomial the reference uses (Abramowitz-Stegun 7.1.26, nn_ops/activations.rs:578), same operation order.
 __device__ __forceinline__ float erf_poly(float x) {
   const float sign = x >= 0.0f ? 1.0f : -1.0f;
@@ -1298,6 +1314,48 @@ __global__ void transpose_perm_kernel(const uint32_t* __restrict__ x, uint32_t* 
   }
 }
 
+// The same permutation when the innermost axis stays innermost (head split / merge of attention tensors): 16-byte
+// pieces of the inner rows, 32-bit index arithmetic.
+__global__ void transpose_perm_vec4_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, uint32_t d1, uint32_t d2, uint32_t w4, uint32_t s0, uint32_t s1,
+                                           uint32_t s2, uint32_t total4) {
+  for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < total4; o += gridDim.x * blockDim.x) {
+    uint32_t t = o;
+    const uint32_t i3 = t % w4;
+    t /= w4;
+    const uint32_t i2 = t % d2;
+    t /= d2;
+    const uint32_t i1 = t % d1;
+    const uint32_t i0 = t / d1;
+    y[o] = x[i0 * s0 + i1 * s1 + i2 * s2 + i3];
+  }
+}
+
+// The same permutation when the input's contiguous axis becomes the output's second-to-last one (V -> V^T per head):
+// 32 x 32 tiles through shared memory, 128-byte reads along the input rows and 128-byte writes along the output rows.
+__global__ void transpose_tiled_kernel(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, Dims4 yd, Dims4 xs, int64_t blocks) {
+  __shared__ uint32_t tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 256 threads: 8 rows of a tile per pass
+  const int64_t th = (yd.H + 31) / 32, tw = (yd.W + 31) / 32;
+  for (int64_t b = blockIdx.x; b < blocks; b += gridDim.x) {
+    int64_t t = b;
+    const int64_t w0 = (t % tw) * 32;
+    t /= tw;
+    const int64_t h0 = (t % th) * 32;
+    t /= th;
+    const int64_t i1 = t % yd.C, i0 = t / yd.C;
+    const uint32_t* src = x + i0 * xs.N + i1 * xs.C;
+    uint32_t* dst = y + (i0 * yd.C + i1) * yd.H * yd.W;
+#pragma unroll
+    for (int k = ty; k < 32; k += 8)
+      if (h0 + tx < yd.H && w0 + k < yd.W) tile[k][tx] = src[(h0 + tx) + (w0 + k) * xs.W];
+    __syncthreads();
+#pragma unroll
+    for (int k = ty; k < 32; k += 8)
+      if (h0 + k < yd.H && w0 + tx < yd.W) dst[(h0 + k) * yd.W + (w0 + tx)] = tile[tx][k];
+    __syncthreads();
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -1342,6 +1400,112 @@ __global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restri
     for (int64_t k = lane; k < n; k += 32) {
       const float v = __fmul_rn(py[k], inv);
       py[k] = round_tf32_flag ? round_tf32(v) : v;
+    }
+  }
+}
+
+// The same softmax for rows of 128 * NV4 lanes: a lane keeps its 4 * NV4 values in registers between the three
+// phases, so the row is read once and written once, in 16-byte pieces.
+template <int NV4>
+__global__ void softmax_rows_reg_kernel(const float4* __restrict__ x, float4* __restrict__ y, int64_t rows, const float* __restrict__ scale,
+                                        const float4* __restrict__ mask, int64_t rows_per_mask, int round_tf32_flag) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const float sc = scale ? scale[0] : 1.f;
+  for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const float4* px = x + r * (32 * NV4);
+    const float4* pm = mask ? mask + (r / rows_per_mask) * (32 * NV4) : nullptr;
+    float v[4 * NV4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NV4; ++j) {
+      const float4 t = px[32 * j + lane];
+      v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
+      if (scale) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[4 * j + e] = __fmul_rn(v[4 * j + e], sc);
+      }
+      if (pm) {
+        const float4 m = __ldg(pm + 32 * j + lane);
+        v[4 * j] = __fadd_rn(v[4 * j], m.x), v[4 * j + 1] = __fadd_rn(v[4 * j + 1], m.y), v[4 * j + 2] = __fadd_rn(v[4 * j + 2], m.z),
+               v[4 * j + 3] = __fadd_rn(v[4 * j + 3], m.w);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) mx = fmaxf(mx, v[4 * j + e]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4 * NV4; ++k) {
+      v[k] = expf(__fsub_rn(v[k], mx));
+      sum += v[k];
+    }
+    const float inv = __frcp_rn(warp_sum(sum));
+#pragma unroll
+    for (int j = 0; j < NV4; ++j) {
+      float o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o[e] = __fmul_rn(v[4 * j + e], inv);
+        if (round_tf32_flag) o[e] = round_tf32(o[e]);
+      }
+      y[r * (32 * NV4) + 32 * j + lane] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// LayerNormalization for rows of 128 * NV4 lanes, the row kept in registers (read once, in 16-byte pieces).
+template <int NV4>
+__global__ void layer_norm_rows_reg_kernel(const float4* __restrict__ x, float4* __restrict__ y, int64_t rows, const float4* __restrict__ scale,
+                                           const float4* __restrict__ bias, float eps, uint32_t* minmax_keys) {
+  const int lane = threadIdx.x & 31;
+  const float n = (float)(128 * NV4);
+  float mn = INFINITY, mx = -INFINITY;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const float4* px = x + r * (32 * NV4);
+    float v[4 * NV4];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV4; ++j) {
+      const float4 t = px[32 * j + lane];
+      v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
+      sum += (t.x + t.y) + (t.z + t.w);
+    }
+    const float mean = __fdiv_rn(warp_sum(sum), n);
+    float vs = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4 * NV4; ++k) {
+      v[k] = __fsub_rn(v[k], mean);
+      vs += __fmul_rn(v[k], v[k]);
+    }
+    const float var = __fdiv_rn(warp_sum(vs), n);
+    const float inv_std = __frcp_rn(__fsqrt_rn(__fadd_rn(var, eps)));
+#pragma unroll
+    for (int j = 0; j < NV4; ++j) {
+      const float4 g = __ldg(scale + 32 * j + lane);
+      float o[4] = {__fmul_rn(__fmul_rn(v[4 * j], inv_std), g.x), __fmul_rn(__fmul_rn(v[4 * j + 1], inv_std), g.y),
+                    __fmul_rn(__fmul_rn(v[4 * j + 2], inv_std), g.z), __fmul_rn(__fmul_rn(v[4 * j + 3], inv_std), g.w)};
+      if (bias) {
+        const float4 b = __ldg(bias + 32 * j + lane);
+        o[0] = __fadd_rn(o[0], b.x), o[1] = __fadd_rn(o[1], b.y), o[2] = __fadd_rn(o[2], b.z), o[3] = __fadd_rn(o[3], b.w);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        mn = fminf(mn, o[e]);
+        mx = fmaxf(mx, o[e]);
+      }
+      y[r * (32 * NV4) + 32 * j + lane] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  if (minmax_keys) {  // uniform across the grid
+    for (int off = 16; off > 0; off >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    if (lane == 0) {
+      if (mn != INFINITY) atomicMin(&minmax_keys[0], float_key(mn));
+      if (mx != -INFINITY) atomicMax(&minmax_keys[1], float_key(mx));
     }
   }
 }
@@ -1652,6 +1816,23 @@ void binary(const TensorRef& a, const TensorRef& b, const TensorRef& out, int op
                                                                round_tf32_flag, total / 4);
     return;
   }
+  if (a.d.numel() == total && a.layout == Layout::PLAIN && b.layout == Layout::PLAIN && out.layout == Layout::PLAIN && a.dt == DT::F32 && b.dt == DT::F32 &&
+      out.dt == DT::F32 && total % 4 == 0 && total / 4 < (int64_t)1 << 31 && (((uintptr_t)a.ptr | (uintptr_t)b.ptr | (uintptr_t)out.ptr) & 15) == 0) {
+    const int64_t od[4] = {out.d.N, out.d.C, out.d.H, out.d.W}, bd[4] = {b.d.N, b.d.C, b.d.H, b.d.W};
+    int k0 = 0;
+    while (k0 < 4 && bd[k0] == 1) ++k0;
+    bool suffix = k0 > 0 && k0 < 4;
+    int64_t nb = 1;
+    for (int j = k0; j < 4; ++j) {
+      suffix = suffix && bd[j] == od[j];
+      nb *= bd[j];
+    }
+    if (suffix && nb % 4 == 0) {
+      binary_suffix_vec4_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((const float4*)a.ptr, (const float4*)b.ptr, (float4*)out.ptr, op, relu_after,
+                                                                         round_tf32_flag, (uint32_t)(total / 4), (uint32_t)(nb / 4));
+      return;
+    }
+  }
   binary_kernel<<<grid_for(total), kThreads, 0, s>>>(a.ptr, a.dt, a.layout, a.d, b.ptr, b.dt, b.layout, b.d, out.ptr, out.dt, out.layout,
                                                      out.d, op, relu_after, round_tf32_flag, total);
 }
@@ -1774,18 +1955,48 @@ void gather_rows(const float* table, const float* idx, float* out, int64_t n_idx
 void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstride, cudaStream_t s) {
   const int64_t total = yd.numel();
   if (total == 0) return;
+  if (xstride.W == 1 && yd.W % 4 == 0 && xstride.N % 4 == 0 && xstride.C % 4 == 0 && xstride.H % 4 == 0 && total < (int64_t)1 << 31 &&
+      ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0) {
+    const uint32_t total4 = (uint32_t)(total / 4);
+    transpose_perm_vec4_kernel<<<grid_for(total4), kThreads, 0, s>>>((const uint4*)x, (uint4*)y, (uint32_t)yd.C, (uint32_t)yd.H, (uint32_t)(yd.W / 4),
+                                                                     (uint32_t)(xstride.N / 4), (uint32_t)(xstride.C / 4), (uint32_t)(xstride.H / 4), total4);
+    return;
+  }
+  if (xstride.H == 1 && xstride.W != 1 && yd.H >= 8 && yd.W >= 8) {
+    const int64_t blocks = yd.N * yd.C * ((yd.H + 31) / 32) * ((yd.W + 31) / 32);
+    transpose_tiled_kernel<<<(unsigned)std::min<int64_t>(blocks, 148 * 64), 256, 0, s>>>((const uint32_t*)x, (uint32_t*)y, yd, xstride, blocks);
+    return;
+  }
   transpose_perm_kernel<<<grid_for(total), kThreads, 0, s>>>((const uint32_t*)x, (uint32_t*)y, yd, xstride, total);
 }
 
 void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, int round_tf32_flag,
                   cudaStream_t s) {
   if (rows * n == 0) return;
-  softmax_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, mask, rows_per_mask > 0 ? rows_per_mask : 1, round_tf32_flag);
+  const int64_t rpm = rows_per_mask > 0 ? rows_per_mask : 1;
+  if (n % 128 == 0 && n <= 512 && n != 384 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)mask) & 15) == 0) {
+    const int g = grid_for(rows * 32);
+    const float4 *x4 = (const float4*)x, *m4 = (const float4*)mask;
+    if (n == 128) softmax_rows_reg_kernel<1><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, scale, m4, rpm, round_tf32_flag);
+    else if (n == 256) softmax_rows_reg_kernel<2><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, scale, m4, rpm, round_tf32_flag);
+    else softmax_rows_reg_kernel<4><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, scale, m4, rpm, round_tf32_flag);
+    return;
+  }
+  softmax_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, mask, rpm, round_tf32_flag);
 }
 
 void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s,
                      unsigned int* minmax_keys) {
   if (rows * n == 0) return;
+  if (n % 256 == 0 && n <= 1024 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)bias) & 15) == 0) {
+    const int g = grid_for(rows * 32);
+    const float4 *x4 = (const float4*)x, *s4 = (const float4*)scale, *b4 = (const float4*)bias;
+    if (n == 256) layer_norm_rows_reg_kernel<2><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    else if (n == 512) layer_norm_rows_reg_kernel<4><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    else if (n == 768) layer_norm_rows_reg_kernel<6><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    else layer_norm_rows_reg_kernel<8><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    return;
+  }
   layer_norm_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, bias, eps, minmax_keys);
 }
 

@@ -8,7 +8,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
+#include "umma_chain.cuh"
 #include "umma_kernel.cuh"
 
 namespace oxb {
@@ -596,6 +598,209 @@ void umma_plan_reset_after_error(UmmaPlan* p) {
   (void)cudaMemset(p->ws_count, 0, cnt * sizeof(unsigned int));
 }
 const char* umma_plan_desc(const UmmaPlan* p) { return p->desc; }
+
+// ---- chain of quantised linear layers over few rows ------------------------------------------------------------
+struct UmmaChain {
+  ChainParams cp;
+  int grid = 0, device = 0;
+  size_t smem = 0;
+  void* scratch = nullptr;  // partial sums of every unit, arrival counters (zero between launches), the grid barrier's counter
+  size_t scratch_bytes = 0;
+  char desc[200];
+};
+
+namespace {
+
+// Units, shared-memory regions and grid of a chain; `cluster` > 1: the K slices of a channel tile are the CTAs of
+// one cluster of that size, 1: as many slices per tile as keep every unit on its own SM, summed through L2.
+bool chain_layout(UmmaChain* c, const UmmaChainLayer* layers, int n_layers, int sms, int cluster, const char** why) {
+  ChainParams& cp = c->cp;
+  cp.cluster = cluster;
+  int grid = 0, kb_max = 0;
+  for (int l = 0; l < n_layers; ++l) {
+    ChainLayerParams& P = cp.layer[l];
+    const int kblocks = layers[l].K / 128;
+    P.N = layers[l].N;
+    P.n_tiles = (int)ceil_div(layers[l].N, 128);
+    int splits = 1;
+    if (cluster > 1) {
+      if (kblocks % cluster != 0 || P.n_tiles * cluster > sms) return *why = "the K blocks do not divide among the CTAs of a cluster", false;
+      splits = cluster;
+    } else {
+      if (P.n_tiles > sms) return *why = "more channel tiles than SMs", false;
+      for (int sp = 1; sp <= kblocks; ++sp)
+        if (kblocks % sp == 0 && P.n_tiles * sp <= sms) splits = sp;
+    }
+    P.splits = splits;
+    P.kb = kblocks / splits;
+    grid = std::max(grid, P.n_tiles * splits);
+    kb_max = std::max(kb_max, P.kb);
+  }
+  // shared memory: [weight regions | activation blocks].  A layer whose slice does not fit beside the earlier
+  // ones takes over the region of an earlier layer once that layer's MMAs have completed.  In a cluster the
+  // activation blocks also hold the CTA's partial sums (128 channels x 64 rows of int32) once the MMAs are done.
+  const size_t x_bytes = std::max<size_t>((size_t)kb_max * CHAIN_X_TILE, cluster > 1 ? (size_t)CHAIN_ROWS * 128 * 4 : 0);
+  if (x_bytes + 1024 >= kSmemBudget) return *why = "activation blocks exceed shared memory", false;
+  const size_t w_budget = kSmemBudget - 1024 - x_bytes;
+  size_t cursor = 0;
+  int taken_by[CHAIN_MAX_LAYERS] = {-1, -1, -1, -1};
+  for (int l = 0; l < n_layers; ++l) {
+    ChainLayerParams& P = cp.layer[l];
+    const size_t need = (size_t)P.kb * CHAIN_W_TILE;
+    if (cursor + need <= w_budget) {
+      P.w_off = (uint32_t)cursor;
+      P.w_after = -1;
+      cursor += need;
+      continue;
+    }
+    int from = -1;
+    for (int j = 0; j < l && from < 0; ++j)
+      if (taken_by[j] < 0 && cp.layer[j].w_after < 0 && (size_t)cp.layer[j].kb * CHAIN_W_TILE >= need) from = j;
+    if (from < 0) return *why = "weight slices do not fit in shared memory", false;
+    taken_by[from] = l;
+    P.w_off = cp.layer[from].w_off;
+    P.w_after = from;
+  }
+  cp.x_off = (uint32_t)cursor;
+  c->smem = cursor + x_bytes + 1024;
+  c->grid = grid;
+  if (chain_max_resident(c->smem, c->device, cluster) < grid) return *why = "the grid cannot be resident at once", false;
+  return true;
+}
+
+}  // namespace
+
+UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int rows, std::string* why) {
+  auto no = [&](const char* msg) -> UmmaChain* {
+    if (why) *why = msg;
+    return nullptr;
+  };
+  load_encoders();
+  if (!g_encode_tiled) return no("no tensor-map encoder");
+  if (n_layers < 2 || n_layers > CHAIN_MAX_LAYERS) return no("a chain has 2 to 4 layers");
+  if (rows < 1 || rows > CHAIN_ROWS) return no("a chain runs at most 64 rows");
+  int device = 0, sms = 0;
+  OXB_CUDA(cudaGetDevice(&device));
+  OXB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  for (int l = 0; l < n_layers; ++l) {
+    const UmmaChainLayer& L = layers[l];
+    if (L.K % 128 != 0 || L.K < 128 || L.N < 1) return no("K is not a multiple of 128 bytes");
+    if (((uintptr_t)L.x & 15) || ((uintptr_t)L.w & 15)) return no("operand not 16-byte aligned");
+    if (l > 0 && (L.x != layers[l - 1].out || L.K != layers[l - 1].N)) return no("layers are not chained");
+    if (dt_size(L.x_dt) != 1 || dt_size(L.w_dt) != 1) return no("operands are not 8-bit");
+  }
+  UmmaChain* c = new UmmaChain();
+  std::memset(&c->cp, 0, sizeof(ChainParams));
+  ChainParams& cp = c->cp;
+  cp.n_layers = n_layers;
+  cp.rows = rows;
+  c->device = device;
+  // Clusters of 4, then 8, then 2 CTAs (partial sums meet in distributed shared memory); a cluster launch that
+  // the driver refuses, or K blocks that do not divide, leave the L2 workspace form.
+  const char* msg = "";
+  bool laid = false;
+  uint64_t* probe_bar = nullptr;
+  for (int cluster : {4, 8, 2, 1}) {
+    const char* m2 = "";
+    if (!chain_layout(c, layers, n_layers, sms, cluster, &m2)) {
+      if (cluster == 1) msg = m2;
+      continue;
+    }
+    if (cluster > 1) {
+      // one empty launch with this geometry: cooperative and cluster attributes together
+      if (!probe_bar && (cudaMalloc(&probe_bar, 256) != cudaSuccess || cudaMemset(probe_bar, 0, 256) != cudaSuccess)) {
+        (void)cudaGetLastError();
+        continue;
+      }
+      ChainParams trial;
+      std::memset(&trial, 0, sizeof trial);
+      trial.cluster = cluster;
+      trial.grid_bar = (unsigned long long*)probe_bar;
+      trial.err_flag = (int*)(probe_bar + 8);
+      const int grid = (c->grid + cluster - 1) / cluster * cluster;
+      if (!try_launch_chain(trial, grid, c->smem, device, cluster)) continue;
+      c->grid = grid;
+    }
+    laid = true;
+    break;
+  }
+  if (probe_bar) cudaFree(probe_bar);
+  if (!laid) {
+    delete c;
+    return no(msg[0] ? msg : "no geometry fits");
+  }
+  // scratch: per layer the partial sums of every unit (L2 workspace form) and n_tiles arrival counters, then the barrier counter
+  size_t off = 0;
+  size_t acc_off[CHAIN_MAX_LAYERS], cnt_off[CHAIN_MAX_LAYERS];
+  for (int l = 0; l < n_layers; ++l) {
+    acc_off[l] = off;
+    if (cp.cluster == 1) off += (size_t)cp.layer[l].n_tiles * cp.layer[l].splits * CHAIN_ROWS * 128 * 4;
+    cnt_off[l] = off;
+    off += align_up((size_t)cp.layer[l].n_tiles * 4, 256);
+  }
+  const size_t bar_off = off;
+  off += 256;
+  if (cudaMalloc(&c->scratch, off) != cudaSuccess || cudaMemset(c->scratch, 0, off) != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (c->scratch) cudaFree(c->scratch);
+    delete c;
+    return no("no memory for the partial sums");
+  }
+  c->scratch_bytes = off;
+  cp.grid_bar = (unsigned long long*)((uint8_t*)c->scratch + bar_off);
+  for (int l = 0; l < n_layers; ++l) {
+    const UmmaChainLayer& L = layers[l];
+    ChainLayerParams& P = cp.layer[l];
+    cuuint32_t estr[2] = {1, 1};
+    cuuint64_t wdim[2] = {(cuuint64_t)L.K, (cuuint64_t)L.N}, wstr[1] = {(cuuint64_t)L.K};
+    cuuint32_t wbox[2] = {128, 128};
+    CUresult rc = g_encode_tiled(&P.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(L.w), wdim, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    cuuint64_t xdim[2] = {(cuuint64_t)L.K, (cuuint64_t)rows}, xstr[1] = {(cuuint64_t)L.K};
+    cuuint32_t xbox[2] = {128, (cuuint32_t)CHAIN_ROWS};
+    if (rc == CUDA_SUCCESS)
+      rc = g_encode_tiled(&P.tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(L.x), xdim, xstr, xbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      cudaFree(c->scratch);
+      delete c;
+      return no("tensor map rejected by the driver");
+    }
+    // the weights are the 128-row operand (A), the activation rows the 64 columns (B)
+    P.idesc = make_idesc(KIND_I8, L.w_dt == DT::I8, L.x_dt == DT::I8, CHAIN_ROWS, 128);
+    P.bias_i = L.bias_i;
+    P.combined = L.combined;
+    P.y_zp = L.y_zp;
+    P.lo = L.lo;
+    P.hi = L.hi;
+    P.out = (uint8_t*)L.out;
+    P.ws = (int32_t*)((uint8_t*)c->scratch + acc_off[l]);
+    P.fma_exact = L.fma_exact;
+    P.tile_count = (unsigned int*)((uint8_t*)c->scratch + cnt_off[l]);
+  }
+  int n = snprintf(c->desc, sizeof c->desc, "umma_i8_chain rows=%d", rows);
+  for (int l = 0; l < n_layers && n < (int)sizeof c->desc; ++l)
+    n += snprintf(c->desc + n, sizeof c->desc - n, " %dx%d:%dt*%ds", layers[l].K, layers[l].N, cp.layer[l].n_tiles, cp.layer[l].splits);
+  if (n < (int)sizeof c->desc)
+    snprintf(c->desc + n, sizeof c->desc - n, " grid=%d %s smem=%zuK", c->grid, cp.cluster > 1 ? "clusters (distributed shared memory)" : "slices through L2", c->smem / 1024);
+  return c;
+}
+
+void umma_chain_destroy(UmmaChain* c) {
+  if (!c) return;
+  if (c->scratch) cudaFree(c->scratch);
+  delete c;
+}
+void umma_chain_reset_after_error(UmmaChain* c) {
+  if (c && c->scratch) (void)cudaMemset(c->scratch, 0, c->scratch_bytes);
+}
+const char* umma_chain_desc(const UmmaChain* c) { return c->desc; }
+void umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s) {
+  ChainParams cp = c->cp;
+  cp.err_flag = err_flag;
+  launch_chain(cp, c->grid, c->smem, c->device, cp.cluster, s);
+  OXB_CUDA(cudaGetLastError());
+}
 
 void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {
   KParams kp = p->kp;

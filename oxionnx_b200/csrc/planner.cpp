@@ -521,6 +521,12 @@ class Planner {
   void emit_contraction(const NodeDef& n, Contraction& c);
 
   void finalize_lifetimes_and_arena();
+  struct ChainLink {
+    int step = -1, rows = 0;
+    k::UmmaChainLayer layer;
+  };
+  std::vector<ChainLink> chain_links_;
+  void link_chains();
   bool try_s2d_stem(const NodeDef& n, Contraction& c, int src_vi);
   bool try_window_stem(const NodeDef& n, Contraction& c, int src_vi);
   std::deque<HostTensor> made_consts_;  // weights rewritten by the planner (space-to-depth stems)
@@ -603,6 +609,44 @@ void Planner::run(const std::vector<std::pair<std::string, std::vector<int64_t>>
   finalize_lifetimes_and_arena();
   for (auto& st : S.steps_)
     if (st.finalize) st.finalize();
+  link_chains();
+}
+
+// Consecutive steps that are quantised linear layers over the same few rows, each reading what the one before
+// wrote, run as one cooperative kernel launched by the first of them; the others keep their place in the plan
+// (values, lifetimes, profile rows) and launch nothing.  Every intermediate row is still written to its own
+// value, so other readers and kept intermediates see what the separate kernels would have produced.
+void Planner::link_chains() {
+  size_t i = 0;
+  while (i < chain_links_.size()) {
+    size_t j = i + 1;
+    while (j < chain_links_.size() && j - i < 4 && chain_links_[j].step == chain_links_[j - 1].step + 1 && chain_links_[j].rows == chain_links_[i].rows &&
+           chain_links_[j].layer.x == chain_links_[j - 1].layer.out && chain_links_[j].layer.K == chain_links_[j - 1].layer.N)
+      ++j;
+    if (j - i >= 2) {
+      std::vector<k::UmmaChainLayer> layers;
+      for (size_t t = i; t < j; ++t) layers.push_back(chain_links_[t].layer);
+      std::string why;
+      k::UmmaChain* chain = k::umma_chain_create(layers.data(), (int)layers.size(), chain_links_[i].rows, &why);
+      if (chain) {
+        S.umma_chains_.push_back(chain);
+        Step& first = S.steps_[chain_links_[i].step];
+        first.kernel = k::umma_chain_desc(chain);
+        int* err = S.err_flag_;
+        first.launch = [this, chain, err](cudaStream_t s) {
+          k::umma_chain_launch(chain, err, s);
+          C.counters.umma_launches++;
+          C.counters.kernel_launches++;
+        };
+        for (size_t t = i + 1; t < j; ++t) {
+          Step& st = S.steps_[chain_links_[t].step];
+          st.kernel = "umma_i8_chain (inside the launch of '" + first.node_name + "')";
+          st.launch = [](cudaStream_t) {};
+        }
+      }
+    }
+    i = j;
+  }
 }
 
 void Planner::finalize_lifetimes_and_arena() {
@@ -1103,6 +1147,28 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
       S.umma_plans_.push_back(plan);
       Step& me = S.steps_[step_index];
       me.kernel = std::string(k::umma_plan_desc(plan)) + (res_vi >= 0 ? " +residual" : "") + (dq_vi >= 0 ? " +dequant" : "");
+      // a quantised linear layer over few rows may become a link of a one-kernel chain (link_chains)
+      if (kind == 0 && e.mode == k::EPI_REQUANT && xzp_vi < 0 && res_vi < 0 && dq_vi < 0 && cs.R == 1 && cs.S == 1 && cs.sh == 1 && cs.sw == 1 &&
+          cs.pt == 0 && cs.pl == 0 && cs.pb == 0 && cs.pr == 0 && cs.group == 1 && cs.x_pixel_stride == 0 && cs.M() <= 64 && cs.C % 128 == 0 &&
+          dt_size(e.out_dt) == 1 && C.cfg().split_k_max != 1) {
+        ChainLink cl;
+        cl.step = step_index;
+        cl.rows = (int)cs.M();
+        cl.layer.x = V(x_vi).ptr;
+        cl.layer.x_dt = xdt;
+        cl.layer.w = wdev;
+        cl.layer.w_dt = wdt;
+        cl.layer.out = V(out_vi).ptr;
+        cl.layer.K = cs.C;
+        cl.layer.N = cs.OC;
+        cl.layer.bias_i = e.bias_i;
+        cl.layer.combined = e.combined;
+        cl.layer.y_zp = e.y_zp;
+        cl.layer.lo = (e.relu_fused && e.lo < 0) ? 0 : e.lo;
+        cl.layer.hi = e.hi;
+        cl.layer.fma_exact = e.combined_fma_ok && C.cfg().requant_f64 != 1;
+        chain_links_.push_back(cl);
+      }
       int* err = S.err_flag_;
       me.launch = [this, plan, err](cudaStream_t s) {
         k::umma_launch(plan, err, s);

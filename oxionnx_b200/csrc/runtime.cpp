@@ -138,6 +138,7 @@ Session::~Session() {
   cudaSetDevice(ctx_->device());
   cudaStreamSynchronize(ctx_->stream());
   for (auto* p : umma_plans_) k::umma_plan_destroy(p);
+  for (auto* c : umma_chains_) k::umma_chain_destroy(c);
   for (auto& s : steps_) {
     if (s.ev0) cudaEventDestroy(s.ev0);
     if (s.ev1) cudaEventDestroy(s.ev1);
@@ -179,6 +180,7 @@ int Session::check_error_flag() {
     int zero = 0;
     OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
     for (auto* p : umma_plans_) k::umma_plan_reset_after_error(p);
+    for (auto* c : umma_chains_) k::umma_chain_reset_after_error(c);
   }
   return flag;
 }
@@ -314,7 +316,8 @@ void Session::download(oxb200_result* fetches, uint32_t n) {
 void Session::finish_download() {
   sync();
   int flag = check_error_flag();
-  if (flag) raise(OXB200_FAILED, "a tensor-core kernel gave up on a bounded wait (code %d); results are not valid", flag);
+  if (flag)
+    raise(OXB200_FAILED, flag == 20 ? "Gather: an index is out of range (device code %d); results are not valid" : "a tensor-core kernel gave up on a bounded wait (code %d); results are not valid", flag);
 }
 
 void Session::download_async(oxb200_result* fetches, uint32_t n) {
@@ -485,6 +488,7 @@ void Session::collect(oxb200_result* fetches, uint32_t n) {
     if (other.busy) other.poisoned = true;
     OXB_CUDA(cudaMemcpy(err_flag_, &zero, sizeof(int), cudaMemcpyHostToDevice));
     for (auto* p : umma_plans_) k::umma_plan_reset_after_error(p);
+    for (auto* c : umma_chains_) k::umma_chain_reset_after_error(c);
     raise(OXB200_FAILED, "a kernel reported code %d during a pipelined run (or the run before it failed while this one was in flight); results are not valid", flag);
   }
   for (uint32_t i = 0; i < n; ++i) {

@@ -53,6 +53,60 @@ def test_int8_mlp_full_size_bit_exact():
     sess.close()
 
 
+@pytest.mark.parametrize("rows,dims", [(64, (256, 512, 384, 128)), (1, (128, 256, 200, 72)), (37, (512, 1024, 1024, 1024, 256)),
+                                       (64, (128, 256, 256, 256, 256, 256, 128))])
+def test_int8_mlp_chain_kernel_matches_oracle_and_separate_kernels(rows, dims):
+    """Consecutive quantised linear layers over at most 64 rows run as one cooperative kernel (weights as the 128-row
+    MMA operand, K slices summed by integer reductions, one grid barrier per layer).  Every layer's rows must equal the
+    oracle's and those of the one-kernel-per-layer plan (split_k_max = 1 keeps the layers apart); channel counts that
+    are not multiples of the 128-channel tile, a single row, a layer whose K keeps it out of the chain, and six layers
+    (two chains) are covered;
+    a replayed CUDA graph gives the same lanes."""
+    graph, weights, feeds, _ = models.build_int8_mlp(rows=rows, dims=dims)
+    sess, out, ref = run_both(graph, weights, feeds())
+    names = [f"q{i}" for i in range(len(dims))]
+    for name in names:
+        assert np.array_equal(sess.fetch_value(name), ref[name]), name
+    assert np.array_equal(out["y"], ref["y"])
+    kernels = [s["kernel"] for s in sess.steps() if s["op"] == "QLinearConv"]
+    assert kernels[0].startswith("umma_i8_chain rows="), kernels
+    assert sum(k.startswith("umma_i8_chain rows=") for k in kernels) == (2 if len(dims) == 7 else 1), kernels
+    launches_chain = sess.cuda_cache_counters()["umma_launches"]
+    sess.close()
+    apart = Session.builder().with_tuning(split_k_max=1).build_from_graph(graph, weights)
+    got = apart.run(feeds())
+    assert np.array_equal(got["y"], out["y"])
+    assert not any("chain" in s["kernel"] for s in apart.steps())
+    assert apart.cuda_cache_counters()["umma_launches"] > launches_chain
+    apart.close()
+    replay = Session.builder().with_cuda_graph().build_from_graph(graph, weights)
+    for i in range(4):
+        f = {"x": feeds()["x"] * (1.0 + 0.5 * i)}
+        want = oracle.run_graph(graph, weights, f)["y"]
+        assert np.array_equal(replay.run(f)["y"], want), i
+    replay.close()
+
+
+def test_int8_mlp_chain_accumulators_beyond_24_bits_take_the_f64_requantisation():
+    """The chain kernel requantises with one float FMA where the accumulator converts exactly (below 2^24) and with the
+    reference's f64 operations elsewhere: all-127 weights over K = 2048 and saturated inputs give 127 * 127 * 2048 = 33 M."""
+    rows, dims = 16, (2048, 256, 128)
+    graph, weights, feeds, _ = models.build_int8_mlp(rows=rows, dims=dims)
+    weights = dict(weights)
+    weights["w0"] = np.full_like(weights["w0"], 127.0)
+    weights["w0"][::3] = -127.0
+    weights["w0_scale"] = np.full_like(weights["w0_scale"], 4e-6)
+    x = feeds()["x"]
+    x[:8] = 100.0   # saturates the input quantiser at 255
+    x[8:12] = -100.0
+    sess, out, ref = run_both(graph, weights, {"x": x})
+    assert any("umma_i8_chain rows=" in s["kernel"] for s in sess.steps())
+    q1 = sess.fetch_value("q1")
+    assert np.array_equal(q1, ref["q1"]) and np.array_equal(out["y"], ref["y"])
+    assert 0 < q1.min() and q1.max() < 255 and len(np.unique(q1)) > 2  # inside the range: the rounding itself is compared
+    sess.close()
+
+
 def test_resnet_f32_small_per_node_and_final():
     graph, weights, feeds, _ = models.build_resnet50_f32(batch=3, image=64, base=16, classes=40)
     sess, out, ref = run_both(graph, weights, feeds(3))

@@ -476,14 +476,24 @@ def test_transformer_glue_ops_match_oracle(ctx_auto):
     gamma = rng.uniform(0.5, 1.5, 768).astype(np.float32)
     beta = rng.standard_normal(768).astype(np.float32)
     for ins, attrs in (([x, gamma, beta], {"axis": -1, "epsilon": 1e-5}), ([x, gamma], {"axis": -1, "epsilon": 1e-12}),
-                       ([x[:, :, :96], gamma[:96], beta[:96]], {"axis": 2})):
+                       ([x[:, :, :96], gamma[:96], beta[:96]], {"axis": 2}), ([x[:, :, :256], gamma[:256], beta[:256]], {}),
+                       ([x[:, :, :512], gamma[:512]], {}), ([np.concatenate([x, x[:, :, :256]], -1), np.tile(gamma, 2)[:1024], np.tile(beta, 2)[:1024]], {})):
         want, = oracle.run_node("LayerNormalization", ins, attrs)
         got = dispatch(ctx, "LayerNormalization", ins, attrs, initializers=(1, 2))
         assert got is not None, ctx.last_error()
         assert got[0].shape == want.shape and np.max(np.abs(got[0] - want)) <= 1e-4, (attrs, np.max(np.abs(got[0] - want)))
+    # trailing-axes broadcasts (a bias row, a position table added to every sample): bit-exact elementwise results
+    pos = rng.standard_normal((37, 768)).astype(np.float32)
+    for op in ("Add", "Sub", "Mul", "Div"):
+        for other in (beta, pos, pos[None], beta[:6].repeat(128)[None, None]):
+            want, = oracle.run_node(op, [x, other])
+            got = dispatch(ctx, op, [x, other])
+            assert got is not None and np.array_equal(got[0], want), (op, other.shape)
     scores = (rng.standard_normal((2, 12, 37, 37)) * 4).astype(np.float32)
     scores[0, :, :, 30:] = -10000.0  # an attention mask already added
-    for ins, attrs in (([scores], {"axis": -1}), ([scores], {}), ([scores[0, 0]], {"axis": 1}), ([x[0]], {"axis": -1})):
+    wide = (rng.standard_normal((2, 3, 128, 128)) * 4).astype(np.float32)  # rows of 128 / 256 / 512 lanes stay in registers
+    for ins, attrs in (([scores], {"axis": -1}), ([scores], {}), ([scores[0, 0]], {"axis": 1}), ([x[0]], {"axis": -1}), ([wide], {}),
+                       ([wide.reshape(2, 3, 64, 256)], {}), ([wide.reshape(6, 32, 512)], {"axis": 2})):
         want, = oracle.run_node("Softmax", ins, attrs)
         got = dispatch(ctx, "Softmax", ins, attrs)
         assert got is not None, ctx.last_error()
@@ -502,9 +512,12 @@ def test_transformer_glue_ops_match_oracle(ctx_auto):
     got = dispatch(ctx, "Gather", [table, ids], {"axis": 0}, initializers=(0,))
     assert got is not None, ctx.last_error()
     assert np.array_equal(got[0], want)
-    # an index outside the table is reported, not clamped: the node falls to the CPU operator, which raises its own error
-    assert dispatch(ctx, "Gather", [table, np.float32([[0, 211]])], {"axis": 0}, initializers=(0,)) is None
-    assert ctx.last_error()
+    # an index outside the table is reported, not clamped (the reference raises its own error there)
+    own = S.CudaContext(0)  # the failure is counted on the context that met it
+    with pytest.raises(S.OnnxError, match="out of range"):
+        dispatch(own, "Gather", [table, np.float32([[0, 211]])], {"axis": 0}, initializers=(0,))
+    assert own.cache_counters()["failures"] == 1
+    own.close()
     t4 = rng.standard_normal((2, 37, 12, 64)).astype(np.float32)
     for ins, attrs in (([t4], {"perm": [0, 2, 1, 3]}), ([t4], {"perm": [0, 2, 3, 1]}), ([t4[0, :, 0]], {}), ([t4], {"perm": [0, 1, 2, 3]})):
         want, = oracle.run_node("Transpose", ins, attrs)
