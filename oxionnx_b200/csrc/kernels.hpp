@@ -283,7 +283,8 @@ UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int row
 void umma_chain_destroy(UmmaChain* c);
 // After a launch that gave up: clears the arrival counters and the grid barrier's counter.
 void umma_chain_reset_after_error(UmmaChain* c);
-void umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s);
+// false when the driver refused the cooperative launch (nothing ran): the caller runs the layers one by one
+bool umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s);
 const char* umma_chain_desc(const UmmaChain* c);
 
 // Packed weight size helpers for the tensor-core path: weights are laid out [OC][R*S*Cpad]

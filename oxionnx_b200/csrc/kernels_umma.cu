@@ -795,11 +795,10 @@ void umma_chain_reset_after_error(UmmaChain* c) {
   if (c && c->scratch) (void)cudaMemset(c->scratch, 0, c->scratch_bytes);
 }
 const char* umma_chain_desc(const UmmaChain* c) { return c->desc; }
-void umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s) {
+bool umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s) {
   ChainParams cp = c->cp;
   cp.err_flag = err_flag;
-  launch_chain(cp, c->grid, c->smem, c->device, cp.cluster, s);
-  OXB_CUDA(cudaGetLastError());
+  return launch_chain(cp, c->grid, c->smem, c->device, cp.cluster, s);
 }
 
 void umma_launch(const UmmaPlan* p, int* err_flag, cudaStream_t s) {

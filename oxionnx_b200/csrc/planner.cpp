@@ -12,7 +12,9 @@
 #include <cmath>
 #include <cstring>
 #include <deque>
+#include <functional>
 #include <limits>
+#include <memory>
 
 #include "runtime.hpp"
 
@@ -633,10 +635,21 @@ void Planner::link_chains() {
         Step& first = S.steps_[chain_links_[i].step];
         first.kernel = k::umma_chain_desc(chain);
         int* err = S.err_flag_;
-        first.launch = [this, chain, err](cudaStream_t s) {
-          k::umma_chain_launch(chain, err, s);
-          C.counters.umma_launches++;
-          C.counters.kernel_launches++;
+        // the layers' own launches stay behind the chain: a cooperative launch the driver refuses (the grid cannot
+        // be co-resident right now, e.g. under a profiler) turns the chain off for this session
+        auto own = std::make_shared<std::vector<std::function<void(cudaStream_t)>>>();
+        for (size_t t = i; t < j; ++t) own->push_back(S.steps_[chain_links_[t].step].launch);
+        auto off = std::make_shared<bool>(false);
+        first.launch = [this, chain, err, own, off](cudaStream_t s) {
+          if (!*off) {
+            if (k::umma_chain_launch(chain, err, s)) {
+              C.counters.umma_launches++;
+              C.counters.kernel_launches++;
+              return;
+            }
+            *off = true;
+          }
+          for (auto& f : *own) f(s);
         };
         for (size_t t = i + 1; t < j; ++t) {
           Step& st = S.steps_[chain_links_[t].step];

@@ -378,8 +378,10 @@ static cudaError_t launch_chain_raw(const ChainParams& p, int grid, size_t smem,
   return cudaLaunchKernelEx(&cfg, umma_chain_kernel, p);
 }
 
-void launch_chain(const ChainParams& p, int grid, size_t smem, int device, int cluster, cudaStream_t s) {
-  OXB_CUDA(launch_chain_raw(p, grid, smem, device, cluster, s));
+bool launch_chain(const ChainParams& p, int grid, size_t smem, int device, int cluster, cudaStream_t s) {
+  if (launch_chain_raw(p, grid, smem, device, cluster, s) == cudaSuccess) return true;
+  (void)cudaGetLastError();  // a refused launch (co-residency not available right now) ran nothing
+  return false;
 }
 
 bool try_launch_chain(const ChainParams& p, int grid, size_t smem, int device, int cluster) {

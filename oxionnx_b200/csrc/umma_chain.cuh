@@ -52,7 +52,8 @@ struct alignas(64) ChainParams {
   int* err_flag;
 };
 
-void launch_chain(const ChainParams& p, int grid, size_t smem, int device, int cluster, cudaStream_t s);
+// false when the driver refuses the launch (nothing ran)
+bool launch_chain(const ChainParams& p, int grid, size_t smem, int device, int cluster, cudaStream_t s);
 // One launch with no layers (the kernel sets up and leaves) on the default stream, waited for: false when the driver
 // refuses the geometry (cooperative launch of clusters) or the launch fails.
 bool try_launch_chain(const ChainParams& p, int grid, size_t smem, int device, int cluster);
