@@ -278,13 +278,25 @@ struct UmmaChainLayer {
   int y_zp = 0, lo = 0, hi = 255;
   int fma_exact = 0;  // every combined[ch] is 0 or within [2^-21, 2^40]: fma(acc, c, 1.5 * 2^23 + zp) is the exact requantisation for |acc| < 2^24
 };
+// Optional ends of a chain: `head_x` (f32 [rows][K of the first layer], 16-byte aligned) makes the first layer
+// quantise its own input, q = clamp(rint(x / scale) + zp, lo, hi), instead of reading 8-bit rows; `tail_out`
+// (f32 [rows][N of the last layer]) also receives (q - zp) * scale of the last layer's rows.
+struct UmmaChainEnds {
+  const float* head_x = nullptr;
+  float head_scale = 1.f, head_zp = 0.f, head_lo = 0.f, head_hi = 255.f;
+  float* tail_out = nullptr;
+  float tail_scale = 1.f, tail_zp = 0.f;
+  int tail_signed = 0;
+};
 struct UmmaChain;
-UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int rows, std::string* why);
+UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int rows, const UmmaChainEnds& ends, std::string* why);
 void umma_chain_destroy(UmmaChain* c);
 // After a launch that gave up: clears the arrival counters and the grid barrier's counter.
 void umma_chain_reset_after_error(UmmaChain* c);
 // false when the driver refused the cooperative launch (nothing ran): the caller runs the layers one by one
-bool umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s);
+// `head_x`: where the f32 rows of a quantising head are for this launch (a graph input's buffer may change from run
+// to run); ignored by a chain without one.
+bool umma_chain_launch(const UmmaChain* c, int* err_flag, const float* head_x, cudaStream_t s);
 const char* umma_chain_desc(const UmmaChain* c);
 
 // Packed weight size helpers for the tensor-core path: weights are laid out [OC][R*S*Cpad]

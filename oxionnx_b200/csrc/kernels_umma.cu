@@ -604,9 +604,10 @@ struct UmmaChain {
   ChainParams cp;
   int grid = 0, device = 0;
   size_t smem = 0;
+  void* w_tiles[CHAIN_MAX_LAYERS] = {nullptr, nullptr, nullptr, nullptr};  // the layers' weights in tile order, owned by the chain
   void* scratch = nullptr;  // partial sums of every unit, arrival counters (zero between launches), the grid barrier's counter
   size_t scratch_bytes = 0;
-  char desc[200];
+  char desc[288];
 };
 
 namespace {
@@ -670,7 +671,9 @@ bool chain_layout(UmmaChain* c, const UmmaChainLayer* layers, int n_layers, int 
 
 }  // namespace
 
-UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int rows, std::string* why) {
+void umma_chain_destroy(UmmaChain* c);
+
+UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int rows, const UmmaChainEnds& ends, std::string* why) {
   auto no = [&](const char* msg) -> UmmaChain* {
     if (why) *why = msg;
     return nullptr;
@@ -695,6 +698,15 @@ UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int row
   cp.n_layers = n_layers;
   cp.rows = rows;
   c->device = device;
+  if (ends.head_x && ((uintptr_t)ends.head_x & 15) == 0) {
+    cp.head_x = ends.head_x;
+    cp.head_k = layers[0].K;
+    cp.head_scale = ends.head_scale, cp.head_zp = ends.head_zp, cp.head_lo = ends.head_lo, cp.head_hi = ends.head_hi;
+  }
+  if (ends.tail_out) {
+    cp.tail_out = ends.tail_out;
+    cp.tail_scale = ends.tail_scale, cp.tail_zp = ends.tail_zp, cp.tail_signed = ends.tail_signed;
+  }
   // Clusters of 4, then 8, then 2 CTAs (partial sums meet in distributed shared memory); a cluster launch that
   // the driver refuses, or K blocks that do not divide, leave the L2 workspace form.
   const char* msg = "";
@@ -752,19 +764,26 @@ UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int row
     const UmmaChainLayer& L = layers[l];
     ChainLayerParams& P = cp.layer[l];
     cuuint32_t estr[2] = {1, 1};
-    cuuint64_t wdim[2] = {(cuuint64_t)L.K, (cuuint64_t)L.N}, wstr[1] = {(cuuint64_t)L.K};
-    cuuint32_t wbox[2] = {128, 128};
-    CUresult rc = g_encode_tiled(&P.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(L.w), wdim, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const size_t w_rows = (size_t)P.n_tiles * (L.K / 128) * 128;  // rows of 128 bytes
+    CUresult rc = CUDA_ERROR_OUT_OF_MEMORY;
+    if (cudaMalloc(&c->w_tiles[l], w_rows * 128) == cudaSuccess) {
+      chain_repack(L.w, c->w_tiles[l], L.N, L.K, nullptr);
+      if (cudaStreamSynchronize(nullptr) == cudaSuccess) {
+        cuuint64_t wdim[2] = {128, (cuuint64_t)w_rows}, wstr[1] = {128};
+        cuuint32_t wbox[2] = {128, 128};
+        rc = g_encode_tiled(&P.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, c->w_tiles[l], wdim, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      }
+    }
+    (void)cudaGetLastError();
     cuuint64_t xdim[2] = {(cuuint64_t)L.K, (cuuint64_t)rows}, xstr[1] = {(cuuint64_t)L.K};
     cuuint32_t xbox[2] = {128, (cuuint32_t)CHAIN_ROWS};
     if (rc == CUDA_SUCCESS)
       rc = g_encode_tiled(&P.tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(L.x), xdim, xstr, xbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) {
-      cudaFree(c->scratch);
-      delete c;
-      return no("tensor map rejected by the driver");
+      umma_chain_destroy(c);
+      return no("no memory for the repacked weights, or tensor map rejected by the driver");
     }
     // the weights are the 128-row operand (A), the activation rows the 64 columns (B)
     P.idesc = make_idesc(KIND_I8, L.w_dt == DT::I8, L.x_dt == DT::I8, CHAIN_ROWS, 128);
@@ -782,12 +801,15 @@ UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int row
   for (int l = 0; l < n_layers && n < (int)sizeof c->desc; ++l)
     n += snprintf(c->desc + n, sizeof c->desc - n, " %dx%d:%dt*%ds", layers[l].K, layers[l].N, cp.layer[l].n_tiles, cp.layer[l].splits);
   if (n < (int)sizeof c->desc)
-    snprintf(c->desc + n, sizeof c->desc - n, " grid=%d %s smem=%zuK", c->grid, cp.cluster > 1 ? "clusters (distributed shared memory)" : "slices through L2", c->smem / 1024);
+    snprintf(c->desc + n, sizeof c->desc - n, " grid=%d %s smem=%zuK%s%s", c->grid, cp.cluster > 1 ? "clusters (distributed shared memory)" : "slices through L2",
+             c->smem / 1024, cp.head_x ? " +quantize" : "", cp.tail_out ? " +dequantize" : "");
   return c;
 }
 
 void umma_chain_destroy(UmmaChain* c) {
   if (!c) return;
+  for (void* w : c->w_tiles)
+    if (w) cudaFree(w);
   if (c->scratch) cudaFree(c->scratch);
   delete c;
 }
@@ -795,9 +817,13 @@ void umma_chain_reset_after_error(UmmaChain* c) {
   if (c && c->scratch) (void)cudaMemset(c->scratch, 0, c->scratch_bytes);
 }
 const char* umma_chain_desc(const UmmaChain* c) { return c->desc; }
-bool umma_chain_launch(const UmmaChain* c, int* err_flag, cudaStream_t s) {
+bool umma_chain_launch(const UmmaChain* c, int* err_flag, const float* head_x, cudaStream_t s) {
   ChainParams cp = c->cp;
   cp.err_flag = err_flag;
+  if (cp.head_x) {
+    if (!head_x || ((uintptr_t)head_x & 15)) return false;
+    cp.head_x = head_x;
+  }
   return launch_chain(cp, c->grid, c->smem, c->device, cp.cluster, s);
 }
 

@@ -524,7 +524,7 @@ class Planner {
 
   void finalize_lifetimes_and_arena();
   struct ChainLink {
-    int step = -1, rows = 0;
+    int step = -1, rows = 0, x_vi = -1, out_vi = -1;
     k::UmmaChainLayer layer;
   };
   std::vector<ChainLink> chain_links_;
@@ -628,8 +628,46 @@ void Planner::link_chains() {
     if (j - i >= 2) {
       std::vector<k::UmmaChainLayer> layers;
       for (size_t t = i; t < j; ++t) layers.push_back(chain_links_[t].layer);
+      // A per-tensor QuantizeLinear right in front of the chain whose only reader is the first layer is done by
+      // that layer while it stages its activation blocks; a per-tensor DequantizeLinear right behind the chain is
+      // written by the last layer beside its 8-bit rows.  Both steps then launch nothing.  The f32 rows must
+      // outlive the quantising step, and the dequantised value must not share memory with what the last layer
+      // still reads (earlier layers' values are dead by then: a grid barrier lies in between).
+      k::UmmaChainEnds ends;
+      int head_step = -1, tail_step = -1;
+      const int first_step = chain_links_[i].step, last_step = chain_links_[j - 1].step;
+      auto overlaps = [&](const Value& a, const Value& b) {
+        const uint8_t *a0 = (const uint8_t*)a.ptr, *b0 = (const uint8_t*)b.ptr;
+        return a0 < b0 + std::max<size_t>(b.bytes, 1) && b0 < a0 + std::max<size_t>(a.bytes, 1);
+      };
+      if (!C.cfg().keep_intermediates) {
+        const Value& xv = V(chain_links_[i].x_vi);
+        if (xv.q_src >= 0 && xv.q_step == first_step - 1 && !graph_outputs_.count(xv.name)) {
+          auto it = consumers_.find(xv.name);
+          int root = xv.q_src;
+          while (V(root).alias_of >= 0) root = V(root).alias_of;
+          const Value& sv = V(xv.q_src);
+          const bool lives = V(root).external || V(root).is_graph_output || V(root).last_use >= first_step;
+          if (it != consumers_.end() && it->second.size() == 1 && lives && sv.dt == DT::F32 && (sv.shape.size() != 4 || order_free(sv)) &&
+              sv.numel() == (int64_t)chain_links_[i].rows * chain_links_[i].layer.K && ((uintptr_t)sv.ptr & 15) == 0) {
+            ends.head_x = (const float*)sv.ptr;
+            ends.head_scale = xv.q_scale, ends.head_zp = xv.q_zp, ends.head_lo = xv.q_lo, ends.head_hi = xv.q_hi;
+            head_step = xv.q_step;
+          }
+        }
+        const int last_out = chain_links_[j - 1].out_vi;
+        for (int vi = 0; vi < (int)S.values_.size() && tail_step < 0; ++vi) {
+          const Value& dv = V(vi);
+          if (dv.dq_src != last_out || dv.dq_step != last_step + 1 || dv.alias_of >= 0 || dv.dt != DT::F32) continue;
+          if ((dv.shape.size() == 4 && !order_free(dv)) || overlaps(dv, V(chain_links_[j - 1].x_vi)) || overlaps(dv, V(last_out))) continue;
+          ends.tail_out = (float*)dv.ptr;
+          ends.tail_scale = dv.dq_scale, ends.tail_zp = dv.dq_zp;
+          ends.tail_signed = V(last_out).dt == DT::I8 ? 1 : 0;
+          tail_step = dv.dq_step;
+        }
+      }
       std::string why;
-      k::UmmaChain* chain = k::umma_chain_create(layers.data(), (int)layers.size(), chain_links_[i].rows, &why);
+      k::UmmaChain* chain = k::umma_chain_create(layers.data(), (int)layers.size(), chain_links_[i].rows, ends, &why);
       if (chain) {
         S.umma_chains_.push_back(chain);
         Step& first = S.steps_[chain_links_[i].step];
@@ -638,11 +676,23 @@ void Planner::link_chains() {
         // the layers' own launches stay behind the chain: a cooperative launch the driver refuses (the grid cannot
         // be co-resident right now, e.g. under a profiler) turns the chain off for this session
         auto own = std::make_shared<std::vector<std::function<void(cudaStream_t)>>>();
+        if (head_step >= 0) own->push_back(S.steps_[head_step].launch);
         for (size_t t = i; t < j; ++t) own->push_back(S.steps_[chain_links_[t].step].launch);
+        if (tail_step >= 0) own->push_back(S.steps_[tail_step].launch);
+        for (int extra : {head_step, tail_step})
+          if (extra >= 0) {
+            S.steps_[extra].kernel = "umma_i8_chain (inside the launch of '" + first.node_name + "')";
+            S.steps_[extra].launch = [](cudaStream_t) {};
+          }
         auto off = std::make_shared<bool>(false);
-        first.launch = [this, chain, err, own, off](cudaStream_t s) {
-          if (!*off) {
-            if (k::umma_chain_launch(chain, err, s)) {
+        const int head_vi = ends.head_x ? V(chain_links_[i].x_vi).q_src : -1;
+        first.launch = [this, chain, err, own, off, head_vi](cudaStream_t s) {
+          // a cooperative kernel node makes a replayed CUDA graph several times slower than the separate kernels
+          // (measured: 232 us against 61 us per pass of the 64-row MLP), so a capture records the layers' own launches
+          cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+          if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess) (void)cudaGetLastError();
+          if (!*off && capturing == cudaStreamCaptureStatusNone) {
+            if (k::umma_chain_launch(chain, err, head_vi >= 0 ? (const float*)V(head_vi).ptr : nullptr, s)) {
               C.counters.umma_launches++;
               C.counters.kernel_launches++;
               return;
@@ -685,6 +735,15 @@ void Planner::finalize_lifetimes_and_arena() {
       root.last_use = std::max(root.last_use, std::max(v.last_use, v.is_graph_output ? n_steps : -1));
       if (v.is_graph_output) root.is_graph_output = true;
     }
+  }
+  // The dequantised copy of a few 8-bit rows may be written by the kernel that produces those rows, and that kernel
+  // may be launched up to three steps earlier (a chain of quantised linear layers, link_chains): its storage is
+  // reserved from there on, so that it never shares memory with what the chain still reads.
+  for (Value& v : S.values_) {
+    if (v.dq_src < 0 || v.dq_step < 0 || v.producer < 0) continue;
+    const Value& src = V(v.dq_src);
+    if (src.producer < 0 || src.shape.size() != 4 || src.shape[0] * src.shape[2] * src.shape[3] > 64) continue;
+    v.producer = std::max(0, std::min(v.producer, src.producer - 3));
   }
   struct Slot {
     size_t bytes;
@@ -1167,6 +1226,8 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
         ChainLink cl;
         cl.step = step_index;
         cl.rows = (int)cs.M();
+        cl.x_vi = x_vi;
+        cl.out_vi = out_vi;
         cl.layer.x = V(x_vi).ptr;
         cl.layer.x_dt = xdt;
         cl.layer.w = wdev;

@@ -1,6 +1,7 @@
 // The cooperative kernel that runs a whole chain of quantised linear layers over at most 64 rows (see
 // umma_chain.cuh for the scheme).  Every wait is bounded: a barrier that does not flip within WAIT_CYCLES makes
 // the CTA record an error code, stop issuing work and leave through the common teardown.
+#include <algorithm>
 #include <mutex>
 
 #include "umma_chain.cuh"
@@ -113,7 +114,11 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
     const int tile = cta / L.splits, slice = cta % L.splits;
     const uint32_t bar = smem_u32(&bar_w[l]);
     mbar_expect_tx(bar, (uint32_t)L.kb * CHAIN_W_TILE);
-    for (int i = 0; i < L.kb; ++i) tma_load_2d(base + L.w_off + (uint32_t)i * CHAIN_W_TILE, &L.tmW, bar, (slice * L.kb + i) * 128, tile * 128);
+    // the weights were repacked tile by tile: K block b of channel tile t is rows [(t * kblocks + b) * 128, +128) of a
+    // matrix of 128-byte rows, 16 KB contiguous in HBM
+    const int kblocks = L.kb * L.splits;
+    for (int i = 0; i < L.kb; ++i)
+      tma_load_2d(base + L.w_off + (uint32_t)i * CHAIN_W_TILE, &L.tmW, bar, 0, (tile * kblocks + slice * L.kb + i) * 128);
   };
   if (warp == 4 && lane == 0)
     for (int l = 0; l < p.n_layers; ++l)
@@ -138,10 +143,55 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
     const int ch = tile * 128 + c_in_tile;
     Requant rq;
     if (warp < 4 && active) rq.load(L, min(ch, L.N - 1));
+    // the last layer may also write the DequantizeLinear that follows it: (q - zp) * scale as f32 lanes
+    const bool tail = l + 1 == p.n_layers && p.tail_out != nullptr;
+    auto store_out = [&](int row, uint8_t q) {
+      L.out[(size_t)row * L.N + ch] = q;
+      if (tail) p.tail_out[(size_t)row * L.N + ch] = __fmul_rn(__fsub_rn(p.tail_signed ? (float)(int)(int8_t)q : (float)q, p.tail_zp), p.tail_scale);
+    };
+    // the first layer may quantise its own activation blocks from f32 rows (the QuantizeLinear in front of the
+    // chain): r = clamp(rint(x / scale) + zp), written in the 128-byte-swizzled K-major layout a TMA load would leave
+    const bool head = l == 0 && p.head_x != nullptr;
+    if (head && active) {
+      if (warp < 4) {
+        uint8_t* xs = smem_raw + (base - smem_u32(smem_raw)) + p.x_off;
+        // four 16-lane pieces per thread and pass: sixteen 16-byte loads in flight before the first is used
+        for (int c0 = (int)threadIdx.x; c0 < L.kb * 512; c0 += 512) {
+          float4 v[4][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + 128 * u, i = c >> 9, r = (c >> 3) & 63, j = c & 7;
+            const float4* src = reinterpret_cast<const float4*>(p.head_x + (size_t)r * p.head_k + (size_t)(slice * L.kb + i) * 128 + j * 16);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) v[u][g] = (c < L.kb * 512 && r < p.rows) ? __ldg(src + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + 128 * u, i = c >> 9, r = (c >> 3) & 63, j = c & 7;
+            if (c >= L.kb * 512) break;
+            uint32_t packed[4] = {0u, 0u, 0u, 0u};
+            if (r < p.rows) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const float f[4] = {v[u][g].x, v[u][g].y, v[u][g].z, v[u][g].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float q = fminf(fmaxf(__fadd_rn(rintf(__fdiv_rn(f[e], p.head_scale)), p.head_zp), p.head_lo), p.head_hi);
+                  packed[g] |= ((uint32_t)__float2int_rn(q) & 0xffu) << (8 * e);
+                }
+              }
+            }
+            *reinterpret_cast<uint4*>(xs + i * CHAIN_X_TILE + r * 128 + ((j ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the MMAs read these rows through the async proxy
+      }
+      asm volatile("bar.sync 2, 160;" ::: "memory");
+    }
     if (warp == 4) {
       // ---------------- loads and MMA issue ----------------
       if (active && !*abortp) {
-        if (lane == 0) {
+        if (lane == 0 && !head) {
           // the rows were written by other CTAs through the generic proxy before the grid barrier
           asm volatile("fence.proxy.async;" ::: "memory");
           const uint32_t bar = smem_u32(&bar_x);
@@ -150,8 +200,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
         }
         __syncwarp();
         bool got = mbar_wait(smem_u32(&bar_w[l]), 0u, abortp);
-        got = mbar_wait(smem_u32(&bar_x), x_phase, abortp) && got;
-        x_phase ^= 1u;
+        if (!head) {
+          got = mbar_wait(smem_u32(&bar_x), x_phase, abortp) && got;
+          x_phase ^= 1u;
+        }
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) fail(abortp, p.err_flag, 21);
         } else {
@@ -261,10 +313,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
           }
 #pragma unroll
           for (int r = 0; r < 32; ++r)
-            if (r < p.rows) L.out[(size_t)r * L.N + ch] = q0[r];
+            if (r < p.rows) store_out(r, q0[r]);
 #pragma unroll
           for (int r = 0; r < 32; ++r)
-            if (32 + r < p.rows) L.out[(size_t)(32 + r) * L.N + ch] = q1[r];
+            if (32 + r < p.rows) store_out(32 + r, q1[r]);
         }
       }
     }
@@ -304,7 +356,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
 #pragma unroll
           for (int r = 0; r < 32; ++r) {
             const int row = rg * rows_per + r;
-            if (r < rows_per && row < p.rows) L.out[(size_t)row * L.N + ch] = q[r];
+            if (r < rows_per && row < p.rows) store_out(row, q[r]);
           }
         }
       }
@@ -336,6 +388,26 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
   }
   __syncthreads();
   if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(CHAIN_ROWS) : "memory");
+}
+
+// [N][K] 8-bit weights -> [channel tile][K block][128 channels][128 bytes of K], channels beyond N zero: what one
+// TMA load of the chain kernel fetches is then 16 KB contiguous instead of 128 pieces a whole weight row apart
+// (cold from HBM, the strided form ran at a fraction of the copy bandwidth).
+__global__ void chain_repack_kernel(const uint4* __restrict__ w, uint4* __restrict__ out, int N, int K, int64_t total16) {
+  const int kblocks = K / 128;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total16; o += (int64_t)gridDim.x * blockDim.x) {
+    const int piece = (int)(o & 7), c = (int)((o >> 3) & 127);
+    const int64_t blk = o >> 10;
+    const int kb = (int)(blk % kblocks), tile = (int)(blk / kblocks);
+    const int ch = tile * 128 + c;
+    out[o] = ch < N ? w[((int64_t)ch * K + kb * 128) / 16 + piece] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+void chain_repack(const void* w, void* out, int N, int K, cudaStream_t s) {
+  const int64_t total16 = (int64_t)((N + 127) / 128) * 128 * K / 16;
+  const int64_t blocks = std::min<int64_t>((total16 + 255) / 256, 148 * 16);
+  chain_repack_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)w, (uint4*)out, N, K, total16);
 }
 
 namespace {

@@ -26,7 +26,7 @@ constexpr int CHAIN_X_TILE = CHAIN_ROWS * 128;  // bytes of one K block of the a
 constexpr int CHAIN_THREADS = 160;              // warps 0..3: accumulator lanes 32w..32w+31; warp 4: TMA and MMA issue
 
 struct alignas(64) ChainLayerParams {
-  CUtensorMap tmW;  // [N][K] 8-bit weights, box 128 bytes of K x 128 channels, 128-byte swizzle
+  CUtensorMap tmW;  // the weights repacked [channel tile][K block][128 channels][128 bytes of K], seen as rows of 128 bytes; box 128 x 128, 128-byte swizzle
   CUtensorMap tmX;  // [rows][K] 8-bit activations, box 128 bytes of K x 64 rows, 128-byte swizzle
   int N;
   int n_tiles, splits;  // unit u < n_tiles * splits is (channel tile u / splits, K slice u % splits)
@@ -48,11 +48,21 @@ struct alignas(64) ChainParams {
   int n_layers, rows;
   int cluster;  // > 1: the K slices of a channel tile are the CTAs of one cluster of this size (splits == cluster in every layer)
   uint32_t x_off;          // byte offset of the activation region (reused by every layer)
+  // optional ends: a QuantizeLinear in front of the first layer (f32 rows of head_k lanes) and a DequantizeLinear
+  // behind the last one (f32 [rows][N] beside the 8-bit rows)
+  const float* head_x;
+  int head_k;
+  float head_scale, head_zp, head_lo, head_hi;
+  float* tail_out;
+  float tail_scale, tail_zp;
+  int tail_signed;
   unsigned long long* grid_bar;  // arrivals at the grid-wide barrier since the scratch was cleared
   int* err_flag;
 };
 
 // false when the driver refuses the launch (nothing ran)
+// repacks [N][K] 8-bit weights (K a multiple of 128) into the tile order tmW describes; out holds ceil(N / 128) * 128 * K bytes
+void chain_repack(const void* w, void* out, int N, int K, cudaStream_t s);
 bool launch_chain(const ChainParams& p, int grid, size_t smem, int device, int cluster, cudaStream_t s);
 // One launch with no layers (the kernel sets up and leaves) on the default stream, waited for: false when the driver
 // refuses the geometry (cooperative launch of clusters) or the launch fails.

@@ -84,6 +84,14 @@ def test_int8_mlp_chain_kernel_matches_oracle_and_separate_kernels(rows, dims):
         f = {"x": feeds()["x"] * (1.0 + 0.5 * i)}
         want = oracle.run_graph(graph, weights, f)["y"]
         assert np.array_equal(replay.run(f)["y"], want), i
+    # without kept intermediates the QuantizeLinear in front of the chain and the DequantizeLinear behind it run inside it
+    steps = replay.steps()
+    fused = [s["kernel"] for s in steps if s["op"] in ("QuantizeLinear", "DequantizeLinear")]
+    assert len(fused) == 2 and fused[0].startswith("umma_i8_chain (inside"), [(s["op"], s["kernel"]) for s in steps]
+    chain_desc = [s["kernel"] for s in steps if s["kernel"].startswith("umma_i8_chain rows=")]
+    assert "+quantize" in chain_desc[0], chain_desc
+    if dims[-2] % 128 == 0:
+        assert fused[1].startswith("umma_i8_chain (inside") and "+dequantize" in chain_desc[-1], (fused, chain_desc)
     replay.close()
 
 
