@@ -780,6 +780,69 @@ __global__ void instance_norm_nhwc_kernel(const float* __restrict__ x, float* __
     }
 }
 
+// The same normalisation with the block's slab (all pixels x 32 channels) staged in shared memory by the first pass:
+// the tensor is read from HBM once instead of three times.  32 warps stride over the pixels, four loads in flight
+// each; the per-warp partial sums are added in warp order as above.
+__global__ void __launch_bounds__(1024) instance_norm_nhwc_smem_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 d, float eps,
+                                                                        const float* scale_nc, const float* shift_nc, int relu, int round_tf32_flag) {
+  extern __shared__ float slab[];  // [pixel][32 channels]
+  __shared__ float red[32][33];
+  const int64_t cgroups = (d.C + 31) / 32;
+  const int64_t n = blockIdx.x / cgroups, cg = blockIdx.x % cgroups;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c = cg * 32 + lane;
+  const bool valid = c < d.C;
+  const int hw = (int)(d.H * d.W);
+  const float* px = x + n * hw * d.C + c;
+  float* py = y + n * hw * d.C + c;
+  float sum = 0.f;
+  int i = warp;
+  for (; i + 96 < hw; i += 128) {
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = valid ? px[(int64_t)(i + 32 * k) * d.C] : 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      slab[(i + 32 * k) * 32 + lane] = v[k];
+      sum += v[k];
+    }
+  }
+  for (; i < hw; i += 32) {
+    const float v = valid ? px[(int64_t)i * d.C] : 0.f;
+    slab[i * 32 + lane] = v;
+    sum += v;
+  }
+  red[warp][lane] = sum;
+  __syncthreads();
+  float tot = 0.f;
+  for (int wv = 0; wv < 32; ++wv) tot += red[wv][lane];
+  const float mean = tot / (float)hw;
+  __syncthreads();
+  float vs = 0.f;
+  for (int j = warp; j < hw; j += 32) {
+    const float dv = slab[j * 32 + lane] - mean;
+    vs += dv * dv;
+  }
+  red[warp][lane] = vs;
+  __syncthreads();
+  tot = 0.f;
+  for (int wv = 0; wv < 32; ++wv) tot += red[wv][lane];
+  const float var = tot / (float)hw;
+  const float inv_std = 1.0f / sqrtf(var + eps);
+  float sc = 1.f, sf = 0.f;
+  const bool mod = scale_nc != nullptr || shift_nc != nullptr;
+  if (valid && scale_nc) sc = scale_nc[n * d.C + c];
+  if (valid && shift_nc) sf = shift_nc[n * d.C + c];
+  if (valid)
+    for (int j = warp; j < hw; j += 32) {
+      float v = (slab[j * 32 + lane] - mean) * inv_std;
+      if (mod) v = v * sc + sf;  // two roundings, as the separate Mul and Add nodes (this file is built without contraction)
+      if (relu) v = fmaxf(v, 0.f);
+      if (round_tf32_flag) v = round_tf32(v);
+      py[(int64_t)j * d.C] = v;
+    }
+}
+
 // ---- resize / pad / concat --------------------------------------------------------------
 __device__ __forceinline__ float src_coord(int coord, int64_t o, float scale, int64_t in_size, int64_t out_size) {
   switch (coord) {
@@ -1895,6 +1958,26 @@ void instance_norm(const TensorRef& x, const TensorRef& y, float eps, const floa
   int64_t cgroups = (x.d.C + 31) / 32;
   int64_t blocks = x.d.N * cgroups;
   if (blocks == 0) return;
+  const int64_t hw = x.d.H * x.d.W;
+  const size_t slab = (size_t)hw * 32 * sizeof(float);
+  if (hw >= 256 && slab <= 200 * 1024) {
+    // the opt-in for more than 48 KB of dynamic shared memory is a per-device property of the kernel
+    static std::mutex mu;
+    static size_t have[64] = {};
+    int dev = 0;
+    OXB_CUDA(cudaGetDevice(&dev));
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      size_t& h = have[dev >= 0 && dev < 64 ? dev : 0];
+      if (slab > h) {
+        OXB_CUDA(cudaFuncSetAttribute(instance_norm_nhwc_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)slab));
+        h = slab;
+      }
+    }
+    instance_norm_nhwc_smem_kernel<<<(unsigned)blocks, 1024, slab, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, eps, scale_nc, shift_nc, relu,
+                                                                        round_tf32_flag);
+    return;
+  }
   instance_norm_nhwc_kernel<<<(unsigned)blocks, 256, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, eps, scale_nc, shift_nc, relu, round_tf32_flag);
 }
 

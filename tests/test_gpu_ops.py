@@ -440,6 +440,11 @@ def test_glue_ops_match_oracle(ctx_auto):
     want, = oracle.run_node("OxiInstanceNorm", [x], {"epsilon": 1e-5})
     got = dispatch(ctx, "OxiInstanceNorm", [x], {"epsilon": 1e-5})[0]
     assert np.allclose(got, want, rtol=1e-4, atol=1e-5)
+    # planes of 256 positions or more are staged in shared memory by the first pass (one read of the tensor)
+    big = (rng.standard_normal((3, 40, 16, 20)) * 3 + 1.5).astype(np.float32)
+    want, = oracle.run_node("OxiInstanceNorm", [big], {"epsilon": 1e-5})
+    got = dispatch(ctx, "OxiInstanceNorm", [big], {"epsilon": 1e-5})[0]
+    assert np.allclose(got, want, rtol=1e-4, atol=1e-5)
     for attrs in ({"mode": "nearest", "coordinate_transformation_mode": "asymmetric", "nearest_mode": "floor"},
                   {"mode": "linear", "coordinate_transformation_mode": "half_pixel"},
                   {"mode": "linear", "coordinate_transformation_mode": "pytorch_half_pixel"}):
