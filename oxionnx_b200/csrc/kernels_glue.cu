@@ -893,16 +893,17 @@ __global__ void resize_nhwc_kernel(const float* __restrict__ x, float* __restric
 }
 
 // Four channels per thread (NHWC f32, C % 4 == 0): the same arithmetic per lane as the scalar kernel.
+template <typename I>  // index type: 32-bit divisions where the tensor allows them
 __global__ void resize_nhwc_vec4_kernel(const float4* __restrict__ x, float4* __restrict__ y, Dims4 xd, Dims4 yd, int mode, int coord, int rule,
                                         float sh, float sw, int64_t total4, int rtf32) {
-  const int64_t c4n = yd.C / 4;
-  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total4; o += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t c4 = o % c4n;
-    int64_t t = o / c4n;
-    const int64_t ox = t % yd.W;
-    t /= yd.W;
-    const int64_t oy = t % yd.H;
-    const int64_t n = t / yd.H;
+  const I c4n = (I)(yd.C / 4), yW = (I)yd.W, yH = (I)yd.H;
+  for (I o = (I)(blockIdx.x * (int64_t)blockDim.x + threadIdx.x); o < (I)total4; o += (I)((int64_t)gridDim.x * blockDim.x)) {
+    const I c4 = o % c4n;
+    I t = o / c4n;
+    const I ox = t % yW;
+    t /= yW;
+    const I oy = t % yH;
+    const int64_t n = t / yH;
     const float sy = src_coord(coord, oy, sh, xd.H, yd.H), sx = src_coord(coord, ox, sw, xd.W, yd.W);
     const float4* base = x + n * xd.H * xd.W * c4n + c4;
     if (mode == 0) {
@@ -956,15 +957,17 @@ __global__ void pad_kernel(const void* x, void* y, DT dt, Layout L, Dims4 xd, Di
 }
 
 // Spatial padding of an NHWC tensor in 16-byte pieces (any storage type whose pixel is a multiple of 16 bytes).
+template <typename I>  // index type: 32-bit divisions where the tensor allows them
 __global__ void pad_nhwc_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, Dims4 xd, Dims4 yd, int64_t vec_per_pixel, int mode, uint4 fill,
                                     int ph, int pw, int64_t total) {
-  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t v = o % vec_per_pixel;
-    int64_t t = o / vec_per_pixel;
-    const int64_t ow = t % yd.W;
-    t /= yd.W;
-    const int64_t oh = t % yd.H;
-    const int64_t n = t / yd.H;
+  const I vpp = (I)vec_per_pixel, yW = (I)yd.W, yH = (I)yd.H;
+  for (I o = (I)(blockIdx.x * (int64_t)blockDim.x + threadIdx.x); o < (I)total; o += (I)((int64_t)gridDim.x * blockDim.x)) {
+    const int64_t v = o % vpp;
+    I t = o / vpp;
+    const int64_t ow = t % yW;
+    t /= yW;
+    const int64_t oh = t % yH;
+    const int64_t n = t / yH;
     bool outside = false;
     const int64_t ih = pad_src(oh - ph, xd.H, mode, outside), iw = pad_src(ow - pw, xd.W, mode, outside);
     y[o] = outside ? fill : x[((n * xd.H + ih) * xd.W + iw) * vec_per_pixel + v];
@@ -1986,8 +1989,12 @@ void resize(const TensorRef& x, const TensorRef& y, int mode, int coord, int nea
   int64_t total = y.d.numel();
   if (total == 0) return;
   if (y.d.C % 4 == 0 && ((uintptr_t)x.ptr & 15) == 0 && ((uintptr_t)y.ptr & 15) == 0) {
-    resize_nhwc_vec4_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((const float4*)x.ptr, (float4*)y.ptr, x.d, y.d, mode, coord, nearest_rule, scale_h,
-                                                                    scale_w, total / 4, round_tf32_flag);
+    if (total / 4 + (int64_t)148 * 64 * kThreads < (int64_t)1 << 31)
+      resize_nhwc_vec4_kernel<uint32_t><<<grid_for(total / 4), kThreads, 0, s>>>((const float4*)x.ptr, (float4*)y.ptr, x.d, y.d, mode, coord, nearest_rule,
+                                                                                scale_h, scale_w, total / 4, round_tf32_flag);
+    else
+      resize_nhwc_vec4_kernel<int64_t><<<grid_for(total / 4), kThreads, 0, s>>>((const float4*)x.ptr, (float4*)y.ptr, x.d, y.d, mode, coord, nearest_rule,
+                                                                               scale_h, scale_w, total / 4, round_tf32_flag);
     return;
   }
   resize_nhwc_kernel<<<grid_for(total), kThreads, 0, s>>>((const float*)x.ptr, (float*)y.ptr, x.d, y.d, mode, coord, nearest_rule, scale_h,
@@ -2016,8 +2023,12 @@ void pad(const TensorRef& x, const TensorRef& y, int mode, float value, int pn, 
     }
     const int64_t vpp = (int64_t)(x.d.C * es / 16);
     const int64_t total_v = y.d.N * y.d.H * y.d.W * vpp;
-    pad_nhwc_vec_kernel<<<grid_for(total_v), kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, y.d, vpp, mode, make_uint4(word, word, word, word), ph,
-                                                              pw, total_v);
+    if (total_v + (int64_t)148 * 64 * kThreads < (int64_t)1 << 31)
+      pad_nhwc_vec_kernel<uint32_t><<<grid_for(total_v), kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, y.d, vpp, mode,
+                                                                          make_uint4(word, word, word, word), ph, pw, total_v);
+    else
+      pad_nhwc_vec_kernel<int64_t><<<grid_for(total_v), kThreads, 0, s>>>((const uint4*)x.ptr, (uint4*)y.ptr, x.d, y.d, vpp, mode,
+                                                                         make_uint4(word, word, word, word), ph, pw, total_v);
     return;
   }
   pad_kernel<<<grid_for(total), kThreads, 0, s>>>(x.ptr, y.ptr, x.dt, x.layout, x.d, y.d, mode, value, pn, pc, ph, pw, total);
