@@ -700,6 +700,7 @@ UmmaChain* umma_chain_create(const UmmaChainLayer* layers, int n_layers, int row
   c->device = device;
   if (ends.head_x && ((uintptr_t)ends.head_x & 15) == 0) {
     cp.head_x = ends.head_x;
+    cp.head_q = (uint8_t*)const_cast<void*>(layers[0].x);
     cp.head_k = layers[0].K;
     cp.head_scale = ends.head_scale, cp.head_zp = ends.head_zp, cp.head_lo = ends.head_lo, cp.head_hi = ends.head_hi;
   }

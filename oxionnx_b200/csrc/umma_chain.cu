@@ -131,6 +131,37 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
     bar_base = ld_acquire_gpu64(p.grid_bar);
     bar_base -= bar_base % gridDim.x;
   }
+  // A QuantizeLinear in front of the chain: the grid quantises the f32 rows once, 16 lanes per thread, into the
+  // first layer's 8-bit rows (q = clamp(rint(x / scale) + zp)), and meets at the grid barrier before anybody loads
+  // them; the weight loads issued above are in flight meanwhile.
+  unsigned int barriers_done = 0;
+  if (p.head_x != nullptr) {
+    if (warp < 4) {
+      const int64_t pieces = (int64_t)p.rows * p.head_k / 16;
+      for (int64_t i = (int64_t)cta * 128 + threadIdx.x; i < pieces; i += (int64_t)gridDim.x * 128) {
+        const float4* src = reinterpret_cast<const float4*>(p.head_x) + i * 4;
+        uint32_t packed[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const float4 v = __ldg(src + g);
+          const float f[4] = {v.x, v.y, v.z, v.w};
+          packed[g] = 0u;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float q = fminf(fmaxf(__fadd_rn(rintf(__fdiv_rn(f[e], p.head_scale)), p.head_zp), p.head_lo), p.head_hi);
+            packed[g] |= ((uint32_t)__float2int_rn(q) & 0xffu) << (8 * e);
+          }
+        }
+        reinterpret_cast<uint4*>(p.head_q)[i] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    }
+    __threadfence();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0 && !grid_barrier(p.grid_bar, bar_base + (unsigned long long)gridDim.x, abortp)) fail(abortp, p.err_flag, 25);
+    __syncthreads();
+    barriers_done = 1;
+  }
   uint32_t x_phase = 0, mma_phase = 0;  // parities of bar_x / bar_mma for this CTA's next active layer
   for (int l = 0; l < p.n_layers; ++l) {
     const ChainLayerParams& L = p.layer[l];
@@ -149,49 +180,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
       L.out[(size_t)row * L.N + ch] = q;
       if (tail) p.tail_out[(size_t)row * L.N + ch] = __fmul_rn(__fsub_rn(p.tail_signed ? (float)(int)(int8_t)q : (float)q, p.tail_zp), p.tail_scale);
     };
-    // the first layer may quantise its own activation blocks from f32 rows (the QuantizeLinear in front of the
-    // chain): r = clamp(rint(x / scale) + zp), written in the 128-byte-swizzled K-major layout a TMA load would leave
-    const bool head = l == 0 && p.head_x != nullptr;
-    if (head && active) {
-      if (warp < 4) {
-        uint8_t* xs = smem_raw + (base - smem_u32(smem_raw)) + p.x_off;
-        // four 16-lane pieces per thread and pass: sixteen 16-byte loads in flight before the first is used
-        for (int c0 = (int)threadIdx.x; c0 < L.kb * 512; c0 += 512) {
-          float4 v[4][4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = c0 + 128 * u, i = c >> 9, r = (c >> 3) & 63, j = c & 7;
-            const float4* src = reinterpret_cast<const float4*>(p.head_x + (size_t)r * p.head_k + (size_t)(slice * L.kb + i) * 128 + j * 16);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) v[u][g] = (c < L.kb * 512 && r < p.rows) ? __ldg(src + g) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = c0 + 128 * u, i = c >> 9, r = (c >> 3) & 63, j = c & 7;
-            if (c >= L.kb * 512) break;
-            uint32_t packed[4] = {0u, 0u, 0u, 0u};
-            if (r < p.rows) {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                const float f[4] = {v[u][g].x, v[u][g].y, v[u][g].z, v[u][g].w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float q = fminf(fmaxf(__fadd_rn(rintf(__fdiv_rn(f[e], p.head_scale)), p.head_zp), p.head_lo), p.head_hi);
-                  packed[g] |= ((uint32_t)__float2int_rn(q) & 0xffu) << (8 * e);
-                }
-              }
-            }
-            *reinterpret_cast<uint4*>(xs + i * CHAIN_X_TILE + r * 128 + ((j ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          }
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the MMAs read these rows through the async proxy
-      }
-      asm volatile("bar.sync 2, 160;" ::: "memory");
-    }
     if (warp == 4) {
       // ---------------- loads and MMA issue ----------------
       if (active && !*abortp) {
-        if (lane == 0 && !head) {
+        if (lane == 0) {
           // the rows were written by other CTAs through the generic proxy before the grid barrier
           asm volatile("fence.proxy.async;" ::: "memory");
           const uint32_t bar = smem_u32(&bar_x);
@@ -200,10 +192,8 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
         }
         __syncwarp();
         bool got = mbar_wait(smem_u32(&bar_w[l]), 0u, abortp);
-        if (!head) {
-          got = mbar_wait(smem_u32(&bar_x), x_phase, abortp) && got;
-          x_phase ^= 1u;
-        }
+        got = mbar_wait(smem_u32(&bar_x), x_phase, abortp) && got;
+        x_phase ^= 1u;
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) fail(abortp, p.err_flag, 21);
         } else {
@@ -360,7 +350,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
           }
         }
       }
-      cluster_sync_all();
+      // Peers may still be reading this CTA's partial sums.  Between layers the grid barrier below covers that (a
+      // peer arrives there only after its reads, and nothing overwrites the partial sums before it); the last
+      // layer has no grid barrier, and the CTA's shared memory must outlive the peers' reads.
+      if (l + 1 == p.n_layers) cluster_sync_all();
     }
     if (l + 1 < p.n_layers) {
       // every CTA's rows of this layer are visible (also to the TMA unit) before anybody loads the next layer's
@@ -369,7 +362,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) umma_chain_kernel(const __gr
       tc_fence_before();
       __syncthreads();
       if (threadIdx.x == 0 && !*abortp) {
-        if (!grid_barrier(p.grid_bar, bar_base + (unsigned long long)(l + 1) * gridDim.x, abortp)) fail(abortp, p.err_flag, 24);
+        if (!grid_barrier(p.grid_bar, bar_base + (unsigned long long)(barriers_done + l + 1) * gridDim.x, abortp)) fail(abortp, p.err_flag, 24);
       }
       __syncthreads();
       tc_fence_after();

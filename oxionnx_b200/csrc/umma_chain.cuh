@@ -51,6 +51,7 @@ struct alignas(64) ChainParams {
   // optional ends: a QuantizeLinear in front of the first layer (f32 rows of head_k lanes) and a DequantizeLinear
   // behind the last one (f32 [rows][N] beside the 8-bit rows)
   const float* head_x;
+  uint8_t* head_q;  // the first layer's 8-bit rows, [rows][head_k]
   int head_k;
   float head_scale, head_zp, head_lo, head_hi;
   float* tail_out;
