@@ -1422,6 +1422,42 @@ __global__ void transpose_tiled_kernel(const uint32_t* __restrict__ x, uint32_t*
   }
 }
 
+// The same transposition for inner extents that are multiples of four on both sides: a block moves a tile of
+// 32 output rows (the input's contiguous axis) x 128 output columns with 16-byte loads along the input rows and
+// 16-byte stores along the output rows.
+__global__ void transpose_tiled_vec4_kernel(const float* __restrict__ x, float* __restrict__ y, Dims4 yd, Dims4 xs, int64_t blocks) {
+  __shared__ float tile[128][33];  // [output column][output row]
+  const int64_t th = (yd.H + 31) / 32, tw = (yd.W + 127) / 128;
+  for (int64_t b = blockIdx.x; b < blocks; b += gridDim.x) {
+    int64_t t = b;
+    const int64_t w0 = (t % tw) * 128;
+    t /= tw;
+    const int64_t h0 = (t % th) * 32;
+    t /= th;
+    const int64_t i1 = t % yd.C, i0 = t / yd.C;
+    const float* src = x + i0 * xs.N + i1 * xs.C;
+    float* dst = y + (i0 * yd.C + i1) * yd.H * yd.W;
+    // loads: 8 threads cover the 32 contiguous input lanes (output rows h0..h0+31) of one output column
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int col = (int)(threadIdx.x >> 3) + 32 * k, h4 = (int)(threadIdx.x & 7) * 4;
+      if (w0 + col < yd.W && h0 + h4 < yd.H) {
+        const float4 v = *reinterpret_cast<const float4*>(src + (w0 + col) * xs.W + h0 + h4);
+        tile[col][h4] = v.x, tile[col][h4 + 1] = v.y, tile[col][h4 + 2] = v.z, tile[col][h4 + 3] = v.w;
+      }
+    }
+    __syncthreads();
+    // stores: 32 threads cover the 128 contiguous output columns of one output row
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int row = (int)(threadIdx.x >> 5) + 8 * k, c4 = (int)(threadIdx.x & 31) * 4;
+      if (h0 + row < yd.H && w0 + c4 < yd.W)
+        *reinterpret_cast<float4*>(dst + (h0 + row) * yd.W + w0 + c4) = make_float4(tile[c4][row], tile[c4 + 1][row], tile[c4 + 2][row], tile[c4 + 3][row]);
+    }
+    __syncthreads();
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -1564,14 +1600,29 @@ __global__ void layer_norm_rows_reg_kernel(const float4* __restrict__ x, float4*
       y[r * (32 * NV4) + 32 * j + lane] = make_float4(o[0], o[1], o[2], o[3]);
     }
   }
-  if (minmax_keys) {  // uniform across the grid
+  if (minmax_keys) {  // uniform across the grid; one pair of atomics per block
     for (int off = 16; off > 0; off >>= 1) {
       mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     }
+    __shared__ float smn[kThreads / 32], smx[kThreads / 32];
+    const int warp = threadIdx.x >> 5;
     if (lane == 0) {
-      if (mn != INFINITY) atomicMin(&minmax_keys[0], float_key(mn));
-      if (mx != -INFINITY) atomicMax(&minmax_keys[1], float_key(mx));
+      smn[warp] = mn;
+      smx[warp] = mx;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      mn = lane < kThreads / 32 ? smn[lane] : INFINITY;
+      mx = lane < kThreads / 32 ? smx[lane] : -INFINITY;
+      for (int off = 4; off > 0; off >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      }
+      if (lane == 0) {
+        if (mn != INFINITY) atomicMin(&minmax_keys[0], float_key(mn));
+        if (mx != -INFINITY) atomicMax(&minmax_keys[1], float_key(mx));
+      }
     }
   }
 }
@@ -2054,6 +2105,12 @@ void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstrid
     const uint32_t total4 = (uint32_t)(total / 4);
     transpose_perm_vec4_kernel<<<grid_for(total4), kThreads, 0, s>>>((const uint4*)x, (uint4*)y, (uint32_t)yd.C, (uint32_t)yd.H, (uint32_t)(yd.W / 4),
                                                                      (uint32_t)(xstride.N / 4), (uint32_t)(xstride.C / 4), (uint32_t)(xstride.H / 4), total4);
+    return;
+  }
+  if (xstride.H == 1 && xstride.W != 1 && yd.H % 4 == 0 && yd.W % 4 == 0 && yd.H >= 8 && yd.W >= 32 && xstride.W % 4 == 0 && xstride.N % 4 == 0 &&
+      xstride.C % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0) {
+    const int64_t blocks = yd.N * yd.C * ((yd.H + 31) / 32) * ((yd.W + 127) / 128);
+    transpose_tiled_vec4_kernel<<<(unsigned)std::min<int64_t>(blocks, 148 * 64), 256, 0, s>>>((const float*)x, (float*)y, yd, xstride, blocks);
     return;
   }
   if (xstride.H == 1 && xstride.W != 1 && yd.H >= 8 && yd.W >= 8) {

@@ -524,7 +524,9 @@ def test_transformer_glue_ops_match_oracle(ctx_auto):
     assert own.cache_counters()["failures"] == 1
     own.close()
     t4 = rng.standard_normal((2, 37, 12, 64)).astype(np.float32)
-    for ins, attrs in (([t4], {"perm": [0, 2, 1, 3]}), ([t4], {"perm": [0, 2, 3, 1]}), ([t4[0, :, 0]], {}), ([t4], {"perm": [0, 1, 2, 3]})):
+    t5 = rng.standard_normal((2, 128, 3, 64)).astype(np.float32)  # extents in multiples of four: the 16-byte tiled form
+    for ins, attrs in (([t4], {"perm": [0, 2, 1, 3]}), ([t4], {"perm": [0, 2, 3, 1]}), ([t4[0, :, 0]], {}), ([t4], {"perm": [0, 1, 2, 3]}),
+                       ([t5], {"perm": [0, 2, 3, 1]}), ([t5[:, :40]], {"perm": [0, 2, 3, 1]}), ([t5[0, :, 0, :36]], {})):
         want, = oracle.run_node("Transpose", ins, attrs)
         got = dispatch(ctx, "Transpose", ins, attrs)
         assert got is not None, (attrs, ctx.last_error())
