@@ -1305,6 +1305,44 @@ __global__ void s2d_window_pack_nchw_f32_kernel(const float* __restrict__ src, D
   }
 }
 
+// The same packing for an 8-bit NCHW source (a graph input declared uint8 / int8) into an 8-bit destination: the
+// two horizontally adjacent pixels of a 2x2 block are one 2-byte load, consecutive threads read consecutive blocks.
+template <int C, bool SIGNED>
+__global__ void s2d_window_pack_nchw_q8_kernel(const uint8_t* __restrict__ src, Dims4 d, void* dst, DT ddt, int pad_left, int wp, int sub, int64_t total,
+                                               int pair_top, int rows_phys) {
+  const int64_t H2 = d.H / 2, W2 = d.W / 2;
+  const int64_t rows = pair_top >= 0 ? rows_phys + 1 : H2;
+  const int lo = ddt == DT::U8 ? 0 : -128, hi = ddt == DT::U8 ? 255 : 127;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t xw = o % wp;
+    int64_t t = o / wp;
+    const int64_t jp = t % rows;
+    const int64_t y = pair_top >= 0 ? jp - pair_top : jp;
+    const int64_t n = t / rows;
+    const int64_t x2 = xw - pad_left;
+    int v[16];
+#pragma unroll
+    for (int cp = 0; cp < 16; ++cp) v[cp] = 0;
+    if (x2 >= 0 && x2 < W2 && y >= 0 && y < H2) {
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const uint8_t* plane = src + ((n * C + c) * d.H + 2 * y) * d.W + 2 * x2;
+        const uint32_t top = __ldg(reinterpret_cast<const uint16_t*>(plane));
+        const uint32_t bot = __ldg(reinterpret_cast<const uint16_t*>(plane + d.W));
+        const uint32_t b[4] = {top & 0xffu, top >> 8, bot & 0xffu, bot >> 8};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k * C + c] = min(max((SIGNED ? (int)(int8_t)b[k] : (int)b[k]) - sub, lo), hi);
+      }
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      w[j] = ((uint32_t)v[4 * j] & 0xffu) | (((uint32_t)v[4 * j + 1] & 0xffu) << 8) | (((uint32_t)v[4 * j + 2] & 0xffu) << 16) | (((uint32_t)v[4 * j + 3] & 0xffu) << 24);
+    if (pair_top >= 0) s2d_store_pair(dst, make_uint4(w[0], w[1], w[2], w[3]), n, jp, xw, rows_phys, wp);
+    else ((uint4*)dst)[o] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // y = x[start0 : start0 + Y0, start1 : ..., ...] over up to four logical (row-major) axes, unit steps.
 __global__ void slice_kernel(const void* x, void* y, int es, Dims4 xd, Dims4 yd, Dims4 start, int64_t total) {
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
@@ -1850,6 +1888,22 @@ void s2d_window_pack(const TensorRef& src, void* dst, DT dst_dt, int pad_left, i
       case 3: s2d_window_pack_nchw_f32_kernel<3><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total, pair_top, rows_phys); break;
       default: s2d_window_pack_nchw_f32_kernel<4><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, q, rcp, safe, total, pair_top, rows_phys); break;
     }
+    return;
+  }
+  if ((src.dt == DT::U8 || src.dt == DT::I8) && (dst_dt == DT::U8 || dst_dt == DT::I8) && src.layout == Layout::PLAIN && src.d.W % 2 == 0 &&
+      ((uintptr_t)src.ptr & 1) == 0 && src.d.C >= 1 && src.d.C <= 4 && !q.quantize) {
+    const int g = grid_for(total);
+    const uint8_t* x = (const uint8_t*)src.ptr;
+#define OXB_Q8_PACK(CC)                                                                                                                          \
+  if (src.dt == DT::I8) s2d_window_pack_nchw_q8_kernel<CC, true><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, total, pair_top, rows_phys); \
+  else s2d_window_pack_nchw_q8_kernel<CC, false><<<g, kThreads, 0, s>>>(x, src.d, dst, dst_dt, pad_left, wp, sub, total, pair_top, rows_phys);
+    switch ((int)src.d.C) {
+      case 1: OXB_Q8_PACK(1) break;
+      case 2: OXB_Q8_PACK(2) break;
+      case 3: OXB_Q8_PACK(3) break;
+      default: OXB_Q8_PACK(4) break;
+    }
+#undef OXB_Q8_PACK
     return;
   }
   s2d_window_pack_kernel<<<grid_for(total), kThreads, 0, s>>>(src.ptr, src.dt, src.layout, src.d, dst, dst_dt, pad_left, wp, sub, q, total, pair_top, rows_phys);
