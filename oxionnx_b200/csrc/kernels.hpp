@@ -204,6 +204,9 @@ struct Epilogue {
   const float* dq_bias = nullptr;         // [OC], padded
   int dq_act = 0;
   DT out_dt = DT::F32;
+  // tensor-core kernel, f32 outputs: two ordered u32 keys into which the kernel merges the extrema of what it writes
+  // (the scratch of a DynamicQuantizeLinear that reads the output next), or null
+  unsigned int* minmax_keys = nullptr;
 };
 
 // Direct CUDA-core convolution (and matmul as a 1x1 convolution): general geometry
@@ -231,6 +234,7 @@ struct BatchedGemm {
   int a_rb = 0, a_rh = 0, a_ch = 0, b_rb = 0, b_rh = 0, b_ch = 0, o_rb = 0, o_rh = 0, o_ch = 0;
   const float* zero_bias = nullptr;  // at least align_up(N, 256) zeros
   int round_tf32 = 0;
+  unsigned int* minmax_keys = nullptr;  // as Epilogue::minmax_keys
 };
 struct UmmaPlan;
 UmmaPlan* umma_plan_create_batched(const BatchedGemm& g, std::string* why);

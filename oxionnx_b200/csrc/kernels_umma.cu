@@ -458,6 +458,7 @@ UmmaPlan* umma_plan_create(const void* x, DT x_dt, const void* w_packed, DT w_dt
   kp.hi = e.hi;
   kp.out_dt = (int)e.out_dt;
   kp.out = out;
+  kp.minmax_keys = e.out_dt == DT::F32 ? e.minmax_keys : nullptr;
   kp.err_flag = nullptr;
   pl->bn = bn;
   pl->kind = kind;
@@ -577,6 +578,7 @@ UmmaPlan* umma_plan_create_batched(const BatchedGemm& g, std::string* why) {
   kp.round_tf32 = g.round_tf32;
   kp.out_dt = (int)DT::F32;
   kp.out = g.out;
+  kp.minmax_keys = g.minmax_keys;
   pl->bn = bn;
   pl->kind = KIND_TF32;
   pl->pair = 0;

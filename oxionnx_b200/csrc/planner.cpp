@@ -996,8 +996,11 @@ void Planner::plan_dynamic_quantize(const NodeDef& n) {
   // A LayerNormalization that writes x can take x's extrema while it writes (one pass over the tensor saved):
   // it merges them into this node's keys, which the apply pass resets for the next run as always.
   bool have_minmax = false;
+  // So can a tensor-core contraction that writes x as f32 lanes (its steps are still named "umma" here; the plan
+  // is built when the arena is laid out and reads the value's keys then).
   if (!C.cfg().keep_intermediates && V(xi).alias_of < 0 && V(xi).producer >= 0 && V(xi).producer < (int)S.steps_.size() &&
-      S.steps_[V(xi).producer].kernel == "layer_norm_rows" && V(xi).minmax_keys == nullptr) {
+      (S.steps_[V(xi).producer].kernel == "layer_norm_rows" || (S.steps_[V(xi).producer].kernel == "umma" && S.steps_[V(xi).producer].family == 0)) &&
+      V(xi).minmax_keys == nullptr) {
     V(xi).minmax_keys = scratch;
     have_minmax = true;
   }
@@ -1209,6 +1212,7 @@ void Planner::emit_contraction(const NodeDef& n, Contraction& c) {
       if (xzp_vi >= 0) e.x_zp_dev = (const float*)V(xzp_vi).ptr;
       if (res_vi >= 0) e.residual = (const float*)V(res_vi).ptr;
       if (dq_vi >= 0) e.dq_x_scale_dev = (const float*)V(dq_vi).ptr;
+      e.minmax_keys = (unsigned int*)V(out_vi).minmax_keys;
       std::string why2;
       k::UmmaTuning tune;
       tune.requant_f64 = C.cfg().requant_f64;
@@ -2784,6 +2788,7 @@ bool Planner::try_plan_attention_product(const NodeDef& n, int ai, int bi) {
     gg.a = V(ra).ptr;
     gg.b = V(rb).ptr;
     gg.out = V(out_vi).ptr;
+    gg.minmax_keys = (unsigned int*)V(out_vi).minmax_keys;
     std::string why2;
     k::UmmaPlan* plan = k::umma_plan_create_batched(gg, &why2);
     if (!plan) OXB_FAIL("MatMul '%s': batched tensor-core plan rejected: %s", n.name.c_str(), why2.c_str());

@@ -114,6 +114,9 @@ struct alignas(64) KParams {
   int y_zp, lo, hi;
   int out_dt;
   void* out;
+  // f32 outputs only, or null: two ordered keys (see float_order_key) into which the kernel merges the minimum and
+  // the maximum of everything it writes, for a DynamicQuantizeLinear that reads the output next
+  unsigned int* minmax_keys;
   int* err_flag;
 };
 
@@ -299,6 +302,12 @@ __device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                :);
+}
+
+// Monotone map from f32 to u32: integer atomicMin / atomicMax on the keys give the exact float extrema.
+__device__ __forceinline__ uint32_t float_order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
 // ---- fused epilogue math ------------------------------------------------------------------
@@ -782,6 +791,9 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
   const uint32_t stage_xor = ((uint32_t)(lane * pitch) >> 7) & (uint32_t)(pitch / 16 - 1);
   uint32_t local = 0;
   const bool plain = !p.batched && p.splits == 1;
+  // extrema of the f32 lanes this thread writes, when a DynamicQuantizeLinear reads the output next
+  const bool track = p.minmax_keys != nullptr && esz == 4 && (VARIANT < V_REQUANT || VARIANT >= V_DEQUANT);
+  float seen_min = INFINITY, seen_max = -INFINITY;
   TileWalk walk(tile0, tile_step, p.n_tiles);
   for (int t = tile0; t < total_tiles; t += tile_step, ++local, walk.next()) {
     if (ES::NG > 1 && (int)(local % ES::NG) != group) continue;
@@ -824,6 +836,15 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     auto math = [&](const uint32_t(&v)[32], int ch) {
       const float* res = (VARIANT >= V_F32_RES && VARIANT < V_REQUANT && row_ok) ? p.residual + (size_t)m * p.OC + oc0 + ch * 32 : nullptr;
       epilogue_chunk<KIND, VARIANT>(p, v, xz, oc0 + ch * 32, esz, res, w);
+      if (track && row_ok) {
+        const int valid = p.OC - (oc0 + ch * 32);  // lanes of a ragged last run hold no output
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < valid) {
+            seen_min = fminf(seen_min, __uint_as_float(w[j]));
+            seen_max = fmaxf(seen_max, __uint_as_float(w[j]));
+          }
+      }
     };
     auto store = [&](int ch) {
       if (p.out_tma) {
@@ -916,6 +937,17 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
     }
   }
   if (p.out_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (track) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      seen_min = fminf(seen_min, __shfl_xor_sync(0xffffffffu, seen_min, off));
+      seen_max = fmaxf(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, off));
+    }
+    if (lane == 0) {
+      if (seen_min != INFINITY) atomicMin(p.minmax_keys, float_order_key(seen_min));
+      if (seen_max != -INFINITY) atomicMax(p.minmax_keys + 1, float_order_key(seen_max));
+    }
+  }
 }
 
 // ---- the kernel ---------------------------------------------------------------------------
