@@ -115,6 +115,45 @@ def test_int8_mlp_chain_accumulators_beyond_24_bits_take_the_f64_requantisation(
     sess.close()
 
 
+@pytest.mark.parametrize("rows,k,n,gelu", [(200, 256, 200, True), (128, 128, 96, False), (37, 384, 1000, True)])
+def test_contraction_hands_its_extrema_to_the_next_dynamic_quantize_linear(rows, k, n, gelu):
+    """A tensor-core contraction that writes f32 lanes merges their minimum and maximum into the keys of the
+    DynamicQuantizeLinear that reads them, which then skips its own first pass.  Row counts that are not a multiple
+    of the 128-row tile and channel counts that are not a multiple of the 32-channel run must not leak padding
+    lanes into the extrema: scale, zero point and every quantised lane equal those of a session that keeps its
+    intermediates (where nothing is handed over) and the oracle's."""
+    from oxionnx_b200.graph import Graph, Node
+    rng = np.random.default_rng(977 + rows)
+    w = {"w": np.clip(np.rint(rng.standard_normal((k, n)) * 40.0), -127, 127).astype(np.float32),
+         "ws": rng.uniform(0.0005, 0.002, n).astype(np.float32), "bias": (rng.standard_normal(n) * 0.5 + 0.8).astype(np.float32)}
+    nodes = [Node("DynamicQuantizeLinear", "q0", ["x"], ["xq", "xs", "xz"], {}),
+             Node("MatMulInteger", "mmi", ["xq", "w", "xz"], ["acc"], {}), Node("Cast", "cast", ["acc"], ["accf"], {"to": 1}),
+             Node("Mul", "scales", ["xs", "ws"], ["sc"], {}), Node("Mul", "rescale", ["accf", "sc"], ["scaled"], {}),
+             Node("Add", "addb", ["scaled", "bias"], ["lin"], {})]
+    last = "lin"
+    if gelu:
+        nodes.append(Node("Gelu", "act", ["lin"], ["act_out"], {}))
+        last = "act_out"
+    nodes.append(Node("DynamicQuantizeLinear", "q1", [last], ["yq", "ys", "yz"], {}))
+    graph = Graph(nodes=nodes, input_names=["x"], output_names=["yq", "ys", "yz"])
+    feeds = {"x": (rng.standard_normal((rows, k)) * 2 + 0.3).astype(np.float32)}
+    handed = Session.builder().build_from_graph(graph, w)
+    got = handed.run(feeds)
+    kernels = {s["node"]: s["kernel"] for s in handed.steps()}
+    assert "extrema from the producer" in kernels["q1"], kernels
+    handed.close()
+    kept = Session.builder().with_keep_intermediates(True).build_from_graph(graph, w)
+    want = kept.run(feeds)
+    assert "extrema from the producer" not in {s["node"]: s["kernel"] for s in kept.steps()}["q1"]
+    kept.close()
+    ref = oracle.run_graph(graph, w, feeds)
+    for name in ("ys", "yz", "yq"):
+        assert np.array_equal(np.ravel(got[name]), np.ravel(want[name])), name
+    assert float(np.ravel(got["yz"])[0]) == float(np.ravel(ref["yz"])[0])
+    assert np.isclose(float(np.ravel(got["ys"])[0]), float(np.ravel(ref["ys"])[0]), rtol=1e-6)
+    assert np.max(np.abs(got["yq"].astype(np.int32) - ref["yq"].astype(np.int32))) <= 1  # the oracle's Gelu may differ in the last place
+
+
 def test_resnet_f32_small_per_node_and_final():
     graph, weights, feeds, _ = models.build_resnet50_f32(batch=3, image=64, base=16, classes=40)
     sess, out, ref = run_both(graph, weights, feeds(3))
