@@ -838,12 +838,26 @@ __device__ __forceinline__ void epilogue_role(const KParams& p, int warp, int la
       epilogue_chunk<KIND, VARIANT>(p, v, xz, oc0 + ch * 32, esz, res, w);
       if (track && row_ok) {
         const int valid = p.OC - (oc0 + ch * 32);  // lanes of a ragged last run hold no output
+        if (valid >= 32) {
+          // two independent chains per bound, so that the 64 comparisons are not one dependent sequence
+          float lo2 = __uint_as_float(w[0]), hi2 = lo2;
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < valid) {
+          for (int j = 0; j < 32; j += 2) {
             seen_min = fminf(seen_min, __uint_as_float(w[j]));
             seen_max = fmaxf(seen_max, __uint_as_float(w[j]));
+            lo2 = fminf(lo2, __uint_as_float(w[j + 1]));
+            hi2 = fmaxf(hi2, __uint_as_float(w[j + 1]));
           }
+          seen_min = fminf(seen_min, lo2);
+          seen_max = fmaxf(seen_max, hi2);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) {
+              seen_min = fminf(seen_min, __uint_as_float(w[j]));
+              seen_max = fmaxf(seen_max, __uint_as_float(w[j]));
+            }
+        }
       }
     };
     auto store = [&](int ch) {
