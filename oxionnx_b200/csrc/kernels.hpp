@@ -121,7 +121,9 @@ void transpose_perm(const void* x, void* y, const Dims4& yd, const Dims4& xstrid
 // softmax_rows optionally applies x * scale[0] and + mask[row / rows_per_mask][:] first (fused Mul / Add producers).
 void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* mask, int64_t rows_per_mask, int round_tf32,
                   cudaStream_t s);
-void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s, unsigned int* minmax_keys = nullptr);
+// `x2`, when given, is added to `x` lane by lane first (the residual Add in front of the normalisation).
+void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s,
+                     unsigned int* minmax_keys = nullptr, const float* x2 = nullptr);
 // Slice with unit steps over logical (row-major) axes padded to four: y[i] = x[i + start], dims as (N, C, H, W).
 void slice_rows(const void* x, void* y, DT dt, const Dims4& xd, const Dims4& yd, const Dims4& start, cudaStream_t s);
 

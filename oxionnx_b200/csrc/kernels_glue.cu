@@ -1596,8 +1596,8 @@ __global__ void softmax_rows_reg_kernel(const float4* __restrict__ x, float4* __
 
 // LayerNormalization for rows of 128 * NV4 lanes, the row kept in registers (read once, in 16-byte pieces).
 template <int NV4>
-__global__ void layer_norm_rows_reg_kernel(const float4* __restrict__ x, float4* __restrict__ y, int64_t rows, const float4* __restrict__ scale,
-                                           const float4* __restrict__ bias, float eps, uint32_t* minmax_keys) {
+__global__ void layer_norm_rows_reg_kernel(const float4* __restrict__ x, const float4* __restrict__ x2, float4* __restrict__ y, int64_t rows,
+                                           const float4* __restrict__ scale, const float4* __restrict__ bias, float eps, uint32_t* minmax_keys) {
   const int lane = threadIdx.x & 31;
   const float n = (float)(128 * NV4);
   float mn = INFINITY, mx = -INFINITY;
@@ -1608,7 +1608,11 @@ __global__ void layer_norm_rows_reg_kernel(const float4* __restrict__ x, float4*
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < NV4; ++j) {
-      const float4 t = px[32 * j + lane];
+      float4 t = px[32 * j + lane];
+      if (x2) {  // the Add in front of the normalisation: one rounded sum per lane, as the separate node gives
+        const float4 u = x2[r * (32 * NV4) + 32 * j + lane];
+        t = make_float4(__fadd_rn(t.x, u.x), __fadd_rn(t.y, u.y), __fadd_rn(t.z, u.z), __fadd_rn(t.w, u.w));
+      }
       v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
       sum += (t.x + t.y) + (t.z + t.w);
     }
@@ -1667,26 +1671,28 @@ __global__ void layer_norm_rows_reg_kernel(const float4* __restrict__ x, float4*
 
 // LayerNormalization over the last axis, one warp per row (nn/normalization.rs layer_norm_into):
 // mean = sum / n, var = sum((x - mean)^2) / n, inv_std = 1 / sqrt(var + eps), (x - mean) * inv_std * scale [+ bias].
-__global__ void layer_norm_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int64_t n, const float* __restrict__ scale,
-                                       const float* __restrict__ bias, float eps, uint32_t* minmax_keys) {
+__global__ void layer_norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ x2, float* __restrict__ y, int64_t rows, int64_t n,
+                                       const float* __restrict__ scale, const float* __restrict__ bias, float eps, uint32_t* minmax_keys) {
   const int lane = threadIdx.x & 31;
   float mn = INFINITY, mx = -INFINITY;  // extrema of what this thread writes (for a DynamicQuantizeLinear reader)
   const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
     const float* px = x + r * n;
+    const float* px2 = x2 ? x2 + r * n : nullptr;
+    auto at = [&](int64_t k) { return px2 ? __fadd_rn(px[k], px2[k]) : px[k]; };  // the Add in front of the normalisation
     float* py = y + r * n;
     float sum = 0.f;
-    for (int64_t k = lane; k < n; k += 32) sum += px[k];
+    for (int64_t k = lane; k < n; k += 32) sum += at(k);
     const float mean = __fdiv_rn(warp_sum(sum), (float)n);
     float vs = 0.f;
     for (int64_t k = lane; k < n; k += 32) {
-      const float d = __fsub_rn(px[k], mean);
+      const float d = __fsub_rn(at(k), mean);
       vs += __fmul_rn(d, d);
     }
     const float var = __fdiv_rn(warp_sum(vs), (float)n);
     const float inv_std = __frcp_rn(__fsqrt_rn(__fadd_rn(var, eps)));
     for (int64_t k = lane; k < n; k += 32) {
-      float v = __fmul_rn(__fmul_rn(__fsub_rn(px[k], mean), inv_std), scale[k]);
+      float v = __fmul_rn(__fmul_rn(__fsub_rn(at(k), mean), inv_std), scale[k]);
       if (bias) v = __fadd_rn(v, bias[k]);
       py[k] = v;
       mn = fminf(mn, v);
@@ -2191,18 +2197,18 @@ void softmax_rows(const float* x, float* y, int64_t rows, int64_t n, const float
 }
 
 void layer_norm_rows(const float* x, float* y, int64_t rows, int64_t n, const float* scale, const float* bias, float eps, cudaStream_t s,
-                     unsigned int* minmax_keys) {
+                     unsigned int* minmax_keys, const float* x2) {
   if (rows * n == 0) return;
-  if (n % 256 == 0 && n <= 1024 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)bias) & 15) == 0) {
+  if (n % 256 == 0 && n <= 1024 && (((uintptr_t)x | (uintptr_t)x2 | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)bias) & 15) == 0) {
     const int g = grid_for(rows * 32);
-    const float4 *x4 = (const float4*)x, *s4 = (const float4*)scale, *b4 = (const float4*)bias;
-    if (n == 256) layer_norm_rows_reg_kernel<2><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
-    else if (n == 512) layer_norm_rows_reg_kernel<4><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
-    else if (n == 768) layer_norm_rows_reg_kernel<6><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
-    else layer_norm_rows_reg_kernel<8><<<g, kThreads, 0, s>>>(x4, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    const float4 *x4 = (const float4*)x, *x24 = (const float4*)x2, *s4 = (const float4*)scale, *b4 = (const float4*)bias;
+    if (n == 256) layer_norm_rows_reg_kernel<2><<<g, kThreads, 0, s>>>(x4, x24, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    else if (n == 512) layer_norm_rows_reg_kernel<4><<<g, kThreads, 0, s>>>(x4, x24, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    else if (n == 768) layer_norm_rows_reg_kernel<6><<<g, kThreads, 0, s>>>(x4, x24, (float4*)y, rows, s4, b4, eps, minmax_keys);
+    else layer_norm_rows_reg_kernel<8><<<g, kThreads, 0, s>>>(x4, x24, (float4*)y, rows, s4, b4, eps, minmax_keys);
     return;
   }
-  layer_norm_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, y, rows, n, scale, bias, eps, minmax_keys);
+  layer_norm_rows_kernel<<<grid_for(rows * 32), kThreads, 0, s>>>(x, x2, y, rows, n, scale, bias, eps, minmax_keys);
 }
 
 void concat_into(const TensorRef& x, const TensorRef& y, int axis, int64_t offset, cudaStream_t s) {

@@ -523,6 +523,10 @@ class Planner {
   void emit_contraction(const NodeDef& n, Contraction& c);
 
   void finalize_lifetimes_and_arena();
+  struct LastAdd {
+    int step = -1, a = -1, b = -1, y = -1;
+  };
+  LastAdd last_add_;
   struct ChainLink {
     int step = -1, rows = 0, x_vi = -1, out_vi = -1;
     k::UmmaChainLayer layer;
@@ -999,7 +1003,8 @@ void Planner::plan_dynamic_quantize(const NodeDef& n) {
   // So can a tensor-core contraction that writes x as f32 lanes (its steps are still named "umma" here; the plan
   // is built when the arena is laid out and reads the value's keys then).
   if (!C.cfg().keep_intermediates && V(xi).alias_of < 0 && V(xi).producer >= 0 && V(xi).producer < (int)S.steps_.size() &&
-      (S.steps_[V(xi).producer].kernel == "layer_norm_rows" || (S.steps_[V(xi).producer].kernel == "umma" && S.steps_[V(xi).producer].family == 0)) &&
+      (S.steps_[V(xi).producer].kernel == "layer_norm_rows" || S.steps_[V(xi).producer].kernel == "add+layer_norm_rows" ||
+       (S.steps_[V(xi).producer].kernel == "umma" && S.steps_[V(xi).producer].family == 0)) &&
       V(xi).minmax_keys == nullptr) {
     V(xi).minmax_keys = scratch;
     have_minmax = true;
@@ -2259,6 +2264,11 @@ void Planner::plan_binary(const NodeDef& n, int ni) {
   int rt = feeds_contraction(out_name) ? 1 : 0;
   TensorRef ar{nullptr, av.dt, al, ad}, br{nullptr, bv.dt, bl, bd}, yr{nullptr, DT::F32, r == 4 ? ol : Layout::PLAIN, od};
   Step& st = add_step(n, relu_after ? "binary+relu" : "binary", 2, {ai, bi}, {yi});
+  // a plain Add of two f32 tensors of one shape in the logical order may be absorbed by a LayerNormalization that
+  // is its only reader (plan_layer_norm)
+  last_add_ = LastAdd{};
+  if (op == k::BIN_ADD && !relu_after && !rt && as == bs && (r != 4 || (order_free(av) && order_free(bv))) && av.dt == DT::F32 && bv.dt == DT::F32)
+    last_add_ = LastAdd{(int)S.steps_.size() - 1, ai, bi, yi};
   st.work = (double)av.bytes + (double)bv.bytes + (double)V(yi).bytes;
   st.launch = [this, ar, br, yr, ai, bi, yi, op, relu_after, rt](cudaStream_t s) {
     k::binary(bound(ar, ai), bound(br, bi), bound(yr, yi), op, relu_after, rt, s);
@@ -2907,11 +2917,27 @@ void Planner::plan_layer_norm(const NodeDef& n) {
   if (bias)
     dbias = (const float*)C.resident_form(in_name(n, 2), "raw_f32", bias->data.size() * 4, [bias](void* p) { std::memcpy(p, bias->data.data(), bias->data.size() * 4); },
                                           cacheable_const(in_name(n, 2)));
+  // The residual Add right in front, read by nothing else: the normalisation adds the two operands while it loads
+  // them (one rounded sum per lane, as the node gives) and the sum is never written.
+  int x2 = -1;
+  if (!C.cfg().keep_intermediates && last_add_.y == xi && last_add_.step == (int)S.steps_.size() - 1 && !graph_outputs_.count(xv.name)) {
+    auto it = consumers_.find(xv.name);
+    if (it != consumers_.end() && it->second.size() == 1) {
+      S.steps_.pop_back();
+      V(xi).producer = -1;
+      x2 = last_add_.b;
+      xi = last_add_.a;
+    }
+  }
+  last_add_ = LastAdd{};
   int yi = add_value(n.outputs[0], xv.shape, DT::F32, Layout::PLAIN);
-  Step& st = add_step(n, "layer_norm_rows", 2, {xi}, {yi});
-  st.work = 2.0 * (double)xv.bytes;
-  st.launch = [this, xi, yi, rows, len, dscale, dbias, eps](cudaStream_t s) {
-    k::layer_norm_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, dscale, dbias, eps, s, (unsigned int*)V(yi).minmax_keys);
+  std::vector<int> reads = {xi};
+  if (x2 >= 0) reads.push_back(x2);
+  Step& st = add_step(n, x2 >= 0 ? "add+layer_norm_rows" : "layer_norm_rows", 2, reads, {yi});
+  st.work = (x2 >= 0 ? 3.0 : 2.0) * (double)xv.bytes;
+  st.launch = [this, xi, x2, yi, rows, len, dscale, dbias, eps](cudaStream_t s) {
+    k::layer_norm_rows((const float*)V(xi).ptr, (float*)V(yi).ptr, rows, len, dscale, dbias, eps, s, (unsigned int*)V(yi).minmax_keys,
+                       x2 >= 0 ? (const float*)V(x2).ptr : nullptr);
     C.counters.glue_launches++;
     C.counters.kernel_launches++;
   };

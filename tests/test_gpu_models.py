@@ -154,6 +154,31 @@ def test_contraction_hands_its_extrema_to_the_next_dynamic_quantize_linear(rows,
     assert np.max(np.abs(got["yq"].astype(np.int32) - ref["yq"].astype(np.int32))) <= 1  # the oracle's Gelu may differ in the last place
 
 
+@pytest.mark.parametrize("shape", [(5, 37, 768), (64, 96), (3, 130, 1024)])
+def test_layer_norm_absorbs_the_residual_add_in_front_of_it(shape):
+    """Add -> LayerNormalization with the sum read by nothing else is one kernel (the sum is never written); the
+    lanes are those of the two separate kernels bit for bit (one rounded sum per lane, then the same arithmetic)."""
+    from oxionnx_b200.graph import Graph, Node
+    rng = np.random.default_rng(41 + shape[-1])
+    w = {"g": rng.uniform(0.5, 1.5, shape[-1]).astype(np.float32), "b": rng.standard_normal(shape[-1]).astype(np.float32)}
+    nodes = [Node("Add", "res", ["x", "y"], ["sum"], {}), Node("LayerNormalization", "ln", ["sum", "g", "b"], ["out"], {"axis": -1, "epsilon": 1e-12}),
+             Node("Mul", "use_y", ["y", "out"], ["out2"], {})]
+    graph = Graph(nodes=nodes, input_names=["x", "y"], output_names=["out", "out2"])
+    feeds = {"x": (rng.standard_normal(shape) * 3).astype(np.float32), "y": (rng.standard_normal(shape) + 0.5).astype(np.float32)}
+    fused = Session.builder().build_from_graph(graph, w)
+    got = fused.run(feeds)
+    kernels = [s["kernel"] for s in fused.steps()]
+    assert "add+layer_norm_rows" in kernels and kernels.count("binary") == 1, kernels  # the Mul stays; the Add is gone
+    fused.close()
+    apart = Session.builder().with_keep_intermediates(True).build_from_graph(graph, w)
+    want = apart.run(feeds)
+    assert "layer_norm_rows" in [s["kernel"] for s in apart.steps()]
+    apart.close()
+    assert np.array_equal(got["out"], want["out"]) and np.array_equal(got["out2"], want["out2"])
+    ref = oracle.run_graph(graph, w, feeds)
+    assert np.max(np.abs(got["out"] - ref["out"])) <= 1e-4
+
+
 def test_resnet_f32_small_per_node_and_final():
     graph, weights, feeds, _ = models.build_resnet50_f32(batch=3, image=64, base=16, classes=40)
     sess, out, ref = run_both(graph, weights, feeds(3))
