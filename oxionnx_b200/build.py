@@ -28,6 +28,7 @@ SOURCES = {
     "umma_f16.cu": [f for f in COMMON if f != "--fmad=false"],
     "umma_probe.cu": [f for f in COMMON if f != "--fmad=false"],
     "umma_chain.cu": [f for f in COMMON if f != "--fmad=false"],
+    "umma_attention.cu": [f for f in COMMON if f != "--fmad=false"],
     "runtime.cpp": COMMON,
     "planner.cpp": COMMON,
     "abi.cpp": COMMON,

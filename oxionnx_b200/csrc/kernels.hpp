@@ -305,6 +305,29 @@ void umma_chain_reset_after_error(UmmaChain* c);
 bool umma_chain_launch(const UmmaChain* c, int* err_flag, const float* head_x, cudaStream_t s);
 const char* umma_chain_desc(const UmmaChain* c);
 
+// One attention layer's f32 side as one tensor-core kernel (scores, scale + mask + softmax, context) for sequences
+// of 128 positions and heads of 64 lanes.  q, k: [B * S, H * D] f32 matrices whose heads are column windows;
+// vt: V transposed per head, [B * H * D, S]; out: [o_rows, o_cols] f32 where head (b, h) starts at row
+// b * o_rb + h * o_rh and column h * o_ch; scale: one device lane or null; mask: [B][S] additive lanes or null.
+struct FusedAttention {
+  const float* q = nullptr;
+  const float* k = nullptr;
+  const float* vt = nullptr;
+  float* out = nullptr;
+  int64_t o_rows = 0, o_cols = 0;
+  int o_rb = 0, o_rh = 0, o_ch = 0;
+  int B = 0, H = 0, S = 0, D = 0;
+  const float* scale = nullptr;
+  const float* mask = nullptr;
+  int round_probs = 1;                  // the probabilities feed a TF32 product
+  unsigned int* minmax_keys = nullptr;  // as Epilogue::minmax_keys, for the context
+};
+struct UmmaAttentionPlan;
+UmmaAttentionPlan* umma_attention_create(const FusedAttention& a, std::string* why);
+void umma_attention_destroy(UmmaAttentionPlan* p);
+void umma_attention_launch(const UmmaAttentionPlan* p, int* err_flag, cudaStream_t s);
+const char* umma_attention_desc(const UmmaAttentionPlan* p);
+
 // Packed weight size helpers for the tensor-core path: weights are laid out [OC][R*S*Cpad]
 // (K-major rows), Cpad = C rounded up to the channel block.
 int umma_channel_block(int C, int kind);  // 0 when C is not eligible

@@ -489,6 +489,7 @@ class Planner {
   bool try_plan_attention_product(const NodeDef& n, int ai, int bi);
   void plan_softmax(const NodeDef& n);
   bool try_plan_scaled_masked_softmax(const NodeDef& n);
+  bool try_plan_fused_attention(const NodeDef& n, int qi, int ki);
   void plan_layer_norm(const NodeDef& n);
   void plan_alias(const NodeDef& n);
   bool try_plan_residual_chain(const NodeDef& n, int ni);
@@ -2739,6 +2740,7 @@ bool Planner::try_plan_attention_product(const NodeDef& n, int ai, int bi) {
   int out_vi = -1;
   std::string label;
   if (a_lazy && la->second.kind == 0 && hb.kind == 1 && la->second.B == B && la->second.S == Sq && la->second.H == H && la->second.D == D) {
+    if (try_plan_fused_attention(n, ai, bi)) return true;
     // scores
     g.M = (int)Sq, g.N = (int)Sq, g.K = (int)D;
     g.a_rows = B * Sq, g.a_cols = H * D, g.a_rb = (int)Sq, g.a_rh = 0, g.a_ch = (int)D;
@@ -2808,6 +2810,116 @@ bool Planner::try_plan_attention_product(const NodeDef& n, int ai, int bi) {
     int* err = S.err_flag_;
     me.launch = [this, plan, err](cudaStream_t s) {
       k::umma_launch(plan, err, s);
+      C.counters.umma_launches++;
+      C.counters.kernel_launches++;
+    };
+  };
+  return true;
+}
+
+// MatMul(Q heads, K heads^T) -> Mul(scalar) -> Add(mask[B,1,1,S]) -> Softmax -> MatMul(., V heads) [-> head merge] for
+// sequences of 128 positions and heads of 64 lanes, none of the intermediates read by anything else: one kernel
+// (umma_attention.cu).  The five or seven nodes are marked done; V is transposed per head first, as for the
+// separate context product.
+bool Planner::try_plan_fused_attention(const NodeDef& n, int qi, int ki) {
+  if (C.cfg().keep_intermediates || C.cfg().kernel_path != 0 || !k::umma_available()) return false;
+  const LazyHeads hq = lazy_heads_.find(qi)->second, hk = lazy_heads_.find(ki)->second;
+  const int64_t B = hq.B, Sq = hq.S, H = hq.H, D = hq.D;
+  if (Sq != 128 || D != 64 || B * H > 0x3fffffffLL) return false;
+  auto only_user = [&](const std::string& name, const char* opn) -> int {
+    if (graph_outputs_.count(name)) return -1;
+    auto it = consumers_.find(name);
+    if (it == consumers_.end() || it->second.size() != 1) return -1;
+    const int ni2 = it->second[0].first;
+    return (!skipped_[ni2] && nodes_[ni2].op == opn) ? ni2 : -1;
+  };
+  // Mul by a scalar initializer
+  const int mul_i = only_user(n.outputs[0], "Mul");
+  if (mul_i < 0 || nodes_[mul_i].inputs.size() != 2 || !nodes_[mul_i].attrs.names().empty()) return false;
+  const NodeDef& mul = nodes_[mul_i];
+  const int s_slot = mul.inputs[0] == n.outputs[0] ? 1 : 0;
+  const HostTensor* sc = const_of(mul.inputs[s_slot]);
+  if (!sc || sc->data.size() != 1 || S.index_.count(mul.inputs[s_slot])) return false;
+  // Add of a mask [B,1,1,S]
+  const int add_i = only_user(mul.outputs[0], "Add");
+  if (add_i < 0 || nodes_[add_i].inputs.size() != 2) return false;
+  const NodeDef& add = nodes_[add_i];
+  const std::string& mask_name = add.inputs[0] == mul.outputs[0] ? add.inputs[1] : add.inputs[0];
+  auto mit = S.index_.find(mask_name);
+  if (mit == S.index_.end()) return false;
+  const int mi = mit->second;
+  if (V(mi).shape != std::vector<int64_t>{B, 1, 1, Sq} || V(mi).dt != DT::F32) return false;
+  // Softmax over the last axis
+  const int sm_i = only_user(add.outputs[0], "Softmax");
+  if (sm_i < 0) return false;
+  int64_t axis = nodes_[sm_i].attrs.i("axis", -1);
+  if (axis < 0) axis += 4;
+  if (axis != 3) return false;
+  // MatMul(probabilities, V heads)
+  const int av_i = only_user(nodes_[sm_i].outputs[0], "MatMul");
+  if (av_i < 0 || nodes_[av_i].inputs.size() != 2 || nodes_[av_i].inputs[0] != nodes_[sm_i].outputs[0]) return false;
+  auto vit = S.index_.find(nodes_[av_i].inputs[1]);
+  if (vit == S.index_.end()) return false;
+  auto lv = lazy_heads_.find(vit->second);
+  if (lv == lazy_heads_.end() || lv->second.materialised || lv->second.kind != 0) return false;
+  const LazyHeads hv = lv->second;
+  if (hv.B != B || hv.S != Sq || hv.H != H || hv.D != D) return false;
+  // a head merge Transpose(0,2,1,3) -> Reshape([B*S, H*D]) behind the product is absorbed into the store
+  const NodeDef& av = nodes_[av_i];
+  std::string out_name = av.outputs[0];
+  std::vector<int64_t> oshape = {B, H, Sq, D};
+  int o_rb = (int)(H * Sq), o_rh = (int)Sq, o_ch = 0;
+  int64_t o_rows = B * H * Sq, o_cols = D;
+  int t_i = only_user(out_name, "Transpose"), r_i = -1;
+  if (t_i >= 0 && nodes_[t_i].attrs.int_list("perm") == std::vector<int64_t>{0, 2, 1, 3}) {
+    r_i = only_user(nodes_[t_i].outputs[0], "Reshape");
+    const HostTensor* sh = r_i >= 0 ? const_in(nodes_[r_i], 1) : nullptr;
+    if (sh && sh->data.size() == 2 && (int64_t)sh->data[0] == B * Sq && (int64_t)sh->data[1] == H * D) {
+      out_name = nodes_[r_i].outputs[0];
+      oshape = {B * Sq, H * D};
+      o_rows = B * Sq, o_cols = H * D, o_rb = (int)Sq, o_rh = 0, o_ch = (int)D;
+    } else {
+      t_i = r_i = -1;
+    }
+  } else {
+    t_i = -1;
+  }
+  // from here on the plan is committed
+  const float* dscale = (const float*)C.resident_form(mul.inputs[s_slot], "raw_f32", 4, [sc](void* p) { std::memcpy(p, sc->data.data(), 4); },
+                                                      cacheable_const(mul.inputs[s_slot]));
+  const int vt = add_value(V(hv.src_vi).name + "@heads_t", {B, H, D, Sq}, DT::F32, Layout::PLAIN);
+  emit_transpose(nodes_[hv.node], hv.src_vi, {0, 2, 3, 1}, vt);
+  skipped_[mul_i] = skipped_[add_i] = skipped_[sm_i] = skipped_[av_i] = 1;
+  if (t_i >= 0) skipped_[t_i] = skipped_[r_i] = 1;
+  lazy_heads_.find(qi)->second.materialised = lazy_heads_.find(ki)->second.materialised = lv->second.materialised = true;
+  const int out_vi = add_value(out_name, oshape, DT::F32, Layout::PLAIN);
+  const int q_root = hq.root_vi, k_root = hk.root_vi;
+  Step& st = add_step(av, "umma", 0, {q_root, k_root, vt, mi}, {out_vi});
+  st.work = 4.0 * (double)B * H * Sq * Sq * D;
+  st.work_is_bytes = false;
+  const int step_index = (int)S.steps_.size() - 1;
+  const std::string av_name = av.name;
+  st.finalize = [this, step_index, q_root, k_root, vt, mi, out_vi, dscale, B, H, Sq, D, o_rows, o_cols, o_rb, o_rh, o_ch, av_name]() {
+    k::FusedAttention fa;
+    fa.q = (const float*)V(q_root).ptr;
+    fa.k = (const float*)V(k_root).ptr;
+    fa.vt = (const float*)V(vt).ptr;
+    fa.out = (float*)V(out_vi).ptr;
+    fa.o_rows = o_rows, fa.o_cols = o_cols, fa.o_rb = o_rb, fa.o_rh = o_rh, fa.o_ch = o_ch;
+    fa.B = (int)B, fa.H = (int)H, fa.S = (int)Sq, fa.D = (int)D;
+    fa.scale = dscale;
+    fa.mask = (const float*)V(mi).ptr;
+    fa.round_probs = 1;
+    fa.minmax_keys = (unsigned int*)V(out_vi).minmax_keys;
+    std::string why2;
+    k::UmmaAttentionPlan* plan = k::umma_attention_create(fa, &why2);
+    if (!plan) OXB_FAIL("MatMul '%s': fused attention plan rejected: %s", av_name.c_str(), why2.c_str());
+    S.umma_attentions_.push_back(plan);
+    Step& me = S.steps_[step_index];
+    me.kernel = k::umma_attention_desc(plan);
+    int* err = S.err_flag_;
+    me.launch = [this, plan, err](cudaStream_t s) {
+      k::umma_attention_launch(plan, err, s);
       C.counters.umma_launches++;
       C.counters.kernel_launches++;
     };

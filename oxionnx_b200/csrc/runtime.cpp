@@ -139,6 +139,7 @@ Session::~Session() {
   cudaStreamSynchronize(ctx_->stream());
   for (auto* p : umma_plans_) k::umma_plan_destroy(p);
   for (auto* c : umma_chains_) k::umma_chain_destroy(c);
+  for (auto* a : umma_attentions_) k::umma_attention_destroy(a);
   for (auto& s : steps_) {
     if (s.ev0) cudaEventDestroy(s.ev0);
     if (s.ev1) cudaEventDestroy(s.ev1);

@@ -168,6 +168,7 @@ class Session {
   std::vector<DeviceBuffer> owned_;  // staging + parameter buffers
   std::vector<k::UmmaPlan*> umma_plans_;
   std::vector<k::UmmaChain*> umma_chains_;
+  std::vector<k::UmmaAttentionPlan*> umma_attentions_;
   size_t n_slots_ = 0;
   int* err_flag_ = nullptr;
   std::map<std::string, std::pair<void*, std::pair<DT, Layout>>> external_bind_;

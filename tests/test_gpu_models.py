@@ -442,6 +442,65 @@ def test_bert_attention_on_the_tensor_cores():
     slow.close()
 
 
+def _round_tf32(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x1000) & 0xFFFFE000).astype(np.uint32).view(np.float32)  # round to nearest, ties away, as cvt.rna
+
+
+@pytest.mark.parametrize("batch,heads,merge,masked", [(3, 2, True, True), (2, 5, False, True), (1, 3, True, False)])
+def test_attention_scores_softmax_and_context_in_one_kernel(batch, heads, merge, masked):
+    """MatMul(Q, K^T) -> Mul(scale) -> Add(mask) -> Softmax -> MatMul(., V) [-> head merge] over 128 positions and heads of
+    64 lanes is one tensor-core kernel whose scores and probabilities stay on the SM.  Its context equals that of the
+    separate kernels (a session that keeps intermediates runs those) to within what one TF32 rounding of a probability
+    can move, and the oracle's within the TF32 tolerance; rows that are masked out carry no weight."""
+    from oxionnx_b200.graph import Graph, Node
+    S_, D = 128, 64
+    rng = np.random.default_rng(5 + batch * 10 + heads)
+    hd = heads * D
+    w = {"heads_shape": np.float32([batch, S_, heads, D]), "rows_shape": np.float32([batch * S_, hd]), "att_scale": np.float32([1.0 / 8.0])}
+    nodes = []
+    def split(name, perm):
+        nodes.append(Node("Reshape", f"{name}_split", [name, "heads_shape"], [f"{name}4r"], {}))
+        nodes.append(Node("Transpose", f"{name}_t", [f"{name}4r"], [f"{name}4"], {"perm": perm}))
+        return f"{name}4"
+    # a projection in front of each operand makes it a device value, as in an encoder layer
+    for name in ("q", "k", "v"):
+        w[f"{name}_w"] = _round_tf32(rng.standard_normal((hd, hd)) / np.sqrt(hd))
+        nodes.append(Node("MatMul", f"{name}_proj", [f"{name}_in", f"{name}_w"], [name], {}))
+    q4, k4, v4 = split("q", [0, 2, 1, 3]), split("k", [0, 2, 3, 1]), split("v", [0, 2, 1, 3])
+    nodes.append(Node("MatMul", "qk", [q4, k4], ["scores"], {}))
+    nodes.append(Node("Mul", "scale", ["scores", "att_scale"], ["scaled"], {}))
+    nodes.append(Node("Add", "mask_add", ["scaled", "mask"], ["masked"], {}))
+    nodes.append(Node("Softmax", "softmax", ["masked"], ["probs"], {"axis": -1}))
+    nodes.append(Node("MatMul", "av", ["probs", v4], ["ctx4"], {}))
+    out = "ctx4"
+    if merge:
+        nodes.append(Node("Transpose", "merge_t", ["ctx4"], ["ctx_t"], {"perm": [0, 2, 1, 3]}))
+        nodes.append(Node("Reshape", "merge", ["ctx_t", "rows_shape"], ["ctx"], {}))
+        out = "ctx"
+    graph = Graph(nodes=nodes, input_names=["q_in", "k_in", "v_in", "mask"], output_names=[out])
+    mask = np.zeros((batch, 1, 1, S_), np.float32)
+    if masked:
+        mask[0, :, :, 100:] = -10000.0
+        mask[-1, :, :, ::3] = -10000.0
+    feeds = {n: _round_tf32(rng.standard_normal((batch * S_, hd)) * 1.5) for n in ("q_in", "k_in", "v_in")}
+    feeds["mask"] = mask
+    fused = Session.builder().build_from_graph(graph, w)
+    got = fused.run(feeds)[out]
+    kernels = [s["kernel"] for s in fused.steps()]
+    assert sum(k.startswith("umma_attention") for k in kernels) == 1 and not any(k.startswith("softmax_rows") or "batched" in k for k in kernels), kernels
+    fused.close()
+    apart = Session.builder().with_keep_intermediates(True).build_from_graph(graph, w)
+    want = apart.run(feeds)[out]
+    assert not any(s["kernel"].startswith("umma_attention") for s in apart.steps())
+    apart.close()
+    ref = oracle.run_graph(graph, w, feeds)[out]
+    top = float(np.max(np.abs(ref)))
+    assert got.shape == ref.shape
+    assert float(np.max(np.abs(got - want))) <= 1e-3 * top, float(np.max(np.abs(got - want))) / top
+    assert float(np.max(np.abs(got - ref))) <= 4e-3 * top, float(np.max(np.abs(got - ref))) / top
+
+
 def test_pipelined_runs_match_synchronous_runs():
     """oxb200_run_submit / oxb200_run_collect: three different batches with two in flight give, in order, exactly
     what the synchronous call gives for each; the same when the input's address is built into a tensor map (one
