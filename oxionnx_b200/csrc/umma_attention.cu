@@ -2,15 +2,16 @@
 // mask) over the last axis, context = probabilities . V, per (batch, head), for sequences of 128 positions and
 // heads of 64 lanes (TF32 operands, f32 accumulation, as the two separate batched products use).
 //
-// The scores never leave the SM: the first product accumulates a 128 x 128 tile in TMEM, each of the four
-// accumulator warps' threads reads one row of it into registers, applies the scalar product and the additive mask
-// (each rounded as the separate Mul and Add nodes round), the row softmax (max, exp(v - max), a sequential f32 sum,
-// one reciprocal, one product per lane, nn/normalization.rs softmax_into) and the TF32 rounding of lanes that feed
+// The scores never leave the SM: the first product accumulates a 128 x 128 tile in TMEM, the accumulator warps'
+// threads read it into registers (32 scores of a row each), applies the scalar product and the additive mask
+// (each rounded as the separate Mul and Add nodes round), the row softmax (max, exp(v - max), an f32 sum, one
+// reciprocal, one product per lane, nn/normalization.rs softmax_into) and the TF32 rounding of lanes that feed
 // a contraction, and writes the row into shared memory in the 128-byte-swizzled K-major layout a TMA load would
 // have left; the second product reads it from there.  Q and K are column windows of their [B * S, H * D]
-// matrices, V arrives transposed per head ([B * H * D, S]), the context is written straight into its (possibly
-// head-merged) matrix.  One warp loads and issues, four warps do the rows; a CTA walks the (batch, head) items
-// and loads the next item's operands as soon as the current product has read them.  Every wait is bounded.
+// matrices, V arrives transposed per head ([B * H * D, S]), the context is stored by TMA straight into its (possibly
+// head-merged) matrix.  One warp loads and issues; sixteen warps do the rows, four threads per row (32 scores each,
+// the row's maximum and sum meet in shared memory behind two mbarriers); a CTA walks the (batch, head) items and
+// loads the next item's operands as soon as the current product has read them.  Every wait is bounded.
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
@@ -25,17 +26,17 @@ namespace k {
 namespace umma {
 
 constexpr int ATT_S = 128, ATT_D = 64;
-constexpr int ATT_THREADS = 160;  // warps 0..3: accumulator rows 32w..32w+31; warp 4: TMA and MMA issue
-constexpr uint32_t ATT_Q_OFF = 0, ATT_K_OFF = 32768, ATT_V_OFF = 65536, ATT_P_OFF = 98304, ATT_SMEM = 98304 + 65536 + 1024;
+constexpr int ATT_ROW_WARPS = 16;                      // warp w: accumulator rows 32 (w & 3) .. + 31, score columns 32 (w >> 2) .. + 31
+constexpr int ATT_THREADS = 32 * ATT_ROW_WARPS + 32;   // plus one warp that loads and issues
+constexpr uint32_t ATT_Q_OFF = 0, ATT_K_OFF = 32768, ATT_V_OFF = 65536, ATT_P_OFF = 98304, ATT_O_OFF = 163840;
+constexpr uint32_t ATT_SMEM = 163840 + 32768 + 1024;   // Q, K, V^T, probabilities, context staging, alignment slack
 
 struct alignas(64) AttnParams {
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;
   int items, heads;
   uint32_t idesc_s, idesc_o;
   const float* scale;  // one device lane, or null
   const float* mask;   // [batch][128] additive, or null
-  float* out;
-  long long o_pitch;  // floats between output rows
   int o_rb, o_rh, o_ch;
   int round_probs;
   unsigned int* minmax_keys;
@@ -44,7 +45,8 @@ struct alignas(64) AttnParams {
 
 __global__ void __launch_bounds__(ATT_THREADS, 1) umma_attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_qk, bar_v, bar_s, bar_p, bar_o;
+  __shared__ __align__(8) uint64_t bar_qk, bar_v, bar_s, bar_p, bar_o, bar_max, bar_sum;
+  __shared__ float row_max[4][ATT_S], row_sum[4][ATT_S];  // per column block of 32 scores
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   const int warp = (int)(threadIdx.x >> 5), lane = (int)(threadIdx.x & 31);
@@ -56,12 +58,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) umma_attention_kernel(const __
     mbar_init(smem_u32(&bar_qk), 1);
     mbar_init(smem_u32(&bar_v), 1);
     mbar_init(smem_u32(&bar_s), 1);
-    mbar_init(smem_u32(&bar_p), 128);
+    mbar_init(smem_u32(&bar_p), 32 * ATT_ROW_WARPS);
     mbar_init(smem_u32(&bar_o), 1);
+    mbar_init(smem_u32(&bar_max), 32 * ATT_ROW_WARPS);
+    mbar_init(smem_u32(&bar_sum), 32 * ATT_ROW_WARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == ATT_ROW_WARPS) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(256) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -76,7 +80,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) umma_attention_kernel(const __
     }
   };
 
-  if (warp == 4) {
+  if (warp == ATT_ROW_WARPS) {
     // ---------------- loads and MMA issue ----------------
     auto load_qk = [&](int item) {
       const int b = item / p.heads, h = item - b * p.heads;
@@ -143,10 +147,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) umma_attention_kernel(const __
       __syncwarp();
     }
   } else {
-    // ---------------- one row of the scores per thread ----------------
-    const int row = warp * 32 + lane;
+    // ---------------- 32 scores of one row per thread; four threads share a row through shared memory ----------------
+    const int quarter = warp & 3, cb = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float sc = p.scale ? __ldg(p.scale) : 1.f;
     float seen_min = INFINITY, seen_max = -INFINITY;
+    // context staging of this warp (the warps of column blocks 0 and 1 write the context): 32 rows x 128 bytes
+    const uint32_t stage = base + ATT_O_OFF + (uint32_t)((cb & 1) * 4 + quarter) * 4096u;
+    uint8_t* stage_ptr = base_ptr + ATT_O_OFF + ((cb & 1) * 4 + quarter) * 4096;
     uint32_t phase = 0;
     for (int item = (int)blockIdx.x; item < p.items; item += (int)gridDim.x, phase ^= 1u) {
       const int b = item / p.heads, h = item - b * p.heads;
@@ -156,23 +165,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) umma_attention_kernel(const __
         break;
       }
       tc_fence_after();
-      float v[ATT_S];
+      float v[32];
       {
         uint32_t r[32];
-        const uint32_t taddr = tmem_s + ((uint32_t)(warp * 32) << 16);
+        tmem_ld32_nowait(tmem_s + lane_base + (uint32_t)cb * 32u, r);
+        tmem_ld_wait_for(r);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld32_nowait(taddr + (uint32_t)c * 32u, r);
-          tmem_ld_wait_for(r);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[32 * c + j] = __uint_as_float(r[j]);
-        }
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
       }
       tc_fence_before();
-      const float4* pm = p.mask ? reinterpret_cast<const float4*>(p.mask + (size_t)b * ATT_S) : nullptr;
+      const float4* pm = p.mask ? reinterpret_cast<const float4*>(p.mask + (size_t)b * ATT_S + cb * 32) : nullptr;
       float mx = -INFINITY;
 #pragma unroll
-      for (int j4 = 0; j4 < ATT_S / 4; ++j4) {
+      for (int j4 = 0; j4 < 8; ++j4) {
         float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
         if (pm) m = __ldg(pm + j4);
         const float mm[4] = {m.x, m.y, m.z, m.w};
@@ -185,56 +190,78 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) umma_attention_kernel(const __
           mx = fmaxf(mx, x);
         }
       }
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < ATT_S; ++j) {
-        v[j] = expf(__fsub_rn(v[j], mx));
-        sum = __fadd_rn(sum, v[j]);
+      row_max[cb][row] = mx;
+      mbar_arrive(smem_u32(&bar_max));
+      got = mbar_wait(smem_u32(&bar_max), phase, abortp);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) give_up(36);
+        break;
       }
-      const float inv = __frcp_rn(sum);
-      // the row, as four K blocks of 32 lanes: 16-byte piece c of row r of a block sits at r * 128 + ((c ^ (r & 7)) << 4)
-      uint8_t* prow = base_ptr + ATT_P_OFF + row * 128;
+      mx = fmaxf(fmaxf(row_max[0][row], row_max[1][row]), fmaxf(row_max[2][row], row_max[3][row]));
+      // exp through ex2.approx (two units in the last place, far inside the softmax tolerance of 1e-5)
+      float part[2] = {0.f, 0.f};
 #pragma unroll
-      for (int j4 = 0; j4 < ATT_S / 4; ++j4) {
+      for (int j = 0; j < 32; ++j) {
+        v[j] = __expf(__fsub_rn(v[j], mx));
+        part[j & 1] = __fadd_rn(part[j & 1], v[j]);
+      }
+      row_sum[cb][row] = __fadd_rn(part[0], part[1]);
+      mbar_arrive(smem_u32(&bar_sum));
+      got = mbar_wait(smem_u32(&bar_sum), phase, abortp);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) give_up(37);
+        break;
+      }
+      const float inv = __frcp_rn(__fadd_rn(__fadd_rn(row_sum[0][row], row_sum[1][row]), __fadd_rn(row_sum[2][row], row_sum[3][row])));
+      // this thread's 32 lanes are K block `cb` of the row: 16-byte piece c sits at row * 128 + ((c ^ (row & 7)) << 4)
+      uint8_t* prow = base_ptr + ATT_P_OFF + cb * 16384 + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
         float o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          o[e] = __fmul_rn(v[4 * j4 + e], inv);
+          o[e] = __fmul_rn(v[4 * c + e], inv);
           if (p.round_probs) o[e] = round_tf32(o[e]);
         }
-        const int kb = j4 >> 3, c = j4 & 7;
-        *reinterpret_cast<float4*>(prow + kb * 16384 + ((c ^ (row & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(prow + ((c ^ (row & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the second product reads the rows through the async proxy
       mbar_arrive(smem_u32(&bar_p));
       got = mbar_wait(smem_u32(&bar_o), phase, abortp);
       if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) give_up(36);
+        if (lane == 0) give_up(38);
         break;
       }
-      tc_fence_after();
-      float* orow = p.out + ((size_t)(b * p.o_rb + h * p.o_rh) + row) * (size_t)p.o_pitch + (size_t)h * p.o_ch;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      if (cb < 2) {
+        // 32 context lanes of the row: staged (swizzled as the store's tensor map expects) and stored by TMA
+        tc_fence_after();
         uint32_t r[32];
-        tmem_ld32_nowait(tmem_o + ((uint32_t)(warp * 32) << 16) + (uint32_t)c * 32u, r);
+        tmem_ld32_nowait(tmem_o + lane_base + (uint32_t)cb * 32u, r);
         tmem_ld_wait_for(r);
+        tc_fence_before();
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous store has read the staging rows
+        __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          *reinterpret_cast<float4*>(orow + 32 * c + j) =
-              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        for (int c = 0; c < 8; ++c) {
+          *reinterpret_cast<uint4*>(stage_ptr + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
           if (p.minmax_keys) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              seen_min = fminf(seen_min, __uint_as_float(r[j + e]));
-              seen_max = fmaxf(seen_max, __uint_as_float(r[j + e]));
+              seen_min = fminf(seen_min, __uint_as_float(r[4 * c + e]));
+              seen_max = fmaxf(seen_max, __uint_as_float(r[4 * c + e]));
             }
           }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&p.tmO, stage, h * p.o_ch + cb * 32, b * p.o_rb + h * p.o_rh + quarter * 32);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
       }
-      tc_fence_before();
     }
-    if (p.minmax_keys) {
+    if (cb < 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (p.minmax_keys && cb < 2) {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) {
         seen_min = fminf(seen_min, __shfl_xor_sync(0xffffffffu, seen_min, off));
@@ -258,7 +285,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) umma_attention_kernel(const __
     }
   }
   __syncthreads();
-  if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"(256) : "memory");
+  if (warp == ATT_ROW_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"(256) : "memory");
 }
 
 }  // namespace umma
@@ -328,8 +355,18 @@ UmmaAttentionPlan* umma_attention_create(const FusedAttention& a, std::string* w
   ap.idesc_o = tf32_idesc(ATT_D, 128);
   ap.scale = a.scale;
   ap.mask = a.mask;
-  ap.out = a.out;
-  ap.o_pitch = a.o_cols;
+  {
+    // the context goes out by TMA: 32 rows x 32 lanes per store, out of 128-byte-swizzled staging rows
+    cuuint64_t gdim[2] = {(cuuint64_t)a.o_cols, (cuuint64_t)a.o_rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)a.o_cols * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&ap.tmO, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a.out, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      delete pl;
+      return no("output tensor map rejected by the driver");
+    }
+  }
   ap.o_rb = a.o_rb, ap.o_rh = a.o_rh, ap.o_ch = a.o_ch;
   ap.round_probs = a.round_probs;
   ap.minmax_keys = a.minmax_keys;
