@@ -333,6 +333,7 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
     conv_algo_bytes = 0.0
     conv_layers = []  # (ops, algorithmic bytes) of every contraction launch of one step: the layer-wise bound below
     slowest = {}
+    umma_kernels = set()
     for _ in range(args.steps):
         flush_l2()
         prof_ms += sess.run_resident(1)
@@ -340,6 +341,10 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
             if s["ms"] < 0:
                 continue
             if s["kernel"].startswith("umma"):
+                fam0 = s["kernel"].split()[0]
+                umma_kernels.add("umma_chain_kernel (cooperative tcgen05 chain of quantised linears)" if fam0 == "umma_i8_chain" else
+                                 ("umma_attention_kernel (tcgen05 scores + softmax + context)" if fam0 == "umma_attention" else
+                                  "umma_conv_kernel (tcgen05 implicit GEMM)"))
                 conv_ms += s["ms"]
                 conv_ops += s["work"]
                 conv_launches += 1
@@ -449,7 +454,7 @@ def measure(args, key, batch, local_rank, world, dist, torch, lib, flush_l2, bar
                       "rule": "sum over the contraction launches of max(ops / tensor peak, algorithmic bytes / measured copy bandwidth)"},
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s" if kind == "i8" else "TFLOP/s",
         "frac": achieved / peak if peak else None, "traffic": traffic, "traffic_note": traffic_note,
-        "kernel": "umma_conv_kernel (tcgen05 implicit GEMM)", "launches_per_step": conv_launches // max(args.steps, 1),
+        "kernel": " + ".join(sorted(umma_kernels)) or "umma_conv_kernel (tcgen05 implicit GEMM)", "launches_per_step": conv_launches // max(args.steps, 1),
         "avg_launch_ms": conv_ms / max(conv_launches, 1), "share_of_step": conv_ms / prof_ms if prof_ms > 0 else None,
         "timed_in": "a second pass of the same K steps with a CUDA-event pair around every kernel (ms_per_step %.3f there)" % (prof_ms / max(args.steps, 1)),
         "peak_basis": f"{factor} x bf16_tflops_sustained of {peaks['source']} ({peaks['bf16_sustained']})",
